@@ -1,0 +1,161 @@
+/*
+ * zkb200 — C ABI of the B200 (sm_100a) proving backend for the Circle-STARK operator traits.
+ *
+ * One entry point per backend operator of the reference's vendored STARK library. Each comment
+ * names the reference interface the function stands in for, by path inside the reference project
+ * (STWO = nitroo/crates/stwo/src). A Rust `Backend` type binds these with `extern "C"`.
+ *
+ * Conventions
+ *  - Every function returns a status: ZKB_OK (0) or a negative ZKB_E* code. Nothing aborts or
+ *    exits the process. zkb_last_error() gives the message of the last failure on a context.
+ *  - M31 values are uint32_t in [0, 2^31 - 1). A "secure column" is four device arrays, one per
+ *    QM31 coordinate (STWO/prover/secure_column.rs:13-15). GKR multilinear columns are device
+ *    arrays of QM31 stored as 4 consecutive uint32_t (as the reference's SecureFieldVec).
+ *    A hash column is 8 uint32_t (32 little-endian bytes) per node.
+ *  - Pointers are DEVICE pointers unless the parameter name starts with h_. Arrays of column
+ *    pointers (`cols`, `coeffs`, `out` of the batched calls, the `[4]` coordinate arrays) are host
+ *    arrays whose entries are device pointers.
+ *  - Work is enqueued on the context's stream and the call returns; calls that write to h_
+ *    outputs synchronise that stream before returning.
+ *  - Buffers are owned by whoever allocated them. The library frees only what zkb_malloc gave out
+ *    and only in zkb_free / zkb_destroy.
+ */
+#ifndef ZKB200_H
+#define ZKB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ZKB_OK 0
+#define ZKB_EINVAL (-1)   /* bad argument (null pointer, size out of range, ...) */
+#define ZKB_ENOMEM (-2)   /* device or host allocation failed */
+#define ZKB_ECUDA (-3)    /* a CUDA call failed; see zkb_last_error */
+#define ZKB_ETIMEOUT (-4) /* a bounded device-side wait ran out */
+#define ZKB_ENCCL (-5)    /* a collective failed */
+
+typedef struct zkb_ctx zkb_ctx;
+
+/* ---- context ------------------------------------------------------------------------------
+ * The reference keeps CUDA state process-global (STWO/stwo_cuda/mod.rs:25-43); here it is an
+ * explicit handle. `max_log_size` is the largest circle-domain log size any later call will use
+ * (the twiddle tower is built once, for Coset::half_odds(max_log_size - 1), replacing
+ * PolyOps::precompute_twiddles, STWO/prover/poly/circle/ops.rs:123 and
+ * STWO/prover/backend/cpu/circle.rs:230-291). */
+int zkb_init(int device, int max_log_size, zkb_ctx** out);
+int zkb_destroy(zkb_ctx* ctx);
+const char* zkb_last_error(zkb_ctx* ctx);
+int zkb_sync(zkb_ctx* ctx);
+/* The CUDA stream (cudaStream_t) all work of this context is ordered on. */
+int zkb_get_stream(zkb_ctx* ctx, void** stream);
+int zkb_max_log_size(zkb_ctx* ctx);
+
+/* ---- device columns (STWO/stwo_cuda/base_field_vec.rs:7-60, bindings.rs:84-103) ------------ */
+int zkb_malloc(zkb_ctx* ctx, size_t bytes, void** dptr);
+int zkb_free(zkb_ctx* ctx, void* dptr);
+int zkb_memset_zero(zkb_ctx* ctx, void* dptr, size_t bytes);
+int zkb_h2d(zkb_ctx* ctx, void* dptr, const void* h_src, size_t bytes); /* returns after the copy */
+int zkb_d2h(zkb_ctx* ctx, void* h_dst, const void* dptr, size_t bytes); /* returns after the copy */
+int zkb_h2d_async(zkb_ctx* ctx, void* dptr, const void* h_pinned_src, size_t bytes);
+int zkb_d2h_async(zkb_ctx* ctx, void* h_pinned_dst, const void* dptr, size_t bytes);
+int zkb_d2d(zkb_ctx* ctx, void* dst, const void* src, size_t bytes);
+int zkb_host_alloc_pinned(zkb_ctx* ctx, size_t bytes, void** h_ptr);
+int zkb_host_free_pinned(zkb_ctx* ctx, void* h_ptr);
+/* Column::batch_at_multi (STWO/prover/backend/mod.rs:70-89; bindings.rs:340-346):
+ * h_out[i * ncols + c] = cols[c][h_idx[i]]. */
+int zkb_gather_multi(zkb_ctx* ctx, const uint32_t* const* cols, int ncols, const uint32_t* h_idx, int nidx,
+                     uint32_t* h_out);
+
+/* ---- twiddles ------------------------------------------------------------------------------
+ * Copies out the tower of Coset::half_odds(log_size) in the reference's layout
+ * (slow_precompute_twiddles, STWO/prover/backend/cpu/circle.rs:274-291): 2^log_size words each,
+ * last word 1. h_itw may be NULL. log_size <= max_log_size - 1. */
+int zkb_twiddles_d2h(zkb_ctx* ctx, int log_size, uint32_t* h_tw, uint32_t* h_itw);
+
+/* ---- PolyOps (STWO/prover/poly/circle/ops.rs:16-145) --------------------------------------- */
+/* interpolate / interpolate_columns (ops.rs:23-39; cpu/circle.rs:28-80): evaluations on the
+ * canonic circle domain of log_n, bit-reversed, to FFT-basis coefficients; in place. */
+int zkb_ifft_cols(zkb_ctx* ctx, uint32_t* const* cols, int ncols, int log_n);
+/* evaluate / evaluate_polynomials / extend (ops.rs:88-120; cpu/circle.rs:182-228): 2^log_n
+ * coefficients to evaluations on the canonic domain of log_out >= log_n, bit-reversed.
+ * out[c] must not alias coeffs[c]. */
+int zkb_lde_cols(zkb_ctx* ctx, const uint32_t* const* coeffs, int ncols, int log_n, uint32_t* const* out,
+                 int log_out);
+/* eval_at_point / batch_eval_at_point (ops.rs:46-63; cpu/circle.rs:82-100): h_out[4*c..] is the
+ * value of column c's polynomial at the QM31 circle point h_point = (x[4], y[4]). */
+int zkb_eval_at_point_cols(zkb_ctx* ctx, const uint32_t* const* coeffs, int ncols, int log_n,
+                           const uint32_t* h_point, uint32_t* h_out);
+
+/* ---- ColumnOps::bit_reverse_column (STWO/prover/backend/mod.rs:39-42; core/utils.rs:71-81) -- */
+int zkb_bit_reverse_m31(zkb_ctx* ctx, uint32_t* col, int log_n);
+int zkb_bit_reverse_qm31(zkb_ctx* ctx, uint32_t* col, int log_n); /* 4-word elements */
+
+/* ---- MerkleOps::commit_on_layer (STWO/prover/vcs/ops.rs:24-29; cpu/blake2s.rs:13-26;
+ * hasher core/vcs/blake2_merkle.rs:18-39). prev: 2^(log_size+1) hashes or NULL. cols: ncols
+ * columns of 2^log_size values (ncols may be 0). m31_out != 0 selects the hasher whose digest
+ * words are reduced mod 2^31-1. out: 2^log_size hashes. */
+int zkb_merkle_layer(zkb_ctx* ctx, int log_size, const uint32_t* prev, const uint32_t* const* cols, int ncols,
+                     int m31_out, uint32_t* out);
+
+/* ---- FriOps (STWO/prover/fri.rs:37-85; cpu/fri.rs:67-123) ---------------------------------- */
+/* fold_circle_into_line: src on the canonic circle domain of log_n_src; dst (2^(log_n_src-1)
+ * entries) is updated as dst*alpha^2 + f0 + alpha*f1. */
+int zkb_fold_circle_into_line(zkb_ctx* ctx, uint32_t* const dst[4], const uint32_t* const src[4], int log_n_src,
+                              const uint32_t h_alpha[4]);
+/* fold_line with fold_step 1: in on the line domain Coset::half_odds(log_n); out has 2^(log_n-1). */
+int zkb_fold_line(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* const in[4], int log_n,
+                  const uint32_t h_alpha[4]);
+
+/* ---- QuotientOps (STWO/prover/pcs/quotient_ops.rs:19-43; cpu/quotients.rs:22-75) ------------ */
+/* accumulate_numerators for ONE sample batch: out[row] = sum_j (c_j * cols[col_idx[j]][row] - b_j),
+ * j < k, with the line coefficients (b_j, c_j) of core/pcs/quotients.rs:229-258 as k x 4 words. */
+int zkb_quot_numerators(zkb_ctx* ctx, const uint32_t* const* cols, int ncols, int log_n, const uint32_t* h_col_idx,
+                        const uint32_t* h_b, const uint32_t* h_c, int k, uint32_t* const out[4]);
+/* compute_quotients_and_combine: n_acc accumulations; acc_cols[4*a + i] is coordinate i of
+ * accumulation a with 2^h_acc_log[a] rows; h_first_lin (n_acc x 4) the summed `a` coefficients;
+ * h_points (n_acc x 8) the sample points (x[4], y[4]). out has 2^lifting_log rows. */
+int zkb_quot_combine(zkb_ctx* ctx, int n_acc, const uint32_t* const* acc_cols, const int* h_acc_log,
+                     const uint32_t* h_first_lin, const uint32_t* h_points, int lifting_log, uint32_t* const out[4]);
+
+/* ---- AccumulationOps (STWO/prover/air/accumulation.rs:127-145; cpu/accumulation.rs:9-48) --- */
+int zkb_accumulate(zkb_ctx* ctx, uint32_t* const col[4], const uint32_t* const other[4], size_t n);
+/* dst (2^log_dst rows) += lift of src (2^log_src rows, log_src <= log_dst):
+ * dst[i] += src[(i >> (log_dst-log_src+1) << 1) + (i & 1)]. lift_and_accumulate over ascending
+ * columns is a chain of these. */
+int zkb_lift_accumulate(zkb_ctx* ctx, uint32_t* const dst[4], int log_dst, const uint32_t* const src[4], int log_src);
+/* generate_secure_powers: h_out[4*i..] = felt^i. Host-side (n is small). */
+int zkb_secure_powers(zkb_ctx* ctx, const uint32_t h_felt[4], size_t n, uint32_t* h_out);
+
+/* ---- GkrOps / MleOps (STWO/prover/lookups/gkr_prover.rs:172-220, mle.rs:9-14;
+ * cpu/lookups/gkr.rs:17-263, cpu/lookups/mle.rs:13-46) ------------------------------------- */
+#define ZKB_GKR_GRAND_PRODUCT 0
+#define ZKB_GKR_LOGUP_GENERIC 1        /* num: QM31 */
+#define ZKB_GKR_LOGUP_MULTIPLICITIES 2 /* num: M31 (1 word per entry) */
+#define ZKB_GKR_LOGUP_SINGLES 3        /* num: NULL, implicitly 1 */
+/* gen_eq_evals: out[x] = v * eq(x, y) for x in {0,1}^ny, bit-reversed; h_y is ny x 4 words. */
+int zkb_gkr_eq_evals(zkb_ctx* ctx, const uint32_t* h_y, int ny, const uint32_t h_v[4], uint32_t* out);
+/* next_layer: n input entries -> n/2. For the three LogUp kinds the result is LOGUP_GENERIC
+ * (num_out, den_out); for GRAND_PRODUCT den/den_out hold the single column. */
+int zkb_gkr_next_layer(zkb_ctx* ctx, int kind, const uint32_t* num, const uint32_t* den, size_t n, uint32_t* num_out,
+                       uint32_t* den_out);
+/* sum_as_poly_in_first_variable, device part: h_out[0..4] = sum at t=0, h_out[4..8] = sum at t=2
+ * of eq_evals[i] * (numerator + lambda * denominator) over i < n/4, before the eq correction
+ * (the caller applies eq_fixed_var_correction and gkr_prover.rs:884-923). n = layer entries. */
+int zkb_gkr_sum(zkb_ctx* ctx, int kind, const uint32_t* num, const uint32_t* den, size_t n, const uint32_t* eq_evals,
+                const uint32_t h_lambda[4], uint32_t h_out[8]);
+/* fix_first_variable: out[i] = in[i] + r * (in[i + n/2] - in[i]); out may alias in for QM31. */
+int zkb_mle_fix_qm31(zkb_ctx* ctx, const uint32_t* in, size_t n, const uint32_t h_r[4], uint32_t* out);
+int zkb_mle_fix_m31(zkb_ctx* ctx, const uint32_t* in, size_t n, const uint32_t h_r[4], uint32_t* out);
+
+/* ---- GrindOps::grind (STWO/core/proof_of_work.rs:3-7; simd/grind.rs:18-93) ------------------
+ * Smallest nonce (hi << 32) | lo, lo < 2^20, whose Blake2s(prefixed_digest || nonce) has at least
+ * pow_bits trailing zero bits in its first word. h_prefixed_digest: 8 words. */
+int zkb_grind(zkb_ctx* ctx, const uint32_t h_prefixed_digest[8], int pow_bits, int m31_out, uint64_t* h_nonce);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZKB200_H */

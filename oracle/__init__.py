@@ -1,0 +1,349 @@
+"""TEST INFRASTRUCTURE ONLY: ctypes bindings over the CPU oracle (oracle/capi.cpp).
+
+Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline legs may import this package.
+The product package never does.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "_build", "libzkoracle.so")
+
+P = 2**31 - 1
+
+
+def build(force=False):
+    """Compile the oracle with the Makefile beside this file."""
+    if force or not os.path.exists(_SO) or any(
+        os.path.getmtime(os.path.join(_HERE, f)) > os.path.getmtime(_SO)
+        for f in os.listdir(_HERE) if f.endswith((".hpp", ".cpp"))
+    ):
+        subprocess.run(["make", "-C", _HERE], check=True, capture_output=True)
+    return _SO
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(build())
+        _lib.zko_m31_mul.restype = C.c_uint32
+        _lib.zko_m31_inv.restype = C.c_uint32
+        _lib.zko_m31_reduce64.restype = C.c_uint32
+        _lib.zko_m31_reduce64.argtypes = [C.c_uint64]
+        _lib.zko_channel_new.restype = C.c_void_p
+        _lib.zko_channel_grind.restype = C.c_uint64
+        _lib.zko_channel_verify_pow.restype = C.c_int
+        _lib.zko_num_threads.restype = C.c_int
+    return _lib
+
+
+def _u32(a):
+    a = np.ascontiguousarray(a, dtype=np.uint32)
+    return a
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _pp(arrs):
+    """Array of pointers to the rows of a list of contiguous uint32 arrays."""
+    return (C.c_void_p * len(arrs))(*[a.ctypes.data for a in arrs])
+
+
+def num_threads():
+    return lib().zko_num_threads()
+
+
+# ---------------------------------------------------------------- fields
+def m31_mul(a, b):
+    return lib().zko_m31_mul(C.c_uint32(a), C.c_uint32(b))
+
+
+def m31_inv(a):
+    return lib().zko_m31_inv(C.c_uint32(a))
+
+
+def m31_reduce64(a):
+    return lib().zko_m31_reduce64(a)
+
+
+def cm31_mul(a, b):
+    a, b, o = _u32(a), _u32(b), np.zeros(2, np.uint32)
+    lib().zko_cm31_mul(_p(a), _p(b), _p(o))
+    return o
+
+
+def cm31_inv(a):
+    a, o = _u32(a), np.zeros(2, np.uint32)
+    lib().zko_cm31_inv(_p(a), _p(o))
+    return o
+
+
+def qm31_mul(a, b):
+    a, b, o = _u32(a), _u32(b), np.zeros(4, np.uint32)
+    lib().zko_qm31_mul(_p(a), _p(b), _p(o))
+    return o
+
+
+def qm31_inv(a):
+    a, o = _u32(a), np.zeros(4, np.uint32)
+    lib().zko_qm31_inv(_p(a), _p(o))
+    return o
+
+
+# ---------------------------------------------------------------- circle
+def circle_point(index):
+    o = np.zeros(2, np.uint32)
+    lib().zko_circle_point(C.c_uint64(index), _p(o))
+    return o
+
+
+def secure_circle_mul(scalar):
+    o = np.zeros(8, np.uint32)
+    lib().zko_secure_circle_mul(C.c_uint64(scalar & (2**64 - 1)), C.c_uint64(scalar >> 64), _p(o))
+    return o
+
+
+def domain_at(log_size, i):
+    o = np.zeros(2, np.uint32)
+    lib().zko_domain_at(C.c_uint32(log_size), C.c_uint64(i), _p(o))
+    return o
+
+
+def twiddles(log_size):
+    """(twiddles, itwiddles) of the tower rooted at Coset::half_odds(log_size)."""
+    tw = np.zeros(1 << log_size, np.uint32)
+    itw = np.zeros(1 << log_size, np.uint32)
+    lib().zko_twiddles(C.c_uint32(log_size), _p(tw), _p(itw))
+    return tw, itw
+
+
+def line_twiddles_slices(domain_log_size, buf):
+    buf = _u32(buf)
+    k = domain_log_size - 1
+    offs = np.zeros(k, np.uint64)
+    lens = np.zeros(k, np.uint64)
+    lib().zko_line_twiddles_slices(C.c_uint32(domain_log_size), _p(buf), C.c_size_t(len(buf)), _p(offs), _p(lens))
+    return [buf[int(o):int(o) + int(n)] for o, n in zip(offs, lens)]
+
+
+# ---------------------------------------------------------------- circle FFT
+def interpolate_cols(cols, log_n):
+    """cols: [ncols, 2^log_n] uint32, evaluations in bit-reversed order -> coefficients."""
+    out = [np.array(c, dtype=np.uint32, copy=True) for c in cols]
+    lib().zko_interpolate_cols(_pp(out), C.c_int(len(out)), C.c_uint32(log_n))
+    return np.stack(out) if out else np.zeros((0, 1 << log_n), np.uint32)
+
+
+def evaluate_cols(coeffs, log_n, log_out):
+    ins = [_u32(c) for c in coeffs]
+    outs = [np.zeros(1 << log_out, np.uint32) for _ in ins]
+    lib().zko_evaluate_cols(_pp(ins), C.c_int(len(ins)), C.c_uint32(log_n), _pp(outs), C.c_uint32(log_out))
+    return np.stack(outs) if outs else np.zeros((0, 1 << log_out), np.uint32)
+
+
+def eval_at_point(coeffs, point8):
+    coeffs, point8, o = _u32(coeffs), _u32(point8), np.zeros(4, np.uint32)
+    log_n = int(len(coeffs)).bit_length() - 1
+    lib().zko_eval_at_point(_p(coeffs), C.c_uint32(log_n), _p(point8), _p(o))
+    return o
+
+
+def bit_reverse(v):
+    v = np.array(v, dtype=np.uint32, copy=True)
+    lib().zko_bit_reverse_u32(_p(v), C.c_uint32(int(len(v)).bit_length() - 1))
+    return v
+
+
+# ---------------------------------------------------------------- hashing
+def blake2s(data: bytes, m31=False):
+    o = np.zeros(32, np.uint8)
+    lib().zko_blake2s(C.c_char_p(data), C.c_size_t(len(data)), C.c_int(int(m31)), _p(o))
+    return o.tobytes()
+
+
+def commit_on_layer(log_size, prev, cols, m31=True):
+    """prev: [2^(log_size+1), 8] uint32 or None; cols: list of uint32 arrays of 2^log_size.
+    Returns [2^log_size, 8] uint32 (the 32 digest bytes as little-endian words)."""
+    cs = [_u32(c) for c in cols]
+    out = np.zeros((1 << log_size, 8), np.uint32)
+    pv = None if prev is None else _u32(prev)
+    lib().zko_commit_on_layer(C.c_uint32(log_size), None if pv is None else _p(pv), _pp(cs), C.c_int(len(cs)),
+                              C.c_int(int(m31)), _p(out))
+    return out
+
+
+class Channel:
+    def __init__(self, m31=True):
+        self._h = C.c_void_p(lib().zko_channel_new(C.c_int(int(m31))))
+
+    def __del__(self):
+        try:
+            lib().zko_channel_free(self._h)
+        except Exception:
+            pass
+
+    def digest(self):
+        o = np.zeros(32, np.uint8)
+        lib().zko_channel_digest(self._h, _p(o))
+        return o.tobytes()
+
+    def mix_u32s(self, data):
+        d = _u32(data)
+        lib().zko_channel_mix_u32s(self._h, _p(d), C.c_size_t(len(d)))
+
+    def mix_u64(self, v):
+        lib().zko_channel_mix_u64(self._h, C.c_uint64(v))
+
+    def mix_felts(self, felts):
+        f = _u32(felts).reshape(-1, 4)
+        lib().zko_channel_mix_felts(self._h, _p(f), C.c_size_t(f.shape[0]))
+
+    def mix_root(self, root_words):
+        r = _u32(root_words)
+        lib().zko_channel_mix_root(self._h, _p(r))
+
+    def draw_u32s(self):
+        o = np.zeros(8, np.uint32)
+        lib().zko_channel_draw_u32s(self._h, _p(o))
+        return o
+
+    def draw_secure_felt(self):
+        o = np.zeros(4, np.uint32)
+        lib().zko_channel_draw_secure_felt(self._h, _p(o))
+        return o
+
+    def draw_secure_felts(self, n):
+        o = np.zeros((n, 4), np.uint32)
+        lib().zko_channel_draw_secure_felts(self._h, C.c_size_t(n), _p(o))
+        return o
+
+    def grind(self, pow_bits):
+        return lib().zko_channel_grind(self._h, C.c_uint32(pow_bits))
+
+    def verify_pow_nonce(self, pow_bits, nonce):
+        return bool(lib().zko_channel_verify_pow(self._h, C.c_uint32(pow_bits), C.c_uint64(nonce)))
+
+    def draw_queries(self, log_domain_size, n):
+        o = np.zeros(n, np.uint64)
+        lib().zko_draw_queries(self._h, C.c_uint32(log_domain_size), C.c_size_t(n), _p(o))
+        return o
+
+
+# ---------------------------------------------------------------- FRI
+def fold_line(cols4, alpha):
+    """cols4: [4, n] uint32 -> [4, n/2]."""
+    ins = [_u32(c) for c in cols4]
+    n = len(ins[0])
+    outs = [np.zeros(n // 2, np.uint32) for _ in range(4)]
+    a = _u32(alpha)
+    lib().zko_fold_line(_pp(ins), C.c_uint32(n.bit_length() - 1), _p(a), _pp(outs))
+    return np.stack(outs)
+
+
+def fold_circle_into_line(dst4, src4, alpha):
+    d = [np.array(c, dtype=np.uint32, copy=True) for c in dst4]
+    s = [_u32(c) for c in src4]
+    a = _u32(alpha)
+    lib().zko_fold_circle_into_line(_pp(d), _pp(s), C.c_uint32(len(s[0]).bit_length() - 1), _p(a))
+    return np.stack(d)
+
+
+# ---------------------------------------------------------------- quotients
+def quot_numerators(cols, point8, col_idx, values, rands):
+    cs = [_u32(c) for c in cols]
+    n = len(cs[0])
+    outs = [np.zeros(n, np.uint32) for _ in range(4)]
+    first = np.zeros(4, np.uint32)
+    ci, va, ra, pt = _u32(col_idx), _u32(values).reshape(-1, 4), _u32(rands).reshape(-1, 4), _u32(point8)
+    lib().zko_quot_numerators(_pp(cs), C.c_int(len(cs)), C.c_uint32(n.bit_length() - 1), _p(pt), C.c_int(len(ci)),
+                              _p(ci), _p(va), _p(ra), _pp(outs), _p(first))
+    return np.stack(outs), first
+
+
+def line_coeffs(point8, value4, alpha4):
+    o = np.zeros(12, np.uint32)
+    a, b, c = _u32(point8), _u32(value4), _u32(alpha4)
+    lib().zko_line_coeffs(_p(a), _p(b), _p(c), _p(o))
+    return o.reshape(3, 4)
+
+
+def quot_combine(accs, first_lin, points, lifting_log):
+    """accs: list of [4, 2^k] arrays; first_lin: [n,4]; points: [n,8]."""
+    flat = [_u32(a[c]) for a in accs for c in range(4)]
+    logs = _u32([len(a[0]).bit_length() - 1 for a in accs])
+    fl, pts = _u32(first_lin).reshape(-1, 4), _u32(points).reshape(-1, 8)
+    outs = [np.zeros(1 << lifting_log, np.uint32) for _ in range(4)]
+    lib().zko_quot_combine(C.c_int(len(accs)), _pp(flat), _p(logs), _p(fl), _p(pts), C.c_uint32(lifting_log), _pp(outs))
+    return np.stack(outs)
+
+
+def accumulate(col4, other4):
+    a = [np.array(c, dtype=np.uint32, copy=True) for c in col4]
+    b = [_u32(c) for c in other4]
+    lib().zko_accumulate(_pp(a), _pp(b), C.c_size_t(len(a[0])))
+    return np.stack(a)
+
+
+def lift_and_accumulate(cols):
+    flat = [_u32(a[c]) for a in cols for c in range(4)]
+    logs = _u32([len(a[0]).bit_length() - 1 for a in cols])
+    outs = [np.zeros(len(cols[-1][0]), np.uint32) for _ in range(4)]
+    lib().zko_lift_and_accumulate(C.c_int(len(cols)), _pp(flat), _p(logs), _pp(outs))
+    return np.stack(outs)
+
+
+def secure_powers(felt4, n):
+    o = np.zeros((n, 4), np.uint32)
+    f = _u32(felt4)
+    lib().zko_secure_powers(_p(f), C.c_size_t(n), _p(o))
+    return o
+
+
+# ---------------------------------------------------------------- GKR
+GRAND_PRODUCT, LOGUP_GENERIC, LOGUP_MULTIPLICITIES, LOGUP_SINGLES = 0, 1, 2, 3
+
+
+def gkr_eq_evals(y, v4):
+    y = _u32(y).reshape(-1, 4)
+    o = np.zeros((1 << y.shape[0], 4), np.uint32)
+    v = _u32(v4)
+    lib().zko_gkr_eq_evals(_p(y), C.c_size_t(y.shape[0]), _p(v), _p(o))
+    return o
+
+
+def gkr_next_layer(kind, num, den):
+    den = _u32(den)
+    n = den.shape[0]
+    num = None if num is None else _u32(num)
+    no, do = np.zeros((n // 2, 4), np.uint32), np.zeros((n // 2, 4), np.uint32)
+    lib().zko_gkr_next_layer(C.c_int(kind), None if num is None else _p(num), _p(den), C.c_size_t(n), _p(no), _p(do))
+    return (None if kind == GRAND_PRODUCT else no), do
+
+
+def gkr_round_sums(kind, num, den, eq_evals, lam):
+    den = _u32(den)
+    n = den.shape[0]
+    num = None if num is None else _u32(num)
+    e, l, o = _u32(eq_evals), _u32(lam), np.zeros(8, np.uint32)
+    lib().zko_gkr_round_sums(C.c_int(kind), None if num is None else _p(num), _p(den), C.c_size_t(n), _p(e), _p(l), _p(o))
+    return o.reshape(2, 4)
+
+
+def mle_fix_first(mle, r4):
+    mle = _u32(mle)
+    r = _u32(r4)
+    n = mle.shape[0]
+    o = np.zeros((n // 2, 4), np.uint32)
+    if mle.ndim == 1:
+        lib().zko_mle_fix_first_m31(_p(mle), C.c_size_t(n), _p(r), _p(o))
+    else:
+        lib().zko_mle_fix_first_qm31(_p(mle), C.c_size_t(n), _p(r), _p(o))
+    return o

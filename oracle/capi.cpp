@@ -1,0 +1,289 @@
+// TEST INFRASTRUCTURE ONLY. C entry points over the CPU oracle so that tests (ctypes) and the
+// bench's CPU-baseline leg can call it. The product library never links this file.
+//
+// Conventions: M31 values are uint32_t in [0, p). A "secure column" is four uint32_t arrays
+// (coordinate layout, as SecureColumnByCoords, nitroo/crates/stwo/src/prover/secure_column.rs:13-15);
+// GKR multilinear columns are arrays of QM31 as 4 consecutive uint32_t.
+#include "protocol.hpp"
+#include <cstdlib>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+using namespace zko;
+
+static inline QM31 q_from(const uint32_t* p) { return QM31::from_u32(p[0], p[1], p[2], p[3]); }
+static inline void q_to(QM31 q, uint32_t* p) { q.to_u32(p); }
+static SecureColumn load_soa(const uint32_t* const c[4], size_t n) {
+    SecureColumn v(n);
+    for (size_t i = 0; i < n; i++) v[i] = QM31::from_u32(c[0][i], c[1][i], c[2][i], c[3][i]);
+    return v;
+}
+static void store_soa(const SecureColumn& v, uint32_t* const c[4]) {
+    for (size_t i = 0; i < v.size(); i++) {
+        uint32_t w[4]; v[i].to_u32(w);
+        for (int k = 0; k < 4; k++) c[k][i] = w[k];
+    }
+}
+
+static const TwiddleTree& tower(uint32_t log_half_coset) {
+    // one canonic twiddle tree per root size, built on demand
+    static std::vector<TwiddleTree*> cache(32, nullptr);
+    TwiddleTree*& t = cache[log_half_coset];
+    if (!t) t = new TwiddleTree(precompute_twiddles(Coset::half_odds(log_half_coset)));
+    return *t;
+}
+
+extern "C" {
+
+int zko_num_threads() {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
+
+// ---- fields (for unit tests of the restatement itself)
+uint32_t zko_m31_mul(uint32_t a, uint32_t b) { return (M31(a) * M31(b)).v; }
+uint32_t zko_m31_inv(uint32_t a) { return M31(a).inverse().v; }
+uint32_t zko_m31_reduce64(uint64_t a) { return M31::reduce(a).v; }
+void zko_cm31_mul(const uint32_t* a, const uint32_t* b, uint32_t* out) {
+    CM31 r = CM31(M31(a[0]), M31(a[1])) * CM31(M31(b[0]), M31(b[1]));
+    out[0] = r.a.v; out[1] = r.b.v;
+}
+void zko_cm31_inv(const uint32_t* a, uint32_t* out) {
+    CM31 r = CM31(M31(a[0]), M31(a[1])).inverse();
+    out[0] = r.a.v; out[1] = r.b.v;
+}
+void zko_qm31_mul(const uint32_t* a, const uint32_t* b, uint32_t* out) { q_to(q_from(a) * q_from(b), out); }
+void zko_qm31_inv(const uint32_t* a, uint32_t* out) { q_to(q_from(a).inverse(), out); }
+
+// ---- circle
+void zko_circle_point(uint64_t index, uint32_t* xy) {
+    auto p = CirclePointIndex{index}.reduce().to_point();
+    xy[0] = p.x.v; xy[1] = p.y.v;
+}
+void zko_secure_circle_mul(uint64_t lo, uint64_t hi, uint32_t* xy8) {
+    auto p = secure_field_circle_gen().mul(lo, hi);
+    q_to(p.x, xy8); q_to(p.y, xy8 + 4);
+}
+// domain point of row `i` (natural order) of the canonic circle domain of `log_size`
+void zko_domain_at(uint32_t log_size, uint64_t i, uint32_t* xy) {
+    auto p = CanonicCoset(log_size).circle_domain().at(i);
+    xy[0] = p.x.v; xy[1] = p.y.v;
+}
+
+// ---- twiddles: the tower of Coset::half_odds(log_size), `2^log_size` entries each
+void zko_twiddles(uint32_t log_size, uint32_t* tw, uint32_t* itw) {
+    const TwiddleTree& t = tower(log_size);
+    for (size_t i = 0; i < t.twiddles.size(); i++) { tw[i] = t.twiddles[i].v; if (itw) itw[i] = t.itwiddles[i].v; }
+}
+void zko_line_twiddles_slices(uint32_t domain_log_size, const uint32_t* buf, size_t buf_len, uint64_t* offs, uint64_t* lens) {
+    std::vector<M31> b(buf_len);
+    for (size_t i = 0; i < buf_len; i++) b[i] = M31(buf[i]);
+    auto s = domain_line_twiddles_from_tree(CanonicCoset(domain_log_size).half_coset(), b);
+    for (size_t i = 0; i < s.size(); i++) { offs[i] = s[i].p - b.data(); lens[i] = s[i].n; }
+}
+
+// ---- circle FFT on canonic domains, many columns (columns are independent; threads split them)
+void zko_interpolate_cols(uint32_t* const* cols, int ncols, uint32_t log_n) {
+    CircleDomain d = CanonicCoset(log_n).circle_domain();
+    const TwiddleTree& t = tower(log_n >= 1 ? log_n - 1 : 0);
+    size_t n = (size_t)1 << log_n;
+#pragma omp parallel for schedule(dynamic)
+    for (int c = 0; c < ncols; c++) {
+        std::vector<M31> v(n);
+        for (size_t i = 0; i < n; i++) v[i] = M31(cols[c][i]);
+        interpolate(v, d, t);
+        for (size_t i = 0; i < n; i++) cols[c][i] = v[i].v;
+    }
+}
+void zko_evaluate_cols(const uint32_t* const* coeffs, int ncols, uint32_t log_n, uint32_t* const* out, uint32_t log_out) {
+    CircleDomain d = CanonicCoset(log_out).circle_domain();
+    const TwiddleTree& t = tower(log_out - 1);
+    size_t n = (size_t)1 << log_n, N = (size_t)1 << log_out;
+#pragma omp parallel for schedule(dynamic)
+    for (int c = 0; c < ncols; c++) {
+        std::vector<M31> v(n);
+        for (size_t i = 0; i < n; i++) v[i] = M31(coeffs[c][i]);
+        std::vector<M31> e = evaluate(v, d, t);
+        for (size_t i = 0; i < N; i++) out[c][i] = e[i].v;
+    }
+}
+void zko_eval_at_point(const uint32_t* coeffs, uint32_t log_n, const uint32_t* point8, uint32_t* out4) {
+    std::vector<M31> v((size_t)1 << log_n);
+    for (size_t i = 0; i < v.size(); i++) v[i] = M31(coeffs[i]);
+    CirclePoint<QM31> p{q_from(point8), q_from(point8 + 4)};
+    q_to(eval_at_point(v, p), out4);
+}
+
+void zko_bit_reverse_u32(uint32_t* v, uint32_t log_n) { bit_reverse(v, (size_t)1 << log_n); }
+
+// ---- hashing
+void zko_blake2s(const uint8_t* data, size_t len, int m31, uint8_t* out32) {
+    Hash h = Hasher::hash(data, len, m31 != 0);
+    memcpy(out32, h.data(), 32);
+}
+// prev: 2^(log_size+1) hashes of 32 bytes, or NULL. out: 2^log_size hashes.
+void zko_commit_on_layer(uint32_t log_size, const uint8_t* prev, const uint32_t* const* cols, int ncols, int m31, uint8_t* out) {
+    size_t n = (size_t)1 << log_size;
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; i++) {
+        std::vector<M31> row(ncols);
+        for (int c = 0; c < ncols; c++) row[c] = M31(cols[c][i]);
+        Hash l, r;
+        if (prev) { memcpy(l.data(), prev + 64 * i, 32); memcpy(r.data(), prev + 64 * i + 32, 32); }
+        Hash h = hash_node(prev ? &l : nullptr, prev ? &r : nullptr, row.data(), row.size(), m31 != 0);
+        memcpy(out + 32 * i, h.data(), 32);
+    }
+}
+
+// ---- channel (opaque handle)
+void* zko_channel_new(int m31) { return new Channel(m31 != 0); }
+void zko_channel_free(void* c) { delete (Channel*)c; }
+void zko_channel_digest(void* c, uint8_t* out32) { memcpy(out32, ((Channel*)c)->digest.data(), 32); }
+void zko_channel_mix_u32s(void* c, const uint32_t* d, size_t n) { ((Channel*)c)->mix_u32s(d, n); }
+void zko_channel_mix_u64(void* c, uint64_t v) { ((Channel*)c)->mix_u64(v); }
+void zko_channel_mix_felts(void* c, const uint32_t* felts, size_t n) {
+    std::vector<QM31> f(n);
+    for (size_t i = 0; i < n; i++) f[i] = q_from(felts + 4 * i);
+    ((Channel*)c)->mix_felts(f);
+}
+void zko_channel_mix_root(void* c, const uint8_t* root32) { Hash h; memcpy(h.data(), root32, 32); ((Channel*)c)->mix_root(h); }
+void zko_channel_draw_u32s(void* c, uint32_t* out8) { auto u = ((Channel*)c)->draw_u32s(); for (int i = 0; i < 8; i++) out8[i] = u[i]; }
+void zko_channel_draw_secure_felt(void* c, uint32_t* out4) { q_to(((Channel*)c)->draw_secure_felt(), out4); }
+void zko_channel_draw_secure_felts(void* c, size_t n, uint32_t* out) {
+    auto v = ((Channel*)c)->draw_secure_felts(n);
+    for (size_t i = 0; i < n; i++) q_to(v[i], out + 4 * i);
+}
+uint64_t zko_channel_grind(void* c, uint32_t pow_bits) { return ((Channel*)c)->grind(pow_bits); }
+int zko_channel_verify_pow(void* c, uint32_t pow_bits, uint64_t nonce) { return ((Channel*)c)->verify_pow_nonce(pow_bits, nonce); }
+void zko_draw_queries(void* c, uint32_t log_domain_size, size_t n, uint64_t* out) {
+    auto q = draw_queries(*(Channel*)c, log_domain_size, n);
+    for (size_t i = 0; i < n; i++) out[i] = q[i];
+}
+
+// ---- FRI folds (secure columns in coordinate layout)
+void zko_fold_line(const uint32_t* const in[4], uint32_t log_n, const uint32_t* alpha4, uint32_t* const out[4]) {
+    SecureColumn e = load_soa(in, (size_t)1 << log_n);
+    LineDomain d{Coset::half_odds(log_n)};
+    store_soa(fold_line(e, d, q_from(alpha4)), out);
+}
+void zko_fold_circle_into_line(uint32_t* const dst[4], const uint32_t* const src[4], uint32_t log_n_src, const uint32_t* alpha4) {
+    size_t n = (size_t)1 << log_n_src;
+    SecureColumn s = load_soa(src, n);
+    const uint32_t* const dc[4] = {dst[0], dst[1], dst[2], dst[3]};
+    SecureColumn d = load_soa(dc, n / 2);
+    fold_circle_into_line(d, s, CanonicCoset(log_n_src).circle_domain(), q_from(alpha4));
+    store_soa(d, dst);
+}
+
+// ---- quotients
+// One sample batch: k entries (col_idx[j], value[j] (QM31), rand[j] (QM31)) at `point8`.
+// Writes the partial numerators (coordinate layout) and the first-linear-term sum.
+void zko_quot_numerators(const uint32_t* const* cols, int /*ncols*/, uint32_t log_n, const uint32_t* point8, int k,
+                         const uint32_t* col_idx, const uint32_t* values, const uint32_t* rands,
+                         uint32_t* const out[4], uint32_t* first_lin4) {
+    size_t n = (size_t)1 << log_n;
+    ColumnSampleBatch b;
+    b.point = {q_from(point8), q_from(point8 + 4)};
+    for (int j = 0; j < k; j++) b.cols_vals_randpows.push_back({col_idx[j], q_from(values + 4 * j), q_from(rands + 4 * j)});
+    auto coeffs = column_line_coeffs({b})[0];
+    QM31 first = QM31::zero();
+    for (auto& lc : coeffs) first = first + lc.a;
+    q_to(first, first_lin4);
+#pragma omp parallel for schedule(static)
+    for (size_t row = 0; row < n; row++) {
+        QM31 numerator = QM31::zero();
+        for (int j = 0; j < k; j++) {
+            QM31 value = coeffs[j].c * M31(cols[col_idx[j]][row]);
+            numerator = numerator + (value - coeffs[j].b);
+        }
+        uint32_t w[4]; numerator.to_u32(w);
+        for (int c = 0; c < 4; c++) out[c][row] = w[c];
+    }
+}
+// Line coefficients (a, b, c) of one sample, as 12 uint32_t.
+void zko_line_coeffs(const uint32_t* point8, const uint32_t* value4, const uint32_t* alpha4, uint32_t* out12) {
+    LineCoeffs lc = complex_conjugate_line_coeffs({{q_from(point8), q_from(point8 + 4)}, q_from(value4)}, q_from(alpha4));
+    q_to(lc.a, out12); q_to(lc.b, out12 + 4); q_to(lc.c, out12 + 8);
+}
+// accs: n_acc accumulations; acc_cols[4*a + c] is coordinate c of accumulation a, of length 2^acc_log[a].
+void zko_quot_combine(int n_acc, const uint32_t* const* acc_cols, const uint32_t* acc_log, const uint32_t* first_lin,
+                      const uint32_t* points, uint32_t lifting_log, uint32_t* const out[4]) {
+    std::vector<AccumulatedNumerators> accs;
+    for (int a = 0; a < n_acc; a++) {
+        const uint32_t* const c[4] = {acc_cols[4 * a], acc_cols[4 * a + 1], acc_cols[4 * a + 2], acc_cols[4 * a + 3]};
+        accs.push_back({{q_from(points + 8 * a), q_from(points + 8 * a + 4)}, load_soa(c, (size_t)1 << acc_log[a]), q_from(first_lin + 4 * a)});
+    }
+    store_soa(compute_quotients_and_combine(accs, lifting_log), out);
+}
+void zko_accumulate(uint32_t* const col[4], const uint32_t* const other[4], size_t n) {
+    const uint32_t* const cc[4] = {col[0], col[1], col[2], col[3]};
+    SecureColumn a = load_soa(cc, n), b = load_soa(other, n);
+    accumulate(a, b);
+    store_soa(a, col);
+}
+// cols[4*i + c], ascending sizes 2^logs[i]; result written into `out` (size of the last).
+void zko_lift_and_accumulate(int ncols, const uint32_t* const* cols, const uint32_t* logs, uint32_t* const out[4]) {
+    std::vector<SecureColumn> v;
+    for (int i = 0; i < ncols; i++) {
+        const uint32_t* const c[4] = {cols[4 * i], cols[4 * i + 1], cols[4 * i + 2], cols[4 * i + 3]};
+        v.push_back(load_soa(c, (size_t)1 << logs[i]));
+    }
+    store_soa(lift_and_accumulate(v), out);
+}
+void zko_secure_powers(const uint32_t* felt4, size_t n, uint32_t* out) {
+    auto v = generate_secure_powers(q_from(felt4), n);
+    for (size_t i = 0; i < n; i++) q_to(v[i], out + 4 * i);
+}
+
+// ---- GKR (QM31 arrays as 4 consecutive words)
+void zko_gkr_eq_evals(const uint32_t* y, size_t ny, const uint32_t* v4, uint32_t* out) {
+    std::vector<QM31> yy(ny);
+    for (size_t i = 0; i < ny; i++) yy[i] = q_from(y + 4 * i);
+    auto e = gen_eq_evals(yy.data(), ny, q_from(v4));
+    for (size_t i = 0; i < e.size(); i++) q_to(e[i], out + 4 * i);
+}
+static Layer load_layer(int kind, const uint32_t* num, const uint32_t* den, size_t n) {
+    Layer l;
+    l.kind = (LayerKind)kind;
+    l.den.resize(n);
+    for (size_t i = 0; i < n; i++) l.den[i] = q_from(den + 4 * i);
+    if (kind == LOGUP_GENERIC) { l.num.resize(n); for (size_t i = 0; i < n; i++) l.num[i] = q_from(num + 4 * i); }
+    if (kind == LOGUP_MULTIPLICITIES) { l.num_base.resize(n); for (size_t i = 0; i < n; i++) l.num_base[i] = M31(num[i]); }
+    return l;
+}
+// n = input entries. Outputs n/2 QM31 each (num_out unused for GRAND_PRODUCT).
+void zko_gkr_next_layer(int kind, const uint32_t* num, const uint32_t* den, size_t n, uint32_t* num_out, uint32_t* den_out) {
+    Layer o = next_layer(load_layer(kind, num, den, n));
+    for (size_t i = 0; i < n / 2; i++) {
+        q_to(o.den[i], den_out + 4 * i);
+        if (o.kind != GRAND_PRODUCT) q_to(o.num[i], num_out + 4 * i);
+    }
+}
+void zko_gkr_round_sums(int kind, const uint32_t* num, const uint32_t* den, size_t n, const uint32_t* eq_evals,
+                        const uint32_t* lambda4, uint32_t* out8) {
+    Layer l = load_layer(kind, num, den, n);
+    size_t n_terms = n / 4;
+    std::vector<QM31> e(n_terms);
+    for (size_t i = 0; i < n_terms; i++) e[i] = q_from(eq_evals + 4 * i);
+    QM31 a0, a2;
+    round_sums(l, e.data(), n_terms, q_from(lambda4), a0, a2);
+    q_to(a0, out8); q_to(a2, out8 + 4);
+}
+void zko_mle_fix_first_qm31(const uint32_t* in, size_t n, const uint32_t* r4, uint32_t* out) {
+    std::vector<QM31> v(n);
+    for (size_t i = 0; i < n; i++) v[i] = q_from(in + 4 * i);
+    auto o = fix_first_variable(v, q_from(r4));
+    for (size_t i = 0; i < o.size(); i++) q_to(o[i], out + 4 * i);
+}
+void zko_mle_fix_first_m31(const uint32_t* in, size_t n, const uint32_t* r4, uint32_t* out) {
+    std::vector<M31> v(n);
+    for (size_t i = 0; i < n; i++) v[i] = M31(in[i]);
+    auto o = fix_first_variable(v, q_from(r4));
+    for (size_t i = 0; i < o.size(); i++) q_to(o[i], out + 4 * i);
+}
+
+}  // extern "C"

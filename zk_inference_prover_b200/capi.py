@@ -1,0 +1,254 @@
+"""ctypes bindings over include/zkb200.h. Every call goes through the C ABI of libzkb200.so."""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = os.path.join(_HERE, "lib", "libzkb200.so")
+
+GKR_GRAND_PRODUCT, GKR_LOGUP_GENERIC, GKR_LOGUP_MULTIPLICITIES, GKR_LOGUP_SINGLES = 0, 1, 2, 3
+
+# Every symbol include/zkb200.h declares.
+EXPORTED_SYMBOLS = [
+    "zkb_init", "zkb_destroy", "zkb_last_error", "zkb_sync", "zkb_get_stream", "zkb_max_log_size",
+    "zkb_malloc", "zkb_free", "zkb_memset_zero", "zkb_h2d", "zkb_d2h", "zkb_h2d_async", "zkb_d2h_async", "zkb_d2d",
+    "zkb_host_alloc_pinned", "zkb_host_free_pinned", "zkb_gather_multi", "zkb_twiddles_d2h",
+    "zkb_ifft_cols", "zkb_lde_cols", "zkb_eval_at_point_cols", "zkb_bit_reverse_m31", "zkb_bit_reverse_qm31",
+    "zkb_merkle_layer", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine",
+    "zkb_accumulate", "zkb_lift_accumulate", "zkb_secure_powers", "zkb_gkr_eq_evals", "zkb_gkr_next_layer",
+    "zkb_gkr_sum", "zkb_mle_fix_qm31", "zkb_mle_fix_m31", "zkb_grind",
+]
+
+
+class ZkbError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(f"zkb200 error {code}: {msg}")
+        self.code = code
+
+
+def lib_path():
+    return _LIB
+
+
+_lib = None
+
+
+def load_library():
+    """Loads libzkb200.so. Raises if it has not been built (there is no fallback path)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB):
+            raise ImportError(
+                f"{_LIB} is missing: build it with `python -m zk_inference_prover_b200.build` "
+                "(nvcc, sm_100a). zkb200 has no CPU fallback."
+            )
+        _lib = C.CDLL(_LIB)
+        _lib.zkb_last_error.restype = C.c_char_p
+        _lib.zkb_last_error.argtypes = [C.c_void_p]
+        for name in EXPORTED_SYMBOLS:
+            if name != "zkb_last_error":
+                getattr(_lib, name).restype = C.c_int
+    return _lib
+
+
+def _u32(a):
+    return np.ascontiguousarray(a, dtype=np.uint32)
+
+
+class DeviceBuffer:
+    """A device allocation of `words` uint32, owned by this object."""
+
+    def __init__(self, ctx, words):
+        self.ctx = ctx
+        self.words = int(words)
+        p = C.c_void_p()
+        ctx._check(ctx.lib.zkb_malloc(ctx.h, C.c_size_t(self.words * 4), C.byref(p)))
+        self.ptr = p.value or 0
+
+    def free(self):
+        if self.ptr:
+            self.ctx.lib.zkb_free(self.ctx.h, C.c_void_p(self.ptr))
+            self.ptr = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+    def upload(self, arr):
+        a = _u32(arr).reshape(-1)
+        assert a.size <= self.words
+        self.ctx._check(self.ctx.lib.zkb_h2d(self.ctx.h, C.c_void_p(self.ptr), a.ctypes.data_as(C.c_void_p), C.c_size_t(a.size * 4)))
+        return self
+
+    def download(self, words=None, shape=None):
+        n = self.words if words is None else int(words)
+        out = np.empty(n, np.uint32)
+        self.ctx._check(self.ctx.lib.zkb_d2h(self.ctx.h, out.ctypes.data_as(C.c_void_p), C.c_void_p(self.ptr), C.c_size_t(n * 4)))
+        return out if shape is None else out.reshape(shape)
+
+    def zero(self):
+        self.ctx._check(self.ctx.lib.zkb_memset_zero(self.ctx.h, C.c_void_p(self.ptr), C.c_size_t(self.words * 4)))
+        return self
+
+    def view(self, offset_words):
+        """Raw device address `offset_words` into the buffer."""
+        return self.ptr + 4 * int(offset_words)
+
+
+def _ptr_array(ptrs):
+    return (C.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+
+
+class Context:
+    """A zkb_ctx: one device, one stream, the twiddle tower up to `max_log_size`."""
+
+    def __init__(self, device=0, max_log_size=20):
+        self.lib = load_library()
+        h = C.c_void_p()
+        rc = self.lib.zkb_init(C.c_int(device), C.c_int(max_log_size), C.byref(h))
+        if rc != 0:
+            raise ZkbError(rc, "zkb_init failed (is a CUDA device visible?)")
+        self.h = h
+        self.max_log_size = max_log_size
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.zkb_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc):
+        if rc != 0:
+            raise ZkbError(rc, self.lib.zkb_last_error(self.h).decode())
+
+    # ---- memory
+    def alloc(self, words):
+        return DeviceBuffer(self, words)
+
+    def upload(self, arr):
+        a = _u32(arr)
+        return DeviceBuffer(self, a.size).upload(a)
+
+    def sync(self):
+        self._check(self.lib.zkb_sync(self.h))
+
+    def stream(self):
+        s = C.c_void_p()
+        self._check(self.lib.zkb_get_stream(self.h, C.byref(s)))
+        return s.value or 0
+
+    def gather_multi(self, col_ptrs, idx):
+        idx = _u32(idx)
+        out = np.empty((len(idx), len(col_ptrs)), np.uint32)
+        self._check(self.lib.zkb_gather_multi(self.h, _ptr_array(col_ptrs), C.c_int(len(col_ptrs)), idx.ctypes.data_as(C.c_void_p),
+                                              C.c_int(len(idx)), out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    # ---- twiddles
+    def twiddles(self, log_size):
+        tw = np.empty(1 << log_size, np.uint32)
+        itw = np.empty(1 << log_size, np.uint32)
+        self._check(self.lib.zkb_twiddles_d2h(self.h, C.c_int(log_size), tw.ctypes.data_as(C.c_void_p), itw.ctypes.data_as(C.c_void_p)))
+        return tw, itw
+
+    # ---- PolyOps
+    def ifft_cols(self, col_ptrs, log_n):
+        self._check(self.lib.zkb_ifft_cols(self.h, _ptr_array(col_ptrs), C.c_int(len(col_ptrs)), C.c_int(log_n)))
+
+    def lde_cols(self, coeff_ptrs, log_n, out_ptrs, log_out):
+        self._check(self.lib.zkb_lde_cols(self.h, _ptr_array(coeff_ptrs), C.c_int(len(coeff_ptrs)), C.c_int(log_n),
+                                          _ptr_array(out_ptrs), C.c_int(log_out)))
+
+    def eval_at_point_cols(self, coeff_ptrs, log_n, point8):
+        pt = _u32(point8)
+        out = np.empty((len(coeff_ptrs), 4), np.uint32)
+        self._check(self.lib.zkb_eval_at_point_cols(self.h, _ptr_array(coeff_ptrs), C.c_int(len(coeff_ptrs)), C.c_int(log_n),
+                                                    pt.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def bit_reverse_m31(self, ptr, log_n):
+        self._check(self.lib.zkb_bit_reverse_m31(self.h, C.c_void_p(ptr), C.c_int(log_n)))
+
+    def bit_reverse_qm31(self, ptr, log_n):
+        self._check(self.lib.zkb_bit_reverse_qm31(self.h, C.c_void_p(ptr), C.c_int(log_n)))
+
+    # ---- MerkleOps
+    def merkle_layer(self, log_size, prev_ptr, col_ptrs, out_ptr, m31_out=True):
+        self._check(self.lib.zkb_merkle_layer(self.h, C.c_int(log_size), C.c_void_p(prev_ptr or None), _ptr_array(col_ptrs),
+                                              C.c_int(len(col_ptrs)), C.c_int(int(m31_out)), C.c_void_p(out_ptr)))
+
+    # ---- FriOps
+    def fold_line(self, out4, in4, log_n, alpha):
+        a = _u32(alpha)
+        self._check(self.lib.zkb_fold_line(self.h, _ptr_array(out4), _ptr_array(in4), C.c_int(log_n), a.ctypes.data_as(C.c_void_p)))
+
+    def fold_circle_into_line(self, dst4, src4, log_n_src, alpha):
+        a = _u32(alpha)
+        self._check(self.lib.zkb_fold_circle_into_line(self.h, _ptr_array(dst4), _ptr_array(src4), C.c_int(log_n_src),
+                                                       a.ctypes.data_as(C.c_void_p)))
+
+    # ---- QuotientOps / AccumulationOps
+    def quot_numerators(self, col_ptrs, log_n, col_idx, b, c, out4):
+        ci, bb, cc = _u32(col_idx), _u32(b), _u32(c)
+        self._check(self.lib.zkb_quot_numerators(self.h, _ptr_array(col_ptrs), C.c_int(len(col_ptrs)), C.c_int(log_n),
+                                                 ci.ctypes.data_as(C.c_void_p), bb.ctypes.data_as(C.c_void_p),
+                                                 cc.ctypes.data_as(C.c_void_p), C.c_int(len(ci)), _ptr_array(out4)))
+
+    def quot_combine(self, acc_ptrs, acc_logs, first_lin, points, lifting_log, out4):
+        logs = np.ascontiguousarray(acc_logs, dtype=np.int32)
+        fl, pts = _u32(first_lin), _u32(points)
+        self._check(self.lib.zkb_quot_combine(self.h, C.c_int(len(logs)), _ptr_array(acc_ptrs), logs.ctypes.data_as(C.c_void_p),
+                                              fl.ctypes.data_as(C.c_void_p), pts.ctypes.data_as(C.c_void_p), C.c_int(lifting_log),
+                                              _ptr_array(out4)))
+
+    def accumulate(self, col4, other4, n):
+        self._check(self.lib.zkb_accumulate(self.h, _ptr_array(col4), _ptr_array(other4), C.c_size_t(n)))
+
+    def lift_accumulate(self, dst4, log_dst, src4, log_src):
+        self._check(self.lib.zkb_lift_accumulate(self.h, _ptr_array(dst4), C.c_int(log_dst), _ptr_array(src4), C.c_int(log_src)))
+
+    def secure_powers(self, felt4, n):
+        f = _u32(felt4)
+        out = np.empty((n, 4), np.uint32)
+        self._check(self.lib.zkb_secure_powers(self.h, f.ctypes.data_as(C.c_void_p), C.c_size_t(n), out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    # ---- GkrOps / MleOps
+    def gkr_eq_evals(self, y, v4, out_ptr):
+        yy, v = _u32(y).reshape(-1, 4), _u32(v4)
+        self._check(self.lib.zkb_gkr_eq_evals(self.h, yy.ctypes.data_as(C.c_void_p), C.c_int(yy.shape[0]), v.ctypes.data_as(C.c_void_p),
+                                              C.c_void_p(out_ptr)))
+
+    def gkr_next_layer(self, kind, num_ptr, den_ptr, n, num_out_ptr, den_out_ptr):
+        self._check(self.lib.zkb_gkr_next_layer(self.h, C.c_int(kind), C.c_void_p(num_ptr or None), C.c_void_p(den_ptr), C.c_size_t(n),
+                                                C.c_void_p(num_out_ptr or None), C.c_void_p(den_out_ptr)))
+
+    def gkr_sum(self, kind, num_ptr, den_ptr, n, eq_ptr, lam):
+        l = _u32(lam)
+        out = np.empty(8, np.uint32)
+        self._check(self.lib.zkb_gkr_sum(self.h, C.c_int(kind), C.c_void_p(num_ptr or None), C.c_void_p(den_ptr), C.c_size_t(n),
+                                         C.c_void_p(eq_ptr), l.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p)))
+        return out.reshape(2, 4)
+
+    def mle_fix_qm31(self, in_ptr, n, r, out_ptr):
+        rr = _u32(r)
+        self._check(self.lib.zkb_mle_fix_qm31(self.h, C.c_void_p(in_ptr), C.c_size_t(n), rr.ctypes.data_as(C.c_void_p), C.c_void_p(out_ptr)))
+
+    def mle_fix_m31(self, in_ptr, n, r, out_ptr):
+        rr = _u32(r)
+        self._check(self.lib.zkb_mle_fix_m31(self.h, C.c_void_p(in_ptr), C.c_size_t(n), rr.ctypes.data_as(C.c_void_p), C.c_void_p(out_ptr)))
+
+    # ---- GrindOps
+    def grind(self, prefixed_digest8, pow_bits, m31_out=True):
+        d = _u32(prefixed_digest8)
+        nonce = C.c_uint64()
+        self._check(self.lib.zkb_grind(self.h, d.ctypes.data_as(C.c_void_p), C.c_int(pow_bits), C.c_int(int(m31_out)), C.byref(nonce)))
+        return nonce.value

@@ -1,0 +1,192 @@
+// MerkleOps::commit_on_layer with the Blake2s hasher, and the proof-of-work grind.
+//
+// A node's message is [left child hash | right child hash |] col_0[i] | col_1[i] | ... with every
+// column value as one little-endian word (nitroo/crates/stwo/src/core/vcs/blake2_merkle.rs:18-39),
+// hashed with Blake2s-256 (RFC 7693) and, for the M31 hasher, each digest word reduced mod 2^31-1
+// (core/vcs/blake2_hash.rs:111-118). One thread hashes one node: the column words ARE the message
+// words, so a 64-byte block is 16 coalesced loads (one per column) straight into registers.
+#include "common.cuh"
+
+namespace zk {
+
+#define B2S_IV0 0x6A09E667u
+#define B2S_IV1 0xBB67AE85u
+#define B2S_IV2 0x3C6EF372u
+#define B2S_IV3 0xA54FF53Au
+#define B2S_IV4 0x510E527Fu
+#define B2S_IV5 0x9B05688Cu
+#define B2S_IV6 0x1F83D9ABu
+#define B2S_IV7 0x5BE0CD19u
+
+__device__ __forceinline__ uint32_t rotr16(uint32_t x) { return __byte_perm(x, 0, 0x1032); }
+__device__ __forceinline__ uint32_t rotr8(uint32_t x) { return __byte_perm(x, 0, 0x0321); }
+__device__ __forceinline__ uint32_t rotr12(uint32_t x) { return __funnelshift_r(x, x, 12); }
+__device__ __forceinline__ uint32_t rotr7(uint32_t x) { return __funnelshift_r(x, x, 7); }
+
+#define B2S_G(a, b, c, d, x, y) \
+    do {                        \
+        a = a + b + (x);        \
+        d = rotr16(d ^ a);      \
+        c = c + d;              \
+        b = rotr12(b ^ c);      \
+        a = a + b + (y);        \
+        d = rotr8(d ^ a);       \
+        c = c + d;              \
+        b = rotr7(b ^ c);       \
+    } while (0)
+
+#define B2S_ROUND(s0, s1, s2, s3, s4, s5, s6, s7, s8, s9, s10, s11, s12, s13, s14, s15) \
+    do {                                                                                 \
+        B2S_G(v0, v4, v8, v12, m[s0], m[s1]);                                            \
+        B2S_G(v1, v5, v9, v13, m[s2], m[s3]);                                            \
+        B2S_G(v2, v6, v10, v14, m[s4], m[s5]);                                           \
+        B2S_G(v3, v7, v11, v15, m[s6], m[s7]);                                           \
+        B2S_G(v0, v5, v10, v15, m[s8], m[s9]);                                           \
+        B2S_G(v1, v6, v11, v12, m[s10], m[s11]);                                         \
+        B2S_G(v2, v7, v8, v13, m[s12], m[s13]);                                          \
+        B2S_G(v3, v4, v9, v14, m[s14], m[s15]);                                          \
+    } while (0)
+
+// One compression (RFC 7693 section 3.2). `t` is the byte count including this block.
+__device__ __forceinline__ void blake2s_compress(uint32_t h[8], const uint32_t m[16], uint32_t t, bool last) {
+    uint32_t v0 = h[0], v1 = h[1], v2 = h[2], v3 = h[3], v4 = h[4], v5 = h[5], v6 = h[6], v7 = h[7];
+    uint32_t v8 = B2S_IV0, v9 = B2S_IV1, v10 = B2S_IV2, v11 = B2S_IV3;
+    uint32_t v12 = B2S_IV4 ^ t, v13 = B2S_IV5, v14 = last ? ~B2S_IV6 : B2S_IV6, v15 = B2S_IV7;
+    B2S_ROUND(0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15);
+    B2S_ROUND(14, 10, 4, 8, 9, 15, 13, 6, 1, 12, 0, 2, 11, 7, 5, 3);
+    B2S_ROUND(11, 8, 12, 0, 5, 2, 15, 13, 10, 14, 3, 6, 7, 1, 9, 4);
+    B2S_ROUND(7, 9, 3, 1, 13, 12, 11, 14, 2, 6, 5, 10, 4, 0, 15, 8);
+    B2S_ROUND(9, 0, 5, 7, 2, 4, 10, 15, 14, 1, 11, 12, 6, 8, 3, 13);
+    B2S_ROUND(2, 12, 6, 10, 0, 11, 8, 3, 4, 13, 7, 5, 15, 14, 1, 9);
+    B2S_ROUND(12, 5, 1, 15, 14, 13, 4, 10, 0, 7, 6, 3, 9, 2, 8, 11);
+    B2S_ROUND(13, 11, 7, 14, 12, 1, 3, 9, 5, 0, 15, 4, 8, 6, 2, 10);
+    B2S_ROUND(6, 15, 14, 9, 11, 3, 0, 8, 12, 2, 13, 7, 1, 4, 10, 5);
+    B2S_ROUND(10, 2, 8, 4, 7, 6, 1, 5, 15, 11, 9, 14, 3, 12, 13, 0);
+    h[0] ^= v0 ^ v8;  h[1] ^= v1 ^ v9;  h[2] ^= v2 ^ v10; h[3] ^= v3 ^ v11;
+    h[4] ^= v4 ^ v12; h[5] ^= v5 ^ v13; h[6] ^= v6 ^ v14; h[7] ^= v7 ^ v15;
+}
+
+__device__ __forceinline__ void blake2s_init(uint32_t h[8]) {
+    h[0] = B2S_IV0 ^ 0x01010020u; h[1] = B2S_IV1; h[2] = B2S_IV2; h[3] = B2S_IV3;
+    h[4] = B2S_IV4; h[5] = B2S_IV5; h[6] = B2S_IV6; h[7] = B2S_IV7;
+}
+
+// A 32-bit word taken mod 2^31-1 (core/fields/m31.rs:58-60 applied to a u32).
+__device__ __forceinline__ uint32_t reduce_word_m31(uint32_t w) {
+    uint32_t s = (w & P) + (w >> 31);
+    return umin32(s, s - P);
+}
+
+__device__ __forceinline__ void store_hash(uint32_t* __restrict__ out, size_t i, const uint32_t h[8], bool m31_out) {
+    uint32_t r[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) r[k] = m31_out ? reduce_word_m31(h[k]) : h[k];
+    uint4* o = reinterpret_cast<uint4*>(out + 8 * i);
+    o[0] = make_uint4(r[0], r[1], r[2], r[3]);
+    o[1] = make_uint4(r[4], r[5], r[6], r[7]);
+}
+
+__global__ void __launch_bounds__(256) merkle_layer_kernel(int log_size, const uint32_t* __restrict__ prev,
+                                                           const uint32_t* const* __restrict__ cols, int ncols,
+                                                           int m31_out, uint32_t* __restrict__ out) {
+    const size_t n = (size_t)1 << log_size;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    uint32_t h[8], m[16];
+    blake2s_init(h);
+    const uint32_t total = (prev ? 64u : 0u) + 4u * (uint32_t)ncols;
+    uint32_t t = 0;
+    int c = 0;
+    if (prev) {
+        const uint4* p = reinterpret_cast<const uint4*>(prev + 16 * i);
+        uint4 a = p[0], b = p[1], cc = p[2], d = p[3];
+        m[0] = a.x; m[1] = a.y; m[2] = a.z; m[3] = a.w; m[4] = b.x; m[5] = b.y; m[6] = b.z; m[7] = b.w;
+        m[8] = cc.x; m[9] = cc.y; m[10] = cc.z; m[11] = cc.w; m[12] = d.x; m[13] = d.y; m[14] = d.z; m[15] = d.w;
+        t = 64;
+        blake2s_compress(h, m, t, total == 64u);
+    }
+    // full blocks of 16 columns that are not the last block
+    while (ncols - c > 16) {
+#pragma unroll
+        for (int k = 0; k < 16; k++) m[k] = cols[c + k][i];
+        c += 16;
+        t += 64;
+        blake2s_compress(h, m, t, false);
+    }
+    // last block: 1..16 remaining columns, or the empty message when nothing was hashed yet
+    if (ncols - c > 0 || total == 0u) {
+        int rem = ncols - c;
+#pragma unroll
+        for (int k = 0; k < 16; k++) m[k] = (k < rem) ? cols[c + k][i] : 0u;
+        t += 4u * (uint32_t)rem;
+        blake2s_compress(h, m, t, true);
+    }
+    store_hash(out, i, h, m31_out != 0);
+}
+
+// Grind: thread `lo` tests nonce (hi << 32) | lo; the minimum passing lo is kept.
+__global__ void grind_kernel(uint32_t d0, uint32_t d1, uint32_t d2, uint32_t d3, uint32_t d4, uint32_t d5, uint32_t d6,
+                             uint32_t d7, uint32_t hi, int pow_bits, int m31_out, unsigned int* __restrict__ best) {
+    uint32_t lo = blockIdx.x * blockDim.x + threadIdx.x;
+    uint32_t h[8], m[16] = {d0, d1, d2, d3, d4, d5, d6, d7, lo, hi, 0, 0, 0, 0, 0, 0};
+    blake2s_init(h);
+    blake2s_compress(h, m, 40u, true);
+    uint32_t w = m31_out ? reduce_word_m31(h[0]) : h[0];
+    int tz = w ? __ffs(w) - 1 : 32;
+    if (tz >= pow_bits) atomicMin(best, lo);
+}
+
+}  // namespace zk
+
+using namespace zk;
+
+extern "C" {
+
+int zkb_merkle_layer(zkb_ctx* ctx, int log_size, const uint32_t* prev, const uint32_t* const* cols, int ncols,
+                     int m31_out, uint32_t* out) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, log_size >= 0 && log_size <= 30 && ncols >= 0 && out != nullptr);
+    ZKB_CHECK_ARG(ctx, ncols == 0 || cols != nullptr);
+    ZKB_CHECK_ARG(ctx, ((uintptr_t)out & 15) == 0 && ((uintptr_t)prev & 15) == 0);
+    DeviceGuard g(ctx);
+    void** d_cols = nullptr;
+    if (ncols) {
+        int rc = stage_ptrs(ctx, (const void* const*)cols, ncols, &d_cols);
+        if (rc) return rc;
+    }
+    size_t n = (size_t)1 << log_size;
+    unsigned threads = n < 256 ? 32 : 256;
+    unsigned blocks = (unsigned)((n + threads - 1) / threads);
+    merkle_layer_kernel<<<blocks, threads, 0, ctx->stream>>>(log_size, prev, (const uint32_t* const*)d_cols, ncols, m31_out,
+                                                             out);
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
+}
+
+int zkb_grind(zkb_ctx* ctx, const uint32_t h_prefixed_digest[8], int pow_bits, int m31_out, uint64_t* h_nonce) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, h_prefixed_digest != nullptr && h_nonce != nullptr && pow_bits >= 0 && pow_bits <= 32);
+    DeviceGuard g(ctx);
+    const uint32_t* d = h_prefixed_digest;
+    const unsigned LOW = 1u << 20;
+    // Bounded search: hi values are tried in order; a miss over 2^20 nonces has probability
+    // (1 - 2^-pow_bits)^(2^20), so the bound of 2^12 rounds is never reached for pow_bits <= 32
+    // in practice and keeps the loop finite.
+    for (uint32_t hi = 0; hi < (1u << 12); hi++) {
+        unsigned int init = 0xffffffffu;
+        ZKB_CUDA(ctx, cudaMemcpyAsync(ctx->ticket + 8, &init, 4, cudaMemcpyHostToDevice, ctx->stream));
+        grind_kernel<<<LOW / 256, 256, 0, ctx->stream>>>(d[0], d[1], d[2], d[3], d[4], d[5], d[6], d[7], hi, pow_bits,
+                                                         m31_out, ctx->ticket + 8);
+        ZKB_LAUNCH_CHECK(ctx);
+        unsigned int best = 0;
+        ZKB_CUDA(ctx, cudaMemcpyAsync(&best, ctx->ticket + 8, 4, cudaMemcpyDeviceToHost, ctx->stream));
+        ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        if (best != 0xffffffffu) {
+            *h_nonce = ((uint64_t)hi << 32) | best;
+            return ZKB_OK;
+        }
+    }
+    return set_error(ctx, ZKB_ETIMEOUT, "zkb_grind: no nonce found in 2^32 attempts");
+}
+
+}  // extern "C"

@@ -1,0 +1,289 @@
+// Context lifetime, device memory helpers, the twiddle tower and small utilities.
+#include <cstdarg>
+#include <vector>
+
+#include "common.cuh"
+
+namespace zk {
+
+int set_error(zkb_ctx* ctx, int code, const char* fmt, ...) {
+    if (ctx) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(ctx->err, sizeof(ctx->err), fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+int stage_ptrs(zkb_ctx* ctx, const void* const* h_ptrs, int n, void*** out) {
+    if (n < 0 || (size_t)n > ctx->ring_cap) return set_error(ctx, ZKB_EINVAL, "stage_ptrs: %d pointers exceed the staging ring", n);
+    if (n == 0) { *out = ctx->d_ring; return ZKB_OK; }
+    if (ctx->ring_pos + (size_t)n > ctx->ring_cap) {
+        // Wrap: earlier slots may still be in flight, so drain the stream first.
+        ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        ctx->ring_pos = 0;
+    }
+    void** h = ctx->h_ring + ctx->ring_pos;
+    void** d = ctx->d_ring + ctx->ring_pos;
+    memcpy(h, h_ptrs, (size_t)n * sizeof(void*));
+    ZKB_CUDA(ctx, cudaMemcpyAsync(d, h, (size_t)n * sizeof(void*), cudaMemcpyHostToDevice, ctx->stream));
+    ctx->ring_pos += (size_t)n;
+    *out = d;
+    return ZKB_OK;
+}
+
+// G * 2^b for the generator G of the order-2^31 circle group over M31
+// (nitroo/crates/stwo/src/core/circle.rs:202-205).
+__constant__ cpoint c_gen_pow2[31];
+
+__device__ __forceinline__ cpoint circle_point_from_index(uint32_t idx) {
+    cpoint r{1u, 0u};
+#pragma unroll 1
+    for (int b = 0; b < 31; b++)
+        if ((idx >> b) & 1u) r = cpoint_add(r, c_gen_pow2[b]);
+    return r;
+}
+
+// tw[t], t in [1, len): k = floor(log2 t) + 1, h = t - 2^(k-1);
+// value = x( half_odds(k).at(bitrev_{k-1}(h)) ), index 2^(29-k) + j * 2^(31-k).
+__global__ void twiddle_tower_kernel(uint32_t* __restrict__ tw, uint32_t* __restrict__ itw, size_t len) {
+    size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= len) return;
+    if (t == 0) { tw[0] = 1u; itw[0] = 1u; return; }
+    int k = 32 - __clz((uint32_t)t);
+    uint32_t h = (uint32_t)t - (1u << (k - 1));
+    uint32_t j = (k > 1) ? (__brev(h) >> (32 - (k - 1))) : 0u;
+    uint32_t index = (1u << (29 - k)) + (j << (31 - k));
+    cpoint p = circle_point_from_index(index & 0x7fffffffu);
+    tw[t] = p.x;
+    itw[t] = m31_inv(p.x);
+}
+
+__global__ void gather_multi_kernel(const uint32_t* const* __restrict__ cols, int ncols, const uint32_t* __restrict__ idx,
+                                    int nidx, uint32_t* __restrict__ out) {
+    size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (size_t)ncols * nidx) return;
+    int i = (int)(t / ncols), c = (int)(t % ncols);
+    out[t] = cols[c][idx[i]];
+}
+
+}  // namespace zk
+
+using namespace zk;
+
+extern "C" {
+
+int zkb_init(int device, int max_log_size, zkb_ctx** out) {
+    if (!out) return ZKB_EINVAL;
+    *out = nullptr;
+    if (max_log_size < 3 || max_log_size > 28) return ZKB_EINVAL;
+    zkb_ctx* ctx = new (std::nothrow) zkb_ctx();
+    if (!ctx) return ZKB_ENOMEM;
+    ctx->device = device;
+    ctx->max_log = max_log_size;
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) { delete ctx; return ZKB_ECUDA; }
+    auto fail = [&](int code) { zkb_destroy(ctx); return code; };
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) return fail(ZKB_ECUDA);
+    ctx->tw_len = (size_t)1 << (max_log_size - 1);
+    if (cudaMalloc(&ctx->tw, ctx->tw_len * 4) != cudaSuccess) return fail(ZKB_ENOMEM);
+    if (cudaMalloc(&ctx->itw, ctx->tw_len * 4) != cudaSuccess) return fail(ZKB_ENOMEM);
+    ctx->ring_cap = RING_SLOTS;
+    if (cudaMallocHost(&ctx->h_ring, ctx->ring_cap * sizeof(void*)) != cudaSuccess) return fail(ZKB_ENOMEM);
+    if (cudaMalloc(&ctx->d_ring, ctx->ring_cap * sizeof(void*)) != cudaSuccess) return fail(ZKB_ENOMEM);
+    ctx->scratch_words = SCRATCH_WORDS;
+    if (cudaMalloc(&ctx->scratch, ctx->scratch_words * 4) != cudaSuccess) return fail(ZKB_ENOMEM);
+    if (cudaMalloc(&ctx->ticket, 64) != cudaSuccess) return fail(ZKB_ENOMEM);
+    if (cudaMemsetAsync(ctx->ticket, 0, 64, ctx->stream) != cudaSuccess) return fail(ZKB_ECUDA);
+    if (cudaMallocHost(&ctx->h_small, SMALL_WORDS * 4) != cudaSuccess) return fail(ZKB_ENOMEM);
+
+    // Generator doublings on the host, then the tower on the device.
+    cpoint g[31];
+    g[0] = {2u, 1268011823u};
+    for (int b = 1; b < 31; b++) g[b] = cpoint_add(g[b - 1], g[b - 1]);
+    if (cudaMemcpyToSymbolAsync(c_gen_pow2, g, sizeof(g), 0, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) return fail(ZKB_ECUDA);
+    unsigned blocks = (unsigned)((ctx->tw_len + 255) / 256);
+    twiddle_tower_kernel<<<blocks, 256, 0, ctx->stream>>>(ctx->tw, ctx->itw, ctx->tw_len);
+    if (cudaGetLastError() != cudaSuccess) return fail(ZKB_ECUDA);
+    if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return fail(ZKB_ECUDA);
+    *out = ctx;
+    return ZKB_OK;
+}
+
+int zkb_destroy(zkb_ctx* ctx) {
+    if (!ctx) return ZKB_EINVAL;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (ctx->tw) cudaFree(ctx->tw);
+    if (ctx->itw) cudaFree(ctx->itw);
+    if (ctx->h_ring) cudaFreeHost(ctx->h_ring);
+    if (ctx->d_ring) cudaFree(ctx->d_ring);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->ticket) cudaFree(ctx->ticket);
+    if (ctx->h_small) cudaFreeHost(ctx->h_small);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return ZKB_OK;
+}
+
+const char* zkb_last_error(zkb_ctx* ctx) { return ctx ? ctx->err : "null context"; }
+
+int zkb_sync(zkb_ctx* ctx) {
+    if (!ctx) return ZKB_EINVAL;
+    DeviceGuard g(ctx);
+    ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return ZKB_OK;
+}
+
+int zkb_get_stream(zkb_ctx* ctx, void** stream) {
+    if (!ctx || !stream) return ZKB_EINVAL;
+    *stream = (void*)ctx->stream;
+    return ZKB_OK;
+}
+
+int zkb_max_log_size(zkb_ctx* ctx) { return ctx ? ctx->max_log : ZKB_EINVAL; }
+
+int zkb_malloc(zkb_ctx* ctx, size_t bytes, void** dptr) {
+    if (!ctx || !dptr) return ZKB_EINVAL;
+    DeviceGuard g(ctx);
+    *dptr = nullptr;
+    if (bytes == 0) return ZKB_OK;
+    ZKB_CUDA(ctx, cudaMalloc(dptr, bytes));
+    return ZKB_OK;
+}
+
+int zkb_free(zkb_ctx* ctx, void* dptr) {
+    if (!ctx) return ZKB_EINVAL;
+    if (!dptr) return ZKB_OK;
+    DeviceGuard g(ctx);
+    ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ZKB_CUDA(ctx, cudaFree(dptr));
+    return ZKB_OK;
+}
+
+int zkb_memset_zero(zkb_ctx* ctx, void* dptr, size_t bytes) {
+    if (!ctx) return ZKB_EINVAL;
+    if (bytes == 0) return ZKB_OK;
+    ZKB_CHECK_ARG(ctx, dptr != nullptr);
+    DeviceGuard g(ctx);
+    ZKB_CUDA(ctx, cudaMemsetAsync(dptr, 0, bytes, ctx->stream));
+    return ZKB_OK;
+}
+
+int zkb_h2d(zkb_ctx* ctx, void* dptr, const void* h_src, size_t bytes) {
+    if (!ctx) return ZKB_EINVAL;
+    if (bytes == 0) return ZKB_OK;
+    ZKB_CHECK_ARG(ctx, dptr != nullptr && h_src != nullptr);
+    DeviceGuard g(ctx);
+    ZKB_CUDA(ctx, cudaMemcpyAsync(dptr, h_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return ZKB_OK;
+}
+
+int zkb_d2h(zkb_ctx* ctx, void* h_dst, const void* dptr, size_t bytes) {
+    if (!ctx) return ZKB_EINVAL;
+    if (bytes == 0) return ZKB_OK;
+    ZKB_CHECK_ARG(ctx, dptr != nullptr && h_dst != nullptr);
+    DeviceGuard g(ctx);
+    ZKB_CUDA(ctx, cudaMemcpyAsync(h_dst, dptr, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return ZKB_OK;
+}
+
+int zkb_h2d_async(zkb_ctx* ctx, void* dptr, const void* h_pinned_src, size_t bytes) {
+    if (!ctx) return ZKB_EINVAL;
+    if (bytes == 0) return ZKB_OK;
+    ZKB_CHECK_ARG(ctx, dptr != nullptr && h_pinned_src != nullptr);
+    DeviceGuard g(ctx);
+    ZKB_CUDA(ctx, cudaMemcpyAsync(dptr, h_pinned_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return ZKB_OK;
+}
+
+int zkb_d2h_async(zkb_ctx* ctx, void* h_pinned_dst, const void* dptr, size_t bytes) {
+    if (!ctx) return ZKB_EINVAL;
+    if (bytes == 0) return ZKB_OK;
+    ZKB_CHECK_ARG(ctx, dptr != nullptr && h_pinned_dst != nullptr);
+    DeviceGuard g(ctx);
+    ZKB_CUDA(ctx, cudaMemcpyAsync(h_pinned_dst, dptr, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    return ZKB_OK;
+}
+
+int zkb_d2d(zkb_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (!ctx) return ZKB_EINVAL;
+    if (bytes == 0) return ZKB_OK;
+    ZKB_CHECK_ARG(ctx, dst != nullptr && src != nullptr);
+    DeviceGuard g(ctx);
+    ZKB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    return ZKB_OK;
+}
+
+int zkb_host_alloc_pinned(zkb_ctx* ctx, size_t bytes, void** h_ptr) {
+    if (!ctx || !h_ptr) return ZKB_EINVAL;
+    DeviceGuard g(ctx);
+    ZKB_CUDA(ctx, cudaMallocHost(h_ptr, bytes ? bytes : 1));
+    return ZKB_OK;
+}
+
+int zkb_host_free_pinned(zkb_ctx* ctx, void* h_ptr) {
+    if (!ctx) return ZKB_EINVAL;
+    if (!h_ptr) return ZKB_OK;
+    DeviceGuard g(ctx);
+    ZKB_CUDA(ctx, cudaFreeHost(h_ptr));
+    return ZKB_OK;
+}
+
+int zkb_gather_multi(zkb_ctx* ctx, const uint32_t* const* cols, int ncols, const uint32_t* h_idx, int nidx,
+                     uint32_t* h_out) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, ncols >= 0 && nidx >= 0);
+    if (ncols == 0 || nidx == 0) return ZKB_OK;
+    ZKB_CHECK_ARG(ctx, cols != nullptr && h_idx != nullptr && h_out != nullptr);
+    size_t total = (size_t)ncols * nidx;
+    ZKB_CHECK_ARG(ctx, total + (size_t)nidx <= ctx->scratch_words);
+    DeviceGuard g(ctx);
+    void** d_cols;
+    int rc = stage_ptrs(ctx, (const void* const*)cols, ncols, &d_cols);
+    if (rc) return rc;
+    uint32_t* d_idx = ctx->scratch;
+    uint32_t* d_out = ctx->scratch + nidx;
+    ZKB_CUDA(ctx, cudaMemcpyAsync(d_idx, h_idx, (size_t)nidx * 4, cudaMemcpyHostToDevice, ctx->stream));
+    gather_multi_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>((const uint32_t* const*)d_cols, ncols,
+                                                                                  d_idx, nidx, d_out);
+    ZKB_LAUNCH_CHECK(ctx);
+    ZKB_CUDA(ctx, cudaMemcpyAsync(h_out, d_out, total * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return ZKB_OK;
+}
+
+int zkb_twiddles_d2h(zkb_ctx* ctx, int log_size, uint32_t* h_tw, uint32_t* h_itw) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, h_tw != nullptr && log_size >= 0 && log_size <= ctx->max_log - 1);
+    DeviceGuard g(ctx);
+    // Level j of the reference layout is T_{log_size - j}: 2^(log_size-j-1) words at offset
+    // 2^log_size - 2^(log_size-j); the last word is the padding value 1.
+    size_t n = (size_t)1 << log_size;
+    for (int j = 0; j < log_size; j++) {
+        int k = log_size - j;
+        size_t len = (size_t)1 << (k - 1), off = n - ((size_t)1 << k);
+        ZKB_CUDA(ctx, cudaMemcpyAsync(h_tw + off, ctx->tw + len, len * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        if (h_itw) ZKB_CUDA(ctx, cudaMemcpyAsync(h_itw + off, ctx->itw + len, len * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    h_tw[n - 1] = 1u;
+    if (h_itw) h_itw[n - 1] = 1u;
+    return ZKB_OK;
+}
+
+int zkb_secure_powers(zkb_ctx* ctx, const uint32_t h_felt[4], size_t n, uint32_t* h_out) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, h_felt != nullptr && (n == 0 || h_out != nullptr));
+    qm31 f{{h_felt[0], h_felt[1], h_felt[2], h_felt[3]}}, acc = qm31_one();
+    for (size_t i = 0; i < n; i++) {
+        for (int k = 0; k < 4; k++) h_out[4 * i + k] = acc.c[k];
+        acc = qm31_mul(acc, f);
+    }
+    return ZKB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,143 @@
+// FriOps: fold_line and fold_circle_into_line on secure columns in coordinate layout.
+//
+// Both fold adjacent pairs (2i, 2i+1) of a bit-reversed evaluation:
+//   f0 = a + b,  f1 = (a - b) * t^-1,  folded = f0 + alpha * f1
+// with t the x-coordinate (line) or y-coordinate (circle) of the pair's domain point
+// (nitroo/crates/stwo/src/prover/backend/cpu/fri.rs:67-123). The inverse coordinates come from the
+// inverse twiddle tower: pair i of the line domain Coset::half_odds(k) uses T_k^-1[i]; pair i of
+// the canonic circle domain of log size L uses the y of point i of Coset::half_odds(L-1).
+#include "common.cuh"
+
+namespace zk {
+
+struct Secure4 { uint32_t* c[4]; };
+struct Secure4C { const uint32_t* c[4]; };
+
+__device__ __forceinline__ qm31 fold_pair(const Secure4C& in, size_t i, uint32_t itw, qm31 alpha) {
+    qm31 a, b;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        uint2 v = reinterpret_cast<const uint2*>(in.c[k])[i];
+        a.c[k] = v.x;
+        b.c[k] = v.y;
+    }
+    qm31 f0 = qm31_add(a, b);
+    qm31 f1 = qm31_mul_m31(qm31_sub(a, b), itw);
+    return qm31_add(f0, qm31_mul(alpha, f1));
+}
+
+__global__ void __launch_bounds__(256) fold_line_kernel(Secure4 out, Secure4C in, int log_n, qm31 alpha,
+                                                        const uint32_t* __restrict__ itw) {
+    size_t half = (size_t)1 << (log_n - 1);
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= half) return;
+    uint32_t t = itw[half + i];  // T_k^-1 starts at 2^(k-1)
+    qm31 r = fold_pair(in, i, t, alpha);
+#pragma unroll
+    for (int k = 0; k < 4; k++) out.c[k][i] = r.c[k];
+}
+
+// log_n == 1, 2 of the line fold and small circle domains need points that are not in the tower
+// (T_k holds only half of each coset and starts at k = 1); they are passed in by the host.
+__global__ void fold_small_kernel(Secure4 out, Secure4C in, int n_out, qm31 alpha, qm31 alpha_sq, int accumulate,
+                                  uint32_t it0, uint32_t it1, uint32_t it2, uint32_t it3) {
+    int i = threadIdx.x;
+    if (i >= n_out) return;
+    uint32_t its[4] = {it0, it1, it2, it3};
+    qm31 r = fold_pair(in, i, its[i], alpha);
+    if (accumulate) {
+        qm31 d{{out.c[0][i], out.c[1][i], out.c[2][i], out.c[3][i]}};
+        r = qm31_add(qm31_mul(d, alpha_sq), r);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; k++) out.c[k][i] = r.c[k];
+}
+
+__global__ void __launch_bounds__(256) fold_circle_kernel(Secure4 dst, Secure4C src, int log_n_src, qm31 alpha,
+                                                          qm31 alpha_sq, const uint32_t* __restrict__ itw) {
+    size_t half = (size_t)1 << (log_n_src - 1);
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= half) return;
+    uint32_t ix, iy;
+    half_coset_point(itw, log_n_src, (uint32_t)i, ix, iy);
+    qm31 f = fold_pair(src, i, iy, alpha);
+    qm31 d{{dst.c[0][i], dst.c[1][i], dst.c[2][i], dst.c[3][i]}};
+    qm31 r = qm31_add(qm31_mul(d, alpha_sq), f);
+#pragma unroll
+    for (int k = 0; k < 4; k++) dst.c[k][i] = r.c[k];
+}
+
+}  // namespace zk
+
+using namespace zk;
+
+// Host-side point of the order-2^31 group: index -> (x, y).
+static cpoint host_point(uint32_t index) {
+    cpoint g{2u, 1268011823u}, r{1u, 0u};
+    for (int b = 0; b < 31; b++) {
+        if ((index >> b) & 1u) r = cpoint_add(r, g);
+        g = cpoint_add(g, g);
+    }
+    return r;
+}
+static uint32_t host_bitrev(uint32_t i, int bits) {
+    uint32_t r = 0;
+    for (int b = 0; b < bits; b++) r |= ((i >> b) & 1u) << (bits - 1 - b);
+    return r;
+}
+
+extern "C" {
+
+int zkb_fold_line(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* const in[4], int log_n,
+                  const uint32_t h_alpha[4]) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, out && in && h_alpha && log_n >= 1 && log_n <= ctx->max_log - 1);
+    Secure4 o;
+    Secure4C s;
+    for (int k = 0; k < 4; k++) {
+        ZKB_CHECK_ARG(ctx, out[k] != nullptr && in[k] != nullptr && ((uintptr_t)in[k] & 7) == 0);
+        o.c[k] = out[k];
+        s.c[k] = in[k];
+    }
+    qm31 alpha{{h_alpha[0], h_alpha[1], h_alpha[2], h_alpha[3]}};
+    DeviceGuard g(ctx);
+    size_t half = (size_t)1 << (log_n - 1);
+    fold_line_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n, alpha, ctx->itw);
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
+}
+
+int zkb_fold_circle_into_line(zkb_ctx* ctx, uint32_t* const dst[4], const uint32_t* const src[4], int log_n_src,
+                              const uint32_t h_alpha[4]) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, dst && src && h_alpha && log_n_src >= 1 && log_n_src <= ctx->max_log);
+    Secure4 o;
+    Secure4C s;
+    for (int k = 0; k < 4; k++) {
+        ZKB_CHECK_ARG(ctx, dst[k] != nullptr && src[k] != nullptr && ((uintptr_t)src[k] & 7) == 0);
+        o.c[k] = dst[k];
+        s.c[k] = src[k];
+    }
+    qm31 alpha{{h_alpha[0], h_alpha[1], h_alpha[2], h_alpha[3]}};
+    qm31 alpha_sq = qm31_sqr(alpha);
+    DeviceGuard g(ctx);
+    if (log_n_src <= 2) {
+        // Points i of Coset::half_odds(log_n_src - 1), bit-reversed: index 2^(31-(L-1)-2) + j * 2^(31-(L-1)).
+        int hl = log_n_src - 1;
+        uint32_t it[4] = {0, 0, 0, 0};
+        for (uint32_t i = 0; i < (1u << hl); i++) {
+            uint32_t j = host_bitrev(i, hl);
+            cpoint p = host_point(((1u << (29 - hl)) + (j << (31 - hl))) & 0x7fffffffu);
+            it[i] = m31_inv(p.y);
+        }
+        fold_small_kernel<<<1, 32, 0, ctx->stream>>>(o, s, 1 << hl, alpha, alpha_sq, 1, it[0], it[1], it[2], it[3]);
+        ZKB_LAUNCH_CHECK(ctx);
+        return ZKB_OK;
+    }
+    size_t half = (size_t)1 << (log_n_src - 1);
+    fold_circle_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n_src, alpha, alpha_sq, ctx->itw);
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
+}
+
+}  // extern "C"

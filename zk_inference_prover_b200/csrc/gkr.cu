@@ -1,0 +1,252 @@
+// GkrOps / MleOps: eq evaluations, layer halving, sum-check round sums, fixing the first variable.
+// Multilinear columns are arrays of QM31 (16 bytes, one 128-bit access each); the numerators of a
+// LogUpMultiplicities layer are M31 words.
+//   nitroo/crates/stwo/src/prover/backend/cpu/lookups/gkr.rs:17-263
+//   nitroo/crates/stwo/src/prover/backend/cpu/lookups/mle.rs:13-46
+#include "common.cuh"
+
+namespace zk {
+
+__device__ __forceinline__ qm31 ldq(const uint32_t* __restrict__ p, size_t i) {
+    uint4 v = reinterpret_cast<const uint4*>(p)[i];
+    return {{v.x, v.y, v.z, v.w}};
+}
+__device__ __forceinline__ void stq(uint32_t* __restrict__ p, size_t i, qm31 v) {
+    reinterpret_cast<uint4*>(p)[i] = make_uint4(v.c[0], v.c[1], v.c[2], v.c[3]);
+}
+
+// out[x] = v * prod_k (bit_k(x) ? y[ny-1-k] : 1 - y[ny-1-k]) — the doubling recursion of
+// cpu/lookups/gkr.rs:216-231 unrolled per index. One stage per launch keeps it to one
+// multiplication per output: stage s turns 2^s values into 2^(s+1) using y[ny-1-s].
+__global__ void __launch_bounds__(256) eq_evals_stage_kernel(uint32_t* __restrict__ evals, size_t len, qm31 y) {
+    size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= len) return;
+    qm31 e = ldq(evals, j);
+    qm31 tmp = qm31_mul(e, y);
+    stq(evals, j + len, tmp);
+    stq(evals, j, qm31_sub(e, tmp));
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(256) next_layer_kernel(const uint32_t* __restrict__ num, const uint32_t* __restrict__ den,
+                                                         size_t half, uint32_t* __restrict__ num_out,
+                                                         uint32_t* __restrict__ den_out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= half) return;
+    qm31 d0 = ldq(den, 2 * i), d1 = ldq(den, 2 * i + 1);
+    if (KIND == ZKB_GKR_GRAND_PRODUCT) {
+        stq(den_out, i, qm31_mul(d0, d1));
+        return;
+    }
+    qm31 n;
+    if (KIND == ZKB_GKR_LOGUP_SINGLES) {
+        n = qm31_add(d0, d1);
+    } else if (KIND == ZKB_GKR_LOGUP_MULTIPLICITIES) {
+        uint2 m = reinterpret_cast<const uint2*>(num)[i];
+        n = qm31_add(qm31_mul_m31(d1, m.x), qm31_mul_m31(d0, m.y));
+    } else {
+        qm31 n0 = ldq(num, 2 * i), n1 = ldq(num, 2 * i + 1);
+        n = qm31_add(qm31_mul(d1, n0), qm31_mul(d0, n1));
+    }
+    stq(num_out, i, n);
+    stq(den_out, i, qm31_mul(d0, d1));
+}
+
+__device__ __forceinline__ qm31 warp_sum(qm31 v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        qm31 o;
+#pragma unroll
+        for (int k = 0; k < 4; k++) o.c[k] = __shfl_down_sync(0xffffffffu, v.c[k], off);
+        v = qm31_add(v, o);
+    }
+    return v;
+}
+
+// Per-block partial sums land in `partials` (8 words per block); the block that takes the last
+// ticket adds them up and writes the 8 result words. Addition mod p is exact, so the order of
+// the reduction does not change the result.
+template <int KIND>
+__global__ void __launch_bounds__(256) gkr_sum_kernel(const uint32_t* __restrict__ num, const uint32_t* __restrict__ den,
+                                                      size_t n_terms, const uint32_t* __restrict__ eq_evals, qm31 lambda,
+                                                      uint32_t* __restrict__ partials, unsigned int* __restrict__ ticket,
+                                                      uint32_t* __restrict__ result) {
+    qm31 s0 = qm31_zero(), s2 = qm31_zero();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_terms; i += (size_t)gridDim.x * blockDim.x) {
+        qm31 d00 = ldq(den, 2 * i), d01 = ldq(den, 2 * i + 1);
+        qm31 d10 = ldq(den, 2 * (n_terms + i)), d11 = ldq(den, 2 * (n_terms + i) + 1);
+        qm31 d20 = qm31_sub(qm31_dbl(d10), d00), d21 = qm31_sub(qm31_dbl(d11), d01);
+        qm31 t0, t2;
+        if (KIND == ZKB_GKR_GRAND_PRODUCT) {
+            t0 = qm31_mul(d00, d01);
+            t2 = qm31_mul(d20, d21);
+        } else {
+            qm31 n0, n2;
+            if (KIND == ZKB_GKR_LOGUP_SINGLES) {
+                n0 = qm31_add(d00, d01);
+                n2 = qm31_add(d20, d21);
+            } else if (KIND == ZKB_GKR_LOGUP_MULTIPLICITIES) {
+                uint2 a = reinterpret_cast<const uint2*>(num)[i];
+                uint2 b = reinterpret_cast<const uint2*>(num)[n_terms + i];
+                uint32_t n20 = m31_sub(m31_dbl(b.x), a.x), n21 = m31_sub(m31_dbl(b.y), a.y);
+                n0 = qm31_add(qm31_mul_m31(d01, a.x), qm31_mul_m31(d00, a.y));
+                n2 = qm31_add(qm31_mul_m31(d21, n20), qm31_mul_m31(d20, n21));
+            } else {
+                qm31 n00 = ldq(num, 2 * i), n01 = ldq(num, 2 * i + 1);
+                qm31 n10 = ldq(num, 2 * (n_terms + i)), n11 = ldq(num, 2 * (n_terms + i) + 1);
+                qm31 n20 = qm31_sub(qm31_dbl(n10), n00), n21 = qm31_sub(qm31_dbl(n11), n01);
+                n0 = qm31_add(qm31_mul(d01, n00), qm31_mul(d00, n01));
+                n2 = qm31_add(qm31_mul(d21, n20), qm31_mul(d20, n21));
+            }
+            t0 = qm31_add(n0, qm31_mul(lambda, qm31_mul(d00, d01)));
+            t2 = qm31_add(n2, qm31_mul(lambda, qm31_mul(d20, d21)));
+        }
+        qm31 e = ldq(eq_evals, i);
+        s0 = qm31_add(s0, qm31_mul(e, t0));
+        s2 = qm31_add(s2, qm31_mul(e, t2));
+    }
+    __shared__ uint32_t sh[8][8];
+    __shared__ bool is_last;
+    s0 = warp_sum(s0);
+    s2 = warp_sum(s2);
+    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < 4; k++) { sh[warp][k] = s0.c[k]; sh[warp][4 + k] = s2.c[k]; }
+    }
+    __syncthreads();
+    if (threadIdx.x < 8) {
+        uint32_t acc = 0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); w++) acc = m31_add(acc, sh[w][threadIdx.x]);
+        partials[8 * blockIdx.x + threadIdx.x] = acc;
+        __threadfence();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned int t = atomicAdd(ticket, 1u);
+        is_last = (t == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (is_last) {
+        __threadfence();
+        if (threadIdx.x < 8) {
+            uint32_t acc = 0;
+            for (unsigned b = 0; b < gridDim.x; b++) acc = m31_add(acc, __ldcg(&partials[8 * b + threadIdx.x]));
+            result[threadIdx.x] = acc;
+        }
+        if (threadIdx.x == 0) *ticket = 0u;  // ready for the next launch
+    }
+}
+
+// out[i] = in[i] + r * (in[i + half] - in[i])
+__global__ void __launch_bounds__(256) mle_fix_qm31_kernel(const uint32_t* __restrict__ in, size_t half, qm31 r,
+                                                           uint32_t* __restrict__ out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= half) return;
+    qm31 a = ldq(in, i), b = ldq(in, i + half);
+    stq(out, i, qm31_add(qm31_mul(r, qm31_sub(b, a)), a));
+}
+__global__ void __launch_bounds__(256) mle_fix_m31_kernel(const uint32_t* __restrict__ in, size_t half, qm31 r,
+                                                          uint32_t* __restrict__ out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= half) return;
+    uint32_t a = in[i], b = in[i + half];
+    qm31 v = qm31_mul_m31(r, m31_sub(b, a));
+    v.c[0] = m31_add(v.c[0], a);
+    stq(out, i, v);
+}
+
+}  // namespace zk
+
+using namespace zk;
+
+static inline qm31 q4(const uint32_t* p) { return qm31{{p[0], p[1], p[2], p[3]}}; }
+
+extern "C" {
+
+int zkb_gkr_eq_evals(zkb_ctx* ctx, const uint32_t* h_y, int ny, const uint32_t h_v[4], uint32_t* out) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, ny >= 0 && ny <= 28 && h_v && out && (ny == 0 || h_y) && ((uintptr_t)out & 15) == 0);
+    DeviceGuard g(ctx);
+    ZKB_CUDA(ctx, cudaMemcpyAsync(out, h_v, 16, cudaMemcpyHostToDevice, ctx->stream));
+    for (int s = 0; s < ny; s++) {
+        size_t len = (size_t)1 << s;
+        eq_evals_stage_kernel<<<(unsigned)((len + 255) / 256), 256, 0, ctx->stream>>>(out, len, q4(h_y + 4 * (ny - 1 - s)));
+        ZKB_LAUNCH_CHECK(ctx);
+    }
+    return ZKB_OK;
+}
+
+int zkb_gkr_next_layer(zkb_ctx* ctx, int kind, const uint32_t* num, const uint32_t* den, size_t n, uint32_t* num_out,
+                       uint32_t* den_out) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, kind >= 0 && kind <= 3 && den && den_out && n >= 2 && (n & (n - 1)) == 0);
+    ZKB_CHECK_ARG(ctx, kind == ZKB_GKR_GRAND_PRODUCT || num_out != nullptr);
+    ZKB_CHECK_ARG(ctx, (kind != ZKB_GKR_LOGUP_GENERIC && kind != ZKB_GKR_LOGUP_MULTIPLICITIES) || num != nullptr);
+    ZKB_CHECK_ARG(ctx, ((uintptr_t)den & 15) == 0 && ((uintptr_t)den_out & 15) == 0 && ((uintptr_t)num_out & 15) == 0);
+    DeviceGuard g(ctx);
+    size_t half = n / 2;
+    unsigned blocks = (unsigned)((half + 255) / 256);
+    switch (kind) {
+        case ZKB_GKR_GRAND_PRODUCT: next_layer_kernel<0><<<blocks, 256, 0, ctx->stream>>>(num, den, half, num_out, den_out); break;
+        case ZKB_GKR_LOGUP_GENERIC: next_layer_kernel<1><<<blocks, 256, 0, ctx->stream>>>(num, den, half, num_out, den_out); break;
+        case ZKB_GKR_LOGUP_MULTIPLICITIES: next_layer_kernel<2><<<blocks, 256, 0, ctx->stream>>>(num, den, half, num_out, den_out); break;
+        default: next_layer_kernel<3><<<blocks, 256, 0, ctx->stream>>>(num, den, half, num_out, den_out); break;
+    }
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
+}
+
+int zkb_gkr_sum(zkb_ctx* ctx, int kind, const uint32_t* num, const uint32_t* den, size_t n, const uint32_t* eq_evals,
+                const uint32_t h_lambda[4], uint32_t h_out[8]) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, kind >= 0 && kind <= 3 && den && eq_evals && h_lambda && h_out && n >= 2 && (n & (n - 1)) == 0);
+    ZKB_CHECK_ARG(ctx, (kind != ZKB_GKR_LOGUP_GENERIC && kind != ZKB_GKR_LOGUP_MULTIPLICITIES) || num != nullptr);
+    DeviceGuard g(ctx);
+    size_t n_terms = n / 4;
+    if (n_terms == 0) {
+        // A one-variable layer: sum_as_poly_in_first_variable is never asked for it by the
+        // protocol (n_variables of the oracle would be 0); keep the call well defined.
+        memset(h_out, 0, 32);
+        return ZKB_OK;
+    }
+    unsigned blocks = (unsigned)((n_terms + 255) / 256);
+    if (blocks > 148u * 8u) blocks = 148u * 8u;
+    uint32_t* partials = ctx->scratch;
+    uint32_t* result = ctx->scratch + 8 * (size_t)blocks;
+    qm31 lam = q4(h_lambda);
+    switch (kind) {
+        case ZKB_GKR_GRAND_PRODUCT: gkr_sum_kernel<0><<<blocks, 256, 0, ctx->stream>>>(num, den, n_terms, eq_evals, lam, partials, ctx->ticket, result); break;
+        case ZKB_GKR_LOGUP_GENERIC: gkr_sum_kernel<1><<<blocks, 256, 0, ctx->stream>>>(num, den, n_terms, eq_evals, lam, partials, ctx->ticket, result); break;
+        case ZKB_GKR_LOGUP_MULTIPLICITIES: gkr_sum_kernel<2><<<blocks, 256, 0, ctx->stream>>>(num, den, n_terms, eq_evals, lam, partials, ctx->ticket, result); break;
+        default: gkr_sum_kernel<3><<<blocks, 256, 0, ctx->stream>>>(num, den, n_terms, eq_evals, lam, partials, ctx->ticket, result); break;
+    }
+    ZKB_LAUNCH_CHECK(ctx);
+    ZKB_CUDA(ctx, cudaMemcpyAsync(ctx->h_small, result, 32, cudaMemcpyDeviceToHost, ctx->stream));
+    ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    memcpy(h_out, ctx->h_small, 32);
+    return ZKB_OK;
+}
+
+int zkb_mle_fix_qm31(zkb_ctx* ctx, const uint32_t* in, size_t n, const uint32_t h_r[4], uint32_t* out) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, in && out && h_r && n >= 2 && (n & (n - 1)) == 0);
+    ZKB_CHECK_ARG(ctx, ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0);
+    DeviceGuard g(ctx);
+    size_t half = n / 2;
+    mle_fix_qm31_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(in, half, q4(h_r), out);
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
+}
+
+int zkb_mle_fix_m31(zkb_ctx* ctx, const uint32_t* in, size_t n, const uint32_t h_r[4], uint32_t* out) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, in && out && h_r && n >= 2 && (n & (n - 1)) == 0 && ((uintptr_t)out & 15) == 0);
+    DeviceGuard g(ctx);
+    size_t half = n / 2;
+    mle_fix_m31_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(in, half, q4(h_r), out);
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,120 @@
+// PolyOps::eval_at_point / batch_eval_at_point: the value of each column's polynomial (FFT-basis
+// coefficients) at one QM31 circle point.
+//
+// The reference folds the coefficient array as a binary tree
+// (nitroo/crates/stwo/src/prover/backend/cpu/circle.rs:82-100, core/poly/utils.rs:11-23):
+// level k joins blocks of 2^k values as lhs + rhs * m_k with m_0 = y, m_1 = x, m_{k+1} = pi(m_k).
+// Field arithmetic is exact, so the tree is evaluated here in chunks: a CTA folds 2^CHUNK values
+// in shared memory, writes one partial, and the partials are folded again with the next factors.
+#include <vector>
+
+#include "common.cuh"
+
+namespace zk {
+
+constexpr int EVAL_CHUNK_LOG = 11;
+constexpr int EVAL_MAX_LEVELS = 32;
+
+struct EvalFactors { qm31 m[EVAL_MAX_LEVELS]; };
+
+// in: either a table of M31 columns (IS_BASE) or a dense [ncols][2^log_in] array of QM31.
+// out: dense [ncols][2^(log_in - chunk_log)] QM31.
+template <bool IS_BASE>
+__global__ void __launch_bounds__(256) eval_fold_kernel(const uint32_t* const* __restrict__ base_cols,
+                                                        const uint32_t* __restrict__ ext_in, int log_in, int chunk_log,
+                                                        int level0, EvalFactors f, uint32_t* __restrict__ out) {
+    __shared__ uint32_t s[4][1 << EVAL_CHUNK_LOG];
+    const uint32_t E = 1u << chunk_log;
+    const size_t chunk = blockIdx.x;
+    const int col = blockIdx.y;
+    const size_t n_in = (size_t)1 << log_in;
+    for (uint32_t e = threadIdx.x; e < E; e += blockDim.x) {
+        size_t idx = chunk * E + e;
+        if (IS_BASE) {
+            s[0][e] = base_cols[col][idx];
+            s[1][e] = 0; s[2][e] = 0; s[3][e] = 0;
+        } else {
+            uint4 v = reinterpret_cast<const uint4*>(ext_in)[(size_t)col * n_in + idx];
+            s[0][e] = v.x; s[1][e] = v.y; s[2][e] = v.z; s[3][e] = v.w;
+        }
+    }
+    __syncthreads();
+    for (int k = 0; k < chunk_log; k++) {
+        const qm31 m = f.m[level0 + k];
+        for (uint32_t t = threadIdx.x; t < (E >> (k + 1)); t += blockDim.x) {
+            uint32_t i0 = t << (k + 1), i1 = i0 + (1u << k);
+            qm31 a{{s[0][i0], s[1][i0], s[2][i0], s[3][i0]}}, b{{s[0][i1], s[1][i1], s[2][i1], s[3][i1]}};
+            qm31 r = qm31_add(a, qm31_mul(b, m));
+            s[0][i0] = r.c[0]; s[1][i0] = r.c[1]; s[2][i0] = r.c[2]; s[3][i0] = r.c[3];
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        size_t n_out = n_in >> chunk_log;
+        reinterpret_cast<uint4*>(out)[(size_t)col * n_out + chunk] = make_uint4(s[0][0], s[1][0], s[2][0], s[3][0]);
+    }
+}
+
+}  // namespace zk
+
+using namespace zk;
+
+extern "C" {
+
+int zkb_eval_at_point_cols(zkb_ctx* ctx, const uint32_t* const* coeffs, int ncols, int log_n, const uint32_t* h_point,
+                           uint32_t* h_out) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, ncols >= 0 && log_n >= 0 && log_n <= 30);
+    if (ncols == 0) return ZKB_OK;
+    ZKB_CHECK_ARG(ctx, coeffs && h_point && h_out);
+    DeviceGuard g(ctx);
+    // factors m_0 = y, m_1 = x, m_{k+1} = 2 m_k^2 - 1
+    EvalFactors f;
+    memset(&f, 0, sizeof(f));
+    qm31 x{{h_point[0], h_point[1], h_point[2], h_point[3]}}, y{{h_point[4], h_point[5], h_point[6], h_point[7]}};
+    f.m[0] = y;
+    for (int k = 1; k < log_n; k++) {
+        f.m[k] = x;
+        x = qm31_double_x(x);
+    }
+    // columns are processed in batches whose partials fit the scratch buffer (two ping-pong halves)
+    int first_chunk = log_n < EVAL_CHUNK_LOG ? log_n : EVAL_CHUNK_LOG;
+    size_t partials_per_col = (size_t)1 << (log_n - first_chunk);
+    size_t half_words = ctx->scratch_words / 2;
+    size_t max_cols = half_words / (4 * partials_per_col);
+    ZKB_CHECK_ARG(ctx, max_cols >= 1);
+    if (max_cols > 32768) max_cols = 32768;
+    for (int c0 = 0; c0 < ncols; c0 += (int)max_cols) {
+        int nc = ncols - c0 < (int)max_cols ? ncols - c0 : (int)max_cols;
+        void** d_cols;
+        int rc = stage_ptrs(ctx, (const void* const*)(coeffs + c0), nc, &d_cols);
+        if (rc) return rc;
+        uint32_t* bufA = ctx->scratch;
+        uint32_t* bufB = ctx->scratch + half_words;
+        int log_cur = log_n, level = 0;
+        {
+            unsigned threads = first_chunk >= 9 ? 256 : 32;
+            dim3 grid((unsigned)partials_per_col, nc);
+            eval_fold_kernel<true><<<grid, threads, 0, ctx->stream>>>((const uint32_t* const*)d_cols, nullptr, log_cur,
+                                                                      first_chunk, level, f, bufA);
+            ZKB_LAUNCH_CHECK(ctx);
+            log_cur -= first_chunk;
+            level += first_chunk;
+        }
+        while (log_cur > 0) {
+            int ch = log_cur < EVAL_CHUNK_LOG ? log_cur : EVAL_CHUNK_LOG;
+            unsigned threads = ch >= 9 ? 256 : 32;
+            dim3 grid(1u << (log_cur - ch), nc);
+            eval_fold_kernel<false><<<grid, threads, 0, ctx->stream>>>(nullptr, bufA, log_cur, ch, level, f, bufB);
+            ZKB_LAUNCH_CHECK(ctx);
+            log_cur -= ch;
+            level += ch;
+            uint32_t* t = bufA; bufA = bufB; bufB = t;
+        }
+        ZKB_CUDA(ctx, cudaMemcpyAsync(h_out + 4 * (size_t)c0, bufA, (size_t)nc * 16, cudaMemcpyDeviceToHost, ctx->stream));
+        ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    return ZKB_OK;
+}
+
+}  // extern "C"
