@@ -53,6 +53,12 @@ int zkb_sync(zkb_ctx* ctx);
 int zkb_get_stream(zkb_ctx* ctx, void** stream);
 int zkb_max_log_size(zkb_ctx* ctx);
 
+/* Timing helpers for benchmarks (no counterpart in the reference, which times with host clocks
+ * around synchronised calls, STWO/prover/lookups/gkr_prover.rs:81-150): CUDA events recorded on
+ * the context's stream. `slot` < 64. zkb_event_elapsed_ms synchronises on event `b`. */
+int zkb_event_record(zkb_ctx* ctx, int slot);
+int zkb_event_elapsed_ms(zkb_ctx* ctx, int a, int b, float* h_ms);
+
 /* ---- device columns (STWO/stwo_cuda/base_field_vec.rs:7-60, bindings.rs:84-103) ------------ */
 int zkb_malloc(zkb_ctx* ctx, size_t bytes, void** dptr);
 int zkb_free(zkb_ctx* ctx, void* dptr);

@@ -12,6 +12,7 @@ GKR_GRAND_PRODUCT, GKR_LOGUP_GENERIC, GKR_LOGUP_MULTIPLICITIES, GKR_LOGUP_SINGLE
 # Every symbol include/zkb200.h declares.
 EXPORTED_SYMBOLS = [
     "zkb_init", "zkb_destroy", "zkb_last_error", "zkb_sync", "zkb_get_stream", "zkb_max_log_size",
+    "zkb_event_record", "zkb_event_elapsed_ms",
     "zkb_malloc", "zkb_free", "zkb_memset_zero", "zkb_h2d", "zkb_d2h", "zkb_h2d_async", "zkb_d2h_async", "zkb_d2d",
     "zkb_host_alloc_pinned", "zkb_host_free_pinned", "zkb_gather_multi", "zkb_twiddles_d2h",
     "zkb_ifft_cols", "zkb_lde_cols", "zkb_eval_at_point_cols", "zkb_bit_reverse_m31", "zkb_bit_reverse_qm31",
@@ -139,6 +140,33 @@ class Context:
 
     def sync(self):
         self._check(self.lib.zkb_sync(self.h))
+
+    def event_record(self, slot):
+        self._check(self.lib.zkb_event_record(self.h, C.c_int(slot)))
+
+    def event_elapsed_ms(self, a, b):
+        ms = C.c_float()
+        self._check(self.lib.zkb_event_elapsed_ms(self.h, C.c_int(a), C.c_int(b), C.byref(ms)))
+        return ms.value
+
+    def alloc_pinned(self, words):
+        """Pinned host memory as a numpy uint32 array (freed with free_pinned)."""
+        p = C.c_void_p()
+        self._check(self.lib.zkb_host_alloc_pinned(self.h, C.c_size_t(int(words) * 4), C.byref(p)))
+        arr = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint32)), shape=(int(words),))
+        return arr, p.value
+
+    def free_pinned(self, addr):
+        self._check(self.lib.zkb_host_free_pinned(self.h, C.c_void_p(addr)))
+
+    def h2d_async(self, dptr, host_addr, nbytes):
+        self._check(self.lib.zkb_h2d_async(self.h, C.c_void_p(dptr), C.c_void_p(host_addr), C.c_size_t(nbytes)))
+
+    def d2h_async(self, host_addr, dptr, nbytes):
+        self._check(self.lib.zkb_d2h_async(self.h, C.c_void_p(host_addr), C.c_void_p(dptr), C.c_size_t(nbytes)))
+
+    def d2d(self, dst, src, nbytes):
+        self._check(self.lib.zkb_d2d(self.h, C.c_void_p(dst), C.c_void_p(src), C.c_size_t(nbytes)))
 
     def stream(self):
         s = C.c_void_p()

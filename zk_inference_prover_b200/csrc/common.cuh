@@ -26,6 +26,7 @@ struct zkb_ctx {
     size_t scratch_words = 0;
     unsigned int* ticket = nullptr;
     uint32_t* h_small = nullptr;  // pinned, for small results read back by the host
+    cudaEvent_t events[64] = {nullptr};
     char err[512] = {0};
 };
 

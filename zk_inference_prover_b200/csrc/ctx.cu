@@ -122,6 +122,8 @@ int zkb_destroy(zkb_ctx* ctx) {
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->ticket) cudaFree(ctx->ticket);
     if (ctx->h_small) cudaFreeHost(ctx->h_small);
+    for (int i = 0; i < 64; i++)
+        if (ctx->events[i]) cudaEventDestroy(ctx->events[i]);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return ZKB_OK;
@@ -139,6 +141,24 @@ int zkb_sync(zkb_ctx* ctx) {
 int zkb_get_stream(zkb_ctx* ctx, void** stream) {
     if (!ctx || !stream) return ZKB_EINVAL;
     *stream = (void*)ctx->stream;
+    return ZKB_OK;
+}
+
+int zkb_event_record(zkb_ctx* ctx, int slot) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, slot >= 0 && slot < 64);
+    DeviceGuard g(ctx);
+    if (!ctx->events[slot]) ZKB_CUDA(ctx, cudaEventCreate(&ctx->events[slot]));
+    ZKB_CUDA(ctx, cudaEventRecord(ctx->events[slot], ctx->stream));
+    return ZKB_OK;
+}
+
+int zkb_event_elapsed_ms(zkb_ctx* ctx, int a, int b, float* h_ms) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, a >= 0 && a < 64 && b >= 0 && b < 64 && h_ms && ctx->events[a] && ctx->events[b]);
+    DeviceGuard g(ctx);
+    ZKB_CUDA(ctx, cudaEventSynchronize(ctx->events[b]));
+    ZKB_CUDA(ctx, cudaEventElapsedTime(h_ms, ctx->events[a], ctx->events[b]));
     return ZKB_OK;
 }
 
