@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "fft_r32.cuh"
 
 namespace zk {
 
@@ -124,24 +125,51 @@ __global__ void fft_small_kernel(uint32_t* const* __restrict__ dst_cols, const u
     for (int k = 0; k < n; k++) dst[k] = v[k];
 }
 
-// Splits layers [0, nl) of an array of 2^log_n words into passes, lowest layers first.
-static std::vector<FftPass> plan_passes(int nl, int log_n) {
-    std::vector<FftPass> v;
-    int kb = log_n < FFT_CONTIG_LOG ? log_n : FFT_CONTIG_LOG;
-    int kf = nl < kb ? nl : kb;
-    v.push_back({0, kb, kf, 0});
-    int r = nl - kf;
-    if (r > 0) {
-        int np = (r + FFT_STRIDED_LAYERS - 1) / FFT_STRIDED_LAYERS;
-        int lo = kf;
-        for (int p = 0; p < np; p++) {
-            int k = r / np + (p < r % np ? 1 : 0);
-            int logw = FFT_MAX_TILE_LOG - k;
-            if (logw > 5) logw = 5;
-            if (logw > lo) logw = lo;
-            v.push_back({lo, k, k, logw});
-            lo += k;
+// One launch of the plan: either a radix-32 window pass or a generic shared-memory pass.
+struct FftStep {
+    int kind;  // 0: generic, 1: radix-32 contiguous, 2: radix-32 strided
+    FftPass generic;
+    R32Pass r32;
+};
+
+// Splits layers [0, nl) of an array of 2^log_n words into launches, lowest layers first.
+// Radix-32 windows need 2^10 rows (log_n >= 10) and 16-byte aligned columns; everything else
+// goes through the generic pass.
+static std::vector<FftStep> plan_steps(int nl, int log_n, bool aligned) {
+    std::vector<FftStep> v;
+    if (log_n < 10 || !aligned) {
+        int kb = log_n < FFT_CONTIG_LOG ? log_n : FFT_CONTIG_LOG;
+        int kf = nl < kb ? nl : kb;
+        v.push_back({0, {0, kb, kf, 0}, {}});
+        int r = nl - kf, lo = kf;
+        if (r > 0) {
+            int np = (r + FFT_STRIDED_LAYERS - 1) / FFT_STRIDED_LAYERS;
+            for (int p = 0; p < np; p++) {
+                int k = r / np + (p < r % np ? 1 : 0);
+                int logw = FFT_MAX_TILE_LOG - k;
+                if (logw > 5) logw = 5;
+                if (logw > lo) logw = lo;
+                v.push_back({0, {lo, k, k, logw}, {}});
+                lo += k;
+            }
         }
+        return v;
+    }
+    int covered = nl < 10 ? nl : 10;
+    v.push_back({1, {}, {0, 0, covered}});
+    while (covered < nl) {
+        int take = nl - covered < 10 ? nl - covered : 10;
+        int lo = covered;
+        if (lo + 10 > log_n) lo = log_n - 10;
+        if (lo >= 3) {
+            v.push_back({2, {}, {lo, covered - lo, covered - lo + take}});
+        } else {
+            int logw = FFT_MAX_TILE_LOG - take;
+            if (logw > 5) logw = 5;
+            if (logw > covered) logw = covered;
+            v.push_back({0, {covered, take, take, logw}, {}});
+        }
+        covered += take;
     }
     return v;
 }
@@ -159,6 +187,26 @@ static int launch_pass(zkb_ctx* ctx, uint32_t* const* d_dst, const uint32_t* con
     dim3 grid(tiles, gy);
     fft_pass_kernel<INVERSE><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log, ps,
                                                                    INVERSE ? ctx->itw : ctx->tw, scale);
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
+}
+
+template <bool INVERSE>
+static int launch_step(zkb_ctx* ctx, uint32_t* const* d_dst, const uint32_t* const* d_src, uint32_t src_mask, int ncols,
+                       int log_n, int dom_log, const FftStep& st, uint32_t scale) {
+    if (st.kind == 0) return launch_pass<INVERSE>(ctx, d_dst, d_src, src_mask, ncols, log_n, dom_log, st.generic, scale);
+    const uint32_t* tower = INVERSE ? ctx->itw : ctx->tw;
+    unsigned gy = ncols < 32768 ? ncols : 32768;
+    if (st.kind == 1) {
+        unsigned units = 1u << (log_n - 10);
+        dim3 grid((units + 7) / 8, gy);
+        fft_r32_contig_kernel<INVERSE><<<grid, 256, 0, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log, st.r32,
+                                                                      tower, scale);
+    } else {
+        dim3 grid(1u << (log_n - 13), gy);
+        fft_r32_strided_kernel<INVERSE><<<grid, 256, 0, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log, st.r32,
+                                                                       tower, scale);
+    }
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }
@@ -195,11 +243,13 @@ int zkb_ifft_cols(zkb_ctx* ctx, uint32_t* const* cols, int ncols, int log_n) {
         ZKB_LAUNCH_CHECK(ctx);
         return ZKB_OK;
     }
-    auto passes = plan_passes(log_n, log_n);
+    bool aligned = true;
+    for (int c = 0; c < ncols; c++) aligned = aligned && ((uintptr_t)cols[c] & 15) == 0;
+    auto steps = plan_steps(log_n, log_n, aligned);
     uint32_t n_inv = m31_inv(1u << log_n);
-    for (size_t p = 0; p < passes.size(); p++) {
-        rc = launch_pass<true>(ctx, dc, (const uint32_t* const*)dc, 0xffffffffu, ncols, log_n, log_n, passes[p],
-                               p + 1 == passes.size() ? n_inv : 0u);
+    for (size_t p = 0; p < steps.size(); p++) {
+        rc = launch_step<true>(ctx, dc, (const uint32_t* const*)dc, 0xffffffffu, ncols, log_n, log_n, steps[p],
+                               p + 1 == steps.size() ? n_inv : 0u);
         if (rc) return rc;
     }
     return ZKB_OK;
@@ -224,13 +274,15 @@ int zkb_lde_cols(zkb_ctx* ctx, const uint32_t* const* coeffs, int ncols, int log
         ZKB_LAUNCH_CHECK(ctx);
         return ZKB_OK;
     }
-    auto passes = plan_passes(log_n, log_out);
+    bool aligned = true;
+    for (int c = 0; c < ncols; c++) aligned = aligned && ((uintptr_t)out[c] & 15) == 0;
+    auto steps = plan_steps(log_n, log_out, aligned);
     uint32_t src_mask = (1u << log_n) - 1u;
-    for (size_t p = passes.size(); p-- > 0;) {
-        bool first = p + 1 == passes.size();
-        rc = launch_pass<false>(ctx, (uint32_t* const*)d_dst,
+    for (size_t p = steps.size(); p-- > 0;) {
+        bool first = p + 1 == steps.size();
+        rc = launch_step<false>(ctx, (uint32_t* const*)d_dst,
                                 first ? (const uint32_t* const*)d_src : (const uint32_t* const*)d_dst,
-                                first ? src_mask : 0xffffffffu, ncols, log_out, log_out, passes[p], 0u);
+                                first ? src_mask : 0xffffffffu, ncols, log_out, log_out, steps[p], 0u);
         if (rc) return rc;
     }
     return ZKB_OK;

@@ -1,0 +1,197 @@
+// Radix-32 register stages for the circle FFT.
+//
+// A pass covers a window of 10 index bits [lo, lo+10): 1024 "rows" m. Every thread keeps 32 values
+// in registers and runs up to 5 butterfly layers on them without touching memory; one exchange
+// through shared memory sits between the two stages of a pass:
+//   stage 1 (window bits 5..9): the thread holds rows m = tm + 32 p, p = 0..31
+//   stage 2 (window bits 0..4): the thread holds rows m = 32 tm + p
+// In stage 1 the twiddle of a butterfly depends only on p and on the bits above the window, so it is
+// the same for every thread of the CTA; in stage 2 it depends on tm. Either way a thread loads each
+// twiddle once (31 + 15 loads for 160 butterflies).
+//
+// Two thread mappings share the per-thread code:
+//   contiguous pass (lo = 0): one warp owns 1024 consecutive words of one column; the exchange is
+//     warp-private (33-word row pitch, no bank conflicts, __syncwarp only);
+//   strided pass (lo >= 3): a CTA of 256 threads owns 1024 rows x 8 consecutive words; thread
+//     (tm = tid / 8, w = tid % 8); global accesses are runs of 32 bytes.
+//
+// The butterfly multiplies by a pre-doubled twiddle: with t2 = 2t, the 64-bit product t2 * v splits
+// as hi = (t v) >> 31 and lo / 2 = (t v) mod 2^31, whose sum is congruent to t v and below 2p.
+#pragma once
+#include "common.cuh"
+
+namespace zk {
+
+__device__ __forceinline__ uint32_t m31_mul_dbl(uint32_t v, uint32_t t2) {
+    uint64_t p = (uint64_t)v * t2;
+    uint32_t s = (uint32_t)(p >> 32) + ((uint32_t)p >> 1);
+    return umin32(s, s - P);
+}
+
+// Forward: (a, b) -> (a + t b, a - t b); with NEG the twiddle is -t.
+template <bool NEG>
+__device__ __forceinline__ void bf_fwd(uint32_t& a, uint32_t& b, uint32_t t2) {
+    uint32_t s = m31_mul_dbl(b, t2);
+    uint32_t x = m31_add(a, s), y = m31_sub(a, s);
+    a = NEG ? y : x;
+    b = NEG ? x : y;
+}
+// Inverse: (a, b) -> (a + b, (a - b) t); with NEG the twiddle is -t.
+template <bool NEG>
+__device__ __forceinline__ void bf_inv(uint32_t& a, uint32_t& b, uint32_t t2) {
+    uint32_t d = NEG ? m31_sub(b, a) : m31_sub(a, b);
+    a = m31_add(a, b);
+    b = m31_mul_dbl(d, t2);
+}
+
+// Five layers on 32 registers. Layer jj pairs p with p + 2^jj and uses twiddle tbl_jj[p >> (jj+1)],
+// tbl_jj = tower + 2^(L - i - 1) + (A << (4 - jj)) for the global layer i = layer0 + jj.
+// Layers outside [act_lo, act_hi) (window-local numbering, this stage starts at `first`) are skipped.
+// When CIRCLE, layer jj = 0 is the circle layer (global layer 0): its twiddles are [y, -y, -x, x]
+// for each pair (x, y) of the layer-1 table (cpu/circle.rs:312-332).
+template <bool INVERSE, bool CIRCLE>
+__device__ __forceinline__ void radix32_stage(uint32_t (&v)[32], const uint32_t* __restrict__ tower, int L, int layer0,
+                                              uint32_t A, int first, int act_lo, int act_hi) {
+#pragma unroll
+    for (int step = 0; step < 5; step++) {
+        const int jj = INVERSE ? step : 4 - step;
+        if (first + jj < act_lo || first + jj >= act_hi) continue;
+        const int i = layer0 + jj;
+        if (CIRCLE && jj == 0) {
+            const uint32_t* __restrict__ t1 = tower + (1u << (L - 2)) + (A << 3);
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                uint32_t x2 = t1[2 * q] << 1, y2 = t1[2 * q + 1] << 1;
+                if (INVERSE) {
+                    bf_inv<false>(v[8 * q + 0], v[8 * q + 1], y2);
+                    bf_inv<true>(v[8 * q + 2], v[8 * q + 3], y2);
+                    bf_inv<true>(v[8 * q + 4], v[8 * q + 5], x2);
+                    bf_inv<false>(v[8 * q + 6], v[8 * q + 7], x2);
+                } else {
+                    bf_fwd<false>(v[8 * q + 0], v[8 * q + 1], y2);
+                    bf_fwd<true>(v[8 * q + 2], v[8 * q + 3], y2);
+                    bf_fwd<true>(v[8 * q + 4], v[8 * q + 5], x2);
+                    bf_fwd<false>(v[8 * q + 6], v[8 * q + 7], x2);
+                }
+            }
+        } else {
+            const uint32_t* __restrict__ tbl = tower + (1u << (L - i - 1)) + (A << (4 - jj));
+#pragma unroll
+            for (int h = 0; h < (16 >> jj); h++) {
+                const uint32_t t2 = tbl[h] << 1;
+#pragma unroll
+                for (int l = 0; l < (1 << jj); l++) {
+                    const int p0 = (h << (jj + 1)) | l, p1 = p0 | (1 << jj);
+                    if (INVERSE) bf_inv<false>(v[p0], v[p1], t2);
+                    else bf_fwd<false>(v[p0], v[p1], t2);
+                }
+            }
+        }
+    }
+}
+
+struct R32Pass {
+    int lo;              // first index bit of the window
+    int act_lo, act_hi;  // active layers, window-local: [act_lo, act_hi) within 0..10
+};
+
+// Contiguous pass: window bits [0, 10). One warp per 1024 consecutive words.
+template <bool INVERSE>
+__global__ void __launch_bounds__(256, INVERSE ? 3 : 2) fft_r32_contig_kernel(uint32_t* const* __restrict__ dst_cols,
+                                                             const uint32_t* const* __restrict__ src_cols, uint32_t src_mask,
+                                                             int ncols, int log_n, int dom_log, R32Pass ps,
+                                                             const uint32_t* __restrict__ tower, uint32_t scale) {
+    __shared__ uint32_t smem[8][33 * 32];
+    const int warp = threadIdx.x >> 5, tm = threadIdx.x & 31;
+    const uint32_t unit = blockIdx.x * 8u + warp;  // = bits above the window
+    if (unit >= (1u << (log_n - 10))) return;
+    uint32_t* __restrict__ s = smem[warp];
+    const uint32_t base = unit << 10;
+    for (int col = blockIdx.y; col < ncols; col += gridDim.y) {
+        const uint32_t* __restrict__ src = src_cols[col];
+        uint32_t* __restrict__ dst = dst_cols[col];
+        uint32_t v[32];
+        if (!INVERSE) {
+#pragma unroll
+            for (int p = 0; p < 32; p++) v[p] = src[(base + tm + 32 * p) & src_mask];
+            radix32_stage<false, false>(v, tower, dom_log, 5, unit, 5, ps.act_lo, ps.act_hi);
+#pragma unroll
+            for (int p = 0; p < 32; p++) s[33 * p + tm] = v[p];
+            __syncwarp();
+#pragma unroll
+            for (int p = 0; p < 32; p++) v[p] = s[33 * tm + p];
+            __syncwarp();
+            radix32_stage<false, true>(v, tower, dom_log, 0, (unit << 5) | tm, 0, ps.act_lo, ps.act_hi);
+            uint4* o = reinterpret_cast<uint4*>(dst + base + 32 * tm);
+#pragma unroll
+            for (int q = 0; q < 8; q++) o[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        } else {
+            const uint4* in = reinterpret_cast<const uint4*>(src + base + 32 * tm);
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                uint4 x = in[q];
+                v[4 * q] = x.x; v[4 * q + 1] = x.y; v[4 * q + 2] = x.z; v[4 * q + 3] = x.w;
+            }
+            radix32_stage<true, true>(v, tower, dom_log, 0, (unit << 5) | tm, 0, ps.act_lo, ps.act_hi);
+#pragma unroll
+            for (int p = 0; p < 32; p++) s[33 * tm + p] = v[p];
+            __syncwarp();
+#pragma unroll
+            for (int p = 0; p < 32; p++) v[p] = s[33 * p + tm];
+            __syncwarp();
+            radix32_stage<true, false>(v, tower, dom_log, 5, unit, 5, ps.act_lo, ps.act_hi);
+#pragma unroll
+            for (int p = 0; p < 32; p++) dst[base + tm + 32 * p] = scale ? m31_mul(v[p], scale) : v[p];
+        }
+    }
+}
+
+// Strided pass: window bits [lo, lo+10), lo >= 3. CTA = 1024 rows x 8 consecutive words.
+template <bool INVERSE>
+__global__ void __launch_bounds__(256, INVERSE ? 3 : 2) fft_r32_strided_kernel(uint32_t* const* __restrict__ dst_cols,
+                                                              const uint32_t* const* __restrict__ src_cols, uint32_t src_mask,
+                                                              int ncols, int log_n, int dom_log, R32Pass ps,
+                                                              const uint32_t* __restrict__ tower, uint32_t scale) {
+    __shared__ uint32_t s[264 * 32];
+    const uint32_t w = threadIdx.x & 7, tm = threadIdx.x >> 3;
+    const uint32_t tile = blockIdx.x;
+    const uint32_t wb = tile & ((1u << (ps.lo - 3)) - 1u);
+    const uint32_t a = tile >> (ps.lo - 3);
+    const uint32_t base = (a << (ps.lo + 10)) | (wb << 3) | w;
+    for (int col = blockIdx.y; col < ncols; col += gridDim.y) {
+        const uint32_t* __restrict__ src = src_cols[col];
+        uint32_t* __restrict__ dst = dst_cols[col];
+        uint32_t v[32];
+        if (!INVERSE) {
+#pragma unroll
+            for (int p = 0; p < 32; p++) v[p] = src[(base | ((tm + 32u * p) << ps.lo)) & src_mask];
+            radix32_stage<false, false>(v, tower, dom_log, ps.lo + 5, a, 5, ps.act_lo, ps.act_hi);
+#pragma unroll
+            for (int p = 0; p < 32; p++) s[264 * p + 8 * tm + w] = v[p];
+            __syncthreads();
+#pragma unroll
+            for (int p = 0; p < 32; p++) v[p] = s[264 * tm + 8 * p + w];
+            radix32_stage<false, false>(v, tower, dom_log, ps.lo, (a << 5) | tm, 0, ps.act_lo, ps.act_hi);
+#pragma unroll
+            for (int p = 0; p < 32; p++) dst[base | ((32u * tm + p) << ps.lo)] = v[p];
+        } else {
+#pragma unroll
+            for (int p = 0; p < 32; p++) v[p] = src[base | ((32u * tm + p) << ps.lo)];
+            radix32_stage<true, false>(v, tower, dom_log, ps.lo, (a << 5) | tm, 0, ps.act_lo, ps.act_hi);
+#pragma unroll
+            for (int p = 0; p < 32; p++) s[264 * tm + 8 * p + w] = v[p];
+            __syncthreads();
+#pragma unroll
+            for (int p = 0; p < 32; p++) v[p] = s[264 * p + 8 * tm + w];
+            radix32_stage<true, false>(v, tower, dom_log, ps.lo + 5, a, 5, ps.act_lo, ps.act_hi);
+#pragma unroll
+            for (int p = 0; p < 32; p++) {
+                uint32_t x = scale ? m31_mul(v[p], scale) : v[p];
+                dst[base | ((tm + 32u * p) << ps.lo)] = x;
+            }
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace zk
