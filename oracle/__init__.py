@@ -347,3 +347,42 @@ def mle_fix_first(mle, r4):
     else:
         lib().zko_mle_fix_first_qm31(_p(mle), C.c_size_t(n), _p(r), _p(o))
     return o
+
+
+# ---------------------------------------------------------------- whole protocols
+def pow_prefixed_digest(channel, pow_bits):
+    o = np.zeros(8, np.uint32)
+    lib().zko_channel_pow_prefixed_digest(channel._h, C.c_uint32(pow_bits), _p(o))
+    return o
+
+
+def pcs_prove(trees, pow_bits=10, log_blowup=1, log_last_layer=0, n_queries=3, two_sample_every=0, cap=1 << 24):
+    """trees: list of lists of uint32 columns (trace evaluations, bit-reversed). Returns the proof words."""
+    flat = [_u32(c) for t in trees for c in t]
+    ncols = np.array([len(t) for t in trees], np.int32)
+    logs = _u32([len(c).bit_length() - 1 for c in flat])
+    out = np.zeros(cap, np.uint32)
+    lib().zko_pcs_prove.restype = C.c_long
+    n = lib().zko_pcs_prove(C.c_int(len(trees)), _p(ncols), _pp(flat), _p(logs), C.c_uint32(pow_bits), C.c_uint32(log_blowup),
+                            C.c_uint32(log_last_layer), C.c_uint32(n_queries), C.c_int(two_sample_every), _p(out), C.c_size_t(cap))
+    if n < 0:
+        raise RuntimeError(f"zko_pcs_prove failed: {n}")
+    return out[:n].copy()
+
+
+def gkr_prove(instances, seed, verify=True, cap=1 << 22):
+    """instances: list of (kind, num or None, den). Returns the proof words (rejects raise)."""
+    kinds = np.array([k for k, _, _ in instances], np.int32)
+    nums = [None if n is None else _u32(n) for _, n, _ in instances]
+    dens = [_u32(d) for _, _, d in instances]
+    ns = np.array([d.shape[0] for d in dens], np.uint64)
+    nump = (C.c_void_p * len(nums))(*[None if n is None else n.ctypes.data for n in nums])
+    out = np.zeros(cap, np.uint32)
+    lib().zko_gkr_prove.restype = C.c_long
+    n = lib().zko_gkr_prove(C.c_int(len(instances)), _p(kinds), nump, _pp(dens), _p(ns), C.c_uint64(seed), C.c_int(int(verify)),
+                            _p(out), C.c_size_t(cap))
+    if n == -2:
+        raise AssertionError("GKR proof rejected by partially_verify_batch")
+    if n < 0:
+        raise RuntimeError(f"zko_gkr_prove failed: {n}")
+    return out[:n].copy()

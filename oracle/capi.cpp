@@ -287,3 +287,93 @@ void zko_mle_fix_first_m31(const uint32_t* in, size_t n, const uint32_t* r4, uin
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------- whole protocols
+extern "C" {
+
+void zko_channel_pow_prefixed_digest(void* c, uint32_t pow_bits, uint32_t* out8) {
+    Hash h = ((Channel*)c)->pow_prefixed_digest(pow_bits);
+    for (int i = 0; i < 8; i++) out8[i] = load_le32(&h[4 * i]);
+}
+
+// Commits `n_trees` trees of trace columns (evaluations on the canonic domain of their own size,
+// bit-reversed), samples every column at one channel-drawn point (columns whose flat index is a
+// multiple of `two_sample_every`, if non-zero, also at the point one trace step before it), and
+// proves the values. Channel: Blake2sM31, default state, PcsConfig mixed in first.
+// Writes the proof words to `out` (capacity `cap` words) and returns the word count, or -1.
+long zko_pcs_prove(int n_trees, const int* tree_ncols, const uint32_t* const* cols, const uint32_t* col_logs,
+                   uint32_t pow_bits, uint32_t log_blowup, uint32_t log_last_layer, uint32_t n_queries,
+                   int two_sample_every, uint32_t* out, size_t cap) {
+    PcsConfig cfg;
+    cfg.pow_bits = pow_bits;
+    cfg.fri = {log_blowup, log_last_layer, n_queries, 1};
+    uint32_t max_log = 0;
+    int total = 0;
+    for (int t = 0; t < n_trees; t++) total += tree_ncols[t];
+    for (int i = 0; i < total; i++) max_log = std::max(max_log, col_logs[i]);
+    Channel ch(true);
+    cfg.mix_into(ch);
+    CommitmentSchemeProver prover(cfg, max_log + log_blowup);
+    int flat = 0;
+    for (int t = 0; t < n_trees; t++) {
+        std::vector<std::vector<M31>> columns;
+        for (int c = 0; c < tree_ncols[t]; c++, flat++) {
+            size_t n = (size_t)1 << col_logs[flat];
+            std::vector<M31> v(n);
+            for (size_t i = 0; i < n; i++) v[i] = M31(cols[flat][i]);
+            columns.push_back(std::move(v));
+        }
+        prover.commit_evals(columns, ch);
+    }
+    CirclePoint<QM31> oods = get_random_point(ch);
+    std::vector<std::vector<std::vector<CirclePoint<QM31>>>> points(n_trees);
+    flat = 0;
+    for (int t = 0; t < n_trees; t++)
+        for (int c = 0; c < tree_ncols[t]; c++, flat++) {
+            std::vector<CirclePoint<QM31>> p;
+            if (two_sample_every && flat % two_sample_every == 0)
+                p.push_back(oods + into_ef(CanonicCoset(col_logs[flat]).step().conjugate()));
+            p.push_back(oods);
+            points[t].push_back(p);
+        }
+    PcsProof proof = prover.prove_values(points, ch);
+    std::vector<uint32_t> w = proof.to_words();
+    // the channel state after the proof pins every Fiat-Shamir step
+    for (int i = 0; i < 8; i++) w.push_back(load_le32(&ch.digest[4 * i]));
+    if (w.size() > cap) return -1;
+    memcpy(out, w.data(), w.size() * 4);
+    return (long)w.size();
+}
+
+// GKR batch proof of `n_inst` instances (kinds as in ops.hpp; nums[i] may be NULL). The channel is
+// Blake2sM31 default state after mix_u64(seed). If verify != 0 the proof is checked with
+// partially_verify_batch and -2 is returned on rejection.
+long zko_gkr_prove(int n_inst, const int* kinds, const uint32_t* const* nums, const uint32_t* const* dens, const uint64_t* ns,
+                   uint64_t seed, int verify, uint32_t* out, size_t cap) {
+    std::vector<Layer> layers;
+    std::vector<int> is_logup;
+    for (int i = 0; i < n_inst; i++) {
+        layers.push_back(load_layer(kinds[i], nums[i], dens[i], ns[i]));
+        is_logup.push_back(kinds[i] != GRAND_PRODUCT);
+    }
+    Channel ch(true);
+    ch.mix_u64(seed);
+    GkrProof proof = gkr_prove_batch(ch, layers);
+    if (verify) {
+        Channel vch(true);
+        vch.mix_u64(seed);
+        std::vector<QM31> ood;
+        std::vector<std::vector<QM31>> claims;
+        if (!gkr_partially_verify_batch(is_logup, proof, vch, ood, claims)) return -2;
+        if (ood.size() != proof.ood_point.size()) return -2;
+        for (size_t k = 0; k < ood.size(); k++) if (ood[k] != proof.ood_point[k]) return -2;
+        if (vch.digest != ch.digest) return -2;
+    }
+    std::vector<uint32_t> w = proof.to_words();
+    for (int i = 0; i < 8; i++) w.push_back(load_le32(&ch.digest[4 * i]));
+    if (w.size() > cap) return -1;
+    memcpy(out, w.data(), w.size() * 4);
+    return (long)w.size();
+}
+
+}  // extern "C"

@@ -196,17 +196,30 @@ static int launch_step(zkb_ctx* ctx, uint32_t* const* d_dst, const uint32_t* con
                        int log_n, int dom_log, const FftStep& st, uint32_t scale) {
     if (st.kind == 0) return launch_pass<INVERSE>(ctx, d_dst, d_src, src_mask, ncols, log_n, dom_log, st.generic, scale);
     const uint32_t* tower = INVERSE ? ctx->itw : ctx->tw;
-    unsigned gy = ncols < 32768 ? ncols : 32768;
-    if (st.kind == 1) {
-        unsigned units = 1u << (log_n - 10);
-        dim3 grid((units + 7) / 8, gy);
-        fft_r32_contig_kernel<INVERSE><<<grid, 256, 0, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log, st.r32,
-                                                                      tower, scale);
-    } else {
-        dim3 grid(1u << (log_n - 13), gy);
-        fft_r32_strided_kernel<INVERSE><<<grid, 256, 0, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log, st.r32,
-                                                                       tower, scale);
+    // Persistent launch: as many CTAs as fit on the device at once, each walking over work items.
+    static int ctas_per_sm[2][2] = {{0, 0}, {0, 0}};  // [contiguous/strided][forward/inverse]
+    static int n_sms = 0;
+    const size_t smem = (size_t)2 * R32_BUF_WORDS * sizeof(uint32_t);
+    const int which = st.kind == 1 ? 0 : 1;
+    const void* fn = st.kind == 1 ? (const void*)fft_r32_contig_kernel<INVERSE> : (const void*)fft_r32_strided_kernel<INVERSE>;
+    const int threads = st.kind == 1 ? 32 * R32_CONTIG_WARPS : 256;
+    if (ctas_per_sm[which][INVERSE] == 0) {
+        ZKB_CUDA(ctx, cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        int k = 0;
+        ZKB_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&k, fn, threads, smem));
+        ZKB_CUDA(ctx, cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, ctx->device));
+        ctas_per_sm[which][INVERSE] = k > 0 ? k : 1;
     }
+    size_t items = st.kind == 1 ? (((size_t)ncols << (log_n - 10)) + R32_CONTIG_WARPS - 1) / R32_CONTIG_WARPS
+                                : ((size_t)ncols << (log_n - 13));
+    size_t max_ctas = (size_t)n_sms * ctas_per_sm[which][INVERSE];
+    unsigned grid = (unsigned)(items < max_ctas ? items : max_ctas);
+    if (st.kind == 1)
+        fft_r32_contig_kernel<INVERSE><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log,
+                                                                              st.r32, tower, scale);
+    else
+        fft_r32_strided_kernel<INVERSE><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log,
+                                                                               st.r32, tower, scale);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }
@@ -275,7 +288,8 @@ int zkb_lde_cols(zkb_ctx* ctx, const uint32_t* const* coeffs, int ncols, int log
         return ZKB_OK;
     }
     bool aligned = true;
-    for (int c = 0; c < ncols; c++) aligned = aligned && ((uintptr_t)out[c] & 15) == 0;
+    for (int c = 0; c < ncols; c++) aligned = aligned && (((uintptr_t)out[c] | (uintptr_t)coeffs[c]) & 15) == 0;
+    if (log_n < 2) aligned = false;  // the staged copies move 16 bytes at a time
     auto steps = plan_steps(log_n, log_out, aligned);
     uint32_t src_mask = (1u << log_n) - 1u;
     for (size_t p = steps.size(); p-- > 0;) {

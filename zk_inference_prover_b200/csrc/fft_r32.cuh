@@ -90,82 +90,162 @@ __device__ __forceinline__ void radix32_stage(uint32_t (&v)[32], const uint32_t*
     }
 }
 
+// ---- asynchronous global -> shared copies (16 bytes each), grouped and waited on per thread
+__device__ __forceinline__ void cp_async16(uint32_t* smem_dst, const uint32_t* gmem_src) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+constexpr int R32_CONTIG_WARPS = 8;    // warps per CTA of the contiguous pass; each runs its own pipeline
+constexpr int R32_BUF_WORDS = 264 * 32;  // one staging buffer: 1024 rows x 8 words, or 8 units of 33 x 32
+
 struct R32Pass {
     int lo;              // first index bit of the window
     int act_lo, act_hi;  // active layers, window-local: [act_lo, act_hi) within 0..10
 };
 
+// Both kernels are persistent: a CTA (strided) or a warp (contiguous) walks over work items
+// (tile, column) and, while it computes one item from shared memory, the next item's words are
+// already on their way from HBM (cp.async into the other staging buffer). The buffer an item
+// arrived in is reused for that item's stage exchange once every value has been read from it.
+
 // Contiguous pass: window bits [0, 10). One warp per 1024 consecutive words.
+// Staging layout: row r = word / 32 holds its eight 16-byte chunks at positions q ^ (r & 7), so
+// that both the stage-1 pattern (row p, word tm) and the 128-bit stage-2 pattern (row tm, chunk q)
+// are free of bank conflicts.
 template <bool INVERSE>
-__global__ void __launch_bounds__(256, INVERSE ? 3 : 2) fft_r32_contig_kernel(uint32_t* const* __restrict__ dst_cols,
-                                                             const uint32_t* const* __restrict__ src_cols, uint32_t src_mask,
-                                                             int ncols, int log_n, int dom_log, R32Pass ps,
-                                                             const uint32_t* __restrict__ tower, uint32_t scale) {
-    __shared__ uint32_t smem[8][33 * 32];
+__global__ void __launch_bounds__(32 * R32_CONTIG_WARPS, (INVERSE ? 24 : 16) / R32_CONTIG_WARPS)
+    fft_r32_contig_kernel(uint32_t* const* __restrict__ dst_cols, const uint32_t* const* __restrict__ src_cols,
+                          uint32_t src_mask, int ncols, int log_n, int dom_log, R32Pass ps,
+                          const uint32_t* __restrict__ tower, uint32_t scale) {
+    extern __shared__ __align__(16) uint32_t dyn_smem[];
     const int warp = threadIdx.x >> 5, tm = threadIdx.x & 31;
-    const uint32_t unit = blockIdx.x * 8u + warp;  // = bits above the window
-    if (unit >= (1u << (log_n - 10))) return;
-    uint32_t* __restrict__ s = smem[warp];
-    const uint32_t base = unit << 10;
-    for (int col = blockIdx.y; col < ncols; col += gridDim.y) {
-        const uint32_t* __restrict__ src = src_cols[col];
-        uint32_t* __restrict__ dst = dst_cols[col];
+    uint32_t* const buf0 = dyn_smem + (2 * warp) * (33 * 32);
+    constexpr int BUF = 33 * 32;
+    const int unit_bits = log_n - 10;
+    const size_t total = (size_t)ncols << unit_bits;
+    // Items are ordered column-major (unit index fastest) and dealt round-robin, so at any time
+    // the whole grid streams through neighbouring units of the same few columns. (Dealing each
+    // worker a run of columns of one unit instead measured 1.5x slower: every access then lands
+    // in a different 16 MiB column.)
+    const size_t stride = (size_t)gridDim.x * R32_CONTIG_WARPS;
+    size_t item = (size_t)blockIdx.x * R32_CONTIG_WARPS + warp;
+    const size_t item_end = total;
+
+    auto prefetch = [&](uint32_t* buf, size_t it) {
+        const uint32_t* __restrict__ src = src_cols[it >> unit_bits];
+        const uint32_t base = (uint32_t)(it & (((size_t)1 << unit_bits) - 1)) << 10;
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const int r = k * 4 + (tm >> 3), q = tm & 7;  // chunk c = 32 k + tm: row c / 8, chunk c % 8
+            cp_async16(buf + r * 32 + ((q ^ (r & 7)) << 2), src + ((base + r * 32 + q * 4) & src_mask));
+        }
+    };
+
+    int cur = 0;
+    if (item < item_end) prefetch(buf0, item);
+    cp_async_commit();
+    for (; item < item_end; item += stride) {
+        if (item + stride < item_end) prefetch(buf0 + (cur ^ 1) * BUF, item + stride);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        uint32_t* __restrict__ s = buf0 + cur * BUF;
+        uint32_t* __restrict__ dst = dst_cols[item >> unit_bits];
+        const uint32_t unit = (uint32_t)(item & (((size_t)1 << unit_bits) - 1));
+        const uint32_t base = unit << 10;
         uint32_t v[32];
         if (!INVERSE) {
 #pragma unroll
-            for (int p = 0; p < 32; p++) v[p] = src[(base + tm + 32 * p) & src_mask];
+            for (int p = 0; p < 32; p++) v[p] = s[p * 32 + ((((tm >> 2) ^ (p & 7)) << 2) | (tm & 3))];
+            __syncwarp();
             radix32_stage<false, false>(v, tower, dom_log, 5, unit, 5, ps.act_lo, ps.act_hi);
 #pragma unroll
             for (int p = 0; p < 32; p++) s[33 * p + tm] = v[p];
             __syncwarp();
 #pragma unroll
             for (int p = 0; p < 32; p++) v[p] = s[33 * tm + p];
-            __syncwarp();
             radix32_stage<false, true>(v, tower, dom_log, 0, (unit << 5) | tm, 0, ps.act_lo, ps.act_hi);
             uint4* o = reinterpret_cast<uint4*>(dst + base + 32 * tm);
 #pragma unroll
             for (int q = 0; q < 8; q++) o[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
         } else {
-            const uint4* in = reinterpret_cast<const uint4*>(src + base + 32 * tm);
 #pragma unroll
             for (int q = 0; q < 8; q++) {
-                uint4 x = in[q];
+                uint4 x = *reinterpret_cast<const uint4*>(s + tm * 32 + ((q ^ (tm & 7)) << 2));
                 v[4 * q] = x.x; v[4 * q + 1] = x.y; v[4 * q + 2] = x.z; v[4 * q + 3] = x.w;
             }
+            __syncwarp();
             radix32_stage<true, true>(v, tower, dom_log, 0, (unit << 5) | tm, 0, ps.act_lo, ps.act_hi);
 #pragma unroll
             for (int p = 0; p < 32; p++) s[33 * tm + p] = v[p];
             __syncwarp();
 #pragma unroll
             for (int p = 0; p < 32; p++) v[p] = s[33 * p + tm];
-            __syncwarp();
             radix32_stage<true, false>(v, tower, dom_log, 5, unit, 5, ps.act_lo, ps.act_hi);
 #pragma unroll
             for (int p = 0; p < 32; p++) dst[base + tm + 32 * p] = scale ? m31_mul(v[p], scale) : v[p];
         }
+        __syncwarp();  // the exchange reads are done before this buffer is refilled
+        cur ^= 1;
     }
+    cp_async_wait<0>();
 }
 
 // Strided pass: window bits [lo, lo+10), lo >= 3. CTA = 1024 rows x 8 consecutive words.
+// Staging and exchange share one layout: row m at word 8 m + 8 (m / 32).
 template <bool INVERSE>
-__global__ void __launch_bounds__(256, INVERSE ? 3 : 2) fft_r32_strided_kernel(uint32_t* const* __restrict__ dst_cols,
-                                                              const uint32_t* const* __restrict__ src_cols, uint32_t src_mask,
-                                                              int ncols, int log_n, int dom_log, R32Pass ps,
-                                                              const uint32_t* __restrict__ tower, uint32_t scale) {
-    __shared__ uint32_t s[264 * 32];
+__global__ void __launch_bounds__(256, INVERSE ? 3 : 2)
+    fft_r32_strided_kernel(uint32_t* const* __restrict__ dst_cols, const uint32_t* const* __restrict__ src_cols,
+                           uint32_t src_mask, int ncols, int log_n, int dom_log, R32Pass ps,
+                           const uint32_t* __restrict__ tower, uint32_t scale) {
+    extern __shared__ __align__(16) uint32_t dyn_smem[];
+    uint32_t* const buf0 = dyn_smem;
+    constexpr int BUF = R32_BUF_WORDS;
     const uint32_t w = threadIdx.x & 7, tm = threadIdx.x >> 3;
-    const uint32_t tile = blockIdx.x;
-    const uint32_t wb = tile & ((1u << (ps.lo - 3)) - 1u);
-    const uint32_t a = tile >> (ps.lo - 3);
-    const uint32_t base = (a << (ps.lo + 10)) | (wb << 3) | w;
-    for (int col = blockIdx.y; col < ncols; col += gridDim.y) {
-        const uint32_t* __restrict__ src = src_cols[col];
-        uint32_t* __restrict__ dst = dst_cols[col];
+    const int tile_bits = log_n - 13;
+    const size_t total = (size_t)ncols << tile_bits;
+
+    auto tile_base = [&](uint32_t tile, uint32_t& a) {
+        const uint32_t wb = tile & ((1u << (ps.lo - 3)) - 1u);
+        a = tile >> (ps.lo - 3);
+        return (a << (ps.lo + 10)) | (wb << 3);
+    };
+    auto prefetch = [&](uint32_t* buf, size_t it) {
+        const uint32_t* __restrict__ src = src_cols[it >> tile_bits];
+        uint32_t a;
+        const uint32_t base = tile_base((uint32_t)(it & (((size_t)1 << tile_bits) - 1)), a);
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const uint32_t c = k * 256 + threadIdx.x;  // chunk: row c / 2, half c % 2
+            const uint32_t m = c >> 1, half = c & 1;
+            cp_async16(buf + 8 * m + 8 * (m >> 5) + 4 * half, src + ((base | (m << ps.lo) | (half << 2)) & src_mask));
+        }
+    };
+
+    int cur = 0;
+    size_t item = blockIdx.x;
+    const size_t item_end = total, stride = gridDim.x;
+    if (item < item_end) prefetch(buf0, item);
+    cp_async_commit();
+    for (; item < item_end; item += stride) {
+        if (item + stride < item_end) prefetch(buf0 + (cur ^ 1) * BUF, item + stride);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        uint32_t* __restrict__ s = buf0 + cur * BUF;
+        uint32_t* __restrict__ dst = dst_cols[item >> tile_bits];
+        uint32_t a;
+        const uint32_t base = tile_base((uint32_t)(item & (((size_t)1 << tile_bits) - 1)), a) | w;
         uint32_t v[32];
         if (!INVERSE) {
 #pragma unroll
-            for (int p = 0; p < 32; p++) v[p] = src[(base | ((tm + 32u * p) << ps.lo)) & src_mask];
+            for (int p = 0; p < 32; p++) v[p] = s[264 * p + 8 * tm + w];
             radix32_stage<false, false>(v, tower, dom_log, ps.lo + 5, a, 5, ps.act_lo, ps.act_hi);
+            // each thread writes back exactly the words it read: no barrier needed before the write
 #pragma unroll
             for (int p = 0; p < 32; p++) s[264 * p + 8 * tm + w] = v[p];
             __syncthreads();
@@ -176,7 +256,7 @@ __global__ void __launch_bounds__(256, INVERSE ? 3 : 2) fft_r32_strided_kernel(u
             for (int p = 0; p < 32; p++) dst[base | ((32u * tm + p) << ps.lo)] = v[p];
         } else {
 #pragma unroll
-            for (int p = 0; p < 32; p++) v[p] = src[base | ((32u * tm + p) << ps.lo)];
+            for (int p = 0; p < 32; p++) v[p] = s[264 * tm + 8 * p + w];
             radix32_stage<true, false>(v, tower, dom_log, ps.lo, (a << 5) | tm, 0, ps.act_lo, ps.act_hi);
 #pragma unroll
             for (int p = 0; p < 32; p++) s[264 * tm + 8 * p + w] = v[p];
@@ -190,8 +270,10 @@ __global__ void __launch_bounds__(256, INVERSE ? 3 : 2) fft_r32_strided_kernel(u
                 dst[base | ((tm + 32u * p) << ps.lo)] = x;
             }
         }
-        __syncthreads();
+        __syncthreads();  // exchange reads are done before this buffer is refilled
+        cur ^= 1;
     }
+    cp_async_wait<0>();
 }
 
 }  // namespace zk
