@@ -75,6 +75,9 @@ int zkb_host_free_pinned(zkb_ctx* ctx, void* h_ptr);
 int zkb_gather_multi(zkb_ctx* ctx, const uint32_t* const* cols, int ncols, const uint32_t* h_idx, int nidx,
                      uint32_t* h_out);
 
+/* Column<Blake2sHash>::batch_at (STWO/prover/backend/mod.rs:68-72): h_out[8*i..] = hashes[h_idx[i]]. */
+int zkb_gather_hashes(zkb_ctx* ctx, const uint32_t* hashes, const uint32_t* h_idx, int nidx, uint32_t* h_out);
+
 /* ---- twiddles ------------------------------------------------------------------------------
  * Copies out the tower of Coset::half_odds(log_size) in the reference's layout
  * (slow_precompute_twiddles, STWO/prover/backend/cpu/circle.rs:274-291): 2^log_size words each,

@@ -1,0 +1,66 @@
+/*
+ * zkb200_prover — whole-protocol drivers over the operator ABI of zkb200.h.
+ *
+ * The reference's protocol code is generic Rust that calls the backend's operators
+ * (STWO = nitroo/crates/stwo/src): CommitmentSchemeProver (STWO/prover/pcs/mod.rs:34-419),
+ * CommitmentTreeProver (:466-630), compute_fri_quotients (STWO/prover/pcs/quotient_ops.rs:73-194),
+ * FriProver (STWO/prover/fri.rs:87-467), MerkleProver (STWO/prover/vcs/prover.rs:17-217) and the GKR
+ * batch prover (STWO/prover/lookups/gkr_prover.rs:657-882, sumcheck.rs:96-176). A Rust build keeps
+ * using that code with the new backend type. These entry points are its C++ counterpart for
+ * programs without a Rust toolchain: the benchmark and the parity tests drive whole commitments
+ * and proofs through them. The Fiat-Shamir channel is Blake2sM31Channel, run on the host.
+ *
+ * Proof word streams (uint32, all field elements canonical):
+ *   PCS: n_trees, roots (8 words each); per tree: n_cols, per column n_samples and the sampled
+ *        values; per tree the Merkle decommitment (n_hashes, hashes, n_values, values); per tree
+ *        n_queried, queried values; proof-of-work nonce (lo, hi); FRI first layer, n_inner, inner
+ *        layers (each: n_witness, witness values, decommitment, commitment); n_coeffs, last-layer
+ *        polynomial; then the 8 words of the channel digest after the proof.
+ *   GKR: n_layers, per layer n_rounds and each round polynomial (n_coeffs, coeffs); per instance
+ *        n_masks and each mask (n_columns, two values per column); per instance the output claims;
+ *        the out-of-domain point; per instance the claims to verify; the final channel digest.
+ */
+#ifndef ZKB200_PROVER_H
+#define ZKB200_PROVER_H
+
+#include "zkb200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct zkb_pcs_config {
+    uint32_t pow_bits;
+    uint32_t log_blowup_factor;
+    uint32_t log_last_layer_degree_bound;
+    uint32_t n_queries;
+} zkb_pcs_config;
+
+#define ZKB_PCS_N_PHASES 8
+/* phase times in h_phase_ms: 0 interpolate, 1 extend (LDE), 2 Merkle commit, 3 out-of-domain
+ * sampling, 4 quotients, 5 FRI commit, 6 grind, 7 decommit. */
+
+/* Commits n_trees trees of trace columns and proves one opening per column at a channel-drawn point
+ * (columns whose flat index is a multiple of two_sample_every, when that is non-zero, are also opened
+ * one trace step before it). d_cols: device columns of 2^col_logs[i] evaluations on the canonic
+ * domain, bit-reversed; they are consumed (interpolated in place). The context's max_log_size must
+ * cover the largest column plus the blow-up. h_phase_ms may be NULL. */
+int zkb_pcs_prove_device(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint32_t* const* d_cols, const uint32_t* col_logs,
+                         const zkb_pcs_config* config, int two_sample_every, uint32_t* h_out, size_t cap, size_t* n_words,
+                         float* h_phase_ms);
+/* Same with host columns (each is copied to the device first; h_cols are left untouched). */
+int zkb_pcs_prove_host(zkb_ctx* ctx, int n_trees, const int* tree_ncols, const uint32_t* const* h_cols, const uint32_t* col_logs,
+                       const zkb_pcs_config* config, int two_sample_every, uint32_t* h_out, size_t cap, size_t* n_words,
+                       float* h_phase_ms);
+
+/* GKR batch proof of n_inst instances. kinds: ZKB_GKR_*; d_nums[i] (NULL where the kind has no
+ * numerators) and d_dens[i] are device arrays of ns[i] entries laid out as zkb_gkr_next_layer takes
+ * them; they are not modified. The channel starts from Blake2sM31Channel::default() after
+ * mix_u64(seed). */
+int zkb_gkr_prove_device(zkb_ctx* ctx, int n_inst, const int* kinds, const uint32_t* const* d_nums, const uint32_t* const* d_dens,
+                         const uint64_t* ns, uint64_t seed, uint32_t* h_out, size_t cap, size_t* n_words);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZKB200_PROVER_H */

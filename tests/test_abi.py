@@ -13,6 +13,10 @@ def test_header_symbols_are_exported(zkb):
     missing = [s for s in sorted(declared) if not hasattr(lib, s)]
     assert not missing, missing
     assert declared == set(zkb.EXPORTED_SYMBOLS)
+    header = open(os.path.join(ROOT, "include", "zkb200_prover.h")).read()
+    declared = set(re.findall(r"\b(zkb_[a-z0-9_]+)\s*\(", header))
+    assert declared == set(zkb.PROVER_SYMBOLS)
+    assert all(hasattr(lib, s) for s in declared)
 
 
 def test_no_oracle_in_product():

@@ -1,0 +1,87 @@
+"""Whole commitments, FRI proofs and GKR proofs from the CUDA path against the CPU oracle's
+restatement of the reference's protocol code, word for word (roots, sampled values, every FRI layer
+root, the last-layer polynomial, the proof-of-work nonce, queried values, decommitments, and the
+channel digest after the proof). The oracle side also checks its own proof: FRI's last layer must
+have the committed degree and the GKR proof must pass partially_verify_batch. Shapes follow
+nitroo/crates/stwo/src/prover/pcs/quotient_ops.rs:324-399 (prove_and_verify_pcs with mixed column
+sizes) and nitroo/crates/stwo/benches/{pcs,lookups}.rs."""
+import numpy as np
+import pytest
+
+from util import m31_column, qm31_array
+
+pytestmark = pytest.mark.gpu
+
+
+def _trees(shape, seed):
+    return [[m31_column(seed + 100 * t + c, 1 << lg) for c, lg in enumerate(logs)] for t, logs in enumerate(shape)]
+
+
+@pytest.mark.parametrize(
+    "shape,kw",
+    [
+        ([[6]], dict(pow_bits=0, log_blowup=1, n_queries=3)),
+        ([[5, 5, 5]], dict(pow_bits=10, log_blowup=1, n_queries=3)),                      # library default PcsConfig
+        ([[8] * 10], dict(pow_bits=10, log_blowup=2, n_queries=3)),
+        ([[4, 6, 6, 5, 8, 8, 4]], dict(pow_bits=3, log_blowup=1, n_queries=20, two_sample_every=2)),
+        ([[6, 6], [7, 5, 7, 3]], dict(pow_bits=0, log_blowup=1, n_queries=100)),           # the prover's own parameters
+        ([[10] * 17 + [7] * 3], dict(pow_bits=5, log_blowup=2, n_queries=16, log_last_layer=2, two_sample_every=5)),
+        ([[12] * 8, [12] * 3 + [9] * 2], dict(pow_bits=8, log_blowup=1, n_queries=30, log_last_layer=1, two_sample_every=3)),
+    ],
+)
+def test_pcs_proof_matches_oracle(ctx, oracle, shape, kw):
+    trees = _trees(shape, 4000)
+    want = oracle.pcs_prove(trees, **kw)
+    got = ctx.pcs_prove_host(trees, **kw)
+    assert len(got) == len(want)
+    assert (got == want).all()
+
+
+def test_pcs_device_columns_and_phases(ctx, oracle):
+    trees = _trees([[11] * 6], 4100)
+    want = oracle.pcs_prove(trees, pow_bits=4, log_blowup=2, n_queries=10)
+    bufs = [ctx.upload(c) for c in trees[0]]
+    got, phases = ctx.pcs_prove_device([[b.ptr for b in bufs]], [11] * 6, pow_bits=4, log_blowup=2, n_queries=10, phases=True)
+    assert (got == want).all()
+    assert set(phases) == {"interpolate", "extend", "merkle", "sample", "quotients", "fri_commit", "grind", "decommit"}
+    assert all(v >= 0 for v in phases.values()) and phases["merkle"] > 0
+
+
+def test_pcs_rejects_too_large_domain(ctx, zkb):
+    with pytest.raises(zkb.ZkbError):
+        ctx.pcs_prove_host([[np.zeros(1 << 10, np.uint32)]], log_blowup=16)
+
+
+def _instance(kind, log_n, seed):
+    n = 1 << log_n
+    den = qm31_array(seed, n, nonzero=True)
+    num = qm31_array(seed + 1, n) if kind == 1 else m31_column(seed + 1, n) if kind == 2 else None
+    return kind, num, den
+
+
+@pytest.mark.parametrize(
+    "spec",
+    [
+        [(2, 6)],
+        [(3, 1)],
+        [(0, 5)],
+        [(1, 4)],
+        [(2, 10), (3, 7), (0, 8), (1, 3)],      # mixed kinds and sizes in one batch
+        [(3, 12), (3, 12), (2, 12)],
+        [(2, 16)],
+    ],
+)
+def test_gkr_proof_matches_oracle(ctx, oracle, spec):
+    insts = [_instance(k, lg, 5000 + 10 * i) for i, (k, lg) in enumerate(spec)]
+    want = oracle.gkr_prove(insts, 0x5EED0004, verify=True)
+    keep, dev = [], []
+    for kind, num, den in insts:
+        nb = ctx.upload(num) if num is not None else None
+        db = ctx.upload(den)
+        keep += [nb, db]
+        dev.append((kind, nb.ptr if nb else 0, db.ptr, den.shape[0]))
+    got = ctx.gkr_prove_device(dev, 0x5EED0004)
+    assert len(got) == len(want)
+    assert (got == want).all()
+    # inputs are not modified
+    assert (keep[1].download(shape=(-1, 4)) == insts[0][2]).all()

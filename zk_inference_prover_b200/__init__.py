@@ -15,4 +15,6 @@ from .capi import (  # noqa: F401
     GKR_LOGUP_MULTIPLICITIES,
     GKR_LOGUP_SINGLES,
     EXPORTED_SYMBOLS,
+    PROVER_SYMBOLS,
+    PCS_PHASES,
 )

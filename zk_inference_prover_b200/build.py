@@ -11,7 +11,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libzkb200.so")
 
-SOURCES = ["ctx.cu", "fft.cu", "bitrev.cu", "blake2s.cu", "fri.cu", "quotients.cu", "gkr.cu", "poly_eval.cu"]
+SOURCES = ["ctx.cu", "fft.cu", "bitrev.cu", "blake2s.cu", "fri.cu", "quotients.cu", "gkr.cu", "poly_eval.cu", "host/prover.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -24,7 +24,7 @@ def _stale():
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "zkb200.h"), __file__]
+    deps = [os.path.join(dp, f) for dp, _, fs in os.walk(CSRC) for f in fs] + [os.path.join(HERE, "..", "include", "zkb200.h"), os.path.join(HERE, "..", "include", "zkb200_prover.h"), __file__]
     return any(os.path.getmtime(d) > t for d in deps)
 
 
@@ -37,7 +37,7 @@ def build(force=False, verbose=False):
     objs = []
     procs = []
     for src in SOURCES:
-        obj = os.path.join(LIB_DIR, src.replace(".cu", ".o"))
+        obj = os.path.join(LIB_DIR, os.path.basename(src).replace(".cu", ".o").replace(".cpp", ".o"))
         extra = os.environ.get("ZKB_NVCC_EXTRA", "").split()
         cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", os.path.join(CSRC, src), "-o", obj]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

@@ -14,12 +14,21 @@ EXPORTED_SYMBOLS = [
     "zkb_init", "zkb_destroy", "zkb_last_error", "zkb_sync", "zkb_get_stream", "zkb_max_log_size",
     "zkb_event_record", "zkb_event_elapsed_ms",
     "zkb_malloc", "zkb_free", "zkb_memset_zero", "zkb_h2d", "zkb_d2h", "zkb_h2d_async", "zkb_d2h_async", "zkb_d2d",
-    "zkb_host_alloc_pinned", "zkb_host_free_pinned", "zkb_gather_multi", "zkb_twiddles_d2h",
+    "zkb_host_alloc_pinned", "zkb_host_free_pinned", "zkb_gather_multi", "zkb_gather_hashes", "zkb_twiddles_d2h",
     "zkb_ifft_cols", "zkb_lde_cols", "zkb_eval_at_point_cols", "zkb_bit_reverse_m31", "zkb_bit_reverse_qm31",
     "zkb_merkle_layer", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine",
     "zkb_accumulate", "zkb_lift_accumulate", "zkb_secure_powers", "zkb_gkr_eq_evals", "zkb_gkr_next_layer",
     "zkb_gkr_sum", "zkb_mle_fix_qm31", "zkb_mle_fix_m31", "zkb_grind",
 ]
+# Every symbol include/zkb200_prover.h declares.
+PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_gkr_prove_device"]
+PCS_PHASES = ["interpolate", "extend", "merkle", "sample", "quotients", "fri_commit", "grind", "decommit"]
+
+
+class PcsConfig(C.Structure):
+    _fields_ = [("pow_bits", C.c_uint32), ("log_blowup_factor", C.c_uint32), ("log_last_layer_degree_bound", C.c_uint32),
+                ("n_queries", C.c_uint32)]
+
 
 
 class ZkbError(RuntimeError):
@@ -47,7 +56,7 @@ def load_library():
         _lib = C.CDLL(_LIB)
         _lib.zkb_last_error.restype = C.c_char_p
         _lib.zkb_last_error.argtypes = [C.c_void_p]
-        for name in EXPORTED_SYMBOLS:
+        for name in EXPORTED_SYMBOLS + PROVER_SYMBOLS:
             if name != "zkb_last_error":
                 getattr(_lib, name).restype = C.c_int
     return _lib
@@ -180,6 +189,13 @@ class Context:
                                               C.c_int(len(idx)), out.ctypes.data_as(C.c_void_p)))
         return out
 
+    def gather_hashes(self, hashes_ptr, idx):
+        idx = _u32(idx)
+        out = np.empty((len(idx), 8), np.uint32)
+        self._check(self.lib.zkb_gather_hashes(self.h, C.c_void_p(hashes_ptr), idx.ctypes.data_as(C.c_void_p), C.c_int(len(idx)),
+                                               out.ctypes.data_as(C.c_void_p)))
+        return out
+
     # ---- twiddles
     def twiddles(self, log_size):
         tw = np.empty(1 << log_size, np.uint32)
@@ -280,3 +296,46 @@ class Context:
         nonce = C.c_uint64()
         self._check(self.lib.zkb_grind(self.h, d.ctypes.data_as(C.c_void_p), C.c_int(pow_bits), C.c_int(int(m31_out)), C.byref(nonce)))
         return nonce.value
+
+    # ---- whole protocols (include/zkb200_prover.h)
+    def _pcs(self, fn, trees_ptrs, logs, pow_bits, log_blowup, log_last_layer, n_queries, two_sample_every, cap, phases):
+        flat = [p for t in trees_ptrs for p in t]
+        ncols = np.array([len(t) for t in trees_ptrs], np.int32)
+        lg = _u32(logs)
+        cfg = PcsConfig(pow_bits, log_blowup, log_last_layer, n_queries)
+        out = np.empty(cap, np.uint32)
+        n = C.c_size_t()
+        ph = np.zeros(len(PCS_PHASES), np.float32)
+        self._check(fn(self.h, C.c_int(len(trees_ptrs)), ncols.ctypes.data_as(C.c_void_p), _ptr_array(flat), lg.ctypes.data_as(C.c_void_p),
+                       C.byref(cfg), C.c_int(two_sample_every), out.ctypes.data_as(C.c_void_p), C.c_size_t(cap), C.byref(n),
+                       ph.ctypes.data_as(C.c_void_p) if phases else None))
+        words = out[:n.value].copy()
+        return (words, dict(zip(PCS_PHASES, ph.tolist()))) if phases else words
+
+    def pcs_prove_device(self, trees_ptrs, logs, pow_bits=10, log_blowup=1, log_last_layer=0, n_queries=3, two_sample_every=0,
+                         cap=1 << 24, phases=False):
+        """trees_ptrs: per tree, device addresses of the trace columns (consumed). logs: flat log sizes."""
+        return self._pcs(self.lib.zkb_pcs_prove_device, trees_ptrs, logs, pow_bits, log_blowup, log_last_layer, n_queries,
+                         two_sample_every, cap, phases)
+
+    def pcs_prove_host(self, trees, pow_bits=10, log_blowup=1, log_last_layer=0, n_queries=3, two_sample_every=0, cap=1 << 24,
+                       phases=False):
+        """trees: per tree, host uint32 arrays (trace evaluations, bit-reversed)."""
+        arrs = [[_u32(c) for c in t] for t in trees]
+        ptrs = [[c.ctypes.data for c in t] for t in arrs]
+        logs = [len(c).bit_length() - 1 for t in arrs for c in t]
+        return self._pcs(self.lib.zkb_pcs_prove_host, ptrs, logs, pow_bits, log_blowup, log_last_layer, n_queries,
+                         two_sample_every, cap, phases)
+
+    def gkr_prove_device(self, instances, seed, cap=1 << 22):
+        """instances: list of (kind, num_ptr or 0, den_ptr, n_entries)."""
+        kinds = np.array([k for k, _, _, _ in instances], np.int32)
+        nums = (C.c_void_p * len(instances))(*[(n or None) for _, n, _, _ in instances])
+        dens = (C.c_void_p * len(instances))(*[d for _, _, d, _ in instances])
+        ns = np.array([n for _, _, _, n in instances], np.uint64)
+        out = np.empty(cap, np.uint32)
+        nw = C.c_size_t()
+        self._check(self.lib.zkb_gkr_prove_device(self.h, C.c_int(len(instances)), kinds.ctypes.data_as(C.c_void_p), nums, dens,
+                                                  ns.ctypes.data_as(C.c_void_p), C.c_uint64(seed), out.ctypes.data_as(C.c_void_p),
+                                                  C.c_size_t(cap), C.byref(nw)))
+        return out[:nw.value].copy()

@@ -68,9 +68,18 @@ __global__ void gather_multi_kernel(const uint32_t* const* __restrict__ cols, in
     out[t] = cols[c][idx[i]];
 }
 
+__global__ void gather_hashes_kernel(const uint4* __restrict__ hashes, const uint32_t* __restrict__ idx, int nidx,
+                                     uint4* __restrict__ out) {
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= 2 * nidx) return;
+    out[t] = hashes[2 * (size_t)idx[t >> 1] + (t & 1)];
+}
+
 }  // namespace zk
 
 using namespace zk;
+
+extern "C" int zk_set_error_public(zkb_ctx* ctx, int code, const char* msg) { return set_error(ctx, code, "%s", msg); }
 
 extern "C" {
 
@@ -98,6 +107,12 @@ int zkb_init(int device, int max_log_size, zkb_ctx** out) {
     if (cudaMemsetAsync(ctx->ticket, 0, 64, ctx->stream) != cudaSuccess) return fail(ZKB_ECUDA);
     if (cudaMallocHost(&ctx->h_small, SMALL_WORDS * 4) != cudaSuccess) return fail(ZKB_ENOMEM);
 
+    {
+        cudaMemPool_t pool;
+        if (cudaDeviceGetDefaultMemPool(&pool, device) != cudaSuccess) return fail(ZKB_ECUDA);
+        unsigned long long keep = ~0ull;
+        if (cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep) != cudaSuccess) return fail(ZKB_ECUDA);
+    }
     // Generator doublings on the host, then the tower on the device.
     cpoint g[31];
     g[0] = {2u, 1268011823u};
@@ -169,7 +184,9 @@ int zkb_malloc(zkb_ctx* ctx, size_t bytes, void** dptr) {
     DeviceGuard g(ctx);
     *dptr = nullptr;
     if (bytes == 0) return ZKB_OK;
-    ZKB_CUDA(ctx, cudaMalloc(dptr, bytes));
+    // Stream-ordered allocation from the device's default pool (kept warm: the release threshold
+    // is raised in zkb_init), so neither allocation nor release synchronises the device.
+    ZKB_CUDA(ctx, cudaMallocAsync(dptr, bytes, ctx->stream));
     return ZKB_OK;
 }
 
@@ -177,8 +194,7 @@ int zkb_free(zkb_ctx* ctx, void* dptr) {
     if (!ctx) return ZKB_EINVAL;
     if (!dptr) return ZKB_OK;
     DeviceGuard g(ctx);
-    ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    ZKB_CUDA(ctx, cudaFree(dptr));
+    ZKB_CUDA(ctx, cudaFreeAsync(dptr, ctx->stream));
     return ZKB_OK;
 }
 
@@ -272,6 +288,24 @@ int zkb_gather_multi(zkb_ctx* ctx, const uint32_t* const* cols, int ncols, const
                                                                                   d_idx, nidx, d_out);
     ZKB_LAUNCH_CHECK(ctx);
     ZKB_CUDA(ctx, cudaMemcpyAsync(h_out, d_out, total * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return ZKB_OK;
+}
+
+int zkb_gather_hashes(zkb_ctx* ctx, const uint32_t* hashes, const uint32_t* h_idx, int nidx, uint32_t* h_out) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, nidx >= 0);
+    if (nidx == 0) return ZKB_OK;
+    ZKB_CHECK_ARG(ctx, hashes != nullptr && h_idx != nullptr && h_out != nullptr && ((uintptr_t)hashes & 15) == 0);
+    ZKB_CHECK_ARG(ctx, (size_t)nidx * 9 + 4 <= ctx->scratch_words);
+    DeviceGuard g(ctx);
+    uint32_t* d_out = ctx->scratch;  // 8 words per hash, 16-byte aligned
+    uint32_t* d_idx = ctx->scratch + 8 * (size_t)nidx;
+    ZKB_CUDA(ctx, cudaMemcpyAsync(d_idx, h_idx, (size_t)nidx * 4, cudaMemcpyHostToDevice, ctx->stream));
+    gather_hashes_kernel<<<(2 * nidx + 127) / 128, 128, 0, ctx->stream>>>(reinterpret_cast<const uint4*>(hashes), d_idx, nidx,
+                                                                        reinterpret_cast<uint4*>(d_out));
+    ZKB_LAUNCH_CHECK(ctx);
+    ZKB_CUDA(ctx, cudaMemcpyAsync(h_out, d_out, (size_t)nidx * 32, cudaMemcpyDeviceToHost, ctx->stream));
     ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return ZKB_OK;
 }

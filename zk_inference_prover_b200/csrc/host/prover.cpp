@@ -1,0 +1,856 @@
+// Protocol drivers over B200Backend: Merkle prover, FRI prover, commitment-scheme prover and the
+// GKR batch prover, with the call order of the reference's backend-generic code (cited per
+// function; STWO = nitroo/crates/stwo/src). All field and hash work on columns happens on the
+// device through the operator ABI; the host runs the Fiat-Shamir channel, the query bookkeeping
+// and scalar QM31 arithmetic on a handful of values per round.
+#include <algorithm>
+#include <chrono>
+#include <map>
+#include <numeric>
+#include <set>
+
+#include "../../../include/zkb200_prover.h"
+#include "b200_backend.hpp"
+#include "channel.hpp"
+
+// Records a message on the context (defined with the context, ctx.cu).
+extern "C" int zk_set_error_public(zkb_ctx* ctx, int code, const char* msg);
+
+namespace b200 {
+
+using namespace zk;
+
+static inline uint32_t ilog2(size_t n) { uint32_t l = 0; while (((size_t)1 << (l + 1)) <= n) l++; return l; }
+static inline qm31 operator+(qm31 a, qm31 b) { return qm31_add(a, b); }
+static inline qm31 operator-(qm31 a, qm31 b) { return qm31_sub(a, b); }
+static inline qm31 operator*(qm31 a, qm31 b) { return qm31_mul(a, b); }
+
+static std::vector<size_t> sorted_dedup(std::vector<size_t> v) {
+    std::sort(v.begin(), v.end());
+    v.erase(std::unique(v.begin(), v.end()), v.end());
+    return v;
+}
+static std::vector<size_t> fold_queries(const std::vector<size_t>& q, uint32_t n_folds) {  // core/queries.rs:55-62
+    std::vector<size_t> out;
+    for (auto x : q) { size_t y = x >> n_folds; if (out.empty() || out.back() != y) out.push_back(y); }
+    return out;
+}
+
+// ------------------------------------------------------------------ MerkleProver (STWO/prover/vcs/prover.rs:17-217)
+struct MerkleDecommitment { std::vector<Hash> hash_witness; std::vector<uint32_t> column_witness; };
+
+struct MerkleProver {
+    std::vector<HashColumn> layers;  // layers[log_size]; layers[0] holds the root
+
+    static MerkleProver commit(const Device& d, const std::vector<const BaseColumn*>& columns) {  // :39-64
+        MerkleProver mp;
+        if (columns.empty()) {
+            mp.layers.push_back(B200Backend::commit_on_layer(d, 0, nullptr, {}));
+            return mp;
+        }
+        std::vector<const BaseColumn*> sorted(columns);
+        std::stable_sort(sorted.begin(), sorted.end(), [](const BaseColumn* a, const BaseColumn* b) { return a->len() > b->len(); });
+        uint32_t max_log = sorted[0]->log_size();
+        mp.layers.resize(max_log + 1);
+        size_t pos = 0;
+        for (uint32_t log = max_log + 1; log-- > 0;) {
+            std::vector<const BaseColumn*> layer_cols;
+            while (pos < sorted.size() && sorted[pos]->log_size() == log) layer_cols.push_back(sorted[pos++]);
+            mp.layers[log] = B200Backend::commit_on_layer(d, log, log == max_log ? nullptr : &mp.layers[log + 1], layer_cols);
+        }
+        return mp;
+    }
+    Hash root(const Device& d) const { return B200Backend::batch_at(d, layers[0], {0})[0]; }
+
+    // :84-217 — index planning on the host, one hash gather and at most two value gathers per layer.
+    std::pair<std::vector<uint32_t>, MerkleDecommitment> decommit(const Device& d,
+                                                                  const std::map<uint32_t, std::vector<size_t>>& queries_per_log_size,
+                                                                  const std::vector<const BaseColumn*>& columns) const {
+        std::vector<uint32_t> queried_values;
+        MerkleDecommitment dec;
+        std::vector<const BaseColumn*> sorted(columns);
+        std::stable_sort(sorted.begin(), sorted.end(), [](const BaseColumn* a, const BaseColumn* b) { return a->len() > b->len(); });
+        size_t pos = 0;
+        std::vector<size_t> last;
+        for (uint32_t log = (uint32_t)layers.size(); log-- > 0;) {
+            bool has_prev = (size_t)log + 1 < layers.size();
+            std::set<size_t> prev_set(last.begin(), last.end()), merged, col_queries;
+            for (auto q : last) merged.insert(q / 2);
+            auto it = queries_per_log_size.find(log);
+            if (it != queries_per_log_size.end()) col_queries.insert(it->second.begin(), it->second.end());
+            merged.insert(col_queries.begin(), col_queries.end());
+            std::vector<size_t> merged_nodes(merged.begin(), merged.end());
+            std::vector<const BaseColumn*> layer_cols;
+            while (pos < sorted.size() && sorted[pos]->log_size() == log) layer_cols.push_back(sorted[pos++]);
+            std::vector<size_t> witness_children, queried_nodes, witness_nodes;
+            for (size_t node : merged_nodes) {
+                if (has_prev) {
+                    if (!prev_set.count(2 * node)) witness_children.push_back(2 * node);
+                    if (!prev_set.count(2 * node + 1)) witness_children.push_back(2 * node + 1);
+                }
+                (col_queries.count(node) ? queried_nodes : witness_nodes).push_back(node);
+            }
+            if (has_prev && !witness_children.empty()) {
+                auto hs = B200Backend::batch_at(d, layers[log + 1], witness_children);
+                dec.hash_witness.insert(dec.hash_witness.end(), hs.begin(), hs.end());
+            }
+            if (!layer_cols.empty()) {
+                auto qv = B200Backend::batch_at_multi(d, layer_cols, queried_nodes);
+                queried_values.insert(queried_values.end(), qv.begin(), qv.end());
+                auto wv = B200Backend::batch_at_multi(d, layer_cols, witness_nodes);
+                dec.column_witness.insert(dec.column_witness.end(), wv.begin(), wv.end());
+            }
+            last = merged_nodes;
+        }
+        return {queried_values, dec};
+    }
+};
+
+// ------------------------------------------------------------------ FRI (STWO/prover/fri.rs:87-467)
+struct FriConfig {
+    uint32_t log_blowup_factor, log_last_layer_degree_bound, n_queries, line_fold_step;
+    size_t last_layer_domain_size() const { return (size_t)1 << (log_last_layer_degree_bound + log_blowup_factor); }
+};
+struct FriLayerProof { std::vector<qm31> fri_witness; MerkleDecommitment decommitment; Hash commitment; };
+struct FriProof { FriLayerProof first_layer; std::vector<FriLayerProof> inner_layers; std::vector<qm31> last_layer_poly; };
+
+static cpoint host_circle_point(uint32_t index) {
+    cpoint g{2u, 1268011823u}, r{1u, 0u};
+    for (int b = 0; b < 31; b++) {
+        if ((index >> b) & 1u) r = cpoint_add(r, g);
+        g = cpoint_add(g, g);
+    }
+    return r;
+}
+template <class T> static void bit_reverse_vec(std::vector<T>& v) {
+    uint32_t log = ilog2(v.size());
+    for (size_t i = 0; i < v.size(); i++) {
+        size_t j = 0;
+        for (uint32_t b = 0; b < log; b++) j |= ((i >> b) & 1) << (log - 1 - b);
+        if (j > i) std::swap(v[i], v[j]);
+    }
+}
+// LineEvaluation::interpolate on the host (STWO/prover/line.rs:41-66) for the last FRI layer, whose
+// domain is Coset::half_odds(log): initial index 2^(29-log), step 2^(31-log).
+static std::vector<qm31> line_interpolate(std::vector<qm31> values) {
+    uint32_t log = ilog2(values.size());
+    bit_reverse_vec(values);
+    for (uint32_t k = log; k > 0; k--) {  // domain of the current chunk size 2^k: half_odds(k)
+        size_t size = (size_t)1 << k, half = size / 2;
+        for (size_t off = 0; off < values.size(); off += size)
+            for (size_t i = 0; i < half; i++) {
+                uint32_t idx = ((1u << (29 - k)) + ((uint32_t)i << (31 - k))) & 0x7fffffffu;
+                uint32_t xinv = m31_inv(host_circle_point(idx).x);
+                qm31 a = values[off + i], b = values[off + half + i];
+                values[off + i] = a + b;
+                values[off + half + i] = qm31_mul_m31(a - b, xinv);
+            }
+    }
+    uint32_t len_inv = m31_inv((uint32_t)values.size());
+    for (auto& v : values) v = qm31_mul_m31(v, len_inv);
+    return values;
+}
+
+static std::vector<qm31> secure_at_batch(const Device& d, const SecureColumnByCoords& col, const std::vector<size_t>& positions) {
+    auto flat = B200Backend::batch_at_multi(d, col.refs(), positions);  // secure_column.rs:33-44
+    std::vector<qm31> out(positions.size());
+    for (size_t j = 0; j < positions.size(); j++) out[j] = {{flat[4 * j], flat[4 * j + 1], flat[4 * j + 2], flat[4 * j + 3]}};
+    return out;
+}
+
+// fri.rs:392-436
+static void decommitment_positions_and_witness(const Device& d, const SecureColumnByCoords& column, const std::vector<size_t>& queries,
+                                               uint32_t fold_step, std::vector<size_t>& positions, std::vector<qm31>& witness) {
+    std::vector<bool> is_witness;
+    size_t i = 0;
+    while (i < queries.size()) {
+        size_t j = i;
+        while (j < queries.size() && (queries[j] >> fold_step) == (queries[i] >> fold_step)) j++;
+        size_t start = (queries[i] >> fold_step) << fold_step, qi = i;
+        for (size_t p = start; p < start + ((size_t)1 << fold_step); p++) {
+            positions.push_back(p);
+            if (qi < j && queries[qi] == p) { qi++; is_witness.push_back(false); }
+            else is_witness.push_back(true);
+        }
+        i = j;
+    }
+    auto evals = secure_at_batch(d, column, positions);
+    for (size_t k = 0; k < positions.size(); k++)
+        if (is_witness[k]) witness.push_back(evals[k]);
+}
+
+struct FriProver {
+    FriConfig config;
+    const SecureColumnByCoords* first_column = nullptr;
+    MerkleProver first_tree;
+    struct Inner { SecureColumnByCoords eval; MerkleProver tree; uint32_t fold_step; };
+    std::vector<Inner> inner;
+    std::vector<qm31> last_layer_poly;
+
+    // fri.rs:109-221
+    static FriProver commit(const Device& d, Channel& ch, FriConfig config, const SecureColumnByCoords& column) {
+        FriProver fp;
+        fp.config = config;
+        fp.first_column = &column;
+        fp.first_tree = MerkleProver::commit(d, column.refs());
+        ch.mix_root(fp.first_tree.root(d));
+        uint32_t first_log = column.columns[0].log_size(), inner_log = first_log - 1;
+        SecureColumnByCoords layer(d, (size_t)1 << inner_log, true);
+        qm31 alpha = ch.draw_secure_felt();
+        B200Backend::fold_circle_into_line(d, layer, column, alpha);
+        uint32_t last_log = ilog2(config.last_layer_domain_size());
+        if (inner_log != last_log) {
+            for (;;) {
+                uint32_t cur_log = layer.columns[0].log_size();
+                bool last_fold = !(cur_log > last_log + config.line_fold_step);
+                uint32_t step = last_fold ? cur_log - last_log : config.line_fold_step;
+                Inner in{std::move(layer), {}, step};
+                in.tree = MerkleProver::commit(d, in.eval.refs());
+                ch.mix_root(in.tree.root(d));
+                qm31 a = ch.draw_secure_felt();
+                layer = B200Backend::fold_line(d, in.eval, a);
+                for (uint32_t s = 1; s < step; s++) {  // backend/cpu/fri.rs:15-30
+                    a = a * a;
+                    layer = B200Backend::fold_line(d, layer, a);
+                }
+                fp.inner.push_back(std::move(in));
+                if (last_fold) break;
+            }
+        }
+        // commit_last_layer, fri.rs:193-221
+        if (layer.len() != config.last_layer_domain_size()) throw Error(ZKB_EINVAL, "FRI: unexpected last layer size");
+        std::vector<size_t> all(layer.len());
+        std::iota(all.begin(), all.end(), 0);
+        std::vector<qm31> coeffs = line_interpolate(secure_at_batch(d, layer, all));
+        bit_reverse_vec(coeffs);
+        size_t bound = (size_t)1 << config.log_last_layer_degree_bound;
+        for (size_t i = bound; i < coeffs.size(); i++)
+            if (!qm31_is_zero(coeffs[i])) throw Error(ZKB_EINVAL, "FRI: invalid degree");
+        coeffs.resize(bound);
+        bit_reverse_vec(coeffs);
+        fp.last_layer_poly = coeffs;
+        ch.mix_felts(fp.last_layer_poly);
+        return fp;
+    }
+
+    static FriLayerProof decommit_layer(const Device& d, const SecureColumnByCoords& col, const MerkleProver& tree,
+                                        const std::vector<size_t>& queries, uint32_t fold_step) {
+        FriLayerProof lp;
+        std::vector<size_t> positions;
+        decommitment_positions_and_witness(d, col, queries, fold_step, positions, lp.fri_witness);
+        std::map<uint32_t, std::vector<size_t>> q{{col.columns[0].log_size(), positions}};
+        lp.decommitment = tree.decommit(d, q, col.refs()).second;
+        lp.commitment = tree.root(d);
+        return lp;
+    }
+
+    // fri.rs:223-281
+    FriProof decommit(const Device& d, Channel& ch, std::vector<size_t>& query_positions) const {
+        uint32_t first_log = first_column->columns[0].log_size();
+        query_positions = sorted_dedup(draw_queries(ch, first_log, config.n_queries));
+        FriProof proof;
+        proof.first_layer = decommit_layer(d, *first_column, first_tree, query_positions, 1);
+        std::vector<size_t> q = fold_queries(query_positions, 1);
+        for (auto& in : inner) {
+            proof.inner_layers.push_back(decommit_layer(d, in.eval, in.tree, q, in.fold_step));
+            q = fold_queries(q, in.fold_step);
+        }
+        proof.last_layer_poly = last_layer_poly;
+        return proof;
+    }
+};
+
+// ------------------------------------------------------------------ commitment scheme (STWO/prover/pcs/mod.rs)
+struct PcsConfig {
+    uint32_t pow_bits;
+    FriConfig fri;
+    void mix_into(Channel& ch) const {  // STWO/core/pcs/mod.rs:47-69 (lifting_log_size None -> 0)
+        qm31 f[2] = {{{pow_bits, fri.log_blowup_factor, fri.n_queries, fri.log_last_layer_degree_bound}}, {{fri.line_fold_step, 0, 0, 0}}};
+        ch.mix_felts(f, 2);
+    }
+};
+
+struct CommitmentTreeProver {  // pcs/mod.rs:466-630
+    std::vector<BaseColumn> coeffs;  // views of the caller's columns after interpolation
+    std::vector<BaseColumn> evals;
+    MerkleProver commitment;
+    uint32_t max_log() const { return (uint32_t)commitment.layers.size() - 1; }
+};
+
+static CirclePointQ point_add(CirclePointQ p, CirclePointQ q) {  // STWO/core/circle.rs:103-113
+    return {p.x * q.x - p.y * q.y, p.x * q.y + p.y * q.x};
+}
+static CirclePointQ point_repeated_double(CirclePointQ p, uint32_t n) {
+    for (uint32_t i = 0; i < n; i++) p = point_add(p, p);
+    return p;
+}
+static CirclePointQ get_random_point(Channel& ch) {  // circle.rs:147-163
+    qm31 t = ch.draw_secure_felt();
+    qm31 t2 = t * t;
+    qm31 inv = qm31_inv(t2 + qm31_one());
+    return {(qm31_one() - t2) * inv, qm31_dbl(t) * inv};
+}
+static bool point_less(const CirclePointQ& a, const CirclePointQ& b) {
+    for (int k = 0; k < 4; k++) if (a.x.c[k] != b.x.c[k]) return a.x.c[k] < b.x.c[k];
+    for (int k = 0; k < 4; k++) if (a.y.c[k] != b.y.c[k]) return a.y.c[k] < b.y.c[k];
+    return false;
+}
+
+struct PcsProof {
+    std::vector<Hash> commitments;
+    std::vector<std::vector<std::vector<qm31>>> sampled_values;
+    std::vector<MerkleDecommitment> decommitments;
+    std::vector<std::vector<uint32_t>> queried_values;
+    uint64_t proof_of_work = 0;
+    FriProof fri;
+    static void put_q(std::vector<uint32_t>& o, qm31 q) { o.insert(o.end(), q.c, q.c + 4); }
+    static void put_hash(std::vector<uint32_t>& o, const Hash& h) { o.insert(o.end(), h.begin(), h.end()); }
+    static void put_dec(std::vector<uint32_t>& o, const MerkleDecommitment& d) {
+        o.push_back((uint32_t)d.hash_witness.size());
+        for (auto& h : d.hash_witness) put_hash(o, h);
+        o.push_back((uint32_t)d.column_witness.size());
+        o.insert(o.end(), d.column_witness.begin(), d.column_witness.end());
+    }
+    static void put_layer(std::vector<uint32_t>& o, const FriLayerProof& l) {
+        o.push_back((uint32_t)l.fri_witness.size());
+        for (auto q : l.fri_witness) put_q(o, q);
+        put_dec(o, l.decommitment);
+        put_hash(o, l.commitment);
+    }
+    std::vector<uint32_t> to_words() const {
+        std::vector<uint32_t> o;
+        o.push_back((uint32_t)commitments.size());
+        for (auto& h : commitments) put_hash(o, h);
+        for (auto& t : sampled_values) {
+            o.push_back((uint32_t)t.size());
+            for (auto& c : t) { o.push_back((uint32_t)c.size()); for (auto q : c) put_q(o, q); }
+        }
+        for (auto& d : decommitments) put_dec(o, d);
+        for (auto& t : queried_values) { o.push_back((uint32_t)t.size()); o.insert(o.end(), t.begin(), t.end()); }
+        o.push_back((uint32_t)proof_of_work);
+        o.push_back((uint32_t)(proof_of_work >> 32));
+        put_layer(o, fri.first_layer);
+        o.push_back((uint32_t)fri.inner_layers.size());
+        for (auto& l : fri.inner_layers) put_layer(o, l);
+        o.push_back((uint32_t)fri.last_layer_poly.size());
+        for (auto q : fri.last_layer_poly) put_q(o, q);
+        return o;
+    }
+};
+
+struct CommitmentSchemeProver {
+    const Device& d;
+    PcsConfig config;
+    std::vector<CommitmentTreeProver> trees;
+    float* phase_ms;
+    int ev = 32;  // event slots 32.. mark phase boundaries
+    std::vector<std::pair<int, int>> marks;  // (phase, slot after it)
+
+    CommitmentSchemeProver(const Device& dev, PcsConfig cfg, float* phases) : d(dev), config(cfg), phase_ms(phases) {
+        if (phase_ms) { for (int i = 0; i < ZKB_PCS_N_PHASES; i++) phase_ms[i] = 0.f; mark(-1); }
+    }
+    void mark(int phase) {
+        if (!phase_ms || ev >= 63) return;
+        d.check(zkb_event_record(d.ctx(), ev));
+        marks.push_back({phase, ev++});
+    }
+    void finish_timing() {
+        if (!phase_ms) return;
+        for (size_t i = 1; i < marks.size(); i++) {
+            float ms = 0.f;
+            d.check(zkb_event_elapsed_ms(d.ctx(), marks[i - 1].second, marks[i].second, &ms));
+            if (marks[i].first >= 0) phase_ms[marks[i].first] += ms;
+        }
+    }
+
+    // TreeBuilder::extend_evals + commit (pcs/mod.rs:429-464) -> CommitmentTreeProver::new (:481-537).
+    // `columns` are consumed: interpolated in place, per size group.
+    void commit_evals(std::vector<BaseColumn> columns, Channel& ch) {
+        CommitmentTreeProver t;
+        std::map<uint32_t, std::vector<size_t>> by_log;
+        for (size_t i = 0; i < columns.size(); i++) by_log[columns[i].log_size()].push_back(i);
+        for (auto& g : by_log) {
+            std::vector<BaseColumn*> cols;
+            for (auto i : g.second) cols.push_back(&columns[i]);
+            B200Backend::interpolate_columns(d, cols);
+        }
+        mark(0);
+        t.evals.resize(columns.size());
+        for (auto& g : by_log) {
+            std::vector<const BaseColumn*> cols;
+            for (auto i : g.second) cols.push_back(&columns[i]);
+            auto ev_cols = B200Backend::evaluate_polynomials(d, cols, config.fri.log_blowup_factor);
+            for (size_t k = 0; k < g.second.size(); k++) t.evals[g.second[k]] = std::move(ev_cols[k]);
+        }
+        mark(1);
+        t.coeffs = std::move(columns);
+        std::vector<const BaseColumn*> refs;
+        for (auto& e : t.evals) refs.push_back(&e);
+        t.commitment = MerkleProver::commit(d, refs);
+        ch.mix_root(t.commitment.root(d));
+        mark(2);
+        trees.push_back(std::move(t));
+    }
+
+    // pcs/quotient_ops.rs:73-194 with STWO/core/pcs/quotients.rs:306-345 and :75-104
+    SecureColumnByCoords compute_fri_quotients(const std::vector<std::vector<std::vector<PointSample>>>& samples, qm31 random_coeff,
+                                               uint32_t lifting_log) {
+        std::vector<const BaseColumn*> flat_cols;
+        std::vector<uint32_t> flat_logs;
+        std::vector<std::vector<std::pair<PointSample, qm31>>> flat_samples;
+        qm31 pow = qm31_one();
+        // step of CanonicCoset(lifting_log): the point of index 2^(31 - lifting_log)
+        cpoint gen = host_circle_point(1u << (31 - lifting_log));
+        for (size_t t = 0; t < trees.size(); t++)
+            for (size_t c = 0; c < trees[t].evals.size(); c++) {
+                uint32_t log_size = trees[t].evals[c].log_size();
+                flat_cols.push_back(&trees[t].evals[c]);
+                flat_logs.push_back(log_size);
+                std::vector<std::pair<PointSample, qm31>> v;
+                const auto& sc = samples[t][c];
+                if (!sc.empty()) {
+                    if (sc.size() == 2) {
+                        cpoint per = gen;
+                        for (uint32_t k = 0; k < log_size; k++) per = cpoint_add(per, per);
+                        CirclePointQ pq{qm31_from_m31(per.x), qm31_from_m31(per.y)};
+                        v.push_back({PointSample{point_add(sc[1].point, pq), sc[1].value}, pow});
+                        pow = pow * random_coeff;
+                    }
+                    for (auto& smp : sc) { v.push_back({smp, pow}); pow = pow * random_coeff; }
+                }
+                flat_samples.push_back(v);
+            }
+        std::vector<size_t> order(flat_cols.size());
+        std::iota(order.begin(), order.end(), 0);
+        std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return flat_logs[a] < flat_logs[b]; });
+        std::vector<AccumulatedNumerators> accs;
+        for (size_t i = 0; i < order.size();) {
+            size_t j = i;
+            while (j < order.size() && flat_logs[order[j]] == flat_logs[order[i]]) j++;
+            std::vector<const BaseColumn*> group_cols;
+            std::vector<ColumnSampleBatch> batches;
+            for (size_t k = i; k < j; k++) {
+                group_cols.push_back(flat_cols[order[k]]);
+                for (auto& sp : flat_samples[order[k]]) {
+                    ColumnSampleBatch* b = nullptr;
+                    for (auto& x : batches) if (x.point == sp.first.point) { b = &x; break; }
+                    if (!b) { batches.push_back({sp.first.point, {}}); b = &batches.back(); }
+                    b->cols_vals_randpows.push_back({k - i, sp.first.value, sp.second});
+                }
+            }
+            B200Backend::accumulate_numerators(d, group_cols, batches, accs);
+            i = j;
+        }
+        std::stable_sort(accs.begin(), accs.end(),
+                         [](const AccumulatedNumerators& a, const AccumulatedNumerators& b) { return point_less(a.sample_point, b.sample_point); });
+        std::vector<AccumulatedNumerators> per_point;
+        for (size_t i = 0; i < accs.size();) {
+            size_t j = i;
+            while (j < accs.size() && accs[j].sample_point == accs[i].sample_point) j++;
+            qm31 first = qm31_zero();
+            std::vector<SecureColumnByCoords> cols;
+            for (size_t k = i; k < j; k++) {
+                first = first + accs[k].first_linear_term_acc;
+                cols.push_back(std::move(accs[k].partial_numerators_acc));
+            }
+            CirclePointQ pt = accs[i].sample_point;
+            per_point.push_back({pt, B200Backend::lift_and_accumulate(d, std::move(cols)), first});
+            i = j;
+        }
+        return B200Backend::compute_quotients_and_combine(d, per_point, lifting_log);
+    }
+
+    // pcs/mod.rs:168-419
+    PcsProof prove_values(const std::vector<std::vector<std::vector<CirclePointQ>>>& sampled_points, Channel& ch) {
+        PcsProof proof;
+        uint32_t lifting_log = trees.back().max_log();
+        // batch out-of-domain evaluation: one call per (coefficient size, transformed point) group (:187-265)
+        std::vector<std::vector<std::vector<PointSample>>> samples(trees.size());
+        struct Group { uint32_t log; CirclePointQ pt; std::vector<std::array<size_t, 3>> where; std::vector<const BaseColumn*> cols; };
+        std::vector<Group> groups;
+        for (size_t t = 0; t < trees.size(); t++) {
+            samples[t].resize(trees[t].coeffs.size());
+            for (size_t c = 0; c < trees[t].coeffs.size(); c++) {
+                uint32_t poly_log = trees[t].evals[c].log_size(), coeff_log = trees[t].coeffs[c].log_size();
+                for (size_t k = 0; k < sampled_points[t][c].size(); k++) {
+                    CirclePointQ p = sampled_points[t][c][k];
+                    samples[t][c].push_back({p, qm31_zero()});
+                    CirclePointQ tp = point_repeated_double(p, lifting_log - poly_log);
+                    Group* g = nullptr;
+                    for (auto& x : groups) if (x.log == coeff_log && x.pt == tp) { g = &x; break; }
+                    if (!g) { groups.push_back({coeff_log, tp, {}, {}}); g = &groups.back(); }
+                    g->where.push_back({t, c, k});
+                    g->cols.push_back(&trees[t].coeffs[c]);
+                }
+            }
+        }
+        for (auto& g : groups) {
+            auto vals = B200Backend::batch_eval_at_point(d, g.cols, g.pt);
+            for (size_t i = 0; i < vals.size(); i++) samples[g.where[i][0]][g.where[i][1]][g.where[i][2]].value = vals[i];
+        }
+        std::vector<qm31> flat_values;
+        for (size_t t = 0; t < trees.size(); t++) {
+            proof.sampled_values.emplace_back();
+            for (auto& col : samples[t]) {
+                std::vector<qm31> v;
+                for (auto& smp : col) { v.push_back(smp.value); flat_values.push_back(smp.value); }
+                proof.sampled_values[t].push_back(v);
+            }
+        }
+        mark(3);
+        ch.mix_felts(flat_values);
+        qm31 random_coeff = ch.draw_secure_felt();
+        SecureColumnByCoords quotients = compute_fri_quotients(samples, random_coeff, lifting_log);
+        mark(4);
+        FriProver fri = FriProver::commit(d, ch, config.fri, quotients);
+        mark(5);
+        proof.proof_of_work = B200Backend::grind(d, ch.pow_prefixed_digest(config.pow_bits), config.pow_bits);
+        ch.mix_u64(proof.proof_of_work);
+        mark(6);
+        std::vector<size_t> query_positions;
+        proof.fri = fri.decommit(d, ch, query_positions);
+        for (auto& t : trees) {  // STWO/core/pcs/utils.rs:200-218, then pcs/mod.rs:575-630
+            uint32_t tree_max = t.max_log();
+            std::vector<size_t> q;
+            for (auto pos : query_positions) q.push_back(((pos >> (lifting_log - tree_max + 1)) << 1) + (pos & 1));
+            std::map<uint32_t, std::vector<size_t>> per_log;
+            std::vector<const BaseColumn*> refs;
+            for (auto& e : t.evals) {
+                refs.push_back(&e);
+                uint32_t log = e.log_size();
+                if (per_log.count(log)) continue;
+                std::vector<size_t> positions;
+                for (auto pos : q) positions.push_back(((pos >> (tree_max - log + 1)) << 1) + (pos & 1));
+                per_log[log] = sorted_dedup(positions);
+            }
+            auto r = t.commitment.decommit(d, per_log, refs);
+            proof.queried_values.push_back(std::move(r.first));
+            proof.decommitments.push_back(std::move(r.second));
+            proof.commitments.push_back(t.commitment.root(d));
+        }
+        mark(7);
+        return proof;
+    }
+};
+
+// ------------------------------------------------------------------ GKR (STWO/prover/lookups)
+// Dense univariate polynomial over QM31, low coefficient first (lookups/utils.rs:12-146).
+struct UniPoly {
+    std::vector<qm31> c;
+    void trim() { while (!c.empty() && qm31_is_zero(c.back())) c.pop_back(); }
+    qm31 eval(qm31 x) const {
+        qm31 acc = qm31_zero();
+        for (size_t i = c.size(); i-- > 0;) acc = acc * x + c[i];
+        return acc;
+    }
+    static UniPoly mul(UniPoly a, UniPoly b) {
+        a.trim(); b.trim();
+        if (a.c.empty() || b.c.empty()) return {};
+        UniPoly r;
+        r.c.assign(a.c.size() + b.c.size() - 1, qm31_zero());
+        for (size_t i = 0; i < a.c.size(); i++)
+            for (size_t j = 0; j < b.c.size(); j++) r.c[i + j] = r.c[i + j] + a.c[i] * b.c[j];
+        r.trim();
+        return r;
+    }
+    static UniPoly add(const UniPoly& a, const UniPoly& b) {
+        UniPoly r;
+        for (size_t i = 0; i < std::max(a.c.size(), b.c.size()); i++)
+            r.c.push_back((i < a.c.size() ? a.c[i] : qm31_zero()) + (i < b.c.size() ? b.c[i] : qm31_zero()));
+        return r;
+    }
+    static UniPoly interpolate_lagrange(const std::vector<qm31>& xs, const std::vector<qm31>& ys) {  // utils.rs:26-54
+        UniPoly coeffs;
+        for (size_t i = 0; i < xs.size(); i++) {
+            qm31 prod = ys[i];
+            for (size_t j = 0; j < xs.size(); j++)
+                if (i != j) prod = prod * qm31_inv(xs[i] - xs[j]);
+            UniPoly term;
+            term.c = {prod};
+            term.trim();
+            for (size_t j = 0; j < xs.size(); j++)
+                if (i != j) { UniPoly lin; lin.c = {qm31_neg(xs[j]), qm31_one()}; term = mul(term, lin); }
+            coeffs = add(coeffs, term);
+        }
+        coeffs.trim();
+        return coeffs;
+    }
+};
+
+static qm31 eq1(qm31 x, qm31 y) { return x * y + (qm31_one() - x) * (qm31_one() - y); }  // utils.rs:165-170
+static qm31 horner(const std::vector<qm31>& v, qm31 x) {
+    qm31 acc = qm31_zero();
+    for (size_t i = v.size(); i-- > 0;) acc = acc * x + v[i];
+    return acc;
+}
+
+// gkr_prover.rs:884-923
+static UniPoly correct_sum_as_poly_in_first_variable(qm31 f0, qm31 f2, qm31 claim, const std::vector<qm31>& y, size_t k) {
+    size_t n = y.size();
+    qm31 a = qm31_one();
+    for (size_t i = 0; i < n - k + 1; i++) a = a * eq1(qm31_zero(), y[i]);
+    a = qm31_inv(a);
+    qm31 two = qm31_from_m31(2);
+    qm31 b = (qm31_one() - y[n - k]) * qm31_inv(qm31_one() - qm31_dbl(y[n - k]));
+    qm31 r0 = f0 * eq1(qm31_zero(), y[n - k]) * a;
+    qm31 r1 = claim - r0;
+    qm31 r2 = f2 * eq1(two, y[n - k]) * a;
+    return UniPoly::interpolate_lagrange({qm31_zero(), qm31_one(), two, b}, {r0, r1, r2, qm31_zero()});
+}
+
+struct GkrOracle {  // GkrMultivariatePolyOracle, gkr_prover.rs:473-556
+    Layer input_layer;
+    qm31 eq_fixed_var_correction;
+    size_t n_variables() const { return input_layer.n_variables() - 1; }
+};
+
+static std::vector<qm31> mle_to_cpu(const Device& d, const SecureMle& m) {
+    auto w = m.words.to_cpu();
+    std::vector<qm31> out(m.len());
+    for (size_t i = 0; i < out.size(); i++) out[i] = {{w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]}};
+    return out;
+}
+
+static Layer layer_view(const Device& d, int kind, const uint32_t* num, const uint32_t* den, size_t n) {
+    Layer l;
+    l.kind = kind;
+    l.den.words = BaseColumn::view(d, const_cast<uint32_t*>(den), 4 * n);
+    if (kind == ZKB_GKR_LOGUP_GENERIC) l.num.words = BaseColumn::view(d, const_cast<uint32_t*>(num), 4 * n);
+    if (kind == ZKB_GKR_LOGUP_MULTIPLICITIES) l.num_base = BaseColumn::view(d, const_cast<uint32_t*>(num), n);
+    return l;
+}
+
+// gkr_prover.rs:657-882 with sumcheck.rs:96-176. Returns the proof word stream.
+static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::vector<Layer> input_layers) {
+    size_t n_inst = input_layers.size();
+    std::vector<size_t> n_layers_by_inst;
+    for (auto& l : input_layers) n_layers_by_inst.push_back(l.n_variables());
+    size_t n_layers = *std::max_element(n_layers_by_inst.begin(), n_layers_by_inst.end());
+    std::vector<std::vector<Layer>> towers(n_inst);  // gen_layers, :847-852
+    for (size_t i = 0; i < n_inst; i++) {
+        towers[i].push_back(std::move(input_layers[i]));
+        while (towers[i].back().n_variables() > 0) towers[i].push_back(B200Backend::next_layer(d, towers[i].back()));
+    }
+    std::vector<std::vector<UniPoly>> sumcheck_round_polys;
+    std::vector<std::vector<std::vector<std::array<qm31, 2>>>> masks_by_inst(n_inst);
+    std::vector<std::vector<qm31>> output_claims(n_inst), claims(n_inst);
+    std::vector<bool> active(n_inst, false);
+    std::vector<qm31> ood_point;
+
+    auto take = [&](size_t i) { Layer l = std::move(towers[i].back()); towers[i].pop_back(); return l; };
+    for (size_t layer = 0; layer < n_layers; layer++) {
+        size_t n_remaining = n_layers - layer;
+        for (size_t i = 0; i < n_inst; i++)
+            if (n_layers_by_inst[i] == n_remaining) {
+                Layer out = take(i);  // output layer: one entry per column
+                std::vector<qm31> vals;
+                qm31 den0 = mle_to_cpu(d, out.den)[0];
+                if (out.kind == ZKB_GKR_GRAND_PRODUCT) vals = {den0};
+                else if (out.kind == ZKB_GKR_LOGUP_GENERIC) vals = {mle_to_cpu(d, out.num)[0], den0};
+                else if (out.kind == ZKB_GKR_LOGUP_MULTIPLICITIES) vals = {qm31_from_m31(out.num_base.to_cpu()[0]), den0};
+                else vals = {qm31_one(), den0};
+                claims[i] = vals;
+                output_claims[i] = vals;
+                active[i] = true;
+            }
+        for (size_t i = 0; i < n_inst; i++)
+            if (active[i]) ch.mix_felts(claims[i]);
+        // EqEvals::generate, :235-247
+        SecureMle eq_evals;
+        if (ood_point.empty()) eq_evals = B200Backend::gen_eq_evals(d, {}, qm31_one());
+        else eq_evals = B200Backend::gen_eq_evals(d, std::vector<qm31>(ood_point.begin() + 1, ood_point.end()), eq1(qm31_zero(), ood_point[0]));
+        qm31 sumcheck_alpha = ch.draw_secure_felt();
+        qm31 lambda = ch.draw_secure_felt();
+        std::vector<GkrOracle> oracles;
+        std::vector<qm31> sc_claims;
+        std::vector<size_t> sc_inst;
+        for (size_t i = 0; i < n_inst; i++)
+            if (active[i]) {
+                oracles.push_back({take(i), qm31_one()});
+                sc_claims.push_back(horner(claims[i], lambda));
+                sc_inst.push_back(i);
+            }
+        size_t nv = 0;
+        for (auto& o : oracles) nv = std::max(nv, o.n_variables());
+        for (size_t k = 0; k < oracles.size(); k++) sc_claims[k] = qm31_mul_m31(sc_claims[k], 1u << (nv - oracles[k].n_variables()));
+        std::vector<UniPoly> round_polys;
+        std::vector<qm31> assignment;
+        const uint32_t half = m31_inv(2);
+        for (size_t round = 0; round < nv; round++) {
+            size_t n_rem = nv - round;
+            std::vector<UniPoly> this_round;
+            for (size_t k = 0; k < oracles.size(); k++) {
+                UniPoly rp;
+                if (n_rem == oracles[k].n_variables()) {
+                    auto sums = B200Backend::round_sums(d, oracles[k].input_layer, eq_evals, lambda);
+                    rp = correct_sum_as_poly_in_first_variable(sums.first * oracles[k].eq_fixed_var_correction,
+                                                               sums.second * oracles[k].eq_fixed_var_correction, sc_claims[k], ood_point,
+                                                               oracles[k].n_variables());
+                } else {
+                    rp.c = {qm31_mul_m31(sc_claims[k], half)};
+                    rp.trim();
+                }
+                if (!(rp.eval(qm31_zero()) + rp.eval(qm31_one()) == sc_claims[k])) throw Error(ZKB_EINVAL, "sumcheck: round polynomial does not match the claim");
+                this_round.push_back(rp);
+            }
+            UniPoly combined;
+            for (size_t k = this_round.size(); k-- > 0;) {
+                for (auto& c : combined.c) c = c * sumcheck_alpha;
+                combined = UniPoly::add(combined, this_round[k]);
+            }
+            ch.mix_felts(combined.c);
+            qm31 challenge = ch.draw_secure_felt();
+            for (size_t k = 0; k < oracles.size(); k++) sc_claims[k] = this_round[k].eval(challenge);
+            for (size_t k = 0; k < oracles.size(); k++)
+                if (n_rem == oracles[k].n_variables() && oracles[k].n_variables() != 0) {
+                    qm31 z0 = ood_point[ood_point.size() - oracles[k].n_variables()];
+                    oracles[k].eq_fixed_var_correction = oracles[k].eq_fixed_var_correction * eq1(challenge, z0);
+                    oracles[k].input_layer = B200Backend::fix_first_variable(d, std::move(oracles[k].input_layer), challenge);
+                }
+            round_polys.push_back(combined);
+            assignment.push_back(challenge);
+        }
+        sumcheck_round_polys.push_back(round_polys);
+        std::vector<std::vector<std::array<qm31, 2>>> masks;  // try_into_mask, :572-597
+        for (auto& o : oracles) {
+            const Layer& l = o.input_layer;
+            if (l.len() != 2) throw Error(ZKB_EINVAL, "gkr: oracle is not constant after sumcheck");
+            auto den = mle_to_cpu(d, l.den);
+            if (l.kind == ZKB_GKR_GRAND_PRODUCT) masks.push_back({{den[0], den[1]}});
+            else if (l.kind == ZKB_GKR_LOGUP_GENERIC) { auto num = mle_to_cpu(d, l.num); masks.push_back({{num[0], num[1]}, {den[0], den[1]}}); }
+            else if (l.kind == ZKB_GKR_LOGUP_SINGLES) masks.push_back({{qm31_one(), qm31_one()}, {den[0], den[1]}});
+            else throw Error(ZKB_EINVAL, "gkr: a multiplicities layer cannot be a mask");
+        }
+        for (size_t k = 0; k < oracles.size(); k++) {
+            std::vector<qm31> flat;
+            for (auto& col : masks[k]) { flat.push_back(col[0]); flat.push_back(col[1]); }
+            ch.mix_felts(flat);
+            masks_by_inst[sc_inst[k]].push_back(masks[k]);
+        }
+        qm31 challenge = ch.draw_secure_felt();
+        ood_point = assignment;
+        ood_point.push_back(challenge);
+        for (size_t k = 0; k < oracles.size(); k++) {
+            std::vector<qm31> next;
+            for (auto& col : masks[k]) next.push_back(challenge * (col[1] - col[0]) + col[0]);
+            claims[sc_inst[k]] = next;
+        }
+    }
+    std::vector<uint32_t> o;
+    auto put = [&](qm31 q) { o.insert(o.end(), q.c, q.c + 4); };
+    o.push_back((uint32_t)sumcheck_round_polys.size());
+    for (auto& l : sumcheck_round_polys) {
+        o.push_back((uint32_t)l.size());
+        for (auto& p : l) { o.push_back((uint32_t)p.c.size()); for (auto q : p.c) put(q); }
+    }
+    for (auto& inst : masks_by_inst) {
+        o.push_back((uint32_t)inst.size());
+        for (auto& m : inst) { o.push_back((uint32_t)m.size()); for (auto& col : m) { put(col[0]); put(col[1]); } }
+    }
+    for (auto& c : output_claims) { o.push_back((uint32_t)c.size()); for (auto q : c) put(q); }
+    o.push_back((uint32_t)ood_point.size());
+    for (auto q : ood_point) put(q);
+    for (auto& c : claims) { o.push_back((uint32_t)c.size()); for (auto q : c) put(q); }
+    return o;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+static int pcs_prove_impl(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint32_t* const* d_cols, const uint32_t* const* h_cols,
+                          const uint32_t* col_logs, const zkb_pcs_config* cfg, int two_sample_every, uint32_t* h_out, size_t cap,
+                          size_t* n_words, float* h_phase_ms) {
+    if (!ctx) return ZKB_EINVAL;
+    if (!tree_ncols || !col_logs || !cfg || !h_out || !n_words || n_trees <= 0 || (!d_cols && !h_cols)) return ZKB_EINVAL;
+    try {
+        Device dev(ctx);
+        PcsConfig config{cfg->pow_bits, {cfg->log_blowup_factor, cfg->log_last_layer_degree_bound, cfg->n_queries, 1}};
+        int total = 0;
+        uint32_t max_log = 0;
+        for (int t = 0; t < n_trees; t++) total += tree_ncols[t];
+        for (int i = 0; i < total; i++) max_log = std::max(max_log, col_logs[i]);
+        if ((int)(max_log + config.fri.log_blowup_factor) > zkb_max_log_size(ctx)) return ZKB_EINVAL;
+        Channel ch;
+        config.mix_into(ch);
+        CommitmentSchemeProver prover(dev, config, h_phase_ms);
+        int flat = 0;
+        for (int t = 0; t < n_trees; t++) {
+            std::vector<BaseColumn> columns;
+            for (int c = 0; c < tree_ncols[t]; c++, flat++) {
+                size_t n = (size_t)1 << col_logs[flat];
+                if (d_cols) columns.push_back(BaseColumn::view(dev, d_cols[flat], n));
+                else columns.emplace_back(dev, h_cols[flat], n);
+            }
+            prover.commit_evals(std::move(columns), ch);
+        }
+        CirclePointQ oods = get_random_point(ch);
+        std::vector<std::vector<std::vector<CirclePointQ>>> points(n_trees);
+        flat = 0;
+        for (int t = 0; t < n_trees; t++)
+            for (int c = 0; c < tree_ncols[t]; c++, flat++) {
+                std::vector<CirclePointQ> p;
+                if (two_sample_every && flat % two_sample_every == 0) {
+                    // one trace step back: the conjugate of the step of CanonicCoset(col_log)
+                    cpoint st = host_circle_point(1u << (31 - col_logs[flat]));
+                    p.push_back(point_add(oods, {qm31_from_m31(st.x), qm31_from_m31(m31_neg(st.y))}));
+                }
+                p.push_back(oods);
+                points[t].push_back(p);
+            }
+        PcsProof proof = prover.prove_values(points, ch);
+        prover.finish_timing();
+        std::vector<uint32_t> w = proof.to_words();
+        w.insert(w.end(), ch.digest().begin(), ch.digest().end());
+        *n_words = w.size();
+        if (w.size() > cap) return zk_set_error_public(ctx, ZKB_EINVAL, "zkb_pcs_prove: output buffer too small");
+        memcpy(h_out, w.data(), w.size() * 4);
+        return ZKB_OK;
+    } catch (const Error& e) {
+        return zk_set_error_public(ctx, e.code, e.what());
+    } catch (const std::exception& e) {
+        return zk_set_error_public(ctx, ZKB_ENOMEM, e.what());
+    }
+}
+
+extern "C" {
+
+int zkb_pcs_prove_device(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint32_t* const* d_cols, const uint32_t* col_logs,
+                         const zkb_pcs_config* config, int two_sample_every, uint32_t* h_out, size_t cap, size_t* n_words,
+                         float* h_phase_ms) {
+    return pcs_prove_impl(ctx, n_trees, tree_ncols, d_cols, nullptr, col_logs, config, two_sample_every, h_out, cap, n_words, h_phase_ms);
+}
+
+int zkb_pcs_prove_host(zkb_ctx* ctx, int n_trees, const int* tree_ncols, const uint32_t* const* h_cols, const uint32_t* col_logs,
+                       const zkb_pcs_config* config, int two_sample_every, uint32_t* h_out, size_t cap, size_t* n_words,
+                       float* h_phase_ms) {
+    return pcs_prove_impl(ctx, n_trees, tree_ncols, nullptr, h_cols, col_logs, config, two_sample_every, h_out, cap, n_words, h_phase_ms);
+}
+
+int zkb_gkr_prove_device(zkb_ctx* ctx, int n_inst, const int* kinds, const uint32_t* const* d_nums, const uint32_t* const* d_dens,
+                         const uint64_t* ns, uint64_t seed, uint32_t* h_out, size_t cap, size_t* n_words) {
+    if (!ctx) return ZKB_EINVAL;
+    if (n_inst <= 0 || !kinds || !d_nums || !d_dens || !ns || !h_out || !n_words) return ZKB_EINVAL;
+    try {
+        Device dev(ctx);
+        std::vector<Layer> layers;
+        for (int i = 0; i < n_inst; i++) {
+            if (kinds[i] < 0 || kinds[i] > 3 || ns[i] < 1 || (ns[i] & (ns[i] - 1))) return ZKB_EINVAL;
+            layers.push_back(layer_view(dev, kinds[i], d_nums[i], d_dens[i], ns[i]));
+        }
+        Channel ch;
+        ch.mix_u64(seed);
+        std::vector<uint32_t> w = gkr_prove_batch(dev, ch, std::move(layers));
+        w.insert(w.end(), ch.digest().begin(), ch.digest().end());
+        *n_words = w.size();
+        if (w.size() > cap) return zk_set_error_public(ctx, ZKB_EINVAL, "zkb_gkr_prove: output buffer too small");
+        memcpy(h_out, w.data(), w.size() * 4);
+        return ZKB_OK;
+    } catch (const Error& e) {
+        return zk_set_error_public(ctx, e.code, e.what());
+    } catch (const std::exception& e) {
+        return zk_set_error_public(ctx, ZKB_ENOMEM, e.what());
+    }
+}
+
+}  // extern "C"
