@@ -2,9 +2,11 @@
 """Benchmark of the commitment hot path on B200: the PCS-commit microbench shape.
 
 Workload (one "step"): `--cols` M31 trace columns of 2^`--log-size` values each are interpolated,
-extended to the canonic domain of log size `--log-size + --log-blowup` (the low-degree extension) and
-committed with the Blake2s-M31 Merkle tree (leaf layer over all columns, then every upper layer down to
-the root). Inputs are seeded synthetic columns (SplitMix64, seed 0x5EED0001 + column index).
+extended to the canonic domain of log size `--log-size + --log-blowup` (the low-degree extension),
+committed with the Blake2s-M31 Merkle tree, opened at one channel-drawn point per column, and the
+opening is proved: quotients, FRI commit to the last layer, proof of work, query decommitment
+(PcsConfig: pow_bits 10, FriConfig(0, log_blowup, 3, 1), the library default with the blow-up
+of the workload). Inputs are seeded synthetic columns (SplitMix64, seed 0x5EED0001 + column index).
 
   python bench.py [--gpus N] [--steps K] [--warmup W]            the CUDA library through its C ABI
   python bench.py --impl reference ...                             the CPU restatement of the reference
@@ -101,28 +103,27 @@ def measured_hbm_peak():
 
 
 def cpu_leg(args, sample_cols):
-    """Times the CPU oracle (a port of the reference's CpuBackend) on `sample_cols` columns of the workload."""
+    """Times the CPU oracle (a C++ port of the reference's CpuBackend and protocol code, OpenMP over
+    columns / rows where the operator allows) on `sample_cols` columns of the workload: the same
+    commit + prove flow as the GPU step."""
     import oracle
 
     log_n, log_out = args.log_size, args.log_size + args.log_blowup
-    vals = np.stack([splitmix_column(SEED0 + c, 1 << log_n) for c in range(sample_cols)])
+    cols = [splitmix_column(SEED0 + c, 1 << log_n) for c in range(sample_cols)]
     oracle.twiddles(log_out - 1)  # the tower is built once, outside the timed region (as precompute_twiddles is)
     t0 = time.perf_counter()
-    coeffs = oracle.interpolate_cols(vals, log_n)
-    ev = oracle.evaluate_cols(coeffs, log_n, log_out)
-    layer = oracle.commit_on_layer(log_out, None, list(ev), m31=True)
-    for lg in range(log_out - 1, -1, -1):
-        layer = oracle.commit_on_layer(lg, layer, [], m31=True)
+    words = oracle.pcs_prove([cols], pow_bits=args.pow_bits, log_blowup=args.log_blowup, log_last_layer=0,
+                             n_queries=args.n_queries, cap=1 << 26)
     dt = time.perf_counter() - t0
     cells = sample_cols * (1 << log_n)
-    return cells / dt, dt, oracle.num_threads(), layer
+    return cells / dt, dt, oracle.num_threads(), words
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
     sample_cols = min(args.cols, args.ref_cols)
-    for _ in range(args.warmup if args.warmup < 1 else 1):
+    for _ in range(min(args.warmup, 1)):
         cpu_leg(args, sample_cols)
     vals, times = [], []
     for _ in range(args.steps):
@@ -130,8 +131,8 @@ def run_reference(args, rank):
         vals.append(v)
         times.append(dt)
     value = float(np.mean(vals))
-    sample = (f"{sample_cols} of {args.cols} columns at full height 2^{args.log_size}: interpolate + LDE to 2^"
-              f"{args.log_size + args.log_blowup} + Blake2s-M31 Merkle tree, all host threads (OpenMP)")
+    sample = (f"{sample_cols} of {args.cols} columns at full height 2^{args.log_size}: commit (interpolate, LDE, Merkle) + "
+              f"prove (sample, quotients, FRI, grind, decommit)")
     line = {
         "impl": "reference", "metric": "committed_m31_cells_per_s", "value": value, "unit": "cells/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": float(np.mean(times)) * 1e3, "higher_is_better": True,
@@ -140,16 +141,28 @@ def run_reference(args, rank):
         "cpu_baseline": {"value": value, "unit": "cells/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "cells/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference is Rust and cannot be built with this image's toolchains; this arm times the C++ restatement "
-                "of its CpuBackend (oracle/), not the reference's SIMD backend",
+                "of its CpuBackend and protocol code (oracle/), not the reference's SIMD backend",
     }
     print(json.dumps(line))
 
 
 def workload_config(args):
-    return {"workload": f"pcs_commit_{args.cols}cols_log{args.log_size}_blowup{1 << args.log_blowup}",
-            "columns": args.cols, "log_size": args.log_size, "log_blowup": args.log_blowup,
-            "hasher": "blake2s_m31", "parallelism": f"replicas x{args.gpus}" if args.gpus > 1 else "single",
+    return {"workload": f"pcs_prove_{args.cols}cols_log{args.log_size}_blowup{1 << args.log_blowup}",
+            "columns": args.cols, "log_size": args.log_size, "log_blowup": args.log_blowup, "pow_bits": args.pow_bits,
+            "n_queries": args.n_queries, "log_last_layer_degree_bound": 0, "hasher": "blake2s_m31",
+            "step": "interpolate + LDE + Merkle commit + out-of-domain sample + quotients + FRI commit + grind + decommit",
+            "parallelism": f"replicas x{args.gpus}" if args.gpus > 1 else "single",
             "l2": "inputs (>= 1 GiB per step) are larger than L2"}
+
+
+# Algorithmic bytes of the operators (per step), for the roofline figures.
+def algorithmic_bytes(ncols, n, N):
+    return {
+        "interpolate": 8.0 * n * ncols,                 # read n + write n per column
+        "extend": (4.0 * n + 4.0 * N) * ncols,          # read n coefficients, write N evaluations
+        "merkle_leaves": 4.0 * ncols * N + 32.0 * N,    # read every evaluation, write one hash per row
+        "quot_numerators": 4.0 * ncols * N + 16.0 * N,  # one sample batch
+    }
 
 
 def run_ours(args, rank, world, local_rank):
@@ -171,36 +184,32 @@ def run_ours(args, rank, world, local_rank):
     h_trace, h_addr = ctx.alloc_pinned(ncols * n)
     for c in range(ncols):
         h_trace[c * n:(c + 1) * n] = splitmix_column(SEED0 + c, n)
-    h_root, h_root_addr = ctx.alloc_pinned(8)
+    host_cols = [h_trace[c * n:(c + 1) * n] for c in range(ncols)]
 
     d_src = ctx.alloc(ncols * n)    # resident copy of the trace
-    d_work = ctx.alloc(ncols * n)   # interpolated in place
-    d_eval = ctx.alloc(ncols * N)
-    layers = [ctx.alloc(8 << lg) for lg in range(log_out + 1)]  # layers[lg]: 2^lg hashes
+    d_work = ctx.alloc(ncols * n)   # consumed by each proof
     ctx.h2d_async(d_src.ptr, h_addr, ncols * n * 4)
     ctx.sync()
     work_ptrs = [d_work.view(c * n) for c in range(ncols)]
-    eval_ptrs = [d_eval.view(c * N) for c in range(ncols)]
+    kw = dict(pow_bits=args.pow_bits, log_blowup=args.log_blowup, log_last_layer=0, n_queries=args.n_queries, cap=1 << 26)
 
-    EV_START, EV_IN, EV_IFFT, EV_LDE, EV_LEAF, EV_TREE = 0, 1, 2, 3, 4, 5
+    EV_A, EV_B = 0, 1
+    phases = {}
 
-    def step(e2e):
-        ctx.event_record(EV_START)
+    def step(e2e, collect):
+        ctx.event_record(EV_A)
         if e2e:
-            ctx.h2d_async(d_work.ptr, h_addr, ncols * n * 4)
+            words = ctx.pcs_prove_host([host_cols], **kw)
         else:
-            ctx.d2d(d_work.ptr, d_src.ptr, ncols * n * 4)
-        ctx.event_record(EV_IN)
-        ctx.ifft_cols(work_ptrs, log_n)
-        ctx.event_record(EV_IFFT)
-        ctx.lde_cols(work_ptrs, log_n, eval_ptrs, log_out)
-        ctx.event_record(EV_LDE)
-        ctx.merkle_layer(log_out, 0, eval_ptrs, layers[log_out].ptr, m31_out=True)
-        ctx.event_record(EV_LEAF)
-        for lg in range(log_out - 1, -1, -1):
-            ctx.merkle_layer(lg, layers[lg + 1].ptr, [], layers[lg].ptr, m31_out=True)
-        ctx.d2h_async(h_root_addr, layers[0].ptr, 32)
-        ctx.event_record(EV_TREE)
+            ctx.d2d(d_work.ptr, d_src.ptr, ncols * n * 4)   # the trace "arrives" in device memory
+            if collect:
+                words, ph = ctx.pcs_prove_device([work_ptrs], [log_n] * ncols, phases=True, **kw)
+                for k, v in ph.items():
+                    phases[k] = phases.get(k, 0.0) + v
+            else:
+                words = ctx.pcs_prove_device([work_ptrs], [log_n] * ncols, **kw)
+        ctx.event_record(EV_B)
+        return words, ctx.event_elapsed_ms(EV_A, EV_B)
 
     def barrier():
         ctx.sync()
@@ -208,35 +217,30 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
         ctx.sync()
 
-    phases = {"input_copy": 0.0, "ifft": 0.0, "lde": 0.0, "merkle_leaves": 0.0, "merkle_upper": 0.0}
-
     def timed(e2e, collect):
+        words = None
         for _ in range(args.warmup):
-            step(e2e)
+            words, _ = step(e2e, False)
         barrier()
-        t0 = time.perf_counter()
         total_ms = 0.0
         for _ in range(args.steps):
-            step(e2e)
-            # events of this step are read before the next step re-records them
-            total_ms += ctx.event_elapsed_ms(EV_START, EV_TREE)
-            if collect:
-                for name, a, b in [("input_copy", EV_START, EV_IN), ("ifft", EV_IN, EV_IFFT), ("lde", EV_IFFT, EV_LDE),
-                                   ("merkle_leaves", EV_LDE, EV_LEAF), ("merkle_upper", EV_LEAF, EV_TREE)]:
-                    phases[name] += ctx.event_elapsed_ms(a, b)
+            words, ms = step(e2e, collect)
+            total_ms += ms
         barrier()
-        wall_ms = (time.perf_counter() - t0) * 1e3
-        return total_ms, wall_ms
+        return total_ms, words
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    dev_ms, dev_wall = timed(False, True)
-    root_resident = h_root.copy()
+    dev_ms, words_dev = timed(False, True)
     clocks = sampler.stop() if rank == 0 else None
-    e2e_ms, e2e_wall = timed(True, False)
-    root_e2e = h_root.copy()
-    assert (root_resident == root_e2e).all(), "resident and end-to-end legs disagree on the Merkle root"
+    # per-kernel timeline of one more (untimed) step
+    ctx.d2d(d_work.ptr, d_src.ptr, ncols * n * 4)
+    ctx.profile_begin()
+    ctx.pcs_prove_device([work_ptrs], [log_n] * ncols, **kw)
+    kernels = ctx.profile_end()
+    e2e_ms, words_e2e = timed(True, False)
+    assert len(words_dev) == len(words_e2e) and (words_dev == words_e2e).all(), "resident and end-to-end legs disagree"
 
     if dist is not None:
         import torch
@@ -252,41 +256,44 @@ def run_ours(args, rank, world, local_rank):
 
     if rank == 0:
         per = {k: v / args.steps for k, v in phases.items()}
-        # dominant kernel: the leaf-layer Blake2s kernel (one launch per step). Algorithmic bytes:
-        # 4 * ncols * rows read + 32 * rows written.
         peak, peak_kind = measured_hbm_peak()
-        leaf_bytes = 4.0 * ncols * N + 32.0 * N
-        lde_bytes = (4.0 * n + 4.0 * N) * ncols
-        ifft_bytes = 8.0 * n * ncols
-        dom = max([("merkle_leaves", leaf_bytes), ("lde", lde_bytes), ("ifft", ifft_bytes)], key=lambda kv: per[kv[0]])
-        achieved = dom[1] / (per[dom[0]] * 1e-3) / 1e9
-        roofline = {"bound": "hbm", "kernel": {"merkle_leaves": "merkle_layer_kernel", "lde": "fft_pass_kernel<false>",
-                                                 "ifft": "fft_pass_kernel<true>"}[dom[0]],
-                    "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
-                    "peak_kind": peak_kind,
-                    "per_phase_ms": per,
-                    "per_phase_gbs": {"ifft": ifft_bytes / (per["ifft"] * 1e-3) / 1e9, "lde": lde_bytes / (per["lde"] * 1e-3) / 1e9,
-                                      "merkle_leaves": leaf_bytes / (per["merkle_leaves"] * 1e-3) / 1e9}}
+        ab = algorithmic_bytes(ncols, n, N)
+        # dominant operator: the LDE (two launches: the strided radix-32 pass, then the contiguous one)
+        fwd = [(k, v) for k, v in kernels.items() if "forward" in k]
+        lde_ms = sum(v[0] for _, v in fwd)
+        achieved = ab["extend"] / (lde_ms * 1e-3) / 1e9 if lde_ms else None
+        kern = {k: {"ms": round(v[0], 4), "launches": v[1]} for k, v in sorted(kernels.items(), key=lambda kv: -kv[1][0])}
+        roofline = {"bound": "hbm", "kernel": "+".join(k for k, _ in fwd) + " (the launches of one LDE)",
+                    "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak if achieved else None,
+                    "traffic": None, "peak_kind": peak_kind,
+                    "note": "integer-issue bound, not HBM bound: about 10.5 thread instructions per butterfly (see DESIGN.md)",
+                    "per_phase_ms": per, "kernels_one_step": kern,
+                    "per_operator_gbs": {
+                        "interpolate": ab["interpolate"] / (sum(v[0] for k, v in kernels.items() if "inverse" in k) * 1e-3) / 1e9,
+                        "extend": achieved,
+                        "merkle_leaves": ab["merkle_leaves"] / (max((v[0] / v[1] for k, v in kernels.items() if "columns" in k), default=1e9) * 1e-3) / 1e9,
+                        "quot_numerators": ab["quot_numerators"] / (kernels.get("quot_numerators_kernel", (1e9, 1))[0] * 1e-3) / 1e9}}
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             sample_cols = min(ncols, args.ref_cols)
             v, dt, threads, _ = cpu_leg(args, sample_cols)
             cpu = {"value": v, "unit": "cells/s", "cores": threads, "kind": "port",
-                   "sample": f"{sample_cols} of {ncols} columns at full height 2^{log_n} ({dt:.1f} s of CPU work): interpolate + LDE + Merkle tree"}
-        launches = n_fft_passes(log_n) * 2 + (log_out + 1)
+                   "sample": f"{sample_cols} of {ncols} columns at full height 2^{log_n} ({dt:.1f} s of CPU work): the same commit + prove flow"}
+        launches = sum(v[1] for v in kernels.values())
+        import hashlib
+
         line = {
             "metric": "committed_m31_cells_per_s", "value": value, "unit": "cells/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "u32 (M31)", "data": "synthetic", "config": workload_config(args),
-            "e2e": {"value": e2e_value, "unit": "cells/s", "h2d_bytes_per_step": ncols * n * 4, "d2h_bytes_per_step": 32,
+            "e2e": {"value": e2e_value, "unit": "cells/s", "h2d_bytes_per_step": ncols * n * 4, "d2h_bytes_per_step": int(len(words_dev)) * 4,
                     "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": launches * args.steps,
             "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
-            "root": "".join(f"{int(w):08x}" for w in root_resident),
+            "proof_words": int(len(words_dev)), "proof_sha256": hashlib.sha256(words_dev.tobytes()).hexdigest(),
         }
         print(json.dumps(line))
     ctx.free_pinned(h_addr)
-    ctx.free_pinned(h_root_addr)
     ctx.close()
     if dist is not None:
         dist.destroy_process_group()
@@ -301,6 +308,8 @@ def main():
     ap.add_argument("--cols", type=int, default=256)
     ap.add_argument("--log-size", type=int, default=20)
     ap.add_argument("--log-blowup", type=int, default=2)
+    ap.add_argument("--pow-bits", type=int, default=10)
+    ap.add_argument("--n-queries", type=int, default=3)
     ap.add_argument("--ref-cols", type=int, default=32, help="columns in the bounded CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

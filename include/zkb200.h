@@ -59,6 +59,13 @@ int zkb_max_log_size(zkb_ctx* ctx);
 int zkb_event_record(zkb_ctx* ctx, int slot);
 int zkb_event_elapsed_ms(zkb_ctx* ctx, int a, int b, float* h_ms);
 
+/* Per-kernel timeline: between zkb_profile_begin and zkb_profile_end the large kernels (FFT passes,
+ * Merkle layers, quotient kernels, FRI folds) are bracketed by CUDA events. zkb_profile_end
+ * synchronises and writes up to `cap` aggregated records: h_names[i] (a static string), h_ms[i]
+ * (total milliseconds) and h_count[i] (launches); *n receives the number of distinct kernels. */
+int zkb_profile_begin(zkb_ctx* ctx);
+int zkb_profile_end(zkb_ctx* ctx, const char** h_names, float* h_ms, int* h_count, int cap, int* n);
+
 /* ---- device columns (STWO/stwo_cuda/base_field_vec.rs:7-60, bindings.rs:84-103) ------------ */
 int zkb_malloc(zkb_ctx* ctx, size_t bytes, void** dptr);
 int zkb_free(zkb_ctx* ctx, void* dptr);

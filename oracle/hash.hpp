@@ -145,8 +145,9 @@ inline std::vector<Hash> commit_on_layer(uint32_t log_size, const std::vector<Ha
                                          const std::vector<const M31*>& columns, bool m31) {
     size_t n = (size_t)1 << log_size;
     std::vector<Hash> out(n);
-    std::vector<M31> row(columns.size());
+#pragma omp parallel for schedule(static) if (n >= 1024)
     for (size_t i = 0; i < n; i++) {
+        std::vector<M31> row(columns.size());
         for (size_t c = 0; c < columns.size(); c++) row[c] = columns[c][i];
         out[i] = prev ? hash_node(&(*prev)[2 * i], &(*prev)[2 * i + 1], row.data(), row.size(), m31)
                       : hash_node(nullptr, nullptr, row.data(), row.size(), m31);

@@ -25,6 +25,7 @@ inline SecureColumn fold_line(const SecureColumn& eval, const LineDomain& domain
     size_t n = eval.size();
     assert(n >= 2);
     SecureColumn out(n / 2);
+#pragma omp parallel for schedule(static) if (n >= 4096)
     for (size_t i = 0; i < n / 2; i++) {
         M31 x = domain.at(bit_reverse_index(i << 1, domain.log_size()));
         QM31 f0 = eval[2 * i], f1 = eval[2 * i + 1];
@@ -37,6 +38,7 @@ inline SecureColumn fold_line(const SecureColumn& eval, const LineDomain& domain
 inline void fold_circle_into_line(SecureColumn& dst, const SecureColumn& src, const CircleDomain& domain, QM31 alpha) {
     assert(src.size() >> 1 == dst.size());
     QM31 alpha_sq = alpha * alpha;
+#pragma omp parallel for schedule(static) if (dst.size() >= 4096)
     for (size_t i = 0; i < dst.size(); i++) {
         CirclePoint<M31> p = domain.at(bit_reverse_index(i << 1, domain.log_size()));
         QM31 f0 = src[2 * i], f1 = src[2 * i + 1];
@@ -95,6 +97,7 @@ inline void accumulate_numerators(const std::vector<const M31*>& columns, size_t
     auto coeffs = column_line_coeffs(batches);
     for (size_t bi = 0; bi < batches.size(); bi++) {
         SecureColumn acc(size);
+#pragma omp parallel for schedule(static) if (size >= 4096)
         for (size_t row = 0; row < size; row++) {
             QM31 numerator = QM31::zero();
             for (size_t j = 0; j < batches[bi].cols_vals_randpows.size(); j++) {
@@ -116,6 +119,7 @@ inline SecureColumn compute_quotients_and_combine(const std::vector<AccumulatedN
     SecureColumn q(n);
     std::vector<CirclePoint<QM31>> pts;
     for (auto& a : accs) pts.push_back(a.sample_point);
+#pragma omp parallel for schedule(static) if (n >= 4096)
     for (size_t row = 0; row < n; row++) {
         CirclePoint<M31> dp = domain.at(bit_reverse_index(row, lifting_log_size));
         auto inv = denominator_inverses(pts, dp);

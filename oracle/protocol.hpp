@@ -330,12 +330,16 @@ struct CommitmentSchemeProver {
     // extend by the blow-up factor, build the Merkle tree, mix the root.
     void commit_evals(const std::vector<std::vector<M31>>& columns, Channel& ch) {
         CommitmentTree t;
-        for (auto& col : columns) {
+        t.evals.resize(columns.size());
+        t.coeffs.resize(columns.size());
+#pragma omp parallel for schedule(dynamic)
+        for (size_t k = 0; k < columns.size(); k++) {
+            const auto& col = columns[k];
             uint32_t log = ilog2(col.size());
             std::vector<M31> c(col);
             interpolate(c, CanonicCoset(log).circle_domain(), twiddles);
-            t.evals.push_back(evaluate(c, CanonicCoset(log + config.fri.log_blowup_factor).circle_domain(), twiddles));
-            t.coeffs.push_back(std::move(c));
+            t.evals[k] = evaluate(c, CanonicCoset(log + config.fri.log_blowup_factor).circle_domain(), twiddles);
+            t.coeffs[k] = std::move(c);
         }
         std::vector<ColumnRef> refs;
         for (auto& e : t.evals) refs.push_back({e.data(), e.size()});
@@ -422,15 +426,15 @@ struct CommitmentSchemeProver {
         for (size_t t = 0; t < trees.size(); t++) {
             samples[t].resize(trees[t].coeffs.size());
             proof.sampled_values.emplace_back();
+#pragma omp parallel for schedule(dynamic)
             for (size_t c = 0; c < trees[t].coeffs.size(); c++) {
                 uint32_t poly_log = ilog2(trees[t].evals[c].size());
+                for (auto& p : sampled_points[t][c])
+                    samples[t][c].push_back({p, eval_at_point(trees[t].coeffs[c], p.repeated_double(lifting_log - poly_log))});
+            }
+            for (size_t c = 0; c < trees[t].coeffs.size(); c++) {
                 std::vector<QM31> vals;
-                for (auto& p : sampled_points[t][c]) {
-                    QM31 v = eval_at_point(trees[t].coeffs[c], p.repeated_double(lifting_log - poly_log));
-                    samples[t][c].push_back({p, v});
-                    vals.push_back(v);
-                    flat_values.push_back(v);
-                }
+                for (auto& smp : samples[t][c]) { vals.push_back(smp.value); flat_values.push_back(smp.value); }
                 proof.sampled_values[t].push_back(vals);
             }
         }

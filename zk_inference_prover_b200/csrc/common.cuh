@@ -27,6 +27,11 @@ struct zkb_ctx {
     unsigned int* ticket = nullptr;
     uint32_t* h_small = nullptr;  // pinned, for small results read back by the host
     cudaEvent_t events[64] = {nullptr};
+    // Optional per-kernel timeline (zkb_profile_*): pairs of events around selected launches.
+    bool prof_on = false;
+    struct ProfRec { const char* name; cudaEvent_t a, b; };
+    ProfRec* prof = nullptr;
+    int prof_n = 0, prof_cap = 0;
     char err[512] = {0};
 };
 
@@ -69,6 +74,22 @@ struct DeviceGuard {
 // Copies `n` host-resident device pointers into the staging ring and returns their device
 // address through *out. Ordered on the context's stream.
 int stage_ptrs(zkb_ctx* ctx, const void* const* h_ptrs, int n, void*** out);
+
+// Brackets a kernel launch with events when the timeline is on (see zkb_profile_begin).
+struct ProfScope {
+    zkb_ctx* ctx;
+    int slot = -1;
+    ProfScope(zkb_ctx* c, const char* name) : ctx(c) {
+        if (!c->prof_on || c->prof_n >= c->prof_cap) return;
+        slot = c->prof_n++;
+        c->prof[slot].name = name;
+        if (!c->prof[slot].a) { cudaEventCreate(&c->prof[slot].a); cudaEventCreate(&c->prof[slot].b); }
+        cudaEventRecord(c->prof[slot].a, c->stream);
+    }
+    ~ProfScope() {
+        if (slot >= 0) cudaEventRecord(ctx->prof[slot].b, ctx->stream);
+    }
+};
 
 // Reserves `words` of scratch (whole buffer is shared; one user per enqueued op sequence).
 inline uint32_t* scratch_ptr(zkb_ctx* ctx) { return ctx->scratch; }

@@ -139,6 +139,11 @@ int zkb_destroy(zkb_ctx* ctx) {
     if (ctx->h_small) cudaFreeHost(ctx->h_small);
     for (int i = 0; i < 64; i++)
         if (ctx->events[i]) cudaEventDestroy(ctx->events[i]);
+    if (ctx->prof) {
+        for (int i = 0; i < ctx->prof_cap; i++)
+            if (ctx->prof[i].a) { cudaEventDestroy(ctx->prof[i].a); cudaEventDestroy(ctx->prof[i].b); }
+        delete[] ctx->prof;
+    }
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return ZKB_OK;
@@ -174,6 +179,42 @@ int zkb_event_elapsed_ms(zkb_ctx* ctx, int a, int b, float* h_ms) {
     DeviceGuard g(ctx);
     ZKB_CUDA(ctx, cudaEventSynchronize(ctx->events[b]));
     ZKB_CUDA(ctx, cudaEventElapsedTime(h_ms, ctx->events[a], ctx->events[b]));
+    return ZKB_OK;
+}
+
+int zkb_profile_begin(zkb_ctx* ctx) {
+    if (!ctx) return ZKB_EINVAL;
+    DeviceGuard g(ctx);
+    if (!ctx->prof) {
+        ctx->prof_cap = 8192;
+        ctx->prof = new (std::nothrow) zkb_ctx::ProfRec[ctx->prof_cap]();
+        if (!ctx->prof) { ctx->prof_cap = 0; return set_error(ctx, ZKB_ENOMEM, "zkb_profile_begin: out of host memory"); }
+    }
+    ctx->prof_n = 0;
+    ctx->prof_on = true;
+    return ZKB_OK;
+}
+
+int zkb_profile_end(zkb_ctx* ctx, const char** h_names, float* h_ms, int* h_count, int cap, int* n) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, h_names && h_ms && h_count && n && cap > 0);
+    DeviceGuard g(ctx);
+    ctx->prof_on = false;
+    ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    int k = 0;
+    for (int i = 0; i < ctx->prof_n; i++) {
+        float ms = 0.f;
+        ZKB_CUDA(ctx, cudaEventElapsedTime(&ms, ctx->prof[i].a, ctx->prof[i].b));
+        int j = 0;
+        while (j < k && h_names[j] != ctx->prof[i].name) j++;
+        if (j == k) {
+            if (k == cap) continue;
+            h_names[k] = ctx->prof[i].name; h_ms[k] = 0.f; h_count[k] = 0; k++;
+        }
+        h_ms[j] += ms;
+        h_count[j] += 1;
+    }
+    *n = k;
     return ZKB_OK;
 }
 

@@ -185,6 +185,7 @@ static int launch_pass(zkb_ctx* ctx, uint32_t* const* d_dst, const uint32_t* con
     unsigned gy = ncols < 32768 ? ncols : 32768;
     size_t smem = (size_t)4 << tile_log;
     dim3 grid(tiles, gy);
+    ProfScope prof(ctx, INVERSE ? "fft_pass_kernel<inverse>" : "fft_pass_kernel<forward>");
     fft_pass_kernel<INVERSE><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log, ps,
                                                                    INVERSE ? ctx->itw : ctx->tw, scale);
     ZKB_LAUNCH_CHECK(ctx);
@@ -214,6 +215,8 @@ static int launch_step(zkb_ctx* ctx, uint32_t* const* d_dst, const uint32_t* con
                                 : ((size_t)ncols << (log_n - 13));
     size_t max_ctas = (size_t)n_sms * ctas_per_sm[which][INVERSE];
     unsigned grid = (unsigned)(items < max_ctas ? items : max_ctas);
+    ProfScope prof(ctx, st.kind == 1 ? (INVERSE ? "fft_r32_contig_kernel<inverse>" : "fft_r32_contig_kernel<forward>")
+                                     : (INVERSE ? "fft_r32_strided_kernel<inverse>" : "fft_r32_strided_kernel<forward>"));
     if (st.kind == 1)
         fft_r32_contig_kernel<INVERSE><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log,
                                                                               st.r32, tower, scale);

@@ -102,6 +102,7 @@ int zkb_fold_line(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* const in
     qm31 alpha{{h_alpha[0], h_alpha[1], h_alpha[2], h_alpha[3]}};
     DeviceGuard g(ctx);
     size_t half = (size_t)1 << (log_n - 1);
+    ProfScope prof(ctx, "fold_line_kernel");
     fold_line_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n, alpha, ctx->itw);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
@@ -135,6 +136,7 @@ int zkb_fold_circle_into_line(zkb_ctx* ctx, uint32_t* const dst[4], const uint32
         return ZKB_OK;
     }
     size_t half = (size_t)1 << (log_n_src - 1);
+    ProfScope prof(ctx, "fold_circle_kernel");
     fold_circle_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n_src, alpha, alpha_sq, ctx->itw);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;

@@ -95,6 +95,7 @@ int zkb_eval_at_point_cols(zkb_ctx* ctx, const uint32_t* const* coeffs, int ncol
         {
             unsigned threads = first_chunk >= 9 ? 256 : 32;
             dim3 grid((unsigned)partials_per_col, nc);
+            ProfScope prof(ctx, "eval_fold_kernel<base>");
             eval_fold_kernel<true><<<grid, threads, 0, ctx->stream>>>((const uint32_t* const*)d_cols, nullptr, log_cur,
                                                                       first_chunk, level, f, bufA);
             ZKB_LAUNCH_CHECK(ctx);

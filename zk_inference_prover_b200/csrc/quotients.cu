@@ -206,6 +206,7 @@ int zkb_quot_numerators(zkb_ctx* ctx, const uint32_t* const* cols, int ncols, in
     }
     size_t n = (size_t)1 << log_n;
     size_t threads_total = n / NUM_ROWS_PER_THREAD;
+    ProfScope prof(ctx, "quot_numerators_kernel");
     quot_numerators_kernel<<<(unsigned)((threads_total + 255) / 256), 256, 0, ctx->stream>>>(
         (const uint32_t* const*)d_cols, d_idx, reinterpret_cast<const uint4*>(d_c), k, b_sum, n, o);
     ZKB_LAUNCH_CHECK(ctx);
@@ -250,6 +251,7 @@ int zkb_quot_combine(zkb_ctx* ctx, int n_acc, const uint32_t* const* acc_cols, c
             cpoint p1 = hl ? host_point_q(((1u << (29 - hl)) + (1u << (31 - hl))) & 0x7fffffffu) : p0;
             quot_combine_small_kernel<<<1, 32, 0, ctx->stream>>>(args, lifting_log, o, p0.x, p0.y, p1.x, p1.y);
         } else {
+            ProfScope prof(ctx, "quot_combine_kernel");
             quot_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(args, lifting_log, o, ctx->tw);
         }
         ZKB_LAUNCH_CHECK(ctx);
@@ -286,6 +288,7 @@ int zkb_lift_accumulate(zkb_ctx* ctx, uint32_t* const dst[4], int log_dst, const
     }
     DeviceGuard g(ctx);
     size_t n = (size_t)1 << log_dst;
+    ProfScope prof(ctx, "lift_accumulate_kernel");
     lift_accumulate_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(a, log_dst, b, log_dst - log_src);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
