@@ -166,6 +166,25 @@ int zkb_gkr_sum(zkb_ctx* ctx, int kind, const uint32_t* num, const uint32_t* den
 int zkb_mle_fix_qm31(zkb_ctx* ctx, const uint32_t* in, size_t n, const uint32_t h_r[4], uint32_t* out);
 int zkb_mle_fix_m31(zkb_ctx* ctx, const uint32_t* in, size_t n, const uint32_t h_r[4], uint32_t* out);
 
+/* Round sums with no allocation anywhere. This entry point has no counterpart in the reference. It
+ * is for callers that cannot allocate device memory when they need the sums: a prover running with
+ * its allocator locked after it has carved the card into a fixed arena, a thread that must not
+ * trigger the device-wide synchronisation an allocation or free can cause, a host that forbids
+ * allocation after start-up. It takes no context (creating one allocates); the per-block partial
+ * sums and the ticket live in a 64.25 KiB array built into the library, held by every GPU that
+ * loads it until the process exits. Same arithmetic and argument meaning as zkb_gkr_sum, except:
+ * `device` and `stream` (a cudaStream_t, may be NULL for the default stream) say where to run,
+ * d_out receives the 8 result words ON THE DEVICE (stream-ordered; nothing is copied or
+ * synchronised), and n is limited to 2^28 entries (larger layers are refused with ZKB_EINVAL).
+ * The first call on a device looks up the array's device address; make that call before any
+ * stream capture. All calls share the one array, so calls that overlap on the same GPU (two
+ * streams, two threads) race; issue them on one stream or order them yourself. It calls neither
+ * cudaMalloc nor cudaFree nor any allocating routine. zkb_gkr_sum_noalloc_error() returns the text
+ * of the last failure. */
+int zkb_gkr_sum_noalloc(int device, void* stream, int kind, const uint32_t* num, const uint32_t* den, size_t n,
+                        const uint32_t* eq_evals, const uint32_t h_lambda[4], uint32_t* d_out);
+const char* zkb_gkr_sum_noalloc_error(void);
+
 /* ---- GrindOps::grind (STWO/core/proof_of_work.rs:3-7; simd/grind.rs:18-93) ------------------
  * Smallest nonce (hi << 32) | lo, lo < 2^20, whose Blake2s(prefixed_digest || nonce) has at least
  * pow_bits trailing zero bits in its first word. h_prefixed_digest: 8 words. */

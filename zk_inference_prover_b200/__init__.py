@@ -10,6 +10,7 @@ from .capi import (  # noqa: F401
     ZkbError,
     lib_path,
     load_library,
+    gkr_sum_noalloc,
     GKR_GRAND_PRODUCT,
     GKR_LOGUP_GENERIC,
     GKR_LOGUP_MULTIPLICITIES,

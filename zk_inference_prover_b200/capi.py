@@ -18,7 +18,7 @@ EXPORTED_SYMBOLS = [
     "zkb_ifft_cols", "zkb_lde_cols", "zkb_eval_at_point_cols", "zkb_bit_reverse_m31", "zkb_bit_reverse_qm31",
     "zkb_merkle_layer", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine",
     "zkb_accumulate", "zkb_lift_accumulate", "zkb_secure_powers", "zkb_gkr_eq_evals", "zkb_gkr_next_layer",
-    "zkb_gkr_sum", "zkb_mle_fix_qm31", "zkb_mle_fix_m31", "zkb_grind",
+    "zkb_gkr_sum", "zkb_mle_fix_qm31", "zkb_mle_fix_m31", "zkb_grind", "zkb_gkr_sum_noalloc", "zkb_gkr_sum_noalloc_error",
 ]
 # Every symbol include/zkb200_prover.h declares.
 PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_gkr_prove_device"]
@@ -56,14 +56,25 @@ def load_library():
         _lib = C.CDLL(_LIB)
         _lib.zkb_last_error.restype = C.c_char_p
         _lib.zkb_last_error.argtypes = [C.c_void_p]
+        _lib.zkb_gkr_sum_noalloc_error.restype = C.c_char_p
         for name in EXPORTED_SYMBOLS + PROVER_SYMBOLS:
-            if name != "zkb_last_error":
+            if name not in ("zkb_last_error", "zkb_gkr_sum_noalloc_error"):
                 getattr(_lib, name).restype = C.c_int
     return _lib
 
 
 def _u32(a):
     return np.ascontiguousarray(a, dtype=np.uint32)
+
+
+def gkr_sum_noalloc(device, stream, kind, num_ptr, den_ptr, n, eq_ptr, lam, out_ptr):
+    """zkb_gkr_sum_noalloc: needs no Context; the 8 result words land in device memory at out_ptr."""
+    lib = load_library()
+    l = _u32(lam)
+    rc = lib.zkb_gkr_sum_noalloc(C.c_int(device), C.c_void_p(stream or None), C.c_int(kind), C.c_void_p(num_ptr or None), C.c_void_p(den_ptr),
+                                 C.c_size_t(n), C.c_void_p(eq_ptr), l.ctypes.data_as(C.c_void_p), C.c_void_p(out_ptr))
+    if rc != 0:
+        raise ZkbError(rc, lib.zkb_gkr_sum_noalloc_error().decode())
 
 
 class DeviceBuffer:

@@ -250,3 +250,78 @@ int zkb_mle_fix_m31(zkb_ctx* ctx, const uint32_t* in, size_t n, const uint32_t h
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Round sums without any allocation.
+//
+// Some callers may not allocate device memory at the point where they need a sum-check round sum:
+// a prover that has handed the whole card to a fixed arena and runs with the allocator locked, a
+// host thread inside a region where cudaMalloc/cudaFree would synchronise the device and stall other
+// streams, or a plugin loaded into a process that forbids allocation after start-up. zkb_gkr_sum
+// needs a context, and creating a context allocates (twiddles, scratch, pinned buffers).
+// zkb_gkr_sum_noalloc needs none: its only scratch, the per-block partial sums and the ticket that
+// elects the last block, lives in the fixed array below, which every GPU that loads this library
+// holds from load until exit.
+namespace zk {
+
+constexpr int NOALLOC_MAX_BLOCKS = 2048;
+constexpr size_t NOALLOC_MAX_ENTRIES = (size_t)1 << 28;  // largest layer (n) accepted
+// 8 words per block of partial sums, then 64 words whose first is the ticket: 64.25 KiB.
+static __device__ __align__(256) uint32_t g_noalloc_scratch[8 * NOALLOC_MAX_BLOCKS + 64];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static uint32_t* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};  // device address of the array, per device
+static char g_noalloc_err[256] = "";
+
+}  // namespace zk
+
+extern "C" {
+
+const char* zkb_gkr_sum_noalloc_error(void) { return zk::g_noalloc_err; }
+
+int zkb_gkr_sum_noalloc(int device, void* stream, int kind, const uint32_t* num, const uint32_t* den, size_t n,
+                        const uint32_t* eq_evals, const uint32_t h_lambda[4], uint32_t* d_out) {
+    auto fail = [](int code, const char* msg) { snprintf(zk::g_noalloc_err, sizeof(zk::g_noalloc_err), "zkb_gkr_sum_noalloc: %s", msg); return code; };
+    if (device < 0 || device >= NOALLOC_MAX_DEVICES) return fail(ZKB_EINVAL, "device index out of range");
+    if (kind < 0 || kind > 3 || !den || !eq_evals || !h_lambda || !d_out) return fail(ZKB_EINVAL, "null pointer or unknown layer kind");
+    if ((kind == ZKB_GKR_LOGUP_GENERIC || kind == ZKB_GKR_LOGUP_MULTIPLICITIES) && !num) return fail(ZKB_EINVAL, "this layer kind needs numerators");
+    if (n < 4 || (n & (n - 1))) return fail(ZKB_EINVAL, "n must be a power of two, at least 4");
+    if (n > NOALLOC_MAX_ENTRIES) return fail(ZKB_EINVAL, "layer larger than the built-in scratch allows (2^28 entries at most)");
+    int prev = -1;
+    if (cudaGetDevice(&prev) != cudaSuccess) return fail(ZKB_ECUDA, "cudaGetDevice failed");
+    if (prev != device && cudaSetDevice(device) != cudaSuccess) return fail(ZKB_ECUDA, "cudaSetDevice failed");
+    int rc = ZKB_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    // Set-up, once per device and with that device current: the array's name is only a host-side
+    // handle, the kernel needs its address on this device.
+    if (!zk::g_noalloc_ptr[device]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, zk::g_noalloc_scratch);
+        if (e != cudaSuccess || !p) rc = fail(ZKB_ECUDA, cudaGetErrorString(e));
+        else zk::g_noalloc_ptr[device] = (uint32_t*)p;
+    }
+    if (rc == ZKB_OK) {
+        uint32_t* partials = zk::g_noalloc_ptr[device];
+        unsigned int* ticket = (unsigned int*)(partials + 8 * NOALLOC_MAX_BLOCKS);
+        size_t n_terms = n / 4;
+        unsigned blocks = (unsigned)((n_terms + 255) / 256);
+        if (blocks > (unsigned)NOALLOC_MAX_BLOCKS) blocks = NOALLOC_MAX_BLOCKS;
+        qm31 lam = q4(h_lambda);
+        // the ticket must start at zero whatever an earlier call left behind
+        cudaError_t e = cudaMemsetAsync(ticket, 0, sizeof(unsigned int), st);
+        if (e == cudaSuccess) {
+            switch (kind) {
+                case ZKB_GKR_GRAND_PRODUCT: gkr_sum_kernel<0><<<blocks, 256, 0, st>>>(num, den, n_terms, eq_evals, lam, partials, ticket, d_out); break;
+                case ZKB_GKR_LOGUP_GENERIC: gkr_sum_kernel<1><<<blocks, 256, 0, st>>>(num, den, n_terms, eq_evals, lam, partials, ticket, d_out); break;
+                case ZKB_GKR_LOGUP_MULTIPLICITIES: gkr_sum_kernel<2><<<blocks, 256, 0, st>>>(num, den, n_terms, eq_evals, lam, partials, ticket, d_out); break;
+                default: gkr_sum_kernel<3><<<blocks, 256, 0, st>>>(num, den, n_terms, eq_evals, lam, partials, ticket, d_out); break;
+            }
+            e = cudaGetLastError();
+        }
+        if (e != cudaSuccess) rc = fail(ZKB_ECUDA, cudaGetErrorString(e));
+    }
+    if (prev >= 0 && prev != device) cudaSetDevice(prev);
+    return rc;
+}
+
+}  // extern "C"
