@@ -85,6 +85,12 @@ int zkb_gather_multi(zkb_ctx* ctx, const uint32_t* const* cols, int ncols, const
 /* Column<Blake2sHash>::batch_at (STWO/prover/backend/mod.rs:68-72): h_out[8*i..] = hashes[h_idx[i]]. */
 int zkb_gather_hashes(zkb_ctx* ctx, const uint32_t* hashes, const uint32_t* h_idx, int nidx, uint32_t* h_out);
 
+/* One round trip for many small reads: h_out[i] = *h_addrs[i], each a device address of a word.
+ * It serves the decommitment phase, where the reference issues one batch_at / batch_at_multi per tree
+ * layer (STWO/prover/vcs/prover.rs:160-207): the positions of ALL layers are known before any value is
+ * read, so a caller can collect every address first and read them together. */
+int zkb_gather_words(zkb_ctx* ctx, const uint32_t* const* h_addrs, size_t n, uint32_t* h_out);
+
 /* ---- twiddles ------------------------------------------------------------------------------
  * Copies out the tower of Coset::half_odds(log_size) in the reference's layout
  * (slow_precompute_twiddles, STWO/prover/backend/cpu/circle.rs:274-291): 2^log_size words each,
@@ -115,6 +121,12 @@ int zkb_bit_reverse_qm31(zkb_ctx* ctx, uint32_t* col, int log_n); /* 4-word elem
  * words are reduced mod 2^31-1. out: 2^log_size hashes. */
 int zkb_merkle_layer(zkb_ctx* ctx, int log_size, const uint32_t* prev, const uint32_t* const* cols, int ncols,
                      int m31_out, uint32_t* out);
+
+/* The upper part of a tree in one launch, for trees whose small layers take no columns (every FRI
+ * layer tree; a trace tree without tiny columns): given the layer of 2^top_log hashes
+ * (top_log <= 10), writes lower_layers[k] (2^k hashes) for k = top_log-1 .. 0, each node being
+ * commit_on_layer(k, prev = layer k+1, no columns). Equivalent to top_log calls of zkb_merkle_layer. */
+int zkb_merkle_top(zkb_ctx* ctx, int top_log, const uint32_t* top_layer, uint32_t* const* lower_layers, int m31_out);
 
 /* ---- FriOps (STWO/prover/fri.rs:37-85; cpu/fri.rs:67-123) ---------------------------------- */
 /* fold_circle_into_line: src on the canonic circle domain of log_n_src; dst (2^(log_n_src-1)

@@ -318,3 +318,15 @@ def test_invalid_arguments_return_status(ctx, zkb):
     b = ctx.upload(np.arange(8))
     ctx.bit_reverse_m31(b.ptr, 3)
     assert list(b.download()) == [0, 4, 2, 6, 1, 5, 3, 7]
+
+
+@pytest.mark.parametrize("top_log", [1, 3, 6, 10])
+def test_merkle_top_equals_layer_by_layer(ctx, oracle, top_log):
+    top = m31_column(1800 + top_log, (1 << top_log) * 8).reshape(-1, 8)
+    tb = ctx.upload(top)
+    lowers = [ctx.alloc(8 << k) for k in range(top_log)]
+    ctx.merkle_top(top_log, tb.ptr, [b.ptr for b in lowers])
+    prev = top
+    for k in range(top_log - 1, -1, -1):
+        prev = oracle.commit_on_layer(k, prev, [], m31=True)
+        assert (lowers[k].download(shape=(-1, 8)) == prev).all()

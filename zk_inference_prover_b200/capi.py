@@ -14,9 +14,9 @@ EXPORTED_SYMBOLS = [
     "zkb_init", "zkb_destroy", "zkb_last_error", "zkb_sync", "zkb_get_stream", "zkb_max_log_size",
     "zkb_event_record", "zkb_event_elapsed_ms", "zkb_profile_begin", "zkb_profile_end",
     "zkb_malloc", "zkb_free", "zkb_memset_zero", "zkb_h2d", "zkb_d2h", "zkb_h2d_async", "zkb_d2h_async", "zkb_d2d",
-    "zkb_host_alloc_pinned", "zkb_host_free_pinned", "zkb_gather_multi", "zkb_gather_hashes", "zkb_twiddles_d2h",
+    "zkb_host_alloc_pinned", "zkb_host_free_pinned", "zkb_gather_multi", "zkb_gather_hashes", "zkb_gather_words", "zkb_twiddles_d2h",
     "zkb_ifft_cols", "zkb_lde_cols", "zkb_eval_at_point_cols", "zkb_bit_reverse_m31", "zkb_bit_reverse_qm31",
-    "zkb_merkle_layer", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine",
+    "zkb_merkle_layer", "zkb_merkle_top", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine",
     "zkb_accumulate", "zkb_lift_accumulate", "zkb_secure_powers", "zkb_gkr_eq_evals", "zkb_gkr_next_layer",
     "zkb_gkr_sum", "zkb_mle_fix_qm31", "zkb_mle_fix_m31", "zkb_grind", "zkb_gkr_sum_noalloc", "zkb_gkr_sum_noalloc_error",
 ]
@@ -219,6 +219,12 @@ class Context:
                                                out.ctypes.data_as(C.c_void_p)))
         return out
 
+    def gather_words(self, addrs):
+        a = np.ascontiguousarray(addrs, dtype=np.uint64)
+        out = np.empty(len(a), np.uint32)
+        self._check(self.lib.zkb_gather_words(self.h, a.ctypes.data_as(C.c_void_p), C.c_size_t(len(a)), out.ctypes.data_as(C.c_void_p)))
+        return out
+
     # ---- twiddles
     def twiddles(self, log_size):
         tw = np.empty(1 << log_size, np.uint32)
@@ -251,6 +257,9 @@ class Context:
     def merkle_layer(self, log_size, prev_ptr, col_ptrs, out_ptr, m31_out=True):
         self._check(self.lib.zkb_merkle_layer(self.h, C.c_int(log_size), C.c_void_p(prev_ptr or None), _ptr_array(col_ptrs),
                                               C.c_int(len(col_ptrs)), C.c_int(int(m31_out)), C.c_void_p(out_ptr)))
+
+    def merkle_top(self, top_log, top_ptr, lower_ptrs, m31_out=True):
+        self._check(self.lib.zkb_merkle_top(self.h, C.c_int(top_log), C.c_void_p(top_ptr), _ptr_array(lower_ptrs), C.c_int(int(m31_out))))
 
     # ---- FriOps
     def fold_line(self, out4, in4, log_n, alpha):

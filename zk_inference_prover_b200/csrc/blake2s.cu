@@ -124,6 +124,29 @@ __global__ void __launch_bounds__(256) merkle_layer_kernel(int log_size, const u
     store_hash(out, i, h, m31_out != 0);
 }
 
+// The top of a tree in one launch: layers 2^(top_log-1) ... 2^0 from layer 2^top_log, nodes only
+// (no columns are injected). One CTA; a barrier separates the levels.
+constexpr int MERKLE_TOP_MAX_LOG = 10;
+struct MerkleTopArgs { uint32_t* layer[MERKLE_TOP_MAX_LOG + 1]; };  // layer[k]: 2^k hashes
+
+__global__ void __launch_bounds__(512) merkle_top_kernel(MerkleTopArgs a, int top_log, int m31_out) {
+    for (int lg = top_log - 1; lg >= 0; lg--) {
+        const uint32_t* __restrict__ prev = a.layer[lg + 1];
+        for (uint32_t i = threadIdx.x; i < (1u << lg); i += blockDim.x) {
+            uint32_t h[8], m[16];
+            blake2s_init(h);
+            const uint4* p = reinterpret_cast<const uint4*>(prev + 16 * (size_t)i);
+            uint4 x0 = p[0], x1 = p[1], x2 = p[2], x3 = p[3];
+            m[0] = x0.x; m[1] = x0.y; m[2] = x0.z; m[3] = x0.w; m[4] = x1.x; m[5] = x1.y; m[6] = x1.z; m[7] = x1.w;
+            m[8] = x2.x; m[9] = x2.y; m[10] = x2.z; m[11] = x2.w; m[12] = x3.x; m[13] = x3.y; m[14] = x3.z; m[15] = x3.w;
+            blake2s_compress(h, m, 64u, true);
+            store_hash(a.layer[lg], i, h, m31_out != 0);
+        }
+        __threadfence_block();
+        __syncthreads();
+    }
+}
+
 // Grind: thread `lo` tests nonce (hi << 32) | lo; the minimum passing lo is kept.
 __global__ void grind_kernel(uint32_t d0, uint32_t d1, uint32_t d2, uint32_t d3, uint32_t d4, uint32_t d5, uint32_t d6,
                              uint32_t d7, uint32_t hi, int pow_bits, int m31_out, unsigned int* __restrict__ best) {
@@ -160,6 +183,24 @@ int zkb_merkle_layer(zkb_ctx* ctx, int log_size, const uint32_t* prev, const uin
     ProfScope prof(ctx, ncols ? "merkle_layer_kernel(columns)" : "merkle_layer_kernel(nodes only)");
     merkle_layer_kernel<<<blocks, threads, 0, ctx->stream>>>(log_size, prev, (const uint32_t* const*)d_cols, ncols, m31_out,
                                                              out);
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
+}
+
+int zkb_merkle_top(zkb_ctx* ctx, int top_log, const uint32_t* top_layer, uint32_t* const* lower_layers, int m31_out) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, top_log >= 0 && top_log <= MERKLE_TOP_MAX_LOG && top_layer != nullptr && ((uintptr_t)top_layer & 15) == 0);
+    if (top_log == 0) return ZKB_OK;
+    ZKB_CHECK_ARG(ctx, lower_layers != nullptr);
+    MerkleTopArgs a;
+    a.layer[top_log] = const_cast<uint32_t*>(top_layer);
+    for (int k = 0; k < top_log; k++) {
+        ZKB_CHECK_ARG(ctx, lower_layers[k] != nullptr && ((uintptr_t)lower_layers[k] & 15) == 0);
+        a.layer[k] = lower_layers[k];
+    }
+    DeviceGuard g(ctx);
+    ProfScope prof(ctx, "merkle_top_kernel");
+    merkle_top_kernel<<<1, top_log >= 10 ? 512 : (top_log >= 6 ? 1 << (top_log - 1) : 32), 0, ctx->stream>>>(a, top_log, m31_out);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }

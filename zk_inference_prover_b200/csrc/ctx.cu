@@ -75,6 +75,11 @@ __global__ void gather_hashes_kernel(const uint4* __restrict__ hashes, const uin
     out[t] = hashes[2 * (size_t)idx[t >> 1] + (t & 1)];
 }
 
+__global__ void gather_words_kernel(const uint32_t* const* __restrict__ addrs, size_t n, uint32_t* __restrict__ out) {
+    size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n) out[t] = *addrs[t];
+}
+
 }  // namespace zk
 
 using namespace zk;
@@ -330,6 +335,26 @@ int zkb_gather_multi(zkb_ctx* ctx, const uint32_t* const* cols, int ncols, const
     ZKB_LAUNCH_CHECK(ctx);
     ZKB_CUDA(ctx, cudaMemcpyAsync(h_out, d_out, total * 4, cudaMemcpyDeviceToHost, ctx->stream));
     ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return ZKB_OK;
+}
+
+int zkb_gather_words(zkb_ctx* ctx, const uint32_t* const* h_addrs, size_t n, uint32_t* h_out) {
+    if (!ctx) return ZKB_EINVAL;
+    if (n == 0) return ZKB_OK;
+    ZKB_CHECK_ARG(ctx, h_addrs != nullptr && h_out != nullptr);
+    DeviceGuard g(ctx);
+    // addresses (2 words each) and results share the scratch buffer; large requests go in slices
+    const size_t slice = ctx->scratch_words / 3;
+    for (size_t off = 0; off < n; off += slice) {
+        size_t m = n - off < slice ? n - off : slice;
+        const uint32_t** d_addrs = reinterpret_cast<const uint32_t**>(ctx->scratch);
+        uint32_t* d_out = ctx->scratch + 2 * slice;
+        ZKB_CUDA(ctx, cudaMemcpyAsync(d_addrs, h_addrs + off, m * sizeof(void*), cudaMemcpyHostToDevice, ctx->stream));
+        gather_words_kernel<<<(unsigned)((m + 255) / 256), 256, 0, ctx->stream>>>(d_addrs, m, d_out);
+        ZKB_LAUNCH_CHECK(ctx);
+        ZKB_CUDA(ctx, cudaMemcpyAsync(h_out + off, d_out, m * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
     return ZKB_OK;
 }
 

@@ -36,8 +36,32 @@ static std::vector<size_t> fold_queries(const std::vector<size_t>& q, uint32_t n
     return out;
 }
 
+// Every address a decommitment will read is known once the query positions are: collect them all,
+// read them in one device round trip, then assemble the proof parts from the results.
+struct GatherPlan {
+    std::vector<const uint32_t*> addrs;
+    std::vector<uint32_t> words;
+    size_t add(const uint32_t* p) { addrs.push_back(p); return addrs.size() - 1; }
+    size_t add_hash(const uint32_t* p) { size_t s = addrs.size(); for (int k = 0; k < 8; k++) addrs.push_back(p + k); return s; }
+    void execute(const Device& d) {
+        words.resize(addrs.size());
+        d.check(zkb_gather_words(d.ctx(), addrs.data(), addrs.size(), words.data()));
+    }
+    Hash hash_at(size_t slot) const { Hash h; for (int k = 0; k < 8; k++) h[k] = words[slot + k]; return h; }
+};
+
 // ------------------------------------------------------------------ MerkleProver (STWO/prover/vcs/prover.rs:17-217)
 struct MerkleDecommitment { std::vector<Hash> hash_witness; std::vector<uint32_t> column_witness; };
+struct PendingMerkle {  // slots of a planned decommitment
+    std::vector<size_t> hash_slots, queried_slots, witness_slots;
+    std::pair<std::vector<uint32_t>, MerkleDecommitment> finish(const GatherPlan& plan) const {
+        std::pair<std::vector<uint32_t>, MerkleDecommitment> r;
+        for (auto s : hash_slots) r.second.hash_witness.push_back(plan.hash_at(s));
+        for (auto s : queried_slots) r.first.push_back(plan.words[s]);
+        for (auto s : witness_slots) r.second.column_witness.push_back(plan.words[s]);
+        return r;
+    }
+};
 
 struct MerkleProver {
     std::vector<HashColumn> layers;  // layers[log_size]; layers[0] holds the root
@@ -57,17 +81,28 @@ struct MerkleProver {
             std::vector<const BaseColumn*> layer_cols;
             while (pos < sorted.size() && sorted[pos]->log_size() == log) layer_cols.push_back(sorted[pos++]);
             mp.layers[log] = B200Backend::commit_on_layer(d, log, log == max_log ? nullptr : &mp.layers[log + 1], layer_cols);
+            if (log > 0 && log <= 10 && pos == sorted.size()) {
+                // no columns left below: the rest of the tree is nodes only, built in one launch
+                std::vector<uint32_t*> lower;
+                for (uint32_t k = 0; k < log; k++) { mp.layers[k] = HashColumn(d, (size_t)8 << k); lower.push_back(mp.layers[k].ptr()); }
+                d.check(zkb_merkle_top(d.ctx(), (int)log, mp.layers[log].ptr(), lower.data(), 1));
+                break;
+            }
         }
         return mp;
     }
-    Hash root(const Device& d) const { return B200Backend::batch_at(d, layers[0], {0})[0]; }
+    Hash root(const Device& d) const {
+        if (!have_root) { root_cache = B200Backend::batch_at(d, layers[0], {0})[0]; have_root = true; }
+        return root_cache;
+    }
+    mutable Hash root_cache{};
+    mutable bool have_root = false;
 
-    // :84-217 — index planning on the host, one hash gather and at most two value gathers per layer.
-    std::pair<std::vector<uint32_t>, MerkleDecommitment> decommit(const Device& d,
-                                                                  const std::map<uint32_t, std::vector<size_t>>& queries_per_log_size,
-                                                                  const std::vector<const BaseColumn*>& columns) const {
-        std::vector<uint32_t> queried_values;
-        MerkleDecommitment dec;
+    // :84-217 — the reference plans the indices of all layers on the host first (its phase 1) and then
+    // reads layer by layer; here the reads of all layers join one GatherPlan.
+    PendingMerkle plan_decommit(GatherPlan& plan, const std::map<uint32_t, std::vector<size_t>>& queries_per_log_size,
+                                const std::vector<const BaseColumn*>& columns) const {
+        PendingMerkle pm;
         std::vector<const BaseColumn*> sorted(columns);
         std::stable_sort(sorted.begin(), sorted.end(), [](const BaseColumn* a, const BaseColumn* b) { return a->len() > b->len(); });
         size_t pos = 0;
@@ -90,19 +125,14 @@ struct MerkleProver {
                 }
                 (col_queries.count(node) ? queried_nodes : witness_nodes).push_back(node);
             }
-            if (has_prev && !witness_children.empty()) {
-                auto hs = B200Backend::batch_at(d, layers[log + 1], witness_children);
-                dec.hash_witness.insert(dec.hash_witness.end(), hs.begin(), hs.end());
-            }
-            if (!layer_cols.empty()) {
-                auto qv = B200Backend::batch_at_multi(d, layer_cols, queried_nodes);
-                queried_values.insert(queried_values.end(), qv.begin(), qv.end());
-                auto wv = B200Backend::batch_at_multi(d, layer_cols, witness_nodes);
-                dec.column_witness.insert(dec.column_witness.end(), wv.begin(), wv.end());
-            }
+            for (size_t child : witness_children) pm.hash_slots.push_back(plan.add_hash(layers[log + 1].ptr() + 8 * child));
+            for (size_t node : queried_nodes)
+                for (auto c : layer_cols) pm.queried_slots.push_back(plan.add(c->ptr() + node));
+            for (size_t node : witness_nodes)
+                for (auto c : layer_cols) pm.witness_slots.push_back(plan.add(c->ptr() + node));
             last = merged_nodes;
         }
-        return {queried_values, dec};
+        return pm;
     }
 };
 
@@ -158,10 +188,18 @@ static std::vector<qm31> secure_at_batch(const Device& d, const SecureColumnByCo
     return out;
 }
 
-// fri.rs:392-436
-static void decommitment_positions_and_witness(const Device& d, const SecureColumnByCoords& column, const std::vector<size_t>& queries,
-                                               uint32_t fold_step, std::vector<size_t>& positions, std::vector<qm31>& witness) {
+struct PendingFriLayer {
+    std::vector<size_t> eval_slots;  // 4 per decommitment position
     std::vector<bool> is_witness;
+    PendingMerkle merkle;
+    Hash commitment;
+};
+
+// fri.rs:392-436 — positions first, then one gather for all of them (here: joined to the plan).
+static PendingFriLayer plan_fri_layer(GatherPlan& plan, const Device& d, const SecureColumnByCoords& column, const MerkleProver& tree,
+                                      const std::vector<size_t>& queries, uint32_t fold_step) {
+    PendingFriLayer pl;
+    std::vector<size_t> positions;
     size_t i = 0;
     while (i < queries.size()) {
         size_t j = i;
@@ -169,14 +207,17 @@ static void decommitment_positions_and_witness(const Device& d, const SecureColu
         size_t start = (queries[i] >> fold_step) << fold_step, qi = i;
         for (size_t p = start; p < start + ((size_t)1 << fold_step); p++) {
             positions.push_back(p);
-            if (qi < j && queries[qi] == p) { qi++; is_witness.push_back(false); }
-            else is_witness.push_back(true);
+            if (qi < j && queries[qi] == p) { qi++; pl.is_witness.push_back(false); }
+            else pl.is_witness.push_back(true);
         }
         i = j;
     }
-    auto evals = secure_at_batch(d, column, positions);
-    for (size_t k = 0; k < positions.size(); k++)
-        if (is_witness[k]) witness.push_back(evals[k]);
+    for (size_t p : positions)
+        for (int k = 0; k < 4; k++) pl.eval_slots.push_back(plan.add(column.columns[k].ptr() + p));
+    std::map<uint32_t, std::vector<size_t>> q{{column.columns[0].log_size(), positions}};
+    pl.merkle = tree.plan_decommit(plan, q, column.refs());
+    pl.commitment = tree.root(d);
+    return pl;
 }
 
 struct FriProver {
@@ -233,32 +274,41 @@ struct FriProver {
         return fp;
     }
 
-    static FriLayerProof decommit_layer(const Device& d, const SecureColumnByCoords& col, const MerkleProver& tree,
-                                        const std::vector<size_t>& queries, uint32_t fold_step) {
-        FriLayerProof lp;
-        std::vector<size_t> positions;
-        decommitment_positions_and_witness(d, col, queries, fold_step, positions, lp.fri_witness);
-        std::map<uint32_t, std::vector<size_t>> q{{col.columns[0].log_size(), positions}};
-        lp.decommitment = tree.decommit(d, q, col.refs()).second;
-        lp.commitment = tree.root(d);
-        return lp;
-    }
-
-    // fri.rs:223-281
-    FriProof decommit(const Device& d, Channel& ch, std::vector<size_t>& query_positions) const {
+    // fri.rs:223-281, planned: `finish` is called after the plan has been executed.
+    std::vector<PendingFriLayer> plan_decommit(GatherPlan& plan, const Device& d, Channel& ch, std::vector<size_t>& query_positions) const {
         uint32_t first_log = first_column->columns[0].log_size();
         query_positions = sorted_dedup(draw_queries(ch, first_log, config.n_queries));
-        FriProof proof;
-        proof.first_layer = decommit_layer(d, *first_column, first_tree, query_positions, 1);
+        std::vector<PendingFriLayer> pending;
+        pending.push_back(plan_fri_layer(plan, d, *first_column, first_tree, query_positions, 1));
         std::vector<size_t> q = fold_queries(query_positions, 1);
         for (auto& in : inner) {
-            proof.inner_layers.push_back(decommit_layer(d, in.eval, in.tree, q, in.fold_step));
+            pending.push_back(plan_fri_layer(plan, d, in.eval, in.tree, q, in.fold_step));
             q = fold_queries(q, in.fold_step);
         }
+        return pending;
+    }
+    FriProof finish_decommit(const GatherPlan& plan, const std::vector<PendingFriLayer>& pending) const {
+        FriProof proof;
+        auto layer = [&](const PendingFriLayer& pl) {
+            FriLayerProof lp;
+            for (size_t k = 0; k < pl.is_witness.size(); k++)
+                if (pl.is_witness[k])
+                    lp.fri_witness.push_back({{plan.words[pl.eval_slots[4 * k]], plan.words[pl.eval_slots[4 * k + 1]],
+                                               plan.words[pl.eval_slots[4 * k + 2]], plan.words[pl.eval_slots[4 * k + 3]]}});
+            lp.decommitment = pl.merkle.finish(plan).second;
+            lp.commitment = pl.commitment;
+            return lp;
+        };
+        proof.first_layer = layer(pending[0]);
+        for (size_t k = 1; k < pending.size(); k++) proof.inner_layers.push_back(layer(pending[k]));
         proof.last_layer_poly = last_layer_poly;
         return proof;
     }
 };
+
+}  // namespace b200
+
+namespace b200 {
 
 // ------------------------------------------------------------------ commitment scheme (STWO/prover/pcs/mod.rs)
 struct PcsConfig {
@@ -508,7 +558,9 @@ struct CommitmentSchemeProver {
         ch.mix_u64(proof.proof_of_work);
         mark(6);
         std::vector<size_t> query_positions;
-        proof.fri = fri.decommit(d, ch, query_positions);
+        GatherPlan plan;
+        auto fri_pending = fri.plan_decommit(plan, d, ch, query_positions);
+        std::vector<PendingMerkle> tree_pending;
         for (auto& t : trees) {  // STWO/core/pcs/utils.rs:200-218, then pcs/mod.rs:575-630
             uint32_t tree_max = t.max_log();
             std::vector<size_t> q;
@@ -523,10 +575,15 @@ struct CommitmentSchemeProver {
                 for (auto pos : q) positions.push_back(((pos >> (tree_max - log + 1)) << 1) + (pos & 1));
                 per_log[log] = sorted_dedup(positions);
             }
-            auto r = t.commitment.decommit(d, per_log, refs);
+            tree_pending.push_back(t.commitment.plan_decommit(plan, per_log, refs));
+        }
+        plan.execute(d);
+        proof.fri = fri.finish_decommit(plan, fri_pending);
+        for (size_t k = 0; k < trees.size(); k++) {
+            auto r = tree_pending[k].finish(plan);
             proof.queried_values.push_back(std::move(r.first));
             proof.decommitments.push_back(std::move(r.second));
-            proof.commitments.push_back(t.commitment.root(d));
+            proof.commitments.push_back(trees[k].commitment.root(d));
         }
         mark(7);
         return proof;

@@ -4,8 +4,11 @@
 // The reference folds the coefficient array as a binary tree
 // (nitroo/crates/stwo/src/prover/backend/cpu/circle.rs:82-100, core/poly/utils.rs:11-23):
 // level k joins blocks of 2^k values as lhs + rhs * m_k with m_0 = y, m_1 = x, m_{k+1} = pi(m_k).
-// Field arithmetic is exact, so the tree is evaluated here in chunks: a CTA folds 2^CHUNK values
-// in shared memory, writes one partial, and the partials are folded again with the next factors.
+// Field arithmetic is exact and distributive, so the tree equals sum_i c_i * prod_{k: bit k of i} m_k.
+// The lowest 11 levels are evaluated as that weighted sum: a CTA takes 2048 coefficients, every
+// thread multiplies its 8 coefficients (M31) by weights it keeps in registers (QM31), accumulating
+// unreduced in 64 bits, and the CTA adds the 256 partial sums. What remains per column is a short
+// array of partials, folded level by level in shared memory with the remaining factors.
 #include <vector>
 
 #include "common.cuh"
@@ -16,6 +19,64 @@ constexpr int EVAL_CHUNK_LOG = 11;
 constexpr int EVAL_MAX_LEVELS = 32;
 
 struct EvalFactors { qm31 m[EVAL_MAX_LEVELS]; };
+
+// weights[i] = prod over set bits k of i of m_k, i < 2^EVAL_CHUNK_LOG.
+__global__ void eval_weights_kernel(EvalFactors f, int bits, uint32_t* __restrict__ weights) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (1u << bits)) return;
+    qm31 w = qm31_one();
+    for (int k = 0; k < bits; k++)
+        if ((i >> k) & 1u) w = qm31_mul(w, f.m[k]);
+    reinterpret_cast<uint4*>(weights)[i] = make_uint4(w.c[0], w.c[1], w.c[2], w.c[3]);
+}
+
+__device__ __forceinline__ uint64_t fold64_eval(uint64_t v) { return (v & P) + (v >> 31); }
+
+// out[col][chunk] = sum_{e < 2048} cols[col][2048 chunk + e] * weights[e]
+__global__ void __launch_bounds__(256) eval_dot_kernel(const uint32_t* const* __restrict__ cols, int log_n,
+                                                       const uint32_t* __restrict__ weights, uint32_t* __restrict__ out) {
+    __shared__ uint32_t red[8][4];
+    const int t = threadIdx.x;
+    uint4 w[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) w[u] = reinterpret_cast<const uint4*>(weights)[t + 256 * u];
+    const size_t chunks = (size_t)1 << (log_n - EVAL_CHUNK_LOG);
+    const int col = blockIdx.y;
+    const uint32_t* __restrict__ c = cols[col];
+    for (size_t chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
+        const uint32_t* __restrict__ p = c + (chunk << EVAL_CHUNK_LOG) + t;
+        uint32_t v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) v[u] = p[256 * u];
+        uint64_t a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            a0 += (uint64_t)v[u] * w[u].x; a1 += (uint64_t)v[u] * w[u].y;
+            a2 += (uint64_t)v[u] * w[u].z; a3 += (uint64_t)v[u] * w[u].w;
+            if (u == 3) { a0 = fold64_eval(a0); a1 = fold64_eval(a1); a2 = fold64_eval(a2); a3 = fold64_eval(a3); }
+        }
+        qm31 s{{m31_reduce64(a0), m31_reduce64(a1), m31_reduce64(a2), m31_reduce64(a3)}};
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            qm31 o;
+#pragma unroll
+            for (int k = 0; k < 4; k++) o.c[k] = __shfl_down_sync(0xffffffffu, s.c[k], off);
+            s = qm31_add(s, o);
+        }
+        if ((t & 31) == 0) {
+#pragma unroll
+            for (int k = 0; k < 4; k++) red[t >> 5][k] = s.c[k];
+        }
+        __syncthreads();
+        if (t < 4) {
+            uint32_t acc = 0;
+#pragma unroll
+            for (int wv = 0; wv < 8; wv++) acc = m31_add(acc, red[wv][t]);
+            out[4 * ((size_t)col * chunks + chunk) + t] = acc;
+        }
+        __syncthreads();
+    }
+}
 
 // in: either a table of M31 columns (IS_BASE) or a dense [ncols][2^log_in] array of QM31.
 // out: dense [ncols][2^(log_in - chunk_log)] QM31.
@@ -77,31 +138,43 @@ int zkb_eval_at_point_cols(zkb_ctx* ctx, const uint32_t* const* coeffs, int ncol
         f.m[k] = x;
         x = qm31_double_x(x);
     }
-    // columns are processed in batches whose partials fit the scratch buffer (two ping-pong halves)
+    // Scratch: [weights: 2048 QM31] [ping] [pong]; columns go in batches whose partials fit.
+    const bool use_dot = log_n >= EVAL_CHUNK_LOG;
     int first_chunk = log_n < EVAL_CHUNK_LOG ? log_n : EVAL_CHUNK_LOG;
     size_t partials_per_col = (size_t)1 << (log_n - first_chunk);
-    size_t half_words = ctx->scratch_words / 2;
+    uint32_t* weights = ctx->scratch;
+    const size_t weights_words = (size_t)4 << EVAL_CHUNK_LOG;
+    size_t half_words = (ctx->scratch_words - weights_words) / 2;
     size_t max_cols = half_words / (4 * partials_per_col);
     ZKB_CHECK_ARG(ctx, max_cols >= 1);
     if (max_cols > 32768) max_cols = 32768;
+    if (use_dot) {
+        eval_weights_kernel<<<(1 << EVAL_CHUNK_LOG) / 256, 256, 0, ctx->stream>>>(f, EVAL_CHUNK_LOG, weights);
+        ZKB_LAUNCH_CHECK(ctx);
+    }
     for (int c0 = 0; c0 < ncols; c0 += (int)max_cols) {
         int nc = ncols - c0 < (int)max_cols ? ncols - c0 : (int)max_cols;
         void** d_cols;
         int rc = stage_ptrs(ctx, (const void* const*)(coeffs + c0), nc, &d_cols);
         if (rc) return rc;
-        uint32_t* bufA = ctx->scratch;
-        uint32_t* bufB = ctx->scratch + half_words;
+        uint32_t* bufA = ctx->scratch + weights_words;
+        uint32_t* bufB = bufA + half_words;
         int log_cur = log_n, level = 0;
-        {
+        if (use_dot) {
+            unsigned gx = (unsigned)(partials_per_col < 64 ? partials_per_col : 64);
+            dim3 grid(gx, nc);
+            ProfScope prof(ctx, "eval_dot_kernel");
+            eval_dot_kernel<<<grid, 256, 0, ctx->stream>>>((const uint32_t* const*)d_cols, log_n, weights, bufA);
+            ZKB_LAUNCH_CHECK(ctx);
+        } else {
             unsigned threads = first_chunk >= 9 ? 256 : 32;
             dim3 grid((unsigned)partials_per_col, nc);
-            ProfScope prof(ctx, "eval_fold_kernel<base>");
             eval_fold_kernel<true><<<grid, threads, 0, ctx->stream>>>((const uint32_t* const*)d_cols, nullptr, log_cur,
                                                                       first_chunk, level, f, bufA);
             ZKB_LAUNCH_CHECK(ctx);
-            log_cur -= first_chunk;
-            level += first_chunk;
         }
+        log_cur -= first_chunk;
+        level += first_chunk;
         while (log_cur > 0) {
             int ch = log_cur < EVAL_CHUNK_LOG ? log_cur : EVAL_CHUNK_LOG;
             unsigned threads = ch >= 9 ? 256 : 32;
