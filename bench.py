@@ -299,6 +299,59 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_sharded_commit(args, rank, world, local_rank):
+    """--mode sharded-commit: ONE commitment split over the ranks (columns -> all-to-all -> row subtrees).
+    Strong scaling: the workload is fixed, every rank does 1/world of the LDE and of the leaf hashing."""
+    import torch
+    import torch.distributed as dist
+
+    import zk_inference_prover_b200 as z
+    from zk_inference_prover_b200.sharded import ContextOps, ShardedCommitment
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1 or not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29511")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    log_n, log_out, ncols = args.log_size, args.log_size + args.log_blowup, args.cols
+    n = 1 << log_n
+    ctx = z.Context(device=local_rank, max_log_size=log_out)
+    sc = ShardedCommitment(ContextOps(ctx), dev)
+    c0, c1 = sc.local_columns(ncols)
+    src = torch.from_numpy(np.stack([splitmix_column(SEED0 + c, n) for c in range(c0, c1)]).view(np.int32).copy()).to(dev)
+    times = []
+    root = None
+    for it in range(args.warmup + args.steps):
+        trace = src.clone()
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        root, local, _ = sc.commit(trace, log_n, args.log_blowup)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        if it >= args.warmup:
+            times.append(e0.elapsed_time(e1))
+        del local, trace
+    t = torch.tensor([sum(times)], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms = float(t[0]) / args.steps
+        cells = ncols * n
+        print(json.dumps({
+            "metric": "committed_m31_cells_per_s", "value": cells / (ms * 1e-3), "unit": "cells/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "u32 (M31)", "data": "synthetic",
+            "config": {"workload": f"sharded_commit_{ncols}cols_log{log_n}_blowup{1 << args.log_blowup}", "columns": ncols,
+                       "log_size": log_n, "log_blowup": args.log_blowup, "step": "interpolate + LDE (column-sharded) + all-to-all + Merkle tree (row-sharded)",
+                       "parallelism": f"columns/rows x{world}"},
+            "root": "".join(f"{int(w) & 0xffffffff:08x}" for w in root.cpu().tolist())}))
+    ctx.close()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -312,12 +365,16 @@ def main():
     ap.add_argument("--n-queries", type=int, default=3)
     ap.add_argument("--ref-cols", type=int, default=32, help="columns in the bounded CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--mode", default="proof", choices=["proof", "sharded-commit"],
+                    help="proof: one whole PCS proof per rank (ranks are independent); sharded-commit: one commitment over all ranks")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+    elif args.mode == "sharded-commit":
+        run_sharded_commit(args, rank, world, local_rank)
     else:
         run_ours(args, rank, world, local_rank)
 

@@ -1,0 +1,147 @@
+"""One commitment over G GPUs: column-sharded LDE, one all-to-all, row-sharded Merkle subtrees.
+
+The reference has no multi-device code. The hot path shards naturally:
+
+  1. rank r owns a contiguous block of `ncols / G` trace columns and runs interpolate + LDE on them
+     (columns are independent);
+  2. ONE exchange turns the column-sharded evaluations `[ncols/G][N]` into row-sharded ones
+     `[ncols][N/G]`: rank d receives rows `[d N/G, (d+1) N/G)` of every column. Evaluations are in
+     bit-reversed order, so that row range is a contiguous subtree of the Merkle tree and the sibling
+     pairs (2i, 2i+1) the FRI folds use stay on one rank;
+  3. every rank hashes its leaves and the `log2(N/G)` layers above them (MerkleOps::commit_on_layer,
+     nitroo/crates/stwo/src/prover/vcs/ops.rs:24-29, in the layer order of
+     nitroo/crates/stwo/src/prover/vcs/prover.rs:39-64);
+  4. the G subtree roots (32 bytes each) are all-gathered and every rank hashes the top `log2 G`
+     layers, so all ranks hold the root the single-GPU commitment produces, bit for bit.
+
+`ops` supplies the operators on raw addresses (the zkb200 Context on GPUs; the tests pass a CPU
+stand-in so that the sharding logic runs under `gloo`), `torch.distributed` supplies the exchange.
+No kernel here reads another GPU's memory: the all-to-all lands in local HBM first.
+"""
+import math
+
+import torch
+import torch.distributed as dist
+
+
+def _is_pow2(x):
+    return x > 0 and (x & (x - 1)) == 0
+
+
+class ShardedCommitment:
+    def __init__(self, ops, device, group=None):
+        self.ops = ops
+        self.device = device
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        if not _is_pow2(self.world):
+            raise ValueError("the number of ranks must be a power of two")
+        self.log_g = int(math.log2(self.world))
+
+    # ---- plan
+    def local_columns(self, ncols):
+        """[start, end) of the global column indices this rank owns."""
+        if ncols % self.world:
+            raise ValueError("the column count must be a multiple of the number of ranks")
+        per = ncols // self.world
+        return self.rank * per, (self.rank + 1) * per
+
+    def local_rows(self, log_out):
+        n = (1 << log_out) // self.world
+        return self.rank * n, (self.rank + 1) * n
+
+    # ---- exchange
+    def _all_to_all(self, recv, send):
+        """recv[s] <- send[rank] of rank s, for tensors of shape [G, ...]."""
+        if dist.get_backend(self.group) == "nccl":
+            dist.all_to_all_single(recv.view(-1), send.view(-1), group=self.group)
+            return
+        # gloo has no all-to-all: pairwise exchange, lower rank sends first
+        recv[self.rank].copy_(send[self.rank])
+        for peer in range(self.world):
+            if peer == self.rank:
+                continue
+            if self.rank < peer:
+                dist.send(send[peer].contiguous(), peer, group=self.group)
+                dist.recv(recv[peer], peer, group=self.group)
+            else:
+                dist.recv(recv[peer], peer, group=self.group)
+                dist.send(send[peer].contiguous(), peer, group=self.group)
+
+    # ---- the commitment
+    def commit(self, trace, log_n, log_blowup):
+        """trace: int32 tensor [ncols_local, 2^log_n] (this rank's columns, evaluations in bit-reversed
+        order; consumed). Returns (root words as an int32 tensor of 8, row-sharded evaluations
+        [ncols, N/G], coefficients [ncols_local, 2^log_n])."""
+        ops, G = self.ops, self.world
+        ncl = trace.shape[0]
+        log_out = log_n + log_blowup
+        N = 1 << log_out
+        if log_out - self.log_g < 1:
+            raise ValueError("each rank needs at least two rows")
+        rows = N // G
+        es = trace.element_size()
+        # 1. interpolate + LDE on the local columns
+        ops.ifft_cols([trace[c].data_ptr() for c in range(ncl)], log_n)
+        evals = torch.empty((ncl, N), dtype=trace.dtype, device=self.device)
+        ops.lde_cols([trace[c].data_ptr() for c in range(ncl)], log_n, [evals[c].data_ptr() for c in range(ncl)], log_out)
+        ops.sync()
+        # 2. pack per destination and exchange: send[d] = rows [d rows, (d+1) rows) of my columns
+        send = evals.view(ncl, G, rows).permute(1, 0, 2).contiguous()
+        del evals
+        recv = torch.empty((G, ncl, rows), dtype=trace.dtype, device=self.device)
+        self._all_to_all(recv, send)
+        del send
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        local = recv.view(G * ncl, rows)  # global column order: source rank major
+        # 3. the local subtree
+        log_local = log_out - self.log_g
+        col_ptrs = [local[c].data_ptr() for c in range(G * ncl)]
+        layer = torch.empty((rows, 8), dtype=trace.dtype, device=self.device)
+        ops.merkle_layer(log_local, 0, col_ptrs, layer.data_ptr())
+        for lg in range(log_local - 1, -1, -1):
+            nxt = torch.empty((1 << lg, 8), dtype=trace.dtype, device=self.device)
+            ops.merkle_layer(lg, layer.data_ptr(), [], nxt.data_ptr())
+            layer = nxt
+        ops.sync()
+        # 4. top of the tree from the G subtree roots
+        roots = torch.empty((G, 8), dtype=trace.dtype, device=self.device)
+        dist.all_gather_into_tensor(roots.view(-1), layer.view(-1), group=self.group) if dist.get_backend(self.group) == "nccl" \
+            else self._all_gather(roots, layer)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        top = roots
+        for lg in range(self.log_g - 1, -1, -1):
+            nxt = torch.empty((1 << lg, 8), dtype=trace.dtype, device=self.device)
+            ops.merkle_layer(lg, top.data_ptr(), [], nxt.data_ptr())
+            top = nxt
+        ops.sync()
+        assert es == 4
+        return top.view(-1), local, trace
+
+    def _all_gather(self, out, mine):
+        parts = [torch.empty_like(mine.view(-1)) for _ in range(self.world)]
+        dist.all_gather(parts, mine.view(-1).contiguous(), group=self.group)
+        for s in range(self.world):
+            out[s].copy_(parts[s])
+
+
+class ContextOps:
+    """The zkb200 operators on raw device addresses (the GPU side of `ops`)."""
+
+    def __init__(self, ctx):
+        self.ctx = ctx
+
+    def ifft_cols(self, ptrs, log_n):
+        self.ctx.ifft_cols(ptrs, log_n)
+
+    def lde_cols(self, src, log_n, dst, log_out):
+        self.ctx.lde_cols(src, log_n, dst, log_out)
+
+    def merkle_layer(self, log_size, prev_ptr, col_ptrs, out_ptr):
+        self.ctx.merkle_layer(log_size, prev_ptr, col_ptrs, out_ptr, m31_out=True)
+
+    def sync(self):
+        self.ctx.sync()
