@@ -202,6 +202,32 @@ const char* zkb_gkr_sum_noalloc_error(void);
  * pow_bits trailing zero bits in its first word. h_prefixed_digest: 8 words. */
 int zkb_grind(zkb_ctx* ctx, const uint32_t h_prefixed_digest[8], int pow_bits, int m31_out, uint64_t* h_nonce);
 
+/* ---- The Freivalds attention-witness component ------------------------------------------------
+ * Rows are tiled by a grid over the input channels (prover/src/layout.rs:141-183, descending
+ * groups): groups * chunks + lead = 2^log_rows. */
+typedef struct zkb_grid {
+    uint32_t log_rows, groups, chunks, lead;
+} zkb_grid;
+/* Witness scatter (prover/src/gadgets/freivalds/trace.rs:43-162; device original
+ * zk_witness_gen_freivalds, prover/src/gadgets/freivalds/device.rs:26-38): from int8 activations
+ * qx[tokens][n_in] and weights qw[m][n_in][n_out[m]] (device arrays; qw is a host array of device
+ * pointers) writes the pq committed columns (activation + 128) and the n_mats*pk + 4 preprocessed
+ * columns (weights, then the selectors chunk+1<chunks, chunk==0, j>0, j+1==rows), every column in
+ * committed order (row j at index coset_perm(j), prover/src/common.rs:76-80), and adds the 8-bit
+ * range multiplicities of every committed cell to m_r8[table_len] (device) and the count of cells
+ * outside the table to *off_table (device). grid->groups must equal n_in. */
+int zkb_freivalds_scatter(zkb_ctx* ctx, const int8_t* qx, const int8_t* const* qw, const uint32_t* h_n_out, const zkb_grid* grid,
+                          uint32_t pq, uint32_t pk, uint32_t n_in, uint32_t tokens, uint32_t n_mats, uint32_t* const* base_cols,
+                          uint32_t* const* pre_cols, uint32_t* m_r8, uint32_t table_len, unsigned long long* off_table);
+/* Accumulators (prover/src/gadgets/freivalds/claims.rs:37-109; device original devacc::freivalds,
+ * prover/src/devacc.rs:665-713 over zk_acc_freivalds / zk_acc_scan / zk_acc_stage2 / zk_acc_split):
+ * from the committed columns (pq) and the weight columns (n_mats*pk) and the challenges s, rv,
+ * writes v, then (u_m, acc_m) per matrix, each as 4 coordinate columns in committed order
+ * (out_cols: (1 + 2 n_mats) * 4 device columns), and the claims acc_m[last row] (n_mats x 4 words). */
+int zkb_freivalds_acc(zkb_ctx* ctx, const uint32_t* const* base_cols, const uint32_t* const* pre_cols, const zkb_grid* grid, uint32_t pq,
+                      uint32_t pk, uint32_t n_mats, const uint32_t h_s[4], const uint32_t h_rv[4], uint32_t* const* out_cols,
+                      uint32_t* h_claims);
+
 #ifdef __cplusplus
 }
 #endif

@@ -386,3 +386,42 @@ def gkr_prove(instances, seed, verify=True, cap=1 << 22):
     if n < 0:
         raise RuntimeError(f"zko_gkr_prove failed: {n}")
     return out[:n].copy()
+
+
+# ---------------------------------------------------------------- Freivalds component
+def coset_perm(i, log_n):
+    lib().zko_coset_perm.restype = C.c_uint64
+    return lib().zko_coset_perm(C.c_uint64(i), C.c_uint32(log_n))
+
+
+def freivalds_columns(qx, qws, grid, pq, pk, table_len=256):
+    """qx: int8 [tokens, n_in]; qws: list of int8 [n_in, n_out_m]; grid = (log_rows, groups, chunks, lead).
+    Returns (base [pq, rows], pre [n_mats*pk+4, rows], m_r8 [table_len], off_table)."""
+    qx = np.ascontiguousarray(qx, np.int8)
+    qws = [np.ascontiguousarray(w, np.int8) for w in qws]
+    tokens, n_in = qx.shape
+    n_out = _u32([w.shape[1] for w in qws])
+    log_rows, groups, chunks, lead = grid
+    rows = 1 << log_rows
+    base = [np.zeros(rows, np.uint32) for _ in range(pq)]
+    pre = [np.zeros(rows, np.uint32) for _ in range(len(qws) * pk + 4)]
+    m_r8 = np.zeros(table_len, np.uint32)
+    off = C.c_uint64()
+    lib().zko_freivalds_columns(_p(qx), _pp(qws), _p(n_out), C.c_uint32(len(qws)), C.c_uint32(log_rows), C.c_uint32(groups),
+                                C.c_uint32(chunks), C.c_uint32(lead), C.c_uint32(pq), C.c_uint32(pk), C.c_uint32(n_in),
+                                C.c_uint32(tokens), _pp(base), _pp(pre), _p(m_r8), C.c_uint32(table_len), C.byref(off))
+    return np.stack(base), np.stack(pre), m_r8, off.value
+
+
+def freivalds_acc(base, pre, n_mats, grid, pq, pk, s4, rv4):
+    """Returns (columns [(1+2 n_mats)*4, rows] in committed order, claims [n_mats, 4])."""
+    b = [_u32(c) for c in base]
+    p = [_u32(c) for c in pre[:n_mats * pk]]
+    log_rows, groups, chunks, lead = grid
+    rows = 1 << log_rows
+    out = [np.zeros(rows, np.uint32) for _ in range((1 + 2 * n_mats) * 4)]
+    claims = np.zeros((n_mats, 4), np.uint32)
+    s, r = _u32(s4), _u32(rv4)
+    lib().zko_freivalds_acc(_pp(b), _pp(p), C.c_uint32(n_mats), C.c_uint32(log_rows), C.c_uint32(groups), C.c_uint32(chunks),
+                            C.c_uint32(lead), C.c_uint32(pq), C.c_uint32(pk), _p(s), _p(r), _pp(out), _p(claims))
+    return np.stack(out), claims

@@ -377,3 +377,40 @@ long zko_gkr_prove(int n_inst, const int* kinds, const uint32_t* const* nums, co
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------- Freivalds component
+#include "freivalds.hpp"
+extern "C" {
+
+uint64_t zko_coset_perm(uint64_t i, uint32_t log_n) { return coset_perm(i, log_n); }
+
+// base_out: pq columns, pre_out: n_mats*pk+4 columns, each 2^log_rows words; m_r8: table_len counters.
+void zko_freivalds_columns(const int8_t* qx, const int8_t* const* qw, const uint32_t* n_out, uint32_t n_mats, uint32_t log_rows,
+                           uint32_t groups, uint32_t chunks, uint32_t lead, uint32_t pq, uint32_t pk, uint32_t n_in, uint32_t tokens,
+                           uint32_t* const* base_out, uint32_t* const* pre_out, uint32_t* m_r8, uint32_t table_len, uint64_t* off_table) {
+    std::vector<const int8_t*> w(qw, qw + n_mats);
+    std::vector<uint32_t> no(n_out, n_out + n_mats);
+    FreivaldsColumns fc = freivalds_columns(qx, w, no, Grid{log_rows, groups, chunks, lead}, pq, pk, n_in, tokens, table_len);
+    size_t rows = (size_t)1 << log_rows;
+    for (size_t c = 0; c < fc.base.size(); c++) for (size_t i = 0; i < rows; i++) base_out[c][i] = fc.base[c][i].v;
+    for (size_t c = 0; c < fc.pre.size(); c++) for (size_t i = 0; i < rows; i++) pre_out[c][i] = fc.pre[c][i].v;
+    for (size_t i = 0; i < table_len; i++) m_r8[i] = fc.m_r8[i];
+    *off_table = fc.off_table;
+}
+
+// out: (1 + 2 n_mats) * 4 columns; claims: n_mats * 4 words.
+void zko_freivalds_acc(const uint32_t* const* base, const uint32_t* const* pre, uint32_t n_mats, uint32_t log_rows, uint32_t groups,
+                       uint32_t chunks, uint32_t lead, uint32_t pq, uint32_t pk, const uint32_t* s4, const uint32_t* rv4,
+                       uint32_t* const* out, uint32_t* claims) {
+    size_t rows = (size_t)1 << log_rows;
+    std::vector<std::vector<M31>> b(pq, std::vector<M31>(rows)), p(n_mats * pk, std::vector<M31>(rows));
+    for (uint32_t c = 0; c < pq; c++) for (size_t i = 0; i < rows; i++) b[c][i] = M31(base[c][i]);
+    for (uint32_t c = 0; c < n_mats * pk; c++) for (size_t i = 0; i < rows; i++) p[c][i] = M31(pre[c][i]);
+    std::vector<std::vector<M31>> cols;
+    std::vector<QM31> cl;
+    freivalds_accumulators(b, p, Grid{log_rows, groups, chunks, lead}, pq, pk, n_mats, q_from(s4), q_from(rv4), cols, cl);
+    for (size_t c = 0; c < cols.size(); c++) for (size_t i = 0; i < rows; i++) out[c][i] = cols[c][i].v;
+    for (size_t m = 0; m < cl.size(); m++) q_to(cl[m], claims + 4 * m);
+}
+
+}  // extern "C"

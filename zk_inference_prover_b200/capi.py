@@ -19,10 +19,15 @@ EXPORTED_SYMBOLS = [
     "zkb_merkle_layer", "zkb_merkle_top", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine",
     "zkb_accumulate", "zkb_lift_accumulate", "zkb_secure_powers", "zkb_gkr_eq_evals", "zkb_gkr_next_layer",
     "zkb_gkr_sum", "zkb_mle_fix_qm31", "zkb_mle_fix_m31", "zkb_grind", "zkb_gkr_sum_noalloc", "zkb_gkr_sum_noalloc_error",
+    "zkb_freivalds_scatter", "zkb_freivalds_acc",
 ]
 # Every symbol include/zkb200_prover.h declares.
 PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_gkr_prove_device"]
 PCS_PHASES = ["interpolate", "extend", "merkle", "sample", "quotients", "fri_commit", "grind", "decommit"]
+
+
+class Grid(C.Structure):
+    _fields_ = [("log_rows", C.c_uint32), ("groups", C.c_uint32), ("chunks", C.c_uint32), ("lead", C.c_uint32)]
 
 
 class PcsConfig(C.Structure):
@@ -157,6 +162,13 @@ class Context:
     def upload(self, arr):
         a = _u32(arr)
         return DeviceBuffer(self, a.size).upload(a)
+
+    def upload_bytes(self, arr):
+        """Any contiguous host array, byte for byte, into a fresh device buffer (rounded up to words)."""
+        a = np.ascontiguousarray(arr)
+        buf = DeviceBuffer(self, (a.nbytes + 3) // 4)
+        self._check(self.lib.zkb_h2d(self.h, C.c_void_p(buf.ptr), a.ctypes.data_as(C.c_void_p), C.c_size_t(a.nbytes)))
+        return buf
 
     def sync(self):
         self._check(self.lib.zkb_sync(self.h))
@@ -321,6 +333,24 @@ class Context:
     def mle_fix_m31(self, in_ptr, n, r, out_ptr):
         rr = _u32(r)
         self._check(self.lib.zkb_mle_fix_m31(self.h, C.c_void_p(in_ptr), C.c_size_t(n), rr.ctypes.data_as(C.c_void_p), C.c_void_p(out_ptr)))
+
+    # ---- Freivalds component
+    def freivalds_scatter(self, qx_ptr, qw_ptrs, n_out, grid, pq, pk, n_in, tokens, base_ptrs, pre_ptrs, m_r8_ptr, table_len, off_ptr):
+        g = Grid(*grid)
+        no = _u32(n_out)
+        self._check(self.lib.zkb_freivalds_scatter(self.h, C.c_void_p(qx_ptr), _ptr_array(qw_ptrs), no.ctypes.data_as(C.c_void_p), C.byref(g),
+                                                   C.c_uint32(pq), C.c_uint32(pk), C.c_uint32(n_in), C.c_uint32(tokens), C.c_uint32(len(qw_ptrs)),
+                                                   _ptr_array(base_ptrs), _ptr_array(pre_ptrs), C.c_void_p(m_r8_ptr), C.c_uint32(table_len),
+                                                   C.c_void_p(off_ptr)))
+
+    def freivalds_acc(self, base_ptrs, pre_ptrs, grid, pq, pk, n_mats, s4, rv4, out_ptrs):
+        g = Grid(*grid)
+        s, r = _u32(s4), _u32(rv4)
+        claims = np.empty((n_mats, 4), np.uint32)
+        self._check(self.lib.zkb_freivalds_acc(self.h, _ptr_array(base_ptrs), _ptr_array(pre_ptrs), C.byref(g), C.c_uint32(pq), C.c_uint32(pk),
+                                               C.c_uint32(n_mats), s.ctypes.data_as(C.c_void_p), r.ctypes.data_as(C.c_void_p),
+                                               _ptr_array(out_ptrs), claims.ctypes.data_as(C.c_void_p)))
+        return claims
 
     # ---- GrindOps
     def grind(self, prefixed_digest8, pow_bits, m31_out=True):
