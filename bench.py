@@ -92,6 +92,23 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+import contextlib
+
+
+@contextlib.contextmanager
+def stdout_to_stderr():
+    """Routes file descriptor 1 to stderr for the duration (native libraries write to the fd directly)."""
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        yield
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved, 1)
+        os.close(saved)
+
+
 def measured_hbm_peak():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -174,7 +191,9 @@ def run_ours(args, rank, world, local_rank):
         import torch.distributed as dist
 
         torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        with stdout_to_stderr():  # NCCL prints a version banner on stdout; the contract is ONE JSON line
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            dist.barrier()
 
     log_n, log_out, ncols = args.log_size, args.log_size + args.log_blowup, args.cols
     n, N = 1 << log_n, 1 << log_out
@@ -313,7 +332,9 @@ def run_sharded_commit(args, rank, world, local_rank):
     if world > 1 or not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29511")
-        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        with stdout_to_stderr():
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+            dist.barrier()
     log_n, log_out, ncols = args.log_size, args.log_size + args.log_blowup, args.cols
     n = 1 << log_n
     ctx = z.Context(device=local_rank, max_log_size=log_out)
@@ -352,6 +373,100 @@ def run_sharded_commit(args, rank, world, local_rank):
     dist.destroy_process_group()
 
 
+def run_gkr(args, rank):
+    """--mode gkr: the GKR logup microbench: one LogUpMultiplicities instance of 2^gkr_log fractions,
+    M31 numerators, non-zero QM31 denominators, channel seeded with mix_u64(0x5EED0004)."""
+    if rank != 0:
+        return
+    import zk_inference_prover_b200 as z
+    from util import m31_column, qm31_array
+
+    n = 1 << args.gkr_log
+    ctx = z.Context(device=0, max_log_size=10)
+    num = ctx.upload(m31_column(0x5EED0002, n))
+    den = ctx.upload(qm31_array(0x5EED0003, n, nonzero=True))
+    inst = [(z.GKR_LOGUP_MULTIPLICITIES, num.ptr, den.ptr, n)]
+    words = None
+    times = []
+    for it in range(args.warmup + args.steps):
+        ctx.sync()
+        ctx.event_record(0)
+        words = ctx.gkr_prove_device(inst, 0x5EED0004)
+        ctx.event_record(1)
+        if it >= args.warmup:
+            times.append(ctx.event_elapsed_ms(0, 1))
+    ctx.profile_begin()
+    ctx.gkr_prove_device(inst, 0x5EED0004)
+    kernels = ctx.profile_end()
+    import hashlib
+
+    ms = float(np.mean(times))
+    line = {"metric": "gkr_fractions_per_s", "value": n / (ms * 1e-3), "unit": "fractions/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u32 (M31/QM31)", "data": "synthetic",
+            "config": {"workload": f"gkr_logup_multiplicities_2^{args.gkr_log}", "instances": 1},
+            "rounds": sum(range(1, args.gkr_log)), "proof_words": int(len(words)),
+            "proof_sha256": hashlib.sha256(words.tobytes()).hexdigest(),
+            "kernels_one_step": {k: {"ms": round(v[0], 4), "launches": v[1]} for k, v in kernels.items()}}
+    if not args.no_cpu_baseline:
+        import oracle
+
+        small = min(args.gkr_log, 20)
+        m = 1 << small
+        t0 = time.perf_counter()
+        oracle.gkr_prove([(2, m31_column(0x5EED0002, m), qm31_array(0x5EED0003, m, nonzero=True))], 0x5EED0004, verify=False)
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": m / dt, "unit": "fractions/s", "cores": 1, "kind": "port",
+                                "sample": f"one instance of 2^{small} fractions ({dt:.1f} s), scalar"}
+    print(json.dumps(line))
+    ctx.close()
+
+
+def run_freivalds(args, rank):
+    """--mode freivalds: the Freivalds component at the scaled-segment shape: n_in = n_out = 4096,
+    32 tokens, 256 chunks (pk = 16, pq = 1, 2^20 rows), two matrices sharing the input."""
+    if rank != 0:
+        return
+    import zk_inference_prover_b200 as z
+    from util import qm31_array
+
+    n_in, n_out, tokens, chunks, n_mats = 4096, 4096, 32, 256, 2
+    pk, pq = n_out // chunks, -(-tokens // chunks)
+    rows = n_in * chunks
+    log_rows = (rows - 1).bit_length()
+    grid = (log_rows, n_in, chunks, (1 << log_rows) - rows)
+    rng = np.random.default_rng(0x5EED0005)
+    qx = rng.integers(-128, 128, (tokens, n_in), dtype=np.int8)
+    qws = [rng.integers(-128, 128, (n_in, n_out), dtype=np.int8) for _ in range(n_mats)]
+    ctx = z.Context(device=0, max_log_size=10)
+    d_qx, d_qw = ctx.upload_bytes(qx), [ctx.upload_bytes(w) for w in qws]
+    R = 1 << log_rows
+    base = [ctx.alloc(R) for _ in range(pq)]
+    pre = [ctx.alloc(R) for _ in range(n_mats * pk + 4)]
+    out = [ctx.alloc(R) for _ in range((1 + 2 * n_mats) * 4)]
+    m_r8, off = ctx.alloc(256).zero(), ctx.alloc(2).zero()
+    s, rv = qm31_array(1, 1)[0], qm31_array(2, 1)[0]
+    t_sc, t_acc = [], []
+    for it in range(args.warmup + args.steps):
+        ctx.event_record(0)
+        ctx.freivalds_scatter(d_qx.ptr, [w.ptr for w in d_qw], [n_out] * n_mats, grid, pq, pk, n_in, tokens, [b.ptr for b in base],
+                              [p.ptr for p in pre], m_r8.ptr, 256, off.ptr)
+        ctx.event_record(1)
+        ctx.freivalds_acc([b.ptr for b in base], [p.ptr for p in pre[:n_mats * pk]], grid, pq, pk, n_mats, s, rv, [o.ptr for o in out])
+        ctx.event_record(2)
+        if it >= args.warmup:
+            t_sc.append(ctx.event_elapsed_ms(0, 1))
+            t_acc.append(ctx.event_elapsed_ms(1, 2))
+    cells = (pq + n_mats * pk + 4) * R
+    sc, ac = float(np.mean(t_sc)), float(np.mean(t_acc))
+    print(json.dumps({"metric": "freivalds_cells_per_s", "value": cells / ((sc + ac) * 1e-3), "unit": "cells/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": sc + ac, "higher_is_better": True,
+                      "config": {"workload": "freivalds_nin4096_nout4096_tokens32_chunks256_2mats", "rows": R, "pq": pq, "pk": pk},
+                      "scatter_ms": sc, "scatter_gbs": (cells * 4 + n_mats * n_in * n_out) / (sc * 1e-3) / 1e9,
+                      "acc_ms": ac, "acc_gbs": (4.0 * (pq + n_mats * pk) * R + 16.0 * (1 + 2 * n_mats) * R) / (ac * 1e-3) / 1e9}))
+    ctx.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -365,7 +480,8 @@ def main():
     ap.add_argument("--n-queries", type=int, default=3)
     ap.add_argument("--ref-cols", type=int, default=32, help="columns in the bounded CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--mode", default="proof", choices=["proof", "sharded-commit"],
+    ap.add_argument("--gkr-log", type=int, default=24)
+    ap.add_argument("--mode", default="proof", choices=["proof", "sharded-commit", "gkr", "freivalds"],
                     help="proof: one whole PCS proof per rank (ranks are independent); sharded-commit: one commitment over all ranks")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -375,6 +491,10 @@ def main():
         run_reference(args, rank)
     elif args.mode == "sharded-commit":
         run_sharded_commit(args, rank, world, local_rank)
+    elif args.mode == "gkr":
+        run_gkr(args, rank)
+    elif args.mode == "freivalds":
+        run_freivalds(args, rank)
     else:
         run_ours(args, rank, world, local_rank)
 

@@ -174,6 +174,12 @@ int zkb_gkr_next_layer(zkb_ctx* ctx, int kind, const uint32_t* num, const uint32
  * (the caller applies eq_fixed_var_correction and gkr_prover.rs:884-923). n = layer entries. */
 int zkb_gkr_sum(zkb_ctx* ctx, int kind, const uint32_t* num, const uint32_t* den, size_t n, const uint32_t* eq_evals,
                 const uint32_t h_lambda[4], uint32_t h_out[8]);
+/* One sum-check round in one launch: fix_first_variable with challenge r on every column of the layer
+ * (n entries -> n/2, written to num_out / den_out; a LOGUP_MULTIPLICITIES layer becomes LOGUP_GENERIC,
+ * Layer::fix_first_variable, gkr_prover.rs:354-381) AND the sums zkb_gkr_sum would return for the fixed
+ * layer (h_out as there). n >= 8. The outputs must not alias the inputs. */
+int zkb_gkr_fix_and_sum(zkb_ctx* ctx, int kind, const uint32_t* num, const uint32_t* den, size_t n, const uint32_t h_r[4],
+                        const uint32_t* eq_evals, const uint32_t h_lambda[4], uint32_t* num_out, uint32_t* den_out, uint32_t h_out[8]);
 /* fix_first_variable: out[i] = in[i] + r * (in[i + n/2] - in[i]); out may alias in for QM31. */
 int zkb_mle_fix_qm31(zkb_ctx* ctx, const uint32_t* in, size_t n, const uint32_t h_r[4], uint32_t* out);
 int zkb_mle_fix_m31(zkb_ctx* ctx, const uint32_t* in, size_t n, const uint32_t h_r[4], uint32_t* out);

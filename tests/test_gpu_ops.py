@@ -330,3 +330,32 @@ def test_merkle_top_equals_layer_by_layer(ctx, oracle, top_log):
     for k in range(top_log - 1, -1, -1):
         prev = oracle.commit_on_layer(k, prev, [], m31=True)
         assert (lowers[k].download(shape=(-1, 8)) == prev).all()
+
+
+@pytest.mark.parametrize("ny", [12, 13, 17, 22])
+def test_gkr_eq_evals_two_table_path(ctx, oracle, ny):
+    y = qm31_array(1900 + ny, ny)
+    v = qm31_array(1901, 1)[0]
+    out = ctx.alloc(4 << ny)
+    ctx.gkr_eq_evals(y, v, out.ptr)
+    assert (out.download(shape=(-1, 4)) == oracle.gkr_eq_evals(y, v)).all()
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2, 3])
+@pytest.mark.parametrize("log_n", [3, 4, 10, 17])
+def test_gkr_fix_and_sum(ctx, oracle, kind, log_n):
+    n = 1 << log_n
+    num, den = _layer(kind, n, 2000 + kind)
+    eq = qm31_array(2010, max(n // 8, 1))
+    lam, r = qm31_array(2011, 1)[0], qm31_array(2012, 1)[0]
+    nb = ctx.upload(num) if num is not None else None
+    db, eb = ctx.upload(den), ctx.upload(eq)
+    no, do = ctx.alloc(2 * n), ctx.alloc(2 * n)
+    got = ctx.gkr_fix_and_sum(kind, nb.ptr if nb else 0, db.ptr, n, r, eb.ptr, lam, no.ptr, do.ptr)
+    fden = oracle.mle_fix_first(den, r)
+    fnum = oracle.mle_fix_first(num, r) if num is not None else None
+    assert (do.download(shape=(-1, 4)) == fden).all()
+    if fnum is not None:
+        assert (no.download(shape=(-1, 4)) == fnum).all()
+    out_kind = 1 if kind == 2 else kind
+    assert (got == oracle.gkr_round_sums(out_kind, fnum, fden, eq, lam)).all()

@@ -18,7 +18,7 @@ EXPORTED_SYMBOLS = [
     "zkb_ifft_cols", "zkb_lde_cols", "zkb_eval_at_point_cols", "zkb_bit_reverse_m31", "zkb_bit_reverse_qm31",
     "zkb_merkle_layer", "zkb_merkle_top", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine",
     "zkb_accumulate", "zkb_lift_accumulate", "zkb_secure_powers", "zkb_gkr_eq_evals", "zkb_gkr_next_layer",
-    "zkb_gkr_sum", "zkb_mle_fix_qm31", "zkb_mle_fix_m31", "zkb_grind", "zkb_gkr_sum_noalloc", "zkb_gkr_sum_noalloc_error",
+    "zkb_gkr_sum", "zkb_gkr_fix_and_sum", "zkb_mle_fix_qm31", "zkb_mle_fix_m31", "zkb_grind", "zkb_gkr_sum_noalloc", "zkb_gkr_sum_noalloc_error",
     "zkb_freivalds_scatter", "zkb_freivalds_acc",
 ]
 # Every symbol include/zkb200_prover.h declares.
@@ -324,6 +324,14 @@ class Context:
         out = np.empty(8, np.uint32)
         self._check(self.lib.zkb_gkr_sum(self.h, C.c_int(kind), C.c_void_p(num_ptr or None), C.c_void_p(den_ptr), C.c_size_t(n),
                                          C.c_void_p(eq_ptr), l.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p)))
+        return out.reshape(2, 4)
+
+    def gkr_fix_and_sum(self, kind, num_ptr, den_ptr, n, r, eq_ptr, lam, num_out_ptr, den_out_ptr):
+        rr, l = _u32(r), _u32(lam)
+        out = np.empty(8, np.uint32)
+        self._check(self.lib.zkb_gkr_fix_and_sum(self.h, C.c_int(kind), C.c_void_p(num_ptr or None), C.c_void_p(den_ptr), C.c_size_t(n),
+                                                 rr.ctypes.data_as(C.c_void_p), C.c_void_p(eq_ptr), l.ctypes.data_as(C.c_void_p),
+                                                 C.c_void_p(num_out_ptr or None), C.c_void_p(den_out_ptr), out.ctypes.data_as(C.c_void_p)))
         return out.reshape(2, 4)
 
     def mle_fix_qm31(self, in_ptr, n, r, out_ptr):

@@ -15,18 +15,6 @@ __device__ __forceinline__ void stq(uint32_t* __restrict__ p, size_t i, qm31 v) 
     reinterpret_cast<uint4*>(p)[i] = make_uint4(v.c[0], v.c[1], v.c[2], v.c[3]);
 }
 
-// out[x] = v * prod_k (bit_k(x) ? y[ny-1-k] : 1 - y[ny-1-k]) — the doubling recursion of
-// cpu/lookups/gkr.rs:216-231 unrolled per index. One stage per launch keeps it to one
-// multiplication per output: stage s turns 2^s values into 2^(s+1) using y[ny-1-s].
-__global__ void __launch_bounds__(256) eq_evals_stage_kernel(uint32_t* __restrict__ evals, size_t len, qm31 y) {
-    size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (j >= len) return;
-    qm31 e = ldq(evals, j);
-    qm31 tmp = qm31_mul(e, y);
-    stq(evals, j + len, tmp);
-    stq(evals, j, qm31_sub(e, tmp));
-}
-
 template <int KIND>
 __global__ void __launch_bounds__(256) next_layer_kernel(const uint32_t* __restrict__ num, const uint32_t* __restrict__ den,
                                                          size_t half, uint32_t* __restrict__ num_out,
@@ -164,19 +152,6 @@ static inline qm31 q4(const uint32_t* p) { return qm31{{p[0], p[1], p[2], p[3]}}
 
 extern "C" {
 
-int zkb_gkr_eq_evals(zkb_ctx* ctx, const uint32_t* h_y, int ny, const uint32_t h_v[4], uint32_t* out) {
-    if (!ctx) return ZKB_EINVAL;
-    ZKB_CHECK_ARG(ctx, ny >= 0 && ny <= 28 && h_v && out && (ny == 0 || h_y) && ((uintptr_t)out & 15) == 0);
-    DeviceGuard g(ctx);
-    ZKB_CUDA(ctx, cudaMemcpyAsync(out, h_v, 16, cudaMemcpyHostToDevice, ctx->stream));
-    for (int s = 0; s < ny; s++) {
-        size_t len = (size_t)1 << s;
-        eq_evals_stage_kernel<<<(unsigned)((len + 255) / 256), 256, 0, ctx->stream>>>(out, len, q4(h_y + 4 * (ny - 1 - s)));
-        ZKB_LAUNCH_CHECK(ctx);
-    }
-    return ZKB_OK;
-}
-
 int zkb_gkr_next_layer(zkb_ctx* ctx, int kind, const uint32_t* num, const uint32_t* den, size_t n, uint32_t* num_out,
                        uint32_t* den_out) {
     if (!ctx) return ZKB_EINVAL;
@@ -187,6 +162,7 @@ int zkb_gkr_next_layer(zkb_ctx* ctx, int kind, const uint32_t* num, const uint32
     DeviceGuard g(ctx);
     size_t half = n / 2;
     unsigned blocks = (unsigned)((half + 255) / 256);
+    ProfScope prof(ctx, "next_layer_kernel");
     switch (kind) {
         case ZKB_GKR_GRAND_PRODUCT: next_layer_kernel<0><<<blocks, 256, 0, ctx->stream>>>(num, den, half, num_out, den_out); break;
         case ZKB_GKR_LOGUP_GENERIC: next_layer_kernel<1><<<blocks, 256, 0, ctx->stream>>>(num, den, half, num_out, den_out); break;
@@ -215,12 +191,14 @@ int zkb_gkr_sum(zkb_ctx* ctx, int kind, const uint32_t* num, const uint32_t* den
     uint32_t* partials = ctx->scratch;
     uint32_t* result = ctx->scratch + 8 * (size_t)blocks;
     qm31 lam = q4(h_lambda);
+    ProfScope* prof = new ProfScope(ctx, "gkr_sum_kernel");
     switch (kind) {
         case ZKB_GKR_GRAND_PRODUCT: gkr_sum_kernel<0><<<blocks, 256, 0, ctx->stream>>>(num, den, n_terms, eq_evals, lam, partials, ctx->ticket, result); break;
         case ZKB_GKR_LOGUP_GENERIC: gkr_sum_kernel<1><<<blocks, 256, 0, ctx->stream>>>(num, den, n_terms, eq_evals, lam, partials, ctx->ticket, result); break;
         case ZKB_GKR_LOGUP_MULTIPLICITIES: gkr_sum_kernel<2><<<blocks, 256, 0, ctx->stream>>>(num, den, n_terms, eq_evals, lam, partials, ctx->ticket, result); break;
         default: gkr_sum_kernel<3><<<blocks, 256, 0, ctx->stream>>>(num, den, n_terms, eq_evals, lam, partials, ctx->ticket, result); break;
     }
+    delete prof;
     ZKB_LAUNCH_CHECK(ctx);
     ZKB_CUDA(ctx, cudaMemcpyAsync(ctx->h_small, result, 32, cudaMemcpyDeviceToHost, ctx->stream));
     ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -234,6 +212,7 @@ int zkb_mle_fix_qm31(zkb_ctx* ctx, const uint32_t* in, size_t n, const uint32_t 
     ZKB_CHECK_ARG(ctx, ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0);
     DeviceGuard g(ctx);
     size_t half = n / 2;
+    ProfScope prof(ctx, "mle_fix_qm31_kernel");
     mle_fix_qm31_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(in, half, q4(h_r), out);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
@@ -244,6 +223,7 @@ int zkb_mle_fix_m31(zkb_ctx* ctx, const uint32_t* in, size_t n, const uint32_t h
     ZKB_CHECK_ARG(ctx, in && out && h_r && n >= 2 && (n & (n - 1)) == 0 && ((uintptr_t)out & 15) == 0);
     DeviceGuard g(ctx);
     size_t half = n / 2;
+    ProfScope prof(ctx, "mle_fix_m31_kernel");
     mle_fix_m31_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(in, half, q4(h_r), out);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;

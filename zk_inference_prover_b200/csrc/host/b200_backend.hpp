@@ -317,6 +317,20 @@ struct B200Backend {
         d.check(zkb_gkr_sum(d.ctx(), layer.kind, layer.num_ptr(), layer.den.words.ptr(), layer.len(), eq_evals.words.ptr(), lambda.c, out));
         return {qm31{{out[0], out[1], out[2], out[3]}}, qm31{{out[4], out[5], out[6], out[7]}}};
     }
+    // fix_first_variable fused with the next round's sums (one launch per sum-check round).
+    static std::pair<Layer, std::pair<qm31, qm31>> fix_first_variable_and_sum(const Device& d, const Layer& layer, qm31 x0,
+                                                                             const SecureMle& eq_evals, qm31 lambda) {
+        size_t n = layer.len();
+        Layer out;
+        out.kind = layer.kind == ZKB_GKR_LOGUP_MULTIPLICITIES ? ZKB_GKR_LOGUP_GENERIC : layer.kind;
+        out.den = SecureMle(d, n / 2);
+        if (out.kind == ZKB_GKR_LOGUP_GENERIC) out.num = SecureMle(d, n / 2);
+        uint32_t s[8];
+        d.check(zkb_gkr_fix_and_sum(d.ctx(), layer.kind, layer.num_ptr(), layer.den.words.ptr(), n, x0.c, eq_evals.words.ptr(), lambda.c,
+                                    out.kind == ZKB_GKR_LOGUP_GENERIC ? out.num.words.ptr() : nullptr, out.den.words.ptr(), s));
+        std::pair<qm31, qm31> sums{qm31{{s[0], s[1], s[2], s[3]}}, qm31{{s[4], s[5], s[6], s[7]}}};
+        return std::make_pair(std::move(out), sums);
+    }
     // Layer::fix_first_variable (gkr_prover.rs:354-381) over MleOps::fix_first_variable.
     static Layer fix_first_variable(const Device& d, Layer layer, qm31 x0) {
         if (layer.n_variables() == 0) return layer;

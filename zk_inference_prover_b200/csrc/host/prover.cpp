@@ -658,6 +658,8 @@ static UniPoly correct_sum_as_poly_in_first_variable(qm31 f0, qm31 f2, qm31 clai
 struct GkrOracle {  // GkrMultivariatePolyOracle, gkr_prover.rs:473-556
     Layer input_layer;
     qm31 eq_fixed_var_correction;
+    bool have_sums = false;  // the next round's sums, produced together with the last fix
+    std::pair<qm31, qm31> sums;
     size_t n_variables() const { return input_layer.n_variables() - 1; }
 };
 
@@ -723,7 +725,7 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
         std::vector<size_t> sc_inst;
         for (size_t i = 0; i < n_inst; i++)
             if (active[i]) {
-                oracles.push_back({take(i), qm31_one()});
+                oracles.push_back({take(i), qm31_one(), false, {}});
                 sc_claims.push_back(horner(claims[i], lambda));
                 sc_inst.push_back(i);
             }
@@ -739,7 +741,8 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
             for (size_t k = 0; k < oracles.size(); k++) {
                 UniPoly rp;
                 if (n_rem == oracles[k].n_variables()) {
-                    auto sums = B200Backend::round_sums(d, oracles[k].input_layer, eq_evals, lambda);
+                    auto sums = oracles[k].have_sums ? oracles[k].sums : B200Backend::round_sums(d, oracles[k].input_layer, eq_evals, lambda);
+                    oracles[k].have_sums = false;
                     rp = correct_sum_as_poly_in_first_variable(sums.first * oracles[k].eq_fixed_var_correction,
                                                                sums.second * oracles[k].eq_fixed_var_correction, sc_claims[k], ood_point,
                                                                oracles[k].n_variables());
@@ -762,7 +765,14 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
                 if (n_rem == oracles[k].n_variables() && oracles[k].n_variables() != 0) {
                     qm31 z0 = ood_point[ood_point.size() - oracles[k].n_variables()];
                     oracles[k].eq_fixed_var_correction = oracles[k].eq_fixed_var_correction * eq1(challenge, z0);
-                    oracles[k].input_layer = B200Backend::fix_first_variable(d, std::move(oracles[k].input_layer), challenge);
+                    if (oracles[k].input_layer.len() >= 8) {
+                        auto fs = B200Backend::fix_first_variable_and_sum(d, oracles[k].input_layer, challenge, eq_evals, lambda);
+                        oracles[k].input_layer = std::move(fs.first);
+                        oracles[k].sums = fs.second;
+                        oracles[k].have_sums = true;
+                    } else {
+                        oracles[k].input_layer = B200Backend::fix_first_variable(d, std::move(oracles[k].input_layer), challenge);
+                    }
                 }
             round_polys.push_back(combined);
             assignment.push_back(challenge);
