@@ -163,6 +163,23 @@ def run_reference(args, rank):
     print(json.dumps(line))
 
 
+def golden_check(name, words):
+    """Compares a proof with the committed digest of the CPU oracle's proof of the same seeded workload."""
+    import hashlib
+
+    path = os.path.join(ROOT, "tests", "golden", "proof_digests.json")
+    try:
+        want = json.load(open(path)).get(name)
+    except OSError:
+        want = None
+    if want is None:
+        return {"golden": None, "note": "no committed digest for this workload"}
+    ok = int(len(words)) == want["words"] and hashlib.sha256(words.tobytes()).hexdigest() == want["sha256"]
+    if not ok:
+        raise SystemExit(f"proof differs from the committed oracle digest {name}")
+    return {"golden": name, "match": True}
+
+
 def workload_config(args):
     return {"workload": f"pcs_prove_{args.cols}cols_log{args.log_size}_blowup{1 << args.log_blowup}",
             "columns": args.cols, "log_size": args.log_size, "log_blowup": args.log_blowup, "pow_bits": args.pow_bits,
@@ -310,6 +327,8 @@ def run_ours(args, rank, world, local_rank):
             "gpu_launches": launches * args.steps,
             "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
             "proof_words": int(len(words_dev)), "proof_sha256": hashlib.sha256(words_dev.tobytes()).hexdigest(),
+            "parity": golden_check(f"pcs_{ncols}x2e{log_n}_blowup{1 << args.log_blowup}", words_dev)
+            if (args.pow_bits, args.n_queries) == (10, 3) else None,
         }
         print(json.dumps(line))
     ctx.free_pinned(h_addr)
@@ -407,6 +426,8 @@ def run_gkr(args, rank):
             "config": {"workload": f"gkr_logup_multiplicities_2^{args.gkr_log}", "instances": 1},
             "rounds": sum(range(1, args.gkr_log)), "proof_words": int(len(words)),
             "proof_sha256": hashlib.sha256(words.tobytes()).hexdigest(),
+            "parity": golden_check(f"gkr_logup_multiplicities_2e{args.gkr_log}", words),
+            "gpu_launches": sum(v[1] for v in kernels.values()) * args.steps,
             "kernels_one_step": {k: {"ms": round(v[0], 4), "launches": v[1]} for k, v in kernels.items()}}
     if not args.no_cpu_baseline:
         import oracle
