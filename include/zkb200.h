@@ -74,6 +74,12 @@ int zkb_h2d(zkb_ctx* ctx, void* dptr, const void* h_src, size_t bytes); /* retur
 int zkb_d2h(zkb_ctx* ctx, void* h_dst, const void* dptr, size_t bytes); /* returns after the copy */
 int zkb_h2d_async(zkb_ctx* ctx, void* dptr, const void* h_pinned_src, size_t bytes);
 int zkb_d2h_async(zkb_ctx* ctx, void* h_pinned_dst, const void* dptr, size_t bytes);
+/* Host-to-device copy on the context's second (copy) stream, so that it overlaps kernels on the compute stream.
+ * The copy starts after everything enqueued on the compute stream so far (the destination may just have been
+ * allocated there). fence >= 0 records fence slot `fence` (0..63) after the copy; zkb_wait_fence makes the compute
+ * stream wait for that slot. Neither call blocks the host. fence = -1 records nothing. */
+int zkb_h2d_overlapped(zkb_ctx* ctx, void* dptr, const void* h_pinned_src, size_t bytes, int fence);
+int zkb_wait_fence(zkb_ctx* ctx, int fence);
 int zkb_d2d(zkb_ctx* ctx, void* dst, const void* src, size_t bytes);
 int zkb_host_alloc_pinned(zkb_ctx* ctx, size_t bytes, void** h_ptr);
 int zkb_host_free_pinned(zkb_ctx* ctx, void* h_ptr);

@@ -13,7 +13,7 @@ GKR_GRAND_PRODUCT, GKR_LOGUP_GENERIC, GKR_LOGUP_MULTIPLICITIES, GKR_LOGUP_SINGLE
 EXPORTED_SYMBOLS = [
     "zkb_init", "zkb_destroy", "zkb_last_error", "zkb_sync", "zkb_get_stream", "zkb_max_log_size",
     "zkb_event_record", "zkb_event_elapsed_ms", "zkb_profile_begin", "zkb_profile_end",
-    "zkb_malloc", "zkb_free", "zkb_memset_zero", "zkb_h2d", "zkb_d2h", "zkb_h2d_async", "zkb_d2h_async", "zkb_d2d",
+    "zkb_malloc", "zkb_free", "zkb_memset_zero", "zkb_h2d", "zkb_d2h", "zkb_h2d_async", "zkb_d2h_async", "zkb_h2d_overlapped", "zkb_wait_fence", "zkb_d2d",
     "zkb_host_alloc_pinned", "zkb_host_free_pinned", "zkb_gather_multi", "zkb_gather_hashes", "zkb_gather_words", "zkb_twiddles_d2h",
     "zkb_ifft_cols", "zkb_lde_cols", "zkb_eval_at_point_cols", "zkb_bit_reverse_m31", "zkb_bit_reverse_qm31",
     "zkb_merkle_layer", "zkb_merkle_top", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine",

@@ -27,6 +27,10 @@ struct zkb_ctx {
     unsigned int* ticket = nullptr;
     uint32_t* h_small = nullptr;  // pinned, for small results read back by the host
     cudaEvent_t events[64] = {nullptr};
+    // A second stream for host-to-device copies that overlap compute, and the fences between the two.
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t fences[64] = {nullptr};
+    cudaEvent_t copy_gate = nullptr;  // orders the copy stream after allocations made on `stream`
     // Optional per-kernel timeline (zkb_profile_*): pairs of events around selected launches.
     bool prof_on = false;
     struct ProfRec { const char* name; cudaEvent_t a, b; };

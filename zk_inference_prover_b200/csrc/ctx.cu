@@ -149,6 +149,10 @@ int zkb_destroy(zkb_ctx* ctx) {
             if (ctx->prof[i].a) { cudaEventDestroy(ctx->prof[i].a); cudaEventDestroy(ctx->prof[i].b); }
         delete[] ctx->prof;
     }
+    for (int i = 0; i < 64; i++)
+        if (ctx->fences[i]) cudaEventDestroy(ctx->fences[i]);
+    if (ctx->copy_gate) cudaEventDestroy(ctx->copy_gate);
+    if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return ZKB_OK;
@@ -159,6 +163,7 @@ const char* zkb_last_error(zkb_ctx* ctx) { return ctx ? ctx->err : "null context
 int zkb_sync(zkb_ctx* ctx) {
     if (!ctx) return ZKB_EINVAL;
     DeviceGuard g(ctx);
+    if (ctx->copy_stream) ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->copy_stream));
     ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return ZKB_OK;
 }
@@ -279,6 +284,31 @@ int zkb_h2d_async(zkb_ctx* ctx, void* dptr, const void* h_pinned_src, size_t byt
     ZKB_CHECK_ARG(ctx, dptr != nullptr && h_pinned_src != nullptr);
     DeviceGuard g(ctx);
     ZKB_CUDA(ctx, cudaMemcpyAsync(dptr, h_pinned_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return ZKB_OK;
+}
+
+int zkb_h2d_overlapped(zkb_ctx* ctx, void* dptr, const void* h_pinned_src, size_t bytes, int fence) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, fence >= -1 && fence < 64 && (bytes == 0 || (dptr != nullptr && h_pinned_src != nullptr)));
+    DeviceGuard g(ctx);
+    if (!ctx->copy_stream) ZKB_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+    if (!ctx->copy_gate) ZKB_CUDA(ctx, cudaEventCreateWithFlags(&ctx->copy_gate, cudaEventDisableTiming));
+    // the destination may have been allocated (stream-ordered) on the compute stream just now
+    ZKB_CUDA(ctx, cudaEventRecord(ctx->copy_gate, ctx->stream));
+    ZKB_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->copy_gate, 0));
+    if (bytes) ZKB_CUDA(ctx, cudaMemcpyAsync(dptr, h_pinned_src, bytes, cudaMemcpyHostToDevice, ctx->copy_stream));
+    if (fence >= 0) {
+        if (!ctx->fences[fence]) ZKB_CUDA(ctx, cudaEventCreateWithFlags(&ctx->fences[fence], cudaEventDisableTiming));
+        ZKB_CUDA(ctx, cudaEventRecord(ctx->fences[fence], ctx->copy_stream));
+    }
+    return ZKB_OK;
+}
+
+int zkb_wait_fence(zkb_ctx* ctx, int fence) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, fence >= 0 && fence < 64 && ctx->fences[fence] != nullptr);
+    DeviceGuard g(ctx);
+    ZKB_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->fences[fence], 0));
     return ZKB_OK;
 }
 

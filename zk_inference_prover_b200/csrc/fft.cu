@@ -200,7 +200,7 @@ static int launch_step(zkb_ctx* ctx, uint32_t* const* d_dst, const uint32_t* con
     // Persistent launch: as many CTAs as fit on the device at once, each walking over work items.
     static int ctas_per_sm[2][2] = {{0, 0}, {0, 0}};  // [contiguous/strided][forward/inverse]
     static int n_sms = 0;
-    const size_t smem = (size_t)2 * R32_BUF_WORDS * sizeof(uint32_t);
+    const size_t smem = st.kind == 1 ? r32_contig_smem(INVERSE) : r32_strided_smem(INVERSE);
     const int which = st.kind == 1 ? 0 : 1;
     const void* fn = st.kind == 1 ? (const void*)fft_r32_contig_kernel<INVERSE> : (const void*)fft_r32_strided_kernel<INVERSE>;
     const int threads = st.kind == 1 ? 32 * R32_CONTIG_WARPS : 256;

@@ -18,6 +18,8 @@
 // The butterfly multiplies by a pre-doubled twiddle: with t2 = 2t, the 64-bit product t2 * v splits
 // as hi = (t v) >> 31 and lo / 2 = (t v) mod 2^31, whose sum is congruent to t v and below 2p.
 #pragma once
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace zk {
@@ -44,24 +46,39 @@ __device__ __forceinline__ void bf_inv(uint32_t& a, uint32_t& b, uint32_t t2) {
     b = m31_mul_dbl(d, t2);
 }
 
-// Five layers on 32 registers. Layer jj pairs p with p + 2^jj and uses twiddle tbl_jj[p >> (jj+1)],
-// tbl_jj = tower + 2^(L - i - 1) + (A << (4 - jj)) for the global layer i = layer0 + jj.
+// CNT consecutive twiddles, fetched with the widest loads (the tables are aligned to their length).
+template <int CNT>
+__device__ __forceinline__ void load_tw(const uint32_t* __restrict__ p, uint32_t (&t)[16]) {
+    if constexpr (CNT >= 4) {
+#pragma unroll
+        for (int q = 0; q < CNT / 4; q++) {
+            uint4 x = reinterpret_cast<const uint4*>(p)[q];
+            t[4 * q] = x.x; t[4 * q + 1] = x.y; t[4 * q + 2] = x.z; t[4 * q + 3] = x.w;
+        }
+    } else if constexpr (CNT == 2) {
+        uint2 x = *reinterpret_cast<const uint2*>(p);
+        t[0] = x.x; t[1] = x.y;
+    } else {
+        t[0] = p[0];
+    }
+}
+
+// Five layers on 32 registers. Layer jj pairs p with p + 2^jj and uses the 16 >> jj twiddles at
+// tb[jj] (global or shared memory): tb[jj][p >> (jj+1)].
 // Layers outside [act_lo, act_hi) (window-local numbering, this stage starts at `first`) are skipped.
 // When CIRCLE, layer jj = 0 is the circle layer (global layer 0): its twiddles are [y, -y, -x, x]
-// for each pair (x, y) of the layer-1 table (cpu/circle.rs:312-332).
+// for each pair (x, y) of the eight layer-1 twiddles at tb[0] (cpu/circle.rs:312-332).
 template <bool INVERSE, bool CIRCLE>
-__device__ __forceinline__ void radix32_stage(uint32_t (&v)[32], const uint32_t* __restrict__ tower, int L, int layer0,
-                                              uint32_t A, int first, int act_lo, int act_hi) {
-#pragma unroll
-    for (int step = 0; step < 5; step++) {
-        const int jj = INVERSE ? step : 4 - step;
-        if (first + jj < act_lo || first + jj >= act_hi) continue;
-        const int i = layer0 + jj;
-        if (CIRCLE && jj == 0) {
-            const uint32_t* __restrict__ t1 = tower + (1u << (L - 2)) + (A << 3);
+__device__ __forceinline__ void radix32_stage(uint32_t (&v)[32], const uint32_t* const (&tb)[5], int first, int act_lo, int act_hi) {
+    uint32_t t[16];
+    auto layer = [&](auto JJ) {
+        constexpr int jj = decltype(JJ)::value;
+        if (first + jj < act_lo || first + jj >= act_hi) return;
+        if constexpr (CIRCLE && jj == 0) {
+            load_tw<8>(tb[0], t);
 #pragma unroll
             for (int q = 0; q < 4; q++) {
-                uint32_t x2 = t1[2 * q] << 1, y2 = t1[2 * q + 1] << 1;
+                uint32_t x2 = t[2 * q] << 1, y2 = t[2 * q + 1] << 1;
                 if (INVERSE) {
                     bf_inv<false>(v[8 * q + 0], v[8 * q + 1], y2);
                     bf_inv<true>(v[8 * q + 2], v[8 * q + 3], y2);
@@ -75,10 +92,10 @@ __device__ __forceinline__ void radix32_stage(uint32_t (&v)[32], const uint32_t*
                 }
             }
         } else {
-            const uint32_t* __restrict__ tbl = tower + (1u << (L - i - 1)) + (A << (4 - jj));
+            load_tw<(16 >> jj)>(tb[jj], t);
 #pragma unroll
             for (int h = 0; h < (16 >> jj); h++) {
-                const uint32_t t2 = tbl[h] << 1;
+                const uint32_t t2 = t[h] << 1;
 #pragma unroll
                 for (int l = 0; l < (1 << jj); l++) {
                     const int p0 = (h << (jj + 1)) | l, p1 = p0 | (1 << jj);
@@ -87,7 +104,23 @@ __device__ __forceinline__ void radix32_stage(uint32_t (&v)[32], const uint32_t*
                 }
             }
         }
+    };
+    if (INVERSE) {
+        layer(std::integral_constant<int, 0>{}); layer(std::integral_constant<int, 1>{}); layer(std::integral_constant<int, 2>{});
+        layer(std::integral_constant<int, 3>{}); layer(std::integral_constant<int, 4>{});
+    } else {
+        layer(std::integral_constant<int, 4>{}); layer(std::integral_constant<int, 3>{}); layer(std::integral_constant<int, 2>{});
+        layer(std::integral_constant<int, 1>{}); layer(std::integral_constant<int, 0>{});
     }
+}
+
+// Twiddle pointers of a stage in the tower (global memory): layer jj of the stage is the global layer
+// layer0 + jj and its table starts at tower + 2^(L - i - 1) + (A << (4 - jj)).
+template <bool CIRCLE>
+__device__ __forceinline__ void tower_ptrs(const uint32_t* (&tb)[5], const uint32_t* __restrict__ tower, int L, int layer0, uint32_t A) {
+#pragma unroll
+    for (int jj = 0; jj < 5; jj++) tb[jj] = tower + (1u << (L - layer0 - jj - 1)) + (A << (4 - jj));
+    if (CIRCLE) tb[0] = tower + (1u << (L - 2)) + (A << 3);
 }
 
 // ---- asynchronous global -> shared copies (16 bytes each), grouped and waited on per thread
@@ -95,12 +128,34 @@ __device__ __forceinline__ void cp_async16(uint32_t* smem_dst, const uint32_t* g
     unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem_src) : "memory");
 }
+__device__ __forceinline__ void cp_async4(uint32_t* smem_dst, const uint32_t* gmem_src) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(gmem_src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
 constexpr int R32_CONTIG_WARPS = 8;    // warps per CTA of the contiguous pass; each runs its own pipeline
 constexpr int R32_BUF_WORDS = 264 * 32;  // one staging buffer: 1024 rows x 8 words, or 8 units of 33 x 32
+// Forward passes also stage the twiddles of the next work item (cp.async, same group as its data): the
+// twiddles a thread needs are short consecutive runs of the tower, different for every item.
+//   contiguous: [0,480) the per-thread stage (layers 1..4: 256 + 128 + 64 + 32 words; the circle layer reuses
+//               the layer-1 run), [480,511) the CTA-uniform stage (layers 5..9: 16 + 8 + 4 + 2 + 1 words)
+//   strided:    [0,992) the per-thread stage (512 + 256 + 128 + 64 + 32), [992,1023) the uniform stage
+constexpr int R32_TW_CONTIG = 512;
+constexpr int R32_TW_STRIDED = 1024;
+__host__ __device__ constexpr size_t r32_contig_smem(bool inverse) {
+    return (size_t)R32_CONTIG_WARPS * 2 * (33 * 32 + (inverse ? 0 : R32_TW_CONTIG)) * sizeof(uint32_t);
+}
+__host__ __device__ constexpr size_t r32_strided_smem(bool inverse) {
+    return (size_t)2 * (R32_BUF_WORDS + (inverse ? 0 : R32_TW_STRIDED)) * sizeof(uint32_t);
+}
+// Word k (0..30) of a uniform-stage block: layer jj and index h within its run of 16 >> jj.
+__device__ __forceinline__ void uniform_slot(int k, int& jj, int& h) {
+    jj = (k >= 16) + (k >= 24) + (k >= 28) + (k >= 30);
+    h = k - (32 - (32 >> jj));
+}
 
 struct R32Pass {
     int lo;              // first index bit of the window
@@ -125,6 +180,7 @@ __global__ void __launch_bounds__(32 * R32_CONTIG_WARPS, (INVERSE ? 24 : 16) / R
     const int warp = threadIdx.x >> 5, tm = threadIdx.x & 31;
     uint32_t* const buf0 = dyn_smem + (2 * warp) * (33 * 32);
     constexpr int BUF = 33 * 32;
+    uint32_t* const tw0 = dyn_smem + 2 * R32_CONTIG_WARPS * BUF + (2 * warp) * R32_TW_CONTIG;
     const int unit_bits = log_n - 10;
     const size_t total = (size_t)ncols << unit_bits;
     // Items are ordered column-major (unit index fastest) and dealt round-robin, so at any time
@@ -135,21 +191,41 @@ __global__ void __launch_bounds__(32 * R32_CONTIG_WARPS, (INVERSE ? 24 : 16) / R
     size_t item = (size_t)blockIdx.x * R32_CONTIG_WARPS + warp;
     const size_t item_end = total;
 
-    auto prefetch = [&](uint32_t* buf, size_t it) {
+    auto prefetch = [&](int b, size_t it) {
+        uint32_t* buf = buf0 + b * BUF;
         const uint32_t* __restrict__ src = src_cols[it >> unit_bits];
-        const uint32_t base = (uint32_t)(it & (((size_t)1 << unit_bits) - 1)) << 10;
+        const uint32_t un = (uint32_t)(it & (((size_t)1 << unit_bits) - 1));
+        const uint32_t base = un << 10;
 #pragma unroll
         for (int k = 0; k < 8; k++) {
             const int r = k * 4 + (tm >> 3), q = tm & 7;  // chunk c = 32 k + tm: row c / 8, chunk c % 8
             cp_async16(buf + r * 32 + ((q ^ (r & 7)) << 2), src + ((base + r * 32 + q * 4) & src_mask));
         }
+        if (!INVERSE) {
+            uint32_t* tw = tw0 + b * R32_TW_CONTIG;
+            // per-thread stage: chunk c of 120 (16 bytes each): layers 1, 2, 3, 4 hold 64, 32, 16, 8 chunks
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const int c = 32 * k + tm;
+                if (c < 120) {
+                    const int jj = 1 + (c >= 64) + (c >= 96) + (c >= 112);
+                    const int cc = c - (128 - (256 >> jj));
+                    cp_async16(tw + 4 * c, tower + (1u << (dom_log - jj - 1)) + (un << (9 - jj)) + 4 * cc);
+                }
+            }
+            if (tm < 31) {
+                int jj, h;
+                uniform_slot(tm, jj, h);
+                cp_async4(tw + 480 + tm, tower + (1u << (dom_log - 5 - jj - 1)) + (un << (4 - jj)) + h);
+            }
+        }
     };
 
     int cur = 0;
-    if (item < item_end) prefetch(buf0, item);
+    if (item < item_end) prefetch(0, item);
     cp_async_commit();
     for (; item < item_end; item += stride) {
-        if (item + stride < item_end) prefetch(buf0 + (cur ^ 1) * BUF, item + stride);
+        if (item + stride < item_end) prefetch(cur ^ 1, item + stride);
         cp_async_commit();
         cp_async_wait<1>();
         __syncwarp();
@@ -162,13 +238,20 @@ __global__ void __launch_bounds__(32 * R32_CONTIG_WARPS, (INVERSE ? 24 : 16) / R
 #pragma unroll
             for (int p = 0; p < 32; p++) v[p] = s[p * 32 + ((((tm >> 2) ^ (p & 7)) << 2) | (tm & 3))];
             __syncwarp();
-            radix32_stage<false, false>(v, tower, dom_log, 5, unit, 5, ps.act_lo, ps.act_hi);
+            const uint32_t* tw = tw0 + cur * R32_TW_CONTIG;
+            {
+                const uint32_t* tb[5] = {tw + 480, tw + 496, tw + 504, tw + 508, tw + 510};
+                radix32_stage<false, false>(v, tb, 5, ps.act_lo, ps.act_hi);
+            }
 #pragma unroll
             for (int p = 0; p < 32; p++) s[33 * p + tm] = v[p];
             __syncwarp();
 #pragma unroll
             for (int p = 0; p < 32; p++) v[p] = s[33 * tm + p];
-            radix32_stage<false, true>(v, tower, dom_log, 0, (unit << 5) | tm, 0, ps.act_lo, ps.act_hi);
+            {
+                const uint32_t* tb[5] = {tw + 8 * tm, tw + 8 * tm, tw + 256 + 4 * tm, tw + 384 + 2 * tm, tw + 448 + tm};
+                radix32_stage<false, true>(v, tb, 0, ps.act_lo, ps.act_hi);
+            }
             uint4* o = reinterpret_cast<uint4*>(dst + base + 32 * tm);
 #pragma unroll
             for (int q = 0; q < 8; q++) o[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
@@ -179,13 +262,16 @@ __global__ void __launch_bounds__(32 * R32_CONTIG_WARPS, (INVERSE ? 24 : 16) / R
                 v[4 * q] = x.x; v[4 * q + 1] = x.y; v[4 * q + 2] = x.z; v[4 * q + 3] = x.w;
             }
             __syncwarp();
-            radix32_stage<true, true>(v, tower, dom_log, 0, (unit << 5) | tm, 0, ps.act_lo, ps.act_hi);
+            const uint32_t* tb[5];
+            tower_ptrs<true>(tb, tower, dom_log, 0, (unit << 5) | tm);
+            radix32_stage<true, true>(v, tb, 0, ps.act_lo, ps.act_hi);
 #pragma unroll
             for (int p = 0; p < 32; p++) s[33 * tm + p] = v[p];
             __syncwarp();
 #pragma unroll
             for (int p = 0; p < 32; p++) v[p] = s[33 * p + tm];
-            radix32_stage<true, false>(v, tower, dom_log, 5, unit, 5, ps.act_lo, ps.act_hi);
+            tower_ptrs<false>(tb, tower, dom_log, 5, unit);
+            radix32_stage<true, false>(v, tb, 5, ps.act_lo, ps.act_hi);
 #pragma unroll
             for (int p = 0; p < 32; p++) dst[base + tm + 32 * p] = scale ? m31_mul(v[p], scale) : v[p];
         }
@@ -205,6 +291,7 @@ __global__ void __launch_bounds__(256, INVERSE ? 3 : 2)
     extern __shared__ __align__(16) uint32_t dyn_smem[];
     uint32_t* const buf0 = dyn_smem;
     constexpr int BUF = R32_BUF_WORDS;
+    uint32_t* const tw0 = dyn_smem + 2 * BUF;
     const uint32_t w = threadIdx.x & 7, tm = threadIdx.x >> 3;
     const int tile_bits = log_n - 13;
     const size_t total = (size_t)ncols << tile_bits;
@@ -214,7 +301,8 @@ __global__ void __launch_bounds__(256, INVERSE ? 3 : 2)
         a = tile >> (ps.lo - 3);
         return (a << (ps.lo + 10)) | (wb << 3);
     };
-    auto prefetch = [&](uint32_t* buf, size_t it) {
+    auto prefetch = [&](int b, size_t it) {
+        uint32_t* buf = buf0 + b * BUF;
         const uint32_t* __restrict__ src = src_cols[it >> tile_bits];
         uint32_t a;
         const uint32_t base = tile_base((uint32_t)(it & (((size_t)1 << tile_bits) - 1)), a);
@@ -224,15 +312,29 @@ __global__ void __launch_bounds__(256, INVERSE ? 3 : 2)
             const uint32_t m = c >> 1, half = c & 1;
             cp_async16(buf + 8 * m + 8 * (m >> 5) + 4 * half, src + ((base | (m << ps.lo) | (half << 2)) & src_mask));
         }
+        if (!INVERSE) {
+            uint32_t* tw = tw0 + b * R32_TW_STRIDED;
+            const int c = threadIdx.x;  // chunk c of 248: layers lo+0..lo+4 hold 128, 64, 32, 16, 8 chunks
+            if (c < 248) {
+                const int jj = (c >= 128) + (c >= 192) + (c >= 224) + (c >= 240);
+                const int cc = c - (256 - (256 >> jj));
+                cp_async16(tw + 4 * c, tower + (1u << (dom_log - ps.lo - jj - 1)) + (a << (9 - jj)) + 4 * cc);
+            }
+            if (c < 31) {
+                int jj, h;
+                uniform_slot(c, jj, h);
+                cp_async4(tw + 992 + c, tower + (1u << (dom_log - ps.lo - 5 - jj - 1)) + (a << (4 - jj)) + h);
+            }
+        }
     };
 
     int cur = 0;
     size_t item = blockIdx.x;
     const size_t item_end = total, stride = gridDim.x;
-    if (item < item_end) prefetch(buf0, item);
+    if (item < item_end) prefetch(0, item);
     cp_async_commit();
     for (; item < item_end; item += stride) {
-        if (item + stride < item_end) prefetch(buf0 + (cur ^ 1) * BUF, item + stride);
+        if (item + stride < item_end) prefetch(cur ^ 1, item + stride);
         cp_async_commit();
         cp_async_wait<1>();
         __syncthreads();
@@ -244,26 +346,36 @@ __global__ void __launch_bounds__(256, INVERSE ? 3 : 2)
         if (!INVERSE) {
 #pragma unroll
             for (int p = 0; p < 32; p++) v[p] = s[264 * p + 8 * tm + w];
-            radix32_stage<false, false>(v, tower, dom_log, ps.lo + 5, a, 5, ps.act_lo, ps.act_hi);
+            const uint32_t* tw = tw0 + cur * R32_TW_STRIDED;
+            {
+                const uint32_t* tb[5] = {tw + 992, tw + 1008, tw + 1016, tw + 1020, tw + 1022};
+                radix32_stage<false, false>(v, tb, 5, ps.act_lo, ps.act_hi);
+            }
             // each thread writes back exactly the words it read: no barrier needed before the write
 #pragma unroll
             for (int p = 0; p < 32; p++) s[264 * p + 8 * tm + w] = v[p];
             __syncthreads();
 #pragma unroll
             for (int p = 0; p < 32; p++) v[p] = s[264 * tm + 8 * p + w];
-            radix32_stage<false, false>(v, tower, dom_log, ps.lo, (a << 5) | tm, 0, ps.act_lo, ps.act_hi);
+            {
+                const uint32_t* tb[5] = {tw + 16 * tm, tw + 512 + 8 * tm, tw + 768 + 4 * tm, tw + 896 + 2 * tm, tw + 960 + tm};
+                radix32_stage<false, false>(v, tb, 0, ps.act_lo, ps.act_hi);
+            }
 #pragma unroll
             for (int p = 0; p < 32; p++) dst[base | ((32u * tm + p) << ps.lo)] = v[p];
         } else {
 #pragma unroll
             for (int p = 0; p < 32; p++) v[p] = s[264 * tm + 8 * p + w];
-            radix32_stage<true, false>(v, tower, dom_log, ps.lo, (a << 5) | tm, 0, ps.act_lo, ps.act_hi);
+            const uint32_t* tb[5];
+            tower_ptrs<false>(tb, tower, dom_log, ps.lo, (a << 5) | tm);
+            radix32_stage<true, false>(v, tb, 0, ps.act_lo, ps.act_hi);
 #pragma unroll
             for (int p = 0; p < 32; p++) s[264 * tm + 8 * p + w] = v[p];
             __syncthreads();
 #pragma unroll
             for (int p = 0; p < 32; p++) v[p] = s[264 * p + 8 * tm + w];
-            radix32_stage<true, false>(v, tower, dom_log, ps.lo + 5, a, 5, ps.act_lo, ps.act_hi);
+            tower_ptrs<false>(tb, tower, dom_log, ps.lo + 5, a);
+            radix32_stage<true, false>(v, tb, 5, ps.act_lo, ps.act_hi);
 #pragma unroll
             for (int p = 0; p < 32; p++) {
                 uint32_t x = scale ? m31_mul(v[p], scale) : v[p];

@@ -415,22 +415,42 @@ struct CommitmentSchemeProver {
 
     // TreeBuilder::extend_evals + commit (pcs/mod.rs:429-464) -> CommitmentTreeProver::new (:481-537).
     // `columns` are consumed: interpolated in place, per size group.
-    void commit_evals(std::vector<BaseColumn> columns, Channel& ch) {
+    // `fence_of` (optional, one entry per column) names the copy fence after which a column's values have
+    // arrived from the host; columns are then interpolated and extended fence by fence, while later
+    // columns are still in flight.
+    void commit_evals(std::vector<BaseColumn> columns, Channel& ch, const std::vector<int>* fence_of = nullptr) {
         CommitmentTreeProver t;
         std::map<uint32_t, std::vector<size_t>> by_log;
         for (size_t i = 0; i < columns.size(); i++) by_log[columns[i].log_size()].push_back(i);
-        for (auto& g : by_log) {
-            std::vector<BaseColumn*> cols;
-            for (auto i : g.second) cols.push_back(&columns[i]);
-            B200Backend::interpolate_columns(d, cols);
-        }
-        mark(0);
         t.evals.resize(columns.size());
-        for (auto& g : by_log) {
-            std::vector<const BaseColumn*> cols;
-            for (auto i : g.second) cols.push_back(&columns[i]);
-            auto ev_cols = B200Backend::evaluate_polynomials(d, cols, config.fri.log_blowup_factor);
-            for (size_t k = 0; k < g.second.size(); k++) t.evals[g.second[k]] = std::move(ev_cols[k]);
+        if (fence_of) {
+            mark(0);
+            std::map<int, std::map<uint32_t, std::vector<size_t>>> by_fence;  // fences in the order they complete
+            for (size_t i = 0; i < columns.size(); i++) by_fence[(*fence_of)[i]][columns[i].log_size()].push_back(i);
+            for (auto& f : by_fence) {
+                d.check(zkb_wait_fence(d.ctx(), f.first));
+                for (auto& g : f.second) {
+                    std::vector<BaseColumn*> cols;
+                    std::vector<const BaseColumn*> ccols;
+                    for (auto i : g.second) { cols.push_back(&columns[i]); ccols.push_back(&columns[i]); }
+                    B200Backend::interpolate_columns(d, cols);
+                    auto ev_cols = B200Backend::evaluate_polynomials(d, ccols, config.fri.log_blowup_factor);
+                    for (size_t k = 0; k < g.second.size(); k++) t.evals[g.second[k]] = std::move(ev_cols[k]);
+                }
+            }
+        } else {
+            for (auto& g : by_log) {
+                std::vector<BaseColumn*> cols;
+                for (auto i : g.second) cols.push_back(&columns[i]);
+                B200Backend::interpolate_columns(d, cols);
+            }
+            mark(0);
+            for (auto& g : by_log) {
+                std::vector<const BaseColumn*> cols;
+                for (auto i : g.second) cols.push_back(&columns[i]);
+                auto ev_cols = B200Backend::evaluate_polynomials(d, cols, config.fri.log_blowup_factor);
+                for (size_t k = 0; k < g.second.size(); k++) t.evals[g.second[k]] = std::move(ev_cols[k]);
+            }
         }
         mark(1);
         t.coeffs = std::move(columns);
@@ -842,14 +862,42 @@ static int pcs_prove_impl(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint
         config.mix_into(ch);
         CommitmentSchemeProver prover(dev, config, h_phase_ms);
         int flat = 0;
-        for (int t = 0; t < n_trees; t++) {
-            std::vector<BaseColumn> columns;
-            for (int c = 0; c < tree_ncols[t]; c++, flat++) {
-                size_t n = (size_t)1 << col_logs[flat];
-                if (d_cols) columns.push_back(BaseColumn::view(dev, d_cols[flat], n));
-                else columns.emplace_back(dev, h_cols[flat], n);
+        if (d_cols) {
+            for (int t = 0; t < n_trees; t++) {
+                std::vector<BaseColumn> columns;
+                for (int c = 0; c < tree_ncols[t]; c++, flat++)
+                    columns.push_back(BaseColumn::view(dev, d_cols[flat], (size_t)1 << col_logs[flat]));
+                prover.commit_evals(std::move(columns), ch);
             }
-            prover.commit_evals(std::move(columns), ch);
+        } else {
+            // Host columns: every copy of every tree is enqueued on the copy stream first, with a fence
+            // after each ~1/32 of the bytes, so that the transfer runs at link speed from start to end
+            // while the compute stream interpolates and extends what has already arrived.
+            size_t total_bytes = 0;
+            for (int i = 0; i < total; i++) total_bytes += (size_t)4 << col_logs[i];
+            const size_t per_fence = std::max<size_t>(total_bytes / 32, 1);
+            std::vector<std::vector<BaseColumn>> tree_cols(n_trees);
+            std::vector<std::vector<int>> tree_fences(n_trees);
+            for (int t = 0; t < n_trees; t++)
+                for (int c = 0; c < tree_ncols[t]; c++, flat++) tree_cols[t].emplace_back(dev, (size_t)1 << col_logs[flat]);
+            flat = 0;
+            int fence = 0;
+            size_t since = 0;
+            for (int t = 0; t < n_trees; t++)
+                for (int c = 0; c < tree_ncols[t]; c++, flat++) {
+                    size_t bytes = (size_t)4 << col_logs[flat];
+                    since += bytes;
+                    bool close = since >= per_fence || flat == total - 1;
+                    dev.check(zkb_h2d_overlapped(ctx, tree_cols[t][c].ptr(), h_cols[flat], bytes, close ? fence : -1));
+                    tree_fences[t].push_back(fence);
+                    if (close) { since = 0; if (fence < 63) fence++; }
+                }
+            try {
+                for (int t = 0; t < n_trees; t++) prover.commit_evals(std::move(tree_cols[t]), ch, &tree_fences[t]);
+            } catch (...) {
+                zkb_sync(ctx);  // no column may be freed while the copy stream still writes into it
+                throw;
+            }
         }
         CirclePointQ oods = get_random_point(ch);
         std::vector<std::vector<std::vector<CirclePointQ>>> points(n_trees);
