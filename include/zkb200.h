@@ -128,6 +128,14 @@ int zkb_bit_reverse_qm31(zkb_ctx* ctx, uint32_t* col, int log_n); /* 4-word elem
 int zkb_merkle_layer(zkb_ctx* ctx, int log_size, const uint32_t* prev, const uint32_t* const* cols, int ncols,
                      int m31_out, uint32_t* out);
 
+/* The leaf layer of a tree (no children) in several calls, a run of columns at a time, so that hashing overlaps
+ * the production of later columns. Call with consecutive runs in column order: cols_before = columns absorbed by
+ * earlier calls (a multiple of 16), total_cols = columns of the layer. Every call but the last must bring a
+ * multiple of 16 columns (whole Blake2s blocks); the call with cols_before + ncols == total_cols finalises. `out`
+ * (2^log_size x 8 words) carries the chaining values between calls and holds the hashes zkb_merkle_layer(log_size,
+ * NULL, all columns) would produce after the last one. */
+int zkb_merkle_leaves_partial(zkb_ctx* ctx, int log_size, const uint32_t* const* cols, int ncols, int cols_before, int total_cols,
+                              int m31_out, uint32_t* out);
 /* The upper part of a tree in one launch, for trees whose small layers take no columns (every FRI
  * layer tree; a trace tree without tiny columns): given the layer of 2^top_log hashes
  * (top_log <= 10), writes lower_layers[k] (2^k hashes) for k = top_log-1 .. 0, each node being

@@ -359,3 +359,21 @@ def test_gkr_fix_and_sum(ctx, oracle, kind, log_n):
         assert (no.download(shape=(-1, 4)) == fnum).all()
     out_kind = 1 if kind == 2 else kind
     assert (got == oracle.gkr_round_sums(out_kind, fnum, fden, eq, lam)).all()
+
+
+@pytest.mark.parametrize("m31", [True, False])
+@pytest.mark.parametrize("log_size,runs", [(5, [1]), (6, [16]), (4, [16, 1]), (7, [16, 16]), (9, [32, 16, 7]), (3, [48, 16]),
+                                           (10, [16, 16, 16, 16, 3])])
+def test_merkle_leaves_in_runs_of_columns(ctx, oracle, zkb, log_size, runs, m31):
+    n, total = 1 << log_size, sum(runs)
+    cols = [edge_m31_column(2100 + c, n) for c in range(total)]
+    bufs = [ctx.upload(c) for c in cols]
+    out = ctx.alloc(n * 8)
+    before = 0
+    for r in runs:
+        ctx.merkle_leaves_partial(log_size, [b.ptr for b in bufs[before:before + r]], before, total, out.ptr, m31_out=m31)
+        before += r
+    assert (out.download(shape=(n, 8)) == oracle.commit_on_layer(log_size, None, cols, m31=m31)).all()
+    # a run that is not the last one must hold whole blocks
+    with pytest.raises(zkb.ZkbError):
+        ctx.merkle_leaves_partial(log_size, [bufs[0].ptr], 0, total + 1, out.ptr)

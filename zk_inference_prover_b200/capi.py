@@ -16,7 +16,7 @@ EXPORTED_SYMBOLS = [
     "zkb_malloc", "zkb_free", "zkb_memset_zero", "zkb_h2d", "zkb_d2h", "zkb_h2d_async", "zkb_d2h_async", "zkb_h2d_overlapped", "zkb_wait_fence", "zkb_d2d",
     "zkb_host_alloc_pinned", "zkb_host_free_pinned", "zkb_gather_multi", "zkb_gather_hashes", "zkb_gather_words", "zkb_twiddles_d2h",
     "zkb_ifft_cols", "zkb_lde_cols", "zkb_eval_at_point_cols", "zkb_bit_reverse_m31", "zkb_bit_reverse_qm31",
-    "zkb_merkle_layer", "zkb_merkle_top", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine",
+    "zkb_merkle_layer", "zkb_merkle_leaves_partial", "zkb_merkle_top", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine",
     "zkb_accumulate", "zkb_lift_accumulate", "zkb_secure_powers", "zkb_gkr_eq_evals", "zkb_gkr_next_layer",
     "zkb_gkr_sum", "zkb_gkr_fix_and_sum", "zkb_mle_fix_qm31", "zkb_mle_fix_m31", "zkb_grind", "zkb_gkr_sum_noalloc", "zkb_gkr_sum_noalloc_error",
     "zkb_freivalds_scatter", "zkb_freivalds_acc",
@@ -269,6 +269,11 @@ class Context:
     def merkle_layer(self, log_size, prev_ptr, col_ptrs, out_ptr, m31_out=True):
         self._check(self.lib.zkb_merkle_layer(self.h, C.c_int(log_size), C.c_void_p(prev_ptr or None), _ptr_array(col_ptrs),
                                               C.c_int(len(col_ptrs)), C.c_int(int(m31_out)), C.c_void_p(out_ptr)))
+
+    def merkle_leaves_partial(self, log_size, col_ptrs, cols_before, total_cols, out_ptr, m31_out=True):
+        arr = (C.c_void_p * len(col_ptrs))(*col_ptrs)
+        self._check(self.lib.zkb_merkle_leaves_partial(self.h, C.c_int(log_size), arr, C.c_int(len(col_ptrs)), C.c_int(cols_before),
+                                                       C.c_int(total_cols), C.c_int(1 if m31_out else 0), C.c_void_p(out_ptr)))
 
     def merkle_top(self, top_log, top_ptr, lower_ptrs, m31_out=True):
         self._check(self.lib.zkb_merkle_top(self.h, C.c_int(top_log), C.c_void_p(top_ptr), _ptr_array(lower_ptrs), C.c_int(int(m31_out))))

@@ -124,6 +124,46 @@ __global__ void __launch_bounds__(256) merkle_layer_kernel(int log_size, const u
     store_hash(out, i, h, m31_out != 0);
 }
 
+// A leaf layer (no children) hashed in several calls, a run of columns at a time, so that hashing can
+// start while later columns are still being produced. `out` carries the chaining value between calls
+// (8 words per leaf, exactly the space of the final hash). A call that is not the last one absorbs
+// whole 64-byte blocks only (ncols a multiple of 16); the last call pads and finalises.
+__global__ void __launch_bounds__(256) merkle_leaves_partial_kernel(int log_size, const uint32_t* const* __restrict__ cols,
+                                                                    int ncols, uint32_t cols_before, int is_last, int m31_out,
+                                                                    uint32_t* __restrict__ out) {
+    const size_t n = (size_t)1 << log_size;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    uint32_t h[8], m[16];
+    uint4* o = reinterpret_cast<uint4*>(out + 8 * i);
+    if (cols_before == 0) {
+        blake2s_init(h);
+    } else {
+        uint4 a = o[0], b = o[1];
+        h[0] = a.x; h[1] = a.y; h[2] = a.z; h[3] = a.w; h[4] = b.x; h[5] = b.y; h[6] = b.z; h[7] = b.w;
+    }
+    uint32_t t = 4u * cols_before;
+    int c = 0;
+    while (ncols - c > 16 || (!is_last && ncols - c == 16)) {
+#pragma unroll
+        for (int k = 0; k < 16; k++) m[k] = cols[c + k][i];
+        c += 16;
+        t += 64;
+        blake2s_compress(h, m, t, false);
+    }
+    if (is_last) {
+        int rem = ncols - c;
+#pragma unroll
+        for (int k = 0; k < 16; k++) m[k] = (k < rem) ? cols[c + k][i] : 0u;
+        t += 4u * (uint32_t)rem;
+        blake2s_compress(h, m, t, true);
+        store_hash(out, i, h, m31_out != 0);
+    } else {
+        o[0] = make_uint4(h[0], h[1], h[2], h[3]);
+        o[1] = make_uint4(h[4], h[5], h[6], h[7]);
+    }
+}
+
 // The top of a tree in one launch: layers 2^(top_log-1) ... 2^0 from layer 2^top_log, nodes only
 // (no columns are injected). One CTA; a barrier separates the levels.
 constexpr int MERKLE_TOP_MAX_LOG = 10;
@@ -183,6 +223,26 @@ int zkb_merkle_layer(zkb_ctx* ctx, int log_size, const uint32_t* prev, const uin
     ProfScope prof(ctx, ncols ? "merkle_layer_kernel(columns)" : "merkle_layer_kernel(nodes only)");
     merkle_layer_kernel<<<blocks, threads, 0, ctx->stream>>>(log_size, prev, (const uint32_t* const*)d_cols, ncols, m31_out,
                                                              out);
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
+}
+
+int zkb_merkle_leaves_partial(zkb_ctx* ctx, int log_size, const uint32_t* const* cols, int ncols, int cols_before, int total_cols,
+                              int m31_out, uint32_t* out) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, log_size >= 0 && log_size <= 30 && cols != nullptr && out != nullptr && ((uintptr_t)out & 15) == 0);
+    ZKB_CHECK_ARG(ctx, ncols >= 1 && cols_before >= 0 && cols_before % 16 == 0 && cols_before + ncols <= total_cols);
+    const bool is_last = cols_before + ncols == total_cols;
+    ZKB_CHECK_ARG(ctx, is_last || ncols % 16 == 0);
+    DeviceGuard g(ctx);
+    void** d_cols = nullptr;
+    int rc = stage_ptrs(ctx, (const void* const*)cols, ncols, &d_cols);
+    if (rc) return rc;
+    size_t n = (size_t)1 << log_size;
+    unsigned threads = n < 256 ? 32 : 256;
+    ProfScope prof(ctx, "merkle_leaves_partial_kernel");
+    merkle_leaves_partial_kernel<<<(unsigned)((n + threads - 1) / threads), threads, 0, ctx->stream>>>(
+        log_size, (const uint32_t* const*)d_cols, ncols, (uint32_t)cols_before, is_last ? 1 : 0, m31_out, out);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }

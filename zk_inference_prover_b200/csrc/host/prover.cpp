@@ -66,7 +66,8 @@ struct PendingMerkle {  // slots of a planned decommitment
 struct MerkleProver {
     std::vector<HashColumn> layers;  // layers[log_size]; layers[0] holds the root
 
-    static MerkleProver commit(const Device& d, const std::vector<const BaseColumn*>& columns) {  // :39-64
+    // `leaves`, when given, is the already hashed largest layer (see zkb_merkle_leaves_partial).
+    static MerkleProver commit(const Device& d, const std::vector<const BaseColumn*>& columns, HashColumn* leaves = nullptr) {  // :39-64
         MerkleProver mp;
         if (columns.empty()) {
             mp.layers.push_back(B200Backend::commit_on_layer(d, 0, nullptr, {}));
@@ -80,7 +81,8 @@ struct MerkleProver {
         for (uint32_t log = max_log + 1; log-- > 0;) {
             std::vector<const BaseColumn*> layer_cols;
             while (pos < sorted.size() && sorted[pos]->log_size() == log) layer_cols.push_back(sorted[pos++]);
-            mp.layers[log] = B200Backend::commit_on_layer(d, log, log == max_log ? nullptr : &mp.layers[log + 1], layer_cols);
+            if (log == max_log && leaves) mp.layers[log] = std::move(*leaves);
+            else mp.layers[log] = B200Backend::commit_on_layer(d, log, log == max_log ? nullptr : &mp.layers[log + 1], layer_cols);
             if (log > 0 && log <= 10 && pos == sorted.size()) {
                 // no columns left below: the rest of the tree is nodes only, built in one launch
                 std::vector<uint32_t*> lower;
@@ -423,8 +425,25 @@ struct CommitmentSchemeProver {
         std::map<uint32_t, std::vector<size_t>> by_log;
         for (size_t i = 0; i < columns.size(); i++) by_log[columns[i].log_size()].push_back(i);
         t.evals.resize(columns.size());
+        HashColumn leaves;
+        bool have_leaves = false;
         if (fence_of) {
             mark(0);
+            // One column size: the leaf layer is hashed run by run (whole Blake2s blocks of 16 columns) as the
+            // extended columns appear, instead of after the last one.
+            const bool incremental = by_log.size() == 1 && columns.size() > 16;
+            const uint32_t leaf_log = columns[0].log_size() + config.fri.log_blowup_factor;
+            size_t hashed = 0, extended = 0;
+            if (incremental) leaves = HashColumn(d, (size_t)8 << leaf_log);
+            auto hash_ready = [&](bool final) {
+                size_t avail = extended - hashed;
+                size_t take = final ? avail : (avail > 16 ? (avail - 1) / 16 * 16 : 0);  // keep at least one column for the final call
+                if (!take) return;
+                std::vector<const uint32_t*> p;
+                for (size_t c = hashed; c < hashed + take; c++) p.push_back(t.evals[c].ptr());
+                d.check(zkb_merkle_leaves_partial(d.ctx(), (int)leaf_log, p.data(), (int)take, (int)hashed, (int)columns.size(), 1, leaves.ptr()));
+                hashed += take;
+            };
             std::map<int, std::map<uint32_t, std::vector<size_t>>> by_fence;  // fences in the order they complete
             for (size_t i = 0; i < columns.size(); i++) by_fence[(*fence_of)[i]][columns[i].log_size()].push_back(i);
             for (auto& f : by_fence) {
@@ -436,8 +455,10 @@ struct CommitmentSchemeProver {
                     B200Backend::interpolate_columns(d, cols);
                     auto ev_cols = B200Backend::evaluate_polynomials(d, ccols, config.fri.log_blowup_factor);
                     for (size_t k = 0; k < g.second.size(); k++) t.evals[g.second[k]] = std::move(ev_cols[k]);
+                    if (incremental) { extended = g.second.back() + 1; hash_ready(false); }
                 }
             }
+            if (incremental) { hash_ready(true); have_leaves = true; }
         } else {
             for (auto& g : by_log) {
                 std::vector<BaseColumn*> cols;
@@ -456,7 +477,7 @@ struct CommitmentSchemeProver {
         t.coeffs = std::move(columns);
         std::vector<const BaseColumn*> refs;
         for (auto& e : t.evals) refs.push_back(&e);
-        t.commitment = MerkleProver::commit(d, refs);
+        t.commitment = MerkleProver::commit(d, refs, have_leaves ? &leaves : nullptr);
         ch.mix_root(t.commitment.root(d));
         mark(2);
         trees.push_back(std::move(t));

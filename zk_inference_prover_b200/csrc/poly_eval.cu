@@ -33,46 +33,62 @@ __global__ void eval_weights_kernel(EvalFactors f, int bits, uint32_t* __restric
 __device__ __forceinline__ uint64_t fold64_eval(uint64_t v) { return (v & P) + (v >> 31); }
 
 // out[col][chunk] = sum_{e < 2048} cols[col][2048 chunk + e] * weights[e]
-__global__ void __launch_bounds__(256) eval_dot_kernel(const uint32_t* const* __restrict__ cols, int log_n,
+// Thread t owns elements 4t..4t+3 and 1024+4t..1024+4t+3 of every chunk (two 16-byte loads) and keeps
+// their eight weights in registers. DOT_CHUNKS chunks are in flight per iteration; their per-warp sums
+// use the hardware warp reduction on 16-bit halves (32 x 2^16 fits a word) and meet in shared memory
+// once per iteration.
+constexpr int DOT_CHUNKS = 4;
+__global__ void __launch_bounds__(256) eval_dot_kernel(const uint32_t* const* __restrict__ cols, int ncols, int log_n,
                                                        const uint32_t* __restrict__ weights, uint32_t* __restrict__ out) {
-    __shared__ uint32_t red[8][4];
-    const int t = threadIdx.x;
+    __shared__ uint32_t red[DOT_CHUNKS][4][2][8];  // [chunk][component][lo/hi][warp]
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     uint4 w[8];
 #pragma unroll
-    for (int u = 0; u < 8; u++) w[u] = reinterpret_cast<const uint4*>(weights)[t + 256 * u];
+    for (int u = 0; u < 8; u++) w[u] = reinterpret_cast<const uint4*>(weights)[(u >> 2) * 1024 + 4 * t + (u & 3)];
     const size_t chunks = (size_t)1 << (log_n - EVAL_CHUNK_LOG);
-    const int col = blockIdx.y;
-    const uint32_t* __restrict__ c = cols[col];
-    for (size_t chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
-        const uint32_t* __restrict__ p = c + (chunk << EVAL_CHUNK_LOG) + t;
-        uint32_t v[8];
+    const size_t groups = (chunks + DOT_CHUNKS - 1) / DOT_CHUNKS;
+    // persistent CTAs over (column, group of chunks): the weights are read once per CTA
+    for (size_t item = blockIdx.x; item < groups * (size_t)ncols; item += gridDim.x) {
+        const size_t col = item / groups, chunk0 = (item % groups) * DOT_CHUNKS;
+        const uint32_t* __restrict__ c = cols[col];
+        uint4 v[DOT_CHUNKS][2];
 #pragma unroll
-        for (int u = 0; u < 8; u++) v[u] = p[256 * u];
-        uint64_t a0 = 0, a1 = 0, a2 = 0, a3 = 0;
-#pragma unroll
-        for (int u = 0; u < 8; u++) {
-            a0 += (uint64_t)v[u] * w[u].x; a1 += (uint64_t)v[u] * w[u].y;
-            a2 += (uint64_t)v[u] * w[u].z; a3 += (uint64_t)v[u] * w[u].w;
-            if (u == 3) { a0 = fold64_eval(a0); a1 = fold64_eval(a1); a2 = fold64_eval(a2); a3 = fold64_eval(a3); }
+        for (int g = 0; g < DOT_CHUNKS; g++) {
+            if (chunk0 + g < chunks) {
+                const uint4* p = reinterpret_cast<const uint4*>(c + ((chunk0 + g) << EVAL_CHUNK_LOG));
+                v[g][0] = __ldcs(p + t);
+                v[g][1] = __ldcs(p + 256 + t);
+            } else {
+                v[g][0] = v[g][1] = make_uint4(0, 0, 0, 0);
+            }
         }
-        qm31 s{{m31_reduce64(a0), m31_reduce64(a1), m31_reduce64(a2), m31_reduce64(a3)}};
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-            qm31 o;
+        for (int g = 0; g < DOT_CHUNKS; g++) {
+            const uint32_t e[8] = {v[g][0].x, v[g][0].y, v[g][0].z, v[g][0].w, v[g][1].x, v[g][1].y, v[g][1].z, v[g][1].w};
+            uint64_t a0 = 0, a1 = 0, a2 = 0, a3 = 0;
 #pragma unroll
-            for (int k = 0; k < 4; k++) o.c[k] = __shfl_down_sync(0xffffffffu, s.c[k], off);
-            s = qm31_add(s, o);
-        }
-        if ((t & 31) == 0) {
+            for (int u = 0; u < 8; u++) {
+                a0 += (uint64_t)e[u] * w[u].x; a1 += (uint64_t)e[u] * w[u].y;
+                a2 += (uint64_t)e[u] * w[u].z; a3 += (uint64_t)e[u] * w[u].w;
+                if (u == 3) { a0 = fold64_eval(a0); a1 = fold64_eval(a1); a2 = fold64_eval(a2); a3 = fold64_eval(a3); }
+            }
+            const uint32_t r[4] = {m31_reduce64(a0), m31_reduce64(a1), m31_reduce64(a2), m31_reduce64(a3)};
 #pragma unroll
-            for (int k = 0; k < 4; k++) red[t >> 5][k] = s.c[k];
+            for (int k = 0; k < 4; k++) {
+                uint32_t lo = __reduce_add_sync(0xffffffffu, r[k] & 0xffffu);
+                uint32_t hi = __reduce_add_sync(0xffffffffu, r[k] >> 16);
+                if (lane == 0) { red[g][k][0][warp] = lo; red[g][k][1][warp] = hi; }
+            }
         }
         __syncthreads();
-        if (t < 4) {
-            uint32_t acc = 0;
+        if (t < 4 * DOT_CHUNKS) {
+            const int g = t >> 2, k = t & 3;
+            if (chunk0 + g < chunks) {
+                uint64_t lo = 0, hi = 0;
 #pragma unroll
-            for (int wv = 0; wv < 8; wv++) acc = m31_add(acc, red[wv][t]);
-            out[4 * ((size_t)col * chunks + chunk) + t] = acc;
+                for (int wv = 0; wv < 8; wv++) { lo += red[g][k][0][wv]; hi += red[g][k][1][wv]; }
+                out[4 * ((size_t)col * chunks + chunk0 + g) + k] = m31_reduce64(lo + (hi << 16));
+            }
         }
         __syncthreads();
     }
@@ -139,7 +155,8 @@ int zkb_eval_at_point_cols(zkb_ctx* ctx, const uint32_t* const* coeffs, int ncol
         x = qm31_double_x(x);
     }
     // Scratch: [weights: 2048 QM31] [ping] [pong]; columns go in batches whose partials fit.
-    const bool use_dot = log_n >= EVAL_CHUNK_LOG;
+    bool use_dot = log_n >= EVAL_CHUNK_LOG;
+    for (int c = 0; c < ncols; c++) use_dot = use_dot && ((uintptr_t)coeffs[c] & 15) == 0;  // 16-byte loads
     int first_chunk = log_n < EVAL_CHUNK_LOG ? log_n : EVAL_CHUNK_LOG;
     size_t partials_per_col = (size_t)1 << (log_n - first_chunk);
     uint32_t* weights = ctx->scratch;
@@ -161,10 +178,10 @@ int zkb_eval_at_point_cols(zkb_ctx* ctx, const uint32_t* const* coeffs, int ncol
         uint32_t* bufB = bufA + half_words;
         int log_cur = log_n, level = 0;
         if (use_dot) {
-            unsigned gx = (unsigned)(partials_per_col < 64 ? partials_per_col : 64);
-            dim3 grid(gx, nc);
+            size_t items = (partials_per_col + DOT_CHUNKS - 1) / DOT_CHUNKS * (size_t)nc;
+            unsigned grid = (unsigned)(items < 2 * 148 ? items : 2 * 148);
             ProfScope prof(ctx, "eval_dot_kernel");
-            eval_dot_kernel<<<grid, 256, 0, ctx->stream>>>((const uint32_t* const*)d_cols, log_n, weights, bufA);
+            eval_dot_kernel<<<grid, 256, 0, ctx->stream>>>((const uint32_t* const*)d_cols, nc, log_n, weights, bufA);
             ZKB_LAUNCH_CHECK(ctx);
         } else {
             unsigned threads = first_chunk >= 9 ? 256 : 32;

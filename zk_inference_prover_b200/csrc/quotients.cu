@@ -22,53 +22,84 @@ struct Secure4C { const uint32_t* c[4]; };
 // Partially folds a 64-bit accumulator to below 2^34 without changing its residue.
 __device__ __forceinline__ uint64_t fold64(uint64_t v) { return (v & P) + (v >> 31); }
 
-constexpr int NUM_ROWS_PER_THREAD = 2;
+// R consecutive rows per thread (one 8- or 16-byte load per column). The column addresses and the
+// coefficients of a tile of columns are resolved once per CTA into shared memory, so the inner loop
+// is one independent streaming load per column and 4 R multiply-adds: the kernel is bound by HBM.
+constexpr int NUM_TILE = 128;
 
+template <int R>
 __global__ void __launch_bounds__(256) quot_numerators_kernel(const uint32_t* const* __restrict__ cols,
                                                               const uint32_t* __restrict__ col_idx,
                                                               const uint4* __restrict__ coeff_c, int k, qm31 b_sum,
                                                               size_t n, Secure4 out) {
-    size_t row0 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * NUM_ROWS_PER_THREAD;
-    if (row0 >= n) return;
-    uint64_t acc[NUM_ROWS_PER_THREAD][4];
+    __shared__ const uint32_t* s_col[NUM_TILE];
+    __shared__ uint4 s_c[NUM_TILE];
+    const size_t row0 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * R;
+    const bool live = row0 < n;
+    uint64_t acc[R][4];
 #pragma unroll
-    for (int r = 0; r < NUM_ROWS_PER_THREAD; r++)
+    for (int r = 0; r < R; r++)
 #pragma unroll
         for (int q = 0; q < 4; q++) acc[r][q] = 0;
-    int j = 0;
-    for (; j + 4 <= k; j += 4) {
+    auto load = [&](const uint32_t* col, uint32_t (&v)[R]) {
+        if constexpr (R == 4) {
+            uint4 x = __ldcs(reinterpret_cast<const uint4*>(col + row0));
+            v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+        } else {
+            uint2 x = __ldcs(reinterpret_cast<const uint2*>(col + row0));
+            v[0] = x.x; v[1] = x.y;
+        }
+    };
+    auto mac = [&](const uint4& c, const uint32_t (&v)[R]) {
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
-            const uint32_t* col = cols[col_idx[j + u]];
-            uint4 c = coeff_c[j + u];
-            uint2 v = *reinterpret_cast<const uint2*>(col + row0);
-            acc[0][0] += (uint64_t)c.x * v.x; acc[0][1] += (uint64_t)c.y * v.x;
-            acc[0][2] += (uint64_t)c.z * v.x; acc[0][3] += (uint64_t)c.w * v.x;
-            acc[1][0] += (uint64_t)c.x * v.y; acc[1][1] += (uint64_t)c.y * v.y;
-            acc[1][2] += (uint64_t)c.z * v.y; acc[1][3] += (uint64_t)c.w * v.y;
+        for (int r = 0; r < R; r++) {
+            acc[r][0] += (uint64_t)c.x * v[r]; acc[r][1] += (uint64_t)c.y * v[r];
+            acc[r][2] += (uint64_t)c.z * v[r]; acc[r][3] += (uint64_t)c.w * v[r];
+        }
+    };
+    for (int tile0 = 0; tile0 < k; tile0 += NUM_TILE) {
+        const int tk = k - tile0 < NUM_TILE ? k - tile0 : NUM_TILE;
+        __syncthreads();
+        if ((int)threadIdx.x < tk) {
+            s_col[threadIdx.x] = cols[col_idx[tile0 + threadIdx.x]];
+            s_c[threadIdx.x] = coeff_c[tile0 + threadIdx.x];
+        }
+        __syncthreads();
+        if (!live) continue;
+        int j = 0;
+        for (; j + 4 <= tk; j += 4) {
+            uint32_t v[4][R];
+#pragma unroll
+            for (int u = 0; u < 4; u++) load(s_col[j + u], v[u]);
+#pragma unroll
+            for (int u = 0; u < 4; u++) mac(s_c[j + u], v[u]);
+            // four 62-bit products on top of a folded (< 2^34) accumulator fit in 64 bits
+#pragma unroll
+            for (int r = 0; r < R; r++)
+#pragma unroll
+                for (int q = 0; q < 4; q++) acc[r][q] = fold64(acc[r][q]);
+        }
+        for (; j < tk; j++) {  // at most 3 tail products
+            uint32_t v[R];
+            load(s_col[j], v);
+            mac(s_c[j], v);
         }
 #pragma unroll
-        for (int r = 0; r < NUM_ROWS_PER_THREAD; r++)
+        for (int r = 0; r < R; r++)
 #pragma unroll
             for (int q = 0; q < 4; q++) acc[r][q] = fold64(acc[r][q]);
     }
-    for (; j < k; j++) {
-        const uint32_t* col = cols[col_idx[j]];
-        uint4 c = coeff_c[j];
-        uint2 v = *reinterpret_cast<const uint2*>(col + row0);
-        // at most 3 tail products on top of a folded (< 2^34) accumulator
-        acc[0][0] += (uint64_t)c.x * v.x; acc[0][1] += (uint64_t)c.y * v.x;
-        acc[0][2] += (uint64_t)c.z * v.x; acc[0][3] += (uint64_t)c.w * v.x;
-        acc[1][0] += (uint64_t)c.x * v.y; acc[1][1] += (uint64_t)c.y * v.y;
-        acc[1][2] += (uint64_t)c.z * v.y; acc[1][3] += (uint64_t)c.w * v.y;
-    }
-    uint32_t res[NUM_ROWS_PER_THREAD][4];
+    if (!live) return;
+    uint32_t res[R][4];
 #pragma unroll
-    for (int r = 0; r < NUM_ROWS_PER_THREAD; r++)
+    for (int r = 0; r < R; r++)
 #pragma unroll
         for (int q = 0; q < 4; q++) res[r][q] = m31_sub(m31_reduce64(acc[r][q]), b_sum.c[q]);
 #pragma unroll
-    for (int q = 0; q < 4; q++) *reinterpret_cast<uint2*>(out.c[q] + row0) = make_uint2(res[0][q], res[1][q]);
+    for (int q = 0; q < 4; q++) {
+        if constexpr (R == 4) *reinterpret_cast<uint4*>(out.c[q] + row0) = make_uint4(res[0][q], res[1][q], res[2][q], res[3][q]);
+        else *reinterpret_cast<uint2*>(out.c[q] + row0) = make_uint2(res[0][q], res[1][q]);
+    }
 }
 
 constexpr int MAX_ACCS = 8;
@@ -205,10 +236,16 @@ int zkb_quot_numerators(zkb_ctx* ctx, const uint32_t* const* cols, int ncols, in
         ZKB_CUDA(ctx, cudaMemcpyAsync(d_idx, h_col_idx, (size_t)k * 4, cudaMemcpyHostToDevice, ctx->stream));
     }
     size_t n = (size_t)1 << log_n;
-    size_t threads_total = n / NUM_ROWS_PER_THREAD;
+    bool wide = n >= 4;
+    for (int q = 0; q < 4; q++) wide = wide && ((uintptr_t)out[q] & 15) == 0;
+    for (int c = 0; c < ncols; c++) wide = wide && ((uintptr_t)cols[c] & 15) == 0;
     ProfScope prof(ctx, "quot_numerators_kernel");
-    quot_numerators_kernel<<<(unsigned)((threads_total + 255) / 256), 256, 0, ctx->stream>>>(
-        (const uint32_t* const*)d_cols, d_idx, reinterpret_cast<const uint4*>(d_c), k, b_sum, n, o);
+    if (wide)
+        quot_numerators_kernel<4><<<(unsigned)((n / 4 + 255) / 256), 256, 0, ctx->stream>>>(
+            (const uint32_t* const*)d_cols, d_idx, reinterpret_cast<const uint4*>(d_c), k, b_sum, n, o);
+    else
+        quot_numerators_kernel<2><<<(unsigned)((n / 2 + 255) / 256), 256, 0, ctx->stream>>>(
+            (const uint32_t* const*)d_cols, d_idx, reinterpret_cast<const uint4*>(d_c), k, b_sum, n, o);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }
