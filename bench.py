@@ -299,10 +299,15 @@ def run_ours(args, rank, world, local_rank):
         lde_ms = sum(v[0] for _, v in fwd)
         achieved = ab["extend"] / (lde_ms * 1e-3) / 1e9 if lde_ms else None
         kern = {k: {"ms": round(v[0], 4), "launches": v[1]} for k, v in sorted(kernels.items(), key=lambda kv: -kv[1][0])}
+        # DRAM traffic of the two LDE launches from the ncu capture on 32 columns of this shape
+        # (profiles/fft_r32_lde_32x2e20.md: 714 + 1037 MB), scaled by the column count.
+        traffic = 1751.1e6 / 32 * ncols if (log_n, args.log_blowup) == (20, 2) else None
         roofline = {"bound": "hbm", "kernel": "+".join(k for k, _ in fwd) + " (the launches of one LDE)",
                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak if achieved else None,
-                    "traffic": None, "peak_kind": peak_kind,
-                    "note": "integer-issue bound, not HBM bound: about 10.5 thread instructions per butterfly (see DESIGN.md)",
+                    "traffic": traffic, "peak_kind": peak_kind,
+                    "note": "achieved = algorithmic bytes (read 2^log_size, write 2^(log_size+log_blowup) words per column) / the "
+                            "CUDA-event time of the two launches; the kernels are instruction-issue bound (about 10 instructions "
+                            "per butterfly, DRAM at 24-35% of peak), and the 2.6x traffic is the intermediate array of the two passes",
                     "per_phase_ms": per, "kernels_one_step": kern,
                     "per_operator_gbs": {
                         "interpolate": ab["interpolate"] / (sum(v[0] for k, v in kernels.items() if "inverse" in k) * 1e-3) / 1e9,
