@@ -125,6 +125,8 @@ def cpu_leg(args, sample_cols):
     commit + prove flow as the GPU step."""
     import oracle
 
+    # all the host threads this process may use (torchrun exports OMP_NUM_THREADS=1 to its workers)
+    oracle.set_num_threads(len(os.sched_getaffinity(0)))
     log_n, log_out = args.log_size, args.log_size + args.log_blowup
     cols = [splitmix_column(SEED0 + c, 1 << log_n) for c in range(sample_cols)]
     oracle.twiddles(log_out - 1)  # the tower is built once, outside the timed region (as precompute_twiddles is)

@@ -61,6 +61,11 @@ def num_threads():
     return lib().zko_num_threads()
 
 
+def set_num_threads(n):
+    """OpenMP threads of the heavy loops (launchers such as torchrun export OMP_NUM_THREADS=1)."""
+    lib().zko_set_num_threads(C.c_int(n))
+
+
 # ---------------------------------------------------------------- fields
 def m31_mul(a, b):
     return lib().zko_m31_mul(C.c_uint32(a), C.c_uint32(b))

@@ -44,6 +44,14 @@ int zko_num_threads() {
 #endif
 }
 
+void zko_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 // ---- fields (for unit tests of the restatement itself)
 uint32_t zko_m31_mul(uint32_t a, uint32_t b) { return (M31(a) * M31(b)).v; }
 uint32_t zko_m31_inv(uint32_t a) { return M31(a).inverse().v; }
