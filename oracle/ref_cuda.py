@@ -1,0 +1,145 @@
+"""TEST INFRASTRUCTURE ONLY: ctypes driver for the reference's own CUDA backend, compiled unmodified by
+oracle/Makefile.ref_cuda into oracle/_ref/libstwo_cuda_ref.so (see that file). It is a second checker beside
+the CPU oracle: the tests run the reference's kernels and this repository's kernels on the same inputs and
+compare every word; bench.py times it as a same-box GPU baseline. The calls follow the reference's Rust call
+sites (nitroo/crates/stwo/src/prover/backend/cuda/poly.rs:179-294, 422-576, blake2s.rs:61-118) over the
+C functions declared in nitroo/crates/stwo/src/stwo_cuda/bindings.rs.
+
+The library works on the legacy default stream and its own memory pool; every method here that returns host
+data synchronises through the library's blocking copies."""
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "_ref", "libstwo_cuda_ref.so")
+P = 2**31 - 1
+GEN = (2, 1268011823)  # M31_CIRCLE_GEN, nitroo/crates/stwo/src/core/circle.rs:202-205
+
+
+def available():
+    return os.path.exists(LIB_PATH)
+
+
+class _Point(C.Structure):  # stwo_cuda/cuda/point.cuh:7-10
+    _fields_ = [("x", C.c_uint32), ("y", C.c_uint32)]
+
+
+def _padd(a, b):
+    return ((a[0] * b[0] - a[1] * b[1]) % P, (a[0] * b[1] + a[1] * b[0]) % P)
+
+
+def _pmul(p, k):
+    r = (1, 0)
+    while k:
+        if k & 1:
+            r = _padd(r, p)
+        p = _padd(p, p)
+        k >>= 1
+    return r
+
+
+def _subgroup_gen(log_size):
+    return _pmul(GEN, 1 << (31 - log_size))
+
+
+class RefCuda:
+    def __init__(self):
+        if not available():
+            raise RuntimeError("oracle/_ref/libstwo_cuda_ref.so is not built (make -f oracle/Makefile.ref_cuda)")
+        L = self.lib = C.CDLL(LIB_PATH)
+        vp, u32, i32 = C.c_void_p, C.c_uint32, C.c_int
+        L.copy_uint32_t_vec_from_host_to_device.restype = vp
+        L.copy_uint32_t_vec_from_host_to_device.argtypes = [vp, i32]
+        L.copy_uint32_t_vec_from_device_to_host.restype = None
+        L.copy_uint32_t_vec_from_device_to_host.argtypes = [vp, vp, i32]
+        L.copy_uint32_t_vec_from_device_to_device.restype = None
+        L.copy_uint32_t_vec_from_device_to_device.argtypes = [vp, vp, i32]
+        L.cuda_malloc_uint32_t.restype = vp
+        L.cuda_malloc_uint32_t.argtypes = [i32]
+        L.cuda_alloc_zeroes_uint32_t.restype = vp
+        L.cuda_alloc_zeroes_uint32_t.argtypes = [i32]
+        L.cuda_malloc_blake_2s_hash.restype = vp
+        L.cuda_malloc_blake_2s_hash.argtypes = [i32]
+        L.copy_blake_2s_hash_vec_from_device_to_host.restype = None
+        L.copy_blake_2s_hash_vec_from_device_to_host.argtypes = [vp, vp, u32]
+        L.copy_device_pointer_vec_from_host_to_device.restype = vp
+        L.copy_device_pointer_vec_from_host_to_device.argtypes = [vp, u32]
+        L.cuda_free_memory.restype = None
+        L.cuda_free_memory.argtypes = [vp]
+        L.precompute_twiddles.restype = vp
+        L.precompute_twiddles.argtypes = [_Point, _Point, i32]
+        L.batch_inverse_base_field.restype = None
+        L.batch_inverse_base_field.argtypes = [vp, vp, i32]
+        for f in (L.ntt_b2n_column, L.ntt_n2b_columns):
+            f.restype = None
+            f.argtypes = [vp, u32, u32, vp, u32, u32]
+        L.commit_on_first_layer_m31.restype = None
+        L.commit_on_first_layer_m31.argtypes = [u32, u32, vp, vp]
+        L.commit_on_layer_with_previous_m31.restype = None
+        L.commit_on_layer_with_previous_m31.argtypes = [u32, u32, vp, vp, vp]
+        L.gkr_device_synchronize.restype = None
+        L.gkr_device_synchronize.argtypes = []
+
+    # ---- memory
+    def upload(self, arr):
+        arr = np.ascontiguousarray(arr, dtype=np.uint32)
+        return self.lib.copy_uint32_t_vec_from_host_to_device(arr.ctypes.data, arr.size)
+
+    def download(self, ptr, n):
+        out = np.empty(n, np.uint32)
+        self.lib.copy_uint32_t_vec_from_device_to_host(ptr, out.ctypes.data, n)
+        return out
+
+    def download_hashes(self, ptr, n):
+        out = np.empty((n, 8), np.uint32)
+        self.lib.copy_blake_2s_hash_vec_from_device_to_host(ptr, out.ctypes.data, n)
+        return out
+
+    def free(self, ptr):
+        self.lib.cuda_free_memory(ptr)
+
+    def sync(self):
+        self.lib.gkr_device_synchronize()
+
+    # ---- PolyOps::precompute_twiddles (backend/cuda/poly.rs:554-576) for Coset::half_odds(log_half)
+    def twiddle_tree(self, log_half):
+        initial, step, size = _subgroup_gen(log_half + 2), _subgroup_gen(log_half), 1 << log_half
+        tw = self.lib.precompute_twiddles(_Point(*initial), _Point(*step), size)
+        itw = self.lib.cuda_malloc_uint32_t(size)
+        self.lib.batch_inverse_base_field(tw, itw, size)
+        return {"tw": tw, "itw": itw, "size": size}
+
+    # ---- PolyOps::interpolate_columns (poly.rs:211-294): in place on columns of 2^log_n values
+    def interpolate_columns(self, col_ptrs, log_n, tree):
+        arr = (C.c_void_p * len(col_ptrs))(*col_ptrs)
+        self.lib.ntt_b2n_column(arr, log_n, len(col_ptrs), tree["itw"], tree["size"], 1 << (log_n - 1))
+
+    # ---- PolyOps::evaluate_polynomials (poly.rs:458-552): zero-extended copies, then one batched transform
+    def extend_columns(self, coeff_ptrs, log_n, log_out):
+        out = []
+        for p in coeff_ptrs:
+            q = self.lib.cuda_alloc_zeroes_uint32_t(1 << log_out)
+            self.lib.copy_uint32_t_vec_from_device_to_device(p, q, 1 << log_n)
+            out.append(q)
+        return out
+
+    def evaluate_extended(self, ext_ptrs, log_out, tree):
+        arr = (C.c_void_p * len(ext_ptrs))(*ext_ptrs)
+        self.lib.ntt_n2b_columns(arr, log_out, len(ext_ptrs), tree["tw"], tree["size"], 1 << (log_out - 1))
+
+    # ---- MerkleOps<Blake2sM31MerkleHasher>::commit_on_layer (blake2s.rs:61-96)
+    def commit_on_layer(self, log_size, prev_ptr, col_ptrs):
+        n = 1 << log_size
+        res = self.lib.cuda_malloc_blake_2s_hash(n)
+        arr = (C.c_void_p * max(len(col_ptrs), 1))(*col_ptrs)
+        dptrs = self.lib.copy_device_pointer_vec_from_host_to_device(arr, len(col_ptrs)) if col_ptrs else None
+        if prev_ptr:
+            self.lib.commit_on_layer_with_previous_m31(n, len(col_ptrs), dptrs, prev_ptr, res)
+        else:
+            self.lib.commit_on_first_layer_m31(n, len(col_ptrs), dptrs, res)
+        if dptrs:
+            self.sync()
+            self.free(dptrs)
+        return res
