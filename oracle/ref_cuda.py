@@ -143,3 +143,145 @@ class RefCuda:
             self.sync()
             self.free(dptrs)
         return res
+
+
+class _Q(C.Structure):  # qm31 by value (stwo_cuda/cuda/fields.cuh:10-18; bindings.rs CudaSecureField)
+    _fields_ = [("a", C.c_uint32), ("b", C.c_uint32), ("c", C.c_uint32), ("d", C.c_uint32)]
+
+
+def _q(v):
+    v = [int(x) for x in np.asarray(v).reshape(4)]
+    return _Q(*v)
+
+
+def _ptrs(ps):
+    return (C.c_void_p * len(ps))(*ps)
+
+
+class RefCudaOps(RefCuda):
+    """FriOps, QuotientOps, GkrOps, MleOps and ColumnOps of the reference's CUDA backend
+    (prover/backend/cuda/{fri,quotient}.rs, prover/backend/cuda/lookups/gkr.rs)."""
+
+    def __init__(self):
+        super().__init__()
+        L, vp, u32, i32 = self.lib, C.c_void_p, C.c_uint32, C.c_int
+        for f in (L.fold_line, L.fold_circle_into_line):
+            f.restype = None
+            f.argtypes = [vp, u32, u32, vp, _Q, vp]
+        L.accumulate_numerators_batch.restype = None
+        L.accumulate_numerators_batch.argtypes = [i32, vp, vp, vp, vp, i32, vp, vp, vp, vp]
+        L.compute_quotients_and_combine.restype = None
+        L.compute_quotients_and_combine.argtypes = [i32, i32, u32, u32, i32, vp, vp, vp, vp, vp, vp, vp, vp]
+        L.gen_eq_evals.restype = None
+        L.gen_eq_evals.argtypes = [_Q, vp, u32, vp, u32]
+        L.gkr_next_layer_grand_product.restype = None
+        L.gkr_next_layer_grand_product.argtypes = [vp, vp, u32]
+        L.gkr_next_layer_logup_generic.restype = None
+        L.gkr_next_layer_logup_generic.argtypes = [vp, vp, vp, vp, u32]
+        L.gkr_next_layer_logup_multiplicities.restype = None
+        L.gkr_next_layer_logup_multiplicities.argtypes = [vp, vp, vp, vp, u32]
+        L.gkr_next_layer_logup_singles.restype = None
+        L.gkr_next_layer_logup_singles.argtypes = [vp, vp, vp, u32]
+        L.gkr_sum_grand_product.restype = None
+        L.gkr_sum_grand_product.argtypes = [vp, vp, u32, vp, u32]
+        L.gkr_sum_logup_generic.restype = None
+        L.gkr_sum_logup_generic.argtypes = [vp, vp, vp, _Q, u32, vp, u32]
+        L.gkr_sum_logup_multiplicities.restype = None
+        L.gkr_sum_logup_multiplicities.argtypes = [vp, vp, vp, _Q, u32, vp, u32]
+        L.gkr_sum_logup_singles.restype = None
+        L.gkr_sum_logup_singles.argtypes = [vp, vp, _Q, u32, vp, u32]
+        L.fix_first_variable_base_field.restype = None
+        L.fix_first_variable_base_field.argtypes = [vp, i32, _Q, vp]
+        L.fix_first_variable_secure_field.restype = None
+        L.fix_first_variable_secure_field.argtypes = [vp, i32, _Q, vp]
+        L.bit_reverse_base_field.restype = None
+        L.bit_reverse_base_field.argtypes = [vp, i32]
+
+    def alloc(self, words):
+        return self.lib.cuda_malloc_uint32_t(words)
+
+    def alloc_zero(self, words):
+        return self.lib.cuda_alloc_zeroes_uint32_t(words)
+
+    # FriOps::fold_line (fri.rs:17-46): the line domain is LineDomain(Coset::half_odds(log_n)); the tree's root
+    # coset is a half_odds coset at least that large.
+    def fold_line(self, in_ptrs, log_n, alpha, tree):
+        n = 1 << log_n
+        out = [self.alloc(n // 2) for _ in range(4)]
+        self.lib.fold_line(tree["itw"], tree["size"] - n, n, _ptrs(in_ptrs), _q(alpha), _ptrs(out))
+        return out
+
+    # FriOps::fold_circle_into_line (fri.rs:48-69): src on CanonicCoset(log_n).circle_domain()
+    def fold_circle_into_line(self, dst_ptrs, src_ptrs, log_n, alpha, tree):
+        n = 1 << log_n
+        self.lib.fold_circle_into_line(tree["itw"], tree["size"] - n // 2, n, _ptrs(src_ptrs), _q(alpha), _ptrs(dst_ptrs))
+
+    # QuotientOps::accumulate_numerators, one sample batch (quotient.rs:38-74)
+    def quot_numerators(self, col_ptrs, log_n, col_idx, b, c):
+        n, k = 1 << log_n, len(col_idx)
+        dcols = self.lib.copy_device_pointer_vec_from_host_to_device(_ptrs(col_ptrs), len(col_ptrs))
+        out = [self.alloc_zero(n) for _ in range(4)]
+        b = np.ascontiguousarray(b, np.uint32)
+        c = np.ascontiguousarray(c, np.uint32)
+        idx = np.ascontiguousarray(col_idx, np.uint32)
+        self.lib.accumulate_numerators_batch(n, dcols, b.ctypes.data, c.ctypes.data, idx.ctypes.data, k, *out)
+        self.sync()
+        self.free(dcols)
+        return out
+
+    # QuotientOps::compute_quotients_and_combine (quotient.rs:84-141)
+    def quot_combine(self, acc_ptrs, acc_logs, first_lin, points, max_log):
+        n = 1 << max_log
+        out = [self.alloc_zero(n) for _ in range(4)]
+        logs = np.ascontiguousarray(acc_logs, np.int32)
+        fl = np.ascontiguousarray(first_lin, np.uint32)
+        pts = np.ascontiguousarray(points, np.uint32)  # per accumulation: x (4 words), y (4 words)
+        flat = [p for acc in acc_ptrs for p in acc]
+        self.lib.compute_quotients_and_combine(n, max_log, 1 << (30 - max_log), (1 << (32 - max_log)) & 0xFFFFFFFF, len(acc_ptrs),
+                                               _ptrs(flat), logs.ctypes.data, fl.ctypes.data, pts.ctypes.data, *out)
+        self.sync()
+        return out
+
+    # GkrOps (lookups/gkr.rs)
+    def gen_eq_evals(self, y, v):
+        y = np.ascontiguousarray(y, np.uint32).reshape(-1, 4)
+        m = y.shape[0]
+        out = self.alloc(4 << m)
+        self.lib.gen_eq_evals(_q(v), y.ctypes.data, m, out, 1 << m)
+        return out
+
+    def next_layer(self, kind, num, den, n):
+        no, do = self.alloc(2 * n), self.alloc(2 * n)
+        if kind == 0:
+            self.lib.gkr_next_layer_grand_product(den, do, n // 2)
+        elif kind == 1:
+            self.lib.gkr_next_layer_logup_generic(num, den, no, do, n // 2)
+        elif kind == 2:
+            self.lib.gkr_next_layer_logup_multiplicities(num, den, no, do, n // 2)
+        else:
+            self.lib.gkr_next_layer_logup_singles(den, no, do, n // 2)
+        return no, do
+
+    def round_sums(self, kind, num, den, n, eq, lam):
+        n_terms = n // 4
+        blocks = max(1, min((n_terms + 255) // 256, 96))
+        part = self.alloc(8 * blocks)
+        if kind == 0:
+            self.lib.gkr_sum_grand_product(den, eq, n_terms, part, blocks)
+        elif kind == 1:
+            self.lib.gkr_sum_logup_generic(num, den, eq, _q(lam), n_terms, part, blocks)
+        elif kind == 2:
+            self.lib.gkr_sum_logup_multiplicities(num, den, eq, _q(lam), n_terms, part, blocks)
+        else:
+            self.lib.gkr_sum_logup_singles(den, eq, _q(lam), n_terms, part, blocks)
+        p = self.download(part, 8 * blocks).reshape(blocks, 2, 4).astype(np.uint64)
+        self.free(part)
+        return (p.sum(axis=0) % np.uint64(P)).astype(np.uint32)
+
+    def fix_first_variable(self, ptr, n, r, base):
+        out = self.alloc(2 * n)
+        (self.lib.fix_first_variable_base_field if base else self.lib.fix_first_variable_secure_field)(ptr, n, _q(r), out)
+        return out
+
+    def bit_reverse(self, ptr, n):
+        self.lib.bit_reverse_base_field(ptr, n)

@@ -76,3 +76,131 @@ def test_merkle_layer_with_columns_and_children_matches_reference_cuda(ctx, ref)
     assert (out.download(shape=(n, 8)) == ref.download_hashes(r_out, n)).all()
     for p in r_cols + [r_prev, r_out]:
         ref.free(p)
+
+
+@pytest.fixture(scope="module")
+def refops():
+    from oracle import ref_cuda
+
+    if not ref_cuda.available():
+        pytest.skip("oracle/_ref/libstwo_cuda_ref.so is not built (the reference checkout is needed to build it)")
+    return ref_cuda.RefCudaOps()
+
+
+def _secure(seed, n):
+    return [edge_m31_column(seed + k, n) for k in range(4)]
+
+
+# From 8 points up: on a 4-point circle domain the reference's CUDA fold takes its y twiddle from the pad word of
+# the twiddle slice (stwo_cuda/cuda/poly_utils.cuh:7-18 on a slice of 2 words); its FFTs fall back to the CPU
+# below 16 points (backend/cuda/poly.rs:184-196) and FRI never folds a circle that small.
+@pytest.mark.parametrize("log_n", [3, 5, 11, 17])
+def test_fri_folds_match_reference_cuda(ctx, refops, log_n):
+    from util import qm31_array
+
+    n = 1 << log_n
+    alpha = qm31_array(9100 + log_n, 1)[0]
+    tree = refops.twiddle_tree(max(log_n, 5))
+    # fold_line on LineDomain(half_odds(log_n))
+    ev = _secure(9110, n)
+    r_in = [refops.upload(c) for c in ev]
+    r_out = refops.fold_line(r_in, log_n, alpha, tree)
+    bi, bo = [ctx.upload(c) for c in ev], [ctx.alloc(n // 2) for _ in range(4)]
+    ctx.fold_line([b.ptr for b in bo], [b.ptr for b in bi], log_n, alpha)
+    for k in range(4):
+        assert (bo[k].download(n // 2) == refops.download(r_out[k], n // 2)).all()
+    # fold_circle_into_line from CanonicCoset(log_n).circle_domain() into a non-zero destination
+    dst = _secure(9120, n // 2)
+    r_dst = [refops.upload(c) for c in dst]
+    refops.fold_circle_into_line(r_dst, r_in, log_n, alpha, tree)
+    bd = [ctx.upload(c) for c in dst]
+    ctx.fold_circle_into_line([b.ptr for b in bd], [b.ptr for b in bi], log_n, alpha)
+    for k in range(4):
+        assert (bd[k].download(n // 2) == refops.download(r_dst[k], n // 2)).all()
+    for p in r_in + r_out + r_dst + [tree["tw"], tree["itw"]]:
+        refops.free(p)
+
+
+@pytest.mark.parametrize("log_n,k", [(4, 1), (9, 7), (14, 33)])
+def test_quotients_match_reference_cuda(ctx, refops, log_n, k):
+    from util import qm31_array
+
+    n = 1 << log_n
+    ncols = k + 2
+    cols = [edge_m31_column(9200 + c, n) for c in range(ncols)]
+    idx = np.array([(3 * j + 1) % ncols for j in range(k)], np.uint32)
+    b, c = qm31_array(9210, k), qm31_array(9211, k)
+    r_cols = [refops.upload(x) for x in cols]
+    r_acc = refops.quot_numerators(r_cols, log_n, idx, b, c)
+    bufs = [ctx.upload(x) for x in cols]
+    acc = [ctx.alloc(n) for _ in range(4)]
+    ctx.quot_numerators([x.ptr for x in bufs], log_n, idx, b, c, [a.ptr for a in acc])
+    for q in range(4):
+        assert (acc[q].download(n) == refops.download(r_acc[q], n)).all()
+    # combine three accumulations of different sizes (lifting) at distinct sample points
+    logs = [log_n, max(log_n - 2, 1), log_n]
+    accs = [_secure(9220 + 10 * a, 1 << lg) for a, lg in enumerate(logs)]
+    first_lin, points = qm31_array(9250, 3), qm31_array(9251, 6).reshape(3, 8)
+    r_accs = [[refops.upload(x) for x in a] for a in accs]
+    r_out = refops.quot_combine(r_accs, logs, first_lin, points, log_n)
+    g_accs = [[ctx.upload(x) for x in a] for a in accs]
+    out = [ctx.alloc(n) for _ in range(4)]
+    ctx.quot_combine([x.ptr for a in g_accs for x in a], logs, first_lin, points, log_n, [o.ptr for o in out])
+    for q in range(4):
+        assert (out[q].download(n) == refops.download(r_out[q], n)).all()
+    for p in r_cols + r_acc + r_out + [x for a in r_accs for x in a]:
+        refops.free(p)
+
+
+@pytest.mark.parametrize("kind", [0, 1, 2, 3])
+@pytest.mark.parametrize("log_n", [3, 10, 15])
+def test_gkr_ops_match_reference_cuda(ctx, refops, kind, log_n):
+    from util import qm31_array
+
+    n = 1 << log_n
+    den = qm31_array(9300 + kind, n, nonzero=True)
+    num = qm31_array(9310 + kind, n) if kind == 1 else m31_column(9310 + kind, n) if kind == 2 else None
+    lam, r = qm31_array(9320, 1)[0], qm31_array(9321, 1)[0]
+    y = qm31_array(9322, log_n - 2)
+    r_den, r_num = refops.upload(den), (refops.upload(num) if num is not None else None)
+    g_den, g_num = ctx.upload(den), (ctx.upload(num) if num is not None else None)
+    # gen_eq_evals
+    r_eq = refops.gen_eq_evals(y, lam)
+    g_eq = ctx.alloc(n)
+    ctx.gkr_eq_evals(y, lam, g_eq.ptr)
+    assert (g_eq.download(n) == refops.download(r_eq, n)).all()
+    # next_layer
+    r_no, r_do = refops.next_layer(kind, r_num, r_den, n)
+    g_no, g_do = ctx.alloc(2 * n), ctx.alloc(2 * n)
+    ctx.gkr_next_layer(kind, g_num.ptr if g_num else 0, g_den.ptr, n, g_no.ptr, g_do.ptr)
+    assert (g_do.download(2 * n) == refops.download(r_do, 2 * n)).all()
+    if kind != 0:
+        assert (g_no.download(2 * n) == refops.download(r_no, 2 * n)).all()
+    # sum_as_poly_in_first_variable: the sums at t = 0 and t = 2
+    want = refops.round_sums(kind, r_num, r_den, n, r_eq, lam)
+    got = ctx.gkr_sum(kind, g_num.ptr if g_num else 0, g_den.ptr, n, g_eq.ptr, lam)
+    assert (got == want).all()
+    # fix_first_variable on the denominators (QM31) and, for multiplicities, the M31 numerators
+    r_fx = refops.fix_first_variable(r_den, n, r, base=False)
+    g_fx = ctx.alloc(2 * n)
+    ctx.mle_fix_qm31(g_den.ptr, n, r, g_fx.ptr)
+    assert (g_fx.download(2 * n) == refops.download(r_fx, 2 * n)).all()
+    if kind == 2:
+        r_fb = refops.fix_first_variable(r_num, n, r, base=True)
+        ctx.mle_fix_m31(g_num.ptr, n, r, g_fx.ptr)
+        assert (g_fx.download(2 * n) == refops.download(r_fb, 2 * n)).all()
+        refops.free(r_fb)
+    for p in [r_den, r_eq, r_no, r_do, r_fx] + ([r_num] if r_num else []):
+        refops.free(p)
+
+
+@pytest.mark.parametrize("log_n", [4, 12, 20])
+def test_bit_reverse_matches_reference_cuda(ctx, refops, log_n):
+    n = 1 << log_n
+    v = m31_column(9400 + log_n, n)
+    r = refops.upload(v)
+    refops.bit_reverse(r, n)
+    b = ctx.upload(v)
+    ctx.bit_reverse_m31(b.ptr, log_n)
+    assert (b.download(n) == refops.download(r, n)).all()
+    refops.free(r)
