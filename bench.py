@@ -165,6 +165,52 @@ def run_reference(args, rank):
     print(json.dumps(line))
 
 
+def reference_gpu_leg(args):
+    """Same-box GPU baseline: the reference's own CUDA kernels (compiled unmodified for sm_100a by
+    oracle/Makefile.ref_cuda) on the commitment part of the workload: interpolate_columns, evaluate_polynomials
+    (zero-extended copy + transform, as backend/cuda/poly.rs does) and the Merkle tree layer by layer. Timed with
+    the host clock around device synchronisations (the library works on the default stream)."""
+    from oracle import ref_cuda
+
+    if not ref_cuda.available():
+        return None
+    ref = ref_cuda.RefCuda()
+    log_n, log_out, ncols = args.log_size, args.log_size + args.log_blowup, args.cols
+    n = 1 << log_n
+    tree = ref.twiddle_tree(log_out - 1)
+    src = [ref.upload(splitmix_column(SEED0 + c, n)) for c in range(ncols)]
+    work = [ref.lib.cuda_malloc_uint32_t(n) for _ in range(ncols)]
+    t = {"interpolate": [], "extend": [], "merkle": []}
+    for it in range(3):
+        for a, b in zip(src, work):
+            ref.lib.copy_uint32_t_vec_from_device_to_device(a, b, n)
+        ref.sync()
+        t0 = time.perf_counter()
+        ref.interpolate_columns(work, log_n, tree)
+        ref.sync()
+        t1 = time.perf_counter()
+        ext = ref.extend_columns(work, log_n, log_out)
+        ref.evaluate_extended(ext, log_out, tree)
+        ref.sync()
+        t2 = time.perf_counter()
+        layers = [ref.commit_on_layer(log_out, None, ext)]
+        for lg in range(log_out - 1, -1, -1):
+            layers.append(ref.commit_on_layer(lg, layers[-1], []))
+        ref.sync()
+        t3 = time.perf_counter()
+        for p in ext + layers:
+            ref.free(p)
+        if it:  # the first pass warms up
+            t["interpolate"].append(t1 - t0)
+            t["extend"].append(t2 - t1)
+            t["merkle"].append(t3 - t2)
+    for p in src + work + [tree["tw"], tree["itw"]]:
+        ref.free(p)
+    ms = {k: 1e3 * float(np.mean(v)) for k, v in t.items()}
+    return {"kind": "the reference's CUDA kernels for this path, compiled unmodified for sm_100a, same GPU", "ms": ms,
+            "commit_ms": sum(ms.values()), "cells_per_s_commit_only": ncols * n / (sum(ms.values()) * 1e-3)}
+
+
 def golden_check(name, words):
     """Compares a proof with the committed digest of the CPU oracle's proof of the same seeded workload."""
     import hashlib
@@ -323,6 +369,14 @@ def run_ours(args, rank, world, local_rank):
             cpu = {"value": v, "unit": "cells/s", "cores": threads, "kind": "port",
                    "sample": f"{sample_cols} of {ncols} columns at full height 2^{log_n} ({dt:.1f} s of CPU work): the same commit + prove flow"}
         launches = sum(v[1] for v in kernels.values())
+        gpu_ref = None
+        if world == 1 and not args.no_gpu_baseline:
+            try:
+                gpu_ref = reference_gpu_leg(args)
+                if gpu_ref:
+                    gpu_ref["ours_commit_ms"] = per["interpolate"] + per["extend"] + per["merkle"]
+            except Exception as e:  # the baseline must never cost the bench line
+                gpu_ref = {"unavailable": repr(e)}
         import hashlib
 
         line = {
@@ -332,7 +386,7 @@ def run_ours(args, rank, world, local_rank):
             "e2e": {"value": e2e_value, "unit": "cells/s", "h2d_bytes_per_step": ncols * n * 4, "d2h_bytes_per_step": int(len(words_dev)) * 4,
                     "ms_per_step": e2e_ms / args.steps},
             "gpu_launches": launches * args.steps,
-            "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks,
+            "roofline": roofline, "cpu_baseline": cpu, "gpu_baseline": gpu_ref, "clocks": clocks,
             "proof_words": int(len(words_dev)), "proof_sha256": hashlib.sha256(words_dev.tobytes()).hexdigest(),
             "parity": golden_check(f"pcs_{ncols}x2e{log_n}_blowup{1 << args.log_blowup}", words_dev)
             if (args.pow_bits, args.n_queries) == (10, 3) else None,
@@ -508,6 +562,7 @@ def main():
     ap.add_argument("--n-queries", type=int, default=3)
     ap.add_argument("--ref-cols", type=int, default=32, help="columns in the bounded CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-gpu-baseline", action="store_true")
     ap.add_argument("--gkr-log", type=int, default=24)
     ap.add_argument("--mode", default="proof", choices=["proof", "sharded-commit", "gkr", "freivalds"],
                     help="proof: one whole PCS proof per rank (ranks are independent); sharded-commit: one commitment over all ranks")
