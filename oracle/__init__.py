@@ -1,7 +1,13 @@
 """TEST INFRASTRUCTURE ONLY: ctypes bindings over the CPU oracle (oracle/capi.cpp).
 
-Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline legs may import this package.
+Only tests/, __graft_entry__.smoke() and bench.py's baseline legs may import this package.
 The product package never does.
+
+Pinning: the restatement is checked against the reference's own known-answer vectors (tests/test_oracle_kats.py)
+and, operator by operator on a GPU, against the reference's own CUDA backend compiled out of tree
+(oracle/Makefile.ref_cuda, oracle/ref_cuda.py, tests/test_gpu_reference_cuda.py). The protocol layer above the
+operators has no reference output to compare with here (the reference's provers are Rust): parity of that layer
+is unpinned.
 """
 import ctypes as C
 import os
