@@ -147,6 +147,15 @@ int zkb_merkle_top(zkb_ctx* ctx, int top_log, const uint32_t* top_layer, uint32_
  * entries) is updated as dst*alpha^2 + f0 + alpha*f1. */
 int zkb_fold_circle_into_line(zkb_ctx* ctx, uint32_t* const dst[4], const uint32_t* const src[4], int log_n_src,
                               const uint32_t h_alpha[4]);
+/* The same folds with the challenge read from device memory (4 words, 16-byte aligned), and the channel step that
+ * produces it: d_chan = {digest[8], n_draws} of a Blake2sM31Channel (core/channel/blake2s.rs:20-141); the kernel does
+ * mix_root(root) then draw_secure_felt(), leaves the new state in d_chan, the challenge in d_alpha and, if d_root_copy
+ * is not NULL, a copy of the root there. With these, FriProver::commit (prover/fri.rs:109-221) enqueues every layer's
+ * commit, channel step and fold without returning to the host; the host reads the roots and the channel once at the end. */
+int zkb_fold_line_dalpha(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* const in[4], int log_n, const uint32_t* d_alpha);
+int zkb_fold_circle_into_line_dalpha(zkb_ctx* ctx, uint32_t* const dst[4], const uint32_t* const src[4], int log_n_src,
+                                     const uint32_t* d_alpha);
+int zkb_channel_mix_root_draw(zkb_ctx* ctx, uint32_t* d_chan, const uint32_t* d_root, uint32_t* d_alpha, uint32_t* d_root_copy);
 /* fold_line with fold_step 1: in on the line domain Coset::half_odds(log_n); out has 2^(log_n-1). */
 int zkb_fold_line(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* const in[4], int log_n,
                   const uint32_t h_alpha[4]);

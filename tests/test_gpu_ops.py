@@ -377,3 +377,41 @@ def test_merkle_leaves_in_runs_of_columns(ctx, oracle, zkb, log_size, runs, m31)
     # a run that is not the last one must hold whole blocks
     with pytest.raises(zkb.ZkbError):
         ctx.merkle_leaves_partial(log_size, [bufs[0].ptr], 0, total + 1, out.ptr)
+
+
+def test_device_channel_step_and_folds_with_device_challenge(ctx, oracle):
+    # Three chained steps of mix_root + draw_secure_felt on the device against the oracle's channel, then both
+    # folds with the challenge read from device memory against the by-value folds.
+    ch = oracle.Channel()
+    ch.mix_u64(0xC0FFEE)
+    ch.draw_secure_felt()                      # a channel that has already drawn (n_draws = 1)
+    state = np.zeros(16, np.uint32)
+    state[:8] = np.frombuffer(ch.digest(), np.uint32)
+    state[8] = 1
+    d_chan = ctx.upload(state)
+    d_alpha, d_copy = ctx.alloc(4 * 3), ctx.alloc(8 * 3)
+    alphas = []
+    for k in range(3):
+        root = m31_column(2200 + k, 8)
+        d_root = ctx.upload(root)
+        ctx.channel_mix_root_draw(d_chan.ptr, d_root.ptr, d_alpha.ptr + 16 * k, d_copy.ptr + 32 * k)
+        ch.mix_root(root)
+        alphas.append(ch.draw_secure_felt())
+        assert (d_copy.download(shape=(3, 8))[k] == root).all()
+    got = d_alpha.download(shape=(3, 4))
+    assert (got == np.array(alphas, np.uint32)).all()
+    st = d_chan.download(16)
+    assert (st[:8] == np.frombuffer(ch.digest(), np.uint32)).all() and st[8] == 1
+    for log_n in (1, 2, 3, 9):
+        n = 1 << log_n
+        ev = np.stack([edge_m31_column(2210 + k, n) for k in range(4)])
+        bi = [ctx.upload(c) for c in ev]
+        o1, o2 = [ctx.alloc(n // 2) for _ in range(4)], [ctx.alloc(n // 2) for _ in range(4)]
+        ctx.fold_line([b.ptr for b in o1], [b.ptr for b in bi], log_n, alphas[1])
+        ctx.fold_line_dalpha([b.ptr for b in o2], [b.ptr for b in bi], log_n, d_alpha.ptr + 16)
+        assert all((a.download() == b.download()).all() for a, b in zip(o1, o2))
+        dst = np.stack([edge_m31_column(2220 + k, n // 2) for k in range(4)])
+        c1, c2 = [ctx.upload(c) for c in dst], [ctx.upload(c) for c in dst]
+        ctx.fold_circle_into_line([b.ptr for b in c1], [b.ptr for b in bi], log_n, alphas[2])
+        ctx.fold_circle_into_line_dalpha([b.ptr for b in c2], [b.ptr for b in bi], log_n, d_alpha.ptr + 32)
+        assert all((a.download() == b.download()).all() for a, b in zip(c1, c2))

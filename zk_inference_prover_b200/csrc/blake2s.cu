@@ -187,6 +187,48 @@ __global__ void __launch_bounds__(512) merkle_top_kernel(MerkleTopArgs a, int to
     }
 }
 
+// Blake2sM31Channel on the device, for protocol loops whose next launch only needs a challenge
+// (FRI: mix the layer's root, draw the folding challenge). State: chan[0..8) = digest, chan[8] = n_draws.
+// mix_root is H(digest || root) (core/vcs/blake2_merkle.rs:53-58); draw_secure_felt hashes
+// digest || n_draws (LE) || 0x00 and retries while a word is >= 2p (core/channel/blake2s.rs:34-52,
+// 95-120); every digest word is reduced mod p.
+__global__ void channel_mix_root_draw_kernel(uint32_t* __restrict__ chan, const uint32_t* __restrict__ root,
+                                             uint32_t* __restrict__ alpha_out, uint32_t* __restrict__ root_copy) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    uint32_t h[8], m[16];
+    blake2s_init(h);
+#pragma unroll
+    for (int k = 0; k < 8; k++) { m[k] = chan[k]; m[8 + k] = root[k]; }
+    blake2s_compress(h, m, 64u, true);
+    uint32_t digest[8];
+#pragma unroll
+    for (int k = 0; k < 8; k++) digest[k] = reduce_word_m31(h[k]);
+    uint32_t n_draws = 0, u[8];
+    for (int attempt = 0; attempt < 64; attempt++) {  // the words are already below p: one pass in practice
+        blake2s_init(h);
+#pragma unroll
+        for (int k = 0; k < 8; k++) m[k] = digest[k];
+        m[8] = n_draws;
+#pragma unroll
+        for (int k = 9; k < 16; k++) m[k] = 0u;
+        blake2s_compress(h, m, 37u, true);
+        n_draws++;
+        bool ok = true;
+#pragma unroll
+        for (int k = 0; k < 8; k++) { u[k] = reduce_word_m31(h[k]); ok = ok && u[k] < 2u * P; }
+        if (ok) break;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; k++) chan[k] = digest[k];
+    chan[8] = n_draws;
+#pragma unroll
+    for (int k = 0; k < 4; k++) alpha_out[k] = u[k] >= P ? u[k] - P : u[k];
+    if (root_copy) {
+#pragma unroll
+        for (int k = 0; k < 8; k++) root_copy[k] = root[k];
+    }
+}
+
 // Grind: thread `lo` tests nonce (hi << 32) | lo; the minimum passing lo is kept.
 __global__ void grind_kernel(uint32_t d0, uint32_t d1, uint32_t d2, uint32_t d3, uint32_t d4, uint32_t d5, uint32_t d6,
                              uint32_t d7, uint32_t hi, int pow_bits, int m31_out, unsigned int* __restrict__ best) {
@@ -261,6 +303,16 @@ int zkb_merkle_top(zkb_ctx* ctx, int top_log, const uint32_t* top_layer, uint32_
     DeviceGuard g(ctx);
     ProfScope prof(ctx, "merkle_top_kernel");
     merkle_top_kernel<<<1, top_log >= 10 ? 512 : (top_log >= 6 ? 1 << (top_log - 1) : 32), 0, ctx->stream>>>(a, top_log, m31_out);
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
+}
+
+int zkb_channel_mix_root_draw(zkb_ctx* ctx, uint32_t* d_chan, const uint32_t* d_root, uint32_t* d_alpha, uint32_t* d_root_copy) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, d_chan != nullptr && d_root != nullptr && d_alpha != nullptr);
+    DeviceGuard g(ctx);
+    ProfScope prof(ctx, "channel_mix_root_draw_kernel");
+    channel_mix_root_draw_kernel<<<1, 32, 0, ctx->stream>>>(d_chan, d_root, d_alpha, d_root_copy);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }

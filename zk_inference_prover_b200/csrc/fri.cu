@@ -26,8 +26,19 @@ __device__ __forceinline__ qm31 fold_pair(const Secure4C& in, size_t i, uint32_t
     return qm31_add(f0, qm31_mul(alpha, f1));
 }
 
+// The folding challenge comes by value or, when d_alpha is given, from device memory (written by the
+// channel kernel of the previous step, so that a whole FRI commit phase runs without a host round trip).
+__device__ __forceinline__ qm31 load_alpha(const uint32_t* __restrict__ d_alpha, qm31 alpha) {
+    if (d_alpha) {
+        uint4 v = *reinterpret_cast<const uint4*>(d_alpha);
+        return qm31{{v.x, v.y, v.z, v.w}};
+    }
+    return alpha;
+}
+
 __global__ void __launch_bounds__(256) fold_line_kernel(Secure4 out, Secure4C in, int log_n, qm31 alpha,
-                                                        const uint32_t* __restrict__ itw) {
+                                                        const uint32_t* __restrict__ d_alpha, const uint32_t* __restrict__ itw) {
+    alpha = load_alpha(d_alpha, alpha);
     size_t half = (size_t)1 << (log_n - 1);
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= half) return;
@@ -39,8 +50,10 @@ __global__ void __launch_bounds__(256) fold_line_kernel(Secure4 out, Secure4C in
 
 // log_n == 1, 2 of the line fold and small circle domains need points that are not in the tower
 // (T_k holds only half of each coset and starts at k = 1); they are passed in by the host.
-__global__ void fold_small_kernel(Secure4 out, Secure4C in, int n_out, qm31 alpha, qm31 alpha_sq, int accumulate,
-                                  uint32_t it0, uint32_t it1, uint32_t it2, uint32_t it3) {
+__global__ void fold_small_kernel(Secure4 out, Secure4C in, int n_out, qm31 alpha, const uint32_t* __restrict__ d_alpha,
+                                  int accumulate, uint32_t it0, uint32_t it1, uint32_t it2, uint32_t it3) {
+    alpha = load_alpha(d_alpha, alpha);
+    const qm31 alpha_sq = qm31_sqr(alpha);
     int i = threadIdx.x;
     if (i >= n_out) return;
     uint32_t its[4] = {it0, it1, it2, it3};
@@ -54,7 +67,9 @@ __global__ void fold_small_kernel(Secure4 out, Secure4C in, int n_out, qm31 alph
 }
 
 __global__ void __launch_bounds__(256) fold_circle_kernel(Secure4 dst, Secure4C src, int log_n_src, qm31 alpha,
-                                                          qm31 alpha_sq, const uint32_t* __restrict__ itw) {
+                                                          const uint32_t* __restrict__ d_alpha, const uint32_t* __restrict__ itw) {
+    alpha = load_alpha(d_alpha, alpha);
+    const qm31 alpha_sq = qm31_sqr(alpha);
     size_t half = (size_t)1 << (log_n_src - 1);
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= half) return;
@@ -86,12 +101,11 @@ static uint32_t host_bitrev(uint32_t i, int bits) {
     return r;
 }
 
-extern "C" {
-
-int zkb_fold_line(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* const in[4], int log_n,
-                  const uint32_t h_alpha[4]) {
+static int fold_line_impl(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* const in[4], int log_n,
+                          const uint32_t* h_alpha, const uint32_t* d_alpha) {
     if (!ctx) return ZKB_EINVAL;
-    ZKB_CHECK_ARG(ctx, out && in && h_alpha && log_n >= 1 && log_n <= ctx->max_log - 1);
+    ZKB_CHECK_ARG(ctx, out && in && (h_alpha || d_alpha) && log_n >= 1 && log_n <= ctx->max_log - 1);
+    ZKB_CHECK_ARG(ctx, ((uintptr_t)d_alpha & 15) == 0);
     Secure4 o;
     Secure4C s;
     for (int k = 0; k < 4; k++) {
@@ -99,19 +113,21 @@ int zkb_fold_line(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* const in
         o.c[k] = out[k];
         s.c[k] = in[k];
     }
-    qm31 alpha{{h_alpha[0], h_alpha[1], h_alpha[2], h_alpha[3]}};
+    qm31 alpha = qm31_zero();
+    if (h_alpha) alpha = qm31{{h_alpha[0], h_alpha[1], h_alpha[2], h_alpha[3]}};
     DeviceGuard g(ctx);
     size_t half = (size_t)1 << (log_n - 1);
     ProfScope prof(ctx, "fold_line_kernel");
-    fold_line_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n, alpha, ctx->itw);
+    fold_line_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n, alpha, d_alpha, ctx->itw);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }
 
-int zkb_fold_circle_into_line(zkb_ctx* ctx, uint32_t* const dst[4], const uint32_t* const src[4], int log_n_src,
-                              const uint32_t h_alpha[4]) {
+static int fold_circle_impl(zkb_ctx* ctx, uint32_t* const dst[4], const uint32_t* const src[4], int log_n_src,
+                            const uint32_t* h_alpha, const uint32_t* d_alpha) {
     if (!ctx) return ZKB_EINVAL;
-    ZKB_CHECK_ARG(ctx, dst && src && h_alpha && log_n_src >= 1 && log_n_src <= ctx->max_log);
+    ZKB_CHECK_ARG(ctx, dst && src && (h_alpha || d_alpha) && log_n_src >= 1 && log_n_src <= ctx->max_log);
+    ZKB_CHECK_ARG(ctx, ((uintptr_t)d_alpha & 15) == 0);
     Secure4 o;
     Secure4C s;
     for (int k = 0; k < 4; k++) {
@@ -119,8 +135,8 @@ int zkb_fold_circle_into_line(zkb_ctx* ctx, uint32_t* const dst[4], const uint32
         o.c[k] = dst[k];
         s.c[k] = src[k];
     }
-    qm31 alpha{{h_alpha[0], h_alpha[1], h_alpha[2], h_alpha[3]}};
-    qm31 alpha_sq = qm31_sqr(alpha);
+    qm31 alpha = qm31_zero();
+    if (h_alpha) alpha = qm31{{h_alpha[0], h_alpha[1], h_alpha[2], h_alpha[3]}};
     DeviceGuard g(ctx);
     if (log_n_src <= 2) {
         // Points i of Coset::half_odds(log_n_src - 1), bit-reversed: index 2^(31-(L-1)-2) + j * 2^(31-(L-1)).
@@ -131,15 +147,36 @@ int zkb_fold_circle_into_line(zkb_ctx* ctx, uint32_t* const dst[4], const uint32
             cpoint p = host_point(((1u << (29 - hl)) + (j << (31 - hl))) & 0x7fffffffu);
             it[i] = m31_inv(p.y);
         }
-        fold_small_kernel<<<1, 32, 0, ctx->stream>>>(o, s, 1 << hl, alpha, alpha_sq, 1, it[0], it[1], it[2], it[3]);
+        fold_small_kernel<<<1, 32, 0, ctx->stream>>>(o, s, 1 << hl, alpha, d_alpha, 1, it[0], it[1], it[2], it[3]);
         ZKB_LAUNCH_CHECK(ctx);
         return ZKB_OK;
     }
     size_t half = (size_t)1 << (log_n_src - 1);
     ProfScope prof(ctx, "fold_circle_kernel");
-    fold_circle_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n_src, alpha, alpha_sq, ctx->itw);
+    fold_circle_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n_src, alpha, d_alpha, ctx->itw);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
+}
+
+extern "C" {
+
+int zkb_fold_line(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* const in[4], int log_n, const uint32_t h_alpha[4]) {
+    if (ctx && !h_alpha) return zk::set_error(ctx, ZKB_EINVAL, "zkb_fold_line: null alpha");
+    return fold_line_impl(ctx, out, in, log_n, h_alpha, nullptr);
+}
+int zkb_fold_line_dalpha(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* const in[4], int log_n, const uint32_t* d_alpha) {
+    if (ctx && !d_alpha) return zk::set_error(ctx, ZKB_EINVAL, "zkb_fold_line_dalpha: null alpha");
+    return fold_line_impl(ctx, out, in, log_n, nullptr, d_alpha);
+}
+int zkb_fold_circle_into_line(zkb_ctx* ctx, uint32_t* const dst[4], const uint32_t* const src[4], int log_n_src,
+                              const uint32_t h_alpha[4]) {
+    if (ctx && !h_alpha) return zk::set_error(ctx, ZKB_EINVAL, "zkb_fold_circle_into_line: null alpha");
+    return fold_circle_impl(ctx, dst, src, log_n_src, h_alpha, nullptr);
+}
+int zkb_fold_circle_into_line_dalpha(zkb_ctx* ctx, uint32_t* const dst[4], const uint32_t* const src[4], int log_n_src,
+                                     const uint32_t* d_alpha) {
+    if (ctx && !d_alpha) return zk::set_error(ctx, ZKB_EINVAL, "zkb_fold_circle_into_line_dalpha: null alpha");
+    return fold_circle_impl(ctx, dst, src, log_n_src, nullptr, d_alpha);
 }
 
 }  // extern "C"

@@ -230,6 +230,20 @@ struct B200Backend {
         d.check(zkb_fold_line(d.ctx(), o.data(), i.data(), (int)log_n, alpha.c));
         return out;
     }
+    // The same folds with the challenge in device memory (see zkb_channel_mix_root_draw).
+    static SecureColumnByCoords fold_line(const Device& d, const SecureColumnByCoords& eval, const uint32_t* d_alpha) {
+        uint32_t log_n = eval.columns[0].log_size();
+        SecureColumnByCoords out(d, eval.len() / 2);
+        auto o = out.ptrs();
+        auto i = eval.cptrs();
+        d.check(zkb_fold_line_dalpha(d.ctx(), o.data(), i.data(), (int)log_n, d_alpha));
+        return out;
+    }
+    static void fold_circle_into_line(const Device& d, SecureColumnByCoords& dst, const SecureColumnByCoords& src, const uint32_t* d_alpha) {
+        auto o = dst.ptrs();
+        auto i = src.cptrs();
+        d.check(zkb_fold_circle_into_line_dalpha(d.ctx(), o.data(), i.data(), (int)src.columns[0].log_size(), d_alpha));
+    }
     static void fold_circle_into_line(const Device& d, SecureColumnByCoords& dst, const SecureColumnByCoords& src, qm31 alpha) {
         auto o = dst.ptrs();
         auto i = src.cptrs();

@@ -139,6 +139,9 @@ class Channel {
         st.update_words(&n_bits, 1);
         return st.finalize_m31();
     }
+    // The state as a device-resident copy of the channel holds it (digest, n_draws), and back.
+    uint32_t n_draws() const { return n_draws_; }
+    void set_state(const HashWords& d, uint32_t n_draws) { digest_ = d; n_draws_ = n_draws; }
   private:
     void set(const HashWords& d) { digest_ = d; n_draws_ = 0; }
     HashWords digest_{};

@@ -235,29 +235,62 @@ struct FriProver {
         FriProver fp;
         fp.config = config;
         fp.first_column = &column;
-        fp.first_tree = MerkleProver::commit(d, column.refs());
-        ch.mix_root(fp.first_tree.root(d));
         uint32_t first_log = column.columns[0].log_size(), inner_log = first_log - 1;
-        SecureColumnByCoords layer(d, (size_t)1 << inner_log, true);
-        qm31 alpha = ch.draw_secure_felt();
-        B200Backend::fold_circle_into_line(d, layer, column, alpha);
         uint32_t last_log = ilog2(config.last_layer_domain_size());
-        if (inner_log != last_log) {
-            for (;;) {
-                uint32_t cur_log = layer.columns[0].log_size();
-                bool last_fold = !(cur_log > last_log + config.line_fold_step);
-                uint32_t step = last_fold ? cur_log - last_log : config.line_fold_step;
-                Inner in{std::move(layer), {}, step};
+        SecureColumnByCoords layer(d, (size_t)1 << inner_log, true);
+        if (config.line_fold_step == 1) {
+            // Device-resident commit phase: every layer's tree, the channel step (mix the root, draw the
+            // folding challenge) and the fold are enqueued back to back; the host reads all roots and the
+            // channel state once, after the last fold.
+            size_t n_layers = 1 + (inner_log > last_log ? inner_log - last_log : 0);
+            BaseColumn fs(d, 16 + 12 * n_layers);  // [channel 16 | challenges 4 each (16-byte aligned) | roots 8 each]
+            uint32_t* chan = fs.ptr();
+            uint32_t* alphas = fs.ptr() + 16;
+            uint32_t* roots = fs.ptr() + 16 + 4 * n_layers;
+            uint32_t st[16] = {0};
+            for (int k = 0; k < 8; k++) st[k] = ch.digest()[k];
+            st[8] = ch.n_draws();
+            d.check(zkb_h2d(d.ctx(), chan, st, sizeof(st)));
+            fp.first_tree = MerkleProver::commit(d, column.refs());
+            d.check(zkb_channel_mix_root_draw(d.ctx(), chan, fp.first_tree.layers[0].ptr(), alphas, roots));
+            B200Backend::fold_circle_into_line(d, layer, column, alphas);
+            for (size_t k = 1; k < n_layers; k++) {
+                Inner in{std::move(layer), {}, 1};
                 in.tree = MerkleProver::commit(d, in.eval.refs());
-                ch.mix_root(in.tree.root(d));
-                qm31 a = ch.draw_secure_felt();
-                layer = B200Backend::fold_line(d, in.eval, a);
-                for (uint32_t s = 1; s < step; s++) {  // backend/cpu/fri.rs:15-30
-                    a = a * a;
-                    layer = B200Backend::fold_line(d, layer, a);
-                }
+                d.check(zkb_channel_mix_root_draw(d.ctx(), chan, in.tree.layers[0].ptr(), alphas + 4 * k, roots + 8 * k));
+                layer = B200Backend::fold_line(d, in.eval, alphas + 4 * k);
                 fp.inner.push_back(std::move(in));
-                if (last_fold) break;
+            }
+            std::vector<uint32_t> h = fs.to_cpu();  // one copy, one synchronisation
+            HashWords dg;
+            for (int k = 0; k < 8; k++) dg[k] = h[k];
+            ch.set_state(dg, h[8]);
+            auto root_at = [&](size_t k) { Hash r; for (int w = 0; w < 8; w++) r[w] = h[16 + 4 * n_layers + 8 * k + w]; return r; };
+            fp.first_tree.root_cache = root_at(0);
+            fp.first_tree.have_root = true;
+            for (size_t k = 1; k < n_layers; k++) { fp.inner[k - 1].tree.root_cache = root_at(k); fp.inner[k - 1].tree.have_root = true; }
+        } else {
+            fp.first_tree = MerkleProver::commit(d, column.refs());
+            ch.mix_root(fp.first_tree.root(d));
+            qm31 alpha = ch.draw_secure_felt();
+            B200Backend::fold_circle_into_line(d, layer, column, alpha);
+            if (inner_log != last_log) {
+                for (;;) {
+                    uint32_t cur_log = layer.columns[0].log_size();
+                    bool last_fold = !(cur_log > last_log + config.line_fold_step);
+                    uint32_t step = last_fold ? cur_log - last_log : config.line_fold_step;
+                    Inner in{std::move(layer), {}, step};
+                    in.tree = MerkleProver::commit(d, in.eval.refs());
+                    ch.mix_root(in.tree.root(d));
+                    qm31 a = ch.draw_secure_felt();
+                    layer = B200Backend::fold_line(d, in.eval, a);
+                    for (uint32_t s2 = 1; s2 < step; s2++) {  // backend/cpu/fri.rs:15-30
+                        a = a * a;
+                        layer = B200Backend::fold_line(d, layer, a);
+                    }
+                    fp.inner.push_back(std::move(in));
+                    if (last_fold) break;
+                }
             }
         }
         // commit_last_layer, fri.rs:193-221
