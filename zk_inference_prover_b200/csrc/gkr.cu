@@ -58,7 +58,8 @@ template <int KIND>
 __global__ void __launch_bounds__(256) gkr_sum_kernel(const uint32_t* __restrict__ num, const uint32_t* __restrict__ den,
                                                       size_t n_terms, const uint32_t* __restrict__ eq_evals, qm31 lambda,
                                                       uint32_t* __restrict__ partials, unsigned int* __restrict__ ticket,
-                                                      uint32_t* __restrict__ result) {
+                                                      uint32_t* __restrict__ result, const uint32_t* __restrict__ d_lambda = nullptr) {
+    if (d_lambda) lambda = ldq(d_lambda, 0);  // the challenge of a device-resident transcript
     qm31 s0 = qm31_zero(), s2 = qm31_zero();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_terms; i += (size_t)gridDim.x * blockDim.x) {
         qm31 d00 = ldq(den, 2 * i), d01 = ldq(den, 2 * i + 1);
@@ -128,20 +129,53 @@ __global__ void __launch_bounds__(256) gkr_sum_kernel(const uint32_t* __restrict
 
 // out[i] = in[i] + r * (in[i + half] - in[i])
 __global__ void __launch_bounds__(256) mle_fix_qm31_kernel(const uint32_t* __restrict__ in, size_t half, qm31 r,
-                                                           uint32_t* __restrict__ out) {
+                                                           uint32_t* __restrict__ out, const uint32_t* __restrict__ d_r = nullptr) {
+    if (d_r) r = ldq(d_r, 0);
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= half) return;
     qm31 a = ldq(in, i), b = ldq(in, i + half);
     stq(out, i, qm31_add(qm31_mul(r, qm31_sub(b, a)), a));
 }
 __global__ void __launch_bounds__(256) mle_fix_m31_kernel(const uint32_t* __restrict__ in, size_t half, qm31 r,
-                                                          uint32_t* __restrict__ out) {
+                                                          uint32_t* __restrict__ out, const uint32_t* __restrict__ d_r = nullptr) {
+    if (d_r) r = ldq(d_r, 0);
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= half) return;
     uint32_t a = in[i], b = in[i + half];
     qm31 v = qm31_mul_m31(r, m31_sub(b, a));
     v.c[0] = m31_add(v.c[0], a);
     stq(out, i, v);
+}
+
+// Launchers for the device-resident transcript (gkr_resident.cu): challenges come from device memory and the
+// sums stay on the device.
+int gkr_sum_launch(zkb_ctx* ctx, int kind, const uint32_t* num, const uint32_t* den, size_t n, const uint32_t* eq_evals,
+                   const uint32_t* d_lambda, uint32_t* d_result) {
+    size_t n_terms = n / 4;
+    unsigned blocks = (unsigned)((n_terms + 255) / 256);
+    if (blocks > 148u * 8u) blocks = 148u * 8u;
+    uint32_t* partials = ctx->scratch;
+    qm31 z = qm31_zero();
+    ProfScope* prof = new ProfScope(ctx, "gkr_sum_kernel");
+    switch (kind) {
+        case ZKB_GKR_GRAND_PRODUCT: gkr_sum_kernel<0><<<blocks, 256, 0, ctx->stream>>>(num, den, n_terms, eq_evals, z, partials, ctx->ticket, d_result, d_lambda); break;
+        case ZKB_GKR_LOGUP_GENERIC: gkr_sum_kernel<1><<<blocks, 256, 0, ctx->stream>>>(num, den, n_terms, eq_evals, z, partials, ctx->ticket, d_result, d_lambda); break;
+        case ZKB_GKR_LOGUP_MULTIPLICITIES: gkr_sum_kernel<2><<<blocks, 256, 0, ctx->stream>>>(num, den, n_terms, eq_evals, z, partials, ctx->ticket, d_result, d_lambda); break;
+        default: gkr_sum_kernel<3><<<blocks, 256, 0, ctx->stream>>>(num, den, n_terms, eq_evals, z, partials, ctx->ticket, d_result, d_lambda); break;
+    }
+    delete prof;
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
+}
+
+int gkr_mle_fix_launch(zkb_ctx* ctx, bool base, const uint32_t* in, size_t n, const uint32_t* d_r, uint32_t* out) {
+    size_t half = n / 2;
+    unsigned blocks = (unsigned)((half + 255) / 256);
+    ProfScope prof(ctx, base ? "mle_fix_m31_kernel" : "mle_fix_qm31_kernel");
+    if (base) mle_fix_m31_kernel<<<blocks, 256, 0, ctx->stream>>>(in, half, qm31_zero(), out, d_r);
+    else mle_fix_qm31_kernel<<<blocks, 256, 0, ctx->stream>>>(in, half, qm31_zero(), out, d_r);
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
 }
 
 }  // namespace zk

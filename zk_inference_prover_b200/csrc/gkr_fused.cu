@@ -38,7 +38,11 @@ template <int KIND>
 __global__ void __launch_bounds__(256) fold_sum_kernel(const uint32_t* __restrict__ num, const uint32_t* __restrict__ den, size_t n, qm31 r,
                                                        const uint32_t* __restrict__ eq_evals, qm31 lambda, uint32_t* __restrict__ num_out,
                                                        uint32_t* __restrict__ den_out, uint32_t* __restrict__ partials,
-                                                       unsigned int* __restrict__ ticket, uint32_t* __restrict__ result) {
+                                                       unsigned int* __restrict__ ticket, uint32_t* __restrict__ result,
+                                                       const uint32_t* __restrict__ d_r = nullptr,
+                                                       const uint32_t* __restrict__ d_lambda = nullptr) {
+    if (d_r) r = ldq2(d_r, 0);  // challenges of a device-resident transcript
+    if (d_lambda) lambda = ldq2(d_lambda, 0);
     const size_t half = n / 2, nt = half / 4;
     qm31 s0 = qm31_zero(), s2 = qm31_zero();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nt; i += (size_t)gridDim.x * blockDim.x) {
@@ -113,8 +117,16 @@ __global__ void __launch_bounds__(256) fold_sum_kernel(const uint32_t* __restric
 
 // table[x] = v * prod_k (bit k of x ? y_k : 1 - y_k), x < 2^m, m <= 11; ys[k] pairs with bit k. One CTA.
 struct EqYs { qm31 y[12]; };
-__global__ void __launch_bounds__(1024) eq_table_kernel(EqYs ys, int m, qm31 v, uint32_t* __restrict__ out) {
+// With d_y, the variables come from device memory instead: step k uses d_y[ny - 1 - (first_bit + k)], and the
+// scale is d_v (or one when d_v is null and use_one is set).
+__global__ void __launch_bounds__(1024) eq_table_kernel(EqYs ys, int m, qm31 v, uint32_t* __restrict__ out,
+                                                        const uint32_t* __restrict__ d_y = nullptr, int ny = 0, int first_bit = 0,
+                                                        const uint32_t* __restrict__ d_v = nullptr) {
     __shared__ uint32_t s[4][2048];
+    if (d_y) {
+        for (int k = 0; k < m; k++) ys.y[k] = ldq2(d_y, ny - 1 - (first_bit + k));
+        if (d_v) v = ldq2(d_v, 0);
+    }
     if (threadIdx.x == 0) { s[0][0] = v.c[0]; s[1][0] = v.c[1]; s[2][0] = v.c[2]; s[3][0] = v.c[3]; }
     __syncthreads();
     // step k of the doubling appends index bit k
@@ -140,6 +152,54 @@ __global__ void __launch_bounds__(256) eq_product_kernel(const uint32_t* __restr
     size_t x = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (x >= n) return;
     stq2(out, x, qm31_mul(ldq2(A, x & (((size_t)1 << a) - 1)), ldq2(B, x >> a)));
+}
+
+int gkr_eq_evals_launch(zkb_ctx* ctx, const uint32_t* d_y, int ny, const uint32_t* d_v, uint32_t* out) {
+    EqYs ys;
+    memset(&ys, 0, sizeof(ys));
+    auto table = [&](int first_bit, int bits, const uint32_t* dv, qm31 v, uint32_t* dst) {
+        ProfScope prof(ctx, "eq_table_kernel");
+        eq_table_kernel<<<1, bits >= 10 ? 1024 : (bits >= 5 ? 1 << bits : 32), 0, ctx->stream>>>(ys, bits, v, dst, d_y ? d_y : out, ny,
+                                                                                                  first_bit, dv);
+    };
+    if (ny <= 11) {
+        table(0, ny, d_v, qm31_one(), out);
+        ZKB_LAUNCH_CHECK(ctx);
+        return ZKB_OK;
+    }
+    if (ny > 22) return set_error(ctx, ZKB_EINVAL, "gkr_eq_evals: more than 22 variables");
+    const int a = 11, b = ny - 11;
+    uint32_t* A = ctx->scratch;
+    uint32_t* B = ctx->scratch + (4u << 11);
+    table(0, a, d_v, qm31_one(), A);
+    table(a, b, nullptr, qm31_one(), B);
+    size_t n = (size_t)1 << ny;
+    {
+        ProfScope prof(ctx, "eq_product_kernel");
+        eq_product_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(A, B, a, n, out);
+    }
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
+}
+
+int gkr_fold_sum_launch(zkb_ctx* ctx, int kind, const uint32_t* num, const uint32_t* den, size_t n, const uint32_t* d_r,
+                        const uint32_t* eq_evals, const uint32_t* d_lambda, uint32_t* num_out, uint32_t* den_out, uint32_t* d_result) {
+    const size_t nt = n / 8;
+    unsigned blocks = (unsigned)((nt + 255) / 256);
+    if (blocks > 148u * 8u) blocks = 148u * 8u;
+    uint32_t* partials = ctx->scratch + (8u << 11);  // clear of the two eq tables
+    qm31 z = qm31_zero();
+    {
+        ProfScope prof(ctx, "fold_sum_kernel");
+        switch (kind) {
+            case ZKB_GKR_GRAND_PRODUCT: fold_sum_kernel<0><<<blocks, 256, 0, ctx->stream>>>(num, den, n, z, eq_evals, z, num_out, den_out, partials, ctx->ticket, d_result, d_r, d_lambda); break;
+            case ZKB_GKR_LOGUP_GENERIC: fold_sum_kernel<1><<<blocks, 256, 0, ctx->stream>>>(num, den, n, z, eq_evals, z, num_out, den_out, partials, ctx->ticket, d_result, d_r, d_lambda); break;
+            case ZKB_GKR_LOGUP_MULTIPLICITIES: fold_sum_kernel<2><<<blocks, 256, 0, ctx->stream>>>(num, den, n, z, eq_evals, z, num_out, den_out, partials, ctx->ticket, d_result, d_r, d_lambda); break;
+            default: fold_sum_kernel<3><<<blocks, 256, 0, ctx->stream>>>(num, den, n, z, eq_evals, z, num_out, den_out, partials, ctx->ticket, d_result, d_r, d_lambda); break;
+        }
+    }
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
 }
 
 }  // namespace zk

@@ -11,6 +11,7 @@
 
 #include "../../../include/zkb200_prover.h"
 #include "b200_backend.hpp"
+#include "../gkr_resident.hpp"
 #include "channel.hpp"
 
 // Records a message on the context (defined with the context, ctx.cu).
@@ -1009,7 +1010,19 @@ int zkb_gkr_prove_device(zkb_ctx* ctx, int n_inst, const int* kinds, const uint3
         }
         Channel ch;
         ch.mix_u64(seed);
-        std::vector<uint32_t> w = gkr_prove_batch(dev, ch, std::move(layers));
+        std::vector<uint32_t> w;
+        if (gkr_resident_supported(n_inst, ns)) {
+            // the transcript stays on the device: no host round trip per sum-check round
+            uint32_t dg[8], nd = ch.n_draws();
+            for (int k = 0; k < 8; k++) dg[k] = ch.digest()[k];
+            int rc = gkr_prove_resident(ctx, std::move(layers), dg, &nd, w);
+            if (rc) return rc;
+            HashWords hw;
+            for (int k = 0; k < 8; k++) hw[k] = dg[k];
+            ch.set_state(hw, nd);
+        } else {
+            w = gkr_prove_batch(dev, ch, std::move(layers));
+        }
         w.insert(w.end(), ch.digest().begin(), ch.digest().end());
         *n_words = w.size();
         if (w.size() > cap) return zk_set_error_public(ctx, ZKB_EINVAL, "zkb_gkr_prove: output buffer too small");
