@@ -44,36 +44,86 @@ struct ResState {
 };
 
 // ---- channel (core/channel/blake2s.rs:58-120 with the M31 reduction of every digest word)
-__device__ void chan_mix_words(ResState* st, const uint32_t* w, int n) {
-    uint32_t h[8], m[16];
+// The transcript steps are executed by one whole warp. Scalar work is done redundantly by every lane (free
+// under SIMT); the Blake2s compression is spread over four lanes, one column / diagonal G function each
+// (RFC 7693 section 3.2), which shortens its dependency chain fourfold. The message block sits in shared
+// memory so that a lane can pick the two words its G function needs in a round.
+__constant__ uint8_t c_sigma[10][16] = {
+    {0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15}, {14, 10, 4, 8, 9, 15, 13, 6, 1, 12, 0, 2, 11, 7, 5, 3},
+    {11, 8, 12, 0, 5, 2, 15, 13, 10, 14, 3, 6, 7, 1, 9, 4}, {7, 9, 3, 1, 13, 12, 11, 14, 2, 6, 5, 10, 4, 0, 15, 8},
+    {9, 0, 5, 7, 2, 4, 10, 15, 14, 1, 11, 12, 6, 8, 3, 13}, {2, 12, 6, 10, 0, 11, 8, 3, 4, 13, 7, 5, 15, 14, 1, 9},
+    {12, 5, 1, 15, 14, 13, 4, 10, 0, 7, 6, 3, 9, 2, 8, 11}, {13, 11, 7, 14, 12, 1, 3, 9, 5, 0, 15, 4, 8, 6, 2, 10},
+    {6, 15, 14, 9, 11, 3, 0, 8, 12, 2, 13, 7, 1, 4, 10, 5}, {10, 2, 8, 4, 7, 6, 1, 5, 15, 11, 9, 14, 3, 12, 13, 0}};
+
+struct Chan { uint32_t digest[8]; uint32_t n_draws; };
+
+// Warp-collective. h: chaining value (same in every lane); m: 16 message words in shared memory.
+__device__ void b2s_compress_warp(uint32_t h[8], const uint32_t* m, uint32_t t, bool last) {
+    const int l = threadIdx.x & 3;
+    const uint32_t iv[8] = {B2S_IV0, B2S_IV1, B2S_IV2, B2S_IV3, B2S_IV4, B2S_IV5, B2S_IV6, B2S_IV7};
+    uint32_t a = h[l], b = h[4 + l], c = iv[l], d = iv[4 + l];
+    if (l == 0) d ^= t;
+    if (l == 2 && last) d = ~d;
+    for (int r = 0; r < 10; r++) {
+        uint32_t x = m[c_sigma[r][2 * l]], y = m[c_sigma[r][2 * l + 1]];
+        B2S_G(a, b, c, d, x, y);
+        b = __shfl_sync(0xffffffffu, b, (l + 1) & 3, 4);
+        c = __shfl_sync(0xffffffffu, c, (l + 2) & 3, 4);
+        d = __shfl_sync(0xffffffffu, d, (l + 3) & 3, 4);
+        x = m[c_sigma[r][8 + 2 * l]];
+        y = m[c_sigma[r][8 + 2 * l + 1]];
+        B2S_G(a, b, c, d, x, y);
+        b = __shfl_sync(0xffffffffu, b, (l + 3) & 3, 4);
+        c = __shfl_sync(0xffffffffu, c, (l + 2) & 3, 4);
+        d = __shfl_sync(0xffffffffu, d, (l + 1) & 3, 4);
+    }
+    const uint32_t lo = a ^ c, hi = b ^ d;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        h[i] ^= __shfl_sync(0xffffffffu, lo, i, 4);
+        h[4 + i] ^= __shfl_sync(0xffffffffu, hi, i, 4);
+    }
+}
+
+__shared__ uint32_t s_block[16];  // the message block of the compression in flight (one transcript warp per CTA)
+
+// Warp-collective: digest <- H(digest || w[0..n)), every word reduced mod p.
+__device__ void chan_mix_words(Chan& ch, const uint32_t* w, int n) {
+    const int lane = threadIdx.x & 31;
+    uint32_t h[8];
     blake2s_init(h);
     const int total = 8 + n;
     uint32_t t = 0;
     int pos = 0;
-    while (total - pos > 16) {
-        for (int k = 0; k < 16; k++) { int i = pos + k; m[k] = i < 8 ? st->digest[i] : w[i - 8]; }
+    for (;;) {
+        const int rem = total - pos;
+        const bool last = rem <= 16;
+        __syncwarp();
+        if (lane < 16) {
+            const int i = pos + lane;
+            s_block[lane] = lane < rem ? (i < 8 ? ch.digest[i & 7] : w[i - 8]) : 0u;
+        }
+        __syncwarp();
+        t += last ? 4u * (uint32_t)rem : 64u;
+        b2s_compress_warp(h, s_block, t, last);
+        if (last) break;
         pos += 16;
-        t += 64;
-        blake2s_compress(h, m, t, false);
     }
-    int rem = total - pos;
-    for (int k = 0; k < 16; k++) { int i = pos + k; m[k] = k < rem ? (i < 8 ? st->digest[i] : w[i - 8]) : 0u; }
-    t += 4u * (uint32_t)rem;
-    blake2s_compress(h, m, t, true);
-    for (int k = 0; k < 8; k++) st->digest[k] = reduce_word_m31(h[k]);
-    st->n_draws = 0;
+    for (int k = 0; k < 8; k++) ch.digest[k] = reduce_word_m31(h[k]);
+    ch.n_draws = 0;
 }
-__device__ void chan_mix_felts(ResState* st, const qm31* f, int n) { chan_mix_words(st, (const uint32_t*)f, 4 * n); }
-__device__ qm31 chan_draw_felt(ResState* st) {
+__device__ void chan_mix_felts(Chan& ch, const qm31* f, int n) { chan_mix_words(ch, (const uint32_t*)f, 4 * n); }
+__device__ qm31 chan_draw_felt(Chan& ch) {
+    const int lane = threadIdx.x & 31;
     uint32_t u[8];
     for (int attempt = 0; attempt < 64; attempt++) {
-        uint32_t h[8], m[16];
+        uint32_t h[8];
         blake2s_init(h);
-        for (int k = 0; k < 8; k++) m[k] = st->digest[k];
-        m[8] = st->n_draws;
-        for (int k = 9; k < 16; k++) m[k] = 0u;
-        blake2s_compress(h, m, 37u, true);
-        st->n_draws++;
+        __syncwarp();
+        if (lane < 16) s_block[lane] = lane < 8 ? ch.digest[lane] : (lane == 8 ? ch.n_draws : 0u);
+        __syncwarp();
+        b2s_compress_warp(h, s_block, 37u, true);
+        ch.n_draws++;
         bool ok = true;
         for (int k = 0; k < 8; k++) { u[k] = reduce_word_m31(h[k]); ok = ok && u[k] < 2u * P; }
         if (ok) break;
@@ -81,6 +131,16 @@ __device__ qm31 chan_draw_felt(ResState* st) {
     qm31 r;
     for (int k = 0; k < 4; k++) r.c[k] = u[k] >= P ? u[k] - P : u[k];
     return r;
+}
+__device__ Chan chan_load(const ResState* st) {
+    Chan ch;
+    for (int k = 0; k < 8; k++) ch.digest[k] = st->digest[k];
+    ch.n_draws = st->n_draws;
+    return ch;
+}
+__device__ void chan_store(ResState* st, const Chan& ch) {
+    for (int k = 0; k < 8; k++) st->digest[k] = ch.digest[k];
+    st->n_draws = ch.n_draws;
 }
 
 // ---- univariate polynomials of degree <= 3 (lookups/utils.rs:26-54, 165-170)
@@ -104,42 +164,78 @@ __device__ qm31 eq1(qm31 x, qm31 y) {
 // the five inversions the formula needs (of prod_i eq(0, y_i), 1 - 2y, and of b, 1 - b, 2 - b, which are
 // (1 - y), -y, (1 - 3y) over (1 - 2y)) are taken with ONE inversion of their product (Montgomery's trick);
 // the fourth Lagrange term has value 0 and vanishes, exactly as its trimmed polynomial does on the host.
+// Warp-collective helpers: lane l computes its own product (or inverse), then every lane reads the results it
+// needs. The independent multiplications of a level run side by side instead of one after the other.
+__device__ __forceinline__ qm31 bcast(qm31 v, int src) {
+    qm31 r;
+#pragma unroll
+    for (int c = 0; c < 4; c++) r.c[c] = __shfl_sync(0xffffffffu, v.c[c], src);
+    return r;
+}
+template <int N>
+__device__ __forceinline__ void par_mul(const qm31 (&x)[N], const qm31 (&y)[N], qm31 (&out)[N]) {
+    const int lane = threadIdx.x & 31;
+    qm31 mx = x[0], my = y[0];
+#pragma unroll
+    for (int i = 1; i < N; i++)
+        if (lane == i) { mx = x[i]; my = y[i]; }
+    const qm31 p = qm31_mul(mx, my);
+#pragma unroll
+    for (int i = 0; i < N; i++) out[i] = bcast(p, i);
+}
 __device__ Poly4 correct_sum(qm31 f0, qm31 f2, qm31 claim, const qm31* y, const qm31* one_minus_y_prefix, int n, int k) {
+    const int lane = threadIdx.x & 31;
     // a = prod_{i < n-k+1} eq(0, y_i) = prod (1 - y_i): kept as prefix products by layer_end
     const qm31 a = one_minus_y_prefix[n - k + 1];
     const qm31 one = qm31_one(), yk = y[n - k];
     const qm31 d = qm31_sub(one, qm31_dbl(yk));                       // 1 - 2y
     const qm31 omy = qm31_sub(one, yk);                                // 1 - y = eq(0, y)
-    const qm31 v[5] = {a, d, omy, yk, qm31_sub(omy, qm31_dbl(yk))};   // a, 1-2y, 1-y, y, 1-3y
-    qm31 pre[5], inv[5];
-    qm31 run = one;
-    for (int i = 0; i < 5; i++) { pre[i] = run; run = qm31_mul(run, v[i]); }
-    qm31 r = qm31_inv(run);
-    for (int i = 5; i-- > 0;) { inv[i] = qm31_mul(r, pre[i]); r = qm31_mul(r, v[i]); }
-    const qm31 a_inv = inv[0];
-    const qm31 b = qm31_mul(omy, inv[1]);
-    const qm31 inv_b = qm31_mul(d, inv[2]);               // 1 / b
-    const qm31 inv_1mb = qm31_neg(qm31_mul(d, inv[3]));   // 1 / (1 - b) = (1 - 2y) / (-y)
-    const qm31 inv_2mb = qm31_mul(d, inv[4]);             // 1 / (2 - b)
-    const uint32_t half = 1u << 30;                        // 1 / 2
-    // eq(0, y) = 1 - y; eq(2, y) = 2y + (1 - 2)(1 - y) = 3y - 1
-    qm31 r0 = qm31_mul(qm31_mul(f0, omy), a_inv);
-    qm31 r1 = qm31_sub(claim, r0);
-    qm31 r2 = qm31_mul(qm31_mul(f2, qm31_neg(v[4])), a_inv);
-    // Lagrange weights p_i = ys[i] * prod_{j != i} 1 / (xs[i] - xs[j]) over xs = {0, 1, 2, b}; ys[3] = 0
-    qm31 p0 = qm31_neg(qm31_mul(qm31_mul_m31(r0, half), inv_b));      // 1/(0-1) * 1/(0-2) * 1/(0-b) = -1/(2b)
-    qm31 p1 = qm31_neg(qm31_mul(r1, inv_1mb));                         // 1/(1-0) * 1/(1-2) * 1/(1-b)
-    qm31 p2 = qm31_mul(qm31_mul_m31(r2, half), inv_2mb);               // 1/(2-0) * 1/(2-1) * 1/(2-b)
-    // sum_i p_i prod_{j != i} (t - xs[j]), expanded:
+    const qm31 m3y = qm31_sub(omy, qm31_dbl(yk));                      // 1 - 3y = -eq(2, y)
+    // level 1: the five inversions (of a, 1-2y, 1-y, y, 1-3y), one per lane
+    qm31 mine = a;
+    if (lane == 1) mine = d;
+    if (lane == 2) mine = omy;
+    if (lane == 3) mine = yk;
+    if (lane == 4) mine = m3y;
+    const qm31 minv = qm31_inv(mine);
+    const qm31 a_inv = bcast(minv, 0), d_inv = bcast(minv, 1), omy_inv = bcast(minv, 2), y_inv = bcast(minv, 3), m3y_inv = bcast(minv, 4);
+    // level 2
+    qm31 l2[6];
+    {
+        const qm31 x[6] = {omy, d, d, d, f0, f2}, z[6] = {d_inv, omy_inv, y_inv, m3y_inv, omy, qm31_neg(m3y)};
+        par_mul<6>(x, z, l2);
+    }
+    const qm31 b = l2[0], inv_b = l2[1], inv_1mb = qm31_neg(l2[2]), inv_2mb = l2[3];   // b, 1/b, 1/(1-b), 1/(2-b)
+    // level 3: r0 = f0 eq(0, y) / a, r2 = f2 eq(2, y) / a
+    qm31 l3[2];
+    {
+        const qm31 x[2] = {l2[4], l2[5]}, z[2] = {a_inv, a_inv};
+        par_mul<2>(x, z, l3);
+    }
+    const qm31 r0 = l3[0], r2 = l3[1], r1 = qm31_sub(claim, r0);
+    // level 4: Lagrange weights p_i = ys[i] * prod_{j != i} 1 / (xs[i] - xs[j]) over xs = {0, 1, 2, b}; ys[3] = 0
+    const uint32_t half = 1u << 30;  // 1 / 2
+    qm31 l4[3];
+    {
+        const qm31 x[3] = {qm31_mul_m31(r0, half), r1, qm31_mul_m31(r2, half)}, z[3] = {inv_b, inv_1mb, inv_2mb};
+        par_mul<3>(x, z, l4);
+    }
+    const qm31 p0 = qm31_neg(l4[0]), p1 = qm31_neg(l4[1]), p2 = l4[2];
+    // level 5: sum_i p_i prod_{j != i} (t - xs[j]), expanded:
     //   (t-1)(t-2)(t-b) = t^3 - (3+b) t^2 + (2+3b) t - 2b;  t(t-2)(t-b) = t^3 - (2+b) t^2 + 2b t;  t(t-1)(t-b) = t^3 - (1+b) t^2 + b t
     const qm31 b2 = qm31_dbl(b), b3 = qm31_add(b2, b);
+    qm31 l5[7];
+    {
+        const qm31 x[7] = {qm31_add(qm31_from_m31(3), b), qm31_add(qm31_from_m31(2), b), qm31_add(one, b), qm31_add(qm31_from_m31(2), b3), b2, b, b2};
+        const qm31 z[7] = {p0, p1, p2, p0, p1, p2, p0};
+        par_mul<7>(x, z, l5);
+    }
     Poly4 c;
     c.n = 4;
     c.c[3] = qm31_add(qm31_add(p0, p1), p2);
-    c.c[2] = qm31_neg(qm31_add(qm31_add(qm31_mul(qm31_add(qm31_from_m31(3), b), p0), qm31_mul(qm31_add(qm31_from_m31(2), b), p1)),
-                               qm31_mul(qm31_add(one, b), p2)));
-    c.c[1] = qm31_add(qm31_add(qm31_mul(qm31_add(qm31_from_m31(2), b3), p0), qm31_mul(b2, p1)), qm31_mul(b, p2));
-    c.c[0] = qm31_neg(qm31_mul(b2, p0));
+    c.c[2] = qm31_neg(qm31_add(qm31_add(l5[0], l5[1]), l5[2]));
+    c.c[1] = qm31_add(qm31_add(l5[3], l5[4]), l5[5]);
+    c.c[0] = qm31_neg(l5[6]);
     p_trim(c);
     return c;
 }
@@ -152,8 +248,10 @@ struct BeginArgs {
     const uint32_t* out_den[RES_MAX_INST];
     int oracle_inst[RES_MAX_INST], oracle_nvars[RES_MAX_INST];
 };
+// Every lane of the warp runs the step and writes the same values; see the channel above.
 __global__ void res_layer_begin_kernel(ResState* st, BeginArgs a) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    if (threadIdx.x >= 32 || blockIdx.x != 0) return;
+    Chan ch = chan_load(st);
     for (int i = 0; i < a.n_inst; i++)
         if (a.activate[i]) {
             const uint32_t* d = a.out_den[i];
@@ -167,15 +265,18 @@ __global__ void res_layer_begin_kernel(ResState* st, BeginArgs a) {
             for (int k = 0; k < n; k++) st->output_claims[i][k] = st->claims[i][k];
             st->n_output_claims[i] = n;
         }
+    __syncwarp();
     for (int i = 0; i < a.n_inst; i++)
-        if (a.active[i]) chan_mix_felts(st, st->claims[i], (int)st->n_claims[i]);
+        if (a.active[i]) chan_mix_felts(ch, st->claims[i], (int)st->n_claims[i]);
     st->eq_v = st->ood_len == 0 ? qm31_one() : eq1(qm31_zero(), st->ood[0]);
-    st->alpha = chan_draw_felt(st);
-    st->lambda = chan_draw_felt(st);
+    const qm31 alpha = chan_draw_felt(ch), lambda = chan_draw_felt(ch);
+    st->alpha = alpha;
+    st->lambda = lambda;
+    chan_store(st, ch);
     for (int k = 0; k < a.n_oracles; k++) {
         int i = a.oracle_inst[k];
         qm31 acc = qm31_zero();
-        for (int j = (int)st->n_claims[i]; j-- > 0;) acc = qm31_add(qm31_mul(acc, st->lambda), st->claims[i][j]);
+        for (int j = (int)st->n_claims[i]; j-- > 0;) acc = qm31_add(qm31_mul(acc, lambda), st->claims[i][j]);
         st->sc_claim[k] = qm31_mul_m31(acc, 1u << (a.nv - a.oracle_nvars[k]));
         st->eq_corr[k] = qm31_one();
     }
@@ -185,8 +286,10 @@ struct RoundArgs {
     int n_oracles, n_rem, round, poly_slot;
     int nvars[RES_MAX_INST];
 };
-__global__ void res_round_kernel(ResState* st, RoundArgs a) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+// Warp-collective.
+__device__ void round_step(ResState* st, const RoundArgs& a) {
+    Chan ch = chan_load(st);
+    const qm31 alpha = st->alpha;
     Poly4 rp[RES_MAX_INST];
     const uint32_t half = m31_inv(2);
     for (int k = 0; k < a.n_oracles; k++) {
@@ -209,20 +312,156 @@ __global__ void res_round_kernel(ResState* st, RoundArgs a) {
     combined.n = 0;
     for (int j = 0; j < 4; j++) combined.c[j] = qm31_zero();
     for (int k = a.n_oracles; k-- > 0;) {
-        for (int j = 0; j < combined.n; j++) combined.c[j] = qm31_mul(combined.c[j], st->alpha);
+        for (int j = 0; j < combined.n; j++) combined.c[j] = qm31_mul(combined.c[j], alpha);
         combined = p_add(combined, rp[k]);
     }
-    chan_mix_felts(st, combined.c, combined.n);
-    qm31 challenge = chan_draw_felt(st);
+    chan_mix_felts(ch, combined.c, combined.n);
+    qm31 challenge = chan_draw_felt(ch);
+    chan_store(st, ch);
     for (int k = 0; k < a.n_oracles; k++) st->sc_claim[k] = p_eval(rp[k], challenge);
     for (int k = 0; k < a.n_oracles; k++)
         if (a.n_rem == a.nvars[k] && a.nvars[k] != 0) {
-            qm31 z0 = st->ood[st->ood_len - a.nvars[k]];
-            st->eq_corr[k] = qm31_mul(st->eq_corr[k], eq1(challenge, z0));
+            const qm31 z0 = st->ood[st->ood_len - a.nvars[k]], old = st->eq_corr[k];
+            const qm31 upd = qm31_mul(old, eq1(challenge, z0));
+            __syncwarp();  // every lane has read the old value before any lane replaces it
+            st->eq_corr[k] = upd;
         }
     st->round_polys[a.poly_slot] = combined;
     st->assignment[a.round] = challenge;
     st->challenge = challenge;
+}
+__global__ void res_round_kernel(ResState* st, RoundArgs a) {
+    if (threadIdx.x >= 32 || blockIdx.x != 0) return;
+    round_step(st, a);
+}
+
+// The last rounds of a layer's sum-check in ONE launch: once every live oracle has at most 2^14 entries, a
+// single CTA runs round after round (sums over the layer, the transcript step on thread 0, fix_first_variable),
+// so a round costs its own latency and no launch. The first fold goes from the oracle's layer into work buffers
+// (the layer may be the caller's input, which is never modified), later folds are in place there.
+constexpr int TAIL_MAX_LOG = 14;
+constexpr int TAIL_THREADS = 1024;
+struct TailArgs {
+    int n_oracles, nv, round_start, first_poly_slot;
+    int kind[RES_MAX_INST], nvars[RES_MAX_INST];
+    const uint32_t* num[RES_MAX_INST];
+    const uint32_t* den[RES_MAX_INST];
+    uint32_t* num_w[RES_MAX_INST];  // n/2 QM31 each (unused for kinds without numerators)
+    uint32_t* den_w[RES_MAX_INST];
+    const uint32_t* eq_evals;
+};
+__device__ __forceinline__ qm31 ldq_r(const uint32_t* p, size_t i) {
+    uint4 v = reinterpret_cast<const uint4*>(p)[i];
+    return {{v.x, v.y, v.z, v.w}};
+}
+__device__ __forceinline__ void stq_r(uint32_t* p, size_t i, qm31 v) {
+    reinterpret_cast<uint4*>(p)[i] = make_uint4(v.c[0], v.c[1], v.c[2], v.c[3]);
+}
+// The summand of sum_as_poly_in_first_variable at t = 0 and t = 2 for term i (cpu/lookups/gkr.rs:39-211).
+__device__ void sum_term(int kind, const uint32_t* num, const uint32_t* den, size_t nt, size_t i, qm31 lambda, qm31& t0, qm31& t2) {
+    qm31 d00 = ldq_r(den, 2 * i), d01 = ldq_r(den, 2 * i + 1), d10 = ldq_r(den, 2 * (nt + i)), d11 = ldq_r(den, 2 * (nt + i) + 1);
+    qm31 d20 = qm31_sub(qm31_dbl(d10), d00), d21 = qm31_sub(qm31_dbl(d11), d01);
+    if (kind == ZKB_GKR_GRAND_PRODUCT) {
+        t0 = qm31_mul(d00, d01);
+        t2 = qm31_mul(d20, d21);
+        return;
+    }
+    qm31 n0, n2;
+    if (kind == ZKB_GKR_LOGUP_SINGLES) {
+        n0 = qm31_add(d00, d01);
+        n2 = qm31_add(d20, d21);
+    } else if (kind == ZKB_GKR_LOGUP_MULTIPLICITIES) {
+        uint32_t a0 = num[2 * i], a1 = num[2 * i + 1], b0 = num[2 * (nt + i)], b1 = num[2 * (nt + i) + 1];
+        uint32_t n20 = m31_sub(m31_dbl(b0), a0), n21 = m31_sub(m31_dbl(b1), a1);
+        n0 = qm31_add(qm31_mul_m31(d01, a0), qm31_mul_m31(d00, a1));
+        n2 = qm31_add(qm31_mul_m31(d21, n20), qm31_mul_m31(d20, n21));
+    } else {
+        qm31 n00 = ldq_r(num, 2 * i), n01 = ldq_r(num, 2 * i + 1), n10 = ldq_r(num, 2 * (nt + i)), n11 = ldq_r(num, 2 * (nt + i) + 1);
+        qm31 n20 = qm31_sub(qm31_dbl(n10), n00), n21 = qm31_sub(qm31_dbl(n11), n01);
+        n0 = qm31_add(qm31_mul(d01, n00), qm31_mul(d00, n01));
+        n2 = qm31_add(qm31_mul(d21, n20), qm31_mul(d20, n21));
+    }
+    t0 = qm31_add(n0, qm31_mul(lambda, qm31_mul(d00, d01)));
+    t2 = qm31_add(n2, qm31_mul(lambda, qm31_mul(d20, d21)));
+}
+__global__ void __launch_bounds__(TAIL_THREADS) res_tail_kernel(ResState* st, TailArgs a) {
+    __shared__ uint32_t red[TAIL_THREADS / 32][8];
+    __shared__ qm31 sh_challenge;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // every thread tracks the oracles' current layers identically
+    int kind[RES_MAX_INST], nvars[RES_MAX_INST];
+    const uint32_t* num[RES_MAX_INST];
+    const uint32_t* den[RES_MAX_INST];
+    bool folded[RES_MAX_INST];
+    for (int k = 0; k < a.n_oracles; k++) { kind[k] = a.kind[k]; nvars[k] = a.nvars[k]; num[k] = a.num[k]; den[k] = a.den[k]; folded[k] = false; }
+    const qm31 lambda = st->lambda;
+    for (int round = a.round_start; round < a.nv; round++) {
+        const int n_rem = a.nv - round;
+        for (int k = 0; k < a.n_oracles; k++) {
+            if (n_rem != nvars[k]) continue;
+            const size_t nt = ((size_t)2 << nvars[k]) / 4;  // the layer has 2^(nvars + 1) entries
+            qm31 s0 = qm31_zero(), s2 = qm31_zero();
+            for (size_t i = tid; i < nt; i += TAIL_THREADS) {
+                qm31 t0, t2;
+                sum_term(kind[k], num[k], den[k], nt, i, lambda, t0, t2);
+                qm31 e = ldq_r(a.eq_evals, i);
+                s0 = qm31_add(s0, qm31_mul(e, t0));
+                s2 = qm31_add(s2, qm31_mul(e, t2));
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    s0.c[c] = m31_add(s0.c[c], __shfl_down_sync(0xffffffffu, s0.c[c], off));
+                    s2.c[c] = m31_add(s2.c[c], __shfl_down_sync(0xffffffffu, s2.c[c], off));
+                }
+            if (lane == 0)
+                for (int c = 0; c < 4; c++) { red[warp][c] = s0.c[c]; red[warp][4 + c] = s2.c[c]; }
+            __syncthreads();
+            if (tid < 8) {
+                uint32_t acc = 0;
+                for (int w = 0; w < TAIL_THREADS / 32; w++) acc = m31_add(acc, red[w][tid]);
+                st->sums[k][tid] = acc;
+            }
+            __syncthreads();
+        }
+        if (warp == 0) {
+            RoundArgs ra;
+            ra.n_oracles = a.n_oracles;
+            ra.n_rem = n_rem;
+            ra.round = round;
+            ra.poly_slot = a.first_poly_slot + (round - a.round_start);
+            for (int k = 0; k < a.n_oracles; k++) ra.nvars[k] = nvars[k];
+            round_step(st, ra);
+            __syncwarp();
+            if (lane == 0) sh_challenge = st->challenge;
+        }
+        __syncthreads();
+        const qm31 r = sh_challenge;
+        for (int k = 0; k < a.n_oracles; k++) {
+            if (n_rem != nvars[k] || nvars[k] == 0) continue;
+            const size_t half = (size_t)1 << nvars[k];  // entries after the fold
+            const bool has_num = kind[k] == ZKB_GKR_LOGUP_GENERIC || kind[k] == ZKB_GKR_LOGUP_MULTIPLICITIES;
+            for (size_t i = tid; i < half; i += TAIL_THREADS) {
+                qm31 x = ldq_r(den[k], i), y = ldq_r(den[k], i + half);
+                stq_r(a.den_w[k], i, qm31_add(qm31_mul(r, qm31_sub(y, x)), x));
+                if (kind[k] == ZKB_GKR_LOGUP_MULTIPLICITIES) {
+                    uint32_t p = num[k][i], q = num[k][i + half];
+                    qm31 v = qm31_mul_m31(r, m31_sub(q, p));
+                    v.c[0] = m31_add(v.c[0], p);
+                    stq_r(a.num_w[k], i, v);
+                } else if (has_num) {
+                    qm31 p = ldq_r(num[k], i), q = ldq_r(num[k], i + half);
+                    stq_r(a.num_w[k], i, qm31_add(qm31_mul(r, qm31_sub(q, p)), p));
+                }
+            }
+            den[k] = a.den_w[k];
+            if (has_num) { num[k] = a.num_w[k]; kind[k] = ZKB_GKR_LOGUP_GENERIC; }
+            folded[k] = true;
+            nvars[k]--;
+        }
+        __syncthreads();  // the folded layers are complete (and visible) before the next round reads them
+    }
 }
 
 struct EndArgs {
@@ -232,7 +471,8 @@ struct EndArgs {
     const uint32_t* den[RES_MAX_INST];
 };
 __global__ void res_layer_end_kernel(ResState* st, EndArgs a) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    if (threadIdx.x >= 32 || blockIdx.x != 0) return;
+    Chan ch = chan_load(st);
     int ncols[RES_MAX_INST];
     for (int k = 0; k < a.n_oracles; k++) {  // try_into_mask, gkr_prover.rs:572-597
         qm31* m = st->masks[a.layer][k];
@@ -244,8 +484,10 @@ __global__ void res_layer_end_kernel(ResState* st, EndArgs a) {
             m[0] = qm31{{q[0], q[1], q[2], q[3]}}; m[1] = qm31{{q[4], q[5], q[6], q[7]}}; m[2] = d0; m[3] = d1; ncols[k] = 2;
         } else { m[0] = qm31_one(); m[1] = qm31_one(); m[2] = d0; m[3] = d1; ncols[k] = 2; }
     }
-    for (int k = 0; k < a.n_oracles; k++) chan_mix_felts(st, st->masks[a.layer][k], 2 * ncols[k]);
-    qm31 challenge = chan_draw_felt(st);
+    __syncwarp();
+    for (int k = 0; k < a.n_oracles; k++) chan_mix_felts(ch, st->masks[a.layer][k], 2 * ncols[k]);
+    qm31 challenge = chan_draw_felt(ch);
+    chan_store(st, ch);
     for (int j = 0; j < a.nv; j++) st->ood[j] = st->assignment[j];
     st->ood[a.nv] = challenge;
     st->ood_len = (uint32_t)a.nv + 1u;
@@ -356,7 +598,9 @@ int gkr_prove_resident(zkb_ctx* ctx, std::vector<Layer> input_layers, uint32_t d
         std::vector<bool> have_sums(n_or, false);
         layer_first_poly[layer] = poly_slot;
         layer_nv[layer] = nv;
-        for (int round = 0; round < nv; round++) {
+        // rounds in which some layer still has more than 2^TAIL_MAX_LOG entries run as separate launches
+        const int round_start = nv > TAIL_MAX_LOG - 1 ? nv - (TAIL_MAX_LOG - 1) : 0;
+        for (int round = 0; round < round_start; round++) {
             const int n_rem = nv - round;
             for (int k = 0; k < n_or; k++)
                 if (n_rem == nvars[k] && !have_sums[k]) {
@@ -400,21 +644,61 @@ int gkr_prove_resident(zkb_ctx* ctx, std::vector<Layer> input_layers, uint32_t d
                     nvars[k]--;  // the oracle's n_variables() follows its layer
                 }
         }
+        // the remaining rounds: one launch
+        std::vector<SecureMle> work;  // alive until layer_end has been enqueued (stream-ordered frees)
+        std::vector<int> fin_kind(n_or);
+        std::vector<const uint32_t*> fin_num(n_or), fin_den(n_or);
+        TailArgs ta;
+        memset(&ta, 0, sizeof(ta));
+        ta.n_oracles = n_or;
+        ta.nv = nv;
+        ta.round_start = round_start;
+        ta.first_poly_slot = poly_slot;
+        ta.eq_evals = eq_evals.words.ptr();
+        for (int k = 0; k < n_or; k++) {
+            const Layer& l = oracle_layers[k];
+            ta.kind[k] = l.kind;
+            ta.nvars[k] = nvars[k];
+            ta.num[k] = l.num_ptr();
+            ta.den[k] = l.den.words.ptr();
+            fin_kind[k] = l.kind;
+            fin_num[k] = l.num_ptr();
+            fin_den[k] = l.den.words.ptr();
+            if (l.len() > ((size_t)1 << TAIL_MAX_LOG) && round_start < nv) return set_error(ctx, ZKB_EINVAL, "gkr: tail layer too large");
+            if (nvars[k] >= 1 && round_start < nv) {  // folded at least once by the tail kernel
+                const bool has_num = l.kind == ZKB_GKR_LOGUP_GENERIC || l.kind == ZKB_GKR_LOGUP_MULTIPLICITIES;
+                work.emplace_back(d, l.len() / 2);
+                ta.den_w[k] = work.back().words.ptr();
+                fin_den[k] = ta.den_w[k];
+                if (has_num) {
+                    work.emplace_back(d, l.len() / 2);
+                    ta.num_w[k] = work.back().words.ptr();
+                    fin_num[k] = ta.num_w[k];
+                    fin_kind[k] = ZKB_GKR_LOGUP_GENERIC;
+                }
+            } else if (l.len() != 2) {
+                return set_error(ctx, ZKB_EINVAL, "gkr: oracle is not constant after sumcheck");
+            }
+        }
+        if (round_start < nv) {
+            ProfScope prof(ctx, "res_tail_kernel");
+            res_tail_kernel<<<1, TAIL_THREADS, 0, stream>>>(st, ta);
+            ZKB_LAUNCH_CHECK(ctx);
+            poly_slot += nv - round_start;
+        }
         EndArgs ea;
         memset(&ea, 0, sizeof(ea));
         ea.n_oracles = n_or;
         ea.nv = nv;
         ea.layer = (int)layer;
         for (int k = 0; k < n_or; k++) {
-            const Layer& l = oracle_layers[k];
-            if (l.len() != 2) return set_error(ctx, ZKB_EINVAL, "gkr: oracle is not constant after sumcheck");
-            if (l.kind == ZKB_GKR_LOGUP_MULTIPLICITIES) return set_error(ctx, ZKB_EINVAL, "gkr: a multiplicities layer cannot be a mask");
-            ea.kind[k] = l.kind;
+            if (fin_kind[k] == ZKB_GKR_LOGUP_MULTIPLICITIES) return set_error(ctx, ZKB_EINVAL, "gkr: a multiplicities layer cannot be a mask");
+            ea.kind[k] = fin_kind[k];
             ea.inst[k] = ba.oracle_inst[k];
-            ea.den[k] = l.den.words.ptr();
-            ea.num[k] = l.num_ptr();
+            ea.den[k] = fin_den[k];
+            ea.num[k] = fin_num[k];
             layer_oracle_inst[layer].push_back(ba.oracle_inst[k]);
-            layer_oracle_cols[layer].push_back(l.kind == ZKB_GKR_GRAND_PRODUCT ? 1 : 2);
+            layer_oracle_cols[layer].push_back(fin_kind[k] == ZKB_GKR_GRAND_PRODUCT ? 1 : 2);
         }
         { ProfScope prof(ctx, "res_layer_end_kernel"); res_layer_end_kernel<<<1, 32, 0, stream>>>(st, ea); }
         ZKB_LAUNCH_CHECK(ctx);
