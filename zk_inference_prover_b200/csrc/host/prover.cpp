@@ -358,6 +358,7 @@ struct PcsConfig {
 
 struct CommitmentTreeProver {  // pcs/mod.rs:466-630
     std::vector<BaseColumn> coeffs;  // views of the caller's columns after interpolation
+    BaseColumn coeff_slab;           // host path: the one allocation the coefficient columns are views of
     std::vector<BaseColumn> evals;
     MerkleProver commitment;
     uint32_t max_log() const { return (uint32_t)commitment.layers.size() - 1; }
@@ -454,8 +455,10 @@ struct CommitmentSchemeProver {
     // `fence_of` (optional, one entry per column) names the copy fence after which a column's values have
     // arrived from the host; columns are then interpolated and extended fence by fence, while later
     // columns are still in flight.
-    void commit_evals(std::vector<BaseColumn> columns, Channel& ch, const std::vector<int>* fence_of = nullptr) {
+    void commit_evals(std::vector<BaseColumn> columns, Channel& ch, const std::vector<int>* fence_of = nullptr,
+                      BaseColumn* slab = nullptr) {
         CommitmentTreeProver t;
+        if (slab) t.coeff_slab = std::move(*slab);
         std::map<uint32_t, std::vector<size_t>> by_log;
         for (size_t i = 0; i < columns.size(); i++) by_log[columns[i].log_size()].push_back(i);
         t.evals.resize(columns.size());
@@ -931,24 +934,52 @@ static int pcs_prove_impl(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint
             size_t total_bytes = 0;
             for (int i = 0; i < total; i++) total_bytes += (size_t)4 << col_logs[i];
             const size_t per_fence = std::max<size_t>(total_bytes / 32, 1);
+            // The columns of a tree live in one allocation (each padded to 64 words), so that columns that
+            // are adjacent in host memory, as a row-major trace is, go up in one copy per fence.
             std::vector<std::vector<BaseColumn>> tree_cols(n_trees);
             std::vector<std::vector<int>> tree_fences(n_trees);
-            for (int t = 0; t < n_trees; t++)
-                for (int c = 0; c < tree_ncols[t]; c++, flat++) tree_cols[t].emplace_back(dev, (size_t)1 << col_logs[flat]);
+            std::vector<BaseColumn> slabs;
+            for (int t = 0; t < n_trees; t++) {
+                size_t words = 0;
+                for (int c = 0; c < tree_ncols[t]; c++) words += std::max<size_t>((size_t)1 << col_logs[flat + c], 64);
+                slabs.emplace_back(dev, words);
+                size_t off = 0;
+                for (int c = 0; c < tree_ncols[t]; c++, flat++) {
+                    size_t n = (size_t)1 << col_logs[flat];
+                    tree_cols[t].push_back(BaseColumn::view(dev, slabs.back().ptr() + off, n));
+                    off += std::max<size_t>(n, 64);
+                }
+            }
             flat = 0;
             int fence = 0;
             size_t since = 0;
+            // a pending run of copies that are contiguous on both sides
+            uint32_t* run_dst = nullptr;
+            const uint32_t* run_src = nullptr;
+            size_t run_bytes = 0;
+            auto flush = [&](int fence_id) {
+                if (run_bytes) dev.check(zkb_h2d_overlapped(ctx, run_dst, run_src, run_bytes, fence_id));
+                else if (fence_id >= 0) dev.check(zkb_h2d_overlapped(ctx, nullptr, nullptr, 0, fence_id));
+                run_bytes = 0;
+            };
             for (int t = 0; t < n_trees; t++)
                 for (int c = 0; c < tree_ncols[t]; c++, flat++) {
                     size_t bytes = (size_t)4 << col_logs[flat];
+                    uint32_t* dst = tree_cols[t][c].ptr();
+                    if (run_bytes && (const uint8_t*)run_src + run_bytes == (const uint8_t*)h_cols[flat] &&
+                        (uint8_t*)run_dst + run_bytes == (uint8_t*)dst) {
+                        run_bytes += bytes;
+                    } else {
+                        flush(-1);
+                        run_dst = dst; run_src = h_cols[flat]; run_bytes = bytes;
+                    }
                     since += bytes;
                     bool close = since >= per_fence || flat == total - 1;
-                    dev.check(zkb_h2d_overlapped(ctx, tree_cols[t][c].ptr(), h_cols[flat], bytes, close ? fence : -1));
                     tree_fences[t].push_back(fence);
-                    if (close) { since = 0; if (fence < 63) fence++; }
+                    if (close) { flush(fence); since = 0; if (fence < 63) fence++; }
                 }
             try {
-                for (int t = 0; t < n_trees; t++) prover.commit_evals(std::move(tree_cols[t]), ch, &tree_fences[t]);
+                for (int t = 0; t < n_trees; t++) prover.commit_evals(std::move(tree_cols[t]), ch, &tree_fences[t], &slabs[t]);
             } catch (...) {
                 zkb_sync(ctx);  // no column may be freed while the copy stream still writes into it
                 throw;
