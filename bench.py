@@ -388,8 +388,8 @@ def run_ours(args, rank, world, local_rank):
             "gpu_launches": launches * args.steps,
             "roofline": roofline, "cpu_baseline": cpu, "gpu_baseline": gpu_ref, "clocks": clocks,
             "proof_words": int(len(words_dev)), "proof_sha256": hashlib.sha256(words_dev.tobytes()).hexdigest(),
-            "parity": golden_check(f"pcs_{ncols}x2e{log_n}_blowup{1 << args.log_blowup}", words_dev)
-            if (args.pow_bits, args.n_queries) == (10, 3) else None,
+            "parity": golden_check(f"pcs_{ncols}x2e{log_n}_blowup{1 << args.log_blowup}" +
+                                   ("" if (args.pow_bits, args.n_queries) == (10, 3) else f"_pow{args.pow_bits}_q{args.n_queries}"), words_dev),
         }
         print(json.dumps(line))
     ctx.free_pinned(h_addr)

@@ -39,6 +39,8 @@ PCS_SMALL = {
 # the benchmark workload: seeds 0x5EED0001 + column, default PcsConfig, blow-up 4
 PCS_FULL = {
     "pcs_256x2e20_blowup4": ([[20] * 256], 0x5EED0001, dict(pow_bits=10, log_blowup=2, n_queries=3, cap=1 << 26)),
+    # the same trace with the prover's own parameters (prover/src/util.rs:14-28): blow-up 2, 100 queries, no grinding
+    "pcs_256x2e20_blowup2_pow0_q100": ([[20] * 256], 0x5EED0001, dict(pow_bits=0, log_blowup=1, n_queries=100, cap=1 << 26)),
 }
 # name -> (list of (kind, log size, seed), channel seed)
 GKR_SMALL = {
