@@ -285,3 +285,38 @@ class RefCudaOps(RefCuda):
 
     def bit_reverse(self, ptr, n):
         self.lib.bit_reverse_base_field(ptr, n)
+
+
+class RefCudaMore(RefCudaOps):
+    """AccumulationOps, batch_eval_at_point and GrindOps of the reference's CUDA backend
+    (prover/backend/cuda/{accumulation,poly}.rs, stwo_cuda/cuda/grind_blake2s.cu)."""
+
+    def __init__(self):
+        super().__init__()
+        L, vp, u32, i32 = self.lib, C.c_void_p, C.c_uint32, C.c_int
+        L.accumulate.restype = None
+        L.accumulate.argtypes = [i32, vp, vp]
+        L.lift_and_accumulate.restype = None
+        L.lift_and_accumulate.argtypes = [i32] + [vp] * 8 + [i32]
+        L.batch_eval_at_points.restype = None
+        L.batch_eval_at_points.argtypes = [vp, i32, i32, _Q, _Q, vp]
+        L.grind_blake2s.restype = C.c_uint64
+        L.grind_blake2s.argtypes = [vp, u32]
+
+    def accumulate(self, left4, right4, n):
+        self.lib.accumulate(n, _ptrs(left4), _ptrs(right4))
+
+    def lift_and_accumulate(self, dst4, log_dst, src4, log_src):
+        self.lib.lift_and_accumulate(1 << log_dst, *dst4, *src4, log_dst - log_src)
+
+    def batch_eval_at_point(self, coeff_ptrs, log_n, point8):
+        pt = np.ascontiguousarray(point8, np.uint32).reshape(8)
+        d = self.lib.copy_device_pointer_vec_from_host_to_device(_ptrs(coeff_ptrs), len(coeff_ptrs))
+        out = np.zeros((len(coeff_ptrs), 4), np.uint32)
+        self.lib.batch_eval_at_points(d, 1 << log_n, len(coeff_ptrs), _q(pt[:4]), _q(pt[4:]), out.ctypes.data)
+        self.free(d)
+        return out
+
+    def grind(self, prefixed_digest8, pow_bits):
+        d = np.ascontiguousarray(prefixed_digest8, np.uint32)
+        return int(self.lib.grind_blake2s(d.ctypes.data, pow_bits))

@@ -204,3 +204,51 @@ def test_bit_reverse_matches_reference_cuda(ctx, refops, log_n):
     ctx.bit_reverse_m31(b.ptr, log_n)
     assert (b.download(n) == refops.download(r, n)).all()
     refops.free(r)
+
+
+@pytest.fixture(scope="module")
+def refmore():
+    from oracle import ref_cuda
+
+    if not ref_cuda.available():
+        pytest.skip("oracle/_ref/libstwo_cuda_ref.so is not built (the reference checkout is needed to build it)")
+    return ref_cuda.RefCudaMore()
+
+
+def test_accumulation_matches_reference_cuda(ctx, refmore):
+    log_dst, log_src = 12, 9
+    n, m = 1 << log_dst, 1 << log_src
+    a, b, small = _secure(9500, n), _secure(9510, n), _secure(9520, m)
+    ra, rb, rs = [refmore.upload(x) for x in a], [refmore.upload(x) for x in b], [refmore.upload(x) for x in small]
+    refmore.accumulate(ra, rb, n)
+    refmore.lift_and_accumulate(ra, log_dst, rs, log_src)
+    ga, gb, gs = [ctx.upload(x) for x in a], [ctx.upload(x) for x in b], [ctx.upload(x) for x in small]
+    ctx.accumulate([x.ptr for x in ga], [x.ptr for x in gb], n)
+    ctx.lift_accumulate([x.ptr for x in ga], log_dst, [x.ptr for x in gs], log_src)
+    for q in range(4):
+        assert (ga[q].download(n) == refmore.download(ra[q], n)).all()
+    for p in ra + rb + rs:
+        refmore.free(p)
+
+
+@pytest.mark.parametrize("log_n,ncols", [(10, 3), (16, 5), (20, 2)])
+def test_batch_eval_at_point_matches_reference_cuda(ctx, refmore, log_n, ncols):
+    from util import qm31_array
+
+    n = 1 << log_n
+    coeffs = [edge_m31_column(9600 + c, n) for c in range(ncols)]
+    point = qm31_array(9610 + log_n, 2).reshape(8)  # the evaluation is algebraic: any (x, y) pair will do
+    r = [refmore.upload(c) for c in coeffs]
+    want = refmore.batch_eval_at_point(r, log_n, point)
+    bufs = [ctx.upload(c) for c in coeffs]
+    got = ctx.eval_at_point_cols([b.ptr for b in bufs], log_n, point)
+    assert (got == want).all()
+    for p in r:
+        refmore.free(p)
+
+
+@pytest.mark.parametrize("pow_bits", [0, 5, 12, 20])
+def test_grind_matches_reference_cuda(ctx, refmore, pow_bits):
+    digest = m31_column(9700 + pow_bits, 8)
+    # the reference's kernel tests the raw first word of the digest (stwo_cuda/cuda/grind_blake2s.cu:105-112)
+    assert ctx.grind(digest, pow_bits, m31_out=False) == refmore.grind(digest, pow_bits)
