@@ -340,7 +340,7 @@ __global__ void res_round_kernel(ResState* st, RoundArgs a) {
 // so a round costs its own latency and no launch. The first fold goes from the oracle's layer into work buffers
 // (the layer may be the caller's input, which is never modified), later folds are in place there.
 constexpr int TAIL_MAX_LOG = 14;
-constexpr int TAIL_THREADS = 1024;
+constexpr int TAIL_THREADS = 512;
 struct TailArgs {
     int n_oracles, nv, round_start, first_poly_slot;
     int kind[RES_MAX_INST], nvars[RES_MAX_INST];
