@@ -320,3 +320,96 @@ class RefCudaMore(RefCudaOps):
     def grind(self, prefixed_digest8, pow_bits):
         d = np.ascontiguousarray(prefixed_digest8, np.uint32)
         return int(self.lib.grind_blake2s(d.ctypes.data, pow_bits))
+
+
+class _ZkGrid(C.Structure):  # stwo_cuda/cuda/zk_attention_freivalds_witness_gen.cuh:52-59 (= ZkAccGrid, zk_acc.cuh:88-95)
+    _fields_ = [(n, C.c_uint32) for n in ("log_rows", "rows", "groups", "chunks", "lead", "descending")]
+
+
+class _ZkMult(C.Structure):
+    _fields_ = [("m", C.c_void_p), ("n", C.c_uint32)]
+
+
+class _ZkFreivaldsCfg(C.Structure):
+    _fields_ = [("g", _ZkGrid)] + [(n, C.c_uint32) for n in ("pq", "pk", "n_in", "tokens", "n_mats", "mutate")]
+
+
+class _ZkAccFreivalds(C.Structure):
+    _fields_ = [("g", _ZkGrid)] + [(n, C.c_uint32) for n in ("pq", "pk", "n_mats", "off_x", "mutate")]
+
+
+class _ZkAccS2(C.Structure):  # zk_acc.cuh:194-202
+    _fields_ = [(n, C.c_uint32) for n in ("dst", "src0", "src1", "sel_i")] + [("m_i", _Q), ("m_l", _Q), ("m_n", _Q)]
+
+
+class RefCudaFreivalds(RefCudaMore):
+    """The Freivalds attention-witness component of the reference's device path
+    (prover/src/gadgets/freivalds/device.rs:56-133 and prover/src/devacc.rs:665-713)."""
+
+    def __init__(self):
+        super().__init__()
+        L, vp, u32 = self.lib, C.c_void_p, C.c_uint32
+        L.zk_witness_gen_freivalds.restype = None
+        L.zk_witness_gen_freivalds.argtypes = [vp, vp, vp, vp, u32, vp, u32, _ZkMult, vp, _ZkFreivaldsCfg]
+        L.zk_acc_freivalds.restype = None
+        L.zk_acc_freivalds.argtypes = [vp, vp, vp, vp, _Q, _Q, vp, vp, vp, _ZkAccFreivalds]
+        L.zk_acc_scan.restype = None
+        L.zk_acc_scan.argtypes = [vp, vp, u32, u32, u32]
+        L.zk_acc_stage2.restype = None
+        L.zk_acc_stage2.argtypes = [vp, vp, vp, vp, u32, u32, u32]
+        L.zk_acc_split.restype = None
+        L.zk_acc_split.argtypes = [vp, vp, vp, u32, u32, u32, u32]
+        L.zk_acc_last.restype = None
+        L.zk_acc_last.argtypes = [vp, vp, u32, u32]
+
+    @staticmethod
+    def _grid(grid):
+        log_rows, groups, chunks, lead = grid
+        return _ZkGrid(log_rows, 1 << log_rows, groups, chunks, lead, 1)
+
+    def upload_i8(self, arr):
+        b = np.ascontiguousarray(arr, np.int8).reshape(-1)
+        pad = (-b.size) % 4
+        w = np.concatenate([b, np.zeros(pad, np.int8)]).view(np.uint32)
+        return self.upload(w)
+
+    def scatter(self, qx, qws, grid, pq, pk):
+        tokens, n_in = qx.shape
+        rows = 1 << grid[0]
+        d_qx = self.upload_i8(qx)
+        d_qw = [self.upload_i8(w) for w in qws]
+        n_out = np.array([w.shape[1] for w in qws], np.uint32)
+        base = [self.alloc(rows) for _ in range(pq)]
+        pre = [self.alloc(rows) for _ in range(len(qws) * pk + 4)]
+        m_r8, counts = self.alloc_zero(256), self.alloc_zero(3)
+        cfg = _ZkFreivaldsCfg(self._grid(grid), pq, pk, n_in, tokens, len(qws), 0)
+        self.lib.zk_witness_gen_freivalds(d_qx, _ptrs(d_qw), n_out.ctypes.data, _ptrs(base), len(base), _ptrs(pre), len(pre),
+                                          _ZkMult(m_r8, 256), counts, cfg)
+        for p in [d_qx] + d_qw:
+            self.free(p)
+        return base, pre, m_r8, counts
+
+    def acc(self, base, pre, grid, pq, pk, n_mats, s, rv, s_pow, rv_pow, s_step, rv_step):
+        rows = 1 << grid[0]
+        lanes = 1 + 2 * n_mats
+        a, b, flags = self.alloc(4 * lanes * rows), self.alloc(4 * lanes * rows), self.alloc_zero(rows)
+        sp, rp = np.ascontiguousarray(s_pow, np.uint32), np.ascontiguousarray(rv_pow, np.uint32)
+        cfg = _ZkAccFreivalds(self._grid(grid), pq, pk, n_mats, 128, 0)
+        self.lib.zk_acc_freivalds(_ptrs(base), _ptrs(pre[:n_mats * pk]), sp.ctypes.data, rp.ctypes.data, _q(s_step), _q(rv_step), flags, a, b, cfg)
+        self.lib.zk_acc_scan(a, b, rows, 1 + n_mats, 0)
+        one = _Q(1, 0, 0, 0)
+        s2 = (_ZkAccS2 * n_mats)(*[_ZkAccS2(1 + n_mats + m, 1 + m, 0, 0, one, one, one) for m in range(n_mats)])
+        self.lib.zk_acc_stage2(flags, a, b, s2, n_mats, rows, 0)
+        off = 16 * (1 + n_mats) * rows  # bytes: a QM31 is four words
+        self.lib.zk_acc_scan(a + off, b + off, rows, n_mats, 0)
+        last = np.zeros((lanes, 4), np.uint32)
+        self.lib.zk_acc_last(b, last.ctypes.data, rows, lanes)
+        order = [0]
+        for m in range(n_mats):
+            order += [1 + m, 1 + n_mats + m]
+        order = np.array(order, np.uint32)
+        out = [self.alloc(rows) for _ in range(4 * len(order))]
+        self.lib.zk_acc_split(b, _ptrs(out), order.ctypes.data, len(order), rows, grid[0], 0)
+        for p in (a, b, flags):
+            self.free(p)
+        return out, last[1 + n_mats:1 + 2 * n_mats]

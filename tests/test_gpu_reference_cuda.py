@@ -252,3 +252,41 @@ def test_grind_matches_reference_cuda(ctx, refmore, pow_bits):
     digest = m31_column(9700 + pow_bits, 8)
     # the reference's kernel tests the raw first word of the digest (stwo_cuda/cuda/grind_blake2s.cu:105-112)
     assert ctx.grind(digest, pow_bits, m31_out=False) == refmore.grind(digest, pow_bits)
+
+
+@pytest.mark.parametrize("tokens,n_in,n_outs,chunks", [(5, 6, [7, 5], 4), (9, 4, [4, 6, 2], 3), (32, 64, [64, 48, 64], 16), (17, 128, [96], 64)])
+def test_freivalds_component_matches_reference_cuda(ctx, oracle, tokens, n_in, n_outs, chunks):
+    from oracle import ref_cuda
+    from test_freivalds import _case, layout
+    from util import qm31_array
+
+    if not ref_cuda.available():
+        pytest.skip("oracle/_ref/libstwo_cuda_ref.so is not built (the reference checkout is needed to build it)")
+    ref = ref_cuda.RefCudaFreivalds()
+    qx, qws = _case(13, tokens, n_in, n_outs)
+    grid, pq, pk = layout(n_in, max(n_outs), tokens, chunks)
+    rows, n_mats = 1 << grid[0], len(qws)
+    # witness scatter
+    r_base, r_pre, r_m, r_counts = ref.scatter(qx, qws, grid, pq, pk)
+    d_qx, d_qw = ctx.upload_bytes(qx), [ctx.upload_bytes(w) for w in qws]
+    base, pre = [ctx.alloc(rows) for _ in range(pq)], [ctx.alloc(rows) for _ in range(n_mats * pk + 4)]
+    m_r8, off = ctx.alloc(256).zero(), ctx.alloc(2).zero()
+    ctx.freivalds_scatter(d_qx.ptr, [w.ptr for w in d_qw], n_outs, grid, pq, pk, n_in, tokens, [b.ptr for b in base],
+                          [p.ptr for p in pre], m_r8.ptr, 256, off.ptr)
+    for c in range(pq):
+        assert (base[c].download() == ref.download(r_base[c], rows)).all()
+    for c in range(n_mats * pk + 4):
+        assert (pre[c].download() == ref.download(r_pre[c], rows)).all()
+    assert (m_r8.download() == ref.download(r_m, 256)).all()
+    assert int(off.download()[0]) == int(ref.download(r_counts, 3)[0])
+    # accumulators: v, then (u_m, acc_m) per matrix, and the claims
+    s, rv = qm31_array(41, 1)[0], qm31_array(42, 1)[0]
+    s_pow, rv_pow = oracle.secure_powers(s, pq + 1), oracle.secure_powers(rv, pk + 1)
+    r_out, r_claims = ref.acc(r_base, r_pre, grid, pq, pk, n_mats, s, rv, s_pow[:pq], rv_pow[:pk], s_pow[pq], rv_pow[pk])
+    out = [ctx.alloc(rows) for _ in range((1 + 2 * n_mats) * 4)]
+    claims = ctx.freivalds_acc([b.ptr for b in base], [p.ptr for p in pre[:n_mats * pk]], grid, pq, pk, n_mats, s, rv, [o.ptr for o in out])
+    for c in range(len(out)):
+        assert (out[c].download() == ref.download(r_out[c], rows)).all()
+    assert (claims == r_claims).all()
+    for p in r_base + r_pre + r_out + [r_m, r_counts]:
+        ref.free(p)
