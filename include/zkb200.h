@@ -19,6 +19,10 @@
  *    outputs synchronise that stream before returning.
  *  - Buffers are owned by whoever allocated them. The library frees only what zkb_malloc gave out
  *    and only in zkb_free / zkb_destroy.
+ *  - A context serves one host thread at a time (its stream, scratch and staging ring are not
+ *    locked). Several contexts, on one device or on several, may be used from different threads
+ *    concurrently; the traits' per-column default methods that the reference runs on rayon workers
+ *    (STWO/prover/poly/circle/ops.rs:28-39, 98-120) are replaced by the batched calls below.
  */
 #ifndef ZKB200_H
 #define ZKB200_H
