@@ -114,15 +114,6 @@ __device__ __forceinline__ void radix32_stage(uint32_t (&v)[32], const uint32_t*
     }
 }
 
-// Twiddle pointers of a stage in the tower (global memory): layer jj of the stage is the global layer
-// layer0 + jj and its table starts at tower + 2^(L - i - 1) + (A << (4 - jj)).
-template <bool CIRCLE>
-__device__ __forceinline__ void tower_ptrs(const uint32_t* (&tb)[5], const uint32_t* __restrict__ tower, int L, int layer0, uint32_t A) {
-#pragma unroll
-    for (int jj = 0; jj < 5; jj++) tb[jj] = tower + (1u << (L - layer0 - jj - 1)) + (A << (4 - jj));
-    if (CIRCLE) tb[0] = tower + (1u << (L - 2)) + (A << 3);
-}
-
 // ---- asynchronous global -> shared copies (16 bytes each), grouped and waited on per thread
 __device__ __forceinline__ void cp_async16(uint32_t* smem_dst, const uint32_t* gmem_src) {
     unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
@@ -138,7 +129,7 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 constexpr int R32_CONTIG_WARPS = 8;    // warps per CTA of the contiguous pass; each runs its own pipeline
 constexpr int R32_BUF_WORDS = 264 * 32;  // one staging buffer: 1024 rows x 8 words, or 8 units of 33 x 32
-// Forward passes also stage the twiddles of the next work item (cp.async, same group as its data): the
+// Every pass also stages the twiddles of the next work item (cp.async, same group as its data): the
 // twiddles a thread needs are short consecutive runs of the tower, different for every item.
 //   contiguous: [0,480) the per-thread stage (layers 1..4: 256 + 128 + 64 + 32 words; the circle layer reuses
 //               the layer-1 run), [480,511) the CTA-uniform stage (layers 5..9: 16 + 8 + 4 + 2 + 1 words)
@@ -146,10 +137,12 @@ constexpr int R32_BUF_WORDS = 264 * 32;  // one staging buffer: 1024 rows x 8 wo
 constexpr int R32_TW_CONTIG = 512;
 constexpr int R32_TW_STRIDED = 1024;
 __host__ __device__ constexpr size_t r32_contig_smem(bool inverse) {
-    return (size_t)R32_CONTIG_WARPS * 2 * (33 * 32 + (inverse ? 0 : R32_TW_CONTIG)) * sizeof(uint32_t);
+    (void)inverse;
+    return (size_t)R32_CONTIG_WARPS * 2 * (33 * 32 + R32_TW_CONTIG) * sizeof(uint32_t);
 }
 __host__ __device__ constexpr size_t r32_strided_smem(bool inverse) {
-    return (size_t)2 * (R32_BUF_WORDS + (inverse ? 0 : R32_TW_STRIDED)) * sizeof(uint32_t);
+    (void)inverse;
+    return (size_t)2 * (R32_BUF_WORDS + R32_TW_STRIDED) * sizeof(uint32_t);
 }
 // Word k (0..30) of a uniform-stage block: layer jj and index h within its run of 16 >> jj.
 __device__ __forceinline__ void uniform_slot(int k, int& jj, int& h) {
@@ -172,7 +165,7 @@ struct R32Pass {
 // that both the stage-1 pattern (row p, word tm) and the 128-bit stage-2 pattern (row tm, chunk q)
 // are free of bank conflicts.
 template <bool INVERSE>
-__global__ void __launch_bounds__(32 * R32_CONTIG_WARPS, (INVERSE ? 24 : 16) / R32_CONTIG_WARPS)
+__global__ void __launch_bounds__(32 * R32_CONTIG_WARPS, 16 / R32_CONTIG_WARPS)
     fft_r32_contig_kernel(uint32_t* const* __restrict__ dst_cols, const uint32_t* const* __restrict__ src_cols,
                           uint32_t src_mask, int ncols, int log_n, int dom_log, R32Pass ps,
                           const uint32_t* __restrict__ tower, uint32_t scale) {
@@ -201,7 +194,7 @@ __global__ void __launch_bounds__(32 * R32_CONTIG_WARPS, (INVERSE ? 24 : 16) / R
             const int r = k * 4 + (tm >> 3), q = tm & 7;  // chunk c = 32 k + tm: row c / 8, chunk c % 8
             cp_async16(buf + r * 32 + ((q ^ (r & 7)) << 2), src + ((base + r * 32 + q * 4) & src_mask));
         }
-        if (!INVERSE) {
+        {
             uint32_t* tw = tw0 + b * R32_TW_CONTIG;
             // per-thread stage: chunk c of 120 (16 bytes each): layers 1, 2, 3, 4 hold 64, 32, 16, 8 chunks
 #pragma unroll
@@ -262,16 +255,20 @@ __global__ void __launch_bounds__(32 * R32_CONTIG_WARPS, (INVERSE ? 24 : 16) / R
                 v[4 * q] = x.x; v[4 * q + 1] = x.y; v[4 * q + 2] = x.z; v[4 * q + 3] = x.w;
             }
             __syncwarp();
-            const uint32_t* tb[5];
-            tower_ptrs<true>(tb, tower, dom_log, 0, (unit << 5) | tm);
-            radix32_stage<true, true>(v, tb, 0, ps.act_lo, ps.act_hi);
+            const uint32_t* tw = tw0 + cur * R32_TW_CONTIG;
+            {
+                const uint32_t* tb[5] = {tw + 8 * tm, tw + 8 * tm, tw + 256 + 4 * tm, tw + 384 + 2 * tm, tw + 448 + tm};
+                radix32_stage<true, true>(v, tb, 0, ps.act_lo, ps.act_hi);
+            }
 #pragma unroll
             for (int p = 0; p < 32; p++) s[33 * tm + p] = v[p];
             __syncwarp();
 #pragma unroll
             for (int p = 0; p < 32; p++) v[p] = s[33 * p + tm];
-            tower_ptrs<false>(tb, tower, dom_log, 5, unit);
-            radix32_stage<true, false>(v, tb, 5, ps.act_lo, ps.act_hi);
+            {
+                const uint32_t* tb[5] = {tw + 480, tw + 496, tw + 504, tw + 508, tw + 510};
+                radix32_stage<true, false>(v, tb, 5, ps.act_lo, ps.act_hi);
+            }
 #pragma unroll
             for (int p = 0; p < 32; p++) dst[base + tm + 32 * p] = scale ? m31_mul(v[p], scale) : v[p];
         }
@@ -312,7 +309,7 @@ __global__ void __launch_bounds__(256, INVERSE ? 3 : 2)
             const uint32_t m = c >> 1, half = c & 1;
             cp_async16(buf + 8 * m + 8 * (m >> 5) + 4 * half, src + ((base | (m << ps.lo) | (half << 2)) & src_mask));
         }
-        if (!INVERSE) {
+        {
             uint32_t* tw = tw0 + b * R32_TW_STRIDED;
             const int c = threadIdx.x;  // chunk c of 248: layers lo+0..lo+4 hold 128, 64, 32, 16, 8 chunks
             if (c < 248) {
@@ -366,16 +363,20 @@ __global__ void __launch_bounds__(256, INVERSE ? 3 : 2)
         } else {
 #pragma unroll
             for (int p = 0; p < 32; p++) v[p] = s[264 * tm + 8 * p + w];
-            const uint32_t* tb[5];
-            tower_ptrs<false>(tb, tower, dom_log, ps.lo, (a << 5) | tm);
-            radix32_stage<true, false>(v, tb, 0, ps.act_lo, ps.act_hi);
+            const uint32_t* tw = tw0 + cur * R32_TW_STRIDED;
+            {
+                const uint32_t* tb[5] = {tw + 16 * tm, tw + 512 + 8 * tm, tw + 768 + 4 * tm, tw + 896 + 2 * tm, tw + 960 + tm};
+                radix32_stage<true, false>(v, tb, 0, ps.act_lo, ps.act_hi);
+            }
 #pragma unroll
             for (int p = 0; p < 32; p++) s[264 * tm + 8 * p + w] = v[p];
             __syncthreads();
 #pragma unroll
             for (int p = 0; p < 32; p++) v[p] = s[264 * p + 8 * tm + w];
-            tower_ptrs<false>(tb, tower, dom_log, ps.lo + 5, a);
-            radix32_stage<true, false>(v, tb, 5, ps.act_lo, ps.act_hi);
+            {
+                const uint32_t* tb[5] = {tw + 992, tw + 1008, tw + 1016, tw + 1020, tw + 1022};
+                radix32_stage<true, false>(v, tb, 5, ps.act_lo, ps.act_hi);
+            }
 #pragma unroll
             for (int p = 0; p < 32; p++) {
                 uint32_t x = scale ? m31_mul(v[p], scale) : v[p];
