@@ -541,11 +541,40 @@ def run_freivalds(args, rank):
             t_acc.append(ctx.event_elapsed_ms(1, 2))
     cells = (pq + n_mats * pk + 4) * R
     sc, ac = float(np.mean(t_sc)), float(np.mean(t_acc))
+    gpu_ref = None
+    if not args.no_gpu_baseline:
+        try:  # the reference's own device chain on the same inputs (host clock around its blocking calls)
+            import oracle
+            from oracle import ref_cuda
+
+            if ref_cuda.available():
+                ref = ref_cuda.RefCudaFreivalds()
+                s_pow, rv_pow = oracle.secure_powers(s, pq + 1), oracle.secure_powers(rv, pk + 1)
+                rs, ra = [], []
+                for it in range(3):
+                    ref.sync()
+                    t0 = time.perf_counter()
+                    r_base, r_pre, r_m, r_c = ref.scatter(qx, qws, grid, pq, pk)
+                    ref.sync()
+                    t1 = time.perf_counter()
+                    r_out, _ = ref.acc(r_base, r_pre, grid, pq, pk, n_mats, s, rv, s_pow[:pq], rv_pow[:pk], s_pow[pq], rv_pow[pk])
+                    ref.sync()
+                    t2 = time.perf_counter()
+                    for p_ in r_base + r_pre + r_out + [r_m, r_c]:
+                        ref.free(p_)
+                    if it:
+                        rs.append(t1 - t0)
+                        ra.append(t2 - t1)
+                gpu_ref = {"kind": "the reference's CUDA kernels, compiled unmodified for sm_100a, same GPU",
+                           "scatter_ms_including_its_upload": 1e3 * float(np.mean(rs)), "acc_ms": 1e3 * float(np.mean(ra))}
+        except Exception as e:
+            gpu_ref = {"unavailable": repr(e)}
     print(json.dumps({"metric": "freivalds_cells_per_s", "value": cells / ((sc + ac) * 1e-3), "unit": "cells/s", "n_gpus": 1,
                       "steps": args.steps, "warmup": args.warmup, "ms_per_step": sc + ac, "higher_is_better": True,
                       "config": {"workload": "freivalds_nin4096_nout4096_tokens32_chunks256_2mats", "rows": R, "pq": pq, "pk": pk},
                       "scatter_ms": sc, "scatter_gbs": (cells * 4 + n_mats * n_in * n_out) / (sc * 1e-3) / 1e9,
-                      "acc_ms": ac, "acc_gbs": (4.0 * (pq + n_mats * pk) * R + 16.0 * (1 + 2 * n_mats) * R) / (ac * 1e-3) / 1e9}))
+                      "acc_ms": ac, "acc_gbs": (4.0 * (pq + n_mats * pk) * R + 16.0 * (1 + 2 * n_mats) * R) / (ac * 1e-3) / 1e9,
+                      "gpu_baseline": gpu_ref}))
     ctx.close()
 
 
