@@ -160,6 +160,13 @@ int zkb_fold_line_dalpha(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* c
 int zkb_fold_circle_into_line_dalpha(zkb_ctx* ctx, uint32_t* const dst[4], const uint32_t* const src[4], int log_n_src,
                                      const uint32_t* d_alpha);
 int zkb_channel_mix_root_draw(zkb_ctx* ctx, uint32_t* d_chan, const uint32_t* d_root, uint32_t* d_alpha, uint32_t* d_root_copy);
+/* The same, and `leaves` (2^(log_n - 1) x 8 words) receives the Blake2s-M31 leaf hashes of the folded layer
+ * (what zkb_merkle_layer(log_n - 1, NULL, the four output columns) would write): the next FRI tree starts from
+ * them. log_n >= 2 for the line fold (at least two leaves), log_n_src >= 3 for the circle fold. */
+int zkb_fold_line_dalpha_leaves(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* const in[4], int log_n, const uint32_t* d_alpha,
+                                uint32_t* leaves);
+int zkb_fold_circle_into_line_dalpha_leaves(zkb_ctx* ctx, uint32_t* const dst[4], const uint32_t* const src[4], int log_n_src,
+                                            const uint32_t* d_alpha, uint32_t* leaves);
 /* fold_line with fold_step 1: in on the line domain Coset::half_odds(log_n); out has 2^(log_n-1). */
 int zkb_fold_line(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* const in[4], int log_n,
                   const uint32_t h_alpha[4]);

@@ -415,3 +415,13 @@ def test_device_channel_step_and_folds_with_device_challenge(ctx, oracle):
         ctx.fold_circle_into_line([b.ptr for b in c1], [b.ptr for b in bi], log_n, alphas[2])
         ctx.fold_circle_into_line_dalpha([b.ptr for b in c2], [b.ptr for b in bi], log_n, d_alpha.ptr + 32)
         assert all((a.download() == b.download()).all() for a, b in zip(c1, c2))
+        # the variants that also hash the folded layer's Merkle leaves
+        o3, lv, want_lv = [ctx.alloc(n // 2) for _ in range(4)], ctx.alloc(4 * n), ctx.alloc(4 * n)
+        ctx.fold_line_dalpha_leaves([b.ptr for b in o3], [b.ptr for b in bi], log_n, d_alpha.ptr + 16, lv.ptr)
+        ctx.merkle_layer(log_n - 1, 0, [b.ptr for b in o1], want_lv.ptr)
+        assert all((a.download() == b.download()).all() for a, b in zip(o1, o3)) and (lv.download() == want_lv.download()).all()
+        if log_n >= 3:
+            c3 = [ctx.upload(c) for c in dst]
+            ctx.fold_circle_into_line_dalpha_leaves([b.ptr for b in c3], [b.ptr for b in bi], log_n, d_alpha.ptr + 32, lv.ptr)
+            ctx.merkle_layer(log_n - 1, 0, [b.ptr for b in c1], want_lv.ptr)
+            assert all((a.download() == b.download()).all() for a, b in zip(c1, c3)) and (lv.download() == want_lv.download()).all()

@@ -16,7 +16,7 @@ EXPORTED_SYMBOLS = [
     "zkb_malloc", "zkb_free", "zkb_memset_zero", "zkb_h2d", "zkb_d2h", "zkb_h2d_async", "zkb_d2h_async", "zkb_h2d_overlapped", "zkb_wait_fence", "zkb_d2d",
     "zkb_host_alloc_pinned", "zkb_host_free_pinned", "zkb_gather_multi", "zkb_gather_hashes", "zkb_gather_words", "zkb_twiddles_d2h",
     "zkb_ifft_cols", "zkb_lde_cols", "zkb_eval_at_point_cols", "zkb_bit_reverse_m31", "zkb_bit_reverse_qm31",
-    "zkb_merkle_layer", "zkb_merkle_leaves_partial", "zkb_merkle_top", "zkb_fold_line_dalpha", "zkb_fold_circle_into_line_dalpha", "zkb_channel_mix_root_draw", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine",
+    "zkb_merkle_layer", "zkb_merkle_leaves_partial", "zkb_merkle_top", "zkb_fold_line_dalpha", "zkb_fold_circle_into_line_dalpha", "zkb_channel_mix_root_draw", "zkb_fold_line_dalpha_leaves", "zkb_fold_circle_into_line_dalpha_leaves", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine",
     "zkb_accumulate", "zkb_lift_accumulate", "zkb_secure_powers", "zkb_gkr_eq_evals", "zkb_gkr_next_layer",
     "zkb_gkr_sum", "zkb_gkr_fix_and_sum", "zkb_mle_fix_qm31", "zkb_mle_fix_m31", "zkb_grind", "zkb_gkr_sum_noalloc", "zkb_gkr_sum_noalloc_error",
     "zkb_freivalds_scatter", "zkb_freivalds_acc",
@@ -294,6 +294,14 @@ class Context:
     def fold_circle_into_line_dalpha(self, dst4, src4, log_n_src, d_alpha):
         self._check(self.lib.zkb_fold_circle_into_line_dalpha(self.h, _ptr_array(dst4), _ptr_array(src4), C.c_int(log_n_src),
                                                               C.c_void_p(d_alpha)))
+
+    def fold_line_dalpha_leaves(self, out4, in4, log_n, d_alpha, leaves_ptr):
+        self._check(self.lib.zkb_fold_line_dalpha_leaves(self.h, _ptr_array(out4), _ptr_array(in4), C.c_int(log_n), C.c_void_p(d_alpha),
+                                                         C.c_void_p(leaves_ptr)))
+
+    def fold_circle_into_line_dalpha_leaves(self, dst4, src4, log_n_src, d_alpha, leaves_ptr):
+        self._check(self.lib.zkb_fold_circle_into_line_dalpha_leaves(self.h, _ptr_array(dst4), _ptr_array(src4), C.c_int(log_n_src),
+                                                                     C.c_void_p(d_alpha), C.c_void_p(leaves_ptr)))
 
     def channel_mix_root_draw(self, d_chan, d_root, d_alpha, d_root_copy=0):
         self._check(self.lib.zkb_channel_mix_root_draw(self.h, C.c_void_p(d_chan), C.c_void_p(d_root), C.c_void_p(d_alpha),

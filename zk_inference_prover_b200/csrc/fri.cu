@@ -6,6 +6,7 @@
 // (nitroo/crates/stwo/src/prover/backend/cpu/fri.rs:67-123). The inverse coordinates come from the
 // inverse twiddle tower: pair i of the line domain Coset::half_odds(k) uses T_k^-1[i]; pair i of
 // the canonic circle domain of log size L uses the y of point i of Coset::half_odds(L-1).
+#include "blake2s.cuh"
 #include "common.cuh"
 
 namespace zk {
@@ -36,8 +37,24 @@ __device__ __forceinline__ qm31 load_alpha(const uint32_t* __restrict__ d_alpha,
     return alpha;
 }
 
+// The folded value is the next FRI layer's Merkle leaf (its four coordinates are the layer's four columns,
+// prover/fri.rs:169-188): hashing it here saves the leaf launch and the re-read of the layer.
+__device__ __forceinline__ void store_leaf(uint32_t* __restrict__ leaves, size_t i, qm31 r) {
+    uint32_t h[8], m[16];
+    blake2s_init(h);
+#pragma unroll
+    for (int k = 0; k < 4; k++) m[k] = r.c[k];
+#pragma unroll
+    for (int k = 4; k < 16; k++) m[k] = 0u;
+    blake2s_compress(h, m, 16u, true);
+    uint4* o = reinterpret_cast<uint4*>(leaves + 8 * i);
+    o[0] = make_uint4(reduce_word_m31(h[0]), reduce_word_m31(h[1]), reduce_word_m31(h[2]), reduce_word_m31(h[3]));
+    o[1] = make_uint4(reduce_word_m31(h[4]), reduce_word_m31(h[5]), reduce_word_m31(h[6]), reduce_word_m31(h[7]));
+}
+
 __global__ void __launch_bounds__(256) fold_line_kernel(Secure4 out, Secure4C in, int log_n, qm31 alpha,
-                                                        const uint32_t* __restrict__ d_alpha, const uint32_t* __restrict__ itw) {
+                                                        const uint32_t* __restrict__ d_alpha, const uint32_t* __restrict__ itw,
+                                                        uint32_t* __restrict__ leaves = nullptr) {
     alpha = load_alpha(d_alpha, alpha);
     size_t half = (size_t)1 << (log_n - 1);
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -46,6 +63,7 @@ __global__ void __launch_bounds__(256) fold_line_kernel(Secure4 out, Secure4C in
     qm31 r = fold_pair(in, i, t, alpha);
 #pragma unroll
     for (int k = 0; k < 4; k++) out.c[k][i] = r.c[k];
+    if (leaves) store_leaf(leaves, i, r);
 }
 
 // log_n == 1, 2 of the line fold and small circle domains need points that are not in the tower
@@ -67,7 +85,8 @@ __global__ void fold_small_kernel(Secure4 out, Secure4C in, int n_out, qm31 alph
 }
 
 __global__ void __launch_bounds__(256) fold_circle_kernel(Secure4 dst, Secure4C src, int log_n_src, qm31 alpha,
-                                                          const uint32_t* __restrict__ d_alpha, const uint32_t* __restrict__ itw) {
+                                                          const uint32_t* __restrict__ d_alpha, const uint32_t* __restrict__ itw,
+                                                          uint32_t* __restrict__ leaves = nullptr) {
     alpha = load_alpha(d_alpha, alpha);
     const qm31 alpha_sq = qm31_sqr(alpha);
     size_t half = (size_t)1 << (log_n_src - 1);
@@ -80,6 +99,7 @@ __global__ void __launch_bounds__(256) fold_circle_kernel(Secure4 dst, Secure4C 
     qm31 r = qm31_add(qm31_mul(d, alpha_sq), f);
 #pragma unroll
     for (int k = 0; k < 4; k++) dst.c[k][i] = r.c[k];
+    if (leaves) store_leaf(leaves, i, r);
 }
 
 }  // namespace zk
@@ -102,7 +122,7 @@ static uint32_t host_bitrev(uint32_t i, int bits) {
 }
 
 static int fold_line_impl(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* const in[4], int log_n,
-                          const uint32_t* h_alpha, const uint32_t* d_alpha) {
+                          const uint32_t* h_alpha, const uint32_t* d_alpha, uint32_t* leaves = nullptr) {
     if (!ctx) return ZKB_EINVAL;
     ZKB_CHECK_ARG(ctx, out && in && (h_alpha || d_alpha) && log_n >= 1 && log_n <= ctx->max_log - 1);
     ZKB_CHECK_ARG(ctx, ((uintptr_t)d_alpha & 15) == 0);
@@ -118,13 +138,13 @@ static int fold_line_impl(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* 
     DeviceGuard g(ctx);
     size_t half = (size_t)1 << (log_n - 1);
     ProfScope prof(ctx, "fold_line_kernel");
-    fold_line_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n, alpha, d_alpha, ctx->itw);
+    fold_line_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n, alpha, d_alpha, ctx->itw, leaves);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }
 
 static int fold_circle_impl(zkb_ctx* ctx, uint32_t* const dst[4], const uint32_t* const src[4], int log_n_src,
-                            const uint32_t* h_alpha, const uint32_t* d_alpha) {
+                            const uint32_t* h_alpha, const uint32_t* d_alpha, uint32_t* leaves = nullptr) {
     if (!ctx) return ZKB_EINVAL;
     ZKB_CHECK_ARG(ctx, dst && src && (h_alpha || d_alpha) && log_n_src >= 1 && log_n_src <= ctx->max_log);
     ZKB_CHECK_ARG(ctx, ((uintptr_t)d_alpha & 15) == 0);
@@ -138,6 +158,7 @@ static int fold_circle_impl(zkb_ctx* ctx, uint32_t* const dst[4], const uint32_t
     qm31 alpha = qm31_zero();
     if (h_alpha) alpha = qm31{{h_alpha[0], h_alpha[1], h_alpha[2], h_alpha[3]}};
     DeviceGuard g(ctx);
+    if (log_n_src <= 2 && leaves) return set_error(ctx, ZKB_EINVAL, "fold with leaf hashing needs at least 8 source points");
     if (log_n_src <= 2) {
         // Points i of Coset::half_odds(log_n_src - 1), bit-reversed: index 2^(31-(L-1)-2) + j * 2^(31-(L-1)).
         int hl = log_n_src - 1;
@@ -153,7 +174,7 @@ static int fold_circle_impl(zkb_ctx* ctx, uint32_t* const dst[4], const uint32_t
     }
     size_t half = (size_t)1 << (log_n_src - 1);
     ProfScope prof(ctx, "fold_circle_kernel");
-    fold_circle_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n_src, alpha, d_alpha, ctx->itw);
+    fold_circle_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n_src, alpha, d_alpha, ctx->itw, leaves);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }
@@ -177,6 +198,17 @@ int zkb_fold_circle_into_line_dalpha(zkb_ctx* ctx, uint32_t* const dst[4], const
                                      const uint32_t* d_alpha) {
     if (ctx && !d_alpha) return zk::set_error(ctx, ZKB_EINVAL, "zkb_fold_circle_into_line_dalpha: null alpha");
     return fold_circle_impl(ctx, dst, src, log_n_src, nullptr, d_alpha);
+}
+
+int zkb_fold_line_dalpha_leaves(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* const in[4], int log_n, const uint32_t* d_alpha,
+                                uint32_t* leaves) {
+    if (ctx && (!d_alpha || !leaves || ((uintptr_t)leaves & 15))) return zk::set_error(ctx, ZKB_EINVAL, "zkb_fold_line_dalpha_leaves: bad argument");
+    return fold_line_impl(ctx, out, in, log_n, nullptr, d_alpha, leaves);
+}
+int zkb_fold_circle_into_line_dalpha_leaves(zkb_ctx* ctx, uint32_t* const dst[4], const uint32_t* const src[4], int log_n_src,
+                                            const uint32_t* d_alpha, uint32_t* leaves) {
+    if (ctx && (!d_alpha || !leaves || ((uintptr_t)leaves & 15))) return zk::set_error(ctx, ZKB_EINVAL, "zkb_fold_circle_into_line_dalpha_leaves: bad argument");
+    return fold_circle_impl(ctx, dst, src, log_n_src, nullptr, d_alpha, leaves);
 }
 
 }  // extern "C"

@@ -239,10 +239,26 @@ struct B200Backend {
         d.check(zkb_fold_line_dalpha(d.ctx(), o.data(), i.data(), (int)log_n, d_alpha));
         return out;
     }
-    static void fold_circle_into_line(const Device& d, SecureColumnByCoords& dst, const SecureColumnByCoords& src, const uint32_t* d_alpha) {
+    static void fold_circle_into_line(const Device& d, SecureColumnByCoords& dst, const SecureColumnByCoords& src, const uint32_t* d_alpha,
+                                      HashColumn* leaves = nullptr) {
         auto o = dst.ptrs();
         auto i = src.cptrs();
-        d.check(zkb_fold_circle_into_line_dalpha(d.ctx(), o.data(), i.data(), (int)src.columns[0].log_size(), d_alpha));
+        if (leaves) {
+            *leaves = HashColumn(d, 8 * dst.len());
+            d.check(zkb_fold_circle_into_line_dalpha_leaves(d.ctx(), o.data(), i.data(), (int)src.columns[0].log_size(), d_alpha, leaves->ptr()));
+        } else {
+            d.check(zkb_fold_circle_into_line_dalpha(d.ctx(), o.data(), i.data(), (int)src.columns[0].log_size(), d_alpha));
+        }
+    }
+    // fold_line that also hashes the folded layer's Merkle leaves (the layer's four columns are its coordinates)
+    static SecureColumnByCoords fold_line(const Device& d, const SecureColumnByCoords& eval, const uint32_t* d_alpha, HashColumn& leaves) {
+        uint32_t log_n = eval.columns[0].log_size();
+        SecureColumnByCoords out(d, eval.len() / 2);
+        leaves = HashColumn(d, 8 * (eval.len() / 2));
+        auto o = out.ptrs();
+        auto i = eval.cptrs();
+        d.check(zkb_fold_line_dalpha_leaves(d.ctx(), o.data(), i.data(), (int)log_n, d_alpha, leaves.ptr()));
+        return out;
     }
     static void fold_circle_into_line(const Device& d, SecureColumnByCoords& dst, const SecureColumnByCoords& src, qm31 alpha) {
         auto o = dst.ptrs();

@@ -254,12 +254,18 @@ struct FriProver {
             d.check(zkb_h2d(d.ctx(), chan, st, sizeof(st)));
             fp.first_tree = MerkleProver::commit(d, column.refs());
             d.check(zkb_channel_mix_root_draw(d.ctx(), chan, fp.first_tree.layers[0].ptr(), alphas, roots));
-            B200Backend::fold_circle_into_line(d, layer, column, alphas);
+            // every fold but the last also hashes the leaves of the layer it produces: that layer is committed next
+            HashColumn leaves;
+            bool have_leaves = n_layers > 1 && first_log >= 3;
+            B200Backend::fold_circle_into_line(d, layer, column, alphas, have_leaves ? &leaves : nullptr);
             for (size_t k = 1; k < n_layers; k++) {
                 Inner in{std::move(layer), {}, 1};
-                in.tree = MerkleProver::commit(d, in.eval.refs());
+                std::vector<const BaseColumn*> refs = in.eval.refs();
+                in.tree = MerkleProver::commit(d, refs, have_leaves ? &leaves : nullptr);
                 d.check(zkb_channel_mix_root_draw(d.ctx(), chan, in.tree.layers[0].ptr(), alphas + 4 * k, roots + 8 * k));
-                layer = B200Backend::fold_line(d, in.eval, alphas + 4 * k);
+                have_leaves = k + 1 < n_layers;
+                if (have_leaves) layer = B200Backend::fold_line(d, in.eval, alphas + 4 * k, leaves);
+                else layer = B200Backend::fold_line(d, in.eval, alphas + 4 * k);
                 fp.inner.push_back(std::move(in));
             }
             std::vector<uint32_t> h = fs.to_cpu();  // one copy, one synchronisation
