@@ -323,6 +323,29 @@ def run_ours(args, rank, world, local_rank):
     ctx.profile_begin()
     ctx.pcs_prove_device([work_ptrs], [log_n] * ncols, **kw)
     kernels = ctx.profile_end()
+    # operators of the workload that the proof does not time on their own: bit reversal of extended columns,
+    # the first circle fold and the first line fold (algorithmic bytes: 8n, 34n, 26n for n source elements)
+    standalone = {}
+    if rank == 0:
+        nb = min(ncols, 32)
+        cols_b = [ctx.alloc(N) for _ in range(nb)]
+        sec = [ctx.alloc(N) for _ in range(4)]
+        half = [ctx.alloc(N // 2).zero() for _ in range(4)]
+        quarter = [ctx.alloc(N // 4) for _ in range(4)]
+        alpha = np.array([5, 6, 7, 8], np.uint32)
+        for rep in range(2):
+            ctx.event_record(2)
+            for c in cols_b:
+                ctx.bit_reverse_m31(c.ptr, log_out)
+            ctx.event_record(3)
+            ctx.fold_circle_into_line([h_.ptr for h_ in half], [s_.ptr for s_ in sec], log_out, alpha)
+            ctx.event_record(4)
+            ctx.fold_line([q.ptr for q in quarter], [h_.ptr for h_ in half], log_out - 1, alpha)
+            ctx.event_record(5)
+        standalone = {"bit_reverse": 8.0 * N * nb / (ctx.event_elapsed_ms(2, 3) * 1e-3) / 1e9,
+                      "fold_circle_into_line": 34.0 * N / (ctx.event_elapsed_ms(3, 4) * 1e-3) / 1e9,
+                      "fold_line": 26.0 * (N // 2) / (ctx.event_elapsed_ms(4, 5) * 1e-3) / 1e9}
+        del cols_b, sec, half, quarter
     e2e_ms, words_e2e = timed(True, False)
     assert len(words_dev) == len(words_e2e) and (words_dev == words_e2e).all(), "resident and end-to-end legs disagree"
 
@@ -360,8 +383,10 @@ def run_ours(args, rank, world, local_rank):
                     "per_operator_gbs": {
                         "interpolate": ab["interpolate"] / (sum(v[0] for k, v in kernels.items() if "inverse" in k) * 1e-3) / 1e9,
                         "extend": achieved,
-                        "merkle_leaves": ab["merkle_leaves"] / (max((v[0] / v[1] for k, v in kernels.items() if "columns" in k), default=1e9) * 1e-3) / 1e9,
-                        "quot_numerators": ab["quot_numerators"] / (kernels.get("quot_numerators_kernel", (1e9, 1))[0] * 1e-3) / 1e9}}
+                        "merkle_leaves": ab["merkle_leaves"] / (kernels.get("merkle_layer_kernel(leaves)", (1e9, 1))[0] * 1e-3) / 1e9,
+                        "quot_numerators": ab["quot_numerators"] / (kernels.get("quot_numerators_kernel", (1e9, 1))[0] * 1e-3) / 1e9,
+                        **standalone}}
+        roofline["per_operator_frac_of_hbm_peak"] = {k: v / peak for k, v in roofline["per_operator_gbs"].items()}
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             sample_cols = min(ncols, args.ref_cols)

@@ -195,7 +195,7 @@ int zkb_merkle_layer(zkb_ctx* ctx, int log_size, const uint32_t* prev, const uin
     size_t n = (size_t)1 << log_size;
     unsigned threads = n < 256 ? 32 : 256;
     unsigned blocks = (unsigned)((n + threads - 1) / threads);
-    ProfScope prof(ctx, ncols ? "merkle_layer_kernel(columns)" : "merkle_layer_kernel(nodes only)");
+    ProfScope prof(ctx, !ncols ? "merkle_layer_kernel(nodes only)" : (!prev && ncols > 16 ? "merkle_layer_kernel(leaves)" : "merkle_layer_kernel(columns)"));
     merkle_layer_kernel<<<blocks, threads, 0, ctx->stream>>>(log_size, prev, (const uint32_t* const*)d_cols, ncols, m31_out,
                                                              out);
     ZKB_LAUNCH_CHECK(ctx);
