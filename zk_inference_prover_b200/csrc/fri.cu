@@ -66,6 +66,59 @@ __global__ void __launch_bounds__(256) fold_line_kernel(Secure4 out, Secure4C in
     if (leaves) store_leaf(leaves, i, r);
 }
 
+// Two output elements per thread: one 16-byte load per coordinate column brings both pairs, and twice the bytes
+// are in flight per thread (these kernels wait on memory, not on arithmetic).
+__device__ __forceinline__ void fold_pair2(const Secure4C& in, size_t i2, uint32_t t0, uint32_t t1, qm31 alpha, qm31& r0, qm31& r1) {
+    qm31 a0, b0, a1, b1;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        uint4 v = reinterpret_cast<const uint4*>(in.c[k])[i2];
+        a0.c[k] = v.x; b0.c[k] = v.y; a1.c[k] = v.z; b1.c[k] = v.w;
+    }
+    r0 = qm31_add(qm31_add(a0, b0), qm31_mul(alpha, qm31_mul_m31(qm31_sub(a0, b0), t0)));
+    r1 = qm31_add(qm31_add(a1, b1), qm31_mul(alpha, qm31_mul_m31(qm31_sub(a1, b1), t1)));
+}
+
+__global__ void __launch_bounds__(256) fold_line_kernel2(Secure4 out, Secure4C in, int log_n, qm31 alpha,
+                                                         const uint32_t* __restrict__ d_alpha, const uint32_t* __restrict__ itw,
+                                                         uint32_t* __restrict__ leaves) {
+    alpha = load_alpha(d_alpha, alpha);
+    const size_t half = (size_t)1 << (log_n - 1);
+    const size_t i2 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (2 * i2 >= half) return;
+    const uint2 t = reinterpret_cast<const uint2*>(itw + half)[i2];
+    qm31 r0, r1;
+    fold_pair2(in, i2, t.x, t.y, alpha, r0, r1);
+#pragma unroll
+    for (int k = 0; k < 4; k++) reinterpret_cast<uint2*>(out.c[k])[i2] = make_uint2(r0.c[k], r1.c[k]);
+    if (leaves) { store_leaf(leaves, 2 * i2, r0); store_leaf(leaves, 2 * i2 + 1, r1); }
+}
+
+__global__ void __launch_bounds__(256) fold_circle_kernel2(Secure4 dst, Secure4C src, int log_n_src, qm31 alpha,
+                                                           const uint32_t* __restrict__ d_alpha, const uint32_t* __restrict__ itw,
+                                                           uint32_t* __restrict__ leaves) {
+    alpha = load_alpha(d_alpha, alpha);
+    const qm31 alpha_sq = qm31_sqr(alpha);
+    const size_t half = (size_t)1 << (log_n_src - 1);
+    const size_t i2 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (2 * i2 >= half) return;
+    uint32_t ix, iy0, iy1;
+    half_coset_point(itw, log_n_src, (uint32_t)(2 * i2), ix, iy0);
+    half_coset_point(itw, log_n_src, (uint32_t)(2 * i2 + 1), ix, iy1);
+    qm31 f0, f1;
+    fold_pair2(src, i2, iy0, iy1, alpha, f0, f1);
+    qm31 d0, d1;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        uint2 v = reinterpret_cast<const uint2*>(dst.c[k])[i2];
+        d0.c[k] = v.x; d1.c[k] = v.y;
+    }
+    const qm31 r0 = qm31_add(qm31_mul(d0, alpha_sq), f0), r1 = qm31_add(qm31_mul(d1, alpha_sq), f1);
+#pragma unroll
+    for (int k = 0; k < 4; k++) reinterpret_cast<uint2*>(dst.c[k])[i2] = make_uint2(r0.c[k], r1.c[k]);
+    if (leaves) { store_leaf(leaves, 2 * i2, r0); store_leaf(leaves, 2 * i2 + 1, r1); }
+}
+
 // log_n == 1, 2 of the line fold and small circle domains need points that are not in the tower
 // (T_k holds only half of each coset and starts at k = 1); they are passed in by the host.
 __global__ void fold_small_kernel(Secure4 out, Secure4C in, int n_out, qm31 alpha, const uint32_t* __restrict__ d_alpha,
@@ -137,8 +190,13 @@ static int fold_line_impl(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* 
     if (h_alpha) alpha = qm31{{h_alpha[0], h_alpha[1], h_alpha[2], h_alpha[3]}};
     DeviceGuard g(ctx);
     size_t half = (size_t)1 << (log_n - 1);
+    bool wide = log_n >= 3;
+    for (int k = 0; k < 4; k++) wide = wide && ((uintptr_t)in[k] & 15) == 0 && ((uintptr_t)out[k] & 7) == 0;
     ProfScope prof(ctx, "fold_line_kernel");
-    fold_line_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n, alpha, d_alpha, ctx->itw, leaves);
+    if (wide)
+        fold_line_kernel2<<<(unsigned)((half / 2 + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n, alpha, d_alpha, ctx->itw, leaves);
+    else
+        fold_line_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n, alpha, d_alpha, ctx->itw, leaves);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }
@@ -173,8 +231,13 @@ static int fold_circle_impl(zkb_ctx* ctx, uint32_t* const dst[4], const uint32_t
         return ZKB_OK;
     }
     size_t half = (size_t)1 << (log_n_src - 1);
+    bool wide = log_n_src >= 4;
+    for (int k = 0; k < 4; k++) wide = wide && ((uintptr_t)src[k] & 15) == 0 && ((uintptr_t)dst[k] & 7) == 0;
     ProfScope prof(ctx, "fold_circle_kernel");
-    fold_circle_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n_src, alpha, d_alpha, ctx->itw, leaves);
+    if (wide)
+        fold_circle_kernel2<<<(unsigned)((half / 2 + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n_src, alpha, d_alpha, ctx->itw, leaves);
+    else
+        fold_circle_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n_src, alpha, d_alpha, ctx->itw, leaves);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }
