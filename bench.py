@@ -603,6 +603,103 @@ def run_freivalds(args, rank):
     ctx.close()
 
 
+def run_constraints(args, rank):
+    """--mode constraints: evaluate_constraint_quotients_on_domain (zkb_constraint_quotients) for two AIRs of the reference at
+    2^20 trace rows, evaluation domain 2^21: the wide Fibonacci example with --cols columns (base-field arithmetic, bandwidth
+    heavy) and the Freivalds component at the scaled-segment shape pk = 16, pq = 1, two matrices, with its range check
+    (secure-field arithmetic). Inputs are resident; columns are larger than L2."""
+    if rank != 0:
+        return
+    import air_cases
+    import oracle
+    import zk_inference_prover_b200 as z
+    from util import m31_column, qm31_array
+    from zk_inference_prover_b200 import air
+
+    trace_log, eval_log = args.log_size, args.log_size + 1
+    N = 1 << eval_log
+    ctx = z.Context(device=0, max_log_size=10)
+    results = {}
+
+    def time_case(name, src, scalars_shift, n_cols_total):
+        prog = ctx.air_compile(src)
+        st = prog.stats
+        cols = [ctx.upload(m31_column(0x5EED0100 + c, N)) for c in range(n_cols_total)]
+        acc = [ctx.alloc(N).zero() for _ in range(4)]
+        rcp = qm31_array(0x5EED0101, src.n_constraints)
+        ts = []
+        for it in range(args.warmup + args.steps):
+            ctx.event_record(0)
+            ctx.constraint_quotients(prog, [c.ptr for c in cols], rcp, trace_log, eval_log, [a.ptr for a in acc], accumulate=True,
+                                     cumsum_shift=scalars_shift)
+            ctx.event_record(1)
+            ctx.sync()
+            if it >= args.warmup:
+                ts.append(ctx.event_elapsed_ms(0, 1))
+        ms = float(np.mean(ts))
+        bytes_alg = (4.0 * st["n_columns_read"] + 32.0) * N  # every column read once, the accumulator read and written
+        results[name] = {"ms": ms, "rows_per_s": N / (ms * 1e-3), "columns": n_cols_total, "constraints": int(src.n_constraints),
+                         "algorithmic_gbs": bytes_alg / (ms * 1e-3) / 1e9, "m31_gmults_per_s": st["m31_mults"] * N / (ms * 1e-3) / 1e9,
+                         "program": st}
+        return cols, rcp, ms, bytes_alg
+
+    ncols = args.cols
+    wf = air.wide_fibonacci(air.ExprEvaluator(), ncols).source()
+    cols, rcp, wf_ms, wf_bytes = time_case("wide_fibonacci", wf, None, ncols)
+    gpu_ref = None
+    if not args.no_gpu_baseline:
+        try:  # the reference's hand-written kernel for the same AIR on the same columns (it overwrites; host clock around its blocking call)
+            from oracle import ref_cuda
+
+            if ref_cuda.available():
+                ref = ref_cuda.RefCudaAir()
+                denom = oracle.constraint_denom_inv(trace_log, eval_log)
+                ptrs = [c.ptr for c in cols]
+                rt = []
+                for it in range(4):
+                    ref.sync()
+                    t0 = time.perf_counter()
+                    r_out = ref.wide_fibonacci_quotients(ptrs, rcp, denom, trace_log, eval_log)
+                    ref.sync()
+                    dt = time.perf_counter() - t0
+                    for p_ in r_out:
+                        ref.free(p_)
+                    if it:
+                        rt.append(dt)
+                gpu_ref = {"kind": "the reference's wide-Fibonacci CUDA kernel, compiled unmodified for sm_100a, same GPU, same columns",
+                           "ms_including_its_allocations": 1e3 * float(np.mean(rt))}
+        except Exception as e:
+            gpu_ref = {"unavailable": repr(e)}
+    del cols
+    pk, pq, n_mats = 16, 1, 2
+    fp = air_cases.freivalds_params(oracle, pk, pq, n_mats, 0x5EED0102)
+    rel = qm31_array(0x5EED0103, 2)
+    fr = air.freivalds(air.ExprEvaluator(), pk, pq, n_mats, fp["rv_pow"], fp["rv_step"], fp["s_pow"], fp["s_step"], qm31_array(0x5EED0104, n_mats),
+                       128, (rel[0], rel[1])).source()
+    time_case("freivalds_pk16_pq1_2mats_range_check", fr, qm31_array(0x5EED0105, 1)[0], int(sum(fr.tree_cols)))
+    cpu = None
+    if not args.no_cpu_baseline:
+        oracle.set_num_threads(len(os.sched_getaffinity(0)))
+        small_eval = 15
+        case = air_cases.wide_fibonacci_case(oracle, ncols, small_eval - 1, small_eval, 1)
+        t0 = time.perf_counter()
+        air_cases.by_air(oracle, case)
+        dt = time.perf_counter() - t0
+        cpu = {"value": ncols * (1 << (small_eval - 1)) / dt, "unit": "cells/s", "cores": oracle.num_threads(), "kind": "port",
+               "sample": f"wide Fibonacci, {ncols} columns, evaluation domain 2^{small_eval} ({dt:.2f} s), the oracle's CpuDomainEvaluator restatement"}
+    peak, peak_kind = measured_hbm_peak()
+    line = {"metric": "constraint_cells_per_s", "value": ncols * (1 << trace_log) / (wf_ms * 1e-3), "unit": "cells/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": wf_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "u32 (M31)", "data": "synthetic",
+            "config": {"workload": f"constraint_quotients_wide_fibonacci_{ncols}cols_log{trace_log}_eval_log{eval_log}", "l2": "columns (2 GiB) are larger than L2"},
+            "roofline": {"bound": "hbm", "kernel": "air_eval_kernel", "achieved": wf_bytes / (wf_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": wf_bytes / (wf_ms * 1e-3) / 1e9 / peak, "peak_kind": peak_kind, "traffic": None,
+                         "note": "algorithmic bytes: every column read once, the accumulator read and written"},
+            "gpu_launches": args.steps, "airs": results, "gpu_baseline": gpu_ref, "cpu_baseline": cpu}
+    print(json.dumps(line))
+    ctx.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -618,7 +715,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gpu-baseline", action="store_true")
     ap.add_argument("--gkr-log", type=int, default=24)
-    ap.add_argument("--mode", default="proof", choices=["proof", "sharded-commit", "gkr", "freivalds"],
+    ap.add_argument("--mode", default="proof", choices=["proof", "sharded-commit", "gkr", "freivalds", "constraints"],
                     help="proof: one whole PCS proof per rank (ranks are independent); sharded-commit: one commitment over all ranks")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -632,6 +729,8 @@ def main():
         run_gkr(args, rank)
     elif args.mode == "freivalds":
         run_freivalds(args, rank)
+    elif args.mode == "constraints":
+        run_constraints(args, rank)
     else:
         run_ours(args, rank, world, local_rank)
 

@@ -436,3 +436,50 @@ def freivalds_acc(base, pre, n_mats, grid, pq, pk, s4, rv4):
     lib().zko_freivalds_acc(_pp(b), _pp(p), C.c_uint32(n_mats), C.c_uint32(log_rows), C.c_uint32(groups), C.c_uint32(chunks),
                             C.c_uint32(lead), C.c_uint32(pq), C.c_uint32(pk), _p(s), _p(r), _pp(out), _p(claims))
     return np.stack(out), claims
+
+
+# ---- constraint quotients of an AIR (oracle/air.hpp)
+def offset_bit_reversed_circle_domain_index(i, domain_log, eval_log, offset):
+    f = lib().zko_offset_bit_reversed_circle_domain_index
+    f.restype = C.c_uint64
+    return int(f(C.c_uint64(i), C.c_uint32(domain_log), C.c_uint32(eval_log), C.c_int64(offset)))
+
+
+def constraint_denom_inv(trace_log, eval_log):
+    out = np.empty(1 << (eval_log - trace_log), np.uint32)
+    lib().zko_constraint_denom_inv(C.c_uint32(trace_log), C.c_uint32(eval_log), _p(out))
+    return out
+
+
+def _col_ptrs(cols):
+    cols = [None if c is None else _u32(c) for c in cols]
+    return cols, (C.c_void_p * len(cols))(*[None if c is None else c.ctypes.data for c in cols])
+
+
+def constraint_quotients_ssa(source, cols, rcp, trace_log, eval_log, accum=None, cumsum_shift=None, scalars=None):
+    """The lowered program interpreted row by row. cols: flat list (trees concatenated) of 2^eval_log-word arrays.
+    Returns the (4, 2^eval_log) accumulator; `accum` (same shape) is added to if given."""
+    ops, cons, trees = _u32(source.ops), _u32(source.constraints), _u32(source.tree_cols)
+    sc = _u32(source.scalars if scalars is None else scalars)
+    keep, ptrs = _col_ptrs(cols)
+    out = np.zeros((4, 1 << eval_log), np.uint32) if accum is None else _u32(accum).copy()
+    acc_ptrs = (C.c_void_p * 4)(*[out[k].ctypes.data for k in range(4)])
+    shift = _u32(cumsum_shift) if cumsum_shift is not None else None
+    rcp = _u32(rcp)
+    lib().zko_constraint_quotients_ssa(_p(ops), C.c_size_t(ops.shape[0]), _p(cons), C.c_size_t(cons.size), _p(trees), C.c_int(trees.size),
+                                       ptrs, _p(sc), C.c_size_t(sc.size // 4), _p(shift) if shift is not None else None, _p(rcp),
+                                       C.c_uint32(trace_log), C.c_uint32(eval_log), acc_ptrs, C.c_int(accum is not None))
+    return out
+
+
+def constraint_quotients_air(air, iparams, qparams, tree_cols, cols, rcp, trace_log, eval_log, accum=None, claimed_sum=None):
+    """The AIR written against CpuDomainEvaluator: air 0 wide Fibonacci, 1 Plonk, 2 Freivalds (parameters as in capi.cpp)."""
+    ip, qp, trees, rcp = _u32(iparams), _u32(qparams), _u32(tree_cols), _u32(rcp)
+    keep, ptrs = _col_ptrs(cols)
+    out = np.zeros((4, 1 << eval_log), np.uint32) if accum is None else _u32(accum).copy()
+    acc_ptrs = (C.c_void_p * 4)(*[out[k].ctypes.data for k in range(4)])
+    cs = _u32(claimed_sum) if claimed_sum is not None else None
+    lib().zko_constraint_quotients_air(C.c_int(air), _p(ip), _p(qp), _p(trees), C.c_int(trees.size), ptrs,
+                                       _p(cs) if cs is not None else None, _p(rcp), C.c_size_t(rcp.size // 4), C.c_uint32(trace_log),
+                                       C.c_uint32(eval_log), acc_ptrs, C.c_int(accum is not None))
+    return out

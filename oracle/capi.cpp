@@ -422,3 +422,77 @@ void zko_freivalds_acc(const uint32_t* const* base, const uint32_t* const* pre, 
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------- constraint quotients of an AIR
+#include "air.hpp"
+extern "C" {
+
+uint64_t zko_offset_bit_reversed_circle_domain_index(uint64_t i, uint32_t domain_log, uint32_t eval_log, int64_t offset) {
+    return offset_bit_reversed_circle_domain_index((size_t)i, domain_log, eval_log, offset);
+}
+
+void zko_constraint_denom_inv(uint32_t trace_log, uint32_t eval_log, uint32_t* out) {
+    std::vector<M31> d = constraint_denom_inv(trace_log, eval_log);
+    for (size_t i = 0; i < d.size(); i++) out[i] = d[i].v;
+}
+
+static TraceView trace_view(const uint32_t* tree_cols, int n_trees, const uint32_t* const* cols) {
+    TraceView t(n_trees);
+    size_t at = 0;
+    for (int k = 0; k < n_trees; k++)
+        for (uint32_t c = 0; c < tree_cols[k]; c++) t[k].push_back(cols[at++]);
+    return t;
+}
+
+// The lowered program, row by row (ops: n_ops x 5 words).
+void zko_constraint_quotients_ssa(const uint32_t* ops, size_t n_ops, const uint32_t* constraints, size_t n_constraints,
+                                  const uint32_t* tree_cols, int n_trees, const uint32_t* const* cols, const uint32_t* scalars,
+                                  size_t n_scalars, const uint32_t* cumsum_shift, const uint32_t* rcp, uint32_t trace_log,
+                                  uint32_t eval_log, uint32_t* const accum[4], int accumulate) {
+    TraceView t = trace_view(tree_cols, n_trees, cols);
+    std::vector<QM31> sc(n_scalars), coef(n_constraints);
+    for (size_t i = 0; i < n_scalars; i++) sc[i] = q_from(scalars + 4 * i);
+    for (size_t i = 0; i < n_constraints; i++) coef[i] = q_from(rcp + 4 * i);
+    QM31 shift = cumsum_shift ? q_from(cumsum_shift) : QM31::zero();
+    const AirOp* o = reinterpret_cast<const AirOp*>(ops);
+    accumulate_pointwise_cpu([&](size_t row) {
+        return air_interpret_row(o, n_ops, constraints, n_constraints, t, sc.data(), shift, coef.data(), row, trace_log, eval_log);
+    }, eval_log, trace_log, accum, accumulate != 0);
+}
+
+// The AIRs written against CpuDomainEvaluator. air: 0 wide Fibonacci (ip = {n_cols}), 1 Plonk (qp = {z, alpha^0, alpha^1}),
+// 2 Freivalds (ip = {pk, pq, n_mats, act_off, range_check}; qp = {rv_pow[pk], rv_step, s_pow[pq], s_step, claimed[n_mats], z, alpha^0}).
+void zko_constraint_quotients_air(int air, const uint32_t* ip, const uint32_t* qp, const uint32_t* tree_cols, int n_trees,
+                                  const uint32_t* const* cols, const uint32_t* claimed_sum, const uint32_t* rcp, size_t n_constraints,
+                                  uint32_t trace_log, uint32_t eval_log, uint32_t* const accum[4], int accumulate) {
+    TraceView t = trace_view(tree_cols, n_trees, cols);
+    std::vector<QM31> coef(n_constraints);
+    for (size_t i = 0; i < n_constraints; i++) coef[i] = q_from(rcp + 4 * i);
+    QM31 claimed = claimed_sum ? q_from(claimed_sum) : QM31::zero();
+    LookupElements plonk_rel;
+    FreivaldsEval fe{};
+    if (air == 1) {
+        plonk_rel.z = q_from(qp);
+        plonk_rel.alpha_powers = {q_from(qp + 4), q_from(qp + 8)};
+    } else if (air == 2) {
+        fe.pk = ip[0]; fe.pq = ip[1]; fe.n_mats = ip[2]; fe.act_off = ip[3]; fe.range_check = ip[4] != 0;
+        const uint32_t* q = qp;
+        for (size_t p = 0; p < fe.pk; p++, q += 4) fe.rv_pow.push_back(q_from(q));
+        fe.rv_step = q_from(q); q += 4;
+        for (size_t p = 0; p < fe.pq; p++, q += 4) fe.s_pow.push_back(q_from(q));
+        fe.s_step = q_from(q); q += 4;
+        for (size_t m = 0; m < fe.n_mats; m++, q += 4) fe.claimed.push_back(q_from(q));
+        fe.rel_act.z = q_from(q); q += 4;
+        fe.rel_act.alpha_powers = {q_from(q)};
+    }
+    accumulate_pointwise_cpu([&](size_t row) {
+        CpuDomainEvaluator eval(t, row, coef.data(), trace_log, eval_log, trace_log, claimed);
+        if (air == 0) wide_fibonacci_evaluate(eval, ip[0]);
+        else if (air == 1) plonk_evaluate(eval, plonk_rel);
+        else freivalds_evaluate(eval, fe);
+        assert(eval.constraint_index == n_constraints);
+        return eval.row_res;
+    }, eval_log, trace_log, accum, accumulate != 0);
+}
+
+}  // extern "C"

@@ -413,3 +413,29 @@ class RefCudaFreivalds(RefCudaMore):
         for p in (a, b, flags):
             self.free(p)
         return out, last[1 + n_mats:1 + 2 * n_mats]
+
+
+class RefCudaAir(RefCudaOps):
+    """The reference's hand-written constraint kernel for the wide Fibonacci example AIR
+    (stwo_cuda/cuda/evaluate_wide_fibonacci.cu:6-63, launcher :65-125; the AIR is
+    nitroo/crates/examples/src/wide_fibonacci/mod.rs:47-57)."""
+
+    def __init__(self):
+        super().__init__()
+        vp, u32 = C.c_void_p, C.c_uint32
+        f = self.lib.evaluate_wide_fibonacci_constraint_quotients_on_domain
+        f.restype = None
+        f.argtypes = [vp, vp, vp, vp, vp, u32, vp, u32, vp, vp, u32, u32, u32, u32]
+
+    def wide_fibonacci_quotients(self, col_ptrs, rcp, denom_inv, trace_log, eval_log):
+        """col_ptrs: device pointers of the n columns on the evaluation domain. Returns 4 device pointers (the kernel
+        overwrites its output: quotient = denom_inv * sum_i rcp[i] * constraint_i)."""
+        n = 1 << eval_log
+        out = [self.alloc_zero(n) for _ in range(4)]
+        d_rcp, d_den = self.upload(np.ascontiguousarray(rcp, np.uint32).reshape(-1)), self.upload(denom_inv)
+        table = (C.c_void_p * len(col_ptrs))(*col_ptrs)
+        self.lib.evaluate_wide_fibonacci_constraint_quotients_on_domain(out[0], out[1], out[2], out[3], None, 0, table, len(col_ptrs),
+                                                                        d_rcp, d_den, trace_log, eval_log, len(col_ptrs) - 2, 0)
+        self.free(d_rcp)
+        self.free(d_den)
+        return out

@@ -17,6 +17,10 @@ def test_header_symbols_are_exported(zkb):
     declared = set(re.findall(r"\b(zkb_[a-z0-9_]+)\s*\(", header))
     assert declared == set(zkb.PROVER_SYMBOLS)
     assert all(hasattr(lib, s) for s in declared)
+    header = open(os.path.join(ROOT, "include", "zkb200_air.h")).read()
+    declared = set(re.findall(r"\b(zkb_[a-z0-9_]+)\s*\(", header))
+    assert declared == set(zkb.AIR_SYMBOLS)
+    assert all(hasattr(lib, s) for s in declared)
 
 
 def test_no_oracle_in_product():

@@ -1,0 +1,95 @@
+"""Constraint quotients of an AIR on the CPU: the oracle against the reference's known answers, and the two routes
+through the oracle (AIRs written against CpuDomainEvaluator; the lowered single-assignment program) against each other."""
+import numpy as np
+import pytest
+
+import air_cases
+from util import P, m31_column, qm31_array
+
+
+def test_previous_index_known_answer(oracle):
+    """nitroo/crates/stwo/src/core/utils.rs:238-290: neighbours on the circle domain of log size 4."""
+    log_size, n = 4, 16
+    natural = np.arange(n)
+    bit_reversed = oracle.bit_reverse(natural.astype(np.uint32))
+    pairs = sorted((int(bit_reversed[i]), int(bit_reversed[oracle.offset_bit_reversed_circle_domain_index(i, log_size - 3, log_size, -1)]))
+                   for i in range(n))
+    expected = sorted([(0, 4), (15, 11), (1, 5), (14, 10), (2, 6), (13, 9), (3, 7), (12, 8), (4, 0), (11, 15), (5, 1), (10, 14), (6, 2),
+                       (9, 13), (7, 3), (8, 12)])
+    assert pairs == expected
+
+
+def test_offset_composes(oracle):
+    """core/utils.rs:214-236: offset -2 is two steps of -1."""
+    f = oracle.offset_bit_reversed_circle_domain_index
+    for i in range(64):
+        assert f(i, 3, 6, -2) == f(f(i, 3, 6, -1), 3, 6, -1)
+        assert f(f(i, 3, 6, 5), 3, 6, -5) == i
+
+
+@pytest.mark.parametrize("trace_log,eval_log", [(3, 4), (4, 6), (5, 8), (1, 3), (2, 3)])
+def test_denominator_inverses(oracle, zkb, trace_log, eval_log):
+    """denom_inv[row >> trace_log] inverts the trace domain's vanishing polynomial at every row of the evaluation domain
+    (core/constraints.rs:147-165 checks the same polynomial vanishes on its coset and nowhere else on the others)."""
+    d = oracle.constraint_denom_inv(trace_log, eval_log)
+    assert (d == zkb.capi.constraint_denom_inv(trace_log, eval_log)).all()
+    n = 1 << eval_log
+    rows = oracle.bit_reverse(np.arange(n, dtype=np.uint32))  # rows[r] = natural index of bit-reversed row r
+    for r in range(n):
+        x = int(oracle.domain_at(eval_log, int(rows[r]))[0])
+        for _ in range(1, trace_log):
+            x = (2 * x * x - 1) % P
+        assert x != 0 and oracle.m31_mul(x, int(d[r >> trace_log])) == 1
+    # and the same polynomial is zero on the trace domain itself
+    for i in range(1 << trace_log):
+        x = int(oracle.domain_at(trace_log, i)[0])
+        for _ in range(1, trace_log):
+            x = (2 * x * x - 1) % P
+        assert x == 0
+
+
+def test_lowered_program_equals_hand_written_air(oracle):
+    for case in air_cases.small_cases(oracle):
+        a, b = air_cases.by_air(oracle, case), air_cases.by_ssa(oracle, case)
+        assert (a == b).all(), case["name"]
+        assert a.any()
+        acc0 = qm31_array(9, 1 << case["eval_log"]).T.copy()
+        assert (air_cases.by_air(oracle, case, accum=acc0) == air_cases.by_ssa(oracle, case, accum=acc0)).all()
+        # accumulation is addition of the overwrite result
+        assert (air_cases.by_ssa(oracle, case, accum=acc0) == ((acc0.astype(np.uint64) + b) % P).astype(np.uint32)).all()
+
+
+def test_wide_fibonacci_quotient_of_a_valid_trace_is_a_polynomial(oracle):
+    """A trace that satisfies the constraints on the trace domain gives a quotient that is a polynomial of the trace's
+    degree: its coefficients on the evaluation domain vanish above index 2^trace_log (the basis function at that index
+    is the trace domain's own vanishing polynomial, which a degree-2 constraint can leave a multiple of)."""
+    trace_log, eval_log, n_cols = 6, 7, 12
+    n = 1 << trace_log
+    a, b = m31_column(1, n).astype(object), m31_column(2, n).astype(object)
+    trace = [a, b]
+    for _ in range(2, n_cols):
+        a, b = b, (a * a + b * b) % P
+        trace.append(b)
+    trace = [np.array(c, dtype=np.uint32) for c in trace]
+    coeffs = oracle.interpolate_cols(trace, trace_log)
+    cols = oracle.evaluate_cols(coeffs, trace_log, eval_log)
+    case = air_cases.wide_fibonacci_case(oracle, n_cols, trace_log, eval_log, 5)
+    case["cols"] = list(cols)
+    q = air_cases.by_air(oracle, case)
+    assert (q == air_cases.by_ssa(oracle, case)).all()
+    qc = np.stack(oracle.interpolate_cols(list(q), eval_log))
+    assert qc[:, :n].any() and not qc[:, n + 1:].any()
+    # a single corrupted cell breaks it
+    trace[5][3] ^= 1
+    cols = oracle.evaluate_cols(oracle.interpolate_cols(trace, trace_log), trace_log, eval_log)
+    case["cols"] = list(cols)
+    qc = np.stack(oracle.interpolate_cols(list(air_cases.by_air(oracle, case)), eval_log))
+    assert qc[:, n + 1:].any()
+
+
+def test_random_programs_interpret(oracle):
+    """The fuzz generator used on the GPU produces programs the oracle accepts (all opcodes, offsets, dead code)."""
+    src = air_cases.random_program(3, 200, [3, 0, 5, 4], 6, 9)
+    cols = [m31_column(50 + c, 1 << 6) for c in range(12)]
+    out = oracle.constraint_quotients_ssa(src, cols, qm31_array(4, 9), 4, 6, cumsum_shift=[1, 2, 3, 4])
+    assert out.any()

@@ -17,5 +17,9 @@ from .capi import (  # noqa: F401
     GKR_LOGUP_SINGLES,
     EXPORTED_SYMBOLS,
     PROVER_SYMBOLS,
+    AIR_SYMBOLS,
+    AirProgram,
+    constraint_denom_inv,
     PCS_PHASES,
 )
+from . import air, capi  # noqa: F401,E402

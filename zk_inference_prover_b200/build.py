@@ -11,7 +11,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libzkb200.so")
 
-SOURCES = ["ctx.cu", "fft.cu", "bitrev.cu", "blake2s.cu", "fri.cu", "quotients.cu", "gkr.cu", "gkr_fused.cu", "gkr_resident.cu", "poly_eval.cu", "freivalds.cu", "host/prover.cpp"]
+SOURCES = ["ctx.cu", "fft.cu", "bitrev.cu", "blake2s.cu", "fri.cu", "quotients.cu", "gkr.cu", "gkr_fused.cu", "gkr_resident.cu", "poly_eval.cu", "freivalds.cu", "constraints.cu", "host/prover.cpp", "host/air_compile.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -24,7 +24,7 @@ def _stale():
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = [os.path.join(dp, f) for dp, _, fs in os.walk(CSRC) for f in fs] + [os.path.join(HERE, "..", "include", "zkb200.h"), os.path.join(HERE, "..", "include", "zkb200_prover.h"), __file__]
+    deps = [os.path.join(dp, f) for dp, _, fs in os.walk(CSRC) for f in fs] + [os.path.join(HERE, "..", "include", "zkb200.h"), os.path.join(HERE, "..", "include", "zkb200_prover.h"), os.path.join(HERE, "..", "include", "zkb200_air.h"), __file__]
     return any(os.path.getmtime(d) > t for d in deps)
 
 

@@ -23,6 +23,8 @@ EXPORTED_SYMBOLS = [
 ]
 # Every symbol include/zkb200_prover.h declares.
 PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_gkr_prove_device"]
+# Every symbol include/zkb200_air.h declares.
+AIR_SYMBOLS = ["zkb_air_compile", "zkb_air_free", "zkb_air_get_stats", "zkb_constraint_quotients", "zkb_constraint_denom_inv"]
 PCS_PHASES = ["interpolate", "extend", "merkle", "sample", "quotients", "fri_commit", "grind", "decommit"]
 
 
@@ -34,6 +36,11 @@ class PcsConfig(C.Structure):
     _fields_ = [("pow_bits", C.c_uint32), ("log_blowup_factor", C.c_uint32), ("log_last_layer_degree_bound", C.c_uint32),
                 ("n_queries", C.c_uint32)]
 
+
+
+class AirStats(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("n_ops", "n_live_ops", "n_uniform", "n_instr", "n_loads", "n_columns_read", "reg_words",
+                                          "uniform_words", "threads", "smem_bytes", "m31_mults")]
 
 
 class ZkbError(RuntimeError):
@@ -62,7 +69,7 @@ def load_library():
         _lib.zkb_last_error.restype = C.c_char_p
         _lib.zkb_last_error.argtypes = [C.c_void_p]
         _lib.zkb_gkr_sum_noalloc_error.restype = C.c_char_p
-        for name in EXPORTED_SYMBOLS + PROVER_SYMBOLS:
+        for name in EXPORTED_SYMBOLS + PROVER_SYMBOLS + AIR_SYMBOLS:
             if name not in ("zkb_last_error", "zkb_gkr_sum_noalloc_error"):
                 getattr(_lib, name).restype = C.c_int
     return _lib
@@ -126,6 +133,45 @@ class DeviceBuffer:
 
 def _ptr_array(ptrs):
     return (C.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+
+
+def constraint_denom_inv(trace_log, eval_log):
+    """zkb_constraint_denom_inv: host only."""
+    out = np.empty(1 << (eval_log - trace_log), np.uint32)
+    rc = load_library().zkb_constraint_denom_inv(C.c_int(trace_log), C.c_int(eval_log), out.ctypes.data_as(C.c_void_p))
+    if rc != 0:
+        raise ZkbError(rc, "zkb_constraint_denom_inv: invalid sizes")
+    return out
+
+
+class AirProgram:
+    """A compiled AIR (zkb_air_program), owned by this object."""
+
+    def __init__(self, ctx, source):
+        self.ctx, self.source = ctx, source
+        ops, cons, trees = _u32(source.ops), _u32(source.constraints), _u32(source.tree_cols)
+        h = C.c_void_p()
+        ctx._check(ctx.lib.zkb_air_compile(ctx.h, ops.ctypes.data_as(C.c_void_p), C.c_size_t(ops.shape[0]), cons.ctypes.data_as(C.c_void_p),
+                                           C.c_size_t(cons.size), trees.ctypes.data_as(C.c_void_p), C.c_int(trees.size),
+                                           C.c_size_t(source.scalars.shape[0]), C.byref(h)))
+        self.h = h
+
+    @property
+    def stats(self):
+        st = AirStats()
+        self.ctx._check(self.ctx.lib.zkb_air_get_stats(self.h, C.byref(st)))
+        return {n: getattr(st, n) for n, _ in AirStats._fields_}
+
+    def free(self):
+        if getattr(self, "h", None):
+            self.ctx.lib.zkb_air_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
 
 
 class Context:
@@ -383,6 +429,23 @@ class Context:
                                                C.c_uint32(n_mats), s.ctypes.data_as(C.c_void_p), r.ctypes.data_as(C.c_void_p),
                                                _ptr_array(out_ptrs), claims.ctypes.data_as(C.c_void_p)))
         return claims
+
+    # ---- constraint quotients of a lowered AIR (include/zkb200_air.h)
+    def air_compile(self, source):
+        """source: an air.AirSource. Returns an AirProgram bound to this context's device."""
+        return AirProgram(self, source)
+
+    def constraint_quotients(self, prog, col_ptrs, random_coeff_powers, trace_log, eval_log, accum4, accumulate=True, scalars=None,
+                             cumsum_shift=None, denom_inv=None):
+        sc = _u32(prog.source.scalars if scalars is None else scalars)
+        rcp = _u32(random_coeff_powers)
+        assert rcp.size == 4 * prog.source.n_constraints and sc.size == prog.source.scalars.size
+        di = _u32(constraint_denom_inv(trace_log, eval_log) if denom_inv is None else denom_inv)
+        shift = _u32(cumsum_shift) if cumsum_shift is not None else None
+        self._check(self.lib.zkb_constraint_quotients(self.h, prog.h, _ptr_array(col_ptrs), sc.ctypes.data_as(C.c_void_p),
+                                                      shift.ctypes.data_as(C.c_void_p) if shift is not None else None,
+                                                      rcp.ctypes.data_as(C.c_void_p), di.ctypes.data_as(C.c_void_p), C.c_int(trace_log),
+                                                      C.c_int(eval_log), _ptr_array(accum4), C.c_int(int(accumulate))))
 
     # ---- GrindOps
     def grind(self, prefixed_digest8, pow_bits, m31_out=True):

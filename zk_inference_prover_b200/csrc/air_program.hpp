@@ -1,0 +1,90 @@
+// The compiled form of a lowered AIR (see include/zkb200_air.h): what the host evaluates once per call, and the
+// bytecode one evaluation-domain row executes on the device.
+#pragma once
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "../../include/zkb200_air.h"
+#include "m31.cuh"
+
+namespace zk {
+
+// Bytecode opcodes. An instruction is four words {opcode | n << 8, dst, a, b}.
+//   dst      word offset of the destination register in shared memory (the thread adds its lane)
+//   a, b     operands: (word offset << 1) | per_thread. A per-thread operand is a register (the thread adds its lane
+//            and steps a secure-field value by the CTA size); a uniform operand is a word of the table every row shares
+//            (secure-field values are 4 consecutive words).
+// A LOAD instruction is followed by ceil(n / 2) words-quads {column | offset << 20, dst, column | offset << 20, dst}
+// with the mask offset as a signed 12-bit field.
+enum AirBytecode : uint32_t {
+    BC_END = 0,
+    BC_LOAD = 1,
+    BC_ADD_BB = 2,
+    BC_SUB_BB = 3,
+    BC_MUL_BB = 4,
+    BC_NEG_B = 5,
+    BC_INV_B = 6,
+    BC_MOV_B = 7,
+    BC_ADD_EE = 8,
+    BC_SUB_EE = 9,
+    BC_MUL_EE = 10,
+    BC_NEG_E = 11,
+    BC_ADD_EB = 12,  // a secure, b base
+    BC_SUB_EB = 13,  // a secure - b base
+    BC_SUB_BE = 14,  // a base - b secure
+    BC_MUL_EB = 15,  // a secure * b base
+    BC_ACC_B = 16,   // row_res += coefficient(b, uniform secure) * a (base)
+    BC_ACC_E = 17,   // row_res += coefficient(b) * a (secure)
+};
+
+constexpr int AIR_LOAD_BATCH = 8;
+constexpr int AIR_MAX_OFFSET = 2047;      // mask offsets are a signed 12-bit field
+constexpr uint32_t AIR_MAX_COLUMNS = 1u << 20;
+
+struct AirInstr {
+    uint32_t x, y, z, w;
+};
+
+}  // namespace zk
+
+struct zkb_air_program {
+    // ---- the single-assignment program, annotated
+    std::vector<zkb_air_op> ops;
+    std::vector<uint8_t> ext;      // value is a secure-field element (else base field)
+    std::vector<uint8_t> uniform;  // value does not depend on the row
+    std::vector<uint8_t> live;     // reachable from a constraint
+    std::vector<uint32_t> alias;   // instruction whose value this one is (a PACK of (x, 0, 0, 0) is x; a repeated LOAD)
+    std::vector<int32_t> uni_word; // word of the uniform table holding this (uniform) value, or -1
+    std::vector<uint32_t> constraints;
+    std::vector<uint32_t> tree_base;  // first flat column of each tree
+    uint32_t n_cols = 0;
+    size_t n_scalars = 0;
+    bool has_offsets = false;
+    // ---- shared-memory layout, in words: [uniform values | coefficients | column pointers | registers]
+    uint32_t coef_base = 0;   // 4 words per constraint
+    uint32_t ptr_base = 0;    // 2 words per column, 8-byte aligned
+    uint32_t reg_base = 0;
+    uint32_t reg_words = 0;   // per row
+    uint32_t threads = 0;
+    uint32_t smem_bytes = 0;
+    uint32_t ctas_per_sm = 1;
+    // ---- bytecode
+    std::vector<zk::AirInstr> code;
+    zk::AirInstr* d_code = nullptr;
+    int device = -1;
+    zkb_air_stats stats{};
+};
+
+namespace zk {
+
+// Fills prog from the caller's program; returns an empty string or the reason it was rejected.
+std::string air_compile(zkb_air_program& prog, const zkb_air_op* ops, size_t n_ops, const uint32_t* constraints, size_t n_constraints,
+                        const uint32_t* tree_cols, int n_trees, size_t n_scalars);
+
+// Evaluates the row-independent instructions and writes the words [0, ptr_base) of the shared table:
+// uniform values, then the constraint coefficients.
+void air_fill_uniform(const zkb_air_program& prog, const uint32_t* scalars, const uint32_t* cumsum_shift,
+                      const uint32_t* random_coeff_powers, uint32_t* table);
+
+}  // namespace zk

@@ -1,0 +1,286 @@
+// Constraint-quotient evaluation on the evaluation domain: one kernel for every AIR.
+//
+// Replaces the reference's per-shape generated kernels (dispatch: nitroo/crates/stwo/src/stwo_cuda/bindings.rs:557-578;
+// call site: nitroo/crates/constraint-framework/src/prover/component_prover.rs:296-600) and states the same function as
+// accumulate_pointwise_cpu (component_prover.rs:603-633) over CpuDomainEvaluator (prover/cpu_domain.rs:52-98).
+//
+// A CTA owns tiles of `threads` consecutive rows. Each thread interprets the AIR's bytecode (csrc/air_program.hpp,
+// produced by csrc/host/air_compile.cpp) for its row. The values of a row live in shared memory, word w of thread t
+// at [reg_base + w * threads + t], so a warp's access to one register is one conflict-free row of banks, and the
+// row-independent values (literals, relation elements, random-coefficient powers) sit once per CTA in front of them.
+// All threads of a CTA execute the same instruction stream, so the interpreter's dispatch is uniform. Column reads
+// are issued in batches of up to 8 independent loads; for a mask offset the 256 rows of a tile map to another run of
+// consecutive rows except where the offset carries into the tile's own bits, so those reads coalesce as well.
+#include <algorithm>
+#include <new>
+#include <vector>
+
+#include "air_program.hpp"
+#include "common.cuh"
+
+namespace zk {
+
+struct AccumPtrs {
+    uint32_t* c[4];
+};
+
+// Row of the column that a mask at `off` of `row` reads (core/utils.rs:97-113): step the natural-order index inside
+// its half of the circle domain by off * 2^(eval_log - trace_log - 1), forwards in the first half, backwards in the second.
+__device__ __forceinline__ uint32_t offset_row(uint32_t row, int off, int trace_log, int eval_log) {
+    if (off == 0) return row;
+    const uint32_t nat = __brev(row) >> (32 - eval_log);
+    const uint32_t half = 1u << (eval_log - 1);
+    const uint32_t step = (uint32_t)off << (eval_log - trace_log - 1);
+    const uint32_t lo = (nat & half) ? nat - step : nat + step;
+    const uint32_t moved = (lo & (half - 1u)) | (nat & half);
+    return __brev(moved) >> (32 - eval_log);
+}
+
+extern __shared__ __align__(16) uint32_t air_smem[];
+
+__global__ void __launch_bounds__(256, 4)
+air_eval_kernel(const uint4* __restrict__ code, const uint32_t* __restrict__ table, uint32_t table_words, uint32_t ptr_base,
+                const uint32_t* __restrict__ denom_inv, int trace_log, int eval_log, AccumPtrs accum, int accumulate,
+                uint32_t n_tiles) {
+    uint32_t* sm = air_smem;
+    const uint32_t tid = threadIdx.x, T = blockDim.x;
+    for (uint32_t i = tid; i < table_words; i += T) sm[i] = table[i];
+    __syncthreads();
+    const unsigned long long* ptrs = reinterpret_cast<const unsigned long long*>(sm + ptr_base);
+    const uint32_t n_rows = 1u << eval_log;
+
+    auto ldb = [&](uint32_t e) -> uint32_t { return sm[(e >> 1) + ((e & 1u) ? tid : 0u)]; };
+    auto lde = [&](uint32_t e) -> qm31 {
+        const uint32_t base = (e >> 1) + ((e & 1u) ? tid : 0u), stride = (e & 1u) ? T : 1u;
+        return {{sm[base], sm[base + stride], sm[base + 2 * stride], sm[base + 3 * stride]}};
+    };
+    auto stb = [&](uint32_t d, uint32_t v) { sm[d + tid] = v; };
+    auto ste = [&](uint32_t d, qm31 v) {
+#pragma unroll
+        for (int k = 0; k < 4; k++) sm[d + tid + k * T] = v.c[k];
+    };
+
+    for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        const uint32_t row_raw = tile * T + tid;
+        const bool active = row_raw < n_rows;
+        const uint32_t row = active ? row_raw : n_rows - 1;
+        qm31 acc = qm31_zero();
+        uint32_t pc = 0;
+        uint4 ins = __ldg(code);
+        for (;;) {
+            const uint32_t op = ins.x & 0xffu;
+            if (op == BC_END) break;
+            if (op == BC_LOAD) {
+                const uint32_t n = ins.x >> 8;
+                uint32_t v[AIR_LOAD_BATCH], d[AIR_LOAD_BATCH];
+#pragma unroll
+                for (int q = 0; q < AIR_LOAD_BATCH / 2; q++) {
+                    if (2 * q < (int)n) {
+                        const uint4 e = __ldg(code + pc + 1 + q);
+                        const uint32_t* c0 = reinterpret_cast<const uint32_t*>(ptrs[e.x & 0xfffffu]);
+                        v[2 * q] = __ldg(c0 + offset_row(row, (int)e.x >> 20, trace_log, eval_log));
+                        d[2 * q] = e.y;
+                        if (2 * q + 1 < (int)n) {
+                            const uint32_t* c1 = reinterpret_cast<const uint32_t*>(ptrs[e.z & 0xfffffu]);
+                            v[2 * q + 1] = __ldg(c1 + offset_row(row, (int)e.z >> 20, trace_log, eval_log));
+                            d[2 * q + 1] = e.w;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < AIR_LOAD_BATCH; q++)
+                    if (q < (int)n) stb(d[q], v[q]);
+                pc += 1 + (n + 1) / 2;
+                ins = __ldg(code + pc);
+                continue;
+            }
+            const uint4 nxt = __ldg(code + pc + 1);
+            switch (op) {
+                case BC_ADD_BB: stb(ins.y, m31_add(ldb(ins.z), ldb(ins.w))); break;
+                case BC_SUB_BB: stb(ins.y, m31_sub(ldb(ins.z), ldb(ins.w))); break;
+                case BC_MUL_BB: stb(ins.y, m31_mul(ldb(ins.z), ldb(ins.w))); break;
+                case BC_NEG_B: stb(ins.y, m31_neg(ldb(ins.z))); break;
+                case BC_INV_B: stb(ins.y, m31_inv(ldb(ins.z))); break;
+                case BC_MOV_B: stb(ins.y, ldb(ins.z)); break;
+                case BC_ADD_EE: ste(ins.y, qm31_add(lde(ins.z), lde(ins.w))); break;
+                case BC_SUB_EE: ste(ins.y, qm31_sub(lde(ins.z), lde(ins.w))); break;
+                case BC_MUL_EE: ste(ins.y, qm31_mul(lde(ins.z), lde(ins.w))); break;
+                case BC_NEG_E: ste(ins.y, qm31_neg(lde(ins.z))); break;
+                case BC_ADD_EB: {
+                    qm31 a = lde(ins.z);
+                    a.c[0] = m31_add(a.c[0], ldb(ins.w));
+                    ste(ins.y, a);
+                    break;
+                }
+                case BC_SUB_EB: {
+                    qm31 a = lde(ins.z);
+                    a.c[0] = m31_sub(a.c[0], ldb(ins.w));
+                    ste(ins.y, a);
+                    break;
+                }
+                case BC_SUB_BE: {
+                    qm31 b = qm31_neg(lde(ins.w));
+                    b.c[0] = m31_add(b.c[0], ldb(ins.z));
+                    ste(ins.y, b);
+                    break;
+                }
+                case BC_MUL_EB: ste(ins.y, qm31_mul_m31(lde(ins.z), ldb(ins.w))); break;
+                case BC_ACC_B: acc = qm31_add(acc, qm31_mul_m31(lde(ins.w), ldb(ins.z))); break;
+                case BC_ACC_E: acc = qm31_add(acc, qm31_mul(lde(ins.w), lde(ins.z))); break;
+                default: break;
+            }
+            ins = nxt;
+            pc++;
+        }
+        if (active) {
+            const uint32_t di = __ldg(denom_inv + (row >> trace_log));
+            qm31 q = qm31_mul_m31(acc, di);
+            if (accumulate) {
+#pragma unroll
+                for (int k = 0; k < 4; k++) q.c[k] = m31_add(q.c[k], accum.c[k][row]);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; k++) accum.c[k][row] = q.c[k];
+        }
+    }
+}
+
+}  // namespace zk
+
+using namespace zk;
+
+extern "C" {
+
+int zkb_air_compile(zkb_ctx* ctx, const zkb_air_op* ops, size_t n_ops, const uint32_t* constraints, size_t n_constraints,
+                    const uint32_t* tree_cols, int n_trees, size_t n_scalars, zkb_air_program** out) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, ops != nullptr && constraints != nullptr && out != nullptr);
+    ZKB_CHECK_ARG(ctx, n_trees >= 0 && n_trees <= 64 && (n_trees == 0 || tree_cols != nullptr));
+    *out = nullptr;
+    zkb_air_program* prog = new (std::nothrow) zkb_air_program();
+    if (!prog) return set_error(ctx, ZKB_ENOMEM, "zkb_air_compile: out of host memory");
+    std::string why;
+    try {
+        why = air_compile(*prog, ops, n_ops, constraints, n_constraints, tree_cols, n_trees, n_scalars);
+    } catch (const std::bad_alloc&) {
+        delete prog;
+        return set_error(ctx, ZKB_ENOMEM, "zkb_air_compile: out of host memory");
+    }
+    if (!why.empty()) {
+        delete prog;
+        return set_error(ctx, ZKB_EINVAL, "zkb_air_compile: %s", why.c_str());
+    }
+    DeviceGuard g(ctx);
+    prog->device = ctx->device;
+    const size_t bytes = prog->code.size() * sizeof(AirInstr);
+    cudaError_t e = cudaMalloc(&prog->d_code, bytes);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(prog->d_code, prog->code.data(), bytes, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(air_eval_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) {
+        if (prog->d_code) cudaFree(prog->d_code);
+        delete prog;
+        return set_error(ctx, e == cudaErrorMemoryAllocation ? ZKB_ENOMEM : ZKB_ECUDA, "zkb_air_compile: %s", cudaGetErrorString(e));
+    }
+    *out = prog;
+    return ZKB_OK;
+}
+
+int zkb_air_free(zkb_air_program* prog) {
+    if (!prog) return ZKB_OK;
+    if (prog->d_code) {
+        int prev = -1;
+        cudaGetDevice(&prev);
+        if (prev != prog->device) cudaSetDevice(prog->device);
+        cudaFree(prog->d_code);
+        if (prev >= 0 && prev != prog->device) cudaSetDevice(prev);
+    }
+    delete prog;
+    return ZKB_OK;
+}
+
+int zkb_air_get_stats(const zkb_air_program* prog, zkb_air_stats* out) {
+    if (!prog || !out) return ZKB_EINVAL;
+    *out = prog->stats;
+    return ZKB_OK;
+}
+
+int zkb_constraint_quotients(zkb_ctx* ctx, const zkb_air_program* prog, const uint32_t* const* cols, const uint32_t* scalars,
+                             const uint32_t* cumsum_shift, const uint32_t* random_coeff_powers, const uint32_t* denom_inv,
+                             int trace_log, int eval_log, uint32_t* const accum[4], int accumulate) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, prog != nullptr && prog->d_code != nullptr && prog->device == ctx->device);
+    ZKB_CHECK_ARG(ctx, random_coeff_powers != nullptr && denom_inv != nullptr && accum != nullptr);
+    ZKB_CHECK_ARG(ctx, prog->n_cols == 0 || cols != nullptr);
+    ZKB_CHECK_ARG(ctx, prog->n_scalars == 0 || scalars != nullptr);
+    ZKB_CHECK_ARG(ctx, trace_log >= 1 && trace_log < eval_log && eval_log <= 30);
+    ZKB_CHECK_ARG(ctx, eval_log - trace_log <= 16);
+    for (int k = 0; k < 4; k++) ZKB_CHECK_ARG(ctx, accum[k] != nullptr);
+    DeviceGuard g(ctx);
+    // One staged blob: [uniform values | coefficients | column pointers | denominator inverses], in 8-byte units.
+    const uint32_t n_denom = 1u << (eval_log - trace_log);
+    const size_t table_words = (size_t)prog->ptr_base + 2 * (size_t)prog->n_cols;
+    const size_t blob_words = table_words + n_denom + (n_denom & 1);
+    std::vector<uint32_t> blob(blob_words, 0);
+    air_fill_uniform(*prog, scalars, cumsum_shift, random_coeff_powers, blob.data());
+    for (uint32_t c = 0; c < prog->n_cols; c++) {
+        const unsigned long long p = (unsigned long long)(uintptr_t)cols[c];
+        blob[prog->ptr_base + 2 * c] = (uint32_t)p;
+        blob[prog->ptr_base + 2 * c + 1] = (uint32_t)(p >> 32);
+    }
+    for (uint32_t j = 0; j < n_denom; j++) blob[table_words + j] = denom_inv[j];
+    void** d_blob = nullptr;
+    int rc = stage_ptrs(ctx, reinterpret_cast<const void* const*>(blob.data()), (int)(blob_words / 2), &d_blob);
+    if (rc != ZKB_OK) return rc;
+    const uint32_t* d_table = reinterpret_cast<const uint32_t*>(d_blob);
+    AccumPtrs ap{{accum[0], accum[1], accum[2], accum[3]}};
+    const uint32_t T = prog->threads;
+    const uint64_t n_rows = 1ull << eval_log;
+    const uint32_t n_tiles = (uint32_t)((n_rows + T - 1) / T);
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx->device);
+    const uint32_t grid = std::min<uint32_t>(n_tiles, (uint32_t)sms * prog->ctas_per_sm);
+    ProfScope prof(ctx, "air_eval_kernel");
+    air_eval_kernel<<<grid, T, prog->smem_bytes, ctx->stream>>>(reinterpret_cast<const uint4*>(prog->d_code), d_table,
+                                                                 (uint32_t)table_words, prog->ptr_base, d_table + table_words,
+                                                                 trace_log, eval_log, ap, accumulate, n_tiles);
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
+}
+
+int zkb_constraint_denom_inv(int trace_log, int eval_log, uint32_t* out) {
+    if (!out || trace_log < 1 || trace_log >= eval_log || eval_log > 30 || eval_log - trace_log > 16) return ZKB_EINVAL;
+    // Generator of the order-2^31 circle group (core/circle.rs:202-205); a point of index i is i * G.
+    auto point = [](uint32_t idx) {
+        cpoint r{1u, 0u}, g{2u, 1268011823u};
+        for (int b = 0; b < 31; b++) {
+            if ((idx >> b) & 1u) r = cpoint_add(r, g);
+            g = cpoint_add(g, g);
+        }
+        return r;
+    };
+    auto subgroup_gen = [](int log_size) { return 1u << (31 - log_size); };
+    const uint32_t mask = 0x7fffffffu;
+    // trace coset: Coset::odds(trace_log) = (initial G_{trace_log+1}, step G_{trace_log}); the shift of coset_vanishing
+    // is -initial + step/2 (core/constraints.rs:27), which is zero for a canonic coset's index arithmetic below.
+    const uint32_t t_initial = subgroup_gen(trace_log + 1), t_step = subgroup_gen(trace_log);
+    // evaluation domain: CircleDomain(half_odds(eval_log - 1)) = (initial G_{eval_log+1}, step G_{eval_log-1});
+    // at(i) for i below the half size is initial + i * step.
+    const uint32_t e_initial = subgroup_gen(eval_log + 1), e_step = subgroup_gen(eval_log - 1);
+    const uint32_t n = 1u << (eval_log - trace_log), half = 1u << (eval_log - 1);
+    const int bits = eval_log - trace_log;
+    for (uint32_t i = 0; i < n; i++) {
+        // CircleDomain::at: the second half of the domain is the conjugate coset
+        uint32_t idx = i < half ? (e_initial + i * e_step) & mask : (0u - (e_initial + (i - half) * e_step)) & mask;
+        uint32_t shifted = (idx - t_initial + (t_step >> 1)) & mask;
+        uint32_t x = point(shifted).x;
+        for (int k = 1; k < trace_log; k++) x = m31_double_x(x);
+        uint32_t j = 0;
+        for (int k = 0; k < bits; k++) j |= ((i >> k) & 1u) << (bits - 1 - k);
+        out[j] = m31_inv(x);
+    }
+    return ZKB_OK;
+}
+
+}  // extern "C"
