@@ -613,39 +613,41 @@ def run_constraints(args, rank):
     import air_cases
     import oracle
     import zk_inference_prover_b200 as z
-    from util import m31_column, qm31_array
-    from zk_inference_prover_b200 import air
-
     trace_log, eval_log = args.log_size, args.log_size + 1
     N = 1 << eval_log
     ctx = z.Context(device=0, max_log_size=10)
     results = {}
 
-    def time_case(name, src, scalars_shift, n_cols_total):
+    def time_case(which):
+        case = air_cases.bench_case(oracle, which, trace_log, args.cols)
+        src = case["source"]
         prog = ctx.air_compile(src)
         st = prog.stats
-        cols = [ctx.upload(m31_column(0x5EED0100 + c, N)) for c in range(n_cols_total)]
+        cols = [ctx.upload(c) for c in case["cols"]]
+        case["cols"] = None
         acc = [ctx.alloc(N).zero() for _ in range(4)]
-        rcp = qm31_array(0x5EED0101, src.n_constraints)
         ts = []
         for it in range(args.warmup + args.steps):
             ctx.event_record(0)
-            ctx.constraint_quotients(prog, [c.ptr for c in cols], rcp, trace_log, eval_log, [a.ptr for a in acc], accumulate=True,
-                                     cumsum_shift=scalars_shift)
+            ctx.constraint_quotients(prog, [c.ptr for c in cols], case["rcp"], trace_log, eval_log, [a.ptr for a in acc], accumulate=True,
+                                     cumsum_shift=case["cumsum_shift"])
             ctx.event_record(1)
             ctx.sync()
             if it >= args.warmup:
                 ts.append(ctx.event_elapsed_ms(0, 1))
         ms = float(np.mean(ts))
+        # parity: one more pass that overwrites, against the committed digest of the oracle's output
+        ctx.constraint_quotients(prog, [c.ptr for c in cols], case["rcp"], trace_log, eval_log, [a.ptr for a in acc], accumulate=False,
+                                 cumsum_shift=case["cumsum_shift"])
+        parity = golden_check(case["name"], np.stack([a.download() for a in acc]).reshape(-1))
         bytes_alg = (4.0 * st["n_columns_read"] + 32.0) * N  # every column read once, the accumulator read and written
-        results[name] = {"ms": ms, "rows_per_s": N / (ms * 1e-3), "columns": n_cols_total, "constraints": int(src.n_constraints),
-                         "algorithmic_gbs": bytes_alg / (ms * 1e-3) / 1e9, "m31_gmults_per_s": st["m31_mults"] * N / (ms * 1e-3) / 1e9,
-                         "program": st}
-        return cols, rcp, ms, bytes_alg
+        results[which] = {"workload": case["name"], "ms": ms, "rows_per_s": N / (ms * 1e-3), "columns": len(cols),
+                          "constraints": int(src.n_constraints), "algorithmic_gbs": bytes_alg / (ms * 1e-3) / 1e9,
+                          "m31_gmults_per_s": st["m31_mults"] * N / (ms * 1e-3) / 1e9, "program": st, "parity": parity}
+        return cols, case["rcp"], ms, bytes_alg
 
     ncols = args.cols
-    wf = air.wide_fibonacci(air.ExprEvaluator(), ncols).source()
-    cols, rcp, wf_ms, wf_bytes = time_case("wide_fibonacci", wf, None, ncols)
+    cols, rcp, wf_ms, wf_bytes = time_case("wide_fibonacci")
     gpu_ref = None
     if not args.no_gpu_baseline:
         try:  # the reference's hand-written kernel for the same AIR on the same columns (it overwrites; host clock around its blocking call)
@@ -671,12 +673,7 @@ def run_constraints(args, rank):
         except Exception as e:
             gpu_ref = {"unavailable": repr(e)}
     del cols
-    pk, pq, n_mats = 16, 1, 2
-    fp = air_cases.freivalds_params(oracle, pk, pq, n_mats, 0x5EED0102)
-    rel = qm31_array(0x5EED0103, 2)
-    fr = air.freivalds(air.ExprEvaluator(), pk, pq, n_mats, fp["rv_pow"], fp["rv_step"], fp["s_pow"], fp["s_step"], qm31_array(0x5EED0104, n_mats),
-                       128, (rel[0], rel[1])).source()
-    time_case("freivalds_pk16_pq1_2mats_range_check", fr, qm31_array(0x5EED0105, 1)[0], int(sum(fr.tree_cols)))
+    time_case("freivalds")
     cpu = None
     if not args.no_cpu_baseline:
         oracle.set_num_threads(len(os.sched_getaffinity(0)))

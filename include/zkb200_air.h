@@ -63,7 +63,8 @@ typedef struct zkb_air_stats {
     uint32_t n_columns_read;   /* distinct columns read */
     uint32_t reg_words;        /* shared-memory words per row (register file) */
     uint32_t uniform_words;    /* shared-memory words per CTA shared by all rows */
-    uint32_t threads;          /* rows per CTA */
+    uint32_t threads;          /* threads per CTA */
+    uint32_t rows_per_thread;  /* rows one thread evaluates side by side (1, 2 or 4) */
     uint32_t smem_bytes;       /* dynamic shared memory per CTA */
     uint32_t m31_mults;        /* M31 multiplications per row */
 } zkb_air_stats;

@@ -69,6 +69,31 @@ def small_cases(oracle):
     ]
 
 
+def bench_case(oracle, which, trace_log=20, n_cols=256):
+    """The benchmark's two workloads (bench.py --mode constraints), evaluation domain twice the trace: the wide
+    Fibonacci AIR with n_cols columns, and the Freivalds component at pk = 16, pq = 1, two matrices, with its range check.
+    Columns are m31_column(0x5EED0100 + c), the random-coefficient powers qm31_array(0x5EED0101)."""
+    eval_log = trace_log + 1
+    if which == "wide_fibonacci":
+        case = wide_fibonacci_case(oracle, n_cols, trace_log, eval_log, 0)
+        case["name"] = f"air_wide_fibonacci_{n_cols}x2e{trace_log}"
+    else:
+        pk, pq, n_mats = 16, 1, 2
+        fp = freivalds_params(oracle, pk, pq, n_mats, 0x5EED0102)
+        rel, claimed = qm31_array(0x5EED0103, 2), qm31_array(0x5EED0104, n_mats)
+        src = air.freivalds(air.ExprEvaluator(), pk, pq, n_mats, fp["rv_pow"], fp["rv_step"], fp["s_pow"], fp["s_step"], claimed, 128,
+                            (rel[0], rel[1])).source()
+        qp = np.concatenate([fp["rv_pow"], fp["rv_step"][None], fp["s_pow"], fp["s_step"][None], claimed, rel]).astype(np.uint32)
+        claimed_sum = qm31_array(0x5EED0105, 1)[0]
+        case = dict(name=f"air_freivalds_pk16_pq1_2mats_2e{trace_log}", source=src, air=2, ip=[pk, pq, n_mats, 128, 1], qp=qp,
+                    tree_cols=list(src.tree_cols), trace_log=trace_log, eval_log=eval_log, claimed_sum=claimed_sum,
+                    cumsum_shift=_shift(oracle, claimed_sum, trace_log))
+    n_total = int(sum(case["tree_cols"]))
+    case["cols"] = [m31_column(0x5EED0100 + c, 1 << eval_log) for c in range(n_total)]
+    case["rcp"] = qm31_array(0x5EED0101, case["source"].n_constraints)
+    return case
+
+
 def by_air(oracle, case, accum=None):
     """The oracle's hand-written evaluator of the case's AIR."""
     return oracle.constraint_quotients_air(case["air"], case["ip"], case["qp"], case["tree_cols"], case["cols"], case["rcp"],

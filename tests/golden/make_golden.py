@@ -1,5 +1,6 @@
 """Generates tests/golden/proof_digests.json: SHA-256 digests of whole proofs (the word streams of
-include/zkb200_prover.h) produced by the CPU oracle on seeded inputs.
+include/zkb200_prover.h) and of constraint-quotient accumulators (include/zkb200_air.h) produced by the CPU oracle
+on seeded inputs.
 
 The reference is Rust and cannot be run with this image's toolchains, so these vectors are outputs of
 the oracle (which is pinned to the reference's own known-answer tests in tests/test_oracle_kats.py), not
@@ -55,6 +56,20 @@ GKR_FULL = {
 }
 
 
+# constraint quotients of an AIR (tests/air_cases.py): the accumulator's 4 x 2^eval_log words from the oracle's evaluator
+# written against CpuDomainEvaluator. Small: index into air_cases.small_cases; full: the benchmark's two workloads.
+AIR_SMALL = {f"air_small_{i}": i for i in range(8)}
+AIR_FULL = {"air_wide_fibonacci_256x2e20": "wide_fibonacci", "air_freivalds_pk16_pq1_2mats_2e20": "freivalds"}
+
+
+def air_case(name):
+    import air_cases
+
+    if name in AIR_SMALL:
+        return air_cases.small_cases(oracle)[AIR_SMALL[name]]
+    return air_cases.bench_case(oracle, AIR_FULL[name])
+
+
 def pcs_trees(shape, seed):
     if seed == 0x5EED0001:  # the benchmark's convention: one seed per column index
         return [[m31_column(seed + c, 1 << lg) for c, lg in enumerate(logs)] for logs in shape]
@@ -88,6 +103,11 @@ def main():
     for name, (specs, seed) in gkr.items():
         cap = 1 << 22
         out[name] = digest(oracle.gkr_prove([gkr_instance(*s) for s in specs], seed, verify=max(s[1] for s in specs) <= 16, cap=cap))
+        print(name, out[name], flush=True)
+    import air_cases
+
+    for name in list(AIR_SMALL) + (list(AIR_FULL) if args.full else []):
+        out[name] = digest(air_cases.by_air(oracle, air_case(name)))
         print(name, out[name], flush=True)
     json.dump(out, open(OUT, "w"), indent=1, sort_keys=True)
 

@@ -35,8 +35,29 @@ def test_oracle_reproduces_gkr_digest(oracle, name):
     _check(name, oracle.gkr_prove([mg.gkr_instance(*s) for s in specs], seed))
 
 
+@pytest.mark.parametrize("name", sorted(mg.AIR_SMALL))
+def test_oracle_reproduces_air_digest(oracle, name):
+    import air_cases
+
+    case = mg.air_case(name)
+    _check(name, air_cases.by_air(oracle, case))
+    _check(name, air_cases.by_ssa(oracle, case))
+
+
 def test_every_golden_has_a_recipe():
-    assert set(GOLDEN) == set(mg.PCS_SMALL) | set(mg.PCS_FULL) | set(mg.GKR_SMALL) | set(mg.GKR_FULL)
+    assert set(GOLDEN) == set(mg.PCS_SMALL) | set(mg.PCS_FULL) | set(mg.GKR_SMALL) | set(mg.GKR_FULL) | set(mg.AIR_SMALL) | set(mg.AIR_FULL)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(mg.AIR_SMALL) + sorted(mg.AIR_FULL))
+def test_cuda_reproduces_air_digest(ctx, name):
+    case = mg.air_case(name)
+    prog = ctx.air_compile(case["source"])
+    bufs = [ctx.upload(c) for c in case["cols"]]
+    acc = [ctx.alloc(1 << case["eval_log"]) for _ in range(4)]
+    ctx.constraint_quotients(prog, [b.ptr for b in bufs], case["rcp"], case["trace_log"], case["eval_log"], [a.ptr for a in acc],
+                             accumulate=False, cumsum_shift=case["cumsum_shift"])
+    _check(name, np.stack([a.download() for a in acc]))
 
 
 @pytest.mark.gpu

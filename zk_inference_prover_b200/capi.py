@@ -40,7 +40,7 @@ class PcsConfig(C.Structure):
 
 class AirStats(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("n_ops", "n_live_ops", "n_uniform", "n_instr", "n_loads", "n_columns_read", "reg_words",
-                                          "uniform_words", "threads", "smem_bytes", "m31_mults")]
+                                          "uniform_words", "threads", "rows_per_thread", "smem_bytes", "m31_mults")]
 
 
 class ZkbError(RuntimeError):

@@ -10,33 +10,46 @@
 
 namespace zk {
 
-// Bytecode opcodes. An instruction is four words {opcode | n << 8, dst, a, b}.
-//   dst      word offset of the destination register in shared memory (the thread adds its lane)
-//   a, b     operands: (word offset << 1) | per_thread. A per-thread operand is a register (the thread adds its lane
-//            and steps a secure-field value by the CTA size); a uniform operand is a word of the table every row shares
-//            (secure-field values are 4 consecutive words).
+// Bytecode. An instruction is four words {opcode | flags | dst << 8, a, b, c}.
+//   dst      word offset of the destination register in shared memory (a thread adds row_in_thread * threads + lane)
+//   a, b, c  operands: (word offset << 1) | per_row. A per-row operand is a register (the thread adds its row's lane and
+//            steps a secure-field value by the rows of the CTA); a uniform operand is a word of the table every row
+//            shares (a secure-field value is 4 consecutive words).
+//   flags    BC_F_ACC: the result is a constraint; row_res += coefficient(c) * result (instructions with at most two
+//            sources); BC_F_NOSTORE: nothing else reads the result, so it is not written to its register.
 // A LOAD instruction is followed by ceil(n / 2) words-quads {column | offset << 20, dst, column | offset << 20, dst}
 // with the mask offset as a signed 12-bit field.
+// row_res is kept per row as four unreduced 64-bit sums: a base-field constraint adds coefficient * value (< 2^62) to
+// each, and BC_ACC_RED, which the compiler emits after every third such addition, folds them back below 2^31.
 enum AirBytecode : uint32_t {
     BC_END = 0,
     BC_LOAD = 1,
-    BC_ADD_BB = 2,
-    BC_SUB_BB = 3,
-    BC_MUL_BB = 4,
-    BC_NEG_B = 5,
-    BC_INV_B = 6,
-    BC_MOV_B = 7,
-    BC_ADD_EE = 8,
-    BC_SUB_EE = 9,
-    BC_MUL_EE = 10,
-    BC_NEG_E = 11,
-    BC_ADD_EB = 12,  // a secure, b base
-    BC_SUB_EB = 13,  // a secure - b base
-    BC_SUB_BE = 14,  // a base - b secure
-    BC_MUL_EB = 15,  // a secure * b base
-    BC_ACC_B = 16,   // row_res += coefficient(b, uniform secure) * a (base)
-    BC_ACC_E = 17,   // row_res += coefficient(b) * a (secure)
+    BC_ACC_B = 2,   // row_res += coefficient(c) * a (base)
+    BC_ACC_E = 3,   // row_res += coefficient(c) * a (secure)
+    BC_ACC_RED = 4,
+    // base-field results
+    BC_ADD_BB = 8,
+    BC_SUB_BB = 9,
+    BC_MUL_BB = 10,
+    BC_NEG_B = 11,
+    BC_INV_B = 12,
+    BC_MOV_B = 13,
+    BC_FMA_B = 14,   // a * b + c
+    BC_FMS_B = 15,   // a * b - c
+    BC_FNMS_B = 16,  // c - a * b
+    // secure-field results
+    BC_ADD_EE = 24,
+    BC_SUB_EE = 25,
+    BC_MUL_EE = 26,
+    BC_NEG_E = 27,
+    BC_ADD_EB = 28,   // a secure, b base
+    BC_SUB_EB = 29,   // a secure - b base
+    BC_SUB_BE = 30,   // a base - b secure
+    BC_MUL_EB = 31,   // a secure * b base
+    BC_FMA_EB = 32,   // c secure + a secure * b base
+    BC_FNMS_EB = 33,  // c secure - a secure * b base
 };
+constexpr uint32_t BC_OP_MASK = 0x3f, BC_F_ACC = 0x40, BC_F_NOSTORE = 0x80;
 
 constexpr int AIR_LOAD_BATCH = 8;
 constexpr int AIR_MAX_OFFSET = 2047;      // mask offsets are a signed 12-bit field
@@ -67,6 +80,7 @@ struct zkb_air_program {
     uint32_t reg_base = 0;
     uint32_t reg_words = 0;   // per row
     uint32_t threads = 0;
+    uint32_t rows_per_thread = 1;
     uint32_t smem_bytes = 0;
     uint32_t ctas_per_sm = 1;
     // ---- bytecode

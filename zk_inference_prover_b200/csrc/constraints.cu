@@ -4,9 +4,10 @@
 // call site: nitroo/crates/constraint-framework/src/prover/component_prover.rs:296-600) and states the same function as
 // accumulate_pointwise_cpu (component_prover.rs:603-633) over CpuDomainEvaluator (prover/cpu_domain.rs:52-98).
 //
-// A CTA owns tiles of `threads` consecutive rows. Each thread interprets the AIR's bytecode (csrc/air_program.hpp,
-// produced by csrc/host/air_compile.cpp) for its row. The values of a row live in shared memory, word w of thread t
-// at [reg_base + w * threads + t], so a warp's access to one register is one conflict-free row of banks, and the
+// A CTA owns tiles of threads x rows_per_thread consecutive rows. Each thread interprets the AIR's bytecode
+// (csrc/air_program.hpp, produced by csrc/host/air_compile.cpp) for its 1, 2 or 4 rows. The values of a row live in
+// shared memory, word w of row r of the tile at [reg_base + w * rows + r], so a warp's access to one register is one
+// conflict-free row of banks, and the
 // row-independent values (literals, relation elements, random-coefficient powers) sit once per CTA in front of them.
 // All threads of a CTA execute the same instruction stream, so the interpreter's dispatch is uniform. Column reads
 // are issued in batches of up to 8 independent loads; for a mask offset the 256 rows of a tile map to another run of
@@ -38,109 +39,190 @@ __device__ __forceinline__ uint32_t offset_row(uint32_t row, int off, int trace_
 
 extern __shared__ __align__(16) uint32_t air_smem[];
 
-__global__ void __launch_bounds__(256, 4)
+// RPT rows per thread: rows tile * T * RPT + j * T + lane, j < RPT. The instruction fetch, its decoding and the loads
+// of uniform operands are paid once for the RPT rows, whose arithmetic is independent.
+template <int RPT>
+__global__ void __launch_bounds__(256, RPT == 4 ? 2 : RPT == 2 ? 3 : 4)
 air_eval_kernel(const uint4* __restrict__ code, const uint32_t* __restrict__ table, uint32_t table_words, uint32_t ptr_base,
                 const uint32_t* __restrict__ denom_inv, int trace_log, int eval_log, AccumPtrs accum, int accumulate,
                 uint32_t n_tiles) {
     uint32_t* sm = air_smem;
-    const uint32_t tid = threadIdx.x, T = blockDim.x;
+    const uint32_t tid = threadIdx.x, T = blockDim.x, RP = T * RPT;
     for (uint32_t i = tid; i < table_words; i += T) sm[i] = table[i];
     __syncthreads();
     const unsigned long long* ptrs = reinterpret_cast<const unsigned long long*>(sm + ptr_base);
     const uint32_t n_rows = 1u << eval_log;
 
-    auto ldb = [&](uint32_t e) -> uint32_t { return sm[(e >> 1) + ((e & 1u) ? tid : 0u)]; };
-    auto lde = [&](uint32_t e) -> qm31 {
-        const uint32_t base = (e >> 1) + ((e & 1u) ? tid : 0u), stride = (e & 1u) ? T : 1u;
+    // operand readers: word index of row j's copy, and the step between the coordinates of a secure value
+    auto at = [&](uint32_t e, int j) -> uint32_t { return (e >> 1) + ((e & 1u) ? tid + j * T : 0u); };
+    auto ldb = [&](uint32_t e, int j) -> uint32_t { return sm[at(e, j)]; };
+    auto lde = [&](uint32_t e, int j) -> qm31 {
+        const uint32_t base = at(e, j), stride = (e & 1u) ? RP : 1u;
         return {{sm[base], sm[base + stride], sm[base + 2 * stride], sm[base + 3 * stride]}};
-    };
-    auto stb = [&](uint32_t d, uint32_t v) { sm[d + tid] = v; };
-    auto ste = [&](uint32_t d, qm31 v) {
-#pragma unroll
-        for (int k = 0; k < 4; k++) sm[d + tid + k * T] = v.c[k];
     };
 
     for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        const uint32_t row_raw = tile * T + tid;
-        const bool active = row_raw < n_rows;
-        const uint32_t row = active ? row_raw : n_rows - 1;
-        qm31 acc = qm31_zero();
+        uint32_t row[RPT];
+        bool active[RPT];
+#pragma unroll
+        for (int j = 0; j < RPT; j++) {
+            const uint32_t r = tile * RP + j * T + tid;
+            active[j] = r < n_rows;
+            row[j] = active[j] ? r : n_rows - 1;
+        }
+        unsigned long long acc[RPT][4];
+#pragma unroll
+        for (int j = 0; j < RPT; j++)
+#pragma unroll
+            for (int k = 0; k < 4; k++) acc[j][k] = 0;
+
+        // result handlers: accumulate as a constraint and / or store
+        auto finish_b = [&](const uint4& ins, const uint32_t (&r)[RPT]) {
+            if (ins.x & BC_F_ACC) {
+                const qm31 coef = lde(ins.w, 0);
+#pragma unroll
+                for (int j = 0; j < RPT; j++)
+#pragma unroll
+                    for (int k = 0; k < 4; k++) acc[j][k] += (unsigned long long)coef.c[k] * r[j];
+            }
+            if (!(ins.x & BC_F_NOSTORE)) {
+                const uint32_t d = (ins.x >> 8) + tid;
+#pragma unroll
+                for (int j = 0; j < RPT; j++) sm[d + j * T] = r[j];
+            }
+        };
+        auto finish_e = [&](const uint4& ins, const qm31 (&r)[RPT]) {
+            if (ins.x & BC_F_ACC) {
+                const qm31 coef = lde(ins.w, 0);
+#pragma unroll
+                for (int j = 0; j < RPT; j++) {
+                    const qm31 t = qm31_mul(coef, r[j]);
+#pragma unroll
+                    for (int k = 0; k < 4; k++) acc[j][k] += t.c[k];
+                }
+            }
+            if (!(ins.x & BC_F_NOSTORE)) {
+                const uint32_t d = (ins.x >> 8) + tid;
+#pragma unroll
+                for (int j = 0; j < RPT; j++)
+#pragma unroll
+                    for (int k = 0; k < 4; k++) sm[d + j * T + k * RP] = r[j].c[k];
+            }
+        };
+
         uint32_t pc = 0;
         uint4 ins = __ldg(code);
         for (;;) {
-            const uint32_t op = ins.x & 0xffu;
+            const uint32_t op = ins.x & BC_OP_MASK;
             if (op == BC_END) break;
             if (op == BC_LOAD) {
                 const uint32_t n = ins.x >> 8;
-                uint32_t v[AIR_LOAD_BATCH], d[AIR_LOAD_BATCH];
+                uint32_t v[AIR_LOAD_BATCH][RPT], d[AIR_LOAD_BATCH];
 #pragma unroll
                 for (int q = 0; q < AIR_LOAD_BATCH / 2; q++) {
                     if (2 * q < (int)n) {
                         const uint4 e = __ldg(code + pc + 1 + q);
                         const uint32_t* c0 = reinterpret_cast<const uint32_t*>(ptrs[e.x & 0xfffffu]);
-                        v[2 * q] = __ldg(c0 + offset_row(row, (int)e.x >> 20, trace_log, eval_log));
+                        const int off0 = (int)e.x >> 20;
+#pragma unroll
+                        for (int j = 0; j < RPT; j++) v[2 * q][j] = __ldg(c0 + offset_row(row[j], off0, trace_log, eval_log));
                         d[2 * q] = e.y;
                         if (2 * q + 1 < (int)n) {
                             const uint32_t* c1 = reinterpret_cast<const uint32_t*>(ptrs[e.z & 0xfffffu]);
-                            v[2 * q + 1] = __ldg(c1 + offset_row(row, (int)e.z >> 20, trace_log, eval_log));
+                            const int off1 = (int)e.z >> 20;
+#pragma unroll
+                            for (int j = 0; j < RPT; j++) v[2 * q + 1][j] = __ldg(c1 + offset_row(row[j], off1, trace_log, eval_log));
                             d[2 * q + 1] = e.w;
                         }
                     }
                 }
 #pragma unroll
-                for (int q = 0; q < AIR_LOAD_BATCH; q++)
-                    if (q < (int)n) stb(d[q], v[q]);
+                for (int q = 0; q < AIR_LOAD_BATCH; q++) {
+                    if (q < (int)n) {
+#pragma unroll
+                        for (int j = 0; j < RPT; j++) sm[d[q] + tid + j * T] = v[q][j];
+                    }
+                }
                 pc += 1 + (n + 1) / 2;
                 ins = __ldg(code + pc);
                 continue;
             }
             const uint4 nxt = __ldg(code + pc + 1);
+            uint32_t rb[RPT];
+            qm31 re[RPT];
             switch (op) {
-                case BC_ADD_BB: stb(ins.y, m31_add(ldb(ins.z), ldb(ins.w))); break;
-                case BC_SUB_BB: stb(ins.y, m31_sub(ldb(ins.z), ldb(ins.w))); break;
-                case BC_MUL_BB: stb(ins.y, m31_mul(ldb(ins.z), ldb(ins.w))); break;
-                case BC_NEG_B: stb(ins.y, m31_neg(ldb(ins.z))); break;
-                case BC_INV_B: stb(ins.y, m31_inv(ldb(ins.z))); break;
-                case BC_MOV_B: stb(ins.y, ldb(ins.z)); break;
-                case BC_ADD_EE: ste(ins.y, qm31_add(lde(ins.z), lde(ins.w))); break;
-                case BC_SUB_EE: ste(ins.y, qm31_sub(lde(ins.z), lde(ins.w))); break;
-                case BC_MUL_EE: ste(ins.y, qm31_mul(lde(ins.z), lde(ins.w))); break;
-                case BC_NEG_E: ste(ins.y, qm31_neg(lde(ins.z))); break;
-                case BC_ADD_EB: {
-                    qm31 a = lde(ins.z);
-                    a.c[0] = m31_add(a.c[0], ldb(ins.w));
-                    ste(ins.y, a);
+                case BC_ACC_B: {
+                    const qm31 coef = lde(ins.w, 0);
+#pragma unroll
+                    for (int j = 0; j < RPT; j++) {
+                        const uint32_t a = ldb(ins.y, j);
+#pragma unroll
+                        for (int k = 0; k < 4; k++) acc[j][k] += (unsigned long long)coef.c[k] * a;
+                    }
                     break;
                 }
-                case BC_SUB_EB: {
-                    qm31 a = lde(ins.z);
-                    a.c[0] = m31_sub(a.c[0], ldb(ins.w));
-                    ste(ins.y, a);
+                case BC_ACC_E: {
+                    const qm31 coef = lde(ins.w, 0);
+#pragma unroll
+                    for (int j = 0; j < RPT; j++) {
+                        const qm31 t = qm31_mul(coef, lde(ins.y, j));
+#pragma unroll
+                        for (int k = 0; k < 4; k++) acc[j][k] += t.c[k];
+                    }
                     break;
                 }
-                case BC_SUB_BE: {
-                    qm31 b = qm31_neg(lde(ins.w));
-                    b.c[0] = m31_add(b.c[0], ldb(ins.z));
-                    ste(ins.y, b);
+                case BC_ACC_RED:
+#pragma unroll
+                    for (int j = 0; j < RPT; j++)
+#pragma unroll
+                        for (int k = 0; k < 4; k++) acc[j][k] = m31_reduce64(acc[j][k]);
                     break;
-                }
-                case BC_MUL_EB: ste(ins.y, qm31_mul_m31(lde(ins.z), ldb(ins.w))); break;
-                case BC_ACC_B: acc = qm31_add(acc, qm31_mul_m31(lde(ins.w), ldb(ins.z))); break;
-                case BC_ACC_E: acc = qm31_add(acc, qm31_mul(lde(ins.w), lde(ins.z))); break;
+#define ZK_B_CASE(NAME, EXPR)                                    \
+    case NAME:                                                   \
+        _Pragma("unroll") for (int j = 0; j < RPT; j++) rb[j] = (EXPR); \
+        finish_b(ins, rb);                                       \
+        break;
+#define ZK_E_CASE(NAME, EXPR)                                    \
+    case NAME:                                                   \
+        _Pragma("unroll") for (int j = 0; j < RPT; j++) re[j] = (EXPR); \
+        finish_e(ins, re);                                       \
+        break;
+                ZK_B_CASE(BC_ADD_BB, m31_add(ldb(ins.y, j), ldb(ins.z, j)))
+                ZK_B_CASE(BC_SUB_BB, m31_sub(ldb(ins.y, j), ldb(ins.z, j)))
+                ZK_B_CASE(BC_MUL_BB, m31_mul(ldb(ins.y, j), ldb(ins.z, j)))
+                ZK_B_CASE(BC_NEG_B, m31_neg(ldb(ins.y, j)))
+                ZK_B_CASE(BC_INV_B, m31_inv(ldb(ins.y, j)))
+                ZK_B_CASE(BC_MOV_B, ldb(ins.y, j))
+                ZK_B_CASE(BC_FMA_B, m31_add(m31_mul(ldb(ins.y, j), ldb(ins.z, j)), ldb(ins.w, j)))
+                ZK_B_CASE(BC_FMS_B, m31_sub(m31_mul(ldb(ins.y, j), ldb(ins.z, j)), ldb(ins.w, j)))
+                ZK_B_CASE(BC_FNMS_B, m31_sub(ldb(ins.w, j), m31_mul(ldb(ins.y, j), ldb(ins.z, j))))
+                ZK_E_CASE(BC_ADD_EE, qm31_add(lde(ins.y, j), lde(ins.z, j)))
+                ZK_E_CASE(BC_SUB_EE, qm31_sub(lde(ins.y, j), lde(ins.z, j)))
+                ZK_E_CASE(BC_MUL_EE, qm31_mul(lde(ins.y, j), lde(ins.z, j)))
+                ZK_E_CASE(BC_NEG_E, qm31_neg(lde(ins.y, j)))
+                ZK_E_CASE(BC_ADD_EB, qm31_add(lde(ins.y, j), qm31_from_m31(ldb(ins.z, j))))
+                ZK_E_CASE(BC_SUB_EB, qm31_sub(lde(ins.y, j), qm31_from_m31(ldb(ins.z, j))))
+                ZK_E_CASE(BC_SUB_BE, qm31_sub(qm31_from_m31(ldb(ins.y, j)), lde(ins.z, j)))
+                ZK_E_CASE(BC_MUL_EB, qm31_mul_m31(lde(ins.y, j), ldb(ins.z, j)))
+                ZK_E_CASE(BC_FMA_EB, qm31_add(lde(ins.w, j), qm31_mul_m31(lde(ins.y, j), ldb(ins.z, j))))
+                ZK_E_CASE(BC_FNMS_EB, qm31_sub(lde(ins.w, j), qm31_mul_m31(lde(ins.y, j), ldb(ins.z, j))))
+#undef ZK_B_CASE
+#undef ZK_E_CASE
                 default: break;
             }
             ins = nxt;
             pc++;
         }
-        if (active) {
-            const uint32_t di = __ldg(denom_inv + (row >> trace_log));
-            qm31 q = qm31_mul_m31(acc, di);
-            if (accumulate) {
 #pragma unroll
-                for (int k = 0; k < 4; k++) q.c[k] = m31_add(q.c[k], accum.c[k][row]);
+        for (int j = 0; j < RPT; j++) {
+            if (!active[j]) continue;
+            const uint32_t di = __ldg(denom_inv + (row[j] >> trace_log));
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                uint32_t q = m31_mul(m31_reduce64(acc[j][k]), di);
+                if (accumulate) q = m31_add(q, accum.c[k][row[j]]);
+                accum.c[k][row[j]] = q;
             }
-#pragma unroll
-            for (int k = 0; k < 4; k++) accum.c[k][row] = q.c[k];
         }
     }
 }
@@ -176,8 +258,9 @@ int zkb_air_compile(zkb_ctx* ctx, const zkb_air_op* ops, size_t n_ops, const uin
     cudaError_t e = cudaMalloc(&prog->d_code, bytes);
     if (e == cudaSuccess) e = cudaMemcpyAsync(prog->d_code, prog->code.data(), bytes, cudaMemcpyHostToDevice, ctx->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(air_eval_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(air_eval_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(air_eval_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(air_eval_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) {
         if (prog->d_code) cudaFree(prog->d_code);
         delete prog;
@@ -237,14 +320,15 @@ int zkb_constraint_quotients(zkb_ctx* ctx, const zkb_air_program* prog, const ui
     AccumPtrs ap{{accum[0], accum[1], accum[2], accum[3]}};
     const uint32_t T = prog->threads;
     const uint64_t n_rows = 1ull << eval_log;
-    const uint32_t n_tiles = (uint32_t)((n_rows + T - 1) / T);
+    const uint32_t RP = T * prog->rows_per_thread;
+    const uint32_t n_tiles = (uint32_t)((n_rows + RP - 1) / RP);
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx->device);
     const uint32_t grid = std::min<uint32_t>(n_tiles, (uint32_t)sms * prog->ctas_per_sm);
     ProfScope prof(ctx, "air_eval_kernel");
-    air_eval_kernel<<<grid, T, prog->smem_bytes, ctx->stream>>>(reinterpret_cast<const uint4*>(prog->d_code), d_table,
-                                                                 (uint32_t)table_words, prog->ptr_base, d_table + table_words,
-                                                                 trace_log, eval_log, ap, accumulate, n_tiles);
+    auto kernel = prog->rows_per_thread == 4 ? air_eval_kernel<4> : prog->rows_per_thread == 2 ? air_eval_kernel<2> : air_eval_kernel<1>;
+    kernel<<<grid, T, prog->smem_bytes, ctx->stream>>>(reinterpret_cast<const uint4*>(prog->d_code), d_table, (uint32_t)table_words,
+                                                        prog->ptr_base, d_table + table_words, trace_log, eval_log, ap, accumulate, n_tiles);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }

@@ -9,9 +9,11 @@
 //   2. row-independent instructions (literals, run-time scalars and everything computed from them alone) are taken
 //      out of the per-row code; the host evaluates them once per call into a table every row reads.
 //   3. dead instructions are dropped, repeated loads of one (column, offset) are merged.
-//   4. loads are issued in batches of up to 8, each batch just before its first value is needed, so that a row has
+//   4. a multiplication read only by one addition or subtraction is folded into it, and an instruction whose result
+//      is a constraint also adds it to the row's sum (and skips the store when nothing else reads it).
+//   5. loads are issued in batches of up to 8, each batch just before its first value is needed, so that a row has
 //      several column reads in flight while its register footprint stays small.
-//   5. registers (words of shared memory per row) are assigned by a linear scan over the final instruction order;
+//   6. registers (words of shared memory per row) are assigned by a linear scan over the final instruction order;
 //      an operand that dies at an instruction gives its words to the result.
 #include <algorithm>
 #include <map>
@@ -62,7 +64,9 @@ struct Sym {
 };
 struct SymInstr {
     uint32_t op = BC_END, n = 0, dst = 0;
-    Sym a, b;
+    bool has_dst = false;
+    int64_t coef = -1;  // constraint whose coefficient multiplies the result (or the operand of an ACC instruction)
+    Sym a, b, c;
     std::vector<std::pair<uint32_t, uint32_t>> loads;  // (column | offset << 20, dst slot)
 };
 
@@ -171,17 +175,113 @@ std::string air_compile(zkb_air_program& P, const zkb_air_op* ops, size_t n_ops,
         }
     }
 
-    // ---- 3. order of the per-row work: compute instructions in program order, each constraint accumulated as soon
-    //         as its value exists
-    struct Item { int kind; uint32_t idx; };  // 0 compute, 1 accumulate constraint idx, 2 load batch [idx, n)
+    // ---- 3. the bytecode form of every per-row instruction. A multiplication whose only reader is an addition or a
+    //         subtraction is folded into it (a * b + c, a * b - c, c - a * b; for secure values the forms with one
+    //         base factor), which saves its store and reload.
     std::vector<std::vector<uint32_t>> cons_of(N);
     for (uint32_t k = 0; k < n_constraints; k++) cons_of[P.constraints[k]].push_back(k);
-    std::vector<Item> items;
     auto per_row_compute = [&](uint32_t i) { return P.live[i] && !P.uniform[i] && P.alias[i] == i && P.ops[i].op != ZKB_AIR_LOAD; };
+    std::vector<uint32_t> uses(N, 0);
+    for (uint32_t i = 0; i < N; i++)
+        if (per_row_compute(i))
+            for (int k = 0; k < arity(P.ops[i].op); k++) uses[operand(P.ops[i], k)]++;
+    enum Cls { ADD, SUB, MUL, NEG, INV, PACKC };
+    auto cls_of = [](uint32_t op) {
+        switch (op) {
+            case ZKB_AIR_ADD_B: case ZKB_AIR_ADD_E: return ADD;
+            case ZKB_AIR_SUB_B: case ZKB_AIR_SUB_E: return SUB;
+            case ZKB_AIR_MUL_B: case ZKB_AIR_MUL_E: return MUL;
+            case ZKB_AIR_INV_B: return INV;
+            case ZKB_AIR_PACK: return PACKC;
+            default: return NEG;
+        }
+    };
+    struct Form { uint32_t bc = BC_END; int n = 0; uint32_t src[4] = {0, 0, 0, 0}; };
+    std::vector<Form> form(N);
+    std::vector<uint8_t> folded(N, 0);
+    auto foldable_mul = [&](uint32_t m, bool want_ext) {
+        if (!per_row_compute(m) || cls_of(P.ops[m].op) != MUL || uses[m] != 1 || !cons_of[m].empty()) return false;
+        if (!want_ext) return !P.ext[m];
+        return P.ext[m] && P.ext[P.ops[m].a] != P.ext[P.ops[m].b];  // exactly one secure factor
+    };
+    uint64_t mults = 0;
     for (uint32_t i = 0; i < N; i++) {
         if (!per_row_compute(i)) continue;
+        const zkb_air_op& o = P.ops[i];
+        const Cls cls = cls_of(o.op);
+        Form f;
+        if (cls == PACKC) {
+            f.bc = BC_MOV_B;
+            f.n = 4;
+            f.src[0] = o.a; f.src[1] = o.b; f.src[2] = o.c; f.src[3] = o.d;
+            form[i] = f;
+            continue;
+        }
+        if ((cls == ADD || cls == SUB) && o.a != o.b) {
+            const bool we = P.ext[i];
+            uint32_t m = N;
+            bool m_is_b = false;
+            if (foldable_mul(o.b, we) && (!we || P.ext[o.a])) { m = o.b; m_is_b = true; }
+            else if (foldable_mul(o.a, we) && (!we || P.ext[o.b]) && (cls == ADD || !we)) m = o.a;
+            if (m < N) {
+                uint32_t fa = P.ops[m].a, fb = P.ops[m].b;
+                if (we && !P.ext[fa]) std::swap(fa, fb);  // the secure factor first
+                if (cls == ADD) f.bc = we ? BC_FMA_EB : BC_FMA_B;
+                else if (m_is_b) f.bc = we ? BC_FNMS_EB : BC_FNMS_B;
+                else f.bc = BC_FMS_B;
+                f.n = 3;
+                f.src[0] = fa; f.src[1] = fb; f.src[2] = m_is_b ? o.a : o.b;
+                folded[m] = 1;
+                mults += we ? 4 : 1;
+                form[i] = f;
+                continue;
+            }
+        }
+        const int ar = arity(o.op);
+        const bool ea = P.ext[o.a], eb = ar == 2 ? (bool)P.ext[o.b] : false;
+        uint32_t s0 = o.a, s1 = ar == 2 ? o.b : 0;
+        switch (cls) {
+            case ADD:
+                f.bc = ea && eb ? BC_ADD_EE : !ea && !eb ? BC_ADD_BB : BC_ADD_EB;
+                if (!ea && eb) std::swap(s0, s1);
+                break;
+            case SUB: f.bc = ea && eb ? BC_SUB_EE : !ea && !eb ? BC_SUB_BB : ea ? BC_SUB_EB : BC_SUB_BE; break;
+            case MUL:
+                f.bc = ea && eb ? BC_MUL_EE : !ea && !eb ? BC_MUL_BB : BC_MUL_EB;
+                if (!ea && eb) std::swap(s0, s1);
+                break;
+            case NEG: f.bc = ea ? BC_NEG_E : BC_NEG_B; break;
+            case INV: f.bc = BC_INV_B; break;
+            default: break;
+        }
+        f.n = ar;
+        f.src[0] = s0; f.src[1] = s1;
+        form[i] = f;
+    }
+    for (uint32_t i = 0; i < N; i++) {  // multiplications that stayed instructions of their own
+        if (!per_row_compute(i) || folded[i]) continue;
+        if (form[i].bc == BC_MUL_BB) mults += 1;
+        else if (form[i].bc == BC_MUL_EB) mults += 4;
+        else if (form[i].bc == BC_MUL_EE) mults += 16;
+        else if (form[i].bc == BC_INV_B) mults += 37;
+    }
+
+    // ---- 4. order of the per-row work: instructions in program order; a constraint is accumulated by the
+    //         instruction that computes it where that instruction has a free operand field, else right after it
+    struct Item { int kind; uint32_t idx; };  // 0 compute, 1 accumulate constraint idx, 2 load batch [idx, n), 3 fold row_res
+    std::vector<int64_t> acc_fused(N, -1);
+    std::vector<uint8_t> nostore(N, 0);
+    std::vector<Item> items;
+    for (uint32_t i = 0; i < N; i++) {
+        if (!per_row_compute(i) || folded[i]) continue;
         items.push_back({0, i});
-        for (uint32_t k : cons_of[i]) items.push_back({1, k});
+        size_t first = 0;
+        if (!cons_of[i].empty() && form[i].n <= 2) {
+            acc_fused[i] = cons_of[i][0];
+            nostore[i] = uses[i] == 0 && cons_of[i].size() == 1;
+            first = 1;
+        }
+        for (size_t q = first; q < cons_of[i].size(); q++) items.push_back({1, cons_of[i][q]});
     }
     for (uint32_t k = 0; k < n_constraints; k++) {
         uint32_t v = P.constraints[k];
@@ -189,9 +289,9 @@ std::string air_compile(zkb_air_program& P, const zkb_air_op* ops, size_t n_ops,
     }
     auto reads = [&](const Item& it, uint32_t out[4]) -> int {
         if (it.kind == 1) { out[0] = P.constraints[it.idx]; return 1; }
-        const int ar = arity(P.ops[it.idx].op);
-        for (int k = 0; k < ar; k++) out[k] = operand(P.ops[it.idx], k);
-        return ar;
+        if (it.kind != 0) return 0;
+        for (int k = 0; k < form[it.idx].n; k++) out[k] = form[it.idx].src[k];
+        return form[it.idx].n;
     };
     // loads by first use
     std::vector<int64_t> first_use(N, -1);
@@ -209,6 +309,7 @@ std::string air_compile(zkb_air_program& P, const zkb_air_op* ops, size_t n_ops,
     std::vector<uint32_t> batch_len;
     {
         size_t p = 0;
+        int units = 0;  // base-field constraints added to row_res since it was last folded (each below 2^62)
         for (size_t j = 0; j < items.size(); j++) {
             while (p < loads.size() && first_use[loads[p]] <= (int64_t)j) {
                 uint32_t n = (uint32_t)std::min<size_t>(AIR_LOAD_BATCH, loads.size() - p);
@@ -217,15 +318,20 @@ std::string air_compile(zkb_air_program& P, const zkb_air_op* ops, size_t n_ops,
                 batch_len.back() = n;
                 p += n;
             }
-            order.push_back(items[j]);
+            const Item& it = items[j];
+            const bool adds_base = (it.kind == 1 && !P.ext[P.constraints[it.idx]]) || (it.kind == 0 && acc_fused[it.idx] >= 0 && !P.ext[it.idx]);
+            if (adds_base) {
+                if (units == 3) { order.push_back({3, 0}); units = 0; }
+                units++;
+            }
+            order.push_back(it);
             batch_len.resize(order.size(), 0);
         }
     }
 
-    // ---- 4. last reads, then registers
+    // ---- 5. last reads, then registers
     std::vector<int64_t> last_use(N, -1);
     for (size_t j = 0; j < order.size(); j++) {
-        if (order[j].kind == 2) continue;
         uint32_t rd[4];
         int n = reads(order[j], rd);
         for (int k = 0; k < n; k++) last_use[rd[k]] = (int64_t)j;
@@ -253,13 +359,16 @@ std::string air_compile(zkb_air_program& P, const zkb_air_op* ops, size_t n_ops,
             slot[v] = -1;
         }
     };
-    // the coefficient of constraint k is 4 words of the uniform table, after the uniform values; patched below
     std::vector<SymInstr> sym_code;
-    uint64_t mults = 0;
     std::vector<uint8_t> col_read(P.n_cols, 0);
     for (size_t j = 0; j < order.size(); j++) {
         const Item& it = order[j];
         SymInstr si;
+        if (it.kind == 3) {
+            si.op = BC_ACC_RED;
+            sym_code.push_back(si);
+            continue;
+        }
         if (it.kind == 2) {
             si.op = BC_LOAD;
             si.n = batch_len[j];
@@ -280,104 +389,100 @@ std::string air_compile(zkb_air_program& P, const zkb_air_op* ops, size_t n_ops,
             uint32_t v = P.constraints[it.idx];
             si.op = P.ext[v] ? BC_ACC_E : BC_ACC_B;
             si.a = sym(v);
-            si.b.reg = false;
-            si.b.idx = 4 * it.idx;  // relative to coef_base
-            si.n = 1;               // marks b as a coefficient
+            si.coef = (int64_t)it.idx;
             mults += P.ext[v] ? 16 : 4;
             sym_code.push_back(si);
             release(v, (int64_t)j);
             continue;
         }
         const uint32_t i = it.idx;
-        const zkb_air_op& o = P.ops[i];
-        if (o.op == ZKB_AIR_PACK) {
-            const uint32_t src[4] = {o.a, o.b, o.c, o.d};
+        const Form& f = form[i];
+        if (f.bc == BC_MOV_B) {  // PACK: four moves into a fresh secure register
             slot[i] = pool.take(4);
             for (int k = 0; k < 4; k++) {
                 SymInstr mv;
                 mv.op = BC_MOV_B;
+                mv.has_dst = true;
                 mv.dst = (uint32_t)slot[i] + k;
-                mv.a = sym(src[k]);
+                mv.a = sym(f.src[k]);
                 sym_code.push_back(mv);
             }
-            for (int k = 0; k < 4; k++) release(src[k], (int64_t)j);
+            for (int k = 0; k < 4; k++) release(f.src[k], (int64_t)j);
             continue;
         }
-        const int ar = arity(o.op);
-        const bool ea = P.ext[o.a], eb = ar == 2 ? (bool)P.ext[o.b] : false;
-        Sym sa = sym(o.a), sb = ar == 2 ? sym(o.b) : Sym{};
-        enum { ADD, SUB, MUL, NEG, INV } cls;
-        switch (o.op) {
-            case ZKB_AIR_ADD_B: case ZKB_AIR_ADD_E: cls = ADD; break;
-            case ZKB_AIR_SUB_B: case ZKB_AIR_SUB_E: cls = SUB; break;
-            case ZKB_AIR_MUL_B: case ZKB_AIR_MUL_E: cls = MUL; break;
-            case ZKB_AIR_INV_B: cls = INV; break;
-            default: cls = NEG; break;
+        si.op = f.bc;
+        si.a = sym(f.src[0]);
+        if (f.n >= 2) si.b = sym(f.src[1]);
+        if (f.n >= 3) si.c = sym(f.src[2]);
+        for (int k = 0; k < f.n; k++) release(f.src[k], (int64_t)j);  // release() is a no-op the second time
+        if (acc_fused[i] >= 0) {
+            si.coef = acc_fused[i];
+            mults += P.ext[i] ? 16 : 4;
         }
-        switch (cls) {
-            case ADD:
-                si.op = ea && eb ? BC_ADD_EE : !ea && !eb ? BC_ADD_BB : BC_ADD_EB;
-                if (!ea && eb) std::swap(sa, sb);
-                break;
-            case SUB:
-                si.op = ea && eb ? BC_SUB_EE : !ea && !eb ? BC_SUB_BB : ea ? BC_SUB_EB : BC_SUB_BE;
-                break;
-            case MUL:
-                si.op = ea && eb ? BC_MUL_EE : !ea && !eb ? BC_MUL_BB : BC_MUL_EB;
-                if (!ea && eb) std::swap(sa, sb);
-                mults += ea && eb ? 16 : !ea && !eb ? 1 : 4;
-                break;
-            case NEG: si.op = ea ? BC_NEG_E : BC_NEG_B; break;
-            case INV: si.op = BC_INV_B; mults += 37; break;
+        if (!nostore[i]) {
+            slot[i] = pool.take(P.ext[i] ? 4 : 1);
+            si.has_dst = true;
+            si.dst = (uint32_t)slot[i];
         }
-        si.a = sa;
-        si.b = sb;
-        release(o.a, (int64_t)j);
-        if (ar == 2 && o.b != o.a) release(o.b, (int64_t)j);
-        slot[i] = pool.take(P.ext[i] ? 4 : 1);
-        si.dst = (uint32_t)slot[i];
         sym_code.push_back(si);
+        if (last_use[i] < 0 && slot[i] >= 0) {  // stored for a later ACC only; cannot happen, but never leak a register
+            pool.give((uint32_t)slot[i], P.ext[i] ? 4 : 1);
+            slot[i] = -1;
+        }
     }
 
-    // ---- 5. shared-memory layout and CTA size
+    // ---- 6. shared-memory layout, CTA size, rows per thread
     P.reg_words = std::max<uint32_t>(pool.high, 1);
     P.coef_base = uni_words;
     uint32_t table = uni_words + 4 * (uint32_t)n_constraints;
     table += table & 1;
     P.ptr_base = table;
     P.reg_base = P.ptr_base + 2 * P.n_cols;
-    const uint32_t budget = 227 * 1024;
-    uint32_t best_threads = 0, best_resident = 0, best_ctas = 1;
-    for (uint32_t t : {256u, 128u, 64u, 32u}) {
-        uint64_t bytes = 4ull * (P.reg_base + (uint64_t)P.reg_words * t);
-        if (bytes > budget) continue;
-        uint32_t ctas = (uint32_t)std::min<uint64_t>({budget / (bytes + 1024), 1024 / t, 16});
-        ctas = std::max(ctas, 1u);
-        if (ctas * t > best_resident) { best_resident = ctas * t; best_threads = t; best_ctas = ctas; }
+    const uint64_t budget = 227 * 1024;
+    auto smem_of = [&](uint32_t t, uint32_t rpt) { return 4ull * (P.reg_base + (uint64_t)P.reg_words * t * rpt); };
+    P.threads = 0;
+    if (smem_of(256, 4) + 1024 <= budget / 2) {
+        P.threads = 256; P.rows_per_thread = 4; P.ctas_per_sm = 2;
+    } else if (smem_of(256, 2) + 1024 <= budget / 2) {
+        P.threads = 256; P.rows_per_thread = 2;
+        P.ctas_per_sm = (uint32_t)std::min<uint64_t>(3, budget / (smem_of(256, 2) + 1024));
+    } else {
+        uint32_t best_resident = 0;
+        for (uint32_t t : {256u, 128u, 64u, 32u}) {
+            uint64_t bytes = smem_of(t, 1);
+            if (bytes + 1024 > budget) continue;
+            uint32_t ctas = (uint32_t)std::min<uint64_t>({budget / (bytes + 1024), 1024 / t, 16});
+            ctas = std::max(ctas, 1u);
+            if (ctas * t > best_resident) { best_resident = ctas * t; P.threads = t; P.ctas_per_sm = ctas; }
+        }
+        P.rows_per_thread = 1;
     }
-    if (!best_threads)
+    if (!P.threads)
         return "the program keeps " + std::to_string(P.reg_words) + " words alive per row and reads " + std::to_string(P.n_cols) +
                " columns: more than one CTA's shared memory holds";
-    P.threads = best_threads;
-    P.ctas_per_sm = best_ctas;
-    P.smem_bytes = 4 * (P.reg_base + P.reg_words * P.threads);
+    const uint32_t RP = P.threads * P.rows_per_thread;
+    P.smem_bytes = (uint32_t)smem_of(P.threads, P.rows_per_thread);
 
-    // ---- 6. encode
-    auto enc = [&](const Sym& s) { return s.reg ? ((P.reg_base + s.idx * P.threads) << 1) | 1u : (s.idx << 1); };
+    // ---- 7. encode
+    auto enc = [&](const Sym& s) { return s.reg ? ((P.reg_base + s.idx * RP) << 1) | 1u : (s.idx << 1); };
     P.code.clear();
     for (const SymInstr& si : sym_code) {
         if (si.op == BC_LOAD) {
             P.code.push_back({BC_LOAD | (si.n << 8), 0, 0, 0});
             for (uint32_t q = 0; q < si.n; q += 2) {
-                AirInstr e{si.loads[q].first, P.reg_base + si.loads[q].second * P.threads, 0, 0};
-                if (q + 1 < si.n) { e.z = si.loads[q + 1].first; e.w = P.reg_base + si.loads[q + 1].second * P.threads; }
+                AirInstr e{si.loads[q].first, P.reg_base + si.loads[q].second * RP, 0, 0};
+                if (q + 1 < si.n) { e.z = si.loads[q + 1].first; e.w = P.reg_base + si.loads[q + 1].second * RP; }
                 P.code.push_back(e);
             }
             continue;
         }
-        AirInstr e{si.op, P.reg_base + si.dst * P.threads, enc(si.a), 0};
-        if (si.op == BC_ACC_B || si.op == BC_ACC_E) e.w = (P.coef_base + si.b.idx) << 1;
-        else e.w = enc(si.b);
+        AirInstr e{si.op, enc(si.a), enc(si.b), enc(si.c)};
+        if (si.has_dst) e.x |= (P.reg_base + si.dst * RP) << 8;
+        else if (si.op >= BC_ADD_BB) e.x |= BC_F_NOSTORE;
+        if (si.coef >= 0) {
+            e.w = (P.coef_base + 4 * (uint32_t)si.coef) << 1;
+            if (si.op >= BC_ADD_BB) e.x |= BC_F_ACC;
+        }
         P.code.push_back(e);
     }
     P.code.push_back({BC_END, 0, 0, 0});
@@ -398,6 +503,7 @@ std::string air_compile(zkb_air_program& P, const zkb_air_op* ops, size_t n_ops,
     st.reg_words = P.reg_words;
     st.uniform_words = P.ptr_base;
     st.threads = P.threads;
+    st.rows_per_thread = P.rows_per_thread;
     st.smem_bytes = P.smem_bytes;
     st.m31_mults = (uint32_t)std::min<uint64_t>(mults, 0xffffffffu);
     return "";
