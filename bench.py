@@ -640,8 +640,27 @@ def run_constraints(args, rank):
         ctx.constraint_quotients(prog, [c.ptr for c in cols], case["rcp"], trace_log, eval_log, [a.ptr for a in acc], accumulate=False,
                                  cumsum_shift=case["cumsum_shift"])
         parity = golden_check(case["name"], np.stack([a.download() for a in acc]).reshape(-1))
+        # the same program specialised into a kernel of its own (zkb_air_specialize)
+        t0 = time.perf_counter()
+        prog.specialize()
+        jit_s = time.perf_counter() - t0
+        tj = []
+        for it in range(args.warmup + args.steps):
+            ctx.event_record(0)
+            ctx.constraint_quotients(prog, [c.ptr for c in cols], case["rcp"], trace_log, eval_log, [a.ptr for a in acc], accumulate=True,
+                                     cumsum_shift=case["cumsum_shift"])
+            ctx.event_record(1)
+            ctx.sync()
+            if it >= args.warmup:
+                tj.append(ctx.event_elapsed_ms(0, 1))
+        ctx.constraint_quotients(prog, [c.ptr for c in cols], case["rcp"], trace_log, eval_log, [a.ptr for a in acc], accumulate=False,
+                                 cumsum_shift=case["cumsum_shift"])
+        golden_check(case["name"], np.stack([a.download() for a in acc]).reshape(-1))
+        ms_interp, ms = ms, float(np.mean(tj))
+        st = prog.stats
         bytes_alg = (4.0 * st["n_columns_read"] + 32.0) * N  # every column read once, the accumulator read and written
-        results[which] = {"workload": case["name"], "ms": ms, "rows_per_s": N / (ms * 1e-3), "columns": len(cols),
+        results[which] = {"workload": case["name"], "ms": ms, "ms_interpreter": ms_interp, "specialize_s": jit_s,
+                          "rows_per_s": N / (ms * 1e-3), "columns": len(cols),
                           "constraints": int(src.n_constraints), "algorithmic_gbs": bytes_alg / (ms * 1e-3) / 1e9,
                           "m31_gmults_per_s": st["m31_mults"] * N / (ms * 1e-3) / 1e9, "program": st, "parity": parity}
         return cols, case["rcp"], ms, bytes_alg
@@ -689,10 +708,10 @@ def run_constraints(args, rank):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": wf_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "u32 (M31)", "data": "synthetic",
             "config": {"workload": f"constraint_quotients_wide_fibonacci_{ncols}cols_log{trace_log}_eval_log{eval_log}", "l2": "columns (2 GiB) are larger than L2"},
-            "roofline": {"bound": "hbm", "kernel": "air_eval_kernel", "achieved": wf_bytes / (wf_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+            "roofline": {"bound": "hbm", "kernel": "air_jit (the program's specialised kernel)", "achieved": wf_bytes / (wf_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": wf_bytes / (wf_ms * 1e-3) / 1e9 / peak, "peak_kind": peak_kind, "traffic": None,
                          "note": "algorithmic bytes: every column read once, the accumulator read and written"},
-            "gpu_launches": args.steps, "airs": results, "gpu_baseline": gpu_ref, "cpu_baseline": cpu}
+            "gpu_launches": 2 * args.steps, "airs": results, "gpu_baseline": gpu_ref, "cpu_baseline": cpu}
     print(json.dumps(line))
     ctx.close()
 

@@ -67,6 +67,8 @@ typedef struct zkb_air_stats {
     uint32_t rows_per_thread;  /* rows one thread evaluates side by side (1, 2 or 4) */
     uint32_t smem_bytes;       /* dynamic shared memory per CTA */
     uint32_t m31_mults;        /* M31 multiplications per row */
+    uint32_t specialized;      /* 1 once zkb_air_specialize has succeeded */
+    uint32_t specialized_regs; /* registers per thread of the specialised kernel, 0 if unknown */
 } zkb_air_stats;
 
 /* Compiles a program. `constraints[i]` is the instruction whose value is the i-th add_constraint call, in call
@@ -78,6 +80,15 @@ typedef struct zkb_air_stats {
 int zkb_air_compile(zkb_ctx* ctx, const zkb_air_op* ops, size_t n_ops, const uint32_t* constraints, size_t n_constraints,
                     const uint32_t* tree_cols, int n_trees, size_t n_scalars, zkb_air_program** out);
 int zkb_air_free(zkb_air_program* prog);
+
+/* Optional second step: turns the program into straight-line CUDA in which every per-row value is a register,
+ * compiles it for sm_100a with NVRTC (found with dlopen at the first call; nothing links against it) and loads it.
+ * This is the run-time counterpart of the reference's per-shape generated kernels (prover/src/cudagen.rs:1985-2290).
+ * On success zkb_constraint_quotients uses the specialised kernel; zkb_air_select switches between it (1) and the
+ * interpreter (0), whose results are identical. ZKB_ECUDA with a message if NVRTC is absent or the compilation fails:
+ * the program stays usable through the interpreter. Takes about a second per thousand instructions. */
+int zkb_air_specialize(zkb_ctx* ctx, zkb_air_program* prog);
+int zkb_air_select(zkb_air_program* prog, int specialized);
 int zkb_air_get_stats(const zkb_air_program* prog, zkb_air_stats* out);
 
 /* FrameworkComponent::evaluate_constraint_quotients_on_domain for one component.

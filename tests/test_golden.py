@@ -55,9 +55,12 @@ def test_cuda_reproduces_air_digest(ctx, name):
     prog = ctx.air_compile(case["source"])
     bufs = [ctx.upload(c) for c in case["cols"]]
     acc = [ctx.alloc(1 << case["eval_log"]) for _ in range(4)]
-    ctx.constraint_quotients(prog, [b.ptr for b in bufs], case["rcp"], case["trace_log"], case["eval_log"], [a.ptr for a in acc],
-                             accumulate=False, cumsum_shift=case["cumsum_shift"])
-    _check(name, np.stack([a.download() for a in acc]))
+    for specialized in (False, True):
+        if specialized:
+            prog.specialize()
+        ctx.constraint_quotients(prog, [b.ptr for b in bufs], case["rcp"], case["trace_log"], case["eval_log"], [a.ptr for a in acc],
+                                 accumulate=False, cumsum_shift=case["cumsum_shift"])
+        _check(name, np.stack([a.download() for a in acc]))
 
 
 @pytest.mark.gpu

@@ -12,13 +12,22 @@ pytestmark = pytest.mark.gpu
 
 
 def run_gpu(ctx, case, accum=None, prog=None):
+    """Both device paths - the interpreter, then the kernel specialised with NVRTC - which must agree word for word."""
     prog = prog or ctx.air_compile(case["source"])
     n = 1 << case["eval_log"]
     bufs = [ctx.upload(c) for c in case["cols"]]
-    acc = [ctx.upload(accum[k]) if accum is not None else ctx.alloc(n) for k in range(4)]
-    ctx.constraint_quotients(prog, [b.ptr for b in bufs], case["rcp"], case["trace_log"], case["eval_log"], [a.ptr for a in acc],
-                             accumulate=accum is not None, cumsum_shift=case["cumsum_shift"])
-    return np.stack([a.download() for a in acc])
+    out = []
+    for specialized in (False, True):
+        if specialized:
+            prog.specialize()
+            assert prog.stats["specialized"] == 1
+        acc = [ctx.upload(accum[k]) if accum is not None else ctx.alloc(n) for k in range(4)]
+        ctx.constraint_quotients(prog, [b.ptr for b in bufs], case["rcp"], case["trace_log"], case["eval_log"], [a.ptr for a in acc],
+                                 accumulate=accum is not None, cumsum_shift=case["cumsum_shift"])
+        out.append(np.stack([a.download() for a in acc]))
+    prog.select(False)
+    assert (out[0] == out[1]).all(), "the specialised kernel and the interpreter disagree"
+    return out[0]
 
 
 def test_reference_airs_match_oracle(ctx, oracle):
@@ -68,6 +77,12 @@ def test_random_programs_match_oracle(ctx, oracle, seed, n_ops, eval_log):
     ctx.constraint_quotients(prog, [b.ptr for b in bufs], rcp, trace_log, eval_log, [a.ptr for a in acc], accumulate=False, cumsum_shift=shift,
                              scalars=sc2)
     assert (np.stack([a.download() for a in acc]) == want2).all()
+    # and the kernel specialised to the program gives the same words, for both sets of scalars
+    prog.specialize()
+    for sc, w in ((None, want), (sc2, want2)):
+        ctx.constraint_quotients(prog, [b.ptr for b in bufs], rcp, trace_log, eval_log, [a.ptr for a in acc], accumulate=False, cumsum_shift=shift,
+                                 scalars=sc)
+        assert (np.stack([a.download() for a in acc]) == w).all()
 
 
 def test_compile_rejects_bad_programs(ctx, zkb):
@@ -149,6 +164,8 @@ def test_full_size_wide_fibonacci_quotient_is_a_polynomial(ctx, oracle):
     prog = ctx.air_compile(case["source"])
     rcp = qm31_array(77, n_cols - 2)
     for corrupt in (False, True):
+        if corrupt:
+            prog.specialize()   # the second pass runs the specialised kernel
         cols = [ctx.upload(c.astype(np.uint32)) for c in trace]
         if corrupt:
             bad = trace[9].astype(np.uint32)

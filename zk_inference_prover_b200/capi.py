@@ -24,7 +24,7 @@ EXPORTED_SYMBOLS = [
 # Every symbol include/zkb200_prover.h declares.
 PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_gkr_prove_device"]
 # Every symbol include/zkb200_air.h declares.
-AIR_SYMBOLS = ["zkb_air_compile", "zkb_air_free", "zkb_air_get_stats", "zkb_constraint_quotients", "zkb_constraint_denom_inv"]
+AIR_SYMBOLS = ["zkb_air_compile", "zkb_air_free", "zkb_air_specialize", "zkb_air_select", "zkb_air_get_stats", "zkb_constraint_quotients", "zkb_constraint_denom_inv"]
 PCS_PHASES = ["interpolate", "extend", "merkle", "sample", "quotients", "fri_commit", "grind", "decommit"]
 
 
@@ -40,7 +40,7 @@ class PcsConfig(C.Structure):
 
 class AirStats(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("n_ops", "n_live_ops", "n_uniform", "n_instr", "n_loads", "n_columns_read", "reg_words",
-                                          "uniform_words", "threads", "rows_per_thread", "smem_bytes", "m31_mults")]
+                                          "uniform_words", "threads", "rows_per_thread", "smem_bytes", "m31_mults", "specialized", "specialized_regs")]
 
 
 class ZkbError(RuntimeError):
@@ -161,6 +161,16 @@ class AirProgram:
         st = AirStats()
         self.ctx._check(self.ctx.lib.zkb_air_get_stats(self.h, C.byref(st)))
         return {n: getattr(st, n) for n, _ in AirStats._fields_}
+
+    def specialize(self):
+        """zkb_air_specialize: compile a kernel for this program with NVRTC and use it from now on."""
+        self.ctx._check(self.ctx.lib.zkb_air_specialize(self.ctx.h, self.h))
+        return self
+
+    def select(self, specialized):
+        if self.ctx.lib.zkb_air_select(self.h, C.c_int(int(specialized))) != 0:
+            raise ZkbError(-1, "zkb_air_select: the program has no specialised kernel")
+        return self
 
     def free(self):
         if getattr(self, "h", None):

@@ -87,6 +87,10 @@ struct zkb_air_program {
     std::vector<zk::AirInstr> code;
     zk::AirInstr* d_code = nullptr;
     int device = -1;
+    // ---- optional specialised kernel (csrc/host/air_jit.cpp): cudaLibrary_t / cudaKernel_t handles
+    void* jit_library = nullptr;
+    void* jit_kernel = nullptr;
+    bool use_jit = false;
     zkb_air_stats stats{};
 };
 
@@ -100,5 +104,10 @@ std::string air_compile(zkb_air_program& prog, const zkb_air_op* ops, size_t n_o
 // uniform values, then the constraint coefficients.
 void air_fill_uniform(const zkb_air_program& prog, const uint32_t* scalars, const uint32_t* cumsum_shift,
                       const uint32_t* random_coeff_powers, uint32_t* table);
+
+// csrc/host/air_jit.cpp: CUDA source of a kernel specialised to the program, and its compilation with NVRTC
+// (loaded with dlopen). Both return an empty string on success or the reason.
+std::string air_codegen(const zkb_air_program& prog);
+std::string air_nvrtc_compile(const std::string& source, std::vector<char>& cubin, std::string* ptxas_info);
 
 }  // namespace zk

@@ -13,7 +13,9 @@
 // are issued in batches of up to 8 independent loads; for a mask offset the 256 rows of a tile map to another run of
 // consecutive rows except where the offset carries into the tile's own bits, so those reads coalesce as well.
 #include <algorithm>
+#include <cstdlib>
 #include <new>
+#include <string>
 #include <vector>
 
 #include "air_program.hpp"
@@ -276,10 +278,51 @@ int zkb_air_free(zkb_air_program* prog) {
         int prev = -1;
         cudaGetDevice(&prev);
         if (prev != prog->device) cudaSetDevice(prog->device);
+        if (prog->jit_library) cudaLibraryUnload((cudaLibrary_t)prog->jit_library);
         cudaFree(prog->d_code);
         if (prev >= 0 && prev != prog->device) cudaSetDevice(prev);
     }
     delete prog;
+    return ZKB_OK;
+}
+
+int zkb_air_specialize(zkb_ctx* ctx, zkb_air_program* prog) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, prog != nullptr && prog->device == ctx->device);
+    if (prog->jit_kernel) { prog->use_jit = true; return ZKB_OK; }
+    const size_t table_bytes = 4 * ((size_t)prog->ptr_base + 2 * (size_t)prog->n_cols);
+    if (table_bytes > 200 * 1024) return set_error(ctx, ZKB_EINVAL, "zkb_air_specialize: the program's table of %zu bytes does not fit shared memory", table_bytes);
+    std::vector<char> cubin;
+    std::string info, why;
+    try {
+        why = air_nvrtc_compile(air_codegen(*prog), cubin, &info);
+    } catch (const std::bad_alloc&) {
+        return set_error(ctx, ZKB_ENOMEM, "zkb_air_specialize: out of host memory");
+    }
+    if (!why.empty()) return set_error(ctx, ZKB_ECUDA, "zkb_air_specialize: %s", why.c_str());
+    DeviceGuard g(ctx);
+    cudaLibrary_t lib = nullptr;
+    cudaKernel_t kernel = nullptr;
+    cudaError_t e = cudaLibraryLoadData(&lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
+    if (e == cudaSuccess) e = cudaLibraryGetKernel(&kernel, lib, "air_jit");
+    if (e == cudaSuccess && table_bytes > 48 * 1024)
+        e = cudaFuncSetAttribute((const void*)kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)table_bytes);
+    if (e != cudaSuccess) {
+        if (lib) cudaLibraryUnload(lib);
+        return set_error(ctx, ZKB_ECUDA, "zkb_air_specialize: loading the compiled kernel: %s", cudaGetErrorString(e));
+    }
+    prog->jit_library = lib;
+    prog->jit_kernel = kernel;
+    prog->use_jit = true;
+    prog->stats.specialized = 1;
+    const size_t at = info.find("Used ");
+    if (at != std::string::npos) prog->stats.specialized_regs = (uint32_t)atoi(info.c_str() + at + 5);
+    return ZKB_OK;
+}
+
+int zkb_air_select(zkb_air_program* prog, int specialized) {
+    if (!prog || (specialized && !prog->jit_kernel)) return ZKB_EINVAL;
+    prog->use_jit = specialized != 0;
     return ZKB_OK;
 }
 
@@ -325,6 +368,16 @@ int zkb_constraint_quotients(zkb_ctx* ctx, const zkb_air_program* prog, const ui
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx->device);
     const uint32_t grid = std::min<uint32_t>(n_tiles, (uint32_t)sms * prog->ctas_per_sm);
+    if (prog->use_jit) {  // the specialised kernel: one row per thread, the same table and arguments
+        uint32_t tw = (uint32_t)table_words, pb = prog->ptr_base, tiles = (uint32_t)((n_rows + 255) / 256);
+        const uint32_t* d_den = d_table + table_words;
+        uint32_t* q[4] = {accum[0], accum[1], accum[2], accum[3]};
+        void* args[] = {(void*)&d_table, &tw, &pb, (void*)&d_den, &trace_log, &eval_log, &q[0], &q[1], &q[2], &q[3], &accumulate, &tiles};
+        const uint32_t jgrid = std::min<uint32_t>(tiles, (uint32_t)sms * 8);
+        ProfScope prof(ctx, "air_jit");
+        ZKB_CUDA(ctx, cudaLaunchKernel((const void*)prog->jit_kernel, dim3(jgrid), dim3(256), args, table_words * 4, ctx->stream));
+        return ZKB_OK;
+    }
     ProfScope prof(ctx, "air_eval_kernel");
     auto kernel = prog->rows_per_thread == 4 ? air_eval_kernel<4> : prog->rows_per_thread == 2 ? air_eval_kernel<2> : air_eval_kernel<1>;
     kernel<<<grid, T, prog->smem_bytes, ctx->stream>>>(reinterpret_cast<const uint4*>(prog->d_code), d_table, (uint32_t)table_words,
