@@ -73,7 +73,6 @@ struct zkb_air_program {
     std::vector<uint32_t> tree_base;  // first flat column of each tree
     uint32_t n_cols = 0;
     size_t n_scalars = 0;
-    bool has_offsets = false;
     // ---- shared-memory layout, in words: [uniform values | coefficients | column pointers | registers]
     uint32_t coef_base = 0;   // 4 words per constraint
     uint32_t ptr_base = 0;    // 2 words per column, 8-byte aligned

@@ -39,6 +39,16 @@ __device__ __forceinline__ uint32_t offset_row(uint32_t row, int off, int trace_
     return __brev(moved) >> (32 - eval_log);
 }
 
+// Order in which tiles are taken: consecutive tile numbers (CTAs running at the same time) get row ranges that differ
+// in the top three bits of the row index. A mask at offset +-1 reads row +- N/2, N/4, N/8, ... in bit-reversed order, so
+// with this order the neighbour rows of a tile are rows another CTA is reading as a mask-0 value at about the same
+// time, and most of those reads hit L2 instead of going to DRAM a second time.
+__device__ __forceinline__ uint32_t spread_tile(uint32_t t, uint32_t n_tiles) {
+    if (n_tiles < 16u || (n_tiles & (n_tiles - 1u))) return t;
+    const uint32_t bits = 31u - (uint32_t)__clz(n_tiles);
+    return ((t & 7u) << (bits - 3u)) | (t >> 3);
+}
+
 extern __shared__ __align__(16) uint32_t air_smem[];
 
 // RPT rows per thread: rows tile * T * RPT + j * T + lane, j < RPT. The instruction fetch, its decoding and the loads
@@ -63,7 +73,8 @@ air_eval_kernel(const uint4* __restrict__ code, const uint32_t* __restrict__ tab
         return {{sm[base], sm[base + stride], sm[base + 2 * stride], sm[base + 3 * stride]}};
     };
 
-    for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    for (uint32_t t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+        const uint32_t tile = spread_tile(t, n_tiles);
         uint32_t row[RPT];
         bool active[RPT];
 #pragma unroll

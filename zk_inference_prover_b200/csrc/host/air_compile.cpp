@@ -377,7 +377,6 @@ std::string air_compile(zkb_air_program& P, const zkb_air_op* ops, size_t n_ops,
                 const zkb_air_op& o = P.ops[v];
                 uint32_t col = P.tree_base[o.a] + o.b;
                 int32_t off = (int32_t)o.c;
-                if (off != 0) P.has_offsets = true;
                 col_read[col] = 1;
                 slot[v] = pool.take(1);
                 si.loads.push_back({col | ((uint32_t)off << 20), (uint32_t)slot[v]});

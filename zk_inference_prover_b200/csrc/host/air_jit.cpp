@@ -83,6 +83,12 @@ __device__ __forceinline__ u32 offset_row(u32 row, int trace_log, int eval_log) 
     const u32 moved = (lo & (half - 1u)) | (nat & half);
     return __brev(moved) >> (32 - eval_log);
 }
+// consecutive tile numbers get row ranges that differ in the top three bits of the row index (see csrc/constraints.cu)
+__device__ __forceinline__ u32 spread_tile(u32 t, u32 n_tiles) {
+    if (n_tiles < 16u || (n_tiles & (n_tiles - 1u))) return t;
+    const u32 bits = 31u - (u32)__clz(n_tiles);
+    return ((t & 7u) << (bits - 3u)) | (t >> 3);
+}
 extern __shared__ __align__(16) u32 sm[];
 #define U4(w) (qm31{{sm[(w)], sm[(w) + 1], sm[(w) + 2], sm[(w) + 3]}})
 #define COL(c) (reinterpret_cast<const u32*>(ptrs[(c)]))
@@ -104,9 +110,9 @@ std::string air_codegen(const zkb_air_program& G) {
          "  __syncthreads();\n"
          "  const u64* ptrs = reinterpret_cast<const u64*>(sm + ptr_base);\n"
          "  const u32 n_rows = 1u << eval_log;\n"
-         "  for (u32 tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {\n"
-         "    const u32 row = tile * blockDim.x + threadIdx.x;\n"
-         "    if (row >= n_rows) break;\n"
+         "  for (u32 t = blockIdx.x; t < n_tiles; t += gridDim.x) {\n"
+         "    const u32 row = spread_tile(t, n_tiles) * blockDim.x + threadIdx.x;\n"
+         "    if (row >= n_rows) continue;\n"
          "    u64 a0 = 0, a1 = 0, a2 = 0, a3 = 0;\n";
     auto per_row = [&](uint32_t i) { return G.live[i] && !G.uniform[i] && G.alias[i] == i; };
     auto val = [&](uint32_t v) -> std::string {
