@@ -53,6 +53,28 @@ int zkb_pcs_prove_host(zkb_ctx* ctx, int n_trees, const int* tree_ncols, const u
                        const zkb_pcs_config* config, int two_sample_every, uint32_t* h_out, size_t cap, size_t* n_words,
                        float* h_phase_ms);
 
+/* A whole STARK proof of one component: prove() of nitroo/crates/stwo/src/prover/mod.rs:41-173 with the component's
+ * constraints given as a compiled AIR program (zkb200_air.h). The trees are the fork's: preprocessed, model, base
+ * trace, interaction (a tree may have no columns); every column has 2^trace_log evaluations on the canonic domain,
+ * bit-reversed, and d_cols are consumed. The flow: commit the trees; draw the random coefficient; constraint quotients
+ * on the domain of size 2^(trace_log+1) (zkb_constraint_quotients; the committed evaluations are used as they are when
+ * the blow-up is 2); interpolate, split in halves, commit the composition tree (8 columns); draw the out-of-domain
+ * point; sample every column at its mask points (point + offset * trace step, constraint-framework/src/component.rs:
+ * 356-368) and the composition halves at the point; prove the samples. Output: the proof words as zkb_pcs_prove gives
+ * them (5 trees) followed by the channel digest. oods_evals[0..4) is the composition polynomial at the point from the
+ * committed halves, oods_evals[4..8) the same value from the constraints at the sampled mask values: the reference's
+ * prover refuses (ProvingError::ConstraintsNotSatisfied) when they differ, here the caller compares them.
+ * claimed_sum (4 words or NULL) is the LogUp claimed sum of the component; scalars the program's run-time scalars.
+ * composition_ms (may be NULL) receives the device time from the draw of the random coefficient to the interpolated
+ * composition polynomial. The context's max_log_size must cover trace_log + log_blowup_factor (at least 1). */
+typedef struct zkb_air_program zkb_air_program;
+int zkb_stark_prove_device(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint32_t* const* d_cols, uint32_t trace_log,
+                           zkb_air_program* prog, const uint32_t* scalars, const uint32_t* claimed_sum, const zkb_pcs_config* config,
+                           uint32_t* h_out, size_t cap, size_t* n_words, uint32_t* oods_evals, float* h_phase_ms, float* composition_ms);
+int zkb_stark_prove_host(zkb_ctx* ctx, int n_trees, const int* tree_ncols, const uint32_t* const* h_cols, uint32_t trace_log,
+                         zkb_air_program* prog, const uint32_t* scalars, const uint32_t* claimed_sum, const zkb_pcs_config* config,
+                         uint32_t* h_out, size_t cap, size_t* n_words, uint32_t* oods_evals, float* h_phase_ms, float* composition_ms);
+
 /* GKR batch proof of n_inst instances. kinds: ZKB_GKR_*; d_nums[i] (NULL where the kind has no
  * numerators) and d_dens[i] are device arrays of ns[i] entries laid out as zkb_gkr_next_layer takes
  * them; they are not modified. The channel starts from Blake2sM31Channel::default() after

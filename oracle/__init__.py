@@ -483,3 +483,21 @@ def constraint_quotients_air(air, iparams, qparams, tree_cols, cols, rcp, trace_
                                        _p(cs) if cs is not None else None, _p(rcp), C.c_size_t(rcp.size // 4), C.c_uint32(trace_log),
                                        C.c_uint32(eval_log), acc_ptrs, C.c_int(accum is not None))
     return out
+
+
+def stark_prove(air, iparams, qparams, tree_cols, cols, trace_log, composition_log, claimed_sum=None, pow_bits=10, log_blowup=1,
+                log_last_layer=0, n_queries=3, cap=1 << 24):
+    """prove() for one component (oracle/stark.hpp). cols: the trace on the trace domain, trees concatenated.
+    Returns (proof words incl. the channel digest, committed composition value [4], value from the constraints [4])."""
+    ip, qp, trees = _u32(iparams), _u32(qparams), _u32(tree_cols)
+    keep, ptrs = _col_ptrs(cols)
+    cs = _u32(claimed_sum) if claimed_sum is not None else None
+    out = np.zeros(cap, np.uint32)
+    f = lib().zko_stark_prove
+    f.restype = C.c_long
+    n = f(C.c_int(air), _p(ip), _p(qp), _p(trees), C.c_int(trees.size), ptrs, _p(cs) if cs is not None else None, C.c_uint32(trace_log),
+          C.c_uint32(composition_log), C.c_uint32(pow_bits), C.c_uint32(log_blowup), C.c_uint32(log_last_layer), C.c_uint32(n_queries),
+          _p(out), C.c_size_t(cap))
+    if n < 0:
+        raise RuntimeError("stark_prove: output buffer too small")
+    return out[:n - 8].copy(), out[n - 8:n - 4].copy(), out[n - 4:n].copy()

@@ -56,24 +56,29 @@ inline std::vector<M31> constraint_denom_inv(uint32_t trace_log, uint32_t eval_l
     return d;
 }
 
-struct Fraction {
-    QM31 numerator, denominator;
-    Fraction operator+(const Fraction& r) const {  // fraction.rs:27-33
+using TraceView = std::vector<std::vector<const uint32_t*>>;  // [interaction][column] -> 2^eval_log words
+
+// What lifts a base-field value or a secure-field constant into an evaluator's fields.
+inline QM31 to_ef(M31 x) { return QM31(x); }
+inline QM31 to_ef(QM31 x) { return x; }
+template <class F> inline F from_m31(M31 x);
+template <> inline M31 from_m31<M31>(M31 x) { return x; }
+template <> inline QM31 from_m31<QM31>(M31 x) { return QM31(x); }
+inline M31 square(M31 x) { return x.square(); }
+inline QM31 square(QM31 x) { return x.square(); }
+
+template <class EF> struct FractionT {
+    EF numerator, denominator;
+    FractionT operator+(const FractionT& r) const {  // fraction.rs:27-33
         return {r.denominator * numerator + denominator * r.numerator, denominator * r.denominator};
     }
 };
-inline Fraction fraction_sum(const std::vector<Fraction>& v) {  // fraction.rs:56-59
-    if (v.empty()) return {QM31::zero(), QM31::one()};
-    Fraction acc = v[0];
-    for (size_t i = 1; i < v.size(); i++) acc = acc + v[i];
-    return acc;
-}
 
 // logup.rs:62-104
 struct LookupElements {
     QM31 z;
     std::vector<QM31> alpha_powers;
-    QM31 combine(const std::vector<M31>& values) const {
+    template <class F> QM31 combine(const std::vector<F>& values) const {
         assert(alpha_powers.size() >= values.size());
         QM31 acc = QM31::zero();
         for (size_t i = 0; i < values.size(); i++) acc = acc + alpha_powers[i] * values[i];
@@ -81,54 +86,37 @@ struct LookupElements {
     }
 };
 
-using TraceView = std::vector<std::vector<const uint32_t*>>;  // [interaction][column] -> 2^eval_log words
-
-// cpu_domain.rs:17-98 with the LogUp proxy of lib.rs:214-290
-struct CpuDomainEvaluator {
-    const TraceView& trace_eval;
+// The part of EvalAtRow every evaluator shares (lib.rs:70-199) with the LogUp proxy (lib.rs:214-290). Derived supplies
+//   std::vector<F> mask(interaction, column, offsets), void add_constraint(EF) (and add_constraint(F) where F != EF),
+//   static EF combine_ef(F, F, F, F).
+template <class Derived, class F_, class EF_> struct EvalAtRowBase {
+    using F = F_;
+    using EF = EF_;
     std::vector<size_t> column_index_per_interaction;
-    size_t row;
-    const QM31* random_coeff_powers;
-    QM31 row_res = QM31::zero();
-    size_t constraint_index = 0;
-    uint32_t domain_log_size, eval_domain_log_size;
-    // LogupAtRow (logup.rs:15-41)
     int logup_interaction = INTERACTION_TRACE_IDX;
-    QM31 cumsum_shift;
-    std::vector<Fraction> fracs;
+    QM31 cumsum_shift;  // LogupAtRow::new, logup.rs:33-41
+    std::vector<FractionT<EF>> fracs;
 
-    CpuDomainEvaluator(const TraceView& t, size_t row_, const QM31* rcp, uint32_t domain_log, uint32_t eval_log, uint32_t log_size,
-                       QM31 claimed_sum)
-        : trace_eval(t), column_index_per_interaction(t.size(), 0), row(row_), random_coeff_powers(rcp), domain_log_size(domain_log),
-          eval_domain_log_size(eval_log) {
-        cumsum_shift = claimed_sum * QM31(M31((uint32_t)1 << log_size)).inverse();
-    }
+    EvalAtRowBase(size_t n_interactions, QM31 claimed_sum, uint32_t log_size)
+        : column_index_per_interaction(n_interactions, 0), cumsum_shift(claimed_sum * QM31(M31((uint32_t)1 << log_size)).inverse()) {}
+    Derived& self() { return static_cast<Derived&>(*this); }
 
-    std::vector<M31> next_interaction_mask(int interaction, const std::vector<int>& offsets) {
-        size_t col_index = column_index_per_interaction[interaction]++;
-        const uint32_t* col = trace_eval[interaction][col_index];
-        std::vector<M31> out;
-        for (int off : offsets) {
-            if (off == 0) { out.push_back(M31(col[row])); continue; }
-            size_t r = offset_bit_reversed_circle_domain_index(row, domain_log_size, eval_domain_log_size, off);
-            out.push_back(M31(col[r]));
-        }
-        return out;
+    std::vector<F> next_interaction_mask(int interaction, const std::vector<int>& offsets) {
+        size_t col = column_index_per_interaction[interaction]++;
+        return self().mask(interaction, col, offsets);
     }
-    M31 next_trace_mask() { return next_interaction_mask(ORIGINAL_TRACE_IDX, {0})[0]; }
-    M31 get_preprocessed_column() { return next_interaction_mask(PREPROCESSED_TRACE_IDX, {0})[0]; }
+    F next_trace_mask() { return next_interaction_mask(ORIGINAL_TRACE_IDX, {0})[0]; }
+    F get_preprocessed_column() { return next_interaction_mask(PREPROCESSED_TRACE_IDX, {0})[0]; }
     // lib.rs:127-137: four consecutive columns, combined per offset
-    std::vector<QM31> next_extension_interaction_mask(int interaction, const std::vector<int>& offsets) {
-        std::vector<M31> c[4];
+    std::vector<EF> next_extension_interaction_mask(int interaction, const std::vector<int>& offsets) {
+        std::vector<F> c[4];
         for (int k = 0; k < 4; k++) c[k] = next_interaction_mask(interaction, offsets);
-        std::vector<QM31> out;
-        for (size_t j = 0; j < offsets.size(); j++) out.push_back(QM31::from_m31s(c[0][j], c[1][j], c[2][j], c[3][j]));
+        std::vector<EF> out;
+        for (size_t j = 0; j < offsets.size(); j++) out.push_back(Derived::combine_ef(c[0][j], c[1][j], c[2][j], c[3][j]));
         return out;
     }
-    void add_constraint(QM31 c) { row_res = row_res + random_coeff_powers[constraint_index++] * c; }
-    void add_constraint(M31 c) { row_res = row_res + random_coeff_powers[constraint_index++] * c; }
     // lib.rs:169-180
-    void add_to_relation(const LookupElements& rel, QM31 multiplicity, const std::vector<M31>& values) {
+    void add_to_relation(const LookupElements& rel, EF multiplicity, const std::vector<F>& values) {
         fracs.push_back({multiplicity, rel.combine(values)});
     }
     // lib.rs:226-275
@@ -136,21 +124,26 @@ struct CpuDomainEvaluator {
         assert(batching.size() == fracs.size());
         size_t last_batch = 0;
         for (size_t b : batching) last_batch = b > last_batch ? b : last_batch;
-        std::vector<std::vector<Fraction>> by_batch(last_batch + 1);
+        std::vector<std::vector<FractionT<EF>>> by_batch(last_batch + 1);
         for (size_t i = 0; i < batching.size(); i++) by_batch[batching[i]].push_back(fracs[i]);
-        QM31 prev_col_cumsum = QM31::zero();
+        auto sum = [](const std::vector<FractionT<EF>>& v) {  // fraction.rs:56-59
+            FractionT<EF> acc = v[0];
+            for (size_t i = 1; i < v.size(); i++) acc = acc + v[i];
+            return acc;
+        };
+        EF prev_col_cumsum = QM31::zero();
         for (size_t b = 0; b < last_batch; b++) {
-            Fraction cur = fraction_sum(by_batch[b]);
-            QM31 cur_cumsum = next_extension_interaction_mask(logup_interaction, {0})[0];
-            QM31 diff = cur_cumsum - prev_col_cumsum;
+            FractionT<EF> cur = sum(by_batch[b]);
+            EF cur_cumsum = next_extension_interaction_mask(logup_interaction, {0})[0];
+            EF diff = cur_cumsum - prev_col_cumsum;
             prev_col_cumsum = cur_cumsum;
-            add_constraint(diff * cur.denominator - cur.numerator);
+            self().add_constraint(diff * cur.denominator - cur.numerator);
         }
-        Fraction frac = fraction_sum(by_batch[last_batch]);
-        std::vector<QM31> m = next_extension_interaction_mask(logup_interaction, {-1, 0});
-        QM31 diff = m[1] - m[0] - prev_col_cumsum;
-        QM31 shifted = diff + cumsum_shift;
-        add_constraint(shifted * frac.denominator - frac.numerator);
+        FractionT<EF> frac = sum(by_batch[last_batch]);
+        std::vector<EF> m = next_extension_interaction_mask(logup_interaction, {-1, 0});
+        EF diff = m[1] - m[0] - prev_col_cumsum;
+        EF shifted = diff + cumsum_shift;
+        self().add_constraint(shifted * frac.denominator - frac.numerator);
         fracs.clear();
     }
     void finalize_logup() {
@@ -165,28 +158,97 @@ struct CpuDomainEvaluator {
     }
 };
 
+// cpu_domain.rs:17-98
+struct CpuDomainEvaluator : EvalAtRowBase<CpuDomainEvaluator, M31, QM31> {
+    const TraceView& trace_eval;
+    size_t row;
+    const QM31* random_coeff_powers;
+    QM31 row_res = QM31::zero();
+    size_t constraint_index = 0;
+    uint32_t domain_log_size, eval_domain_log_size;
+
+    CpuDomainEvaluator(const TraceView& t, size_t row_, const QM31* rcp, uint32_t domain_log, uint32_t eval_log, uint32_t log_size,
+                       QM31 claimed_sum)
+        : EvalAtRowBase(t.size(), claimed_sum, log_size), trace_eval(t), row(row_), random_coeff_powers(rcp), domain_log_size(domain_log),
+          eval_domain_log_size(eval_log) {}
+    std::vector<M31> mask(int interaction, size_t col_index, const std::vector<int>& offsets) {
+        const uint32_t* col = trace_eval[interaction][col_index];
+        std::vector<M31> out;
+        for (int off : offsets) {
+            if (off == 0) { out.push_back(M31(col[row])); continue; }
+            size_t r = offset_bit_reversed_circle_domain_index(row, domain_log_size, eval_domain_log_size, off);
+            out.push_back(M31(col[r]));
+        }
+        return out;
+    }
+    void add_constraint(QM31 c) { row_res = row_res + random_coeff_powers[constraint_index++] * c; }
+    void add_constraint(M31 c) { row_res = row_res + random_coeff_powers[constraint_index++] * c; }
+    static QM31 combine_ef(M31 a, M31 b, M31 c, M31 d) { return QM31::from_m31s(a, b, c, d); }
+};
+
+// qm31.rs:51-57
+inline QM31 from_partial_evals(QM31 e0, QM31 e1, QM31 e2, QM31 e3) {
+    return e0 + e1 * QM31::from_u32(0, 1, 0, 0) + e2 * QM31::from_u32(0, 0, 1, 0) + e3 * QM31::from_u32(0, 0, 0, 1);
+}
+
+// point.rs:14-80 with PointEvaluationAccumulator (core/air/accumulation.rs:12-36)
+struct PointEvaluator : EvalAtRowBase<PointEvaluator, QM31, QM31> {
+    const std::vector<std::vector<std::vector<QM31>>>& mask_values;  // [interaction][column][k]
+    QM31 random_coeff, denom_inverse;
+    QM31 accumulation = QM31::zero();
+    size_t n_constraints = 0;
+    PointEvaluator(const std::vector<std::vector<std::vector<QM31>>>& m, QM31 random_coeff_, QM31 denom_inverse_, uint32_t log_size,
+                   QM31 claimed_sum)
+        : EvalAtRowBase(m.size(), claimed_sum, log_size), mask_values(m), random_coeff(random_coeff_), denom_inverse(denom_inverse_) {}
+    std::vector<QM31> mask(int interaction, size_t col_index, const std::vector<int>& offsets) {
+        const std::vector<QM31>& v = mask_values[interaction][col_index];
+        assert(v.size() == offsets.size());
+        return v;
+    }
+    void add_constraint(QM31 c) {
+        accumulation = accumulation * random_coeff + denom_inverse * c;
+        n_constraints++;
+    }
+    static QM31 combine_ef(QM31 a, QM31 b, QM31 c, QM31 d) { return from_partial_evals(a, b, c, d); }
+};
+
+// info.rs: which mask offsets each column is asked for, and how many constraints there are
+struct InfoEvaluator : EvalAtRowBase<InfoEvaluator, QM31, QM31> {
+    std::vector<std::vector<std::vector<int>>> mask_offsets;  // [interaction][column] -> offsets
+    size_t n_constraints = 0;
+    explicit InfoEvaluator(size_t n_interactions) : EvalAtRowBase(n_interactions, QM31::zero(), 1), mask_offsets(n_interactions) {}
+    std::vector<QM31> mask(int interaction, size_t col_index, const std::vector<int>& offsets) {
+        if (mask_offsets[interaction].size() <= col_index) mask_offsets[interaction].resize(col_index + 1);
+        mask_offsets[interaction][col_index] = offsets;
+        return std::vector<QM31>(offsets.size(), QM31::one());
+    }
+    void add_constraint(QM31) { n_constraints++; }
+    static QM31 combine_ef(QM31 a, QM31, QM31, QM31) { return a; }
+};
+
 // ---------------------------------------------------------------------------------------------- AIRs, written as in the reference
 
 // nitroo/crates/examples/src/wide_fibonacci/mod.rs:47-57
-inline void wide_fibonacci_evaluate(CpuDomainEvaluator& eval, size_t n_cols) {
-    M31 a = eval.next_trace_mask(), b = eval.next_trace_mask();
+template <class E> inline void wide_fibonacci_evaluate(E& eval, size_t n_cols) {
+    auto a = eval.next_trace_mask(), b = eval.next_trace_mask();
     for (size_t k = 2; k < n_cols; k++) {
-        M31 c = eval.next_trace_mask();
-        eval.add_constraint(c - (a.square() + b.square()));
+        auto c = eval.next_trace_mask();
+        eval.add_constraint(c - (square(a) + square(b)));
         a = b;
         b = c;
     }
 }
 
 // nitroo/crates/examples/src/plonk/mod.rs:51-88
-inline void plonk_evaluate(CpuDomainEvaluator& eval, const LookupElements& lookup) {
-    M31 a_wire = eval.get_preprocessed_column(), b_wire = eval.get_preprocessed_column();
-    M31 c_wire = eval.get_preprocessed_column(), op = eval.get_preprocessed_column();
-    M31 mult = eval.next_trace_mask(), a_val = eval.next_trace_mask(), b_val = eval.next_trace_mask(), c_val = eval.next_trace_mask();
-    eval.add_constraint(c_val - op * (a_val + b_val) + (M31(1) - op) * a_val * b_val);
+template <class E> inline void plonk_evaluate(E& eval, const LookupElements& lookup) {
+    using F = typename E::F;
+    F a_wire = eval.get_preprocessed_column(), b_wire = eval.get_preprocessed_column();
+    F c_wire = eval.get_preprocessed_column(), op = eval.get_preprocessed_column();
+    F mult = eval.next_trace_mask(), a_val = eval.next_trace_mask(), b_val = eval.next_trace_mask(), c_val = eval.next_trace_mask();
+    eval.add_constraint(c_val - op * (a_val + b_val) + (from_m31<F>(M31(1)) - op) * a_val * b_val);
     eval.add_to_relation(lookup, QM31::one(), {a_wire, a_val});
     eval.add_to_relation(lookup, QM31::one(), {b_wire, b_val});
-    eval.add_to_relation(lookup, QM31(-mult), {c_wire, c_val});
+    eval.add_to_relation(lookup, to_ef(-mult), {c_wire, c_val});
     eval.finalize_logup_in_pairs();
 }
 
@@ -203,13 +265,14 @@ struct FreivaldsEval {
     bool range_check;
 };
 // prover/src/gadgets/freivalds/mod.rs:114-186
-inline void freivalds_evaluate(CpuDomainEvaluator& eval, const FreivaldsEval& e) {
-    M31 nofirst = eval.get_preprocessed_column(), last = eval.get_preprocessed_column();
-    M31 notzero = eval.get_preprocessed_column(), end = eval.get_preprocessed_column();
-    std::vector<std::vector<M31>> ws(e.n_mats);
+template <class E> inline void freivalds_evaluate(E& eval, const FreivaldsEval& e) {
+    using F = typename E::F;
+    F nofirst = eval.get_preprocessed_column(), last = eval.get_preprocessed_column();
+    F notzero = eval.get_preprocessed_column(), end = eval.get_preprocessed_column();
+    std::vector<std::vector<F>> ws(e.n_mats);
     for (size_t m = 0; m < e.n_mats; m++)
         for (size_t p = 0; p < e.pk; p++) ws[m].push_back(eval.get_preprocessed_column());
-    std::vector<M31> acts;
+    std::vector<F> acts;
     for (size_t p = 0; p < e.pq; p++) acts.push_back(eval.next_trace_mask());
     std::vector<QM31> vv = eval.next_extension_interaction_mask(INTERACTION_TRACE_IDX, {-1, 0});
     QM31 v_prev = vv[0], v = vv[1];
@@ -230,10 +293,23 @@ inline void freivalds_evaluate(CpuDomainEvaluator& eval, const FreivaldsEval& e)
         eval.add_constraint((aa[1] - e.claimed[m]) * end);
     }
     if (e.range_check) {
-        for (M31 a : acts) eval.add_to_relation(e.rel_act, QM31::one(), {a});
+        for (F a : acts) eval.add_to_relation(e.rel_act, QM31::one(), {a});
         eval.finalize_logup_in_pairs();
     }
 }
+
+// The three AIRs above behind one description (what the C entry points take).
+struct AirSpec {
+    int air = 0;  // 0 wide Fibonacci, 1 Plonk, 2 Freivalds
+    size_t n_cols = 0;
+    LookupElements plonk_rel;
+    FreivaldsEval fe{};
+    template <class E> void evaluate(E& eval) const {
+        if (air == 0) wide_fibonacci_evaluate(eval, n_cols);
+        else if (air == 1) plonk_evaluate(eval, plonk_rel);
+        else freivalds_evaluate(eval, fe);
+    }
+};
 
 // component_prover.rs:603-633 around a row evaluator
 template <class RowFn>

@@ -460,21 +460,18 @@ void zko_constraint_quotients_ssa(const uint32_t* ops, size_t n_ops, const uint3
     }, eval_log, trace_log, accum, accumulate != 0);
 }
 
-// The AIRs written against CpuDomainEvaluator. air: 0 wide Fibonacci (ip = {n_cols}), 1 Plonk (qp = {z, alpha^0, alpha^1}),
+// The AIRs written against the evaluators. air: 0 wide Fibonacci (ip = {n_cols}), 1 Plonk (qp = {z, alpha^0, alpha^1}),
 // 2 Freivalds (ip = {pk, pq, n_mats, act_off, range_check}; qp = {rv_pow[pk], rv_step, s_pow[pq], s_step, claimed[n_mats], z, alpha^0}).
-void zko_constraint_quotients_air(int air, const uint32_t* ip, const uint32_t* qp, const uint32_t* tree_cols, int n_trees,
-                                  const uint32_t* const* cols, const uint32_t* claimed_sum, const uint32_t* rcp, size_t n_constraints,
-                                  uint32_t trace_log, uint32_t eval_log, uint32_t* const accum[4], int accumulate) {
-    TraceView t = trace_view(tree_cols, n_trees, cols);
-    std::vector<QM31> coef(n_constraints);
-    for (size_t i = 0; i < n_constraints; i++) coef[i] = q_from(rcp + 4 * i);
-    QM31 claimed = claimed_sum ? q_from(claimed_sum) : QM31::zero();
-    LookupElements plonk_rel;
-    FreivaldsEval fe{};
-    if (air == 1) {
-        plonk_rel.z = q_from(qp);
-        plonk_rel.alpha_powers = {q_from(qp + 4), q_from(qp + 8)};
-    } else if (air == 2) {
+static AirSpec make_air_spec(int air, const uint32_t* ip, const uint32_t* qp) {
+    AirSpec a;
+    a.air = air;
+    if (air == 0) {
+        a.n_cols = ip[0];
+    } else if (air == 1) {
+        a.plonk_rel.z = q_from(qp);
+        a.plonk_rel.alpha_powers = {q_from(qp + 4), q_from(qp + 8)};
+    } else {
+        FreivaldsEval& fe = a.fe;
         fe.pk = ip[0]; fe.pq = ip[1]; fe.n_mats = ip[2]; fe.act_off = ip[3]; fe.range_check = ip[4] != 0;
         const uint32_t* q = qp;
         for (size_t p = 0; p < fe.pk; p++, q += 4) fe.rv_pow.push_back(q_from(q));
@@ -485,14 +482,61 @@ void zko_constraint_quotients_air(int air, const uint32_t* ip, const uint32_t* q
         fe.rel_act.z = q_from(q); q += 4;
         fe.rel_act.alpha_powers = {q_from(q)};
     }
+    return a;
+}
+
+void zko_constraint_quotients_air(int air, const uint32_t* ip, const uint32_t* qp, const uint32_t* tree_cols, int n_trees,
+                                  const uint32_t* const* cols, const uint32_t* claimed_sum, const uint32_t* rcp, size_t n_constraints,
+                                  uint32_t trace_log, uint32_t eval_log, uint32_t* const accum[4], int accumulate) {
+    TraceView t = trace_view(tree_cols, n_trees, cols);
+    std::vector<QM31> coef(n_constraints);
+    for (size_t i = 0; i < n_constraints; i++) coef[i] = q_from(rcp + 4 * i);
+    QM31 claimed = claimed_sum ? q_from(claimed_sum) : QM31::zero();
+    AirSpec spec = make_air_spec(air, ip, qp);
     accumulate_pointwise_cpu([&](size_t row) {
         CpuDomainEvaluator eval(t, row, coef.data(), trace_log, eval_log, trace_log, claimed);
-        if (air == 0) wide_fibonacci_evaluate(eval, ip[0]);
-        else if (air == 1) plonk_evaluate(eval, plonk_rel);
-        else freivalds_evaluate(eval, fe);
+        spec.evaluate(eval);
         assert(eval.constraint_index == n_constraints);
         return eval.row_res;
     }, eval_log, trace_log, accum, accumulate != 0);
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------- a whole STARK proof of one component
+#include "stark.hpp"
+extern "C" {
+
+// prove() of nitroo/crates/stwo/src/prover/mod.rs:41-173 for one component whose AIR is one of the three above.
+// cols: the trace on the trace domain (2^trace_log words per column), trees concatenated. Output: the PCS proof words,
+// the channel digest (8 words), the composition polynomial's out-of-domain value from the committed halves (4 words) and
+// from the constraints at the sampled mask values (4 words). Returns the word count or -1.
+long zko_stark_prove(int air, const uint32_t* ip, const uint32_t* qp, const uint32_t* tree_cols, int n_trees, const uint32_t* const* cols,
+                     const uint32_t* claimed_sum, uint32_t trace_log, uint32_t composition_log, uint32_t pow_bits, uint32_t log_blowup,
+                     uint32_t log_last_layer, uint32_t n_queries, uint32_t* out, size_t cap) {
+    PcsConfig cfg;
+    cfg.pow_bits = pow_bits;
+    cfg.fri = {log_blowup, log_last_layer, n_queries, 1};
+    AirSpec spec = make_air_spec(air, ip, qp);
+    std::vector<std::vector<std::vector<M31>>> trees(n_trees);
+    size_t at = 0;
+    for (int t = 0; t < n_trees; t++)
+        for (uint32_t c = 0; c < tree_cols[t]; c++, at++) {
+            std::vector<M31> v((size_t)1 << trace_log);
+            for (size_t i = 0; i < v.size(); i++) v[i] = M31(cols[at][i]);
+            trees[t].push_back(std::move(v));
+        }
+    StarkResult r = stark_prove(spec, trees, claimed_sum ? q_from(claimed_sum) : QM31::zero(), trace_log, composition_log, cfg);
+    std::vector<uint32_t> w = r.proof.to_words();
+    for (int i = 0; i < 8; i++) w.push_back(load_le32(&r.digest[4 * i]));
+    uint32_t q[4];
+    r.committed_eval.to_u32(q);
+    w.insert(w.end(), q, q + 4);
+    r.point_eval.to_u32(q);
+    w.insert(w.end(), q, q + 4);
+    if (w.size() > cap) return -1;
+    memcpy(out, w.data(), w.size() * 4);
+    return (long)w.size();
 }
 
 }  // extern "C"

@@ -229,3 +229,83 @@ def test_freivalds_witness_satisfies_its_air(ctx, oracle):
         coeffs = np.stack([x.download() for x in acc])
         assert coeffs[:, :rows].any()
         assert coeffs[:, 2 * rows + 1:].any() == corrupt
+
+
+# ---------------------------------------------------------------------------------------------- whole proofs of one component
+
+def _wide_fibonacci_trace(n_cols, trace_log, seed=1):
+    n = 1 << trace_log
+    a, b = m31_column(seed, n).astype(np.uint64), m31_column(seed + 1, n).astype(np.uint64)
+    trace = [a, b]
+    for _ in range(2, n_cols):
+        a, b = b, (a * a % P + b * b % P) % P
+        trace.append(b)
+    return [c.astype(np.uint32) for c in trace]
+
+
+@pytest.mark.parametrize("n_cols,trace_log,log_blowup,specialize", [(10, 6, 1, False), (10, 6, 2, True), (40, 10, 1, True), (24, 12, 2, False)])
+def test_stark_proof_of_wide_fibonacci_matches_oracle(ctx, oracle, n_cols, trace_log, log_blowup, specialize):
+    """prove() end to end: every word of the proof (5 trees: the composition tree among them), the channel state after it, and
+    the prover's sanity check equal the oracle's; a corrupted trace fails the check on both sides with the same values."""
+    from zk_inference_prover_b200 import air
+
+    trace = _wide_fibonacci_trace(n_cols, trace_log)
+    prog = ctx.air_compile(air.wide_fibonacci(air.ExprEvaluator(), n_cols).source())
+    if specialize:
+        prog.specialize()
+    kw = dict(pow_bits=5, log_blowup=log_blowup, n_queries=7)
+    for corrupt in (False, True):
+        if corrupt:
+            trace[3] = trace[3].copy()
+            trace[3][5] ^= 1
+        want, w_committed, w_point = oracle.stark_prove(0, [n_cols], np.zeros(4, np.uint32), [0, 0, n_cols, 0], trace, trace_log, trace_log + 1, **kw)
+        bufs = [ctx.upload(c) for c in trace]
+        got, committed, at_point, _ = ctx.stark_prove(prog, [[], [], [b.ptr for b in bufs], []], trace_log, **kw)
+        assert (committed == w_committed).all() and (at_point == w_point).all()
+        assert (committed == at_point).all() != corrupt
+        assert len(got) == len(want) and (got == want).all()
+        got_h, c_h, p_h, _ = ctx.stark_prove(prog, [[], [], trace, []], trace_log, host=True, **kw)
+        assert (got_h == want).all() and (c_h == w_committed).all() and (p_h == w_point).all()
+
+
+def test_stark_proof_of_the_freivalds_component_matches_oracle(ctx, oracle):
+    """The Freivalds component proved end to end from the witness the device kernels make: preprocessed selectors and
+    weights, activations, and the Horner / accumulator columns as the interaction tree, masks at offsets -1 and 0."""
+    from test_freivalds import _case, layout
+    from zk_inference_prover_b200 import air
+
+    tokens, n_in, n_outs, chunks = 9, 8, [8, 6], 4
+    qx, qws = _case(41, tokens, n_in, n_outs)
+    grid, pq, pk = layout(n_in, max(n_outs), tokens, chunks)
+    trace_log, n_mats = grid[0], len(qws)
+    base, pre, _, _ = oracle.freivalds_columns(qx, qws, grid, pq, pk)
+    fp = air_cases.freivalds_params(oracle, pk, pq, n_mats, 4100)
+    inter, claims = oracle.freivalds_acc(base, pre, n_mats, grid, pq, pk, fp["s"], fp["rv"])
+    trees = [list(pre[n_mats * pk:]) + list(pre[:n_mats * pk]), [], list(base), list(inter)]
+    rel = qm31_array(5, 2)
+    qp = np.concatenate([fp["rv_pow"], fp["rv_step"][None], fp["s_pow"], fp["s_step"][None], claims, rel]).astype(np.uint32)
+    src = air.freivalds(air.ExprEvaluator(), pk, pq, n_mats, fp["rv_pow"], fp["rv_step"], fp["s_pow"], fp["s_step"], claims, 128, None).source()
+    assert [len(t) for t in trees] == list(src.tree_cols)
+    prog = ctx.air_compile(src).specialize()
+    kw = dict(pow_bits=3, log_blowup=2, n_queries=5)
+    flat = [c for t in trees for c in t]
+    want, w_committed, w_point = oracle.stark_prove(2, [pk, pq, n_mats, 128, 0], qp, list(src.tree_cols), flat, trace_log, trace_log + 1, **kw)
+    assert (w_committed == w_point).all()
+    bufs = [[ctx.upload(c) for c in t] for t in trees]
+    got, committed, at_point, _ = ctx.stark_prove(prog, [[b.ptr for b in t] for t in bufs], trace_log, **kw)
+    assert (committed == w_committed).all() and (at_point == w_point).all()
+    assert len(got) == len(want) and (got == want).all()
+
+
+def test_full_size_stark_proof_passes_its_own_check(ctx):
+    """256 columns x 2^20 rows, blow-up 4 (the benchmark's trace shape) proved as a wide Fibonacci component: the composition
+    polynomial's out-of-domain value from the committed halves equals the value from the constraints at the sampled masks."""
+    from zk_inference_prover_b200 import air
+
+    n_cols, trace_log = 256, 20
+    trace = _wide_fibonacci_trace(n_cols, trace_log)
+    prog = ctx.air_compile(air.wide_fibonacci(air.ExprEvaluator(), n_cols).source()).specialize()
+    bufs = [ctx.upload(c) for c in trace]
+    _, committed, at_point, _ = ctx.stark_prove(prog, [[], [], [b.ptr for b in bufs], []], trace_log, pow_bits=10, log_blowup=2, n_queries=3,
+                                                cap=1 << 26)
+    assert (committed == at_point).all() and committed.any()

@@ -22,7 +22,7 @@ EXPORTED_SYMBOLS = [
     "zkb_freivalds_scatter", "zkb_freivalds_acc",
 ]
 # Every symbol include/zkb200_prover.h declares.
-PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_gkr_prove_device"]
+PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_stark_prove_device", "zkb_stark_prove_host", "zkb_gkr_prove_device"]
 # Every symbol include/zkb200_air.h declares.
 AIR_SYMBOLS = ["zkb_air_compile", "zkb_air_free", "zkb_air_specialize", "zkb_air_select", "zkb_air_get_stats", "zkb_constraint_quotients", "zkb_constraint_denom_inv"]
 PCS_PHASES = ["interpolate", "extend", "merkle", "sample", "quotients", "fri_commit", "grind", "decommit"]
@@ -493,6 +493,35 @@ class Context:
         logs = [len(c).bit_length() - 1 for t in arrs for c in t]
         return self._pcs(self.lib.zkb_pcs_prove_host, ptrs, logs, pow_bits, log_blowup, log_last_layer, n_queries,
                          two_sample_every, cap, phases)
+
+    def stark_prove(self, prog, trees, trace_log, claimed_sum=None, scalars=None, pow_bits=10, log_blowup=1, log_last_layer=0, n_queries=3,
+                    cap=1 << 24, phases=None, host=False):
+        """zkb_stark_prove_device / _host: trees is a list (one entry per tree) of lists of device pointers (or of host arrays
+        when host=True). Returns (proof words incl. channel digest, committed composition value [4], value from the constraints
+        [4], composition_ms)."""
+        ncols = np.array([len(t) for t in trees], dtype=np.int32)
+        cfg = PcsConfig(pow_bits, log_blowup, log_last_layer, n_queries)
+        sc = _u32(prog.source.scalars if scalars is None else scalars)
+        cs = _u32(claimed_sum) if claimed_sum is not None else None
+        out = np.empty(cap, np.uint32)
+        n = C.c_size_t()
+        oods = np.zeros(8, np.uint32)
+        ph = (C.c_float * len(PCS_PHASES))()
+        comp_ms = C.c_float()
+        if host:
+            keep = [_u32(c) for t in trees for c in t]
+            ptrs = (C.c_void_p * len(keep))(*[k.ctypes.data for k in keep])
+            fn = self.lib.zkb_stark_prove_host
+        else:
+            ptrs = _ptr_array([p for t in trees for p in t])
+            fn = self.lib.zkb_stark_prove_device
+        self._check(fn(self.h, C.c_int(len(trees)), ncols.ctypes.data_as(C.c_void_p), ptrs, C.c_uint32(trace_log), prog.h,
+                       sc.ctypes.data_as(C.c_void_p), cs.ctypes.data_as(C.c_void_p) if cs is not None else None, C.byref(cfg),
+                       out.ctypes.data_as(C.c_void_p), C.c_size_t(cap), C.byref(n), oods.ctypes.data_as(C.c_void_p), ph, C.byref(comp_ms)))
+        if phases is not None:
+            phases.update({k: float(ph[i]) for i, k in enumerate(PCS_PHASES)})
+            phases["composition"] = float(comp_ms.value)
+        return out[:n.value].copy(), oods[:4].copy(), oods[4:].copy(), float(comp_ms.value)
 
     def gkr_prove_device(self, instances, seed, cap=1 << 22):
         """instances: list of (kind, num_ptr or 0, den_ptr, n_entries)."""

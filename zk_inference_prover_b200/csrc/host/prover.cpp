@@ -10,6 +10,7 @@
 #include <set>
 
 #include "../../../include/zkb200_prover.h"
+#include "../air_program.hpp"
 #include "b200_backend.hpp"
 #include "../gkr_resident.hpp"
 #include "channel.hpp"
@@ -462,7 +463,7 @@ struct CommitmentSchemeProver {
     // arrived from the host; columns are then interpolated and extended fence by fence, while later
     // columns are still in flight.
     void commit_evals(std::vector<BaseColumn> columns, Channel& ch, const std::vector<int>* fence_of = nullptr,
-                      BaseColumn* slab = nullptr) {
+                      BaseColumn* slab = nullptr, bool are_coeffs = false) {
         CommitmentTreeProver t;
         if (slab) t.coeff_slab = std::move(*slab);
         std::map<uint32_t, std::vector<size_t>> by_log;
@@ -470,7 +471,7 @@ struct CommitmentSchemeProver {
         t.evals.resize(columns.size());
         HashColumn leaves;
         bool have_leaves = false;
-        if (fence_of) {
+        if (fence_of && !columns.empty()) {
             mark(0);
             // One column size: the leaf layer is hashed run by run (whole Blake2s blocks of 16 columns) as the
             // extended columns appear, instead of after the last one.
@@ -504,6 +505,7 @@ struct CommitmentSchemeProver {
             if (incremental) { hash_ready(true); have_leaves = true; }
         } else {
             for (auto& g : by_log) {
+                if (are_coeffs) break;  // TreeBuilder::extend_polys (pcs/mod.rs:437-452): the columns are coefficients already
                 std::vector<BaseColumn*> cols;
                 for (auto i : g.second) cols.push_back(&columns[i]);
                 B200Backend::interpolate_columns(d, cols);
@@ -909,22 +911,10 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
 
 using namespace b200;
 
-static int pcs_prove_impl(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint32_t* const* d_cols, const uint32_t* const* h_cols,
-                          const uint32_t* col_logs, const zkb_pcs_config* cfg, int two_sample_every, uint32_t* h_out, size_t cap,
-                          size_t* n_words, float* h_phase_ms) {
-    if (!ctx) return ZKB_EINVAL;
-    if (!tree_ncols || !col_logs || !cfg || !h_out || !n_words || n_trees <= 0 || (!d_cols && !h_cols)) return ZKB_EINVAL;
-    try {
-        Device dev(ctx);
-        PcsConfig config{cfg->pow_bits, {cfg->log_blowup_factor, cfg->log_last_layer_degree_bound, cfg->n_queries, 1}};
-        int total = 0;
-        uint32_t max_log = 0;
-        for (int t = 0; t < n_trees; t++) total += tree_ncols[t];
-        for (int i = 0; i < total; i++) max_log = std::max(max_log, col_logs[i]);
-        if ((int)(max_log + config.fri.log_blowup_factor) > zkb_max_log_size(ctx)) return ZKB_EINVAL;
-        Channel ch;
-        config.mix_into(ch);
-        CommitmentSchemeProver prover(dev, config, h_phase_ms);
+// Commits the caller's trees in order (TreeBuilder::extend_evals + commit per tree), from device columns or from host
+// columns with the upload overlapped.
+static void commit_input_trees(Device& dev, zkb_ctx* ctx, CommitmentSchemeProver& prover, Channel& ch, int n_trees, const int* tree_ncols,
+                               uint32_t* const* d_cols, const uint32_t* const* h_cols, const uint32_t* col_logs, int total) {
         int flat = 0;
         if (d_cols) {
             for (int t = 0; t < n_trees; t++) {
@@ -948,7 +938,8 @@ static int pcs_prove_impl(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint
             for (int t = 0; t < n_trees; t++) {
                 size_t words = 0;
                 for (int c = 0; c < tree_ncols[t]; c++) words += std::max<size_t>((size_t)1 << col_logs[flat + c], 64);
-                slabs.emplace_back(dev, words);
+                if (words) slabs.emplace_back(dev, words);
+                else slabs.emplace_back();  // a tree without columns (it is still committed: its root is the hash of nothing)
                 size_t off = 0;
                 for (int c = 0; c < tree_ncols[t]; c++, flat++) {
                     size_t n = (size_t)1 << col_logs[flat];
@@ -991,6 +982,26 @@ static int pcs_prove_impl(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint
                 throw;
             }
         }
+}
+
+static int pcs_prove_impl(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint32_t* const* d_cols, const uint32_t* const* h_cols,
+                          const uint32_t* col_logs, const zkb_pcs_config* cfg, int two_sample_every, uint32_t* h_out, size_t cap,
+                          size_t* n_words, float* h_phase_ms) {
+    if (!ctx) return ZKB_EINVAL;
+    if (!tree_ncols || !col_logs || !cfg || !h_out || !n_words || n_trees <= 0 || (!d_cols && !h_cols)) return ZKB_EINVAL;
+    try {
+        Device dev(ctx);
+        PcsConfig config{cfg->pow_bits, {cfg->log_blowup_factor, cfg->log_last_layer_degree_bound, cfg->n_queries, 1}};
+        int total = 0;
+        uint32_t max_log = 0;
+        for (int t = 0; t < n_trees; t++) total += tree_ncols[t];
+        for (int i = 0; i < total; i++) max_log = std::max(max_log, col_logs[i]);
+        if ((int)(max_log + config.fri.log_blowup_factor) > zkb_max_log_size(ctx)) return ZKB_EINVAL;
+        Channel ch;
+        config.mix_into(ch);
+        CommitmentSchemeProver prover(dev, config, h_phase_ms);
+        commit_input_trees(dev, ctx, prover, ch, n_trees, tree_ncols, d_cols, h_cols, col_logs, total);
+        int flat = 0;
         CirclePointQ oods = get_random_point(ch);
         std::vector<std::vector<std::vector<CirclePointQ>>> points(n_trees);
         flat = 0;
@@ -1020,12 +1031,185 @@ static int pcs_prove_impl(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint
     }
 }
 
+// prove() for one component (STWO/prover/mod.rs:41-173): commit the trees, draw the random coefficient, evaluate the
+// constraint quotients on the evaluation domain of twice the trace size (zkb_constraint_quotients), interpolate and
+// split the composition polynomial, commit its eight coordinate halves, sample every column at its mask points around
+// a drawn out-of-domain point, and prove the samples. The prover's own sanity check - the composition polynomial's value
+// at the point, once from the committed halves (core/proof.rs:27-57) and once from the constraints at the sampled mask
+// values (constraint-framework/src/component.rs:374-413, point.rs) - is returned in oods_evals for the caller to compare.
+static int stark_prove_impl(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint32_t* const* d_cols, const uint32_t* const* h_cols,
+                            uint32_t trace_log, zkb_air_program* prog, const uint32_t* scalars, const uint32_t* claimed_sum,
+                            const zkb_pcs_config* cfg, uint32_t* h_out, size_t cap, size_t* n_words, uint32_t* oods_evals,
+                            float* h_phase_ms, float* composition_ms) {
+    if (!ctx) return ZKB_EINVAL;
+    if (!tree_ncols || !cfg || !h_out || !n_words || !prog || !oods_evals || n_trees <= 0 || (!d_cols && !h_cols)) return ZKB_EINVAL;
+    if (prog->n_scalars && !scalars) return ZKB_EINVAL;
+    try {
+        Device dev(ctx);
+        PcsConfig config{cfg->pow_bits, {cfg->log_blowup_factor, cfg->log_last_layer_degree_bound, cfg->n_queries, 1}};
+        const uint32_t blowup = config.fri.log_blowup_factor, comp_log = trace_log + 1;
+        if (trace_log < 1 || blowup < 1 || (int)(trace_log + blowup) > zkb_max_log_size(ctx)) return ZKB_EINVAL;
+        int total = 0;
+        for (int t = 0; t < n_trees; t++) total += tree_ncols[t];
+        if ((uint32_t)total != prog->n_cols || (size_t)n_trees != prog->tree_base.size())
+            return zk_set_error_public(ctx, ZKB_EINVAL, "zkb_stark_prove: the trees do not have the columns the program was compiled for");
+        std::vector<uint32_t> col_logs((size_t)total, trace_log);
+        Channel ch;
+        config.mix_into(ch);
+        CommitmentSchemeProver prover(dev, config, h_phase_ms);
+        commit_input_trees(dev, ctx, prover, ch, n_trees, tree_ncols, d_cols, h_cols, col_logs.data(), total);
+
+        // ---- composition polynomial
+        const size_t n_constraints = prog->constraints.size();
+        const qm31 random_coeff = ch.draw_secure_felt();
+        dev.check(zkb_event_record(ctx, 28));
+        std::vector<qm31> powers(n_constraints);  // the first constraint takes the highest power (component_prover.rs:271)
+        {
+            qm31 pw = qm31_one();
+            for (size_t k = 0; k < n_constraints; k++) { powers[n_constraints - 1 - k] = pw; pw = pw * random_coeff; }
+        }
+        // columns on the evaluation domain: the committed evaluations themselves when the blow-up is 2, else an extension
+        std::vector<BaseColumn> extended;
+        std::vector<const uint32_t*> col_ptrs;
+        for (auto& t : prover.trees) {
+            if (blowup == 1) {
+                for (auto& e : t.evals) col_ptrs.push_back(e.ptr());
+            } else {
+                std::vector<const BaseColumn*> cc;
+                for (auto& c : t.coeffs) cc.push_back(&c);
+                auto ev = B200Backend::evaluate_polynomials(dev, cc, 1);
+                for (auto& e : ev) { col_ptrs.push_back(e.ptr()); extended.push_back(std::move(e)); }
+            }
+        }
+        qm31 shift = qm31_zero(), claimed = qm31_zero();
+        if (claimed_sum) {
+            for (int k = 0; k < 4; k++) claimed.c[k] = claimed_sum[k];
+            shift = claimed * qm31_inv(qm31_from_m31(1u << trace_log));  // LogupAtRow::new, logup.rs:33-41
+        }
+        std::vector<uint32_t> denom_inv(2);
+        if (zkb_constraint_denom_inv((int)trace_log, (int)comp_log, denom_inv.data()) != ZKB_OK) return ZKB_EINVAL;
+        const size_t N = (size_t)1 << comp_log;
+        BaseColumn acc[4] = {BaseColumn(dev, N), BaseColumn(dev, N), BaseColumn(dev, N), BaseColumn(dev, N)};
+        uint32_t* accp[4] = {acc[0].ptr(), acc[1].ptr(), acc[2].ptr(), acc[3].ptr()};
+        dev.check(zkb_constraint_quotients(ctx, prog, col_ptrs.data(), scalars, shift.c, reinterpret_cast<const uint32_t*>(powers.data()),
+                                           denom_inv.data(), (int)trace_log, (int)comp_log, accp, 0));
+        extended.clear();
+        // DomainEvaluationAccumulator::finalize (air/accumulation.rs:89-124), split_at_mid, extend_polys + commit
+        {
+            std::vector<BaseColumn*> ap = {&acc[0], &acc[1], &acc[2], &acc[3]};
+            B200Backend::interpolate_columns(dev, ap);
+            std::vector<BaseColumn> halves;
+            for (int k = 0; k < 4; k++) halves.push_back(BaseColumn::view(dev, acc[k].ptr(), N / 2));
+            for (int k = 0; k < 4; k++) halves.push_back(BaseColumn::view(dev, acc[k].ptr() + N / 2, N / 2));
+            dev.check(zkb_event_record(ctx, 29));
+            prover.commit_evals(std::move(halves), ch, nullptr, nullptr, true);
+        }
+
+        // ---- mask points (component.rs:356-368) and the samples' proof
+        CirclePointQ oods = get_random_point(ch);
+        const uint32_t lifting_log = prover.trees.back().max_log();
+        const uint32_t max_log_degree_bound = lifting_log - blowup;
+        std::vector<std::vector<int32_t>> offsets((size_t)total);
+        for (const zkb_air_op& o : prog->ops)
+            if (o.op == ZKB_AIR_LOAD) {
+                auto& v = offsets[prog->tree_base[o.a] + o.b];
+                if (std::find(v.begin(), v.end(), (int32_t)o.c) == v.end()) v.push_back((int32_t)o.c);
+            }
+        std::vector<std::vector<std::vector<CirclePointQ>>> points((size_t)n_trees + 1);
+        int flat = 0;
+        for (int t = 0; t < n_trees; t++)
+            for (int c = 0; c < tree_ncols[t]; c++, flat++) {
+                std::vector<CirclePointQ> pts;
+                for (int32_t off : offsets[flat]) {
+                    // trace_step.mul_signed(off): the point of index off * 2^(31 - max_log_degree_bound) in the circle group
+                    cpoint st = host_circle_point(((uint32_t)off << (31 - max_log_degree_bound)) & 0x7fffffffu);
+                    pts.push_back(point_add(oods, {qm31_from_m31(st.x), qm31_from_m31(st.y)}));
+                }
+                points[t].push_back(pts);
+            }
+        points.back().assign(8, {oods});
+        PcsProof proof = prover.prove_values(points, ch);
+        prover.finish_timing();
+        if (composition_ms) dev.check(zkb_event_elapsed_ms(ctx, 28, 29, composition_ms));
+
+        // ---- the sanity check of prove_ex
+        auto from_partial_evals = [](qm31 e0, qm31 e1, qm31 e2, qm31 e3) {  // qm31.rs:51-57
+            const qm31 i{{0, 1, 0, 0}}, u{{0, 0, 1, 0}}, iu{{0, 0, 0, 1}};
+            return e0 + e1 * i + e2 * u + e3 * iu;
+        };
+        const auto& comp = proof.sampled_values.back();
+        const qm31 left = from_partial_evals(comp[0][0], comp[1][0], comp[2][0], comp[3][0]);
+        const qm31 right = from_partial_evals(comp[4][0], comp[5][0], comp[6][0], comp[7][0]);
+        const qm31 committed = left + point_repeated_double(oods, max_log_degree_bound - 1).x * right;
+        // coset_vanishing(CanonicCoset(max_log_degree_bound).coset, oods): the shift -initial + step/2 is zero for a canonic coset
+        qm31 vanish = oods.x;
+        for (uint32_t k = 1; k < max_log_degree_bound; k++) vanish = qm31_double_x(vanish);
+        const qm31 denom_inverse = qm31_inv(vanish);
+        // the program at the point: every value is a secure-field element, a LOAD is the sampled mask value
+        std::vector<qm31> v(prog->ops.size(), qm31_zero());
+        flat = 0;
+        std::vector<std::pair<int, int>> where((size_t)total);
+        for (int t = 0; t < n_trees; t++)
+            for (int c = 0; c < tree_ncols[t]; c++, flat++) where[flat] = {t, c};
+        for (size_t i = 0; i < prog->ops.size(); i++) {
+            const zkb_air_op& o = prog->ops[i];
+            switch (o.op) {
+                case ZKB_AIR_LOAD: {
+                    const uint32_t col = prog->tree_base[o.a] + o.b;
+                    const auto& offs = offsets[col];
+                    const size_t k = std::find(offs.begin(), offs.end(), (int32_t)o.c) - offs.begin();
+                    v[i] = proof.sampled_values[where[col].first][where[col].second][k];
+                    break;
+                }
+                case ZKB_AIR_CONST_M31: v[i] = qm31_from_m31(o.a); break;
+                case ZKB_AIR_SCALAR: for (int k = 0; k < 4; k++) v[i].c[k] = scalars[4 * (size_t)o.a + k]; break;
+                case ZKB_AIR_CUMSUM_SHIFT: v[i] = shift; break;
+                case ZKB_AIR_ADD_B: case ZKB_AIR_ADD_E: v[i] = v[o.a] + v[o.b]; break;
+                case ZKB_AIR_SUB_B: case ZKB_AIR_SUB_E: v[i] = v[o.a] - v[o.b]; break;
+                case ZKB_AIR_MUL_B: case ZKB_AIR_MUL_E: v[i] = v[o.a] * v[o.b]; break;
+                case ZKB_AIR_NEG_B: case ZKB_AIR_NEG_E: v[i] = qm31_neg(v[o.a]); break;
+                case ZKB_AIR_INV_B: v[i] = qm31_is_zero(v[o.a]) ? qm31_zero() : qm31_inv(v[o.a]); break;
+                case ZKB_AIR_PACK: v[i] = from_partial_evals(v[o.a], v[o.b], v[o.c], v[o.d]); break;
+                default: break;
+            }
+        }
+        qm31 at_point = qm31_zero();  // PointEvaluationAccumulator (core/air/accumulation.rs:12-36)
+        for (size_t k = 0; k < n_constraints; k++) at_point = at_point * random_coeff + denom_inverse * v[prog->constraints[k]];
+        for (int k = 0; k < 4; k++) { oods_evals[k] = committed.c[k]; oods_evals[4 + k] = at_point.c[k]; }
+
+        std::vector<uint32_t> w = proof.to_words();
+        w.insert(w.end(), ch.digest().begin(), ch.digest().end());
+        *n_words = w.size();
+        if (w.size() > cap) return zk_set_error_public(ctx, ZKB_EINVAL, "zkb_stark_prove: output buffer too small");
+        memcpy(h_out, w.data(), w.size() * 4);
+        return ZKB_OK;
+    } catch (const Error& e) {
+        return zk_set_error_public(ctx, e.code, e.what());
+    } catch (const std::exception& e) {
+        return zk_set_error_public(ctx, ZKB_ENOMEM, e.what());
+    }
+}
+
 extern "C" {
 
 int zkb_pcs_prove_device(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint32_t* const* d_cols, const uint32_t* col_logs,
                          const zkb_pcs_config* config, int two_sample_every, uint32_t* h_out, size_t cap, size_t* n_words,
                          float* h_phase_ms) {
     return pcs_prove_impl(ctx, n_trees, tree_ncols, d_cols, nullptr, col_logs, config, two_sample_every, h_out, cap, n_words, h_phase_ms);
+}
+
+int zkb_stark_prove_device(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint32_t* const* d_cols, uint32_t trace_log,
+                           zkb_air_program* prog, const uint32_t* scalars, const uint32_t* claimed_sum, const zkb_pcs_config* config,
+                           uint32_t* h_out, size_t cap, size_t* n_words, uint32_t* oods_evals, float* h_phase_ms, float* composition_ms) {
+    return stark_prove_impl(ctx, n_trees, tree_ncols, d_cols, nullptr, trace_log, prog, scalars, claimed_sum, config, h_out, cap, n_words,
+                            oods_evals, h_phase_ms, composition_ms);
+}
+
+int zkb_stark_prove_host(zkb_ctx* ctx, int n_trees, const int* tree_ncols, const uint32_t* const* h_cols, uint32_t trace_log,
+                         zkb_air_program* prog, const uint32_t* scalars, const uint32_t* claimed_sum, const zkb_pcs_config* config,
+                         uint32_t* h_out, size_t cap, size_t* n_words, uint32_t* oods_evals, float* h_phase_ms, float* composition_ms) {
+    return stark_prove_impl(ctx, n_trees, tree_ncols, nullptr, h_cols, trace_log, prog, scalars, claimed_sum, config, h_out, cap, n_words,
+                            oods_evals, h_phase_ms, composition_ms);
 }
 
 int zkb_pcs_prove_host(zkb_ctx* ctx, int n_trees, const int* tree_ncols, const uint32_t* const* h_cols, const uint32_t* col_logs,
