@@ -716,6 +716,95 @@ def run_constraints(args, rank):
     ctx.close()
 
 
+def run_stark(args, rank):
+    """--mode stark: a whole STARK proof of one component - prove() of the reference's generic prover - for the wide
+    Fibonacci AIR over --cols columns of 2^--log-size rows: trace commitment, composition polynomial (constraint quotients
+    with the program's specialised kernel), composition commitment, mask-point sampling, quotients, FRI, grind, decommit."""
+    if rank != 0:
+        return
+    import air_cases
+    import oracle
+    import zk_inference_prover_b200 as z
+    from zk_inference_prover_b200 import air
+
+    n_cols, trace_log = args.cols, args.log_size
+    kw = dict(pow_bits=args.pow_bits, log_blowup=args.log_blowup, n_queries=args.n_queries, cap=1 << 26)
+    ctx = z.Context(device=0, max_log_size=trace_log + args.log_blowup)
+    trace = air_cases.wide_fibonacci_trace(n_cols, trace_log)
+    prog = ctx.air_compile(air.wide_fibonacci(air.ExprEvaluator(), n_cols).source())
+    t0 = time.perf_counter()
+    prog.specialize()
+    jit_s = time.perf_counter() - t0
+    n = 1 << trace_log
+    src = [ctx.upload(c) for c in trace]
+    work = [ctx.alloc(n) for _ in range(n_cols)]
+    h_arr, pinned = ctx.alloc_pinned(n_cols * n)
+    host = h_arr.reshape(n_cols, n)
+    for c in range(n_cols):
+        host[c] = trace[c]
+    host_cols = [host[c] for c in range(n_cols)]
+    phases = {}
+
+    def step(e2e):
+        if e2e:
+            ctx.event_record(0)
+            out = ctx.stark_prove(prog, [[], [], host_cols, []], trace_log, host=True, phases=phases, **kw)
+        else:
+            for w_, s_ in zip(work, src):
+                ctx.d2d(w_.ptr, s_.ptr, n * 4)
+            ctx.event_record(0)
+            out = ctx.stark_prove(prog, [[], [], [w_.ptr for w_ in work], []], trace_log, phases=phases, **kw)
+        ctx.event_record(1)
+        ctx.sync()
+        return out, ctx.event_elapsed_ms(0, 1)
+
+    def timed(e2e):
+        for _ in range(args.warmup):
+            out, _ = step(e2e)
+        ms = []
+        for _ in range(args.steps):
+            out, t = step(e2e)
+            ms.append(t)
+        return out, float(np.mean(ms))
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    out_dev, dev_ms = timed(False)
+    clocks = sampler.stop()
+    dev_phases = dict(phases)
+    out_e2e, e2e_ms = timed(True)
+    for out in (out_dev, out_e2e):
+        assert (out[1] == out[2]).all(), "the proof fails the prover's own out-of-domain check"
+    name = f"stark_wide_fibonacci_{n_cols}x2e{trace_log}_blowup{1 << args.log_blowup}"
+    parity = golden_check(name, air_cases.stark_words(out_dev[0], out_dev[1], out_dev[2]))
+    golden_check(name, air_cases.stark_words(out_e2e[0], out_e2e[1], out_e2e[2]))
+    cells = n_cols * n
+    cpu = None
+    if not args.no_cpu_baseline:
+        oracle.set_num_threads(len(os.sched_getaffinity(0)))
+        sc, sl = min(n_cols, 32), min(trace_log, 16)
+        tr = air_cases.wide_fibonacci_trace(sc, sl)
+        t0 = time.perf_counter()
+        oracle.stark_prove(0, [sc], np.zeros(4, np.uint32), [0, 0, sc, 0], tr, sl, sl + 1, pow_bits=args.pow_bits, log_blowup=args.log_blowup,
+                           n_queries=args.n_queries)
+        dt = time.perf_counter() - t0
+        cpu = {"value": sc * (1 << sl) / dt, "unit": "cells/s", "cores": oracle.num_threads(), "kind": "port",
+               "sample": f"the same proof of {sc} columns x 2^{sl} rows ({dt:.1f} s), the oracle's restatement of prove()"}
+    line = {"metric": "committed_m31_cells_per_s", "value": cells / (dev_ms * 1e-3), "unit": "cells/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dev_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32 (M31)",
+            "data": "synthetic (a valid wide Fibonacci trace)",
+            "config": {"workload": f"stark_prove_wide_fibonacci_{n_cols}cols_log{trace_log}_blowup{1 << args.log_blowup}",
+                       "step": "trace commit + composition polynomial + composition commit + mask-point samples + quotients + FRI + grind + decommit",
+                       "pow_bits": args.pow_bits, "n_queries": args.n_queries, "l2": "inputs (1 GiB) are larger than L2"},
+            "e2e": {"value": cells / (e2e_ms * 1e-3), "unit": "cells/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": cells * 4,
+                    "d2h_bytes_per_step": int(out_e2e[0].size * 4)},
+            "per_phase_ms": dev_phases, "specialize_s": jit_s, "clocks": clocks, "parity": parity, "proof_words": int(out_dev[0].size),
+            "cpu_baseline": cpu}
+    print(json.dumps(line))
+    ctx.free_pinned(pinned)
+    ctx.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -731,7 +820,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gpu-baseline", action="store_true")
     ap.add_argument("--gkr-log", type=int, default=24)
-    ap.add_argument("--mode", default="proof", choices=["proof", "sharded-commit", "gkr", "freivalds", "constraints"],
+    ap.add_argument("--mode", default="proof", choices=["proof", "sharded-commit", "gkr", "freivalds", "constraints", "stark"],
                     help="proof: one whole PCS proof per rank (ranks are independent); sharded-commit: one commitment over all ranks")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -747,6 +836,8 @@ def main():
         run_freivalds(args, rank)
     elif args.mode == "constraints":
         run_constraints(args, rank)
+    elif args.mode == "stark":
+        run_stark(args, rank)
     else:
         run_ours(args, rank, world, local_rank)
 

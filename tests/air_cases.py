@@ -159,3 +159,19 @@ def random_program(seed, n_ops, tree_cols, n_scalars, n_constraints, max_offset=
     cons[-1] = 3         # a bare column
     scalars = qm31_array(seed + 11, n_scalars)
     return air.AirSource(np.array(ops, np.uint32).reshape(-1, 5), cons.astype(np.uint32), np.array(tree_cols, np.uint32), scalars)
+
+
+def wide_fibonacci_trace(n_cols, trace_log, seed=1):
+    """A trace that satisfies the wide Fibonacci AIR: every row its own sequence from two seeded values."""
+    n = 1 << trace_log
+    a, b = m31_column(seed, n).astype(np.uint64), m31_column(seed + 1, n).astype(np.uint64)
+    trace = [a, b]
+    for _ in range(2, n_cols):
+        a, b = b, (a * a % P + b * b % P) % P
+        trace.append(b)
+    return [c.astype(np.uint32) for c in trace]
+
+
+def stark_words(words, committed, at_point):
+    """The proof words followed by the two out-of-domain values: what the golden digests of whole proofs cover."""
+    return np.concatenate([words, committed, at_point]).astype(np.uint32)

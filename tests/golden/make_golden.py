@@ -62,6 +62,26 @@ AIR_SMALL = {f"air_small_{i}": i for i in range(8)}
 AIR_FULL = {"air_wide_fibonacci_256x2e20": "wide_fibonacci", "air_freivalds_pk16_pq1_2mats_2e20": "freivalds"}
 
 
+# whole STARK proofs of a wide Fibonacci component (oracle/stark.hpp): name -> (columns, trace log, prover parameters)
+STARK_SMALL = {
+    "stark_wide_fibonacci_10x2e6": (10, 6, dict(pow_bits=5, log_blowup=1, n_queries=7)),
+    "stark_wide_fibonacci_24x2e10_blowup4": (24, 10, dict(pow_bits=10, log_blowup=2, n_queries=3)),
+}
+STARK_FULL = {
+    "stark_wide_fibonacci_256x2e20_blowup4": (256, 20, dict(pow_bits=10, log_blowup=2, n_queries=3, cap=1 << 26)),
+}
+
+
+def stark_oracle(name):
+    import air_cases
+
+    n_cols, trace_log, kw = dict(STARK_SMALL, **STARK_FULL)[name]
+    trace = air_cases.wide_fibonacci_trace(n_cols, trace_log)
+    w, committed, at_point = oracle.stark_prove(0, [n_cols], np.zeros(4, np.uint32), [0, 0, n_cols, 0], trace, trace_log, trace_log + 1, **kw)
+    assert (committed == at_point).all()
+    return air_cases.stark_words(w, committed, at_point)
+
+
 def air_case(name):
     import air_cases
 
@@ -93,21 +113,34 @@ def digest(words):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--full", action="store_true")
+    ap.add_argument("--only", default="", help="regenerate only the cases whose name starts with this")
     args = ap.parse_args()
     out = json.load(open(OUT)) if os.path.exists(OUT) else {}
     pcs = dict(PCS_SMALL, **(PCS_FULL if args.full else {}))
     gkr = dict(GKR_SMALL, **(GKR_FULL if args.full else {}))
+    want = lambda name: name.startswith(args.only)
     for name, (shape, seed, kw) in pcs.items():
+        if not want(name):
+            continue
         out[name] = digest(oracle.pcs_prove(pcs_trees(shape, seed), **kw))
         print(name, out[name], flush=True)
     for name, (specs, seed) in gkr.items():
+        if not want(name):
+            continue
         cap = 1 << 22
         out[name] = digest(oracle.gkr_prove([gkr_instance(*s) for s in specs], seed, verify=max(s[1] for s in specs) <= 16, cap=cap))
         print(name, out[name], flush=True)
     import air_cases
 
     for name in list(AIR_SMALL) + (list(AIR_FULL) if args.full else []):
+        if not want(name):
+            continue
         out[name] = digest(air_cases.by_air(oracle, air_case(name)))
+        print(name, out[name], flush=True)
+    for name in list(STARK_SMALL) + (list(STARK_FULL) if args.full else []):
+        if not want(name):
+            continue
+        out[name] = digest(stark_oracle(name))
         print(name, out[name], flush=True)
     json.dump(out, open(OUT, "w"), indent=1, sort_keys=True)
 

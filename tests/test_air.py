@@ -93,3 +93,41 @@ def test_random_programs_interpret(oracle):
     cols = [m31_column(50 + c, 1 << 6) for c in range(12)]
     out = oracle.constraint_quotients_ssa(src, cols, qm31_array(4, 9), 4, 6, cumsum_shift=[1, 2, 3, 4])
     assert out.any()
+
+
+def test_whole_proof_passes_the_provers_own_check(oracle):
+    """prove() end to end in the oracle (oracle/stark.hpp): for a valid trace the composition polynomial's out-of-domain
+    value from the committed halves equals the value from the constraints at the sampled mask values
+    (nitroo/crates/stwo/src/prover/mod.rs:141-166); one corrupted cell breaks the equality."""
+    n_cols, trace_log = 12, 6
+    trace = air_cases.wide_fibonacci_trace(n_cols, trace_log)
+    args = (0, [n_cols], np.zeros(4, np.uint32), [0, 0, n_cols, 0])
+    for log_blowup in (1, 2):
+        w, committed, at_point = oracle.stark_prove(*args, trace, trace_log, trace_log + 1, log_blowup=log_blowup, pow_bits=4, n_queries=5)
+        assert (committed == at_point).all() and committed.any() and len(w) > 500
+    bad = [c.copy() for c in trace]
+    bad[7][9] ^= 1
+    _, committed, at_point = oracle.stark_prove(*args, bad, trace_log, trace_log + 1, pow_bits=4, n_queries=5)
+    assert not (committed == at_point).all()
+
+
+def test_whole_proof_of_the_freivalds_component(oracle):
+    """The Freivalds witness (masks at offsets -1 and 0 in the interaction tree, four preprocessed selectors) passes the check."""
+    from test_freivalds import _case, layout
+
+    tokens, n_in, n_outs, chunks = 5, 6, [7, 5], 4
+    qx, qws = _case(31, tokens, n_in, n_outs)
+    grid, pq, pk = layout(n_in, max(n_outs), tokens, chunks)
+    trace_log, n_mats = grid[0], len(qws)
+    base, pre, _, _ = oracle.freivalds_columns(qx, qws, grid, pq, pk)
+    fp = air_cases.freivalds_params(oracle, pk, pq, n_mats, 3100)
+    inter, claims = oracle.freivalds_acc(base, pre, n_mats, grid, pq, pk, fp["s"], fp["rv"])
+    cols = list(pre[n_mats * pk:]) + list(pre[:n_mats * pk]) + list(base) + list(inter)
+    qp = np.concatenate([fp["rv_pow"], fp["rv_step"][None], fp["s_pow"], fp["s_step"][None], claims, qm31_array(5, 2)]).astype(np.uint32)
+    tree_cols = [4 + n_mats * pk, 0, pq, 4 * (1 + 2 * n_mats)]
+    _, committed, at_point = oracle.stark_prove(2, [pk, pq, n_mats, 128, 0], qp, tree_cols, cols, trace_log, trace_log + 1, log_blowup=2)
+    assert (committed == at_point).all()
+    cols[-3] = cols[-3].copy()
+    cols[-3][3] ^= 1
+    _, committed, at_point = oracle.stark_prove(2, [pk, pq, n_mats, 128, 0], qp, tree_cols, cols, trace_log, trace_log + 1, log_blowup=2)
+    assert not (committed == at_point).all()

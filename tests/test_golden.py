@@ -44,8 +44,28 @@ def test_oracle_reproduces_air_digest(oracle, name):
     _check(name, air_cases.by_ssa(oracle, case))
 
 
+@pytest.mark.parametrize("name", sorted(mg.STARK_SMALL))
+def test_oracle_reproduces_stark_digest(oracle, name):
+    _check(name, mg.stark_oracle(name))
+
+
 def test_every_golden_has_a_recipe():
-    assert set(GOLDEN) == set(mg.PCS_SMALL) | set(mg.PCS_FULL) | set(mg.GKR_SMALL) | set(mg.GKR_FULL) | set(mg.AIR_SMALL) | set(mg.AIR_FULL)
+    assert set(GOLDEN) == (set(mg.PCS_SMALL) | set(mg.PCS_FULL) | set(mg.GKR_SMALL) | set(mg.GKR_FULL) | set(mg.AIR_SMALL) | set(mg.AIR_FULL)
+                           | set(mg.STARK_SMALL) | set(mg.STARK_FULL))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", sorted(mg.STARK_SMALL) + sorted(mg.STARK_FULL))
+def test_cuda_reproduces_stark_digest(ctx, name):
+    import air_cases
+    from zk_inference_prover_b200 import air
+
+    n_cols, trace_log, kw = dict(mg.STARK_SMALL, **mg.STARK_FULL)[name]
+    trace = air_cases.wide_fibonacci_trace(n_cols, trace_log)
+    prog = ctx.air_compile(air.wide_fibonacci(air.ExprEvaluator(), n_cols).source()).specialize()
+    w, committed, at_point, _ = ctx.stark_prove(prog, [[], [], trace, []], trace_log, host=True, **kw)
+    assert (committed == at_point).all()
+    _check(name, air_cases.stark_words(w, committed, at_point))
 
 
 @pytest.mark.gpu

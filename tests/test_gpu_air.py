@@ -187,8 +187,8 @@ def test_freivalds_witness_satisfies_its_air(ctx, oracle):
     """The columns zkb_freivalds_scatter / zkb_freivalds_acc produce, extended to the evaluation domain, satisfy the
     component's constraints (prover/src/gadgets/freivalds/mod.rs:114-163): the quotient is a polynomial. This ties the
     witness kernels, the mask offsets (rows j-1 in coset order) and the constraint evaluator together. The constraint
-    acc - acc_prev * notzero - (u * v) * last has degree 3, so the evaluation domain is four times the trace and the
-    quotient's coefficients vanish above twice the trace size."""
+    acc - acc_prev * notzero - (u * v) * last has degree 3, so its quotient has up to twice the trace size of
+    coefficients; on an evaluation domain of four times the trace the upper half must vanish."""
     from test_freivalds import _case, layout
     from zk_inference_prover_b200 import air
 
@@ -233,14 +233,7 @@ def test_freivalds_witness_satisfies_its_air(ctx, oracle):
 
 # ---------------------------------------------------------------------------------------------- whole proofs of one component
 
-def _wide_fibonacci_trace(n_cols, trace_log, seed=1):
-    n = 1 << trace_log
-    a, b = m31_column(seed, n).astype(np.uint64), m31_column(seed + 1, n).astype(np.uint64)
-    trace = [a, b]
-    for _ in range(2, n_cols):
-        a, b = b, (a * a % P + b * b % P) % P
-        trace.append(b)
-    return [c.astype(np.uint32) for c in trace]
+_wide_fibonacci_trace = air_cases.wide_fibonacci_trace
 
 
 @pytest.mark.parametrize("n_cols,trace_log,log_blowup,specialize", [(10, 6, 1, False), (10, 6, 2, True), (40, 10, 1, True), (24, 12, 2, False)])

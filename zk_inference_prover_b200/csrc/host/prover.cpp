@@ -1102,6 +1102,7 @@ static int stark_prove_impl(zkb_ctx* ctx, int n_trees, const int* tree_ncols, ui
             for (int k = 0; k < 4; k++) halves.push_back(BaseColumn::view(dev, acc[k].ptr(), N / 2));
             for (int k = 0; k < 4; k++) halves.push_back(BaseColumn::view(dev, acc[k].ptr() + N / 2, N / 2));
             dev.check(zkb_event_record(ctx, 29));
+            prover.mark(-1);  // the composition is timed on its own, not as part of the next tree's first phase
             prover.commit_evals(std::move(halves), ch, nullptr, nullptr, true);
         }
 
