@@ -7,7 +7,9 @@ Pinning: the restatement is checked against the reference's own known-answer vec
 and, operator by operator on a GPU, against the reference's own CUDA backend compiled out of tree
 (oracle/Makefile.ref_cuda, oracle/ref_cuda.py, tests/test_gpu_reference_cuda.py). The protocol layer above the
 operators has no reference output to compare with here (the reference's provers are Rust): parity of that layer
-is unpinned.
+is unpinned, except where the protocol checks itself - a whole proof of a component (stark.hpp) must pass the
+prover's own out-of-domain check, which ties the constraint evaluation, the composition polynomial, the mask points
+and the sampled values together.
 """
 import ctypes as C
 import os
