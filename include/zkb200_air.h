@@ -86,10 +86,17 @@ int zkb_air_free(zkb_air_program* prog);
  * This is the run-time counterpart of the reference's per-shape generated kernels (prover/src/cudagen.rs:1985-2290).
  * On success zkb_constraint_quotients uses the specialised kernel; zkb_air_select switches between it (1) and the
  * interpreter (0), whose results are identical. ZKB_ECUDA with a message if NVRTC is absent or the compilation fails:
- * the program stays usable through the interpreter. Takes about a second per thousand instructions. */
+ * the program stays usable through the interpreter. Takes about a second per thousand instructions. The environment
+ * variable ZKB_NVRTC_LIB, read at the first use, names the NVRTC library to load instead of libnvrtc.so.12. */
 int zkb_air_specialize(zkb_ctx* ctx, zkb_air_program* prog);
 int zkb_air_select(zkb_air_program* prog, int specialized);
 int zkb_air_get_stats(const zkb_air_program* prog, zkb_air_stats* out);
+
+/* Host only, no context and no GPU: runs the compiler on a program and reports what it made of it (or why it refused
+ * it, in err). With check_specialized non-zero it also generates the specialised kernel's source and compiles it for
+ * sm_100a with NVRTC (which needs no device), filling specialized and specialized_regs; ZKB_ECUDA if that fails. */
+int zkb_air_analyze(const zkb_air_op* ops, size_t n_ops, const uint32_t* constraints, size_t n_constraints, const uint32_t* tree_cols,
+                    int n_trees, size_t n_scalars, int check_specialized, zkb_air_stats* out, char* err, size_t err_cap);
 
 /* FrameworkComponent::evaluate_constraint_quotients_on_domain for one component.
  *   cols                 host array of device pointers: the component's columns on the evaluation domain, tree 0's

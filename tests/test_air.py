@@ -131,3 +131,69 @@ def test_whole_proof_of_the_freivalds_component(oracle):
     cols[-3][3] ^= 1
     _, committed, at_point = oracle.stark_prove(2, [pk, pq, n_mats, 128, 0], qp, tree_cols, cols, trace_log, trace_log + 1, log_blowup=2)
     assert not (committed == at_point).all()
+
+
+# ---------------------------------------------------------------------------------------------- the product's compiler, on the host
+
+def test_compiler_report_for_the_reference_airs(oracle, zkb):
+    """zkb_air_analyze (host only): what the lowering to bytecode makes of the three AIRs."""
+    from zk_inference_prover_b200 import air
+
+    wf = zkb.air_analyze(air.wide_fibonacci(air.ExprEvaluator(), 100).source())
+    assert wf["n_loads"] == 100 and wf["n_columns_read"] == 100 and wf["n_uniform"] == 0
+    assert wf["m31_mults"] == 98 * 6          # two squares and a coefficient of four words per constraint
+    assert wf["reg_words"] <= 16 and wf["rows_per_thread"] == 4 and wf["threads"] == 256
+    assert wf["n_instr"] < wf["n_live_ops"]   # multiplications folded, constraints accumulated where they are computed
+    case = air_cases.freivalds_case(oracle, 16, 1, 2, 5, 6, 1)
+    fr = zkb.air_analyze(case["source"])
+    assert fr["n_columns_read"] == int(sum(case["tree_cols"])) and fr["n_loads"] > fr["n_columns_read"]   # masks at -1 and 0
+    assert fr["n_uniform"] > 0 and fr["smem_bytes"] <= 227 * 1024
+    pl = zkb.air_analyze(air_cases.plonk_case(oracle, 5, 6, 2)["source"])
+    assert pl["n_columns_read"] == 16 and pl["n_loads"] == 20
+
+
+def test_compiler_rejects_bad_programs_on_the_host(zkb):
+    from zk_inference_prover_b200 import air
+
+    def src(ops, cons=(0,), trees=(1, 0, 1, 0), n_scalars=1):
+        return air.AirSource(np.array(ops, np.uint32).reshape(-1, 5), np.array(cons, np.uint32), np.array(trees, np.uint32),
+                             np.zeros((n_scalars, 4), np.uint32))
+
+    good = [(air.LOAD, 2, 0, 0, 0), (air.SCALAR, 0, 0, 0, 0), (air.MUL_E, 0, 1, 0, 0)]
+    assert zkb.air_analyze(src(good, cons=(2,)))["n_instr"] >= 2
+    for bad, cons, needle in [
+        ([(air.LOAD, 2, 1, 0, 0)], (0,), "outside the trees"),
+        ([(air.LOAD, 2, 0, 0, 0), (air.ADD_B, 0, 1, 0, 0)], (1,), "not an earlier instruction"),
+        (good + [(air.ADD_B, 0, 2, 0, 0)], (3,), "secure-field operand"),
+        ([(air.CONST_M31, P, 0, 0, 0)], (0,), "canonical"),
+        ([(air.SCALAR, 1, 0, 0, 0)], (0,), "scalar slot"),
+        ([(air.LOAD, 2, 0, 5000, 0)], (0,), "offset"),
+        ([(99, 0, 0, 0, 0)], (0,), "opcode"),
+        (good, (7,), "constraint 0"),
+    ]:
+        with pytest.raises(zkb.ZkbError) as e:
+            zkb.air_analyze(src(bad, cons=cons))
+        assert e.value.code == -1 and needle in str(e.value), (bad, str(e.value))
+    ev = air.ExprEvaluator()
+    vals = [ev.scalar([1, 2, 3, 4]) * ev.next_trace_mask() for _ in range(2000)]
+    acc = vals[0]
+    for v in vals[1:]:
+        acc = acc + v
+    for v in vals:
+        acc = acc * v
+    ev.add_constraint(acc)
+    with pytest.raises(zkb.ZkbError) as e:
+        zkb.air_analyze(ev.source())
+    assert "shared memory" in str(e.value)
+
+
+def test_specialised_kernel_source_compiles_without_a_gpu(oracle, zkb):
+    """The code generator's output goes through NVRTC for sm_100a on the host (no device is needed to compile)."""
+    case = air_cases.freivalds_case(oracle, 8, 3, 2, 5, 6, 1)
+    try:
+        st = zkb.air_analyze(case["source"], check_specialized=True)
+    except zkb.ZkbError as e:
+        if "could not be loaded" in str(e):
+            pytest.skip("NVRTC is not installed here")
+        raise
+    assert st["specialized"] == 1 and 16 <= st["specialized_regs"] <= 255

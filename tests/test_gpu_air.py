@@ -302,3 +302,35 @@ def test_full_size_stark_proof_passes_its_own_check(ctx):
     _, committed, at_point, _ = ctx.stark_prove(prog, [[], [], [b.ptr for b in bufs], []], trace_log, pow_bits=10, log_blowup=2, n_queries=3,
                                                 cap=1 << 26)
     assert (committed == at_point).all() and committed.any()
+
+
+def test_without_nvrtc_the_interpreter_still_serves(oracle):
+    """When NVRTC cannot be loaded, zkb_air_specialize reports it and the program keeps working through the interpreter.
+    (NVRTC is looked up once per process, so this runs in a child process with ZKB_NVRTC_LIB pointing nowhere.)"""
+    import os
+    import subprocess
+    import sys
+
+    code = r'''
+import sys, numpy as np
+sys.path.insert(0, "tests"); sys.path.insert(0, ".")
+import oracle, air_cases
+import zk_inference_prover_b200 as z
+ctx = z.Context(device=0, max_log_size=10)
+case = air_cases.wide_fibonacci_case(oracle, 8, 5, 6, 100)
+prog = ctx.air_compile(case["source"])
+try:
+    prog.specialize()
+    print("UNEXPECTED: specialised")
+except z.ZkbError as e:
+    assert "NVRTC" in str(e), str(e)
+bufs = [ctx.upload(c) for c in case["cols"]]
+acc = [ctx.alloc(64) for _ in range(4)]
+ctx.constraint_quotients(prog, [b.ptr for b in bufs], case["rcp"], 5, 6, [a.ptr for a in acc], accumulate=False)
+assert (np.stack([a.download() for a in acc]) == air_cases.by_air(oracle, case)).all()
+print("OK")
+'''
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, ZKB_NVRTC_LIB="/nonexistent/libnvrtc.so")
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.strip().endswith("OK"), r.stdout + r.stderr

@@ -19,6 +19,7 @@ from .capi import (  # noqa: F401
     PROVER_SYMBOLS,
     AIR_SYMBOLS,
     AirProgram,
+    air_analyze,
     constraint_denom_inv,
     PCS_PHASES,
 )

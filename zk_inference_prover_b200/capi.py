@@ -24,7 +24,7 @@ EXPORTED_SYMBOLS = [
 # Every symbol include/zkb200_prover.h declares.
 PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_stark_prove_device", "zkb_stark_prove_host", "zkb_gkr_prove_device"]
 # Every symbol include/zkb200_air.h declares.
-AIR_SYMBOLS = ["zkb_air_compile", "zkb_air_free", "zkb_air_specialize", "zkb_air_select", "zkb_air_get_stats", "zkb_constraint_quotients", "zkb_constraint_denom_inv"]
+AIR_SYMBOLS = ["zkb_air_compile", "zkb_air_analyze", "zkb_air_free", "zkb_air_specialize", "zkb_air_select", "zkb_air_get_stats", "zkb_constraint_quotients", "zkb_constraint_denom_inv"]
 PCS_PHASES = ["interpolate", "extend", "merkle", "sample", "quotients", "fri_commit", "grind", "decommit"]
 
 
@@ -142,6 +142,20 @@ def constraint_denom_inv(trace_log, eval_log):
     if rc != 0:
         raise ZkbError(rc, "zkb_constraint_denom_inv: invalid sizes")
     return out
+
+
+def air_analyze(source, check_specialized=False):
+    """zkb_air_analyze: the compiler's report on a program (host only, no GPU). Raises ZkbError with its reason if refused."""
+    ops, cons, trees = _u32(source.ops), _u32(source.constraints), _u32(source.tree_cols)
+    st = AirStats()
+    err = C.create_string_buffer(1024)
+    rc = load_library().zkb_air_analyze(ops.ctypes.data_as(C.c_void_p), C.c_size_t(ops.shape[0]), cons.ctypes.data_as(C.c_void_p),
+                                        C.c_size_t(cons.size), trees.ctypes.data_as(C.c_void_p), C.c_int(trees.size),
+                                        C.c_size_t(source.scalars.shape[0]), C.c_int(int(check_specialized)), C.byref(st), err,
+                                        C.c_size_t(1024))
+    if rc != 0:
+        raise ZkbError(rc, err.value.decode())
+    return {n: getattr(st, n) for n, _ in AirStats._fields_}
 
 
 class AirProgram:

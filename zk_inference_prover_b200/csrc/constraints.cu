@@ -13,6 +13,7 @@
 // are issued in batches of up to 8 independent loads; for a mask offset the 256 rows of a tile map to another run of
 // consecutive rows except where the offset carries into the tile's own bits, so those reads coalesce as well.
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <new>
 #include <string>
@@ -329,6 +330,32 @@ int zkb_air_specialize(zkb_ctx* ctx, zkb_air_program* prog) {
     const size_t at = info.find("Used ");
     if (at != std::string::npos) prog->stats.specialized_regs = (uint32_t)atoi(info.c_str() + at + 5);
     return ZKB_OK;
+}
+
+int zkb_air_analyze(const zkb_air_op* ops, size_t n_ops, const uint32_t* constraints, size_t n_constraints, const uint32_t* tree_cols,
+                    int n_trees, size_t n_scalars, int check_specialized, zkb_air_stats* out, char* err, size_t err_cap) {
+    auto say = [&](const std::string& m) { if (err && err_cap) snprintf(err, err_cap, "%s", m.c_str()); };
+    say("");
+    if (!ops || !constraints || !out || n_trees < 0 || n_trees > 64 || (n_trees && !tree_cols)) { say("invalid argument"); return ZKB_EINVAL; }
+    try {
+        zkb_air_program prog;
+        std::string why = air_compile(prog, ops, n_ops, constraints, n_constraints, tree_cols, n_trees, n_scalars);
+        if (!why.empty()) { say(why); return ZKB_EINVAL; }
+        if (check_specialized) {
+            std::vector<char> cubin;
+            std::string info;
+            why = air_nvrtc_compile(air_codegen(prog), cubin, &info);
+            if (!why.empty()) { say(why); return ZKB_ECUDA; }
+            prog.stats.specialized = 1;
+            const size_t at = info.find("Used ");
+            if (at != std::string::npos) prog.stats.specialized_regs = (uint32_t)atoi(info.c_str() + at + 5);
+        }
+        *out = prog.stats;
+        return ZKB_OK;
+    } catch (const std::bad_alloc&) {
+        say("out of host memory");
+        return ZKB_ENOMEM;
+    }
 }
 
 int zkb_air_select(zkb_air_program* prog, int specialized) {

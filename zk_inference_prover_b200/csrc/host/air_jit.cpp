@@ -14,6 +14,7 @@
 #include <dlfcn.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -235,9 +236,13 @@ Nvrtc& nvrtc() {
     static Nvrtc n;
     static std::once_flag once;
     std::call_once(once, [] {
-        for (const char* name : {"libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12", "/usr/local/cuda/lib64/libnvrtc.so"}) {
-            n.handle = dlopen(name, RTLD_NOW | RTLD_LOCAL);
-            if (n.handle) break;
+        if (const char* forced = getenv("ZKB_NVRTC_LIB")) {
+            n.handle = dlopen(forced, RTLD_NOW | RTLD_LOCAL);
+        } else {
+            for (const char* name : {"libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12", "/usr/local/cuda/lib64/libnvrtc.so"}) {
+                n.handle = dlopen(name, RTLD_NOW | RTLD_LOCAL);
+                if (n.handle) break;
+            }
         }
         if (!n.handle) return;
         auto sym = [&](const char* s) { return dlsym(n.handle, s); };
