@@ -75,6 +75,26 @@ int zkb_stark_prove_host(zkb_ctx* ctx, int n_trees, const int* tree_ncols, const
                          zkb_air_program* prog, const uint32_t* scalars, const uint32_t* claimed_sum, const zkb_pcs_config* config,
                          uint32_t* h_out, size_t cap, size_t* n_words, uint32_t* oods_evals, float* h_phase_ms, float* composition_ms);
 
+/* The same for a statement of several components of different sizes (ComponentProvers, prover/air/component_prover.rs:
+ * 161-176): in every tree the columns of component k follow those of components 0..k-1 and have 2^trace_log_k rows.
+ * Each component's constraint quotients go to the accumulation of its own evaluation-domain size with its share of the
+ * random-coefficient powers (DomainEvaluationAccumulator::columns hands them out from the end); the accumulations are
+ * lifted and added in ascending size; every mask point is point + offset * step of the largest trace; one
+ * PointEvaluationAccumulator runs through all components for the out-of-domain check. At least one component must have
+ * the largest size on which the composition polynomial lives. */
+typedef struct zkb_stark_component {
+    zkb_air_program* prog;
+    uint32_t trace_log;
+    const uint32_t* scalars;     /* the program's run-time scalars (may be NULL if it has none) */
+    const uint32_t* claimed_sum; /* 4 words or NULL */
+} zkb_stark_component;
+int zkb_stark_prove_multi_device(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint32_t* const* d_cols, int n_components,
+                                 const zkb_stark_component* components, const zkb_pcs_config* config, uint32_t* h_out, size_t cap,
+                                 size_t* n_words, uint32_t* oods_evals, float* h_phase_ms, float* composition_ms);
+int zkb_stark_prove_multi_host(zkb_ctx* ctx, int n_trees, const int* tree_ncols, const uint32_t* const* h_cols, int n_components,
+                               const zkb_stark_component* components, const zkb_pcs_config* config, uint32_t* h_out, size_t cap,
+                               size_t* n_words, uint32_t* oods_evals, float* h_phase_ms, float* composition_ms);
+
 /* GKR batch proof of n_inst instances. kinds: ZKB_GKR_*; d_nums[i] (NULL where the kind has no
  * numerators) and d_dens[i] are device arrays of ns[i] entries laid out as zkb_gkr_next_layer takes
  * them; they are not modified. The channel starts from Blake2sM31Channel::default() after

@@ -487,19 +487,35 @@ def constraint_quotients_air(air, iparams, qparams, tree_cols, cols, rcp, trace_
     return out
 
 
-def stark_prove(air, iparams, qparams, tree_cols, cols, trace_log, composition_log, claimed_sum=None, pow_bits=10, log_blowup=1,
-                log_last_layer=0, n_queries=3, cap=1 << 24):
-    """prove() for one component (oracle/stark.hpp). cols: the trace on the trace domain, trees concatenated.
+def stark_prove_multi(components, tree_cols, cols, pow_bits=10, log_blowup=1, log_last_layer=0, n_queries=3, cap=1 << 24):
+    """prove() for several components (oracle/stark.hpp). components: list of dicts with air, ip, qp ((n, 4) words), trace_log,
+    claimed_sum (4 words or None). In every tree the columns of component k follow those of the components before it; cols is
+    the flat list (trees concatenated) of the traces on their own trace domains.
     Returns (proof words incl. the channel digest, committed composition value [4], value from the constraints [4])."""
-    ip, qp, trees = _u32(iparams), _u32(qparams), _u32(tree_cols)
+    airs = np.array([c["air"] for c in components], np.int32)
+    logs = _u32([c["trace_log"] for c in components])
+    ips = [_u32(c["ip"]).reshape(-1) for c in components]
+    qps = [_u32(c["qp"]).reshape(-1, 4) for c in components]
+    ip_off = _u32(np.cumsum([0] + [len(x) for x in ips[:-1]]))
+    qp_off = _u32(np.cumsum([0] + [len(x) for x in qps[:-1]]))
+    ip, qp = _u32(np.concatenate(ips)), _u32(np.concatenate(qps).reshape(-1))
+    claimed = _u32(np.stack([np.zeros(4, np.uint32) if c.get("claimed_sum") is None else _u32(c["claimed_sum"]) for c in components]))
+    trees = _u32(tree_cols)
     keep, ptrs = _col_ptrs(cols)
-    cs = _u32(claimed_sum) if claimed_sum is not None else None
+    col_logs = _u32([int(len(c)).bit_length() - 1 for c in keep])
     out = np.zeros(cap, np.uint32)
-    f = lib().zko_stark_prove
+    f = lib().zko_stark_prove_multi
     f.restype = C.c_long
-    n = f(C.c_int(air), _p(ip), _p(qp), _p(trees), C.c_int(trees.size), ptrs, _p(cs) if cs is not None else None, C.c_uint32(trace_log),
-          C.c_uint32(composition_log), C.c_uint32(pow_bits), C.c_uint32(log_blowup), C.c_uint32(log_last_layer), C.c_uint32(n_queries),
-          _p(out), C.c_size_t(cap))
+    n = f(C.c_int(len(components)), _p(airs), _p(logs), _p(ip), _p(ip_off), _p(qp), _p(qp_off), _p(claimed), _p(trees), C.c_int(trees.size),
+          ptrs, _p(col_logs), C.c_uint32(pow_bits), C.c_uint32(log_blowup), C.c_uint32(log_last_layer), C.c_uint32(n_queries), _p(out),
+          C.c_size_t(cap))
     if n < 0:
         raise RuntimeError("stark_prove: output buffer too small")
     return out[:n - 8].copy(), out[n - 8:n - 4].copy(), out[n - 4:n].copy()
+
+
+def stark_prove(air, iparams, qparams, tree_cols, cols, trace_log, composition_log=None, claimed_sum=None, **kw):
+    """One component (composition_log, if given, must be trace_log + 1: the only size the protocol has)."""
+    assert composition_log is None or composition_log == trace_log + 1
+    qp = _u32(qparams).reshape(-1, 4) if np.size(qparams) else np.zeros((1, 4), np.uint32)
+    return stark_prove_multi([dict(air=air, ip=iparams, qp=qp, trace_log=trace_log, claimed_sum=claimed_sum)], tree_cols, cols, **kw)

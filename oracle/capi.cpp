@@ -507,26 +507,31 @@ void zko_constraint_quotients_air(int air, const uint32_t* ip, const uint32_t* q
 #include "stark.hpp"
 extern "C" {
 
-// prove() of nitroo/crates/stwo/src/prover/mod.rs:41-173 for one component whose AIR is one of the three above.
-// cols: the trace on the trace domain (2^trace_log words per column), trees concatenated. Output: the PCS proof words,
-// the channel digest (8 words), the composition polynomial's out-of-domain value from the committed halves (4 words) and
-// from the constraints at the sampled mask values (4 words). Returns the word count or -1.
-long zko_stark_prove(int air, const uint32_t* ip, const uint32_t* qp, const uint32_t* tree_cols, int n_trees, const uint32_t* const* cols,
-                     const uint32_t* claimed_sum, uint32_t trace_log, uint32_t composition_log, uint32_t pow_bits, uint32_t log_blowup,
-                     uint32_t log_last_layer, uint32_t n_queries, uint32_t* out, size_t cap) {
+// prove() of nitroo/crates/stwo/src/prover/mod.rs:41-173 for n_comp components whose AIRs are among the three above.
+// Component k is described by air[k], trace_log[k], its parameter blocks ip + ip_off[k] and qp + 4 * qp_off[k], and
+// claimed_sums + 4k. In every tree the columns of component k follow those of the components before it; cols holds the
+// traces on their trace domains, trees concatenated. Output: the PCS proof words, the channel digest (8 words), the
+// composition polynomial's out-of-domain value from the committed halves (4 words) and from the constraints at the sampled
+// mask values (4 words). Returns the word count or -1.
+long zko_stark_prove_multi(int n_comp, const int* air, const uint32_t* trace_log, const uint32_t* ip, const uint32_t* ip_off,
+                           const uint32_t* qp, const uint32_t* qp_off, const uint32_t* claimed_sums, const uint32_t* tree_cols, int n_trees,
+                           const uint32_t* const* cols, const uint32_t* col_logs, uint32_t pow_bits, uint32_t log_blowup,
+                           uint32_t log_last_layer, uint32_t n_queries, uint32_t* out, size_t cap) {
     PcsConfig cfg;
     cfg.pow_bits = pow_bits;
     cfg.fri = {log_blowup, log_last_layer, n_queries, 1};
-    AirSpec spec = make_air_spec(air, ip, qp);
+    std::vector<StarkComponent> comps;
+    for (int k = 0; k < n_comp; k++)
+        comps.push_back({make_air_spec(air[k], ip + ip_off[k], qp + 4 * (size_t)qp_off[k]), trace_log[k], q_from(claimed_sums + 4 * k)});
     std::vector<std::vector<std::vector<M31>>> trees(n_trees);
     size_t at = 0;
     for (int t = 0; t < n_trees; t++)
         for (uint32_t c = 0; c < tree_cols[t]; c++, at++) {
-            std::vector<M31> v((size_t)1 << trace_log);
+            std::vector<M31> v((size_t)1 << col_logs[at]);
             for (size_t i = 0; i < v.size(); i++) v[i] = M31(cols[at][i]);
             trees[t].push_back(std::move(v));
         }
-    StarkResult r = stark_prove(spec, trees, claimed_sum ? q_from(claimed_sum) : QM31::zero(), trace_log, composition_log, cfg);
+    StarkResult r = stark_prove_multi(comps, trees, cfg);
     std::vector<uint32_t> w = r.proof.to_words();
     for (int i = 0; i < 8; i++) w.push_back(load_le32(&r.digest[4 * i]));
     uint32_t q[4];

@@ -175,3 +175,33 @@ def wide_fibonacci_trace(n_cols, trace_log, seed=1):
 def stark_words(words, committed, at_point):
     """The proof words followed by the two out-of-domain values: what the golden digests of whole proofs cover."""
     return np.concatenate([words, committed, at_point]).astype(np.uint32)
+
+
+def mixed_components_case(oracle, logs=(6, 8), freivalds=True):
+    """A statement of several components of different sizes: wide Fibonacci components with 10, 5, ... columns on traces
+    of the given sizes and, optionally, the Freivalds component on the witness of a small matrix product. Returns
+    (components for the oracle, lowered sources, flat columns (trees concatenated), columns per tree, columns as trees per component)."""
+    from test_freivalds import _case, layout
+
+    comps, sources, per_comp = [], [], []
+    for i, lg in enumerate(logs):
+        n_cols = 10 - 5 * (i % 2)
+        comps.append(dict(air=0, ip=[n_cols], qp=np.zeros((1, 4), np.uint32), trace_log=lg, claimed_sum=None))
+        sources.append(air.wide_fibonacci(air.ExprEvaluator(), n_cols).source())
+        per_comp.append([[], [], wide_fibonacci_trace(n_cols, lg, seed=11 + i), []])
+    if freivalds:
+        tokens, n_in, n_outs, chunks = 5, 6, [7, 5], 4
+        qx, qws = _case(31, tokens, n_in, n_outs)
+        grid, pq, pk = layout(n_in, max(n_outs), tokens, chunks)
+        trace_log, n_mats = grid[0], len(qws)
+        base, pre, _, _ = oracle.freivalds_columns(qx, qws, grid, pq, pk)
+        fp = freivalds_params(oracle, pk, pq, n_mats, 3100)
+        inter, claims = oracle.freivalds_acc(base, pre, n_mats, grid, pq, pk, fp["s"], fp["rv"])
+        qp = np.concatenate([fp["rv_pow"], fp["rv_step"][None], fp["s_pow"], fp["s_step"][None], claims, qm31_array(5, 2)]).astype(np.uint32)
+        comps.append(dict(air=2, ip=[pk, pq, n_mats, 128, 0], qp=qp, trace_log=trace_log, claimed_sum=None))
+        sources.append(air.freivalds(air.ExprEvaluator(), pk, pq, n_mats, fp["rv_pow"], fp["rv_step"], fp["s_pow"], fp["s_step"], claims, 128,
+                                     None).source())
+        per_comp.append([list(pre[n_mats * pk:]) + list(pre[:n_mats * pk]), [], list(base), list(inter)])
+    trees = [[c for pc in per_comp for c in pc[t]] for t in range(4)]
+    flat = [c for t in trees for c in t]
+    return comps, sources, flat, [len(t) for t in trees], per_comp

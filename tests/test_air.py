@@ -197,3 +197,16 @@ def test_specialised_kernel_source_compiles_without_a_gpu(oracle, zkb):
             pytest.skip("NVRTC is not installed here")
         raise
     assert st["specialized"] == 1 and 16 <= st["specialized_regs"] <= 255
+
+
+def test_whole_proof_of_several_components_of_different_sizes(oracle):
+    """Three components on traces of 2^6, 2^8 and 2^5 rows: per-size accumulations lifted and added, mask points in steps of
+    the largest trace, one out-of-domain check running through all of them."""
+    comps, _, flat, tree_cols, _ = air_cases.mixed_components_case(oracle)
+    for log_blowup in (1, 2):
+        _, committed, at_point = oracle.stark_prove_multi(comps, tree_cols, flat, pow_bits=3, log_blowup=log_blowup, n_queries=5)
+        assert (committed == at_point).all() and committed.any()
+    flat[12] = flat[12].copy()
+    flat[12][3] ^= 1
+    _, committed, at_point = oracle.stark_prove_multi(comps, tree_cols, flat, pow_bits=3, log_blowup=1, n_queries=5)
+    assert not (committed == at_point).all()

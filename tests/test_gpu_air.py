@@ -334,3 +334,35 @@ print("OK")
     env = dict(os.environ, ZKB_NVRTC_LIB="/nonexistent/libnvrtc.so")
     r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and r.stdout.strip().endswith("OK"), r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("log_blowup,logs,specialize", [(1, (6, 8), False), (2, (6, 8), True), (1, (9, 7, 9), True)])
+def test_stark_proof_of_several_components_matches_oracle(ctx, oracle, log_blowup, logs, specialize):
+    """A statement of wide Fibonacci components of different sizes and the Freivalds component: sub-accumulations per size,
+    lifted and added; mask points in steps of the largest trace; one out-of-domain check through all components."""
+    comps, sources, flat, tree_cols, per_comp = air_cases.mixed_components_case(oracle, logs=logs)
+    kw = dict(pow_bits=3, log_blowup=log_blowup, n_queries=5)
+    want, w_committed, w_point = oracle.stark_prove_multi(comps, tree_cols, flat, **kw)
+    assert (w_committed == w_point).all()
+    progs = [ctx.air_compile(s) for s in sources]
+    if specialize:
+        for p in progs:
+            p.specialize()
+    trees = [[c for pc in per_comp for c in pc[t]] for t in range(4)]
+    bufs = [[ctx.upload(c) for c in t] for t in trees]
+    components = [(p, c["trace_log"], None) for p, c in zip(progs, comps)]
+    got, committed, at_point, _ = ctx.stark_prove_multi(components, [[b.ptr for b in t] for t in bufs], **kw)
+    assert (committed == w_committed).all() and (at_point == w_point).all()
+    assert len(got) == len(want) and (got == want).all()
+    got_h, c_h, p_h, _ = ctx.stark_prove_multi(components, trees, host=True, **kw)
+    assert (got_h == want).all() and (c_h == w_committed).all() and (p_h == w_point).all()
+    # a corrupted cell of the middle component fails the check, with the oracle's values
+    flat2 = [c.copy() for c in flat]
+    flat2[12][3] ^= 1
+    want2, w_c2, w_p2 = oracle.stark_prove_multi(comps, tree_cols, flat2, **kw)
+    trees2, at = [], 0
+    for t in trees:
+        trees2.append(flat2[at:at + len(t)])
+        at += len(t)
+    got2, c2, p2, _ = ctx.stark_prove_multi(components, trees2, host=True, **kw)
+    assert not (w_c2 == w_p2).all() and (c2 == w_c2).all() and (p2 == w_p2).all() and (got2 == want2).all()

@@ -22,7 +22,7 @@ EXPORTED_SYMBOLS = [
     "zkb_freivalds_scatter", "zkb_freivalds_acc",
 ]
 # Every symbol include/zkb200_prover.h declares.
-PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_stark_prove_device", "zkb_stark_prove_host", "zkb_gkr_prove_device"]
+PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_stark_prove_device", "zkb_stark_prove_host", "zkb_stark_prove_multi_device", "zkb_stark_prove_multi_host", "zkb_gkr_prove_device"]
 # Every symbol include/zkb200_air.h declares.
 AIR_SYMBOLS = ["zkb_air_compile", "zkb_air_analyze", "zkb_air_free", "zkb_air_specialize", "zkb_air_select", "zkb_air_get_stats", "zkb_constraint_quotients", "zkb_constraint_denom_inv"]
 PCS_PHASES = ["interpolate", "extend", "merkle", "sample", "quotients", "fri_commit", "grind", "decommit"]
@@ -41,6 +41,10 @@ class PcsConfig(C.Structure):
 class AirStats(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("n_ops", "n_live_ops", "n_uniform", "n_instr", "n_loads", "n_columns_read", "reg_words",
                                           "uniform_words", "threads", "rows_per_thread", "smem_bytes", "m31_mults", "specialized", "specialized_regs")]
+
+
+class StarkComponent(C.Structure):
+    _fields_ = [("prog", C.c_void_p), ("trace_log", C.c_uint32), ("scalars", C.c_void_p), ("claimed_sum", C.c_void_p)]
 
 
 class ZkbError(RuntimeError):
@@ -531,6 +535,44 @@ class Context:
             fn = self.lib.zkb_stark_prove_device
         self._check(fn(self.h, C.c_int(len(trees)), ncols.ctypes.data_as(C.c_void_p), ptrs, C.c_uint32(trace_log), prog.h,
                        sc.ctypes.data_as(C.c_void_p), cs.ctypes.data_as(C.c_void_p) if cs is not None else None, C.byref(cfg),
+                       out.ctypes.data_as(C.c_void_p), C.c_size_t(cap), C.byref(n), oods.ctypes.data_as(C.c_void_p), ph, C.byref(comp_ms)))
+        if phases is not None:
+            phases.update({k: float(ph[i]) for i, k in enumerate(PCS_PHASES)})
+            phases["composition"] = float(comp_ms.value)
+        return out[:n.value].copy(), oods[:4].copy(), oods[4:].copy(), float(comp_ms.value)
+
+    def stark_prove_multi(self, components, trees, pow_bits=10, log_blowup=1, log_last_layer=0, n_queries=3, cap=1 << 24, phases=None,
+                          host=False):
+        """zkb_stark_prove_multi_device / _host. components: list of (AirProgram, trace_log, claimed_sum or None[, scalars]); trees:
+        per tree the list of device pointers (host arrays when host=True), the columns of component k after those of the components
+        before it. Returns (proof words incl. channel digest, committed composition value [4], value from the constraints [4],
+        composition_ms)."""
+        keep = []
+        arr = (StarkComponent * len(components))()
+        for i, comp in enumerate(components):
+            prog, trace_log, claimed = comp[0], comp[1], comp[2]
+            sc = _u32(prog.source.scalars if len(comp) < 4 or comp[3] is None else comp[3])
+            cs = _u32(claimed) if claimed is not None else None
+            keep += [sc, cs]
+            arr[i].prog = prog.h
+            arr[i].trace_log = trace_log
+            arr[i].scalars = sc.ctypes.data if sc.size else None
+            arr[i].claimed_sum = cs.ctypes.data if cs is not None else None
+        ncols = np.array([len(t) for t in trees], dtype=np.int32)
+        cfg = PcsConfig(pow_bits, log_blowup, log_last_layer, n_queries)
+        out = np.empty(cap, np.uint32)
+        n = C.c_size_t()
+        oods = np.zeros(8, np.uint32)
+        ph = (C.c_float * len(PCS_PHASES))()
+        comp_ms = C.c_float()
+        if host:
+            hk = [_u32(c) for t in trees for c in t]
+            ptrs = (C.c_void_p * len(hk))(*[k.ctypes.data for k in hk])
+            fn = self.lib.zkb_stark_prove_multi_host
+        else:
+            ptrs = _ptr_array([p for t in trees for p in t])
+            fn = self.lib.zkb_stark_prove_multi_device
+        self._check(fn(self.h, C.c_int(len(trees)), ncols.ctypes.data_as(C.c_void_p), ptrs, C.c_int(len(components)), arr, C.byref(cfg),
                        out.ctypes.data_as(C.c_void_p), C.c_size_t(cap), C.byref(n), oods.ctypes.data_as(C.c_void_p), ph, C.byref(comp_ms)))
         if phases is not None:
             phases.update({k: float(ph[i]) for i, k in enumerate(PCS_PHASES)})

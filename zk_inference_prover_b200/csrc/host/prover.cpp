@@ -1031,103 +1031,150 @@ static int pcs_prove_impl(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint
     }
 }
 
-// prove() for one component (STWO/prover/mod.rs:41-173): commit the trees, draw the random coefficient, evaluate the
-// constraint quotients on the evaluation domain of twice the trace size (zkb_constraint_quotients), interpolate and
-// split the composition polynomial, commit its eight coordinate halves, sample every column at its mask points around
-// a drawn out-of-domain point, and prove the samples. The prover's own sanity check - the composition polynomial's value
-// at the point, once from the committed halves (core/proof.rs:27-57) and once from the constraints at the sampled mask
-// values (constraint-framework/src/component.rs:374-413, point.rs) - is returned in oods_evals for the caller to compare.
+// prove() (STWO/prover/mod.rs:41-173) for a statement of one or more components: commit the trees, draw the random
+// coefficient, evaluate every component's constraint quotients on the evaluation domain of twice its trace size
+// (zkb_constraint_quotients) into the accumulation of that size, lift and add the accumulations
+// (DomainEvaluationAccumulator, prover/air/accumulation.rs), interpolate and split the composition polynomial, commit its
+// eight coordinate halves, sample every column at its mask points around a drawn out-of-domain point, and prove the
+// samples. The prover's own sanity check - the composition polynomial's value at the point, once from the committed
+// halves (core/proof.rs:27-57) and once from the constraints at the sampled mask values (core/air/components.rs:76-94,
+// constraint-framework/src/component.rs:374-413, point.rs) - is returned in oods_evals for the caller to compare.
 static int stark_prove_impl(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint32_t* const* d_cols, const uint32_t* const* h_cols,
-                            uint32_t trace_log, zkb_air_program* prog, const uint32_t* scalars, const uint32_t* claimed_sum,
-                            const zkb_pcs_config* cfg, uint32_t* h_out, size_t cap, size_t* n_words, uint32_t* oods_evals,
-                            float* h_phase_ms, float* composition_ms) {
+                            int n_components, const zkb_stark_component* comps, const zkb_pcs_config* cfg, uint32_t* h_out, size_t cap,
+                            size_t* n_words, uint32_t* oods_evals, float* h_phase_ms, float* composition_ms) {
     if (!ctx) return ZKB_EINVAL;
-    if (!tree_ncols || !cfg || !h_out || !n_words || !prog || !oods_evals || n_trees <= 0 || (!d_cols && !h_cols)) return ZKB_EINVAL;
-    if (prog->n_scalars && !scalars) return ZKB_EINVAL;
+    if (!tree_ncols || !cfg || !h_out || !n_words || !comps || !oods_evals || n_trees <= 0 || n_components <= 0 || (!d_cols && !h_cols))
+        return ZKB_EINVAL;
     try {
         Device dev(ctx);
         PcsConfig config{cfg->pow_bits, {cfg->log_blowup_factor, cfg->log_last_layer_degree_bound, cfg->n_queries, 1}};
-        const uint32_t blowup = config.fri.log_blowup_factor, comp_log = trace_log + 1;
-        if (trace_log < 1 || blowup < 1 || (int)(trace_log + blowup) > zkb_max_log_size(ctx)) return ZKB_EINVAL;
+        const uint32_t blowup = config.fri.log_blowup_factor;
+        uint32_t max_trace_log = 0;
+        size_t n_constraints = 0;
+        for (int k = 0; k < n_components; k++) {
+            const zkb_stark_component& c = comps[k];
+            if (!c.prog || c.trace_log < 1 || (size_t)n_trees != c.prog->tree_base.size() || (c.prog->n_scalars && !c.scalars))
+                return zk_set_error_public(ctx, ZKB_EINVAL, "zkb_stark_prove: a component has no program, no scalars, or a program compiled for other trees");
+            max_trace_log = std::max(max_trace_log, c.trace_log);
+            n_constraints += c.prog->constraints.size();
+        }
+        if (blowup < 1 || (int)(max_trace_log + blowup) > zkb_max_log_size(ctx)) return ZKB_EINVAL;
+        // where each component's columns start in each tree (they follow those of the components before it), column sizes
+        auto cols_of = [&](int k, int t) {
+            const auto& tb = comps[k].prog->tree_base;
+            return (t + 1 < n_trees ? tb[t + 1] : comps[k].prog->n_cols) - tb[t];
+        };
+        std::vector<std::vector<uint32_t>> first((size_t)n_components, std::vector<uint32_t>((size_t)n_trees, 0));
+        std::vector<uint32_t> tree_start((size_t)n_trees, 0), col_logs;
         int total = 0;
-        for (int t = 0; t < n_trees; t++) total += tree_ncols[t];
-        if ((uint32_t)total != prog->n_cols || (size_t)n_trees != prog->tree_base.size())
-            return zk_set_error_public(ctx, ZKB_EINVAL, "zkb_stark_prove: the trees do not have the columns the program was compiled for");
-        std::vector<uint32_t> col_logs((size_t)total, trace_log);
+        for (int t = 0; t < n_trees; t++) {
+            tree_start[t] = (uint32_t)total;
+            uint32_t at = 0;
+            for (int k = 0; k < n_components; k++) {
+                first[k][t] = at;
+                at += cols_of(k, t);
+                col_logs.insert(col_logs.end(), cols_of(k, t), comps[k].trace_log);
+            }
+            if ((int)at != tree_ncols[t])
+                return zk_set_error_public(ctx, ZKB_EINVAL, "zkb_stark_prove: the trees do not have the columns the programs were compiled for");
+            total += tree_ncols[t];
+        }
         Channel ch;
         config.mix_into(ch);
         CommitmentSchemeProver prover(dev, config, h_phase_ms);
         commit_input_trees(dev, ctx, prover, ch, n_trees, tree_ncols, d_cols, h_cols, col_logs.data(), total);
 
         // ---- composition polynomial
-        const size_t n_constraints = prog->constraints.size();
         const qm31 random_coeff = ch.draw_secure_felt();
         dev.check(zkb_event_record(ctx, 28));
-        std::vector<qm31> powers(n_constraints);  // the first constraint takes the highest power (component_prover.rs:271)
+        std::vector<qm31> ascending_powers(n_constraints);
         {
             qm31 pw = qm31_one();
-            for (size_t k = 0; k < n_constraints; k++) { powers[n_constraints - 1 - k] = pw; pw = pw * random_coeff; }
+            for (size_t i = 0; i < n_constraints; i++) { ascending_powers[i] = pw; pw = pw * random_coeff; }
         }
-        // columns on the evaluation domain: the committed evaluations themselves when the blow-up is 2, else an extension
-        std::vector<BaseColumn> extended;
-        std::vector<const uint32_t*> col_ptrs;
-        for (auto& t : prover.trees) {
-            if (blowup == 1) {
-                for (auto& e : t.evals) col_ptrs.push_back(e.ptr());
-            } else {
-                std::vector<const BaseColumn*> cc;
-                for (auto& c : t.coeffs) cc.push_back(&c);
-                auto ev = B200Backend::evaluate_polynomials(dev, cc, 1);
-                for (auto& e : ev) { col_ptrs.push_back(e.ptr()); extended.push_back(std::move(e)); }
+        size_t remaining = n_constraints;
+        std::map<uint32_t, SecureColumnByCoords> sub;  // sub_accumulations by log size
+        std::vector<qm31> shifts((size_t)n_components, qm31_zero());
+        for (int k = 0; k < n_components; k++) {
+            const zkb_stark_component& c = comps[k];
+            const size_t n_k = c.prog->constraints.size();
+            // columns(): the last n_k powers, reversed so that the component's first constraint takes the highest (component_prover.rs:271)
+            std::vector<qm31> powers(n_k);
+            for (size_t i = 0; i < n_k; i++) powers[i] = ascending_powers[remaining - 1 - i];
+            remaining -= n_k;
+            const uint32_t eval_log = c.trace_log + 1;
+            // the component's columns on its evaluation domain: the committed evaluations themselves when the blow-up is 2
+            std::vector<BaseColumn> extended;
+            std::vector<const uint32_t*> col_ptrs;
+            for (int t = 0; t < n_trees; t++) {
+                const uint32_t cnt = cols_of(k, t);
+                if (blowup == 1) {
+                    for (uint32_t q = 0; q < cnt; q++) col_ptrs.push_back(prover.trees[t].evals[first[k][t] + q].ptr());
+                } else if (cnt) {
+                    std::vector<const BaseColumn*> cc;
+                    for (uint32_t q = 0; q < cnt; q++) cc.push_back(&prover.trees[t].coeffs[first[k][t] + q]);
+                    auto ev = B200Backend::evaluate_polynomials(dev, cc, 1);
+                    for (auto& e : ev) { col_ptrs.push_back(e.ptr()); extended.push_back(std::move(e)); }
+                }
             }
+            if (c.claimed_sum) {
+                qm31 claimed;
+                for (int q = 0; q < 4; q++) claimed.c[q] = c.claimed_sum[q];
+                shifts[k] = claimed * qm31_inv(qm31_from_m31(1u << c.trace_log));  // LogupAtRow::new, logup.rs:33-41
+            }
+            uint32_t denom_inv[2];
+            if (zkb_constraint_denom_inv((int)c.trace_log, (int)eval_log, denom_inv) != ZKB_OK) return ZKB_EINVAL;
+            auto it = sub.find(eval_log);
+            const bool fresh = it == sub.end();
+            if (fresh) it = sub.emplace(eval_log, SecureColumnByCoords(dev, (size_t)1 << eval_log)).first;
+            auto accp = it->second.ptrs();
+            dev.check(zkb_constraint_quotients(ctx, c.prog, col_ptrs.data(), c.scalars, shifts[k].c, reinterpret_cast<const uint32_t*>(powers.data()),
+                                               denom_inv, (int)c.trace_log, (int)eval_log, accp.data(), fresh ? 0 : 1));
         }
-        qm31 shift = qm31_zero(), claimed = qm31_zero();
-        if (claimed_sum) {
-            for (int k = 0; k < 4; k++) claimed.c[k] = claimed_sum[k];
-            shift = claimed * qm31_inv(qm31_from_m31(1u << trace_log));  // LogupAtRow::new, logup.rs:33-41
-        }
-        std::vector<uint32_t> denom_inv(2);
-        if (zkb_constraint_denom_inv((int)trace_log, (int)comp_log, denom_inv.data()) != ZKB_OK) return ZKB_EINVAL;
+        // DomainEvaluationAccumulator::finalize (air/accumulation.rs:89-124): lift and add ascending sizes, interpolate;
+        // then split_at_mid and extend_polys + commit
+        std::vector<SecureColumnByCoords> ascending;
+        for (auto& kv : sub) ascending.push_back(std::move(kv.second));
+        sub.clear();
+        SecureColumnByCoords acc = B200Backend::lift_and_accumulate(dev, std::move(ascending));
+        const uint32_t comp_log = max_trace_log + 1;
         const size_t N = (size_t)1 << comp_log;
-        BaseColumn acc[4] = {BaseColumn(dev, N), BaseColumn(dev, N), BaseColumn(dev, N), BaseColumn(dev, N)};
-        uint32_t* accp[4] = {acc[0].ptr(), acc[1].ptr(), acc[2].ptr(), acc[3].ptr()};
-        dev.check(zkb_constraint_quotients(ctx, prog, col_ptrs.data(), scalars, shift.c, reinterpret_cast<const uint32_t*>(powers.data()),
-                                           denom_inv.data(), (int)trace_log, (int)comp_log, accp, 0));
-        extended.clear();
-        // DomainEvaluationAccumulator::finalize (air/accumulation.rs:89-124), split_at_mid, extend_polys + commit
+        if (acc.len() != N) return zk_set_error_public(ctx, ZKB_EINVAL, "zkb_stark_prove: no component of the largest size");
         {
-            std::vector<BaseColumn*> ap = {&acc[0], &acc[1], &acc[2], &acc[3]};
+            std::vector<BaseColumn*> ap = {&acc.columns[0], &acc.columns[1], &acc.columns[2], &acc.columns[3]};
             B200Backend::interpolate_columns(dev, ap);
             std::vector<BaseColumn> halves;
-            for (int k = 0; k < 4; k++) halves.push_back(BaseColumn::view(dev, acc[k].ptr(), N / 2));
-            for (int k = 0; k < 4; k++) halves.push_back(BaseColumn::view(dev, acc[k].ptr() + N / 2, N / 2));
+            for (int q = 0; q < 4; q++) halves.push_back(BaseColumn::view(dev, acc.columns[q].ptr(), N / 2));
+            for (int q = 0; q < 4; q++) halves.push_back(BaseColumn::view(dev, acc.columns[q].ptr() + N / 2, N / 2));
             dev.check(zkb_event_record(ctx, 29));
             prover.mark(-1);  // the composition is timed on its own, not as part of the next tree's first phase
             prover.commit_evals(std::move(halves), ch, nullptr, nullptr, true);
         }
 
-        // ---- mask points (component.rs:356-368) and the samples' proof
+        // ---- mask points (component.rs:356-368, core/air/components.rs:32-74) and the samples' proof
         CirclePointQ oods = get_random_point(ch);
         const uint32_t lifting_log = prover.trees.back().max_log();
         const uint32_t max_log_degree_bound = lifting_log - blowup;
-        std::vector<std::vector<int32_t>> offsets((size_t)total);
-        for (const zkb_air_op& o : prog->ops)
-            if (o.op == ZKB_AIR_LOAD) {
-                auto& v = offsets[prog->tree_base[o.a] + o.b];
-                if (std::find(v.begin(), v.end(), (int32_t)o.c) == v.end()) v.push_back((int32_t)o.c);
-            }
+        // per component: the mask offsets of each of its columns, in the order the program asks for them
+        std::vector<std::vector<std::vector<int32_t>>> offsets((size_t)n_components);
         std::vector<std::vector<std::vector<CirclePointQ>>> points((size_t)n_trees + 1);
-        int flat = 0;
-        for (int t = 0; t < n_trees; t++)
-            for (int c = 0; c < tree_ncols[t]; c++, flat++) {
-                std::vector<CirclePointQ> pts;
-                for (int32_t off : offsets[flat]) {
-                    // trace_step.mul_signed(off): the point of index off * 2^(31 - max_log_degree_bound) in the circle group
-                    cpoint st = host_circle_point(((uint32_t)off << (31 - max_log_degree_bound)) & 0x7fffffffu);
-                    pts.push_back(point_add(oods, {qm31_from_m31(st.x), qm31_from_m31(st.y)}));
+        for (int t = 0; t < n_trees; t++) points[t].resize((size_t)tree_ncols[t]);
+        for (int k = 0; k < n_components; k++) {
+            const zkb_air_program* prog = comps[k].prog;
+            offsets[k].resize(prog->n_cols);
+            for (const zkb_air_op& o : prog->ops)
+                if (o.op == ZKB_AIR_LOAD) {
+                    auto& v = offsets[k][prog->tree_base[o.a] + o.b];
+                    if (std::find(v.begin(), v.end(), (int32_t)o.c) == v.end()) v.push_back((int32_t)o.c);
                 }
-                points[t].push_back(pts);
-            }
+            for (int t = 0; t < n_trees; t++)
+                for (uint32_t q = 0; q < cols_of(k, t); q++)
+                    for (int32_t off : offsets[k][prog->tree_base[t] + q]) {
+                        // trace_step.mul_signed(off): the point of index off * 2^(31 - max_log_degree_bound) in the circle group
+                        cpoint st = host_circle_point(((uint32_t)off << (31 - max_log_degree_bound)) & 0x7fffffffu);
+                        points[t][first[k][t] + q].push_back(point_add(oods, {qm31_from_m31(st.x), qm31_from_m31(st.y)}));
+                    }
+        }
         points.back().assign(8, {oods});
         PcsProof proof = prover.prove_values(points, ch);
         prover.finish_timing();
@@ -1144,39 +1191,41 @@ static int stark_prove_impl(zkb_ctx* ctx, int n_trees, const int* tree_ncols, ui
         const qm31 committed = left + point_repeated_double(oods, max_log_degree_bound - 1).x * right;
         // coset_vanishing(CanonicCoset(max_log_degree_bound).coset, oods): the shift -initial + step/2 is zero for a canonic coset
         qm31 vanish = oods.x;
-        for (uint32_t k = 1; k < max_log_degree_bound; k++) vanish = qm31_double_x(vanish);
+        for (uint32_t q = 1; q < max_log_degree_bound; q++) vanish = qm31_double_x(vanish);
         const qm31 denom_inverse = qm31_inv(vanish);
-        // the program at the point: every value is a secure-field element, a LOAD is the sampled mask value
-        std::vector<qm31> v(prog->ops.size(), qm31_zero());
-        flat = 0;
-        std::vector<std::pair<int, int>> where((size_t)total);
-        for (int t = 0; t < n_trees; t++)
-            for (int c = 0; c < tree_ncols[t]; c++, flat++) where[flat] = {t, c};
-        for (size_t i = 0; i < prog->ops.size(); i++) {
-            const zkb_air_op& o = prog->ops[i];
-            switch (o.op) {
-                case ZKB_AIR_LOAD: {
-                    const uint32_t col = prog->tree_base[o.a] + o.b;
-                    const auto& offs = offsets[col];
-                    const size_t k = std::find(offs.begin(), offs.end(), (int32_t)o.c) - offs.begin();
-                    v[i] = proof.sampled_values[where[col].first][where[col].second][k];
-                    break;
+        qm31 at_point = qm31_zero();  // one PointEvaluationAccumulator (core/air/accumulation.rs:12-36) through all components
+        for (int k = 0; k < n_components; k++) {
+            const zkb_air_program* prog = comps[k].prog;
+            // the program at the point: every value is a secure-field element, a LOAD is the sampled mask value
+            std::vector<qm31> v(prog->ops.size(), qm31_zero());
+            std::vector<std::pair<int, uint32_t>> where(prog->n_cols);
+            for (int t = 0; t < n_trees; t++)
+                for (uint32_t q = 0; q < cols_of(k, t); q++) where[prog->tree_base[t] + q] = {t, first[k][t] + q};
+            for (size_t i = 0; i < prog->ops.size(); i++) {
+                const zkb_air_op& o = prog->ops[i];
+                switch (o.op) {
+                    case ZKB_AIR_LOAD: {
+                        const uint32_t col = prog->tree_base[o.a] + o.b;
+                        const auto& offs = offsets[k][col];
+                        const size_t j = std::find(offs.begin(), offs.end(), (int32_t)o.c) - offs.begin();
+                        v[i] = proof.sampled_values[where[col].first][where[col].second][j];
+                        break;
+                    }
+                    case ZKB_AIR_CONST_M31: v[i] = qm31_from_m31(o.a); break;
+                    case ZKB_AIR_SCALAR: for (int q = 0; q < 4; q++) v[i].c[q] = comps[k].scalars[4 * (size_t)o.a + q]; break;
+                    case ZKB_AIR_CUMSUM_SHIFT: v[i] = shifts[k]; break;
+                    case ZKB_AIR_ADD_B: case ZKB_AIR_ADD_E: v[i] = v[o.a] + v[o.b]; break;
+                    case ZKB_AIR_SUB_B: case ZKB_AIR_SUB_E: v[i] = v[o.a] - v[o.b]; break;
+                    case ZKB_AIR_MUL_B: case ZKB_AIR_MUL_E: v[i] = v[o.a] * v[o.b]; break;
+                    case ZKB_AIR_NEG_B: case ZKB_AIR_NEG_E: v[i] = qm31_neg(v[o.a]); break;
+                    case ZKB_AIR_INV_B: v[i] = qm31_is_zero(v[o.a]) ? qm31_zero() : qm31_inv(v[o.a]); break;
+                    case ZKB_AIR_PACK: v[i] = from_partial_evals(v[o.a], v[o.b], v[o.c], v[o.d]); break;
+                    default: break;
                 }
-                case ZKB_AIR_CONST_M31: v[i] = qm31_from_m31(o.a); break;
-                case ZKB_AIR_SCALAR: for (int k = 0; k < 4; k++) v[i].c[k] = scalars[4 * (size_t)o.a + k]; break;
-                case ZKB_AIR_CUMSUM_SHIFT: v[i] = shift; break;
-                case ZKB_AIR_ADD_B: case ZKB_AIR_ADD_E: v[i] = v[o.a] + v[o.b]; break;
-                case ZKB_AIR_SUB_B: case ZKB_AIR_SUB_E: v[i] = v[o.a] - v[o.b]; break;
-                case ZKB_AIR_MUL_B: case ZKB_AIR_MUL_E: v[i] = v[o.a] * v[o.b]; break;
-                case ZKB_AIR_NEG_B: case ZKB_AIR_NEG_E: v[i] = qm31_neg(v[o.a]); break;
-                case ZKB_AIR_INV_B: v[i] = qm31_is_zero(v[o.a]) ? qm31_zero() : qm31_inv(v[o.a]); break;
-                case ZKB_AIR_PACK: v[i] = from_partial_evals(v[o.a], v[o.b], v[o.c], v[o.d]); break;
-                default: break;
             }
+            for (uint32_t cn : prog->constraints) at_point = at_point * random_coeff + denom_inverse * v[cn];
         }
-        qm31 at_point = qm31_zero();  // PointEvaluationAccumulator (core/air/accumulation.rs:12-36)
-        for (size_t k = 0; k < n_constraints; k++) at_point = at_point * random_coeff + denom_inverse * v[prog->constraints[k]];
-        for (int k = 0; k < 4; k++) { oods_evals[k] = committed.c[k]; oods_evals[4 + k] = at_point.c[k]; }
+        for (int q = 0; q < 4; q++) { oods_evals[q] = committed.c[q]; oods_evals[4 + q] = at_point.c[q]; }
 
         std::vector<uint32_t> w = proof.to_words();
         w.insert(w.end(), ch.digest().begin(), ch.digest().end());
@@ -1199,18 +1248,32 @@ int zkb_pcs_prove_device(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint3
     return pcs_prove_impl(ctx, n_trees, tree_ncols, d_cols, nullptr, col_logs, config, two_sample_every, h_out, cap, n_words, h_phase_ms);
 }
 
+int zkb_stark_prove_multi_device(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint32_t* const* d_cols, int n_components,
+                                 const zkb_stark_component* components, const zkb_pcs_config* config, uint32_t* h_out, size_t cap,
+                                 size_t* n_words, uint32_t* oods_evals, float* h_phase_ms, float* composition_ms) {
+    return stark_prove_impl(ctx, n_trees, tree_ncols, d_cols, nullptr, n_components, components, config, h_out, cap, n_words, oods_evals,
+                            h_phase_ms, composition_ms);
+}
+
+int zkb_stark_prove_multi_host(zkb_ctx* ctx, int n_trees, const int* tree_ncols, const uint32_t* const* h_cols, int n_components,
+                               const zkb_stark_component* components, const zkb_pcs_config* config, uint32_t* h_out, size_t cap,
+                               size_t* n_words, uint32_t* oods_evals, float* h_phase_ms, float* composition_ms) {
+    return stark_prove_impl(ctx, n_trees, tree_ncols, nullptr, h_cols, n_components, components, config, h_out, cap, n_words, oods_evals,
+                            h_phase_ms, composition_ms);
+}
+
 int zkb_stark_prove_device(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint32_t* const* d_cols, uint32_t trace_log,
                            zkb_air_program* prog, const uint32_t* scalars, const uint32_t* claimed_sum, const zkb_pcs_config* config,
                            uint32_t* h_out, size_t cap, size_t* n_words, uint32_t* oods_evals, float* h_phase_ms, float* composition_ms) {
-    return stark_prove_impl(ctx, n_trees, tree_ncols, d_cols, nullptr, trace_log, prog, scalars, claimed_sum, config, h_out, cap, n_words,
-                            oods_evals, h_phase_ms, composition_ms);
+    zkb_stark_component c{prog, trace_log, scalars, claimed_sum};
+    return stark_prove_impl(ctx, n_trees, tree_ncols, d_cols, nullptr, 1, &c, config, h_out, cap, n_words, oods_evals, h_phase_ms, composition_ms);
 }
 
 int zkb_stark_prove_host(zkb_ctx* ctx, int n_trees, const int* tree_ncols, const uint32_t* const* h_cols, uint32_t trace_log,
                          zkb_air_program* prog, const uint32_t* scalars, const uint32_t* claimed_sum, const zkb_pcs_config* config,
                          uint32_t* h_out, size_t cap, size_t* n_words, uint32_t* oods_evals, float* h_phase_ms, float* composition_ms) {
-    return stark_prove_impl(ctx, n_trees, tree_ncols, nullptr, h_cols, trace_log, prog, scalars, claimed_sum, config, h_out, cap, n_words,
-                            oods_evals, h_phase_ms, composition_ms);
+    zkb_stark_component c{prog, trace_log, scalars, claimed_sum};
+    return stark_prove_impl(ctx, n_trees, tree_ncols, nullptr, h_cols, 1, &c, config, h_out, cap, n_words, oods_evals, h_phase_ms, composition_ms);
 }
 
 int zkb_pcs_prove_host(zkb_ctx* ctx, int n_trees, const int* tree_ncols, const uint32_t* const* h_cols, const uint32_t* col_logs,
