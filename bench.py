@@ -805,6 +805,106 @@ def run_stark(args, rank):
     ctx.close()
 
 
+def run_segment_replay(args, rank):
+    """--mode segment-replay: the operator trace of one composed decode segment, replayed on seeded random columns.
+
+    A segment of the reference prover is one STARK over hundreds of components of different heights (tens of thousands of
+    columns of 2^4..2^23 rows) plus five batched LogUp-GKR reductions. tests/golden/segment_shapes.json holds those shapes,
+    made from the reference's cell-exact cost model by tests/golden/make_segment_shapes.py. One step here: copy the trace in
+    (device to device), commit the base, interaction and boundary trees, prove one opening per column with the prover's own
+    PcsConfig (blow-up 2, 100 queries, no proof of work), then one GKR batch proof per reduction family over LogUpSingles
+    instances of the components' lookup counts (a component of L lookups per row is split along the binary decomposition of
+    L, as the reference does). Timing only: the witness values, the gadgets' constraint programs and the digest of a real
+    segment need the application code above the operators."""
+    if rank != 0:
+        return
+    import zk_inference_prover_b200 as z
+
+    P = (1 << 31) - 1
+    seg = json.load(open(os.path.join(ROOT, "tests", "golden", "segment_shapes.json")))["segments"][args.segment]
+    trees = [[], [], []]
+    gkr = {}
+    for c in seg["components"]:
+        for _ in range(c["repeat"]):
+            trees[0] += [c["log_rows"]] * c["base_cols"]
+            trees[1] += [c["log_rows"]] * c["interaction_cols"]
+            looks, b = c["lookups_per_row"], 0
+            while looks:
+                if looks & 1:
+                    gkr.setdefault(c["family"], []).append(c["log_rows"] + b)
+                looks >>= 1
+                b += 1
+    for b in seg["boundary_cols"]:
+        trees[2] += [b["log_rows"]] * b["cols"]
+    logs = [l for t in trees for l in t]
+    cells = sum(1 << l for l in logs)
+    assert cells == seg["cells"]["fresh"]
+    log_blowup = 1
+    ctx = z.Context(device=0, max_log_size=max(logs) + log_blowup)
+    rng = np.random.default_rng(0x5EED0006)
+    pristine = ctx.upload(rng.integers(0, P, cells, dtype=np.uint32))
+    work = ctx.alloc(cells)
+    ptrs, off = [], 0
+    for t in trees:
+        tp = []
+        for l in t:
+            tp.append(work.ptr + 4 * off)
+            off += 1 << l
+        ptrs.append(tp)
+    gkr_entries = sum(1 << l for v in gkr.values() for l in v)
+    dens = ctx.upload(rng.integers(1, P, 4 * gkr_entries, dtype=np.uint32))
+    batches, off = [], 0
+    for fam, ls in gkr.items():
+        inst = []
+        for l in sorted(ls, reverse=True):
+            inst.append((z.GKR_LOGUP_SINGLES, 0, dens.ptr + 16 * off, 1 << l))
+            off += 1 << l
+        batches.append((fam, inst))
+    sampler = ClockSampler(0)
+    t_pcs, t_gkr, phases = [], [], None
+    for it in range(args.warmup + args.steps):
+        if it == args.warmup:
+            sampler.start()
+        ctx.sync()
+        ctx.event_record(0)
+        ctx.d2d(work.ptr, pristine.ptr, cells * 4)
+        words, ph = ctx.pcs_prove_device(ptrs, logs, pow_bits=0, log_blowup=log_blowup, log_last_layer=0, n_queries=100,
+                                         cap=1 << 27, phases=True)
+        ctx.event_record(1)
+        gw = [ctx.gkr_prove_device(inst, 0x5EED0007 + i, cap=1 << 24) for i, (_f, inst) in enumerate(batches)]
+        ctx.event_record(2)
+        ctx.sync()
+        if it >= args.warmup:
+            t_pcs.append(ctx.event_elapsed_ms(0, 1))
+            t_gkr.append(ctx.event_elapsed_ms(1, 2))
+            phases = ph if phases is None else {k: phases[k] + ph[k] for k in ph}
+    clocks = sampler.stop()
+    ctx.profile_begin()
+    ctx.d2d(work.ptr, pristine.ptr, cells * 4)
+    ctx.pcs_prove_device(ptrs, logs, pow_bits=0, log_blowup=log_blowup, log_last_layer=0, n_queries=100, cap=1 << 27)
+    for i, (_f, inst) in enumerate(batches):
+        ctx.gkr_prove_device(inst, 0x5EED0007 + i, cap=1 << 24)
+    kernels = ctx.profile_end(cap=128)
+    pcs_ms, gkr_ms = float(np.mean(t_pcs)), float(np.mean(t_gkr))
+    ms = pcs_ms + gkr_ms
+    top = sorted(kernels.items(), key=lambda kv: -kv[1][0])[:12]
+    print(json.dumps({
+        "metric": "segment_proof_ms (operator-trace replay)", "value": ms, "unit": "ms", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+        "dtype": "u32 (M31/QM31)", "data": "synthetic",
+        "config": {"workload": f"segment_replay_{args.segment}", "note": seg["note"], "columns": len(logs),
+                   "tree_columns": [len(t) for t in trees], "log_rows": [min(logs), max(logs)], "log_blowup": log_blowup,
+                   "n_queries": 100, "gkr_batches": {f: len(i) for f, i in batches}, "gkr_entries": gkr_entries,
+                   "l2": "inputs larger than L2"},
+        "cells": cells, "cells_per_s": cells / (ms * 1e-3), "pcs_ms": pcs_ms, "gkr_ms": gkr_ms,
+        "per_phase_ms": {k: v / args.steps for k, v in phases.items()}, "pcs_proof_words": int(words.size),
+        "gkr_proof_words": int(sum(w.size for w in gw)), "clocks": clocks,
+        "gpu_launches": int(sum(v[1] for v in kernels.values())) * args.steps,
+        "launches_one_step": int(sum(v[1] for v in kernels.values())),
+        "top_kernels_one_step": {k: {"ms": round(v[0], 3), "launches": v[1]} for k, v in top}}))
+    ctx.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -820,7 +920,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gpu-baseline", action="store_true")
     ap.add_argument("--gkr-log", type=int, default=24)
-    ap.add_argument("--mode", default="proof", choices=["proof", "sharded-commit", "gkr", "freivalds", "constraints", "stark"],
+    ap.add_argument("--segment", default="layer_8b_s32_c2048", help="segment-replay: a key of tests/golden/segment_shapes.json")
+    ap.add_argument("--mode", default="proof", choices=["proof", "sharded-commit", "gkr", "freivalds", "constraints", "stark", "segment-replay"],
                     help="proof: one whole PCS proof per rank (ranks are independent); sharded-commit: one commitment over all ranks")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -838,6 +939,8 @@ def main():
         run_constraints(args, rank)
     elif args.mode == "stark":
         run_stark(args, rank)
+    elif args.mode == "segment-replay":
+        run_segment_replay(args, rank)
     else:
         run_ours(args, rank, world, local_rank)
 

@@ -268,6 +268,55 @@ int zkb_freivalds_acc(zkb_ctx* ctx, const uint32_t* const* base_cols, const uint
                       uint32_t pk, uint32_t n_mats, const uint32_t h_s[4], const uint32_t h_rv[4], uint32_t* const* out_cols,
                       uint32_t* h_claims);
 
+/* ---- Witness generation of two more column families, in committed order --------------------------
+ * Both write row j of the natural (coset) order at index coset_perm(j) (prover/src/common.rs:76-80), so no
+ * trace column is shuffled, packed or uploaded by the host. All pointers are device pointers unless named h_*;
+ * counters / base_cols / pre_cols are host arrays of device pointers. Nothing is synchronised: results are
+ * ordered on the context's stream. */
+
+/* The shared lookup tables' own columns (device original zk_witness_gen_tables, stwo_cuda/cuda/
+ * zk_table_witness_gen.cu:124-146, called from prover/src/devtab.rs:267): for every committed row i with
+ * d = coset_perm(i): x_col[i] = d; y_col[i] = expmap[pattern(d)] where pattern(d) is d itself when bf16x is
+ * non-zero and otherwise the bf16 bits (round to nearest even) of -d / two_pow, which is exp_int_table
+ * (prover/src/bf16.rs:374) read through the 2^16-entry map of bf16 patterns to numerators; m_col[i] (skipped when
+ * m_col is NULL) = the sum over the n_counters counter arrays of counters[c][d]. Then natural row patch_idx[t] of
+ * y takes patch_val[t] (the rows where a witness's own table differs from the closed form). 2^log_rows rows. */
+int zkb_witness_tables(zkb_ctx* ctx, const uint32_t* expmap, const uint32_t* const* counters, uint32_t n_counters, const uint32_t* patch_idx,
+                       const uint32_t* patch_val, uint32_t n_patch, uint32_t log_rows, int bf16x, double two_pow, uint32_t* x_col,
+                       uint32_t* y_col, uint32_t* m_col);
+
+/* Shape of one matmul dequantize component, as the prover's Map / MatLayout / Spec fix it (the reference passes
+ * the same numbers in ZkDequantWitnessGenCfg, stwo_cuda/cuda/zk_dequant_witness_gen.cuh:38-60, filled at
+ * prover/src/gadgets/dequant/device.rs:290-325). tokens * chunks = 2^log_rows and chunks * per_row = n_out. */
+typedef struct zkb_dequant_cfg {
+    uint32_t variant;   /* 0 = power-of-two scales (jx, jw), 1 = bf16 scale chain (sx, sw, mul2) */
+    uint32_t sticky;    /* the rounding mode keeps a sticky bit (round to nearest even) */
+    uint32_t kmax;      /* largest round-bit weight the normalisation table carries */
+    uint32_t do_ref;    /* also run the double-precision cross-check and count its disagreements */
+    uint32_t tokens, n_out, per_row, chunks, log_rows;
+    uint32_t slot0, per_slot; /* column of slot s, field f: slot0 + s * per_slot + f */
+    uint32_t chan_w;    /* preprocessed scale columns per slot: 1 (variant 0) or 2 (variant 1) */
+    uint32_t f_acc, f_sg, f_m2, f_ph, f_st, f_r, f_m7, f_ef, f_nz, f_eo;
+    uint32_t f_mul[6];  /* variant 1: (product mantissa, carry, exponent) of the two chain steps */
+    uint32_t sh0, sh1;  /* the per-row shared columns (activation scale) */
+    uint32_t n_norm, n_frac, n_mul, n_r8; /* table lengths (bounds of the multiplicity arrays) */
+} zkb_dequant_cfg;
+
+/* One dequantize component (device original zk_witness_gen_dequant, stwo_cuda/cuda/zk_dequant_witness_gen.cu:190-386;
+ * the per-row arithmetic is witness_gen_mat_row, prover/src/gadgets/dequant/trace.rs:503-690): from the int32
+ * accumulators acc[tokens][n_out], the scales (jx[tokens], jw[n_out] or (mantissa, exponent) pairs sx, sw), the
+ * normalisation table norm3 (m7, exponent field, non-zero flag per row) and the mantissa product table mul2
+ * (m7, carry per row) writes every committed column (base_cols, n_base) and every preprocessed column (pre_cols,
+ * n_pre = chan_w * per_row + 5: the per-channel scales, then the selectors not-first, last, j>0 and not last,
+ * j>0 and last, j+1 == rows), adds the table multiplicities to m_norm, m_frac, m_mul and m_r8 (zeroed by the
+ * caller) and counts into counts[3]: range look-ups outside the 8-bit table, cross-check disagreements, and slots
+ * the tables cannot describe (those slots' remaining columns are left unwritten, as in the reference). want_out
+ * (NULL or rows * per_row words) receives the cross-check's bf16 pattern per (natural row, slot). */
+int zkb_witness_dequant(zkb_ctx* ctx, const int32_t* acc, const int32_t* jx, const int32_t* jw, const uint32_t* sx, const uint32_t* sw,
+                        const uint32_t* norm3, const uint32_t* mul2, uint32_t* const* base_cols, uint32_t n_base, uint32_t* const* pre_cols,
+                        uint32_t n_pre, uint32_t* m_norm, uint32_t* m_frac, uint32_t* m_mul, uint32_t* m_r8, uint32_t* counts,
+                        uint32_t* want_out, const zkb_dequant_cfg* cfg);
+
 #ifdef __cplusplus
 }
 #endif

@@ -440,6 +440,43 @@ def freivalds_acc(base, pre, n_mats, grid, pq, pk, s4, rv4):
     return np.stack(out), claims
 
 
+# ---- witness generation: tables, dequantize (oracle/witness.hpp)
+DEQUANT_CFG_FIELDS = ("variant", "sticky", "kmax", "do_ref", "tokens", "n_out", "per_row", "chunks", "log_rows", "slot0", "per_slot", "chan_w",
+                      "f_acc", "f_sg", "f_m2", "f_ph", "f_st", "f_r", "f_m7", "f_ef", "f_nz", "f_eo", "f_mul0", "f_mul1", "f_mul2", "f_mul3",
+                      "f_mul4", "f_mul5", "sh0", "sh1", "n_norm", "n_frac", "n_mul", "n_r8")
+
+
+def witness_tables(expmap, counters, log_rows, bf16x, two_pow, patch_idx=(), patch_val=()):
+    """Returns (x, y, m) columns of 2^log_rows words in committed order."""
+    expmap = _u32(expmap)
+    counters = [_u32(c) for c in counters]
+    pi, pv = _u32(list(patch_idx)), _u32(list(patch_val))
+    rows = 1 << log_rows
+    x, y, m = (np.zeros(rows, np.uint32) for _ in range(3))
+    lib().zko_witness_tables(_p(expmap), _pp(counters), C.c_uint32(len(counters)), _p(pi), _p(pv), C.c_uint32(len(pi)), C.c_uint32(log_rows),
+                             C.c_int(int(bf16x)), C.c_double(two_pow), _p(x), _p(y), _p(m))
+    return x, y, m
+
+
+def witness_dequant(acc, jx, jw, sx, sw, norm3, mul2, n_base, n_pre, cfg):
+    """cfg: dict over DEQUANT_CFG_FIELDS. Returns dict(base [n_base, rows], pre [n_pre, rows], m_norm, m_frac, m_mul, m_r8, counts [3],
+    want [rows * per_row]); columns in committed order."""
+    c34 = _u32([cfg[k] for k in DEQUANT_CFG_FIELDS])
+    rows = 1 << cfg["log_rows"]
+    acc = np.ascontiguousarray(acc, np.int32)
+    jx, jw = np.ascontiguousarray(jx, np.int32), np.ascontiguousarray(jw, np.int32)
+    sx, sw, norm3, mul2 = _u32(sx), _u32(sw), _u32(norm3), _u32(mul2)
+    base = [np.zeros(rows, np.uint32) for _ in range(n_base)]
+    pre = [np.zeros(rows, np.uint32) for _ in range(n_pre)]
+    m_norm, m_frac = np.zeros(cfg["n_norm"], np.uint32), np.zeros(cfg["n_frac"], np.uint32)
+    m_mul, m_r8 = np.zeros(max(1, cfg["n_mul"]), np.uint32), np.zeros(cfg["n_r8"], np.uint32)
+    counts, want = np.zeros(3, np.uint32), np.zeros(rows * cfg["per_row"], np.uint32)
+    lib().zko_witness_dequant(_p(acc), _p(jx), _p(jw), _p(sx), _p(sw), _p(norm3), _p(mul2), _pp(base), C.c_uint32(n_base), _pp(pre),
+                              C.c_uint32(n_pre), _p(m_norm), _p(m_frac), _p(m_mul), _p(m_r8), _p(counts), _p(want), _p(c34))
+    return {"base": np.stack(base), "pre": np.stack(pre), "m_norm": m_norm, "m_frac": m_frac, "m_mul": m_mul[:cfg["n_mul"]], "m_r8": m_r8,
+            "counts": counts, "want": want}
+
+
 # ---- constraint quotients of an AIR (oracle/air.hpp)
 def offset_bit_reversed_circle_domain_index(i, domain_log, eval_log, offset):
     f = lib().zko_offset_bit_reversed_circle_domain_index

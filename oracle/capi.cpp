@@ -423,6 +423,43 @@ void zko_freivalds_acc(const uint32_t* const* base, const uint32_t* const* pre, 
 
 }  // extern "C"
 
+// ---------------------------------------------------------------- witness generation: tables, dequantize
+#include "witness.hpp"
+extern "C" {
+
+void zko_witness_tables(const uint32_t* expmap, const uint32_t* const* counters, uint32_t n_counters, const uint32_t* patch_idx,
+                        const uint32_t* patch_val, uint32_t n_patch, uint32_t log_rows, int bf16x, double two_pow, uint32_t* x, uint32_t* y,
+                        uint32_t* m) {
+    std::vector<const uint32_t*> cn(counters, counters + n_counters);
+    TableColumns t = witness_tables(expmap, cn, patch_idx, patch_val, n_patch, log_rows, bf16x != 0, two_pow);
+    size_t rows = (size_t)1 << log_rows;
+    std::memcpy(x, t.x.data(), rows * 4);
+    std::memcpy(y, t.y.data(), rows * 4);
+    std::memcpy(m, t.m.data(), rows * 4);
+}
+
+// cfg34: the 34 words of DequantCfg in declaration order. want: rows * per_row words.
+void zko_witness_dequant(const int32_t* acc, const int32_t* jx, const int32_t* jw, const uint32_t* sx, const uint32_t* sw, const uint32_t* norm3,
+                         const uint32_t* mul2, uint32_t* const* base_out, uint32_t n_base, uint32_t* const* pre_out, uint32_t n_pre,
+                         uint32_t* m_norm, uint32_t* m_frac, uint32_t* m_mul, uint32_t* m_r8, uint32_t* counts, uint32_t* want,
+                         const uint32_t* cfg34) {
+    static_assert(sizeof(DequantCfg) == 34 * 4, "DequantCfg layout");
+    DequantCfg c;
+    std::memcpy(&c, cfg34, sizeof c);
+    DequantOut o = witness_dequant(acc, jx, jw, sx, sw, norm3, mul2, n_base, n_pre, c);
+    size_t rows = (size_t)1 << c.log_rows;
+    for (uint32_t k = 0; k < n_base; k++) std::memcpy(base_out[k], o.base[k].data(), rows * 4);
+    for (uint32_t k = 0; k < n_pre; k++) std::memcpy(pre_out[k], o.pre[k].data(), rows * 4);
+    std::memcpy(m_norm, o.m_norm.data(), o.m_norm.size() * 4);
+    std::memcpy(m_frac, o.m_frac.data(), o.m_frac.size() * 4);
+    if (m_mul) std::memcpy(m_mul, o.m_mul.data(), o.m_mul.size() * 4);
+    std::memcpy(m_r8, o.m_r8.data(), o.m_r8.size() * 4);
+    std::memcpy(counts, o.counts, 12);
+    std::memcpy(want, o.want.data(), o.want.size() * 4);
+}
+
+}  // extern "C"
+
 // ---------------------------------------------------------------- constraint quotients of an AIR
 #include "air.hpp"
 extern "C" {

@@ -415,6 +415,72 @@ class RefCudaFreivalds(RefCudaMore):
         return out, last[1 + n_mats:1 + 2 * n_mats]
 
 
+class _ZkTabCfg(C.Structure):  # stwo_cuda/cuda/zk_table_witness_gen.cuh:57-68
+    _fields_ = [("log_rows", C.c_uint32), ("rows", C.c_uint32), ("variant", C.c_uint32), ("n_counters", C.c_uint32), ("two_pow", C.c_double),
+                ("mutate", C.c_uint32), ("mut_col", C.c_uint32)]
+
+
+_DEQ_FIELDS = ("variant", "sticky", "kmax", "do_ref", "tokens", "n_out", "per_row", "chunks", "log_rows", "slot0", "per_slot", "chan_w",
+               "f_acc", "f_sg", "f_m2", "f_ph", "f_st", "f_r", "f_m7", "f_ef", "f_nz", "f_eo", "f_mul0", "f_mul1", "f_mul2", "f_mul3",
+               "f_mul4", "f_mul5", "sh0", "sh1", "n_norm", "n_frac", "n_mul", "n_r8")
+
+
+class _ZkDequantCfg(C.Structure):  # stwo_cuda/cuda/zk_dequant_witness_gen.cuh:38-60 (f_mul[6] as six fields)
+    _fields_ = [(n, C.c_uint32) for n in _DEQ_FIELDS + ("mutate",)]
+
+
+class RefCudaWitness(RefCudaMore):
+    """The reference's device witness generation for the tables' own columns (prover/src/devtab.rs:240-290) and for one
+    dequantize component (prover/src/gadgets/dequant/device.rs:199-360), driven as those call sites do, with no defect
+    selected (mutate = 0)."""
+
+    def __init__(self):
+        super().__init__()
+        L, vp, u32 = self.lib, C.c_void_p, C.c_uint32
+        L.zk_witness_gen_tables.restype = None
+        L.zk_witness_gen_tables.argtypes = [vp, vp, vp, vp, u32, vp, vp, vp, _ZkTabCfg]
+        L.zk_witness_gen_dequant.restype = None
+        L.zk_witness_gen_dequant.argtypes = [vp] * 8 + [u32, vp, u32] + [vp] * 6 + [_ZkDequantCfg]
+
+    def upload_any(self, arr):
+        return self.upload(np.ascontiguousarray(arr).view(np.uint32).reshape(-1))
+
+    def tables(self, expmap, counters, log_rows, bf16x, two_pow, patch_idx, patch_val):
+        rows = 1 << log_rows
+        d_map = self.upload(expmap)
+        d_cnt = [self.upload(c) for c in counters]
+        x, y, m = self.alloc(rows), self.alloc(rows), self.alloc_zero(rows)
+        pi = self.upload(patch_idx) if len(patch_idx) else None
+        pv = self.upload(patch_val) if len(patch_idx) else None
+        cfg = _ZkTabCfg(log_rows, rows, 0 if bf16x else 1, len(counters), two_pow, 0, 0)
+        self.lib.zk_witness_gen_tables(d_map, _ptrs(d_cnt) if d_cnt else None, pi, pv, len(patch_idx), x, y, m if counters else None, cfg)
+        out = self.download(x, rows), self.download(y, rows), self.download(m, rows)
+        for p in [d_map, x, y, m] + d_cnt + ([pi, pv] if pi else []):
+            self.free(p)
+        return out
+
+    def dequant(self, case):
+        cfg, rows = case["cfg"], case["rows"]
+        chain = cfg["variant"] == 1
+        d = {k: self.upload_any(case[k]) for k in ("acc", "jx", "jw", "sx", "sw", "norm3", "mul2")}
+        base = [self.alloc_zero(rows) for _ in range(case["n_base"])]
+        pre = [self.alloc_zero(rows) for _ in range(case["n_pre"])]
+        m_norm, m_frac = self.alloc_zero(cfg["n_norm"]), self.alloc_zero(cfg["n_frac"])
+        m_mul, m_r8, counts = self.alloc_zero(cfg["n_mul"]), self.alloc_zero(cfg["n_r8"]), self.alloc_zero(3)
+        want = self.alloc_zero(rows * cfg["per_row"])
+        c = _ZkDequantCfg(*([int(cfg[k]) for k in _DEQ_FIELDS] + [0]))
+        self.lib.zk_witness_gen_dequant(d["acc"], None if chain else d["jx"], None if chain else d["jw"], d["sx"] if chain else None,
+                                        d["sw"] if chain else None, d["norm3"], d["mul2"], _ptrs(base), len(base), _ptrs(pre), len(pre),
+                                        m_norm, m_frac, m_mul, m_r8, counts, want, c)
+        out = {"base": np.stack([self.download(b, rows) for b in base]), "pre": np.stack([self.download(p_, rows) for p_ in pre]),
+               "m_norm": self.download(m_norm, cfg["n_norm"]), "m_frac": self.download(m_frac, cfg["n_frac"]),
+               "m_mul": self.download(m_mul, cfg["n_mul"]), "m_r8": self.download(m_r8, cfg["n_r8"]), "counts": self.download(counts, 3),
+               "want": self.download(want, rows * cfg["per_row"])}
+        for p_ in list(d.values()) + base + pre + [m_norm, m_frac, m_mul, m_r8, counts, want]:
+            self.free(p_)
+        return out
+
+
 class RefCudaAir(RefCudaOps):
     """The reference's hand-written constraint kernel for the wide Fibonacci example AIR
     (stwo_cuda/cuda/evaluate_wide_fibonacci.cu:6-63, launcher :65-125; the AIR is

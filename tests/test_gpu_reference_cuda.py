@@ -290,3 +290,51 @@ def test_freivalds_component_matches_reference_cuda(ctx, oracle, tokens, n_in, n
     assert (claims == r_claims).all()
     for p in r_base + r_pre + r_out + [r_m, r_counts]:
         ref.free(p)
+
+
+@pytest.fixture(scope="module")
+def refwit():
+    from oracle import ref_cuda
+
+    if not ref_cuda.available():
+        pytest.skip("oracle/_ref/libstwo_cuda_ref.so is not built (the reference checkout is needed to build it)")
+    try:
+        return ref_cuda.RefCudaWitness()
+    except AttributeError:
+        pytest.skip("oracle/_ref/libstwo_cuda_ref.so predates the witness-generation kernels; rebuild it")
+
+
+@pytest.mark.parametrize("log_rows,n_counters,bf16x,n_patch", [(5, 1, False, 0), (11, 2, False, 1), (14, 3, True, 2), (20, 2, False, 1)])
+def test_witness_tables_match_reference_cuda(ctx, oracle, refwit, log_rows, n_counters, bf16x, n_patch):
+    """zk_witness_gen_tables (stwo_cuda/cuda/zk_table_witness_gen.cu) against zkb_witness_tables and the oracle."""
+    from test_witness_gen import _run_tables
+    from witness_cases import tables_case
+
+    expmap, counters, pi, pv = tables_case(300 + log_rows, log_rows, n_counters, n_patch)
+    two_pow = 2.0 ** 6
+    ref = refwit.tables(expmap, counters, log_rows, bf16x, two_pow, pi, pv)
+    got = _run_tables(ctx, expmap, counters, log_rows, bf16x, two_pow, pi, pv)
+    want = oracle.witness_tables(expmap, counters, log_rows, bf16x, two_pow, pi, pv)
+    for r, g, w, name in zip(ref, got, want, "xym"):
+        assert np.array_equal(r, g) and np.array_equal(r, w), name
+
+
+@pytest.mark.parametrize("variant,tokens,chunks,per_row,kmax,sticky,do_ref,wide", [
+    (0, 8, 4, 3, 16, 1, 1, False), (0, 32, 32, 16, 19, 1, 1, False), (0, 16, 16, 5, 12, 0, 0, True),
+    (1, 8, 4, 3, 16, 1, 1, False), (1, 64, 64, 16, 19, 1, 1, False), (1, 16, 8, 4, 10, 1, 1, True)])
+def test_witness_dequant_matches_reference_cuda(ctx, oracle, refwit, variant, tokens, chunks, per_row, kmax, sticky, do_ref, wide):
+    """zk_witness_gen_dequant (stwo_cuda/cuda/zk_dequant_witness_gen.cu) against zkb_witness_dequant and the oracle: every
+    committed and preprocessed cell, the four multiplicity arrays, the three counters and the cross-check patterns."""
+    from test_witness_gen import run_dequant
+    from witness_cases import dequant_case
+
+    case = dequant_case(2000 + tokens + per_row, variant, tokens, chunks, per_row, kmax, sticky, do_ref, wide)
+    ref = refwit.dequant(case)
+    got = run_dequant(ctx, case)
+    want = oracle.witness_dequant(case["acc"], case["jx"], case["jw"], case["sx"], case["sw"], case["norm3"], case["mul2"], case["n_base"],
+                                  case["n_pre"], case["cfg"])
+    if not do_ref:
+        want["want"][:] = 0
+    for k in ("counts", "m_norm", "m_frac", "m_mul", "m_r8", "pre", "base", "want"):
+        assert np.array_equal(ref[k], got[k]), k
+        assert np.array_equal(ref[k], want[k]), k

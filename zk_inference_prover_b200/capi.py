@@ -19,7 +19,7 @@ EXPORTED_SYMBOLS = [
     "zkb_merkle_layer", "zkb_merkle_leaves_partial", "zkb_merkle_top", "zkb_fold_line_dalpha", "zkb_fold_circle_into_line_dalpha", "zkb_channel_mix_root_draw", "zkb_fold_line_dalpha_leaves", "zkb_fold_circle_into_line_dalpha_leaves", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine",
     "zkb_accumulate", "zkb_lift_accumulate", "zkb_secure_powers", "zkb_gkr_eq_evals", "zkb_gkr_next_layer",
     "zkb_gkr_sum", "zkb_gkr_fix_and_sum", "zkb_mle_fix_qm31", "zkb_mle_fix_m31", "zkb_grind", "zkb_gkr_sum_noalloc", "zkb_gkr_sum_noalloc_error",
-    "zkb_freivalds_scatter", "zkb_freivalds_acc",
+    "zkb_freivalds_scatter", "zkb_freivalds_acc", "zkb_witness_tables", "zkb_witness_dequant",
 ]
 # Every symbol include/zkb200_prover.h declares.
 PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_stark_prove_device", "zkb_stark_prove_host", "zkb_stark_prove_multi_device", "zkb_stark_prove_multi_host", "zkb_gkr_prove_device"]
@@ -30,6 +30,16 @@ PCS_PHASES = ["interpolate", "extend", "merkle", "sample", "quotients", "fri_com
 
 class Grid(C.Structure):
     _fields_ = [("log_rows", C.c_uint32), ("groups", C.c_uint32), ("chunks", C.c_uint32), ("lead", C.c_uint32)]
+
+
+DEQUANT_CFG_FIELDS = ("variant", "sticky", "kmax", "do_ref", "tokens", "n_out", "per_row", "chunks", "log_rows", "slot0", "per_slot", "chan_w",
+                      "f_acc", "f_sg", "f_m2", "f_ph", "f_st", "f_r", "f_m7", "f_ef", "f_nz", "f_eo", "f_mul0", "f_mul1", "f_mul2", "f_mul3",
+                      "f_mul4", "f_mul5", "sh0", "sh1", "n_norm", "n_frac", "n_mul", "n_r8")
+
+
+class DequantCfg(C.Structure):
+    """zkb_dequant_cfg (f_mul[6] spelled as six fields)."""
+    _fields_ = [(k, C.c_uint32) for k in DEQUANT_CFG_FIELDS]
 
 
 class PcsConfig(C.Structure):
@@ -457,6 +467,23 @@ class Context:
                                                C.c_uint32(n_mats), s.ctypes.data_as(C.c_void_p), r.ctypes.data_as(C.c_void_p),
                                                _ptr_array(out_ptrs), claims.ctypes.data_as(C.c_void_p)))
         return claims
+
+    # ---- witness generation: the tables' own columns and the dequantize component
+    def witness_tables(self, expmap_ptr, counter_ptrs, log_rows, bf16x, two_pow, x_ptr, y_ptr, m_ptr, patch_idx_ptr=0, patch_val_ptr=0, n_patch=0):
+        self._check(self.lib.zkb_witness_tables(self.h, C.c_void_p(expmap_ptr), _ptr_array(counter_ptrs) if counter_ptrs else None,
+                                                C.c_uint32(len(counter_ptrs)), C.c_void_p(patch_idx_ptr or None), C.c_void_p(patch_val_ptr or None),
+                                                C.c_uint32(n_patch), C.c_uint32(log_rows), C.c_int(int(bf16x)), C.c_double(two_pow),
+                                                C.c_void_p(x_ptr), C.c_void_p(y_ptr), C.c_void_p(m_ptr or None)))
+
+    def witness_dequant(self, cfg, acc_ptr, jx_ptr, jw_ptr, sx_ptr, sw_ptr, norm3_ptr, mul2_ptr, base_ptrs, pre_ptrs, m_norm_ptr, m_frac_ptr,
+                        m_mul_ptr, m_r8_ptr, counts_ptr, want_ptr=0):
+        """cfg: dict over DEQUANT_CFG_FIELDS."""
+        c = DequantCfg(*[int(cfg[k]) for k in DEQUANT_CFG_FIELDS])
+        vp = lambda p: C.c_void_p(p or None)
+        self._check(self.lib.zkb_witness_dequant(self.h, vp(acc_ptr), vp(jx_ptr), vp(jw_ptr), vp(sx_ptr), vp(sw_ptr), vp(norm3_ptr), vp(mul2_ptr),
+                                                 _ptr_array(base_ptrs), C.c_uint32(len(base_ptrs)), _ptr_array(pre_ptrs),
+                                                 C.c_uint32(len(pre_ptrs)), vp(m_norm_ptr), vp(m_frac_ptr), vp(m_mul_ptr), vp(m_r8_ptr),
+                                                 vp(counts_ptr), vp(want_ptr), C.byref(c)))
 
     # ---- constraint quotients of a lowered AIR (include/zkb200_air.h)
     def air_compile(self, source):
