@@ -811,7 +811,7 @@ def run_segment_replay(args, rank):
     A segment of the reference prover is one STARK over hundreds of components of different heights (tens of thousands of
     columns of 2^4..2^23 rows) plus five batched LogUp-GKR reductions. tests/golden/segment_shapes.json holds those shapes,
     made from the reference's cell-exact cost model by tests/golden/make_segment_shapes.py. One step here: copy the trace in
-    (device to device), commit the base, interaction and boundary trees, prove one opening per column with the prover's own
+    (device to device), commit the base, interaction and boundary trees and eight composition columns, prove one opening per column with the prover's own
     PcsConfig (blow-up 2, 100 queries, no proof of work), then one GKR batch proof per reduction family over LogUpSingles
     instances of the components' lookup counts (a component of L lookups per row is split along the binary decomposition of
     L, as the reference does). Timing only: the witness values, the gadgets' constraint programs and the digest of a real
@@ -836,14 +836,18 @@ def run_segment_replay(args, rank):
                 b += 1
     for b in seg["boundary_cols"]:
         trees[2] += [b["log_rows"]] * b["cols"]
-    logs = [l for t in trees for l in t]
-    cells = sum(1 << l for l in logs)
+    cells = sum(1 << l for t in trees for l in t)
     assert cells == seg["cells"]["fresh"]
+    # the composition polynomial's eight half-coordinate columns at the height of the tallest trace: the last tree of a proof,
+    # to whose height every column is lifted. Not counted in the committed trace cells.
+    trees.append([max(l for t in trees for l in t)] * 8)
+    logs = [l for t in trees for l in t]
+    total_words = sum(1 << l for l in logs)
     log_blowup = 1
     ctx = z.Context(device=0, max_log_size=max(logs) + log_blowup)
     rng = np.random.default_rng(0x5EED0006)
-    pristine = ctx.upload(rng.integers(0, P, cells, dtype=np.uint32))
-    work = ctx.alloc(cells)
+    pristine = ctx.upload(rng.integers(0, P, total_words, dtype=np.uint32))
+    work = ctx.alloc(total_words)
     ptrs, off = [], 0
     for t in trees:
         tp = []
@@ -867,7 +871,7 @@ def run_segment_replay(args, rank):
             sampler.start()
         ctx.sync()
         ctx.event_record(0)
-        ctx.d2d(work.ptr, pristine.ptr, cells * 4)
+        ctx.d2d(work.ptr, pristine.ptr, total_words * 4)
         words, ph = ctx.pcs_prove_device(ptrs, logs, pow_bits=0, log_blowup=log_blowup, log_last_layer=0, n_queries=100,
                                          cap=1 << 27, phases=True)
         ctx.event_record(1)
@@ -880,7 +884,7 @@ def run_segment_replay(args, rank):
             phases = ph if phases is None else {k: phases[k] + ph[k] for k in ph}
     clocks = sampler.stop()
     ctx.profile_begin()
-    ctx.d2d(work.ptr, pristine.ptr, cells * 4)
+    ctx.d2d(work.ptr, pristine.ptr, total_words * 4)
     ctx.pcs_prove_device(ptrs, logs, pow_bits=0, log_blowup=log_blowup, log_last_layer=0, n_queries=100, cap=1 << 27)
     for i, (_f, inst) in enumerate(batches):
         ctx.gkr_prove_device(inst, 0x5EED0007 + i, cap=1 << 24)

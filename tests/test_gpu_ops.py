@@ -181,7 +181,9 @@ def test_fold_circle_into_line(ctx, oracle, log_n):
 
 
 # ------------------------------------------------------------------ quotients (A9, A10, A11)
-@pytest.mark.parametrize("log_n,ncols,k", [(1, 1, 1), (3, 4, 4), (5, 7, 7), (8, 20, 13), (10, 33, 50), (12, 5, 0)])
+@pytest.mark.parametrize("log_n,ncols,k", [(1, 1, 1), (3, 4, 4), (5, 7, 7), (8, 20, 13), (10, 33, 50), (12, 5, 0),
+                                           # short and wide: the columns are split over the grid (partial sums, then one addition pass)
+                                           (1, 40, 1500), (5, 300, 1100), (9, 1400, 1400), (12, 64, 2049)])
 def test_quot_numerators(ctx, oracle, log_n, ncols, k):
     n = 1 << log_n
     cols = [edge_m31_column(900 + c, n) for c in range(ncols)]

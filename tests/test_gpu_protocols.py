@@ -47,6 +47,14 @@ def test_pcs_device_columns_and_phases(ctx, oracle):
     assert all(v >= 0 for v in phases.values()) and phases["merkle"] > 0
 
 
+def test_pcs_rejects_a_last_tree_that_is_not_the_tallest(ctx, zkb):
+    """Every column is lifted to the height of the last tree (nitroo/crates/stwo/src/prover/pcs/mod.rs:180, :232): a taller
+    column in an earlier tree is refused (the reference's subtraction would overflow and panic)."""
+    trees = _trees([[7, 5], [6]], 4200)
+    with pytest.raises(zkb.ZkbError):
+        ctx.pcs_prove_host(trees, pow_bits=0, log_blowup=1, n_queries=3)
+
+
 def test_pcs_rejects_too_large_domain(ctx, zkb):
     with pytest.raises(zkb.ZkbError):
         ctx.pcs_prove_host([[np.zeros(1 << 10, np.uint32)]], log_blowup=16)
@@ -69,6 +77,9 @@ def _instance(kind, log_n, seed):
         [(2, 10), (3, 7), (0, 8), (1, 3)],      # mixed kinds and sizes in one batch
         [(3, 12), (3, 12), (2, 12)],
         [(2, 16)],
+        # more than 16 instances: the batch path, one launch per sum-check round for all instances (csrc/gkr_batch.cu)
+        [(3, 9)] * 6 + [(3, 7)] * 5 + [(1, 8)] * 3 + [(2, 6), (0, 5), (3, 2), (2, 2), (1, 1), (3, 1), (0, 2), (0, 1)],
+        [(3, 13)] * 20 + [(3, 11)] * 12 + [(2, 12), (1, 10)],
     ],
 )
 def test_gkr_proof_matches_oracle(ctx, oracle, spec):

@@ -3,6 +3,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "gather_blocks.hpp"
 
 namespace zk {
 
@@ -437,3 +438,40 @@ int zkb_secure_powers(zkb_ctx* ctx, const uint32_t h_felt[4], size_t n, uint32_t
 }
 
 }  // extern "C"
+
+namespace zk {
+
+int gather_blocks(zkb_ctx* ctx, const GatherBlock* blocks, int n_blocks, size_t total_words, uint32_t* h_out) {
+    if (n_blocks <= 0 || total_words == 0) return ZKB_OK;
+    DeviceGuard g(ctx);
+    std::vector<uint32_t> idx;
+    for (int b = 0; b < n_blocks; b++) idx.insert(idx.end(), blocks[b].idx, blocks[b].idx + blocks[b].nidx);
+    uint32_t* d_buf = nullptr;  // [indices | results]
+    ZKB_CUDA(ctx, cudaMallocAsync((void**)&d_buf, (idx.size() + total_words) * 4, ctx->stream));
+    cudaError_t e = cudaMemcpyAsync(d_buf, idx.data(), idx.size() * 4, cudaMemcpyHostToDevice, ctx->stream);
+    uint32_t* d_out = d_buf + idx.size();
+    size_t ioff = 0;
+    int rc = ZKB_OK;
+    for (int b = 0; b < n_blocks && e == cudaSuccess && rc == ZKB_OK; b++) {
+        const GatherBlock& blk = blocks[b];
+        size_t total = (size_t)blk.ncols * blk.nidx;
+        if (total) {
+            void** d_cols;
+            rc = stage_ptrs(ctx, (const void* const*)blk.cols, blk.ncols, &d_cols);
+            if (rc == ZKB_OK) {
+                gather_multi_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>((const uint32_t* const*)d_cols, blk.ncols,
+                                                                                              d_buf + ioff, blk.nidx, d_out + blk.out_off);
+                e = cudaGetLastError();
+            }
+        }
+        ioff += blk.nidx;
+    }
+    if (e == cudaSuccess && rc == ZKB_OK) e = cudaMemcpyAsync(h_out, d_out, total_words * 4, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess && rc == ZKB_OK) e = cudaStreamSynchronize(ctx->stream);
+    cudaFreeAsync(d_buf, ctx->stream);
+    if (rc != ZKB_OK) return rc;
+    if (e != cudaSuccess) return set_error(ctx, ZKB_ECUDA, "gather_blocks: %s", cudaGetErrorString(e));
+    return ZKB_OK;
+}
+
+}  // namespace zk

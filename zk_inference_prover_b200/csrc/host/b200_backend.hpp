@@ -185,16 +185,21 @@ struct B200Backend {
         for (auto c : cols) p.push_back(c->ptr());
         d.check(zkb_ifft_cols(d.ctx(), p.data(), (int)p.size(), (int)cols[0]->log_size()));
     }
+    // With `slab`, the extended columns are views of ONE allocation that *slab then owns (a tree of tens of thousands of
+    // short columns would otherwise spend its time in the allocator).
     static std::vector<BaseColumn> evaluate_polynomials(const Device& d, const std::vector<const BaseColumn*>& coeffs,
-                                                        uint32_t log_blowup_factor) {
+                                                        uint32_t log_blowup_factor, BaseColumn* slab = nullptr) {
         std::vector<BaseColumn> out;
         if (coeffs.empty()) return out;
         uint32_t log_n = coeffs[0]->log_size(), log_out = log_n + log_blowup_factor;
         std::vector<const uint32_t*> src;
         std::vector<uint32_t*> dst;
-        for (auto c : coeffs) {
-            out.emplace_back(d, (size_t)1 << log_out);
-            src.push_back(c->ptr());
+        if (slab && coeffs.size() > 1 && log_out >= 2) *slab = BaseColumn(d, coeffs.size() << log_out);
+        else slab = nullptr;
+        for (size_t i = 0; i < coeffs.size(); i++) {
+            if (slab) out.push_back(BaseColumn::view(d, slab->ptr() + (i << log_out), (size_t)1 << log_out));
+            else out.emplace_back(d, (size_t)1 << log_out);
+            src.push_back(coeffs[i]->ptr());
         }
         for (auto& o : out) dst.push_back(o.ptr());
         d.check(zkb_lde_cols(d.ctx(), src.data(), (int)src.size(), (int)log_n, dst.data(), (int)log_out));

@@ -13,6 +13,8 @@
 #include "../air_program.hpp"
 #include "b200_backend.hpp"
 #include "../gkr_resident.hpp"
+#include "../gkr_batch.hpp"
+#include "../gather_blocks.hpp"
 #include "channel.hpp"
 
 // Records a message on the context (defined with the context, ctx.cu).
@@ -45,9 +47,30 @@ struct GatherPlan {
     std::vector<uint32_t> words;
     size_t add(const uint32_t* p) { addrs.push_back(p); return addrs.size() - 1; }
     size_t add_hash(const uint32_t* p) { size_t s = addrs.size(); for (int k = 0; k < 8; k++) addrs.push_back(p + k); return s; }
+    // Rows of many columns at once (the queried and witness values of one tree layer): row-major [row][column] in
+    // block_words from the returned offset. One pointer per column and one index per row travel, not one address per word.
+    struct Block { std::vector<const uint32_t*> cols; std::vector<uint32_t> idx; size_t out_off; };
+    std::vector<Block> blocks;
+    std::vector<uint32_t> block_words;
+    size_t block_total = 0;
+    size_t add_block(const std::vector<const uint32_t*>& cols, const std::vector<size_t>& rows) {
+        Block b;
+        b.cols = cols;
+        for (auto r : rows) b.idx.push_back((uint32_t)r);
+        b.out_off = block_total;
+        block_total += cols.size() * rows.size();
+        blocks.push_back(std::move(b));
+        return blocks.back().out_off;
+    }
     void execute(const Device& d) {
         words.resize(addrs.size());
         d.check(zkb_gather_words(d.ctx(), addrs.data(), addrs.size(), words.data()));
+        if (block_total) {
+            block_words.resize(block_total);
+            std::vector<zk::GatherBlock> gb;
+            for (auto& b : blocks) gb.push_back({b.cols.data(), (int)b.cols.size(), b.idx.data(), (int)b.idx.size(), b.out_off});
+            d.check(zk::gather_blocks(d.ctx(), gb.data(), (int)gb.size(), block_total, block_words.data()));
+        }
     }
     Hash hash_at(size_t slot) const { Hash h; for (int k = 0; k < 8; k++) h[k] = words[slot + k]; return h; }
 };
@@ -55,12 +78,16 @@ struct GatherPlan {
 // ------------------------------------------------------------------ MerkleProver (STWO/prover/vcs/prover.rs:17-217)
 struct MerkleDecommitment { std::vector<Hash> hash_witness; std::vector<uint32_t> column_witness; };
 struct PendingMerkle {  // slots of a planned decommitment
-    std::vector<size_t> hash_slots, queried_slots, witness_slots;
+    std::vector<size_t> hash_slots;
+    struct Run { size_t off, count; bool queried; };  // `count` words of plan.block_words, in proof order
+    std::vector<Run> runs;
     std::pair<std::vector<uint32_t>, MerkleDecommitment> finish(const GatherPlan& plan) const {
         std::pair<std::vector<uint32_t>, MerkleDecommitment> r;
         for (auto s : hash_slots) r.second.hash_witness.push_back(plan.hash_at(s));
-        for (auto s : queried_slots) r.first.push_back(plan.words[s]);
-        for (auto s : witness_slots) r.second.column_witness.push_back(plan.words[s]);
+        for (auto& run : runs) {
+            auto& dst = run.queried ? r.first : r.second.column_witness;
+            dst.insert(dst.end(), plan.block_words.begin() + run.off, plan.block_words.begin() + run.off + run.count);
+        }
         return r;
     }
 };
@@ -130,10 +157,16 @@ struct MerkleProver {
                 (col_queries.count(node) ? queried_nodes : witness_nodes).push_back(node);
             }
             for (size_t child : witness_children) pm.hash_slots.push_back(plan.add_hash(layers[log + 1].ptr() + 8 * child));
-            for (size_t node : queried_nodes)
-                for (auto c : layer_cols) pm.queried_slots.push_back(plan.add(c->ptr() + node));
-            for (size_t node : witness_nodes)
-                for (auto c : layer_cols) pm.witness_slots.push_back(plan.add(c->ptr() + node));
+            if (!layer_cols.empty() && !merged_nodes.empty()) {
+                // every node of the layer is read once; the proof lists the queried nodes' values first, then the witnesses'
+                std::vector<const uint32_t*> ptrs;
+                for (auto c : layer_cols) ptrs.push_back(c->ptr());
+                std::vector<size_t> order(queried_nodes);
+                order.insert(order.end(), witness_nodes.begin(), witness_nodes.end());
+                size_t off = plan.add_block(ptrs, order);
+                if (!queried_nodes.empty()) pm.runs.push_back({off, queried_nodes.size() * ptrs.size(), true});
+                if (!witness_nodes.empty()) pm.runs.push_back({off + queried_nodes.size() * ptrs.size(), witness_nodes.size() * ptrs.size(), false});
+            }
             last = merged_nodes;
         }
         return pm;
@@ -367,6 +400,7 @@ struct CommitmentTreeProver {  // pcs/mod.rs:466-630
     std::vector<BaseColumn> coeffs;  // views of the caller's columns after interpolation
     BaseColumn coeff_slab;           // host path: the one allocation the coefficient columns are views of
     std::vector<BaseColumn> evals;
+    std::vector<BaseColumn> eval_slabs;  // device path: one allocation per column size, which the evals are views of
     MerkleProver commitment;
     uint32_t max_log() const { return (uint32_t)commitment.layers.size() - 1; }
 };
@@ -514,7 +548,8 @@ struct CommitmentSchemeProver {
             for (auto& g : by_log) {
                 std::vector<const BaseColumn*> cols;
                 for (auto i : g.second) cols.push_back(&columns[i]);
-                auto ev_cols = B200Backend::evaluate_polynomials(d, cols, config.fri.log_blowup_factor);
+                t.eval_slabs.emplace_back();
+                auto ev_cols = B200Backend::evaluate_polynomials(d, cols, config.fri.log_blowup_factor, &t.eval_slabs.back());
                 for (size_t k = 0; k < g.second.size(); k++) t.evals[g.second[k]] = std::move(ev_cols[k]);
             }
         }
@@ -600,10 +635,17 @@ struct CommitmentSchemeProver {
     PcsProof prove_values(const std::vector<std::vector<std::vector<CirclePointQ>>>& sampled_points, Channel& ch) {
         PcsProof proof;
         uint32_t lifting_log = trees.back().max_log();
+        // Every column is lifted to the height of the LAST tree (pcs/mod.rs:180: in a proof it is the composition tree, which
+        // is the tallest); a taller column in an earlier tree has no lift.
+        for (auto& t : trees)
+            if (!t.evals.empty() && t.max_log() > lifting_log)
+                throw Error(ZKB_EINVAL, "pcs: the last tree must hold the tallest column (every column is lifted to its height)");
         // batch out-of-domain evaluation: one call per (coefficient size, transformed point) group (:187-265)
         std::vector<std::vector<std::vector<PointSample>>> samples(trees.size());
         struct Group { uint32_t log; CirclePointQ pt; std::vector<std::array<size_t, 3>> where; std::vector<const BaseColumn*> cols; };
         std::vector<Group> groups;
+        struct Doubled { CirclePointQ p; uint32_t shift; CirclePointQ tp; };
+        std::vector<Doubled> doubled;
         for (size_t t = 0; t < trees.size(); t++) {
             samples[t].resize(trees[t].coeffs.size());
             for (size_t c = 0; c < trees[t].coeffs.size(); c++) {
@@ -611,7 +653,11 @@ struct CommitmentSchemeProver {
                 for (size_t k = 0; k < sampled_points[t][c].size(); k++) {
                     CirclePointQ p = sampled_points[t][c][k];
                     samples[t][c].push_back({p, qm31_zero()});
-                    CirclePointQ tp = point_repeated_double(p, lifting_log - poly_log);
+                    // most columns share the point and the shift: double once per distinct (point, shift)
+                    CirclePointQ tp;
+                    bool seen = false;
+                    for (auto& m : doubled) if (m.shift == lifting_log - poly_log && m.p == p) { tp = m.tp; seen = true; break; }
+                    if (!seen) { tp = point_repeated_double(p, lifting_log - poly_log); doubled.push_back({p, lifting_log - poly_log, tp}); }
                     Group* g = nullptr;
                     for (auto& x : groups) if (x.log == coeff_log && x.pt == tp) { g = &x; break; }
                     if (!g) { groups.push_back({coeff_log, tp, {}, {}}); g = &groups.back(); }
@@ -746,6 +792,8 @@ struct GkrOracle {  // GkrMultivariatePolyOracle, gkr_prover.rs:473-556
     qm31 eq_fixed_var_correction;
     bool have_sums = false;  // the next round's sums, produced together with the last fix
     std::pair<qm31, qm31> sums;
+    bool have_mask = false;  // the two entries of every column after the last fix, read back with that round's results
+    qm31 mask_den[2], mask_num[2];
     size_t n_variables() const { return input_layer.n_variables() - 1; }
 };
 
@@ -771,11 +819,49 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
     std::vector<size_t> n_layers_by_inst;
     for (auto& l : input_layers) n_layers_by_inst.push_back(l.n_variables());
     size_t n_layers = *std::max_element(n_layers_by_inst.begin(), n_layers_by_inst.end());
-    std::vector<std::vector<Layer>> towers(n_inst);  // gen_layers, :847-852
-    for (size_t i = 0; i < n_inst; i++) {
-        towers[i].push_back(std::move(input_layers[i]));
-        while (towers[i].back().n_variables() > 0) towers[i].push_back(B200Backend::next_layer(d, towers[i].back()));
+    std::vector<std::vector<Layer>> towers(n_inst);  // gen_layers, :847-852; one launch per level for the whole batch
+    for (size_t i = 0; i < n_inst; i++) towers[i].push_back(std::move(input_layers[i]));
+    std::vector<zk::GkrBatchItem> items;
+    auto item_of = [](const Layer& in, Layer& out, uint32_t mode) {
+        zk::GkrBatchItem it{};
+        it.num = in.num_ptr();
+        it.den = in.den.words.ptr();
+        it.num_out = out.kind == ZKB_GKR_LOGUP_GENERIC ? out.num.words.ptr() : nullptr;
+        it.den_out = out.den.words.ptr();
+        it.n = in.len();
+        it.kind = (uint32_t)in.kind;
+        it.mode = mode;
+        return it;
+    };
+    for (;;) {
+        items.clear();
+        for (size_t i = 0; i < n_inst; i++) {
+            const Layer& in = towers[i].back();
+            if (in.n_variables() == 0) continue;
+            Layer out;
+            out.kind = in.kind == ZKB_GKR_GRAND_PRODUCT ? ZKB_GKR_GRAND_PRODUCT : ZKB_GKR_LOGUP_GENERIC;
+            out.den = SecureMle(d, in.len() / 2);
+            if (out.kind == ZKB_GKR_LOGUP_GENERIC) out.num = SecureMle(d, in.len() / 2);
+            items.push_back(item_of(in, out, 3));
+            towers[i].push_back(std::move(out));
+        }
+        if (items.empty()) break;
+        d.check(zk::gkr_batch_next_layer(d.ctx(), items.data(), (int)items.size()));
     }
+    std::vector<uint32_t> results;
+    // the output layers (one entry per column) of all instances, read in one gather
+    GatherPlan top_plan;
+    std::vector<size_t> top_slot(n_inst, SIZE_MAX);
+    for (size_t i = 0; i < n_inst; i++) {
+        const Layer& t = towers[i].back();
+        if (t.len() != 1 || (t.kind != ZKB_GKR_GRAND_PRODUCT && t.kind != ZKB_GKR_LOGUP_GENERIC)) continue;
+        top_slot[i] = top_plan.addrs.size();
+        for (int w = 0; w < 4; w++) top_plan.add(t.den.words.ptr() + w);
+        if (t.kind == ZKB_GKR_LOGUP_GENERIC)
+            for (int w = 0; w < 4; w++) top_plan.add(t.num.words.ptr() + w);
+    }
+    if (!top_plan.addrs.empty()) top_plan.execute(d);
+    auto top_q = [&](size_t slot) { return qm31{{top_plan.words[slot], top_plan.words[slot + 1], top_plan.words[slot + 2], top_plan.words[slot + 3]}}; };
     std::vector<std::vector<UniPoly>> sumcheck_round_polys;
     std::vector<std::vector<std::vector<std::array<qm31, 2>>>> masks_by_inst(n_inst);
     std::vector<std::vector<qm31>> output_claims(n_inst), claims(n_inst);
@@ -789,9 +875,10 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
             if (n_layers_by_inst[i] == n_remaining) {
                 Layer out = take(i);  // output layer: one entry per column
                 std::vector<qm31> vals;
-                qm31 den0 = mle_to_cpu(d, out.den)[0];
+                const bool planned = top_slot[i] != SIZE_MAX;
+                qm31 den0 = planned ? top_q(top_slot[i]) : mle_to_cpu(d, out.den)[0];
                 if (out.kind == ZKB_GKR_GRAND_PRODUCT) vals = {den0};
-                else if (out.kind == ZKB_GKR_LOGUP_GENERIC) vals = {mle_to_cpu(d, out.num)[0], den0};
+                else if (out.kind == ZKB_GKR_LOGUP_GENERIC) vals = {planned ? top_q(top_slot[i] + 4) : mle_to_cpu(d, out.num)[0], den0};
                 else if (out.kind == ZKB_GKR_LOGUP_MULTIPLICITIES) vals = {qm31_from_m31(out.num_base.to_cpu()[0]), den0};
                 else vals = {qm31_one(), den0};
                 claims[i] = vals;
@@ -824,10 +911,34 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
         for (size_t round = 0; round < nv; round++) {
             size_t n_rem = nv - round;
             std::vector<UniPoly> this_round;
+            // the oracles that enter the sum-check in this round have no sums yet: one launch for all of them
+            items.clear();
+            std::vector<size_t> who;
+            for (size_t k = 0; k < oracles.size(); k++)
+                if (n_rem == oracles[k].n_variables() && !oracles[k].have_sums) {
+                    zk::GkrBatchItem it{};
+                    it.num = oracles[k].input_layer.num_ptr();
+                    it.den = oracles[k].input_layer.den.words.ptr();
+                    it.n = oracles[k].input_layer.len();
+                    it.kind = (uint32_t)oracles[k].input_layer.kind;
+                    it.mode = 0;
+                    items.push_back(it);
+                    who.push_back(k);
+                }
+            if (!items.empty()) {
+                results.resize(items.size() * zk::GKR_BATCH_RESULT_WORDS);
+                qm31 zero = qm31_zero();
+                d.check(zk::gkr_batch_round(d.ctx(), items.data(), (int)items.size(), zero.c, eq_evals.words.ptr(), lambda.c, results.data()));
+                for (size_t j = 0; j < who.size(); j++) {
+                    const uint32_t* w = results.data() + j * zk::GKR_BATCH_RESULT_WORDS;
+                    oracles[who[j]].sums = {qm31{{w[0], w[1], w[2], w[3]}}, qm31{{w[4], w[5], w[6], w[7]}}};
+                    oracles[who[j]].have_sums = true;
+                }
+            }
             for (size_t k = 0; k < oracles.size(); k++) {
                 UniPoly rp;
                 if (n_rem == oracles[k].n_variables()) {
-                    auto sums = oracles[k].have_sums ? oracles[k].sums : B200Backend::round_sums(d, oracles[k].input_layer, eq_evals, lambda);
+                    auto sums = oracles[k].sums;
                     oracles[k].have_sums = false;
                     rp = correct_sum_as_poly_in_first_variable(sums.first * oracles[k].eq_fixed_var_correction,
                                                                sums.second * oracles[k].eq_fixed_var_correction, sc_claims[k], ood_point,
@@ -847,19 +958,42 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
             ch.mix_felts(combined.c);
             qm31 challenge = ch.draw_secure_felt();
             for (size_t k = 0; k < oracles.size(); k++) sc_claims[k] = this_round[k].eval(challenge);
+            // fix the first variable of every active oracle (and take the next round's sums in the same pass): one launch
+            items.clear();
+            who.clear();
+            std::vector<Layer> fixed;
             for (size_t k = 0; k < oracles.size(); k++)
                 if (n_rem == oracles[k].n_variables() && oracles[k].n_variables() != 0) {
                     qm31 z0 = ood_point[ood_point.size() - oracles[k].n_variables()];
                     oracles[k].eq_fixed_var_correction = oracles[k].eq_fixed_var_correction * eq1(challenge, z0);
-                    if (oracles[k].input_layer.len() >= 8) {
-                        auto fs = B200Backend::fix_first_variable_and_sum(d, oracles[k].input_layer, challenge, eq_evals, lambda);
-                        oracles[k].input_layer = std::move(fs.first);
-                        oracles[k].sums = fs.second;
-                        oracles[k].have_sums = true;
-                    } else {
-                        oracles[k].input_layer = B200Backend::fix_first_variable(d, std::move(oracles[k].input_layer), challenge);
-                    }
+                    const Layer& in = oracles[k].input_layer;
+                    Layer out;  // Layer::fix_first_variable, gkr_prover.rs:354-381
+                    out.kind = in.kind == ZKB_GKR_LOGUP_MULTIPLICITIES ? ZKB_GKR_LOGUP_GENERIC : in.kind;
+                    out.den = SecureMle(d, in.len() / 2);
+                    if (out.kind == ZKB_GKR_LOGUP_GENERIC) out.num = SecureMle(d, in.len() / 2);
+                    items.push_back(item_of(in, out, in.len() >= 8 ? 1 : 2));
+                    fixed.push_back(std::move(out));
+                    who.push_back(k);
                 }
+            if (!items.empty()) {
+                results.resize(items.size() * zk::GKR_BATCH_RESULT_WORDS);
+                d.check(zk::gkr_batch_round(d.ctx(), items.data(), (int)items.size(), challenge.c, eq_evals.words.ptr(), lambda.c, results.data()));
+                for (size_t j = 0; j < who.size(); j++) {
+                    GkrOracle& o = oracles[who[j]];
+                    const uint32_t* w = results.data() + j * zk::GKR_BATCH_RESULT_WORDS;
+                    if (items[j].mode == 1) {
+                        o.sums = {qm31{{w[0], w[1], w[2], w[3]}}, qm31{{w[4], w[5], w[6], w[7]}}};
+                        o.have_sums = true;
+                    } else {
+                        for (int e = 0; e < 2; e++) {
+                            o.mask_den[e] = qm31{{w[8 + 4 * e], w[9 + 4 * e], w[10 + 4 * e], w[11 + 4 * e]}};
+                            o.mask_num[e] = qm31{{w[16 + 4 * e], w[17 + 4 * e], w[18 + 4 * e], w[19 + 4 * e]}};
+                        }
+                        o.have_mask = true;
+                    }
+                    o.input_layer = std::move(fixed[j]);
+                }
+            }
             round_polys.push_back(combined);
             assignment.push_back(challenge);
         }
@@ -868,9 +1002,12 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
         for (auto& o : oracles) {
             const Layer& l = o.input_layer;
             if (l.len() != 2) throw Error(ZKB_EINVAL, "gkr: oracle is not constant after sumcheck");
-            auto den = mle_to_cpu(d, l.den);
+            std::vector<qm31> den = o.have_mask ? std::vector<qm31>{o.mask_den[0], o.mask_den[1]} : mle_to_cpu(d, l.den);
             if (l.kind == ZKB_GKR_GRAND_PRODUCT) masks.push_back({{den[0], den[1]}});
-            else if (l.kind == ZKB_GKR_LOGUP_GENERIC) { auto num = mle_to_cpu(d, l.num); masks.push_back({{num[0], num[1]}, {den[0], den[1]}}); }
+            else if (l.kind == ZKB_GKR_LOGUP_GENERIC) {
+                std::vector<qm31> num = o.have_mask ? std::vector<qm31>{o.mask_num[0], o.mask_num[1]} : mle_to_cpu(d, l.num);
+                masks.push_back({{num[0], num[1]}, {den[0], den[1]}});
+            }
             else if (l.kind == ZKB_GKR_LOGUP_SINGLES) masks.push_back({{qm31_one(), qm31_one()}, {den[0], den[1]}});
             else throw Error(ZKB_EINVAL, "gkr: a multiplicities layer cannot be a mask");
         }

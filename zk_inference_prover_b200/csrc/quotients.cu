@@ -31,7 +31,13 @@ template <int R>
 __global__ void __launch_bounds__(256) quot_numerators_kernel(const uint32_t* const* __restrict__ cols,
                                                               const uint32_t* __restrict__ col_idx,
                                                               const uint4* __restrict__ coeff_c, int k, qm31 b_sum,
-                                                              size_t n, Secure4 out) {
+                                                              size_t n, Secure4 out, int chunk = 0,
+                                                              uint32_t* __restrict__ partial = nullptr) {
+    // With `partial`, CTA row blockIdx.y takes the columns [y * chunk, (y + 1) * chunk) and leaves its reduced sums in
+    // partial[(y * 4 + coordinate) * n + row]; quot_partial_sum_kernel adds the rows up. Short, wide groups (thousands of
+    // columns of a few hundred rows) would otherwise run on one or two CTAs.
+    const int k_begin = partial ? (int)blockIdx.y * chunk : 0;
+    const int k_end = partial ? (k_begin + chunk < k ? k_begin + chunk : k) : k;
     __shared__ const uint32_t* s_col[NUM_TILE];
     __shared__ uint4 s_c[NUM_TILE];
     const size_t row0 = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * R;
@@ -57,8 +63,8 @@ __global__ void __launch_bounds__(256) quot_numerators_kernel(const uint32_t* co
             acc[r][2] += (uint64_t)c.z * v[r]; acc[r][3] += (uint64_t)c.w * v[r];
         }
     };
-    for (int tile0 = 0; tile0 < k; tile0 += NUM_TILE) {
-        const int tk = k - tile0 < NUM_TILE ? k - tile0 : NUM_TILE;
+    for (int tile0 = k_begin; tile0 < k_end; tile0 += NUM_TILE) {
+        const int tk = k_end - tile0 < NUM_TILE ? k_end - tile0 : NUM_TILE;
         __syncthreads();
         if ((int)threadIdx.x < tk) {
             s_col[threadIdx.x] = cols[col_idx[tile0 + threadIdx.x]];
@@ -94,12 +100,32 @@ __global__ void __launch_bounds__(256) quot_numerators_kernel(const uint32_t* co
 #pragma unroll
     for (int r = 0; r < R; r++)
 #pragma unroll
-        for (int q = 0; q < 4; q++) res[r][q] = m31_sub(m31_reduce64(acc[r][q]), b_sum.c[q]);
+        for (int q = 0; q < 4; q++) res[r][q] = partial ? m31_reduce64(acc[r][q]) : m31_sub(m31_reduce64(acc[r][q]), b_sum.c[q]);
+    if (partial) {
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            uint32_t* dst = partial + ((size_t)blockIdx.y * 4 + q) * n + row0;
+            if constexpr (R == 4) *reinterpret_cast<uint4*>(dst) = make_uint4(res[0][q], res[1][q], res[2][q], res[3][q]);
+            else *reinterpret_cast<uint2*>(dst) = make_uint2(res[0][q], res[1][q]);
+        }
+        return;
+    }
 #pragma unroll
     for (int q = 0; q < 4; q++) {
         if constexpr (R == 4) *reinterpret_cast<uint4*>(out.c[q] + row0) = make_uint4(res[0][q], res[1][q], res[2][q], res[3][q]);
         else *reinterpret_cast<uint2*>(out.c[q] + row0) = make_uint2(res[0][q], res[1][q]);
     }
+}
+
+// out[q][row] = sum over the S column chunks of partial[(s * 4 + q) * n + row], minus b_sum.
+__global__ void __launch_bounds__(256) quot_partial_sum_kernel(const uint32_t* __restrict__ partial, int S, size_t n, qm31 b_sum, Secure4 out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;  // over 4 * n (coordinate-major)
+    if (i >= 4 * n) return;
+    const int q = (int)(i / n);
+    const size_t row = i - (size_t)q * n;
+    uint64_t acc = 0;
+    for (int s = 0; s < S; s++) acc += partial[((size_t)s * 4 + q) * n + row];  // 31-bit terms: the 64-bit sum cannot overflow
+    out.c[q][row] = m31_sub(m31_reduce64(acc), b_sum.c[q]);
 }
 
 constexpr int MAX_ACCS = 8;
@@ -240,6 +266,27 @@ int zkb_quot_numerators(zkb_ctx* ctx, const uint32_t* const* cols, int ncols, in
     for (int q = 0; q < 4; q++) wide = wide && ((uintptr_t)out[q] & 15) == 0;
     for (int c = 0; c < ncols; c++) wide = wide && ((uintptr_t)cols[c] & 15) == 0;
     ProfScope prof(ctx, "quot_numerators_kernel");
+    // Few rows and many columns: split the columns over the grid's second dimension.
+    const unsigned row_blocks = (unsigned)((n / (wide ? 4 : 2) + 255) / 256);
+    const size_t scratch_free = ctx->scratch_words - (size_t)5 * k;
+    if (row_blocks < 148u && k >= 8 * NUM_TILE && 4 * n * 2 <= scratch_free) {
+        int S = (int)((2u * 148u + row_blocks - 1) / row_blocks);            // about two CTAs per SM
+        int chunk = ((k + S - 1) / S + NUM_TILE - 1) / NUM_TILE * NUM_TILE;  // whole tiles of columns
+        S = (k + chunk - 1) / chunk;
+        while ((size_t)S * 4 * n + 4 > scratch_free) { chunk += NUM_TILE; S = (k + chunk - 1) / chunk; }
+        uint32_t* partial = ctx->scratch + (size_t)5 * k + ((4 - ((size_t)5 * k & 3)) & 3);  // 16-byte aligned
+        dim3 grid(row_blocks, (unsigned)S);
+        if (wide)
+            quot_numerators_kernel<4><<<grid, 256, 0, ctx->stream>>>((const uint32_t* const*)d_cols, d_idx, reinterpret_cast<const uint4*>(d_c), k,
+                                                                     b_sum, n, o, chunk, partial);
+        else
+            quot_numerators_kernel<2><<<grid, 256, 0, ctx->stream>>>((const uint32_t* const*)d_cols, d_idx, reinterpret_cast<const uint4*>(d_c), k,
+                                                                     b_sum, n, o, chunk, partial);
+        ZKB_LAUNCH_CHECK(ctx);
+        quot_partial_sum_kernel<<<(unsigned)((4 * n + 255) / 256), 256, 0, ctx->stream>>>(partial, S, n, b_sum, o);
+        ZKB_LAUNCH_CHECK(ctx);
+        return ZKB_OK;
+    }
     if (wide)
         quot_numerators_kernel<4><<<(unsigned)((n / 4 + 255) / 256), 256, 0, ctx->stream>>>(
             (const uint32_t* const*)d_cols, d_idx, reinterpret_cast<const uint4*>(d_c), k, b_sum, n, o);
