@@ -864,6 +864,7 @@ def run_segment_replay(args, rank):
             inst.append((z.GKR_LOGUP_SINGLES, 0, dens.ptr + 16 * off, 1 << l))
             off += 1 << l
         batches.append((fam, inst))
+    prepared = ctx.pcs_prepare(ptrs, logs, cap=1 << 25)
     sampler = ClockSampler(0)
     t_pcs, t_gkr, phases = [], [], None
     for it in range(args.warmup + args.steps):
@@ -872,8 +873,7 @@ def run_segment_replay(args, rank):
         ctx.sync()
         ctx.event_record(0)
         ctx.d2d(work.ptr, pristine.ptr, total_words * 4)
-        words, ph = ctx.pcs_prove_device(ptrs, logs, pow_bits=0, log_blowup=log_blowup, log_last_layer=0, n_queries=100,
-                                         cap=1 << 27, phases=True)
+        words, ph = ctx.pcs_prove_device(prepared, None, pow_bits=0, log_blowup=log_blowup, log_last_layer=0, n_queries=100, phases=True)
         ctx.event_record(1)
         gw = [ctx.gkr_prove_device(inst, 0x5EED0007 + i, cap=1 << 24) for i, (_f, inst) in enumerate(batches)]
         ctx.event_record(2)
@@ -885,7 +885,7 @@ def run_segment_replay(args, rank):
     clocks = sampler.stop()
     ctx.profile_begin()
     ctx.d2d(work.ptr, pristine.ptr, total_words * 4)
-    ctx.pcs_prove_device(ptrs, logs, pow_bits=0, log_blowup=log_blowup, log_last_layer=0, n_queries=100, cap=1 << 27)
+    ctx.pcs_prove_device(prepared, None, pow_bits=0, log_blowup=log_blowup, log_last_layer=0, n_queries=100)
     for i, (_f, inst) in enumerate(batches):
         ctx.gkr_prove_device(inst, 0x5EED0007 + i, cap=1 << 24)
     kernels = ctx.profile_end(cap=128)

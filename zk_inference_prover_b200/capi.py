@@ -510,18 +510,26 @@ class Context:
         return nonce.value
 
     # ---- whole protocols (include/zkb200_prover.h)
-    def _pcs(self, fn, trees_ptrs, logs, pow_bits, log_blowup, log_last_layer, n_queries, two_sample_every, cap, phases):
+    @staticmethod
+    def pcs_prepare(trees_ptrs, logs, cap=1 << 24):
+        """The argument arrays of a PCS proof, built once: a caller that proves the same tens of thousands of columns again and
+        again passes the result as `trees_ptrs` (and None as `logs`) and does not pay for their conversion, nor for a fresh
+        output buffer, in every call. The returned proof words are then a view of the prepared output buffer."""
         flat = [p for t in trees_ptrs for p in t]
-        ncols = np.array([len(t) for t in trees_ptrs], np.int32)
-        lg = _u32(logs)
+        return {"n_trees": len(trees_ptrs), "ncols": np.array([len(t) for t in trees_ptrs], np.int32), "ptrs": _ptr_array(flat),
+                "logs": _u32(logs), "out": np.empty(cap, np.uint32)}
+
+    def _pcs(self, fn, trees_ptrs, logs, pow_bits, log_blowup, log_last_layer, n_queries, two_sample_every, cap, phases):
+        prepared = trees_ptrs if isinstance(trees_ptrs, dict) else None
+        a = prepared or self.pcs_prepare(trees_ptrs, logs, cap)
         cfg = PcsConfig(pow_bits, log_blowup, log_last_layer, n_queries)
-        out = np.empty(cap, np.uint32)
+        out = a["out"]
         n = C.c_size_t()
         ph = np.zeros(len(PCS_PHASES), np.float32)
-        self._check(fn(self.h, C.c_int(len(trees_ptrs)), ncols.ctypes.data_as(C.c_void_p), _ptr_array(flat), lg.ctypes.data_as(C.c_void_p),
-                       C.byref(cfg), C.c_int(two_sample_every), out.ctypes.data_as(C.c_void_p), C.c_size_t(cap), C.byref(n),
+        self._check(fn(self.h, C.c_int(a["n_trees"]), a["ncols"].ctypes.data_as(C.c_void_p), a["ptrs"], a["logs"].ctypes.data_as(C.c_void_p),
+                       C.byref(cfg), C.c_int(two_sample_every), out.ctypes.data_as(C.c_void_p), C.c_size_t(out.size), C.byref(n),
                        ph.ctypes.data_as(C.c_void_p) if phases else None))
-        words = out[:n.value].copy()
+        words = out[:n.value] if prepared else out[:n.value].copy()
         return (words, dict(zip(PCS_PHASES, ph.tolist()))) if phases else words
 
     def pcs_prove_device(self, trees_ptrs, logs, pow_bits=10, log_blowup=1, log_last_layer=0, n_queries=3, two_sample_every=0,

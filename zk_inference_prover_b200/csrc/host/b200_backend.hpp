@@ -78,6 +78,7 @@ class BaseColumn {
     ~BaseColumn() { release(); }
     uint32_t* ptr() const { return ptr_; }
     size_t len() const { return len_; }
+    void shrink(size_t len) { if (len < len_) len_ = len; }  // keeps the allocation, forgets the tail
     uint32_t log_size() const { uint32_t l = 0; while (((size_t)1 << (l + 1)) <= len_) l++; return l; }
     std::vector<uint32_t> to_cpu() const {
         std::vector<uint32_t> v(len_);
@@ -136,6 +137,7 @@ struct Layer {
     SecureMle num;      // LOGUP_GENERIC numerators
     BaseColumn num_base;  // LOGUP_MULTIPLICITIES numerators
     SecureMle den;      // denominators, or the grand-product column
+    bool writable = false;  // the arrays are the prover's own scratch (a tower layer, a fixed layer): they may be overwritten
     size_t len() const { return den.len(); }
     size_t n_variables() const { size_t l = 0; while (((size_t)1 << (l + 1)) <= len()) l++; return l; }
     const uint32_t* num_ptr() const {

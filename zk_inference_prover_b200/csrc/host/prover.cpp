@@ -773,19 +773,47 @@ static qm31 horner(const std::vector<qm31>& v, qm31 x) {
     return acc;
 }
 
-// gkr_prover.rs:884-923
-static UniPoly correct_sum_as_poly_in_first_variable(qm31 f0, qm31 f2, qm31 claim, const std::vector<qm31>& y, size_t k) {
-    size_t n = y.size();
-    qm31 a = qm31_one();
-    for (size_t i = 0; i < n - k + 1; i++) a = a * eq1(qm31_zero(), y[i]);
-    a = qm31_inv(a);
-    qm31 two = qm31_from_m31(2);
-    qm31 b = (qm31_one() - y[n - k]) * qm31_inv(qm31_one() - qm31_dbl(y[n - k]));
-    qm31 r0 = f0 * eq1(qm31_zero(), y[n - k]) * a;
-    qm31 r1 = claim - r0;
-    qm31 r2 = f2 * eq1(two, y[n - k]) * a;
-    return UniPoly::interpolate_lagrange({qm31_zero(), qm31_one(), two, b}, {r0, r1, r2, qm31_zero()});
-}
+// correct_sum_as_poly_in_first_variable (gkr_prover.rs:884-923), split in two.
+// The part that depends only on the out-of-domain point y and on the number of
+// variables k: every oracle that is active in a round shares it, so it is worked out once per round (two inversions and
+// the Lagrange basis on {0, 1, 2, b}) instead of once per instance (a batch has hundreds). The round polynomial of an
+// oracle is then r0 L0 + r1 L1 + r2 L2 (the value at b is zero), the same field elements as the interpolation gives.
+struct RoundBasis {
+    qm31 e0a, e2a;   // eq(0, y[n-k]) / prod_{i <= n-k} eq(0, y_i) and eq(2, y[n-k]) / the same product
+    qm31 L[3][4];    // coefficients (low first) of the basis polynomials of the nodes 0, 1, 2
+    RoundBasis(const std::vector<qm31>& y, size_t k) {
+        size_t n = y.size();
+        qm31 a = qm31_one();
+        for (size_t i = 0; i < n - k + 1; i++) a = a * eq1(qm31_zero(), y[i]);
+        a = qm31_inv(a);
+        qm31 two = qm31_from_m31(2);
+        qm31 b = (qm31_one() - y[n - k]) * qm31_inv(qm31_one() - qm31_dbl(y[n - k]));
+        e0a = eq1(qm31_zero(), y[n - k]) * a;
+        e2a = eq1(two, y[n - k]) * a;
+        const qm31 xs[4] = {qm31_zero(), qm31_one(), two, b};
+        for (int i = 0; i < 3; i++) {
+            qm31 denom = qm31_one();
+            qm31 poly[4] = {qm31_one(), qm31_zero(), qm31_zero(), qm31_zero()};
+            int deg = 0;
+            for (int j = 0; j < 4; j++) {
+                if (j == i) continue;
+                denom = denom * (xs[i] - xs[j]);
+                for (int t = ++deg; t > 0; t--) poly[t] = poly[t - 1] - xs[j] * poly[t];  // times (x - xs[j])
+                poly[0] = qm31_neg(xs[j] * poly[0]);
+            }
+            qm31 inv = qm31_inv(denom);
+            for (int t = 0; t < 4; t++) L[i][t] = poly[t] * inv;
+        }
+    }
+    UniPoly round_poly(qm31 f0, qm31 f2, qm31 claim) const {
+        qm31 r0 = f0 * e0a, r1 = claim - r0, r2 = f2 * e2a;
+        UniPoly p;
+        p.c.resize(4);
+        for (int t = 0; t < 4; t++) p.c[t] = r0 * L[0][t] + r1 * L[1][t] + r2 * L[2][t];
+        p.trim();
+        return p;
+    }
+};
 
 struct GkrOracle {  // GkrMultivariatePolyOracle, gkr_prover.rs:473-556
     Layer input_layer;
@@ -833,19 +861,31 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
         it.mode = mode;
         return it;
     };
+    std::vector<BaseColumn> slabs;  // one allocation per tower level; the layers of that level are views of it
     for (;;) {
         items.clear();
+        size_t words = 0;
         for (size_t i = 0; i < n_inst; i++) {
             const Layer& in = towers[i].back();
             if (in.n_variables() == 0) continue;
+            words += (in.kind == ZKB_GKR_GRAND_PRODUCT ? 1 : 2) * 4 * (in.len() / 2);
+        }
+        if (!words) break;
+        slabs.emplace_back(d, words);
+        uint32_t* cur = slabs.back().ptr();
+        for (size_t i = 0; i < n_inst; i++) {
+            const Layer& in = towers[i].back();
+            if (in.n_variables() == 0) continue;
+            const size_t half_words = 4 * (in.len() / 2);
             Layer out;
+            out.writable = true;
             out.kind = in.kind == ZKB_GKR_GRAND_PRODUCT ? ZKB_GKR_GRAND_PRODUCT : ZKB_GKR_LOGUP_GENERIC;
-            out.den = SecureMle(d, in.len() / 2);
-            if (out.kind == ZKB_GKR_LOGUP_GENERIC) out.num = SecureMle(d, in.len() / 2);
+            out.den.words = BaseColumn::view(d, cur, half_words);
+            cur += half_words;
+            if (out.kind == ZKB_GKR_LOGUP_GENERIC) { out.num.words = BaseColumn::view(d, cur, half_words); cur += half_words; }
             items.push_back(item_of(in, out, 3));
             towers[i].push_back(std::move(out));
         }
-        if (items.empty()) break;
         d.check(zk::gkr_batch_next_layer(d.ctx(), items.data(), (int)items.size()));
     }
     std::vector<uint32_t> results;
@@ -935,14 +975,14 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
                     oracles[who[j]].have_sums = true;
                 }
             }
+            const RoundBasis basis(ood_point, n_rem);  // every active oracle has n_rem variables left
             for (size_t k = 0; k < oracles.size(); k++) {
                 UniPoly rp;
                 if (n_rem == oracles[k].n_variables()) {
                     auto sums = oracles[k].sums;
                     oracles[k].have_sums = false;
-                    rp = correct_sum_as_poly_in_first_variable(sums.first * oracles[k].eq_fixed_var_correction,
-                                                               sums.second * oracles[k].eq_fixed_var_correction, sc_claims[k], ood_point,
-                                                               oracles[k].n_variables());
+                    rp = basis.round_poly(sums.first * oracles[k].eq_fixed_var_correction, sums.second * oracles[k].eq_fixed_var_correction,
+                                          sc_claims[k]);
                 } else {
                     rp.c = {qm31_mul_m31(sc_claims[k], half)};
                     rp.trim();
@@ -966,12 +1006,26 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
                 if (n_rem == oracles[k].n_variables() && oracles[k].n_variables() != 0) {
                     qm31 z0 = ood_point[ood_point.size() - oracles[k].n_variables()];
                     oracles[k].eq_fixed_var_correction = oracles[k].eq_fixed_var_correction * eq1(challenge, z0);
-                    const Layer& in = oracles[k].input_layer;
+                    Layer& in = oracles[k].input_layer;
                     Layer out;  // Layer::fix_first_variable, gkr_prover.rs:354-381
+                    out.writable = true;
                     out.kind = in.kind == ZKB_GKR_LOGUP_MULTIPLICITIES ? ZKB_GKR_LOGUP_GENERIC : in.kind;
-                    out.den = SecureMle(d, in.len() / 2);
-                    if (out.kind == ZKB_GKR_LOGUP_GENERIC) out.num = SecureMle(d, in.len() / 2);
-                    items.push_back(item_of(in, out, in.len() >= 8 ? 1 : 2));
+                    if (in.writable && in.kind != ZKB_GKR_LOGUP_MULTIPLICITIES) {
+                        // A thread of the fixing kernel reads entries i and i + n/2 and writes entry i, and no other thread
+                        // touches either: the prover's own layers are fixed in place, the result being their first half.
+                        out.den.words = BaseColumn::view(d, in.den.words.ptr(), in.den.words.len() / 2);
+                        if (out.kind == ZKB_GKR_LOGUP_GENERIC) out.num.words = BaseColumn::view(d, in.num.words.ptr(), in.num.words.len() / 2);
+                        items.push_back(item_of(in, out, in.len() >= 8 ? 1 : 2));
+                        // keep the allocation alive under its new, shorter shape
+                        in.den.words.shrink(in.den.words.len() / 2);
+                        if (out.kind == ZKB_GKR_LOGUP_GENERIC) in.num.words.shrink(in.num.words.len() / 2);
+                        out = std::move(in);
+                        out.writable = true;
+                    } else {
+                        out.den = SecureMle(d, in.len() / 2);
+                        if (out.kind == ZKB_GKR_LOGUP_GENERIC) out.num = SecureMle(d, in.len() / 2);
+                        items.push_back(item_of(in, out, in.len() >= 8 ? 1 : 2));
+                    }
                     fixed.push_back(std::move(out));
                     who.push_back(k);
                 }
