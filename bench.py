@@ -866,7 +866,7 @@ def run_segment_replay(args, rank):
         batches.append((fam, inst))
     prepared = ctx.pcs_prepare(ptrs, logs, cap=1 << 25)
     sampler = ClockSampler(0)
-    t_pcs, t_gkr, phases = [], [], None
+    t_pcs, t_gkr, phases, gkr_family_ms = [], [], None, {}
     for it in range(args.warmup + args.steps):
         if it == args.warmup:
             sampler.start()
@@ -875,12 +875,16 @@ def run_segment_replay(args, rank):
         ctx.d2d(work.ptr, pristine.ptr, total_words * 4)
         words, ph = ctx.pcs_prove_device(prepared, None, pow_bits=0, log_blowup=log_blowup, log_last_layer=0, n_queries=100, phases=True)
         ctx.event_record(1)
-        gw = [ctx.gkr_prove_device(inst, 0x5EED0007 + i, cap=1 << 24) for i, (_f, inst) in enumerate(batches)]
-        ctx.event_record(2)
+        gw = []
+        for i, (_f, inst) in enumerate(batches):
+            gw.append(ctx.gkr_prove_device(inst, 0x5EED0007 + i, cap=1 << 24))
+            ctx.event_record(2 + i)
         ctx.sync()
         if it >= args.warmup:
             t_pcs.append(ctx.event_elapsed_ms(0, 1))
-            t_gkr.append(ctx.event_elapsed_ms(1, 2))
+            t_gkr.append(ctx.event_elapsed_ms(1, 1 + len(batches)))
+            for i, (f, _inst) in enumerate(batches):
+                gkr_family_ms[f] = gkr_family_ms.get(f, 0.0) + ctx.event_elapsed_ms(1 + i, 2 + i) / args.steps
             phases = ph if phases is None else {k: phases[k] + ph[k] for k in ph}
     clocks = sampler.stop()
     ctx.profile_begin()
@@ -900,7 +904,7 @@ def run_segment_replay(args, rank):
                    "tree_columns": [len(t) for t in trees], "log_rows": [min(logs), max(logs)], "log_blowup": log_blowup,
                    "n_queries": 100, "gkr_batches": {f: len(i) for f, i in batches}, "gkr_entries": gkr_entries,
                    "l2": "inputs larger than L2"},
-        "cells": cells, "cells_per_s": cells / (ms * 1e-3), "pcs_ms": pcs_ms, "gkr_ms": gkr_ms,
+        "cells": cells, "cells_per_s": cells / (ms * 1e-3), "pcs_ms": pcs_ms, "gkr_ms": gkr_ms, "gkr_ms_by_family": gkr_family_ms,
         "per_phase_ms": {k: v / args.steps for k, v in phases.items()}, "pcs_proof_words": int(words.size),
         "gkr_proof_words": int(sum(w.size for w in gw)), "clocks": clocks,
         "gpu_launches": int(sum(v[1] for v in kernels.values())) * args.steps,

@@ -96,3 +96,21 @@ def test_gkr_proof_matches_oracle(ctx, oracle, spec):
     assert (got == want).all()
     # inputs are not modified
     assert (keep[1].download(shape=(-1, 4)) == insts[0][2]).all()
+
+
+@pytest.mark.parametrize("driver,spec", [("resident", [(2, 10), (3, 7), (0, 8), (1, 3)]), ("resident", [(3, 12), (3, 12), (2, 12)]),
+                                         ("batch", [(2, 11)]), ("batch", [(1, 6), (0, 6)])])
+def test_gkr_drivers_give_the_same_proof(ctx, oracle, monkeypatch, driver, spec):
+    """The library picks the device-resident transcript for one or two instances and the batched rounds otherwise;
+    ZKB_GKR_DRIVER forces either, and both must reproduce the oracle's proof for any batch they accept."""
+    monkeypatch.setenv("ZKB_GKR_DRIVER", driver)
+    insts = [_instance(k, lg, 5200 + 10 * i) for i, (k, lg) in enumerate(spec)]
+    want = oracle.gkr_prove(insts, 0x5EED0004, verify=True)
+    keep, dev = [], []
+    for kind, num, den in insts:
+        nb = ctx.upload(num) if num is not None else None
+        db = ctx.upload(den)
+        keep += [nb, db]
+        dev.append((kind, nb.ptr if nb else 0, db.ptr, den.shape[0]))
+    got = ctx.gkr_prove_device(dev, 0x5EED0004)
+    assert len(got) == len(want) and (got == want).all()

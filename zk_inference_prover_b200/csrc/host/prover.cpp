@@ -6,6 +6,7 @@
 #include <algorithm>
 #include <chrono>
 #include <map>
+#include <memory>
 #include <numeric>
 #include <set>
 
@@ -51,7 +52,7 @@ struct GatherPlan {
     // block_words from the returned offset. One pointer per column and one index per row travel, not one address per word.
     struct Block { std::vector<const uint32_t*> cols; std::vector<uint32_t> idx; size_t out_off; };
     std::vector<Block> blocks;
-    std::vector<uint32_t> block_words;
+    std::unique_ptr<uint32_t[]> block_words;  // not value-initialised: tens of megabytes for a tree of many columns
     size_t block_total = 0;
     size_t add_block(const std::vector<const uint32_t*>& cols, const std::vector<size_t>& rows) {
         Block b;
@@ -66,10 +67,10 @@ struct GatherPlan {
         words.resize(addrs.size());
         d.check(zkb_gather_words(d.ctx(), addrs.data(), addrs.size(), words.data()));
         if (block_total) {
-            block_words.resize(block_total);
+            block_words.reset(new uint32_t[block_total]);
             std::vector<zk::GatherBlock> gb;
             for (auto& b : blocks) gb.push_back({b.cols.data(), (int)b.cols.size(), b.idx.data(), (int)b.idx.size(), b.out_off});
-            d.check(zk::gather_blocks(d.ctx(), gb.data(), (int)gb.size(), block_total, block_words.data()));
+            d.check(zk::gather_blocks(d.ctx(), gb.data(), (int)gb.size(), block_total, block_words.get()));
         }
     }
     Hash hash_at(size_t slot) const { Hash h; for (int k = 0; k < 8; k++) h[k] = words[slot + k]; return h; }
@@ -84,9 +85,13 @@ struct PendingMerkle {  // slots of a planned decommitment
     std::pair<std::vector<uint32_t>, MerkleDecommitment> finish(const GatherPlan& plan) const {
         std::pair<std::vector<uint32_t>, MerkleDecommitment> r;
         for (auto s : hash_slots) r.second.hash_witness.push_back(plan.hash_at(s));
+        size_t nq = 0, nw = 0;
+        for (auto& run : runs) (run.queried ? nq : nw) += run.count;
+        r.first.reserve(nq);
+        r.second.column_witness.reserve(nw);
         for (auto& run : runs) {
             auto& dst = run.queried ? r.first : r.second.column_witness;
-            dst.insert(dst.end(), plan.block_words.begin() + run.off, plan.block_words.begin() + run.off + run.count);
+            dst.insert(dst.end(), plan.block_words.get() + run.off, plan.block_words.get() + run.off + run.count);
         }
         return r;
     }
@@ -447,6 +452,11 @@ struct PcsProof {
     }
     std::vector<uint32_t> to_words() const {
         std::vector<uint32_t> o;
+        size_t expect = 1 << 16;
+        for (auto& t : sampled_values) expect += 6 * t.size();
+        for (auto& d : decommitments) expect += 8 * d.hash_witness.size() + d.column_witness.size();
+        for (auto& t : queried_values) expect += t.size();
+        o.reserve(expect);
         o.push_back((uint32_t)commitments.size());
         for (auto& h : commitments) put_hash(o, h);
         for (auto& t : sampled_values) {
@@ -1487,7 +1497,15 @@ int zkb_gkr_prove_device(zkb_ctx* ctx, int n_inst, const int* kinds, const uint3
         Channel ch;
         ch.mix_u64(seed);
         std::vector<uint32_t> w;
-        if (gkr_resident_supported(n_inst, ns)) {
+        // Two drivers give the same proof. With the transcript on the device a round costs no host round trip but runs its
+        // Fiat-Shamir step on one warp, which pays for ONE large instance; a batch of several instances is cheaper with one
+        // launch and one read-back per round for all of them. ZKB_GKR_DRIVER=resident|batch overrides the choice.
+        bool resident = gkr_resident_supported(n_inst, ns) && n_inst <= 2;
+        if (const char* pick = getenv("ZKB_GKR_DRIVER")) {
+            if (!strcmp(pick, "resident")) resident = gkr_resident_supported(n_inst, ns);
+            else if (!strcmp(pick, "batch")) resident = false;
+        }
+        if (resident) {
             // the transcript stays on the device: no host round trip per sum-check round
             uint32_t dg[8], nd = ch.n_draws();
             for (int k = 0; k < 8; k++) dg[k] = ch.digest()[k];
