@@ -913,6 +913,61 @@ def run_segment_replay(args, rank):
     ctx.close()
 
 
+def run_witness(args, rank):
+    """--mode witness: the two device witness generators at the sizes of a layer segment: the tables' own columns at 2^23 rows
+    with four key-tile counters, and a dequantize component of the bf16-chain variant for a 4096 x 4096 matmul over 512 tokens
+    (16 slots per row, 2^17 rows, 242 committed and 37 preprocessed columns). Byte work: reported against the HBM peak with
+    the algorithmic bytes (every column written once, every counter and accumulator read once)."""
+    if rank != 0:
+        return
+    import zk_inference_prover_b200 as z
+    from witness_cases import dequant_case, tables_case
+
+    peak, peak_kind = measured_hbm_peak()
+    ctx = z.Context(device=0, max_log_size=10)
+    log_rows, n_counters = 23, 4
+    expmap, counters, _, _ = tables_case(7, log_rows, n_counters)
+    rows = 1 << log_rows
+    d_map, d_cnt = ctx.upload(expmap), [ctx.upload(c) for c in counters]
+    x, y, m = ctx.alloc(rows), ctx.alloc(rows), ctx.alloc(rows)
+    case = dequant_case(8, 1, tokens=512, chunks=256, per_row=16, kmax=19, sticky=1, do_ref=0)
+    cfg, drows = case["cfg"], case["rows"]
+    up = lambda a: ctx.upload_bytes(np.ascontiguousarray(a))
+    d_acc, d_norm, d_mul, d_sx, d_sw = up(case["acc"]), ctx.upload(case["norm3"]), ctx.upload(case["mul2"]), ctx.upload(case["sx"]), ctx.upload(case["sw"])
+    base = [ctx.alloc(drows) for _ in range(case["n_base"])]
+    pre = [ctx.alloc(drows) for _ in range(case["n_pre"])]
+    m_norm, m_frac = ctx.alloc(cfg["n_norm"]).zero(), ctx.alloc(cfg["n_frac"]).zero()
+    m_mul, m_r8, counts = ctx.alloc(cfg["n_mul"]).zero(), ctx.alloc(cfg["n_r8"]).zero(), ctx.alloc(3).zero()
+    t_tab, t_deq = [], []
+    for it in range(args.warmup + args.steps):
+        ctx.sync()
+        ctx.event_record(0)
+        ctx.witness_tables(d_map.ptr, [c.ptr for c in d_cnt], log_rows, False, 2.0 ** 7, x.ptr, y.ptr, m.ptr)
+        ctx.event_record(1)
+        ctx.witness_dequant(cfg, d_acc.ptr, 0, 0, d_sx.ptr, d_sw.ptr, d_norm.ptr, d_mul.ptr, [b.ptr for b in base], [p.ptr for p in pre],
+                            m_norm.ptr, m_frac.ptr, m_mul.ptr, m_r8.ptr, counts.ptr, 0)
+        ctx.event_record(2)
+        ctx.sync()
+        if it >= args.warmup:
+            t_tab.append(ctx.event_elapsed_ms(0, 1))
+            t_deq.append(ctx.event_elapsed_ms(1, 2))
+    tab_ms, deq_ms = float(np.mean(t_tab)), float(np.mean(t_deq))
+    tab_bytes = rows * 4 * (3 + n_counters)
+    deq_bytes = drows * 4 * (case["n_base"] + case["n_pre"] + cfg["per_row"])
+    cells = 3 * rows + drows * (case["n_base"] + case["n_pre"])
+    print(json.dumps({
+        "metric": "witness_cells_per_s", "value": cells / ((tab_ms + deq_ms) * 1e-3), "unit": "cells/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": tab_ms + deq_ms, "higher_is_better": True, "dtype": "u32 / i32", "data": "synthetic",
+        "config": {"workload": "witness_tables_2^23_4counters + witness_dequant_chain_512x4096_per_row16"},
+        "tables": {"ms": tab_ms, "algorithmic_bytes": tab_bytes, "gbs": tab_bytes / (tab_ms * 1e-3) / 1e9,
+                   "frac_of_hbm_peak": tab_bytes / (tab_ms * 1e-3) / 1e9 / peak},
+        "dequant": {"ms": deq_ms, "columns": case["n_base"] + case["n_pre"], "rows": drows, "algorithmic_bytes": deq_bytes,
+                    "gbs": deq_bytes / (deq_ms * 1e-3) / 1e9, "frac_of_hbm_peak": deq_bytes / (deq_ms * 1e-3) / 1e9 / peak,
+                    "counts": counts.download().tolist()},
+        "peak_gbs": peak, "peak_kind": peak_kind, "gpu_launches": 2 * args.steps}))
+    ctx.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -929,7 +984,7 @@ def main():
     ap.add_argument("--no-gpu-baseline", action="store_true")
     ap.add_argument("--gkr-log", type=int, default=24)
     ap.add_argument("--segment", default="layer_8b_s32_c2048", help="segment-replay: a key of tests/golden/segment_shapes.json")
-    ap.add_argument("--mode", default="proof", choices=["proof", "sharded-commit", "gkr", "freivalds", "constraints", "stark", "segment-replay"],
+    ap.add_argument("--mode", default="proof", choices=["proof", "sharded-commit", "gkr", "freivalds", "constraints", "stark", "segment-replay", "witness"],
                     help="proof: one whole PCS proof per rank (ranks are independent); sharded-commit: one commitment over all ranks")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -949,6 +1004,8 @@ def main():
         run_stark(args, rank)
     elif args.mode == "segment-replay":
         run_segment_replay(args, rank)
+    elif args.mode == "witness":
+        run_witness(args, rank)
     else:
         run_ours(args, rank, world, local_rank)
 

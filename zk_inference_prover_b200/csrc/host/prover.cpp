@@ -815,8 +815,8 @@ struct RoundBasis {
             for (int t = 0; t < 4; t++) L[i][t] = poly[t] * inv;
         }
     }
-    UniPoly round_poly(qm31 f0, qm31 f2, qm31 claim) const {
-        qm31 r0 = f0 * e0a, r1 = claim - r0, r2 = f2 * e2a;
+    // the polynomial with the values r0, r1, r2 at 0, 1, 2 and zero at b
+    UniPoly round_poly(qm31 r0, qm31 r1, qm31 r2) const {
         UniPoly p;
         p.c.resize(4);
         for (int t = 0; t < 4; t++) p.c[t] = r0 * L[0][t] + r1 * L[1][t] + r2 * L[2][t];
@@ -960,7 +960,6 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
         const uint32_t half = m31_inv(2);
         for (size_t round = 0; round < nv; round++) {
             size_t n_rem = nv - round;
-            std::vector<UniPoly> this_round;
             // the oracles that enter the sum-check in this round have no sums yet: one launch for all of them
             items.clear();
             std::vector<size_t> who;
@@ -985,37 +984,62 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
                     oracles[who[j]].have_sums = true;
                 }
             }
-            const RoundBasis basis(ood_point, n_rem);  // every active oracle has n_rem variables left
-            for (size_t k = 0; k < oracles.size(); k++) {
-                UniPoly rp;
-                if (n_rem == oracles[k].n_variables()) {
-                    auto sums = oracles[k].sums;
+            // Every active oracle has n_rem variables left, so all their round polynomials are r0 L0 + r1 L1 + r2 L2 over the
+            // same basis, and the random linear combination over the batch (sumcheck.rs:139-149, Horner in alpha from the
+            // last oracle down) is (sum alpha^k r0_k) L0 + (sum alpha^k r1_k) L1 + (sum alpha^k r2_k) L2 plus the constants of
+            // the oracles that wait: eleven multiplications per oracle and round instead of a Lagrange interpolation each.
+            // r0 + r1 is the claim by construction, which is the check sumcheck.rs:128-130 makes.
+            const RoundBasis basis(ood_point, n_rem);
+            const size_t K = oracles.size();
+            std::vector<qm31> rv(3 * K);
+            std::vector<char> act(K);
+            qm31 S[3] = {qm31_zero(), qm31_zero(), qm31_zero()}, Sc = qm31_zero();
+            for (size_t k = K; k-- > 0;) {
+                for (int t = 0; t < 3; t++) S[t] = S[t] * sumcheck_alpha;
+                Sc = Sc * sumcheck_alpha;
+                act[k] = n_rem == oracles[k].n_variables();
+                if (act[k]) {
+                    const qm31 corr = oracles[k].eq_fixed_var_correction;
+                    rv[3 * k] = oracles[k].sums.first * corr * basis.e0a;
+                    rv[3 * k + 1] = sc_claims[k] - rv[3 * k];
+                    rv[3 * k + 2] = oracles[k].sums.second * corr * basis.e2a;
                     oracles[k].have_sums = false;
-                    rp = basis.round_poly(sums.first * oracles[k].eq_fixed_var_correction, sums.second * oracles[k].eq_fixed_var_correction,
-                                          sc_claims[k]);
+                    for (int t = 0; t < 3; t++) S[t] = S[t] + rv[3 * k + t];
                 } else {
-                    rp.c = {qm31_mul_m31(sc_claims[k], half)};
-                    rp.trim();
+                    rv[3 * k] = qm31_mul_m31(sc_claims[k], half);
+                    Sc = Sc + rv[3 * k];
                 }
-                if (!(rp.eval(qm31_zero()) + rp.eval(qm31_one()) == sc_claims[k])) throw Error(ZKB_EINVAL, "sumcheck: round polynomial does not match the claim");
-                this_round.push_back(rp);
             }
             UniPoly combined;
-            for (size_t k = this_round.size(); k-- > 0;) {
-                for (auto& c : combined.c) c = c * sumcheck_alpha;
-                combined = UniPoly::add(combined, this_round[k]);
+            combined.c.resize(4);
+            for (int t = 0; t < 4; t++) combined.c[t] = S[0] * basis.L[0][t] + S[1] * basis.L[1][t] + S[2] * basis.L[2][t];
+            combined.c[0] = combined.c[0] + Sc;
+            if (qm31_is_zero(combined.c[3])) {
+                // The combination keeps the length of its longest term. A vanishing leading coefficient does not say which
+                // case this is (every term short, or a cancellation), so this round goes term by term.
+                combined = UniPoly();
+                for (size_t k = K; k-- > 0;) {
+                    UniPoly rp;
+                    if (act[k]) rp = basis.round_poly(rv[3 * k], rv[3 * k + 1], rv[3 * k + 2]);
+                    else { rp.c = {rv[3 * k]}; rp.trim(); }
+                    for (auto& c : combined.c) c = c * sumcheck_alpha;
+                    combined = UniPoly::add(combined, rp);
+                }
             }
             ch.mix_felts(combined.c);
             qm31 challenge = ch.draw_secure_felt();
-            for (size_t k = 0; k < oracles.size(); k++) sc_claims[k] = this_round[k].eval(challenge);
+            qm31 Lc[3];
+            for (int t = 0; t < 3; t++) Lc[t] = ((basis.L[t][3] * challenge + basis.L[t][2]) * challenge + basis.L[t][1]) * challenge + basis.L[t][0];
+            for (size_t k = 0; k < K; k++)
+                sc_claims[k] = act[k] ? rv[3 * k] * Lc[0] + rv[3 * k + 1] * Lc[1] + rv[3 * k + 2] * Lc[2] : rv[3 * k];
+            const qm31 eq_step = eq1(challenge, ood_point[ood_point.size() - n_rem]);  // the same for every active oracle
             // fix the first variable of every active oracle (and take the next round's sums in the same pass): one launch
             items.clear();
             who.clear();
             std::vector<Layer> fixed;
             for (size_t k = 0; k < oracles.size(); k++)
                 if (n_rem == oracles[k].n_variables() && oracles[k].n_variables() != 0) {
-                    qm31 z0 = ood_point[ood_point.size() - oracles[k].n_variables()];
-                    oracles[k].eq_fixed_var_correction = oracles[k].eq_fixed_var_correction * eq1(challenge, z0);
+                    oracles[k].eq_fixed_var_correction = oracles[k].eq_fixed_var_correction * eq_step;
                     Layer& in = oracles[k].input_layer;
                     Layer out;  // Layer::fix_first_variable, gkr_prover.rs:354-381
                     out.writable = true;

@@ -163,9 +163,18 @@ __device__ __forceinline__ uint32_t bf16_round_f64(double x) {
 
 template <int CHAIN>
 __global__ void __launch_bounds__(128) dequant_kernel(const DeqArgs a) {
-    extern __shared__ uint32_t r8_hist[];
+    extern __shared__ __align__(16) uint32_t r8_hist[];
     const zkb_dequant_cfg& c = a.c;
     for (uint32_t k = threadIdx.x; k < c.n_r8; k += blockDim.x) r8_hist[k] = 0;
+    // The column addresses of this CTA's slots, once per CTA: every store of every thread would otherwise start with a
+    // dependent read of the pointer table.
+    uint32_t** s_base = reinterpret_cast<uint32_t**>(r8_hist + ((c.n_r8 + 3u) & ~3u));  // [slot in tile][field]
+    uint32_t** s_pre = s_base + a.slot_tile * c.per_slot;                               // [slot in tile][scale column]
+    {
+        const uint32_t s0 = blockIdx.y * a.slot_tile, ns = min(c.per_row - s0, a.slot_tile);
+        for (uint32_t k = threadIdx.x; k < ns * c.per_slot; k += blockDim.x) s_base[k] = a.base[c.slot0 + s0 * c.per_slot + k];
+        for (uint32_t k = threadIdx.x; k < ns * c.chan_w; k += blockDim.x) s_pre[k] = a.pre[c.chan_w * s0 + k];
+    }
     __syncthreads();
     const uint32_t rows = 1u << c.log_rows;
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -191,20 +200,22 @@ __global__ void __launch_bounds__(128) dequant_kernel(const DeqArgs a) {
         }
         const int32_t* acc_row = a.acc + (size_t)t * c.n_out + (size_t)b * c.per_row;
         for (uint32_t s = s_begin; s < s_end; s++) {
-            const uint32_t ch = b * c.per_row + s, col0 = c.slot0 + s * c.per_slot;
+            const uint32_t ch = b * c.per_row + s;
+            uint32_t* const* col = s_base + (s - s_begin) * c.per_slot;  // col[field] is the slot's column of that field
+            uint32_t* const* pcol = s_pre + (s - s_begin) * c.chan_w;
             uint32_t sw_m = 0, sw_e = 0;
             int jw_c = 0;
             if (CHAIN) {
                 sw_m = __ldg(a.sw + 2u * ch);
                 sw_e = __ldg(a.sw + 2u * ch + 1u);
-                a.pre[2u * s][i] = sw_m;
-                a.pre[2u * s + 1u][i] = sw_e;
+                pcol[0][i] = sw_m;
+                pcol[1][i] = sw_e;
             } else {
                 jw_c = __ldg(a.jw + ch);
-                a.pre[s][i] = m31_of(jw_c);
+                pcol[0][i] = m31_of(jw_c);
             }
             const long long av = __ldg(acc_row + s);
-            a.base[col0 + c.f_acc][i] = m31_of(av);
+            col[c.f_acc][i] = m31_of(av);
             const uint32_t sg = av < 0;
             const unsigned long long mag = (unsigned long long)(av < 0 ? -av : av);
             // mag = m2 * ph + r with a 9-bit extended significand m2 (prover/src/bf16.rs:300-316)
@@ -230,19 +241,19 @@ __global__ void __launch_bounds__(128) dequant_kernel(const DeqArgs a) {
             const uint32_t n_m7 = __ldg(a.norm3 + 3u * ri), n_ef = __ldg(a.norm3 + 3u * ri + 1u), n_nz = __ldg(a.norm3 + 3u * ri + 2u);
             bump_agg(a.m_norm, ri);
             bump_agg(a.m_frac, fi);
-            a.base[col0 + c.f_sg][i] = sg;
-            a.base[col0 + c.f_m2][i] = m2;
-            a.base[col0 + c.f_ph][i] = ph;
-            if (c.sticky) a.base[col0 + c.f_st][i] = st;
-            a.base[col0 + c.f_r][i] = (uint32_t)r;
-            a.base[col0 + c.f_m7][i] = n_m7;
-            a.base[col0 + c.f_ef][i] = n_ef;
-            a.base[col0 + c.f_nz][i] = n_nz;
+            col[c.f_sg][i] = sg;
+            col[c.f_m2][i] = m2;
+            col[c.f_ph][i] = ph;
+            if (c.sticky) col[c.f_st][i] = st;
+            col[c.f_r][i] = (uint32_t)r;
+            col[c.f_m7][i] = n_m7;
+            col[c.f_ef][i] = n_ef;
+            col[c.f_nz][i] = n_nz;
             uint32_t got;
             if (!CHAIN) {
                 const long long shift = (long long)jx_t + jw_c;
                 const long long eo = n_nz == 1u ? (long long)n_ef + shift : 0;
-                a.base[col0 + c.f_eo][i] = m31_of(eo);
+                col[c.f_eo][i] = m31_of(eo);
                 if (eo >= 0 && eo < (long long)c.n_r8) atomicAdd(&r8_hist[eo], 1u); else off_table++;
                 got = bf16_bits(sg, (uint32_t)(eo > 0 ? eo : 0), n_m7);
                 if (c.do_ref) {
@@ -262,9 +273,9 @@ __global__ void __launch_bounds__(128) dequant_kernel(const DeqArgs a) {
                     uint32_t po = 0, ca = 0;
                     if (n_nz == 1u) { po = __ldg(a.mul2 + 2u * mi); ca = __ldg(a.mul2 + 2u * mi + 1u); }
                     const long long eo = n_nz == 1u ? e_in + es - 127 + (long long)ca : 0;
-                    a.base[col0 + c.f_mul[3u * step + 0u]][i] = po;
-                    a.base[col0 + c.f_mul[3u * step + 1u]][i] = ca;
-                    a.base[col0 + c.f_mul[3u * step + 2u]][i] = m31_of(eo);
+                    col[c.f_mul[3u * step + 0u]][i] = po;
+                    col[c.f_mul[3u * step + 1u]][i] = ca;
+                    col[c.f_mul[3u * step + 2u]][i] = m31_of(eo);
                     if (n_nz == 1u) bump_agg(a.m_mul, mi);
                     if (eo >= 0 && eo < (long long)c.n_r8) atomicAdd(&r8_hist[eo], 1u); else off_table++;
                     m_in = po;
@@ -354,15 +365,17 @@ int zkb_witness_dequant(zkb_ctx* ctx, const int32_t* acc, const int32_t* jx, con
     rc = stage_ptrs(ctx, (const void* const*)pre_cols, (int)n_pre, &d_pre);
     if (rc) return rc;
     const uint32_t rows = 1u << c.log_rows, gx = (rows + 127) / 128;
-    // slots per thread: as many as still leave four CTAs per SM
-    uint32_t slot_tile = c.per_row;
-    while (slot_tile > 1 && (uint64_t)gx * ((c.per_row + slot_tile - 1) / slot_tile) < 148u * 4u) slot_tile = (slot_tile + 1) / 2;
+    // Slots per thread. A slot is a chain of dependent table reads, so the kernel lives on the number of warps in flight:
+    // as few slots per thread as it takes to reach 32 CTAs (128 warps) per SM, and never more than four.
+    uint32_t slot_tile = c.per_row < 4 ? c.per_row : 4;
+    while (slot_tile > 1 && (uint64_t)gx * ((c.per_row + slot_tile - 1) / slot_tile) < 148u * 32u) slot_tile = (slot_tile + 1) / 2;
     DeqArgs a{acc, jx, jw, sx, sw, norm3, mul2, (uint32_t* const*)d_base, (uint32_t* const*)d_pre, m_norm, m_frac, m_mul, m_r8, counts,
               want_out, c, slot_tile};
     dim3 grid(gx, (c.per_row + slot_tile - 1) / slot_tile);
     ProfScope prof(ctx, "witness_dequant_kernel");
-    if (c.variant == 1) dequant_kernel<1><<<grid, 128, c.n_r8 * 4, ctx->stream>>>(a);
-    else dequant_kernel<0><<<grid, 128, c.n_r8 * 4, ctx->stream>>>(a);
+    const size_t smem = (size_t)((c.n_r8 + 3u) & ~3u) * 4 + (size_t)slot_tile * (c.per_slot + c.chan_w) * sizeof(uint32_t*);
+    if (c.variant == 1) dequant_kernel<1><<<grid, 128, smem, ctx->stream>>>(a);
+    else dequant_kernel<0><<<grid, 128, smem, ctx->stream>>>(a);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }
