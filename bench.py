@@ -913,6 +913,124 @@ def run_segment_replay(args, rank):
     ctx.close()
 
 
+class SegmentReplay:
+    """The device buffers and argument arrays of one segment shape of tests/golden/segment_shapes.json, and one step over
+    them (see run_segment_replay for what a step is)."""
+
+    def __init__(self, z, ctx, name, seed):
+        P = (1 << 31) - 1
+        seg = json.load(open(os.path.join(ROOT, "tests", "golden", "segment_shapes.json")))["segments"][name]
+        trees, gkr = [[], [], []], {}
+        for c in seg["components"]:
+            for _ in range(c["repeat"]):
+                trees[0] += [c["log_rows"]] * c["base_cols"]
+                trees[1] += [c["log_rows"]] * c["interaction_cols"]
+                looks, b = c["lookups_per_row"], 0
+                while looks:
+                    if looks & 1:
+                        gkr.setdefault(c["family"], []).append(c["log_rows"] + b)
+                    looks >>= 1
+                    b += 1
+        for b in seg["boundary_cols"]:
+            trees[2] += [b["log_rows"]] * b["cols"]
+        self.cells = sum(1 << l for t in trees for l in t)
+        assert self.cells == seg["cells"]["fresh"]
+        trees.append([max(l for t in trees for l in t)] * 8)  # the composition columns: the last and tallest tree
+        logs = [l for t in trees for l in t]
+        self.max_log = max(logs)
+        self.ctx, self.total_words = ctx, sum(1 << l for l in logs)
+        rng = np.random.default_rng(seed)
+        self.pristine = ctx.upload(rng.integers(0, P, self.total_words, dtype=np.uint32))
+        self.work = ctx.alloc(self.total_words)
+        ptrs, off = [], 0
+        for t in trees:
+            tp = []
+            for l in t:
+                tp.append(self.work.ptr + 4 * off)
+                off += 1 << l
+            ptrs.append(tp)
+        entries = sum(1 << l for v in gkr.values() for l in v)
+        self.dens = ctx.upload(rng.integers(1, P, 4 * entries, dtype=np.uint32))
+        self.batches, off = [], 0
+        for _fam, ls in gkr.items():
+            inst = []
+            for l in sorted(ls, reverse=True):
+                inst.append((z.GKR_LOGUP_SINGLES, 0, self.dens.ptr + 16 * off, 1 << l))
+                off += 1 << l
+            self.batches.append(inst)
+        self.prepared = ctx.pcs_prepare(ptrs, logs, cap=1 << 25)
+
+    def step(self):
+        ctx = self.ctx
+        ctx.d2d(self.work.ptr, self.pristine.ptr, self.total_words * 4)
+        ctx.pcs_prove_device(self.prepared, None, pow_bits=0, log_blowup=1, log_last_layer=0, n_queries=100)
+        for i, inst in enumerate(self.batches):
+            ctx.gkr_prove_device(inst, 0x5EED0007 + i, cap=1 << 24)
+
+
+def run_decode_step(args, rank, world, local_rank):
+    """--mode decode-step: the proof of one decode step of the 32-layer model as operator-trace replays: 32 layer segments and
+    the output head (the shapes of run_segment_replay), dealt round-robin to the ranks. Segments are independent proofs, so
+    there is no collective on the data path; NCCL carries the barrier and the maximum over ranks of the device time."""
+    import zk_inference_prover_b200 as z
+
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local_rank)
+        with stdout_to_stderr():
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+            dist.barrier()
+    names = ["layer_8b_s32_c2048"] * 32 + ["head_8b_s32_c2048"]
+    mine = names[rank::world]
+    ctx = z.Context(device=local_rank, max_log_size=24)
+    shapes = {n: SegmentReplay(z, ctx, n, 0x5EED0006 + rank) for n in sorted(set(mine))}
+    sampler = ClockSampler(local_rank)
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            dist.barrier()
+
+    def one_pass():
+        for n in mine:
+            shapes[n].step()
+
+    for _ in range(args.warmup):
+        one_pass()
+    barrier()
+    if rank == 0:
+        sampler.start()
+    ctx.event_record(0)
+    for _ in range(args.steps):
+        one_pass()
+    ctx.event_record(1)
+    barrier()
+    ms = ctx.event_elapsed_ms(0, 1) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    if dist is not None:
+        import torch
+
+        t = torch.tensor([ms], device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    cells = 32 * 226711536 + 191812784
+    if rank == 0:
+        print(json.dumps({
+            "metric": "decode_step_proof_ms (operator-trace replay)", "value": ms, "unit": "ms", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+            "dtype": "u32 (M31/QM31)", "data": "synthetic",
+            "config": {"workload": "decode_step_replay_32_layer_segments_plus_head", "segments": len(names),
+                       "segments_on_rank_0": len(mine), "parallelism": f"segments round-robin over {world} GPU(s), no collective",
+                       "l2": "inputs larger than L2"},
+            "cells": cells, "cells_per_s": cells / (ms * 1e-3), "ms_per_segment": ms / len(mine), "clocks": clocks}))
+    ctx.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def run_witness(args, rank):
     """--mode witness: the two device witness generators at the sizes of a layer segment: the tables' own columns at 2^23 rows
     with four key-tile counters, and a dequantize component of the bf16-chain variant for a 4096 x 4096 matmul over 512 tokens
@@ -984,7 +1102,7 @@ def main():
     ap.add_argument("--no-gpu-baseline", action="store_true")
     ap.add_argument("--gkr-log", type=int, default=24)
     ap.add_argument("--segment", default="layer_8b_s32_c2048", help="segment-replay: a key of tests/golden/segment_shapes.json")
-    ap.add_argument("--mode", default="proof", choices=["proof", "sharded-commit", "gkr", "freivalds", "constraints", "stark", "segment-replay", "witness"],
+    ap.add_argument("--mode", default="proof", choices=["proof", "sharded-commit", "gkr", "freivalds", "constraints", "stark", "segment-replay", "decode-step", "witness"],
                     help="proof: one whole PCS proof per rank (ranks are independent); sharded-commit: one commitment over all ranks")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -1006,6 +1124,8 @@ def main():
         run_segment_replay(args, rank)
     elif args.mode == "witness":
         run_witness(args, rank)
+    elif args.mode == "decode-step":
+        run_decode_step(args, rank, world, local_rank)
     else:
         run_ours(args, rank, world, local_rank)
 
