@@ -52,8 +52,15 @@ struct GatherPlan {
     // block_words from the returned offset. One pointer per column and one index per row travel, not one address per word.
     struct Block { std::vector<const uint32_t*> cols; std::vector<uint32_t> idx; size_t out_off; };
     std::vector<Block> blocks;
-    std::unique_ptr<uint32_t[]> block_words;  // not value-initialised: tens of megabytes for a tree of many columns
+    // Tens of megabytes for trees of many columns. The buffer is kept per thread between proofs: a fresh allocation of
+    // that size comes from mmap, and its first-touch page faults cost as much as the gather itself.
+    uint32_t* block_words = nullptr;
     size_t block_total = 0;
+    static uint32_t* arena(size_t words) {
+        thread_local std::vector<uint32_t> buf;
+        if (buf.size() < words) buf.resize(words);
+        return buf.data();
+    }
     size_t add_block(const std::vector<const uint32_t*>& cols, const std::vector<size_t>& rows) {
         Block b;
         b.cols = cols;
@@ -67,10 +74,10 @@ struct GatherPlan {
         words.resize(addrs.size());
         d.check(zkb_gather_words(d.ctx(), addrs.data(), addrs.size(), words.data()));
         if (block_total) {
-            block_words.reset(new uint32_t[block_total]);
+            block_words = arena(block_total);
             std::vector<zk::GatherBlock> gb;
             for (auto& b : blocks) gb.push_back({b.cols.data(), (int)b.cols.size(), b.idx.data(), (int)b.idx.size(), b.out_off});
-            d.check(zk::gather_blocks(d.ctx(), gb.data(), (int)gb.size(), block_total, block_words.get()));
+            d.check(zk::gather_blocks(d.ctx(), gb.data(), (int)gb.size(), block_total, block_words));
         }
     }
     Hash hash_at(size_t slot) const { Hash h; for (int k = 0; k < 8; k++) h[k] = words[slot + k]; return h; }
@@ -91,7 +98,7 @@ struct PendingMerkle {  // slots of a planned decommitment
         r.second.column_witness.reserve(nw);
         for (auto& run : runs) {
             auto& dst = run.queried ? r.first : r.second.column_witness;
-            dst.insert(dst.end(), plan.block_words.get() + run.off, plan.block_words.get() + run.off + run.count);
+            dst.insert(dst.end(), plan.block_words + run.off, plan.block_words + run.off + run.count);
         }
         return r;
     }
@@ -436,15 +443,30 @@ struct PcsProof {
     std::vector<std::vector<uint32_t>> queried_values;
     uint64_t proof_of_work = 0;
     FriProof fri;
-    static void put_q(std::vector<uint32_t>& o, qm31 q) { o.insert(o.end(), q.c, q.c + 4); }
-    static void put_hash(std::vector<uint32_t>& o, const Hash& h) { o.insert(o.end(), h.begin(), h.end()); }
-    static void put_dec(std::vector<uint32_t>& o, const MerkleDecommitment& d) {
+    // A sink with the two vector operations the writers use, over a caller's buffer: words past the capacity are counted, not
+    // written (the caller compares size() with the capacity afterwards).
+    struct RawSink {
+        uint32_t* out;
+        size_t cap, n = 0;
+        int end() const { return 0; }
+        void reserve(size_t) {}
+        void push_back(uint32_t v) { if (n < cap) out[n] = v; n++; }
+        template <class It> void insert(int, It b, It e) {
+            size_t k = (size_t)(e - b);
+            if (n + k <= cap && k) memcpy(out + n, &*b, k * 4);
+            n += k;
+        }
+        size_t size() const { return n; }
+    };
+    template <class O> static void put_q(O& o, qm31 q) { o.insert(o.end(), q.c, q.c + 4); }
+    template <class O> static void put_hash(O& o, const Hash& h) { o.insert(o.end(), h.begin(), h.end()); }
+    template <class O> static void put_dec(O& o, const MerkleDecommitment& d) {
         o.push_back((uint32_t)d.hash_witness.size());
         for (auto& h : d.hash_witness) put_hash(o, h);
         o.push_back((uint32_t)d.column_witness.size());
         o.insert(o.end(), d.column_witness.begin(), d.column_witness.end());
     }
-    static void put_layer(std::vector<uint32_t>& o, const FriLayerProof& l) {
+    template <class O> static void put_layer(O& o, const FriLayerProof& l) {
         o.push_back((uint32_t)l.fri_witness.size());
         for (auto q : l.fri_witness) put_q(o, q);
         put_dec(o, l.decommitment);
@@ -452,6 +474,10 @@ struct PcsProof {
     }
     std::vector<uint32_t> to_words() const {
         std::vector<uint32_t> o;
+        write(o);
+        return o;
+    }
+    template <class O> void write(O& o) const {
         size_t expect = 1 << 16;
         for (auto& t : sampled_values) expect += 6 * t.size();
         for (auto& d : decommitments) expect += 8 * d.hash_witness.size() + d.column_witness.size();
@@ -472,7 +498,6 @@ struct PcsProof {
         for (auto& l : fri.inner_layers) put_layer(o, l);
         o.push_back((uint32_t)fri.last_layer_poly.size());
         for (auto q : fri.last_layer_poly) put_q(o, q);
-        return o;
     }
 };
 
@@ -1243,11 +1268,11 @@ static int pcs_prove_impl(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint
             }
         PcsProof proof = prover.prove_values(points, ch);
         prover.finish_timing();
-        std::vector<uint32_t> w = proof.to_words();
+        PcsProof::RawSink w{h_out, cap};  // straight into the caller's buffer: a proof of many columns is tens of megabytes
+        proof.write(w);
         w.insert(w.end(), ch.digest().begin(), ch.digest().end());
         *n_words = w.size();
         if (w.size() > cap) return zk_set_error_public(ctx, ZKB_EINVAL, "zkb_pcs_prove: output buffer too small");
-        memcpy(h_out, w.data(), w.size() * 4);
         return ZKB_OK;
     } catch (const Error& e) {
         return zk_set_error_public(ctx, e.code, e.what());
