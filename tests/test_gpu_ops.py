@@ -123,7 +123,7 @@ def test_bit_reverse_qm31(ctx, log_n):
 @pytest.mark.parametrize("log_size,ncols,with_prev", [(0, 0, False), (0, 3, False), (3, 1, False), (4, 16, False), (5, 17, True),
                                                       (6, 0, True), (6, 15, True), (7, 32, False), (8, 33, True), (10, 100, False),
                                                       (12, 256, False), (3, 4, True),
-                                                      # few rows, many columns: four lanes per row (merkle_layer_quad_kernel)
+                                                      # few rows, many columns: the variant that requests the next block's words ahead (merkle_layer_prefetch_kernel)
                                                       (0, 64, False), (2, 65, True), (5, 80, False), (6, 127, True), (7, 128, True),
                                                       (9, 1000, True), (11, 300, False), (13, 64, True)])
 def test_merkle_layer(ctx, oracle, log_size, ncols, with_prev, m31):

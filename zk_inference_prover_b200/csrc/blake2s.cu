@@ -57,88 +57,55 @@ __global__ void __launch_bounds__(256) merkle_layer_kernel(int log_size, const u
     store_hash(out, i, h, m31_out != 0);
 }
 
-// The same node hash with FOUR lanes per node, for layers of few rows and many columns (a segment's trees hold tens of
-// thousands of columns of 2^8 ... 2^11 rows: a leaf is then a chain of up to 2,000 dependent compressions, and one thread
-// per row leaves the GPU empty). Lane l of a quad runs the column step G(v_l, v_4+l, v_8+l, v_12+l) and, after rotating b,
-// c, d by one, two and three lanes, the diagonal step (RFC 7693 section 3.2); the message block of the quad sits in shared
-// memory, each lane having loaded four of its sixteen columns. c_sig_quad[r][l] packs the four message indices lane l needs
-// in round r (x, y of the column step, then of the diagonal step), four bits each.
-__constant__ uint16_t c_sig_quad[10][4] = {
-    {0x9810u, 0xba32u, 0xdc54u, 0xfe76u},
-    {0xc1aeu, 0x2084u, 0x7bf9u, 0x356du},
-    {0xea8bu, 0x630cu, 0x1725u, 0x49dfu},
-    {0x6297u, 0xa513u, 0x4cdu, 0x8febu},
-    {0x1e09u, 0xcb75u, 0x8642u, 0xd3fau},
-    {0xd4c2u, 0x57a6u, 0xefb0u, 0x9138u},
-    {0x705cu, 0x36f1u, 0x29deu, 0xb8a4u},
-    {0x5bdu, 0x4fe7u, 0x681cu, 0xa293u},
-    {0x2cf6u, 0x7d9eu, 0x413bu, 0x5a80u},
-    {0xbf2au, 0xe948u, 0xc367u, 0xd51u}};
-
-__global__ void __launch_bounds__(256) merkle_layer_quad_kernel(int log_size, const uint32_t* __restrict__ prev,
-                                                                const uint32_t* const* __restrict__ cols, int ncols, int m31_out,
-                                                                uint32_t* __restrict__ out) {
-    __shared__ uint32_t s_m[64][17];
-    const int l = threadIdx.x & 3, q = threadIdx.x >> 2;
+// The same node hash for layers of few rows and many columns (a segment's trees hold tens of thousands of columns of
+// 2^8 ... 2^11 rows: a leaf is then a chain of up to 2,000 compressions on a few hundred threads, and what a thread waits for
+// is the memory latency of its next sixteen column words, not the arithmetic). The next block's words are requested before
+// the current block is compressed. (Spreading a compression over four lanes was tried for these layers and is slower: the
+// four column steps of a round are already independent instructions of one thread, and the lane exchanges add latency.)
+__global__ void __launch_bounds__(256) merkle_layer_prefetch_kernel(int log_size, const uint32_t* __restrict__ prev,
+                                                                    const uint32_t* const* __restrict__ cols, int ncols, int m31_out,
+                                                                    uint32_t* __restrict__ out) {
     const size_t n = (size_t)1 << log_size;
-    size_t i = (size_t)blockIdx.x * 64 + q;
-    const bool live = i < n;
-    if (!live) i = n - 1;  // the quad still takes part in its warp's shuffles
-    uint32_t sig[10];
-#pragma unroll
-    for (int r = 0; r < 10; r++) sig[r] = c_sig_quad[r][l];
-    const uint32_t iv_lo = l == 0 ? B2S_IV0 : l == 1 ? B2S_IV1 : l == 2 ? B2S_IV2 : B2S_IV3;
-    const uint32_t iv_hi = l == 0 ? B2S_IV4 : l == 1 ? B2S_IV5 : l == 2 ? B2S_IV6 : B2S_IV7;
-    uint32_t ha = l == 0 ? (B2S_IV0 ^ 0x01010020u) : iv_lo, hb = iv_hi;  // h[l], h[4 + l]
-    uint32_t* m = s_m[q];
-    auto compress = [&](uint32_t t, bool last) {
-        __syncwarp();
-        uint32_t a = ha, b = hb, c = iv_lo, d = iv_hi;
-        if (l == 0) d ^= t;
-        if (l == 2 && last) d = ~d;
-#pragma unroll
-        for (int r = 0; r < 10; r++) {
-            const uint32_t s = sig[r];
-            B2S_G(a, b, c, d, m[s & 15u], m[(s >> 4) & 15u]);
-            b = __shfl_sync(0xffffffffu, b, (l + 1) & 3, 4);
-            c = __shfl_sync(0xffffffffu, c, (l + 2) & 3, 4);
-            d = __shfl_sync(0xffffffffu, d, (l + 3) & 3, 4);
-            B2S_G(a, b, c, d, m[(s >> 8) & 15u], m[(s >> 12) & 15u]);
-            b = __shfl_sync(0xffffffffu, b, (l + 3) & 3, 4);
-            c = __shfl_sync(0xffffffffu, c, (l + 2) & 3, 4);
-            d = __shfl_sync(0xffffffffu, d, (l + 1) & 3, 4);
-        }
-        ha ^= a ^ c;
-        hb ^= b ^ d;
-        __syncwarp();  // every lane is done with the block before the next one overwrites it
-    };
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    uint32_t h[8], m[16], nx[16];
+    blake2s_init(h);
     const uint32_t total = (prev ? 64u : 0u) + 4u * (uint32_t)ncols;
     uint32_t t = 0;
-    int c0 = 0;
+    int c = 0;
+    bool have = ncols > 16;  // a full block that is not the last one
+    if (have) {
+#pragma unroll
+        for (int k = 0; k < 16; k++) nx[k] = cols[k][i];
+    }
     if (prev) {
-        uint4 p = reinterpret_cast<const uint4*>(prev + 16 * i)[l];
-        m[4 * l] = p.x; m[4 * l + 1] = p.y; m[4 * l + 2] = p.z; m[4 * l + 3] = p.w;
+        const uint4* p = reinterpret_cast<const uint4*>(prev + 16 * i);
+        uint4 a = p[0], b = p[1], cc = p[2], d = p[3];
+        m[0] = a.x; m[1] = a.y; m[2] = a.z; m[3] = a.w; m[4] = b.x; m[5] = b.y; m[6] = b.z; m[7] = b.w;
+        m[8] = cc.x; m[9] = cc.y; m[10] = cc.z; m[11] = cc.w; m[12] = d.x; m[13] = d.y; m[14] = d.z; m[15] = d.w;
         t = 64;
-        compress(t, total == 64u);
+        blake2s_compress(h, m, t, total == 64u);
     }
-    while (ncols - c0 > 16) {
+    while (have) {
 #pragma unroll
-        for (int j = 0; j < 4; j++) m[4 * l + j] = cols[c0 + 4 * l + j][i];
-        c0 += 16;
+        for (int k = 0; k < 16; k++) m[k] = nx[k];
+        c += 16;
+        have = ncols - c > 16;
+        if (have) {
+#pragma unroll
+            for (int k = 0; k < 16; k++) nx[k] = cols[c + k][i];
+        }
         t += 64;
-        compress(t, false);
+        blake2s_compress(h, m, t, false);
     }
-    if (ncols - c0 > 0 || total == 0u) {
-        const int rem = ncols - c0;
+    if (ncols - c > 0 || total == 0u) {
+        int rem = ncols - c;
 #pragma unroll
-        for (int j = 0; j < 4; j++) m[4 * l + j] = (4 * l + j < rem) ? cols[c0 + 4 * l + j][i] : 0u;
+        for (int k = 0; k < 16; k++) m[k] = (k < rem) ? cols[c + k][i] : 0u;
         t += 4u * (uint32_t)rem;
-        compress(t, true);
+        blake2s_compress(h, m, t, true);
     }
-    if (live) {
-        out[8 * i + l] = m31_out ? reduce_word_m31(ha) : ha;
-        out[8 * i + 4 + l] = m31_out ? reduce_word_m31(hb) : hb;
-    }
+    store_hash(out, i, h, m31_out != 0);
 }
 
 // A leaf layer (no children) hashed in several calls, a run of columns at a time, so that hashing can
@@ -280,9 +247,10 @@ int zkb_merkle_layer(zkb_ctx* ctx, int log_size, const uint32_t* prev, const uin
     unsigned threads = n < 256 ? 32 : 256;
     unsigned blocks = (unsigned)((n + threads - 1) / threads);
     if (ncols >= 64 && n <= 8192) {
-        // few rows, a long chain of compressions each: four lanes per row
-        ProfScope prof(ctx, "merkle_layer_quad_kernel");
-        merkle_layer_quad_kernel<<<(unsigned)((n + 63) / 64), 256, 0, ctx->stream>>>(log_size, prev, (const uint32_t* const*)d_cols, ncols, m31_out, out);
+        // few rows, a long chain of compressions each: the next block's loads are in flight during a compression;
+        // small CTAs so that the few rows spread over all SMs
+        ProfScope prof(ctx, "merkle_layer_prefetch_kernel");
+        merkle_layer_prefetch_kernel<<<(unsigned)((n + 31) / 32), 32, 0, ctx->stream>>>(log_size, prev, (const uint32_t* const*)d_cols, ncols, m31_out, out);
         ZKB_LAUNCH_CHECK(ctx);
         return ZKB_OK;
     }
