@@ -98,7 +98,10 @@ int zkb_stark_prove_multi_host(zkb_ctx* ctx, int n_trees, const int* tree_ncols,
 /* GKR batch proof of n_inst instances. kinds: ZKB_GKR_*; d_nums[i] (NULL where the kind has no
  * numerators) and d_dens[i] are device arrays of ns[i] entries laid out as zkb_gkr_next_layer takes
  * them; they are not modified. The channel starts from Blake2sM31Channel::default() after
- * mix_u64(seed). */
+ * mix_u64(seed). One or two instances are proved with the Fiat-Shamir transcript resident on the device (no host
+ * round trip per sum-check round); larger batches (up to 8,192 instances) with one launch and one read-back per
+ * round for all instances. Both give the same words; the environment variable ZKB_GKR_DRIVER=resident|batch
+ * forces one of them (resident: at most 16 instances). */
 int zkb_gkr_prove_device(zkb_ctx* ctx, int n_inst, const int* kinds, const uint32_t* const* d_nums, const uint32_t* const* d_dens,
                          const uint64_t* ns, uint64_t seed, uint32_t* h_out, size_t cap, size_t* n_words);
 
