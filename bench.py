@@ -985,18 +985,36 @@ def run_decode_step(args, rank, world, local_rank):
             dist.barrier()
     names = ["layer_8b_s32_c2048"] * 32 + ["head_8b_s32_c2048"]
     mine = names[rank::world]
-    ctx = z.Context(device=local_rank, max_log_size=24)
-    shapes = {n: SegmentReplay(z, ctx, n, 0x5EED0006 + rank) for n in sorted(set(mine))}
+    # A segment's proof keeps the host busy for two thirds of its time, so a rank may run
+    # several proofs side by side: --streams S gives it S host threads, each with a context (a stream) of its own, and deals
+    # the rank's segments to them. The library allows one thread per context and any number of contexts.
+    S = max(1, args.streams)
+    ctxs = [z.Context(device=local_rank, max_log_size=24) for _ in range(S)]
+    ctx = ctxs[0]
+    work = [mine[k::S] for k in range(S)]
+    shapes = [{n: SegmentReplay(z, ctxs[k], n, 0x5EED0006 + rank + 100 * k) for n in sorted(set(work[k]))} for k in range(S)]
     sampler = ClockSampler(local_rank)
 
     def barrier():
-        ctx.sync()
+        for c in ctxs:
+            c.sync()
         if dist is not None:
             dist.barrier()
 
     def one_pass():
-        for n in mine:
-            shapes[n].step()
+        def run(k):
+            for n in work[k]:
+                shapes[k][n].step()
+            ctxs[k].sync()
+
+        if S == 1:
+            run(0)
+            return
+        threads = [threading.Thread(target=run, args=(k,)) for k in range(S)]
+        for th in threads:
+            th.start()
+        for th in threads:
+            th.join()
 
     for _ in range(args.warmup):
         one_pass()
@@ -1004,11 +1022,13 @@ def run_decode_step(args, rank, world, local_rank):
     if rank == 0:
         sampler.start()
     ctx.event_record(0)
+    t0 = time.perf_counter()
     for _ in range(args.steps):
         one_pass()
     ctx.event_record(1)
     barrier()
-    ms = ctx.event_elapsed_ms(0, 1) / args.steps
+    # one stream: CUDA events on it; several: the host clock between the two barriers (no single stream sees all the work)
+    ms = ctx.event_elapsed_ms(0, 1) / args.steps if S == 1 else (time.perf_counter() - t0) * 1e3 / args.steps
     clocks = sampler.stop() if rank == 0 else None
     if dist is not None:
         import torch
@@ -1023,10 +1043,12 @@ def run_decode_step(args, rank, world, local_rank):
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": "u32 (M31/QM31)", "data": "synthetic",
             "config": {"workload": "decode_step_replay_32_layer_segments_plus_head", "segments": len(names),
-                       "segments_on_rank_0": len(mine), "parallelism": f"segments round-robin over {world} GPU(s), no collective",
+                       "segments_on_rank_0": len(mine), "parallelism": f"segments round-robin over {world} GPU(s), no collective", "streams_per_gpu": S,
+                       "timer": "cuda events" if S == 1 else "host clock between barriers",
                        "l2": "inputs larger than L2"},
             "cells": cells, "cells_per_s": cells / (ms * 1e-3), "ms_per_segment": ms / len(mine), "clocks": clocks}))
-    ctx.close()
+    for c in ctxs:
+        c.close()
     if dist is not None:
         dist.destroy_process_group()
 
@@ -1101,6 +1123,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gpu-baseline", action="store_true")
     ap.add_argument("--gkr-log", type=int, default=24)
+    ap.add_argument("--streams", type=int, default=1, help="decode-step: proofs side by side on one GPU (host threads, one context each)")
     ap.add_argument("--segment", default="layer_8b_s32_c2048", help="segment-replay: a key of tests/golden/segment_shapes.json")
     ap.add_argument("--mode", default="proof", choices=["proof", "sharded-commit", "gkr", "freivalds", "constraints", "stark", "segment-replay", "decode-step", "witness"],
                     help="proof: one whole PCS proof per rank (ranks are independent); sharded-commit: one commitment over all ranks")
