@@ -114,3 +114,49 @@ def test_gkr_drivers_give_the_same_proof(ctx, oracle, monkeypatch, driver, spec)
         dev.append((kind, nb.ptr if nb else 0, db.ptr, den.shape[0]))
     got = ctx.gkr_prove_device(dev, 0x5EED0004)
     assert len(got) == len(want) and (got == want).all()
+
+
+def test_two_contexts_on_two_threads_prove_side_by_side(zkb, oracle):
+    """Several contexts may be used from different host threads at once (one thread per context): two threads, each with
+    its own context, prove a PCS opening over many short columns and a GKR batch of 20 instances three times over while the
+    other does the same; every proof must equal the one a single thread produced. (The decommitment's gather buffer is
+    per thread, the staging ring, scratch and stream per context.)"""
+    import threading
+
+    shape = [[6] * 40 + [4] * 70, [5] * 30, [8] * 8]
+    trees = [_trees(shape, 4300), _trees(shape, 4400)]
+    specs = [[(3, 8)] * 12 + [(1, 6)] * 5 + [(2, 7)] * 3, [(3, 9)] * 10 + [(0, 6)] * 6 + [(2, 5)] * 4]
+    kw = dict(pow_bits=0, log_blowup=1, n_queries=20)
+    want_pcs = [oracle.pcs_prove(t, **kw) for t in trees]
+    want_gkr = []
+    insts = []
+    for k, spec in enumerate(specs):
+        ins = [_instance(kd, lg, 5400 + 100 * k + 10 * i) for i, (kd, lg) in enumerate(spec)]
+        insts.append(ins)
+        want_gkr.append(oracle.gkr_prove(ins, 0x5EED0004 + k, verify=False))
+    errors = []
+
+    def worker(k):
+        try:
+            c = zkb.Context(device=0, max_log_size=12)
+            keep, dev = [], []
+            for kind, num, den in insts[k]:
+                nb = c.upload(num) if num is not None else None
+                db = c.upload(den)
+                keep += [nb, db]
+                dev.append((kind, nb.ptr if nb else 0, db.ptr, den.shape[0]))
+            for _ in range(3):
+                got = c.pcs_prove_host(trees[k], **kw)
+                assert len(got) == len(want_pcs[k]) and (got == want_pcs[k]).all()
+                gg = c.gkr_prove_device(dev, 0x5EED0004 + k)
+                assert len(gg) == len(want_gkr[k]) and (gg == want_gkr[k]).all()
+            c.close()
+        except BaseException as e:  # reported by the main thread
+            errors.append(repr(e))
+
+    threads = [threading.Thread(target=worker, args=(k,)) for k in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
