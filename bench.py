@@ -27,13 +27,12 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
-sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 SEED0 = 0x5EED0001
 
 
 def splitmix_column(seed, n):
-    from util import m31_column
+    from zk_inference_prover_b200.synth import m31_column
 
     return m31_column(seed, n)
 
@@ -409,7 +408,7 @@ def run_ours(args, rank, world, local_rank):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "u32 (M31)", "data": "synthetic", "config": workload_config(args),
             "e2e": {"value": e2e_value, "unit": "cells/s", "h2d_bytes_per_step": ncols * n * 4, "d2h_bytes_per_step": int(len(words_dev)) * 4,
-                    "ms_per_step": e2e_ms / args.steps},
+                    "ms_per_step": e2e_ms / args.steps, "host_memory": "pinned (zkb_host_alloc_pinned)"},
             "gpu_launches": launches * args.steps,
             "roofline": roofline, "cpu_baseline": cpu, "gpu_baseline": gpu_ref, "clocks": clocks,
             "proof_words": int(len(words_dev)), "proof_sha256": hashlib.sha256(words_dev.tobytes()).hexdigest(),
@@ -484,7 +483,7 @@ def run_gkr(args, rank):
     if rank != 0:
         return
     import zk_inference_prover_b200 as z
-    from util import m31_column, qm31_array
+    from zk_inference_prover_b200.synth import m31_column, qm31_array
 
     n = 1 << args.gkr_log
     ctx = z.Context(device=0, max_log_size=10)
@@ -535,7 +534,7 @@ def run_freivalds(args, rank):
     if rank != 0:
         return
     import zk_inference_prover_b200 as z
-    from util import qm31_array
+    from zk_inference_prover_b200.synth import qm31_array
 
     n_in, n_out, tokens, chunks, n_mats = 4096, 4096, 32, 256, 2
     pk, pq = n_out // chunks, -(-tokens // chunks)
@@ -610,7 +609,7 @@ def run_constraints(args, rank):
     (secure-field arithmetic). Inputs are resident; columns are larger than L2."""
     if rank != 0:
         return
-    import air_cases
+    from zk_inference_prover_b200 import air_cases
     import oracle
     import zk_inference_prover_b200 as z
     trace_log, eval_log = args.log_size, args.log_size + 1
@@ -722,7 +721,7 @@ def run_stark(args, rank):
     with the program's specialised kernel), composition commitment, mask-point sampling, quotients, FRI, grind, decommit."""
     if rank != 0:
         return
-    import air_cases
+    from zk_inference_prover_b200 import air_cases
     import oracle
     import zk_inference_prover_b200 as z
     from zk_inference_prover_b200 import air
@@ -1061,7 +1060,7 @@ def run_witness(args, rank):
     if rank != 0:
         return
     import zk_inference_prover_b200 as z
-    from witness_cases import dequant_case, tables_case
+    from zk_inference_prover_b200.witness_cases import dequant_case, tables_case
 
     peak, peak_kind = measured_hbm_peak()
     ctx = z.Context(device=0, max_log_size=10)

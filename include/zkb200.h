@@ -205,7 +205,9 @@ int zkb_gkr_next_layer(zkb_ctx* ctx, int kind, const uint32_t* num, const uint32
                        uint32_t* den_out);
 /* sum_as_poly_in_first_variable, device part: h_out[0..4] = sum at t=0, h_out[4..8] = sum at t=2
  * of eq_evals[i] * (numerator + lambda * denominator) over i < n/4, before the eq correction
- * (the caller applies eq_fixed_var_correction and gkr_prover.rs:884-923). n = layer entries. */
+ * (the caller applies eq_fixed_var_correction and gkr_prover.rs:884-923). n = layer entries.
+ * Alignment (checked, ZKB_EINVAL otherwise): den and eq_evals 16 bytes, QM31 numerators 16 bytes,
+ * M31 numerators 8 bytes. */
 int zkb_gkr_sum(zkb_ctx* ctx, int kind, const uint32_t* num, const uint32_t* den, size_t n, const uint32_t* eq_evals,
                 const uint32_t h_lambda[4], uint32_t h_out[8]);
 /* One sum-check round in one launch: fix_first_variable with challenge r on every column of the layer
@@ -227,12 +229,15 @@ int zkb_mle_fix_m31(zkb_ctx* ctx, const uint32_t* in, size_t n, const uint32_t h
  * loads it until the process exits. Same arithmetic and argument meaning as zkb_gkr_sum, except:
  * `device` and `stream` (a cudaStream_t, may be NULL for the default stream) say where to run,
  * d_out receives the 8 result words ON THE DEVICE (stream-ordered; nothing is copied or
- * synchronised), and n is limited to 2^28 entries (larger layers are refused with ZKB_EINVAL).
+ * synchronised), and n is limited to 2^28 entries. That limit is this entry point's stated contract
+ * (the kernel walks the layer with a fixed grid of at most 2,048 blocks, so the array's size does
+ * not depend on n); larger layers are refused with ZKB_EINVAL. Pointers must be aligned as for
+ * zkb_gkr_sum (checked on the host before anything is launched; d_out 4 bytes).
  * The first call on a device looks up the array's device address; make that call before any
  * stream capture. All calls share the one array, so calls that overlap on the same GPU (two
  * streams, two threads) race; issue them on one stream or order them yourself. It calls neither
  * cudaMalloc nor cudaFree nor any allocating routine. zkb_gkr_sum_noalloc_error() returns the text
- * of the last failure. */
+ * of the calling host thread's last failure. */
 int zkb_gkr_sum_noalloc(int device, void* stream, int kind, const uint32_t* num, const uint32_t* den, size_t n,
                         const uint32_t* eq_evals, const uint32_t h_lambda[4], uint32_t* d_out);
 const char* zkb_gkr_sum_noalloc_error(void);

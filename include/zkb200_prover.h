@@ -48,7 +48,11 @@ typedef struct zkb_pcs_config {
 int zkb_pcs_prove_device(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint32_t* const* d_cols, const uint32_t* col_logs,
                          const zkb_pcs_config* config, int two_sample_every, uint32_t* h_out, size_t cap, size_t* n_words,
                          float* h_phase_ms);
-/* Same with host columns (each is copied to the device first; h_cols are left untouched). */
+/* Same with host columns (each is copied to the device first; h_cols are left untouched). The copies
+ * run on a second stream under the interpolation, extension and leaf hashing of what has already
+ * arrived; that overlap only happens when the host columns are page-locked (zkb_host_alloc_pinned,
+ * or memory registered with cudaHostRegister). Pageable columns are accepted and give the same
+ * proof, but the driver stages them and the copy no longer overlaps compute. */
 int zkb_pcs_prove_host(zkb_ctx* ctx, int n_trees, const int* tree_ncols, const uint32_t* const* h_cols, const uint32_t* col_logs,
                        const zkb_pcs_config* config, int two_sample_every, uint32_t* h_out, size_t cap, size_t* n_words,
                        float* h_phase_ms);

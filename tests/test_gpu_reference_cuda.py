@@ -93,7 +93,10 @@ def _secure(seed, n):
 
 # From 8 points up: on a 4-point circle domain the reference's CUDA fold takes its y twiddle from the pad word of
 # the twiddle slice (stwo_cuda/cuda/poly_utils.cuh:7-18 on a slice of 2 words); its FFTs fall back to the CPU
-# below 16 points (backend/cuda/poly.rs:184-196) and FRI never folds a circle that small.
+# below 16 points (backend/cuda/poly.rs:184-196) and FRI never folds a circle that small. At 4 points it is this
+# library that equals CpuBackend (backend/cpu/fri.rs:95-123): tests/test_gpu_ops.py compares the fold with the CPU
+# oracle from a 2^2 domain up, and the oracle restates exactly that function; the reference's CUDA kernel is the
+# side that differs there.
 @pytest.mark.parametrize("log_n", [3, 5, 11, 17])
 def test_fri_folds_match_reference_cuda(ctx, refops, log_n):
     from util import qm31_array

@@ -5,11 +5,13 @@ or a thread that must not cause the device-wide synchronisation an allocation ca
 create a zkb context or let the library allocate scratch. This entry point keeps its scratch in an
 array built into the library. The test calls it through the C ABI twice in a row on the same
 inputs and on different ones, and requires the device-resident result to equal what zkb_gkr_sum
-returns, word for word (integer field arithmetic: the tolerance is zero). This file sorts last so
+returns and what the CPU oracle computes from the same inputs, word for word (integer field
+arithmetic: the tolerance is zero). This file sorts last so
 that a run stopping at the first failure has already run every other test."""
 import numpy as np
 import pytest
 
+import oracle
 from util import m31_column, qm31_array
 
 pytestmark = pytest.mark.gpu
@@ -36,6 +38,7 @@ def test_noalloc_matches_context_entry_point_twice(zkb, ctx, kind, log_n):
         zkb.gkr_sum_noalloc(0, ctx.stream(), kind, nb.ptr if nb else 0, db.ptr, n, eb.ptr, lam, out.ptr)
         got = out.download(shape=(2, 4))  # ordered after the kernel on the same stream
         assert (got == want).all()
+        assert (got == oracle.gkr_round_sums(kind, num, den, eq, lam)).all()  # not only the sibling entry point
         # and once more on identical inputs: the ticket and partials of the last call do not leak
         zkb.gkr_sum_noalloc(0, ctx.stream(), kind, nb.ptr if nb else 0, db.ptr, n, eb.ptr, lam, out.ptr)
         assert (out.download(shape=(2, 4)) == want).all()
@@ -51,3 +54,15 @@ def test_noalloc_rejects_oversize_and_bad_arguments(zkb, ctx):
         zkb.gkr_sum_noalloc(0, ctx.stream(), 1, 0, buf.ptr, 16, buf.ptr, lam, buf.ptr)  # generic layer without numerators
     with pytest.raises(zkb.ZkbError):
         zkb.gkr_sum_noalloc(0, ctx.stream(), 3, 0, buf.ptr, 24, buf.ptr, lam, buf.ptr)  # not a power of two
+    # misaligned pointers are refused on the host; nothing is launched
+    with pytest.raises(zkb.ZkbError) as e:
+        zkb.gkr_sum_noalloc(0, ctx.stream(), 3, 0, buf.ptr + 4, 16, buf.ptr, lam, buf.ptr)
+    assert "aligned" in str(e.value)
+    with pytest.raises(zkb.ZkbError):
+        zkb.gkr_sum_noalloc(0, ctx.stream(), 3, 0, buf.ptr, 16, buf.ptr + 8, lam, buf.ptr)
+    with pytest.raises(zkb.ZkbError):
+        zkb.gkr_sum_noalloc(0, ctx.stream(), 2, buf.ptr + 4, buf.ptr, 16, buf.ptr, lam, buf.ptr)
+    with pytest.raises(zkb.ZkbError):
+        zkb.gkr_sum_noalloc(0, ctx.stream(), 1, buf.ptr + 8, buf.ptr, 16, buf.ptr, lam, buf.ptr)
+    with pytest.raises(zkb.ZkbError):
+        ctx.gkr_sum(3, 0, buf.ptr + 4, 16, buf.ptr, lam)

@@ -10,6 +10,7 @@
 // element index, kbits >= nlayers) by 2^logw consecutive low indices (logw <= lo), so global
 // accesses are runs of 2^logw words. Zero-extension in the forward direction is implicit: the
 // layers above the coefficient count only copy, so the first pass reads coeffs[idx mod n].
+#include <mutex>
 #include <vector>
 
 #include "common.cuh"
@@ -20,6 +21,7 @@ namespace zk {
 constexpr int FFT_MAX_TILE_LOG = 13;    // 8192 words = 32 KiB of shared memory
 constexpr int FFT_CONTIG_LOG = 12;      // layers handled by the contiguous pass
 constexpr int FFT_STRIDED_LAYERS = 10;  // most layers in one strided pass
+constexpr int R32_MAX_DEVICES = 64;     // per-device launch set-up is cached for this many devices
 
 struct FftPass {
     int lo, kbits, nlayers, logw;
@@ -198,22 +200,33 @@ static int launch_step(zkb_ctx* ctx, uint32_t* const* d_dst, const uint32_t* con
     if (st.kind == 0) return launch_pass<INVERSE>(ctx, d_dst, d_src, src_mask, ncols, log_n, dom_log, st.generic, scale);
     const uint32_t* tower = INVERSE ? ctx->itw : ctx->tw;
     // Persistent launch: as many CTAs as fit on the device at once, each walking over work items.
-    static int ctas_per_sm[2][2] = {{0, 0}, {0, 0}};  // [contiguous/strided][forward/inverse]
-    static int n_sms = 0;
+    // The opt-in shared-memory size is a per-device function attribute and the SM count differs between
+    // devices, so both are looked up once per device (under a lock: contexts on several devices may be
+    // driven from several host threads).
     const size_t smem = st.kind == 1 ? r32_contig_smem(INVERSE) : r32_strided_smem(INVERSE);
     const int which = st.kind == 1 ? 0 : 1;
     const void* fn = st.kind == 1 ? (const void*)fft_r32_contig_kernel<INVERSE> : (const void*)fft_r32_strided_kernel<INVERSE>;
     const int threads = st.kind == 1 ? 32 * R32_CONTIG_WARPS : 256;
-    if (ctas_per_sm[which][INVERSE] == 0) {
-        ZKB_CUDA(ctx, cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        int k = 0;
-        ZKB_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&k, fn, threads, smem));
-        ZKB_CUDA(ctx, cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, ctx->device));
-        ctas_per_sm[which][INVERSE] = k > 0 ? k : 1;
+    int ctas = 0, n_sms = 0;
+    {
+        static std::mutex mu;
+        static int s_ctas[R32_MAX_DEVICES][2][2];  // [device][contiguous/strided][forward/inverse]; 0 = not set up
+        static int s_sms[R32_MAX_DEVICES];
+        ZKB_CHECK_ARG(ctx, ctx->device >= 0 && ctx->device < R32_MAX_DEVICES);
+        std::lock_guard<std::mutex> lock(mu);
+        if (s_ctas[ctx->device][which][INVERSE] == 0) {
+            ZKB_CUDA(ctx, cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            int k = 0;
+            ZKB_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&k, fn, threads, smem));
+            ZKB_CUDA(ctx, cudaDeviceGetAttribute(&s_sms[ctx->device], cudaDevAttrMultiProcessorCount, ctx->device));
+            s_ctas[ctx->device][which][INVERSE] = k > 0 ? k : 1;
+        }
+        ctas = s_ctas[ctx->device][which][INVERSE];
+        n_sms = s_sms[ctx->device];
     }
     size_t items = st.kind == 1 ? (((size_t)ncols << (log_n - 10)) + R32_CONTIG_WARPS - 1) / R32_CONTIG_WARPS
                                 : ((size_t)ncols << (log_n - 13));
-    size_t max_ctas = (size_t)n_sms * ctas_per_sm[which][INVERSE];
+    size_t max_ctas = (size_t)n_sms * ctas;
     unsigned grid = (unsigned)(items < max_ctas ? items : max_ctas);
     ProfScope prof(ctx, st.kind == 1 ? (INVERSE ? "fft_r32_contig_kernel<inverse>" : "fft_r32_contig_kernel<forward>")
                                      : (INVERSE ? "fft_r32_strided_kernel<inverse>" : "fft_r32_strided_kernel<forward>"));

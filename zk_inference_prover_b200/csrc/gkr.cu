@@ -212,6 +212,10 @@ int zkb_gkr_sum(zkb_ctx* ctx, int kind, const uint32_t* num, const uint32_t* den
     if (!ctx) return ZKB_EINVAL;
     ZKB_CHECK_ARG(ctx, kind >= 0 && kind <= 3 && den && eq_evals && h_lambda && h_out && n >= 2 && (n & (n - 1)) == 0);
     ZKB_CHECK_ARG(ctx, (kind != ZKB_GKR_LOGUP_GENERIC && kind != ZKB_GKR_LOGUP_MULTIPLICITIES) || num != nullptr);
+    // the kernel reads QM31 entries with 16-byte loads and M31 numerators in pairs (8-byte loads)
+    ZKB_CHECK_ARG(ctx, (((uintptr_t)den | (uintptr_t)eq_evals) & 15) == 0);
+    ZKB_CHECK_ARG(ctx, kind != ZKB_GKR_LOGUP_GENERIC || ((uintptr_t)num & 15) == 0);
+    ZKB_CHECK_ARG(ctx, kind != ZKB_GKR_LOGUP_MULTIPLICITIES || ((uintptr_t)num & 7) == 0);
     DeviceGuard g(ctx);
     size_t n_terms = n / 4;
     if (n_terms == 0) {
@@ -285,7 +289,7 @@ static __device__ __align__(256) uint32_t g_noalloc_scratch[8 * NOALLOC_MAX_BLOC
 
 constexpr int NOALLOC_MAX_DEVICES = 64;
 static uint32_t* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};  // device address of the array, per device
-static char g_noalloc_err[256] = "";
+static thread_local char g_noalloc_err[256] = "";  // per host thread: concurrent failing calls do not garble it
 
 }  // namespace zk
 
@@ -300,7 +304,12 @@ int zkb_gkr_sum_noalloc(int device, void* stream, int kind, const uint32_t* num,
     if (kind < 0 || kind > 3 || !den || !eq_evals || !h_lambda || !d_out) return fail(ZKB_EINVAL, "null pointer or unknown layer kind");
     if ((kind == ZKB_GKR_LOGUP_GENERIC || kind == ZKB_GKR_LOGUP_MULTIPLICITIES) && !num) return fail(ZKB_EINVAL, "this layer kind needs numerators");
     if (n < 4 || (n & (n - 1))) return fail(ZKB_EINVAL, "n must be a power of two, at least 4");
-    if (n > NOALLOC_MAX_ENTRIES) return fail(ZKB_EINVAL, "layer larger than the built-in scratch allows (2^28 entries at most)");
+    if (n > NOALLOC_MAX_ENTRIES) return fail(ZKB_EINVAL, "layer larger than this entry point's stated limit (2^28 entries at most)");
+    // misaligned pointers would fault on the device (16-byte loads of QM31 entries, 8-byte loads of M31 pairs)
+    if ((((uintptr_t)den | (uintptr_t)eq_evals) & 15) != 0) return fail(ZKB_EINVAL, "den and eq_evals must be 16-byte aligned");
+    if (kind == ZKB_GKR_LOGUP_GENERIC && ((uintptr_t)num & 15) != 0) return fail(ZKB_EINVAL, "QM31 numerators must be 16-byte aligned");
+    if (kind == ZKB_GKR_LOGUP_MULTIPLICITIES && ((uintptr_t)num & 7) != 0) return fail(ZKB_EINVAL, "M31 numerators must be 8-byte aligned");
+    if (((uintptr_t)d_out & 3) != 0) return fail(ZKB_EINVAL, "d_out must be 4-byte aligned");
     int prev = -1;
     if (cudaGetDevice(&prev) != cudaSuccess) return fail(ZKB_ECUDA, "cudaGetDevice failed");
     if (prev != device && cudaSetDevice(device) != cudaSuccess) return fail(ZKB_ECUDA, "cudaSetDevice failed");

@@ -1209,6 +1209,7 @@ static void commit_input_trees(Device& dev, zkb_ctx* ctx, CommitmentSchemeProver
                 else if (fence_id >= 0) dev.check(zkb_h2d_overlapped(ctx, nullptr, nullptr, 0, fence_id));
                 run_bytes = 0;
             };
+            try {  // from the first enqueued copy on, no column may be freed while the copy stream still writes into it
             for (int t = 0; t < n_trees; t++)
                 for (int c = 0; c < tree_ncols[t]; c++, flat++) {
                     size_t bytes = (size_t)4 << col_logs[flat];
@@ -1225,10 +1226,9 @@ static void commit_input_trees(Device& dev, zkb_ctx* ctx, CommitmentSchemeProver
                     tree_fences[t].push_back(fence);
                     if (close) { flush(fence); since = 0; if (fence < 63) fence++; }
                 }
-            try {
                 for (int t = 0; t < n_trees; t++) prover.commit_evals(std::move(tree_cols[t]), ch, &tree_fences[t], &slabs[t]);
             } catch (...) {
-                zkb_sync(ctx);  // no column may be freed while the copy stream still writes into it
+                zkb_sync(ctx);
                 throw;
             }
         }
