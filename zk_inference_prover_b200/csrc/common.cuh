@@ -17,6 +17,11 @@ struct zkb_ctx {
     uint32_t* tw = nullptr;
     uint32_t* itw = nullptr;
     size_t tw_len = 0;
+    // The same two towers with every word doubled (2t < 2^32): what the radix-32 butterflies multiply by.
+    uint32_t* tw2 = nullptr;
+    uint32_t* itw2 = nullptr;
+    // One word the kernels with bounded waits set when a wait ran out (0 = none); read by zkb_sync.
+    unsigned int* dev_err = nullptr;
     // Staging ring for tables of column pointers (pinned host mirror + device copy).
     void** h_ring = nullptr;
     void** d_ring = nullptr;

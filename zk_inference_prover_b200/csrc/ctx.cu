@@ -61,6 +61,11 @@ __global__ void twiddle_tower_kernel(uint32_t* __restrict__ tw, uint32_t* __rest
     itw[t] = m31_inv(p.x);
 }
 
+__global__ void double_words_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, size_t len) {
+    size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < len) out[t] = in[t] << 1;
+}
+
 __global__ void gather_multi_kernel(const uint32_t* const* __restrict__ cols, int ncols, const uint32_t* __restrict__ idx,
                                     int nidx, uint32_t* __restrict__ out) {
     size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -104,6 +109,10 @@ int zkb_init(int device, int max_log_size, zkb_ctx** out) {
     ctx->tw_len = (size_t)1 << (max_log_size - 1);
     if (cudaMalloc(&ctx->tw, ctx->tw_len * 4) != cudaSuccess) return fail(ZKB_ENOMEM);
     if (cudaMalloc(&ctx->itw, ctx->tw_len * 4) != cudaSuccess) return fail(ZKB_ENOMEM);
+    if (cudaMalloc(&ctx->tw2, ctx->tw_len * 4) != cudaSuccess) return fail(ZKB_ENOMEM);
+    if (cudaMalloc(&ctx->itw2, ctx->tw_len * 4) != cudaSuccess) return fail(ZKB_ENOMEM);
+    if (cudaMalloc(&ctx->dev_err, 64) != cudaSuccess) return fail(ZKB_ENOMEM);
+    if (cudaMemsetAsync(ctx->dev_err, 0, 64, ctx->stream) != cudaSuccess) return fail(ZKB_ECUDA);
     ctx->ring_cap = RING_SLOTS;
     if (cudaMallocHost(&ctx->h_ring, ctx->ring_cap * sizeof(void*)) != cudaSuccess) return fail(ZKB_ENOMEM);
     if (cudaMalloc(&ctx->d_ring, ctx->ring_cap * sizeof(void*)) != cudaSuccess) return fail(ZKB_ENOMEM);
@@ -111,7 +120,7 @@ int zkb_init(int device, int max_log_size, zkb_ctx** out) {
     if (cudaMalloc(&ctx->scratch, ctx->scratch_words * 4) != cudaSuccess) return fail(ZKB_ENOMEM);
     if (cudaMalloc(&ctx->ticket, 64) != cudaSuccess) return fail(ZKB_ENOMEM);
     if (cudaMemsetAsync(ctx->ticket, 0, 64, ctx->stream) != cudaSuccess) return fail(ZKB_ECUDA);
-    if (cudaMallocHost(&ctx->h_small, SMALL_WORDS * 4) != cudaSuccess) return fail(ZKB_ENOMEM);
+    if (cudaMallocHost(&ctx->h_small, (SMALL_WORDS + 16) * 4) != cudaSuccess) return fail(ZKB_ENOMEM);
 
     {
         cudaMemPool_t pool;
@@ -126,6 +135,8 @@ int zkb_init(int device, int max_log_size, zkb_ctx** out) {
     if (cudaMemcpyToSymbolAsync(c_gen_pow2, g, sizeof(g), 0, cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess) return fail(ZKB_ECUDA);
     unsigned blocks = (unsigned)((ctx->tw_len + 255) / 256);
     twiddle_tower_kernel<<<blocks, 256, 0, ctx->stream>>>(ctx->tw, ctx->itw, ctx->tw_len);
+    double_words_kernel<<<blocks, 256, 0, ctx->stream>>>(ctx->tw, ctx->tw2, ctx->tw_len);
+    double_words_kernel<<<blocks, 256, 0, ctx->stream>>>(ctx->itw, ctx->itw2, ctx->tw_len);
     if (cudaGetLastError() != cudaSuccess) return fail(ZKB_ECUDA);
     if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) return fail(ZKB_ECUDA);
     *out = ctx;
@@ -138,6 +149,9 @@ int zkb_destroy(zkb_ctx* ctx) {
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     if (ctx->tw) cudaFree(ctx->tw);
     if (ctx->itw) cudaFree(ctx->itw);
+    if (ctx->tw2) cudaFree(ctx->tw2);
+    if (ctx->itw2) cudaFree(ctx->itw2);
+    if (ctx->dev_err) cudaFree(ctx->dev_err);
     if (ctx->h_ring) cudaFreeHost(ctx->h_ring);
     if (ctx->d_ring) cudaFree(ctx->d_ring);
     if (ctx->scratch) cudaFree(ctx->scratch);
@@ -165,7 +179,14 @@ int zkb_sync(zkb_ctx* ctx) {
     if (!ctx) return ZKB_EINVAL;
     DeviceGuard g(ctx);
     if (ctx->copy_stream) ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->copy_stream));
+    // a kernel whose bounded wait ran out has set the error word; report it here, where the host waits anyway
+    ZKB_CUDA(ctx, cudaMemcpyAsync(ctx->h_small + SMALL_WORDS, ctx->dev_err, 4, cudaMemcpyDeviceToHost, ctx->stream));
     ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->h_small[SMALL_WORDS] != 0) {
+        unsigned code = ctx->h_small[SMALL_WORDS];
+        cudaMemsetAsync(ctx->dev_err, 0, 4, ctx->stream);
+        return set_error(ctx, ZKB_ETIMEOUT, "zkb_sync: a device-side wait ran out of its iteration limit (code 0x%x); results of the calls since the last sync are not valid", code);
+    }
     return ZKB_OK;
 }
 

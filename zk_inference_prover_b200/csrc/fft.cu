@@ -10,6 +10,7 @@
 // element index, kbits >= nlayers) by 2^logw consecutive low indices (logw <= lo), so global
 // accesses are runs of 2^logw words. Zero-extension in the forward direction is implicit: the
 // layers above the coefficient count only copy, so the first pass reads coeffs[idx mod n].
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -198,15 +199,18 @@ template <bool INVERSE>
 static int launch_step(zkb_ctx* ctx, uint32_t* const* d_dst, const uint32_t* const* d_src, uint32_t src_mask, int ncols,
                        int log_n, int dom_log, const FftStep& st, uint32_t scale) {
     if (st.kind == 0) return launch_pass<INVERSE>(ctx, d_dst, d_src, src_mask, ncols, log_n, dom_log, st.generic, scale);
-    const uint32_t* tower = INVERSE ? ctx->itw : ctx->tw;
     // Persistent launch: as many CTAs as fit on the device at once, each walking over work items.
     // The opt-in shared-memory size is a per-device function attribute and the SM count differs between
     // devices, so both are looked up once per device (under a lock: contexts on several devices may be
     // driven from several host threads).
-    const size_t smem = st.kind == 1 ? r32_contig_smem(INVERSE) : r32_strided_smem(INVERSE);
+    static const int lw = []() { const char* e = getenv("ZKB_FFT_LW"); return e && e[0] == '2' ? 2 : e && e[0] == '4' ? 4 : 3; }();
+    const size_t smem = st.kind == 1 ? r32_contig_smem(INVERSE) : r32_strided_smem(lw);
     const int which = st.kind == 1 ? 0 : 1;
-    const void* fn = st.kind == 1 ? (const void*)fft_r32_contig_kernel<INVERSE> : (const void*)fft_r32_strided_kernel<INVERSE>;
-    const int threads = st.kind == 1 ? 32 * R32_CONTIG_WARPS : 256;
+    const void* fn = st.kind == 1 ? (const void*)fft_r32_contig_kernel<INVERSE>
+                     : lw == 3   ? (const void*)fft_r32_strided_kernel<INVERSE, 3>
+                     : lw == 4   ? (const void*)fft_r32_strided_kernel<INVERSE, 4>
+                                 : (const void*)fft_r32_strided_kernel<INVERSE, 2>;
+    const int threads = st.kind == 1 ? 32 * R32_CONTIG_WARPS : 32 << lw;
     int ctas = 0, n_sms = 0;
     {
         static std::mutex mu;
@@ -225,17 +229,28 @@ static int launch_step(zkb_ctx* ctx, uint32_t* const* d_dst, const uint32_t* con
         n_sms = s_sms[ctx->device];
     }
     size_t items = st.kind == 1 ? (((size_t)ncols << (log_n - 10)) + R32_CONTIG_WARPS - 1) / R32_CONTIG_WARPS
-                                : ((size_t)ncols << (log_n - 13));
+                                : ((size_t)ncols << (log_n - 10 - lw));
     size_t max_ctas = (size_t)n_sms * ctas;
     unsigned grid = (unsigned)(items < max_ctas ? items : max_ctas);
+    if (st.kind == 2) {
+        // a grid that is a multiple of the number of tile rows above the window lets every CTA keep one twiddle table
+        const unsigned n_a = 1u << (log_n - st.r32.lo - 10);
+        if (grid >= n_a) grid -= grid % n_a;
+    }
     ProfScope prof(ctx, st.kind == 1 ? (INVERSE ? "fft_r32_contig_kernel<inverse>" : "fft_r32_contig_kernel<forward>")
                                      : (INVERSE ? "fft_r32_strided_kernel<inverse>" : "fft_r32_strided_kernel<forward>"));
     if (st.kind == 1)
         fft_r32_contig_kernel<INVERSE><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log,
-                                                                              st.r32, tower, scale);
+                                                                              st.r32, INVERSE ? ctx->itw2 : ctx->tw2, scale);
+    else if (lw == 3)
+        fft_r32_strided_kernel<INVERSE, 3><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log,
+                                                                                  st.r32, INVERSE ? ctx->itw2 : ctx->tw2, scale);
+    else if (lw == 4)
+        fft_r32_strided_kernel<INVERSE, 4><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log,
+                                                                                  st.r32, INVERSE ? ctx->itw2 : ctx->tw2, scale);
     else
-        fft_r32_strided_kernel<INVERSE><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log,
-                                                                               st.r32, tower, scale);
+        fft_r32_strided_kernel<INVERSE, 2><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log,
+                                                                                  st.r32, INVERSE ? ctx->itw2 : ctx->tw2, scale);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }
