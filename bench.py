@@ -369,15 +369,26 @@ def run_ours(args, rank, world, local_rank):
         lde_ms = sum(v[0] for _, v in fwd)
         achieved = ab["extend"] / (lde_ms * 1e-3) / 1e9 if lde_ms else None
         kern = {k: {"ms": round(v[0], 4), "launches": v[1]} for k, v in sorted(kernels.items(), key=lambda kv: -kv[1][0])}
-        # DRAM traffic of the two LDE launches from the ncu capture on 32 columns of this shape
-        # (profiles/fft_r32_lde_32x2e20.md: 714 + 1037 MB), scaled by the column count.
-        traffic = 1751.1e6 / 32 * ncols if (log_n, args.log_blowup) == (20, 2) else None
+        # DRAM traffic of the two LDE launches: ncu's dram__bytes_read + dram__bytes_write on 32 columns of this shape
+        # (137 + 482 MB for the wide pass, 569 + 479 MB for the twelve-layer contiguous pass), scaled by the column
+        # count; a figure from a past capture, not measured in this run.
+        traffic = 1666.6e6 / 32 * ncols if (log_n, args.log_blowup) == (20, 2) else None
+        # The passes are bound by instruction issue: report them against the measured rate of the butterfly
+        # arithmetic alone (the library's register-only butterfly kernel, timed in this run at this clock).
+        butterflies = ncols * (N // 2) * log_n  # the layers above the coefficient count only copy
+        ceiling = ctx.fft_arith_ceiling()
+        issue = {"bound": "instruction issue", "achieved": butterflies / (lde_ms * 1e-3) if lde_ms else None, "peak": ceiling,
+                 "unit": "butterflies/s", "frac": butterflies / (lde_ms * 1e-3) / ceiling if lde_ms else None,
+                 "peak_kind": "measured in this run: the same radix-32 butterfly stages on registers only, no global traffic, 2 CTAs x 256 threads per SM",
+                 "note": "about 10.5 machine instructions per butterfly at one instruction per cycle per scheduler saturate the "
+                         "ALU and FMA-heavy pipes together"}
         roofline = {"bound": "hbm", "kernel": "+".join(k for k, _ in fwd) + " (the launches of one LDE)",
                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak if achieved else None,
-                    "traffic": traffic, "peak_kind": peak_kind,
+                    "traffic": traffic, "traffic_source": "ncu capture on 32 of the columns, scaled by the column count (an estimate for this run)",
+                    "peak_kind": peak_kind, "issue": issue,
                     "note": "achieved = algorithmic bytes (read 2^log_size, write 2^(log_size+log_blowup) words per column) / the "
-                            "CUDA-event time of the two launches; the kernels are instruction-issue bound (about 10 instructions "
-                            "per butterfly, DRAM at 24-35% of peak), and the 2.6x traffic is the intermediate array of the two passes",
+                            "CUDA-event time of the two launches; the kernels are instruction-issue bound (see `issue`), DRAM at "
+                            "25-40% of peak; the 2.5x traffic is the array between the two passes",
                     "per_phase_ms": per, "kernels_one_step": kern,
                     "per_operator_gbs": {
                         "interpolate": ab["interpolate"] / (sum(v[0] for k, v in kernels.items() if "inverse" in k) * 1e-3) / 1e9,

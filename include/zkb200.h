@@ -70,6 +70,12 @@ int zkb_event_elapsed_ms(zkb_ctx* ctx, int a, int b, float* h_ms);
 int zkb_profile_begin(zkb_ctx* ctx);
 int zkb_profile_end(zkb_ctx* ctx, const char** h_names, float* h_ms, int* h_count, int cap, int* n);
 
+/* The arithmetic ceiling of the circle-FFT butterfly on this device (no counterpart in the reference): runs the
+ * radix-32 butterfly stages the FFT passes use on registers only, with no global traffic, at the passes' own
+ * occupancy, and returns butterflies per second. An FFT pass cannot run faster than its butterfly count divided
+ * by this figure; the benchmark reports the passes against it beside the HBM figure. Takes about a millisecond. */
+int zkb_fft_arith_ceiling(zkb_ctx* ctx, double* h_butterflies_per_s);
+
 /* ---- device columns (STWO/stwo_cuda/base_field_vec.rs:7-60, bindings.rs:84-103) ------------ */
 int zkb_malloc(zkb_ctx* ctx, size_t bytes, void** dptr);
 int zkb_free(zkb_ctx* ctx, void* dptr);

@@ -12,7 +12,7 @@ GKR_GRAND_PRODUCT, GKR_LOGUP_GENERIC, GKR_LOGUP_MULTIPLICITIES, GKR_LOGUP_SINGLE
 # Every symbol include/zkb200.h declares.
 EXPORTED_SYMBOLS = [
     "zkb_init", "zkb_destroy", "zkb_last_error", "zkb_sync", "zkb_get_stream", "zkb_max_log_size",
-    "zkb_event_record", "zkb_event_elapsed_ms", "zkb_profile_begin", "zkb_profile_end",
+    "zkb_event_record", "zkb_event_elapsed_ms", "zkb_profile_begin", "zkb_profile_end", "zkb_fft_arith_ceiling",
     "zkb_malloc", "zkb_free", "zkb_memset_zero", "zkb_h2d", "zkb_d2h", "zkb_h2d_async", "zkb_d2h_async", "zkb_h2d_overlapped", "zkb_wait_fence", "zkb_d2d",
     "zkb_host_alloc_pinned", "zkb_host_free_pinned", "zkb_gather_multi", "zkb_gather_hashes", "zkb_gather_words", "zkb_twiddles_d2h",
     "zkb_ifft_cols", "zkb_lde_cols", "zkb_eval_at_point_cols", "zkb_bit_reverse_m31", "zkb_bit_reverse_qm31",
@@ -276,6 +276,12 @@ class Context:
         n = C.c_int()
         self._check(self.lib.zkb_profile_end(self.h, names, ms, cnt, C.c_int(cap), C.byref(n)))
         return {names[i].decode(): (ms[i], cnt[i]) for i in range(n.value)}
+
+    def fft_arith_ceiling(self):
+        """Butterflies per second of the register-only butterfly kernel (the ceiling of the FFT passes)."""
+        v = C.c_double()
+        self._check(self.lib.zkb_fft_arith_ceiling(self.h, C.byref(v)))
+        return v.value
 
     def alloc_pinned(self, words):
         """Pinned host memory as a numpy uint32 array (freed with free_pinned)."""

@@ -128,16 +128,18 @@ __global__ void fft_small_kernel(uint32_t* const* __restrict__ dst_cols, const u
     for (int k = 0; k < n; k++) dst[k] = v[k];
 }
 
-// One launch of the plan: either a radix-32 window pass or a generic shared-memory pass.
+// One launch of the plan.
 struct FftStep {
-    int kind;  // 0: generic, 1: radix-32 contiguous, 2: radix-32 strided
+    int kind;  // 0: generic, 1: radix-32 contiguous (10 layers), 3: contiguous over 12 layers, 4: wide strided (8 layers)
     FftPass generic;
     R32Pass r32;
 };
 
 // Splits layers [0, nl) of an array of 2^log_n words into launches, lowest layers first.
-// Radix-32 windows need 2^10 rows (log_n >= 10) and 16-byte aligned columns; everything else
-// goes through the generic pass.
+// From 2^12 words up (16-byte aligned columns): the twelve-layer contiguous pass, then wide strided passes
+// of up to eight layers (their window slides down over layers already done when the array is short; those
+// layers are switched off). 2^10 and 2^11 words: the ten-layer contiguous pass and a generic pass for the
+// rest. Everything else goes through the generic pass.
 static std::vector<FftStep> plan_steps(int nl, int log_n, bool aligned) {
     std::vector<FftStep> v;
     if (log_n < 10 || !aligned) {
@@ -158,20 +160,25 @@ static std::vector<FftStep> plan_steps(int nl, int log_n, bool aligned) {
         }
         return v;
     }
-    int covered = nl < 10 ? nl : 10;
-    v.push_back({1, {}, {0, 0, covered}});
-    while (covered < nl) {
-        int take = nl - covered < 10 ? nl - covered : 10;
-        int lo = covered;
-        if (lo + 10 > log_n) lo = log_n - 10;
-        if (lo >= 3) {
-            v.push_back({2, {}, {lo, covered - lo, covered - lo + take}});
-        } else {
+    if (log_n < 12) {
+        int covered = nl < 10 ? nl : 10;
+        v.push_back({1, {}, {0, 0, covered}});
+        if (covered < nl) {  // log_n = 11, one layer left
+            int take = nl - covered;
             int logw = FFT_MAX_TILE_LOG - take;
             if (logw > 5) logw = 5;
             if (logw > covered) logw = covered;
             v.push_back({0, {covered, take, take, logw}, {}});
         }
+        return v;
+    }
+    int covered = nl < 12 ? nl : 12;
+    v.push_back({3, {}, {0, 0, covered}});
+    while (covered < nl) {  // here log_n >= 13
+        int take = nl - covered < 8 ? nl - covered : 8;
+        int lo = covered;
+        if (lo + 8 > log_n) lo = log_n - 8;
+        v.push_back({4, {}, {lo, covered - lo, covered - lo + take}});
         covered += take;
     }
     return v;
@@ -203,18 +210,16 @@ static int launch_step(zkb_ctx* ctx, uint32_t* const* d_dst, const uint32_t* con
     // The opt-in shared-memory size is a per-device function attribute and the SM count differs between
     // devices, so both are looked up once per device (under a lock: contexts on several devices may be
     // driven from several host threads).
-    static const int lw = []() { const char* e = getenv("ZKB_FFT_LW"); return e && e[0] == '2' ? 2 : e && e[0] == '4' ? 4 : 3; }();
-    const size_t smem = st.kind == 1 ? r32_contig_smem(INVERSE) : r32_strided_smem(lw);
-    const int which = st.kind == 1 ? 0 : 1;
-    const void* fn = st.kind == 1 ? (const void*)fft_r32_contig_kernel<INVERSE>
-                     : lw == 3   ? (const void*)fft_r32_strided_kernel<INVERSE, 3>
-                     : lw == 4   ? (const void*)fft_r32_strided_kernel<INVERSE, 4>
-                                 : (const void*)fft_r32_strided_kernel<INVERSE, 2>;
-    const int threads = st.kind == 1 ? 32 * R32_CONTIG_WARPS : 32 << lw;
+    const int which = st.kind == 1 ? 0 : st.kind == 3 ? 1 : 2;
+    const size_t smem = which == 0 ? r32_contig_smem(INVERSE) : which == 1 ? r32_c12_smem() : r32_wide_smem();
+    const void* fn = which == 0   ? (const void*)fft_r32_contig_kernel<INVERSE>
+                     : which == 1 ? (const void*)fft_r32_contig12_kernel<INVERSE>
+                                  : (const void*)fft_r32_wide_kernel<INVERSE>;
+    const int threads = which == 0 ? 32 * R32_CONTIG_WARPS : which == 1 ? 32 * R32_C12_WARPS : 256;
     int ctas = 0, n_sms = 0;
     {
         static std::mutex mu;
-        static int s_ctas[R32_MAX_DEVICES][2][2];  // [device][contiguous/strided][forward/inverse]; 0 = not set up
+        static int s_ctas[R32_MAX_DEVICES][3][2];  // [device][kernel][forward/inverse]; 0 = not set up
         static int s_sms[R32_MAX_DEVICES];
         ZKB_CHECK_ARG(ctx, ctx->device >= 0 && ctx->device < R32_MAX_DEVICES);
         std::lock_guard<std::mutex> lock(mu);
@@ -228,31 +233,44 @@ static int launch_step(zkb_ctx* ctx, uint32_t* const* d_dst, const uint32_t* con
         ctas = s_ctas[ctx->device][which][INVERSE];
         n_sms = s_sms[ctx->device];
     }
-    size_t items = st.kind == 1 ? (((size_t)ncols << (log_n - 10)) + R32_CONTIG_WARPS - 1) / R32_CONTIG_WARPS
-                                : ((size_t)ncols << (log_n - 10 - lw));
+    size_t items = which == 0   ? (((size_t)ncols << (log_n - 10)) + R32_CONTIG_WARPS - 1) / R32_CONTIG_WARPS
+                   : which == 1 ? ((size_t)ncols << (log_n - 12))
+                                : ((size_t)ncols << (log_n - 13));
     size_t max_ctas = (size_t)n_sms * ctas;
     unsigned grid = (unsigned)(items < max_ctas ? items : max_ctas);
-    if (st.kind == 2) {
+    if (which == 2) {
         // a grid that is a multiple of the number of tile rows above the window lets every CTA keep one twiddle table
-        const unsigned n_a = 1u << (log_n - st.r32.lo - 10);
+        const unsigned n_a = 1u << (log_n - st.r32.lo - 8);
         if (grid >= n_a) grid -= grid % n_a;
     }
-    ProfScope prof(ctx, st.kind == 1 ? (INVERSE ? "fft_r32_contig_kernel<inverse>" : "fft_r32_contig_kernel<forward>")
-                                     : (INVERSE ? "fft_r32_strided_kernel<inverse>" : "fft_r32_strided_kernel<forward>"));
-    if (st.kind == 1)
-        fft_r32_contig_kernel<INVERSE><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log,
-                                                                              st.r32, INVERSE ? ctx->itw2 : ctx->tw2, scale);
-    else if (lw == 3)
-        fft_r32_strided_kernel<INVERSE, 3><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log,
-                                                                                  st.r32, INVERSE ? ctx->itw2 : ctx->tw2, scale);
-    else if (lw == 4)
-        fft_r32_strided_kernel<INVERSE, 4><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log,
-                                                                                  st.r32, INVERSE ? ctx->itw2 : ctx->tw2, scale);
+    const uint32_t* tower = INVERSE ? ctx->itw2 : ctx->tw2;
+    ProfScope prof(ctx, which == 2 ? (INVERSE ? "fft_r32_wide_kernel<inverse>" : "fft_r32_wide_kernel<forward>")
+                                   : (INVERSE ? "fft_r32_contig_kernel<inverse>" : "fft_r32_contig_kernel<forward>"));
+    if (which == 0)
+        fft_r32_contig_kernel<INVERSE><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log, st.r32, tower, scale);
+    else if (which == 1)
+        fft_r32_contig12_kernel<INVERSE><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log, st.r32, tower, scale);
     else
-        fft_r32_strided_kernel<INVERSE, 2><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log,
-                                                                                  st.r32, INVERSE ? ctx->itw2 : ctx->tw2, scale);
+        fft_r32_wide_kernel<INVERSE><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log, st.r32, tower, scale);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
+}
+
+// The butterfly arithmetic alone: 32 values per thread, five layers per round, twiddles from shared memory,
+// no global traffic inside the loop. What this kernel reaches is the ceiling the FFT passes are bound by.
+__global__ void __launch_bounds__(256, 2) butterfly_ceiling_kernel(uint32_t* __restrict__ out, const uint32_t* __restrict__ tower, int rounds) {
+    __shared__ __align__(16) uint32_t tw[32];
+    if (threadIdx.x < 32) tw[threadIdx.x] = tower[32 + threadIdx.x];
+    __syncthreads();
+    uint32_t v[32];
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = tower[(threadIdx.x * 32 + i) & 1023] >> 1;
+    const uint32_t* const tb[5] = {tw, tw + 16, tw + 24, tw + 28, tw + 30};
+    for (int r = 0; r < rounds; r++) radix32_stage<false, false, true>(v, tb, 0, 0, 5);
+    uint32_t acc = 0;
+#pragma unroll
+    for (int i = 0; i < 32; i++) acc ^= v[i];
+    out[(size_t)blockIdx.x * 256 + threadIdx.x] = acc;
 }
 
 }  // namespace zk
@@ -267,6 +285,27 @@ static cpoint host_half_odds_initial(int log) {
 }
 
 extern "C" {
+
+int zkb_fft_arith_ceiling(zkb_ctx* ctx, double* h_butterflies_per_s) {
+    if (!ctx || !h_butterflies_per_s) return ZKB_EINVAL;
+    DeviceGuard g(ctx);
+    int n_sms = 0;
+    ZKB_CUDA(ctx, cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, ctx->device));
+    const int grid = n_sms * 2, rounds = 400;
+    ZKB_CHECK_ARG(ctx, (size_t)grid * 256 <= ctx->scratch_words && ctx->tw_len >= 1024);
+    if (!ctx->events[62]) { ZKB_CUDA(ctx, cudaEventCreate(&ctx->events[62])); }
+    if (!ctx->events[63]) { ZKB_CUDA(ctx, cudaEventCreate(&ctx->events[63])); }
+    butterfly_ceiling_kernel<<<grid, 256, 0, ctx->stream>>>(ctx->scratch, ctx->tw2, 20);  // warm-up
+    ZKB_CUDA(ctx, cudaEventRecord(ctx->events[62], ctx->stream));
+    butterfly_ceiling_kernel<<<grid, 256, 0, ctx->stream>>>(ctx->scratch, ctx->tw2, rounds);
+    ZKB_CUDA(ctx, cudaEventRecord(ctx->events[63], ctx->stream));
+    ZKB_LAUNCH_CHECK(ctx);
+    ZKB_CUDA(ctx, cudaEventSynchronize(ctx->events[63]));
+    float ms = 0.f;
+    ZKB_CUDA(ctx, cudaEventElapsedTime(&ms, ctx->events[62], ctx->events[63]));
+    *h_butterflies_per_s = (double)grid * 256 * 80.0 * rounds / ((double)ms * 1e-3);
+    return ZKB_OK;
+}
 
 int zkb_ifft_cols(zkb_ctx* ctx, uint32_t* const* cols, int ncols, int log_n) {
     if (!ctx) return ZKB_EINVAL;
@@ -323,12 +362,21 @@ int zkb_lde_cols(zkb_ctx* ctx, const uint32_t* const* coeffs, int ncols, int log
     if (log_n < 2) aligned = false;  // the staged copies move 16 bytes at a time
     auto steps = plan_steps(log_n, log_out, aligned);
     uint32_t src_mask = (1u << log_n) - 1u;
-    for (size_t p = steps.size(); p-- > 0;) {
-        bool first = p + 1 == steps.size();
-        rc = launch_step<false>(ctx, (uint32_t* const*)d_dst,
-                                first ? (const uint32_t* const*)d_src : (const uint32_t* const*)d_dst,
-                                first ? src_mask : 0xffffffffu, ncols, log_out, log_out, steps[p], 0u);
-        if (rc) return rc;
+    // ZKB_LDE_CHUNK=k runs all passes over k columns at a time, so that the array between two passes (2^log_out
+    // words per column) is still in the L2 cache when the next pass reads it. Off by default: at 256 x 2^22 the
+    // DRAM traffic drops but the many short launches cost more time than the traffic saves (the passes are bound
+    // by instruction issue, not by DRAM).
+    static const int env_chunk = []() { const char* e = getenv("ZKB_LDE_CHUNK"); return e ? atoi(e) : 0; }();
+    const int chunk = env_chunk > 0 && steps.size() > 1 ? env_chunk : ncols;
+    for (int c0 = 0; c0 < ncols; c0 += chunk) {
+        const int nc = ncols - c0 < chunk ? ncols - c0 : chunk;
+        for (size_t p = steps.size(); p-- > 0;) {
+            bool first = p + 1 == steps.size();
+            rc = launch_step<false>(ctx, (uint32_t* const*)d_dst + c0,
+                                    (first ? (const uint32_t* const*)d_src : (const uint32_t* const*)d_dst) + c0,
+                                    first ? src_mask : 0xffffffffu, nc, log_out, log_out, steps[p], 0u);
+            if (rc) return rc;
+        }
     }
     return ZKB_OK;
 }

@@ -136,13 +136,9 @@ constexpr int R32_PITCH = 36;          // words per staged row of 32 in the cont
 //               the layer-1 run), [480,511) the CTA-uniform stage (layers 5..9: 16 + 8 + 4 + 2 + 1 words)
 //   strided:    [0,992) the per-thread stage (512 + 256 + 128 + 64 + 32), [992,1023) the uniform stage
 constexpr int R32_TW_CONTIG = 512;
-constexpr int R32_TW_STRIDED = 1024;
 __host__ __device__ constexpr size_t r32_contig_smem(bool inverse) {
     (void)inverse;
     return (size_t)R32_CONTIG_WARPS * 2 * (R32_PITCH * 32 + R32_TW_CONTIG) * sizeof(uint32_t);
-}
-__host__ __device__ constexpr size_t r32_strided_smem(int lw) {
-    return (size_t)(2 * 33 * 32 * (1 << lw) + R32_TW_STRIDED) * sizeof(uint32_t);
 }
 // Word k (0..30) of a uniform-stage block: layer jj and index h within its run of 16 >> jj.
 __device__ __forceinline__ void uniform_slot(int k, int& jj, int& h) {
@@ -282,27 +278,67 @@ __global__ void __launch_bounds__(32 * R32_CONTIG_WARPS, 16 / R32_CONTIG_WARPS)
     cp_async_wait<0>();
 }
 
-__host__ __device__ constexpr int r32_strided_min_ctas(bool inverse, int lw) {
-    return lw >= 4 ? 1 : lw == 3 ? (inverse ? 3 : 2) : (inverse ? 6 : 4);
+// ---------------------------------------------------------------------------------------------------------
+// Wide strided pass: window bits [lo, lo+8), lo >= 5. A CTA of 256 threads owns a tile of 256 rows x 32
+// consecutive words, so every global access is a full 128-byte line (a row of the tile), in both directions.
+//   stage A (window bits 3..7, five layers): thread (warp, lane) holds rows warp + 8 p, p = 0..31, word lane;
+//     its twiddles depend only on p and on the bits above the window;
+//   stage B (window bits 0..2, three layers): thread (R = tid / 8, c = tid % 8) holds rows 8 R + q, q = 0..7,
+//     as 16-byte chunks (words 4 c .. 4 c + 3): 128-bit shared loads and 128-bit global stores, eight lanes per line.
+// The tile sits in shared memory densely (row m at word 32 m): stage A reads a row with one access per lane,
+// stage B reads a row with a quarter-warp, so neither pattern has a bank conflict and nothing is padded.
+// The twiddles of a tile depend only on the bits above the window (`a`): 255 words. A CTA keeps one value of
+// `a` for its whole life whenever the grid is a multiple of the number of values, else it reloads on change.
+constexpr int R32_WIDE_TILE = 256 * 32;  // words
+#ifndef R32_WIDE_CTAS
+#define R32_WIDE_CTAS 3
+#endif
+constexpr int R32_WIDE_TW = 256;         // [0,128) [128,192) [192,224): layers lo+0..lo+2; [224,255): layers lo+3..lo+7
+__host__ __device__ constexpr size_t r32_wide_smem() { return (size_t)(2 * R32_WIDE_TILE + R32_WIDE_TW) * sizeof(uint32_t); }
+
+// Three layers over the row index q of v[4 q + j] (eight rows x four words). tw0: 4, tw1: 2, tw2: 1 doubled twiddles.
+template <bool INVERSE>
+__device__ __forceinline__ void radix8x4_stage(uint32_t (&v)[32], const uint32_t* tw0, const uint32_t* tw1, const uint32_t* tw2,
+                                               int act_lo, int act_hi) {
+    auto layer = [&](auto JJ, const uint32_t* tw) {
+        constexpr int jj = decltype(JJ)::value;
+        if (jj < act_lo || jj >= act_hi) return;
+        uint32_t t[4];
+        if constexpr (jj == 0) { uint4 x = *reinterpret_cast<const uint4*>(tw); t[0] = x.x; t[1] = x.y; t[2] = x.z; t[3] = x.w; }
+        else if constexpr (jj == 1) { uint2 x = *reinterpret_cast<const uint2*>(tw); t[0] = x.x; t[1] = x.y; }
+        else t[0] = tw[0];
+#pragma unroll
+        for (int h = 0; h < (4 >> jj); h++) {
+#pragma unroll
+            for (int l = 0; l < (1 << jj); l++) {
+                const int q0 = (h << (jj + 1)) | l, q1 = q0 | (1 << jj);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    if (INVERSE) bf_inv<false>(v[4 * q0 + j], v[4 * q1 + j], t[h]);
+                    else bf_fwd<false>(v[4 * q0 + j], v[4 * q1 + j], t[h]);
+                }
+            }
+        }
+    };
+    if (INVERSE) {
+        layer(std::integral_constant<int, 0>{}, tw0); layer(std::integral_constant<int, 1>{}, tw1); layer(std::integral_constant<int, 2>{}, tw2);
+    } else {
+        layer(std::integral_constant<int, 2>{}, tw2); layer(std::integral_constant<int, 1>{}, tw1); layer(std::integral_constant<int, 0>{}, tw0);
+    }
 }
-// Strided pass: window bits [lo, lo+10), lo >= LW. CTA = 1024 rows x W = 2^LW consecutive words (W = 8 or 4).
-// Staging and exchange share one layout: row m at word W m + W (m / 32).
-// The twiddles of a tile depend only on the bits above the window (`a`), so a CTA keeps one value of `a` for
-// its whole life whenever the grid allows it (blockIdx mod the number of values) and loads that table of
-// 1023 doubled twiddles into shared memory once; otherwise it reloads the table when `a` changes.
-template <bool INVERSE, int LW>
-__global__ void __launch_bounds__(32 << LW, r32_strided_min_ctas(INVERSE, LW))
-    fft_r32_strided_kernel(uint32_t* const* __restrict__ dst_cols, const uint32_t* const* __restrict__ src_cols,
-                           uint32_t src_mask, int ncols, int log_n, int dom_log, R32Pass ps,
-                           const uint32_t* __restrict__ tower, uint32_t scale) {
+
+template <bool INVERSE>
+__global__ void __launch_bounds__(256, R32_WIDE_CTAS)
+    fft_r32_wide_kernel(uint32_t* const* __restrict__ dst_cols, const uint32_t* const* __restrict__ src_cols, uint32_t src_mask,
+                        int ncols, int log_n, int dom_log, R32Pass ps, const uint32_t* __restrict__ tower, uint32_t scale) {
     extern __shared__ __align__(16) uint32_t dyn_smem[];
     uint32_t* const buf0 = dyn_smem;
-    constexpr int W = 1 << LW, NT = 32 << LW;  // words per row of the tile, threads of the CTA
-    constexpr int BUF = 33 * 32 * W;            // row m at word W m + W (m / 32)
+    constexpr int BUF = R32_WIDE_TILE;
     uint32_t* const tw = dyn_smem + 2 * BUF;
-    const uint32_t w = threadIdx.x & (W - 1), tm = threadIdx.x >> LW;
-    const int wb_bits = ps.lo - LW;                // tiles across the words below the window
-    const int a_bits = log_n - ps.lo - 10;         // values of the bits above the window
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;  // stage A
+    const uint32_t R = threadIdx.x >> 3, c = threadIdx.x & 7;         // stage B
+    const int wb_bits = ps.lo - 5;          // tiles across the words below the window
+    const int a_bits = log_n - ps.lo - 8;   // values of the bits above the window
     const uint32_t n_a = 1u << a_bits;
     // Work space: (column, wb) pairs for a fixed `a` when the grid is a multiple of n_a, else (column, a, wb).
     const bool stationary = (gridDim.x % n_a) == 0;
@@ -324,7 +360,7 @@ __global__ void __launch_bounds__(32 << LW, r32_strided_min_ctas(INVERSE, LW))
             wb = tile & ((1u << wb_bits) - 1u);
             a = tile >> wb_bits;
         }
-        return (a << (ps.lo + 10)) | (wb << LW);
+        return (a << (ps.lo + 8)) | (wb << 5);
     };
     auto prefetch = [&](int b, size_t it) {
         uint32_t* buf = buf0 + b * BUF;
@@ -333,24 +369,21 @@ __global__ void __launch_bounds__(32 << LW, r32_strided_min_ctas(INVERSE, LW))
         const uint32_t* __restrict__ src = src_cols[col];
 #pragma unroll
         for (int k = 0; k < 8; k++) {
-            const uint32_t c = k * NT + threadIdx.x;  // 16-byte chunk: row c / (W/4), part c % (W/4)
-            const uint32_t m = c / (W / 4), part = c % (W / 4);
-            cp_async16(buf + W * m + W * (m >> 5) + 4 * part, src + ((base | (m << ps.lo) | (part << 2)) & src_mask));
+            const uint32_t ch = k * 256 + threadIdx.x;  // 16-byte chunk: row ch / 8, part ch % 8
+            const uint32_t m = ch >> 3, q = ch & 7;
+            cp_async16(buf + 32 * m + 4 * q, src + ((base | (m << ps.lo) | (q << 2)) & src_mask));
         }
     };
-    // [0,992) the per-thread stage (layers lo+0..lo+4: 512 + 256 + 128 + 64 + 32 words), [992,1023) the uniform stage
     auto load_twiddles = [&](uint32_t a) {
-        for (int c = threadIdx.x; c < 248; c += NT) {  // chunk c of 248: layers lo+0..lo+4 hold 128, 64, 32, 16, 8 chunks
-            const int jj = (c >= 128) + (c >= 192) + (c >= 224) + (c >= 240);
-            const int cc = c - (256 - (256 >> jj));
-            *reinterpret_cast<uint4*>(tw + 4 * c) =
-                *reinterpret_cast<const uint4*>(tower + (1u << (dom_log - ps.lo - jj - 1)) + (a << (9 - jj)) + 4 * cc);
-        }
-        if (threadIdx.x < 31) {
-            const int c = threadIdx.x;
+        const int t = threadIdx.x;
+        if (t < 224) {
+            const int jj = (t >= 128) + (t >= 192);
+            const int h = t - (256 - (256 >> jj));
+            tw[t] = tower[(1u << (dom_log - ps.lo - jj - 1)) + (a << (7 - jj)) + h];
+        } else if (t < 255) {
             int jj, h;
-            uniform_slot(c, jj, h);
-            tw[992 + c] = tower[(1u << (dom_log - ps.lo - 5 - jj - 1)) + (a << (4 - jj)) + h];
+            uniform_slot(t - 224, jj, h);
+            tw[t] = tower[(1u << (dom_log - ps.lo - 3 - jj - 1)) + (a << (4 - jj)) + h];
         }
     };
 
@@ -359,51 +392,195 @@ __global__ void __launch_bounds__(32 << LW, r32_strided_min_ctas(INVERSE, LW))
     if (item < total) prefetch(0, item);
     cp_async_commit();
     for (; item < total; item += stride) {
+        uint32_t col, a;
+        const uint32_t base = decode(item, col, a);
+        cp_async_wait<0>();
+        __syncthreads();
+        // Past this barrier every thread has finished the previous tile, so the other buffer (and, when `a`
+        // changes, the twiddle table) may be overwritten.
         if (item + stride < total) prefetch(cur ^ 1, item + stride);
         cp_async_commit();
-        uint32_t col, a;
-        const uint32_t base = decode(item, col, a) | w;
-        if (a != cur_a) {  // uniform over the CTA; the previous item's last barrier ordered every read of the old table
+        if (a != cur_a) {  // uniform over the CTA
             load_twiddles(a);
             cur_a = a;
+            __syncthreads();
         }
-        cp_async_wait<1>();
-        __syncthreads();
         uint32_t* __restrict__ s = buf0 + cur * BUF;
         uint32_t* __restrict__ dst = dst_cols[col];
-        const uint32_t* const tb_uni[5] = {tw + 992, tw + 1008, tw + 1016, tw + 1020, tw + 1022};
-        const uint32_t* const tb_lane[5] = {tw + 16 * tm, tw + 512 + 8 * tm, tw + 768 + 4 * tm, tw + 896 + 2 * tm, tw + 960 + tm};
+        const uint32_t* const tb_uni[5] = {tw + 224, tw + 240, tw + 248, tw + 252, tw + 254};
         uint32_t v[32];
         if (!INVERSE) {
 #pragma unroll
-            for (int p = 0; p < 32; p++) v[p] = s[33 * W * p + W * tm + w];
-            radix32_stage<false, false, true>(v, tb_uni, 5, ps.act_lo, ps.act_hi);
-            // each thread writes back exactly the words it read: no barrier needed before the write
+            for (int p = 0; p < 32; p++) v[p] = s[32 * (warp + 8 * p) + lane];
+            radix32_stage<false, false, true>(v, tb_uni, 3, ps.act_lo, ps.act_hi);
 #pragma unroll
-            for (int p = 0; p < 32; p++) s[33 * W * p + W * tm + w] = v[p];
+            for (int p = 0; p < 32; p++) s[32 * (warp + 8 * p) + lane] = v[p];  // the words this thread read itself
             __syncthreads();
 #pragma unroll
-            for (int p = 0; p < 32; p++) v[p] = s[33 * W * tm + W * p + w];
-            radix32_stage<false, false, true>(v, tb_lane, 0, ps.act_lo, ps.act_hi);
+            for (int q = 0; q < 8; q++) {
+                const uint4 x = *reinterpret_cast<const uint4*>(s + 32 * (8 * R + q) + 4 * c);
+                v[4 * q] = x.x; v[4 * q + 1] = x.y; v[4 * q + 2] = x.z; v[4 * q + 3] = x.w;
+            }
+            radix8x4_stage<false>(v, tw + 4 * R, tw + 128 + 2 * R, tw + 192 + R, ps.act_lo, ps.act_hi);
 #pragma unroll
-            for (int p = 0; p < 32; p++) dst[base | ((32u * tm + p) << ps.lo)] = v[p];
+            for (int q = 0; q < 8; q++)
+                *reinterpret_cast<uint4*>(dst + (base | ((8 * R + q) << ps.lo)) + 4 * c) =
+                    make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
         } else {
 #pragma unroll
-            for (int p = 0; p < 32; p++) v[p] = s[33 * W * tm + W * p + w];
-            radix32_stage<true, false, true>(v, tb_lane, 0, ps.act_lo, ps.act_hi);
+            for (int q = 0; q < 8; q++) {
+                const uint4 x = *reinterpret_cast<const uint4*>(s + 32 * (8 * R + q) + 4 * c);
+                v[4 * q] = x.x; v[4 * q + 1] = x.y; v[4 * q + 2] = x.z; v[4 * q + 3] = x.w;
+            }
+            radix8x4_stage<true>(v, tw + 4 * R, tw + 128 + 2 * R, tw + 192 + R, ps.act_lo, ps.act_hi);
 #pragma unroll
-            for (int p = 0; p < 32; p++) s[33 * W * tm + W * p + w] = v[p];
+            for (int q = 0; q < 8; q++)
+                *reinterpret_cast<uint4*>(s + 32 * (8 * R + q) + 4 * c) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
             __syncthreads();
 #pragma unroll
-            for (int p = 0; p < 32; p++) v[p] = s[33 * W * p + W * tm + w];
-            radix32_stage<true, false, true>(v, tb_uni, 5, ps.act_lo, ps.act_hi);
+            for (int p = 0; p < 32; p++) v[p] = s[32 * (warp + 8 * p) + lane];
+            radix32_stage<true, false, true>(v, tb_uni, 3, ps.act_lo, ps.act_hi);
 #pragma unroll
-            for (int p = 0; p < 32; p++) {
-                uint32_t x = scale ? m31_mul(v[p], scale) : v[p];
-                dst[base | ((tm + 32u * p) << ps.lo)] = x;
+            for (int p = 0; p < 32; p++) dst[(base | ((warp + 8 * p) << ps.lo)) + lane] = scale ? m31_mul(v[p], scale) : v[p];
+        }
+        cur ^= 1;
+    }
+    cp_async_wait<0>();
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Contiguous pass over twelve layers: window bits [0, 12). A CTA of four warps owns 4096 consecutive words:
+// four blocks of 1024, staged in the padded-row layout of the ten-layer pass (block b at b * 36 * 32). Layers
+// 10 and 11 pair words 1024 and 2048 apart: every thread runs them as radix-4 butterflies on the four blocks'
+// words at its own eight offsets (in place in shared memory); between that step and the ten layers each warp
+// then runs on its own block (as in fft_r32_contig_kernel) sits one barrier of the four warps.
+// Twiddles of the unit: layers 1..11 are runs of 1024 .. 1 words of the (doubled) tower, 2047 words in all.
+constexpr int R32_C12_WARPS = 4;
+constexpr int R32_C12_BUF = R32_C12_WARPS * R32_PITCH * 32;
+constexpr int R32_C12_TW = 2048;
+__host__ __device__ constexpr size_t r32_c12_smem() { return (size_t)2 * (R32_C12_BUF + R32_C12_TW) * sizeof(uint32_t); }
+
+template <bool INVERSE>
+__global__ void __launch_bounds__(32 * R32_C12_WARPS, 4)
+    fft_r32_contig12_kernel(uint32_t* const* __restrict__ dst_cols, const uint32_t* const* __restrict__ src_cols, uint32_t src_mask,
+                            int ncols, int log_n, int dom_log, R32Pass ps, const uint32_t* __restrict__ tower, uint32_t scale) {
+    extern __shared__ __align__(16) uint32_t dyn_smem[];
+    constexpr int BLK = R32_PITCH * 32, BUF = R32_C12_BUF, NT = 32 * R32_C12_WARPS;
+    uint32_t* const buf0 = dyn_smem;
+    uint32_t* const tw0 = dyn_smem + 2 * BUF;
+    const int warp = threadIdx.x >> 5, tm = threadIdx.x & 31, tid = threadIdx.x;
+    const int unit_bits = log_n - 12;
+    const size_t total = (size_t)ncols << unit_bits, stride = gridDim.x;
+    size_t item = blockIdx.x;
+
+    auto prefetch = [&](int b, size_t it) {
+        uint32_t* buf = buf0 + b * BUF;
+        const uint32_t* __restrict__ src = src_cols[it >> unit_bits];
+        const uint32_t un = (uint32_t)(it & (((size_t)1 << unit_bits) - 1));
+        const uint32_t base = un << 12;
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            const int ch = k * NT + tid;  // 16-byte chunk: block ch / 256, row (ch / 8) % 32, part ch % 8
+            const int blk = ch >> 8, r = (ch >> 3) & 31, q = ch & 7;
+            cp_async16(buf + blk * BLK + R32_PITCH * r + 4 * q, src + ((base + (blk << 10) + 32 * r + 4 * q) & src_mask));
+        }
+        uint32_t* tw = tw0 + b * R32_C12_TW;
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+            const int ch = k * NT + tid;  // chunk of layers 1..9: layer jj holds 256 >> (jj - 1) chunks
+            if (ch < 511) {
+                const int jj = 9 - (31 - __clz(511 - ch));
+                const int cc = ch - (512 - (512 >> (jj - 1)));
+                cp_async16(tw + 4 * ch, tower + (1u << (dom_log - jj - 1)) + (un << (11 - jj)) + 4 * cc);
             }
         }
-        __syncthreads();  // exchange reads are done before this buffer is refilled
+        if (tid < 2) cp_async4(tw + 2044 + tid, tower + (1u << (dom_log - 11)) + (un << 1) + tid);
+        else if (tid == 2) cp_async4(tw + 2046, tower + (1u << (dom_log - 12)) + un);
+    };
+    // Layers 10 and 11 on the four blocks' words at offset o of a block.
+    auto cross_blocks = [&](uint32_t* s, const uint32_t* tw, uint32_t* out, uint32_t out_scale) {
+        const bool on10 = 10 >= ps.act_lo && 10 < ps.act_hi, on11 = 11 >= ps.act_lo && 11 < ps.act_hi;
+        const uint32_t t10a = tw[2044], t10b = tw[2045], t11 = tw[2046];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int o = tid + NT * i;
+            const int pos = R32_PITCH * (o >> 5) + (o & 31);
+            uint32_t x0 = s[pos], x1 = s[BLK + pos], x2 = s[2 * BLK + pos], x3 = s[3 * BLK + pos];
+            if (!INVERSE) {
+                if (on11) { bf_fwd<false>(x0, x2, t11); bf_fwd<false>(x1, x3, t11); }
+                if (on10) { bf_fwd<false>(x0, x1, t10a); bf_fwd<false>(x2, x3, t10b); }
+                s[pos] = x0; s[BLK + pos] = x1; s[2 * BLK + pos] = x2; s[3 * BLK + pos] = x3;
+            } else {
+                if (on10) { bf_inv<false>(x0, x1, t10a); bf_inv<false>(x2, x3, t10b); }
+                if (on11) { bf_inv<false>(x0, x2, t11); bf_inv<false>(x1, x3, t11); }
+                if (out_scale) { x0 = m31_mul(x0, out_scale); x1 = m31_mul(x1, out_scale); x2 = m31_mul(x2, out_scale); x3 = m31_mul(x3, out_scale); }
+                out[o] = x0; out[1024 + o] = x1; out[2048 + o] = x2; out[3072 + o] = x3;
+            }
+        }
+    };
+
+    int cur = 0;
+    if (item < total) prefetch(0, item);
+    cp_async_commit();
+    for (; item < total; item += stride) {
+        cp_async_wait<0>();
+        __syncthreads();
+        // past this barrier every thread has finished the previous unit: the other buffer may be refilled
+        if (item + stride < total) prefetch(cur ^ 1, item + stride);
+        cp_async_commit();
+        uint32_t* __restrict__ sb = buf0 + cur * BUF;
+        uint32_t* __restrict__ s = sb + warp * BLK;
+        uint32_t* __restrict__ dst = dst_cols[item >> unit_bits] + ((size_t)(item & (((size_t)1 << unit_bits) - 1)) << 12);
+        const uint32_t* tw = tw0 + cur * R32_C12_TW;
+        const uint32_t* const tb_uni[5] = {tw + 1920 + 16 * warp, tw + 1984 + 8 * warp, tw + 2016 + 4 * warp, tw + 2032 + 2 * warp,
+                                           tw + 2040 + warp};
+        const uint32_t* const tb_lane[5] = {tw + 256 * warp + 8 * tm, tw + 256 * warp + 8 * tm, tw + 1024 + 128 * warp + 4 * tm,
+                                            tw + 1536 + 64 * warp + 2 * tm, tw + 1792 + 32 * warp + tm};
+        uint4* const row = reinterpret_cast<uint4*>(s + R32_PITCH * tm);
+        uint32_t v[32];
+        if (!INVERSE) {
+            cross_blocks(sb, tw, nullptr, 0u);
+            __syncthreads();
+#pragma unroll
+            for (int p = 0; p < 32; p++) v[p] = s[R32_PITCH * p + tm];
+            radix32_stage<false, false, true>(v, tb_uni, 5, ps.act_lo, ps.act_hi);
+#pragma unroll
+            for (int p = 0; p < 32; p++) s[R32_PITCH * p + tm] = v[p];
+            __syncwarp();
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                uint4 x = row[q];
+                v[4 * q] = x.x; v[4 * q + 1] = x.y; v[4 * q + 2] = x.z; v[4 * q + 3] = x.w;
+            }
+            radix32_stage<false, true, true>(v, tb_lane, 0, ps.act_lo, ps.act_hi);
+#pragma unroll
+            for (int q = 0; q < 8; q++) row[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            __syncwarp();
+            const int j = tm >> 3, c = tm & 7;
+#pragma unroll
+            for (int st = 0; st < 8; st++) {
+                const int r = 4 * st + j;
+                const uint4 x = *reinterpret_cast<const uint4*>(s + R32_PITCH * r + 4 * c);
+                *reinterpret_cast<uint4*>(dst + (warp << 10) + 32 * r + 4 * c) = x;
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                uint4 x = row[q];
+                v[4 * q] = x.x; v[4 * q + 1] = x.y; v[4 * q + 2] = x.z; v[4 * q + 3] = x.w;
+            }
+            radix32_stage<true, true, true>(v, tb_lane, 0, ps.act_lo, ps.act_hi);
+#pragma unroll
+            for (int q = 0; q < 8; q++) row[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            __syncwarp();
+#pragma unroll
+            for (int p = 0; p < 32; p++) v[p] = s[R32_PITCH * p + tm];
+            radix32_stage<true, false, true>(v, tb_uni, 5, ps.act_lo, ps.act_hi);
+#pragma unroll
+            for (int p = 0; p < 32; p++) s[R32_PITCH * p + tm] = v[p];
+            __syncthreads();
+            cross_blocks(sb, tw, dst, scale);
+        }
         cur ^= 1;
     }
     cp_async_wait<0>();
