@@ -187,6 +187,12 @@ int zkb_quot_numerators(zkb_ctx* ctx, const uint32_t* const* cols, int ncols, in
  * h_points (n_acc x 8) the sample points (x[4], y[4]). out has 2^lifting_log rows. */
 int zkb_quot_combine(zkb_ctx* ctx, int n_acc, const uint32_t* const* acc_cols, const int* h_acc_log,
                      const uint32_t* h_first_lin, const uint32_t* h_points, int lifting_log, uint32_t* const out[4]);
+/* The same for the rows [row_begin, row_begin + n_rows) of the lifting domain only: what one rank of a row-sharded
+ * commitment computes (no counterpart in the reference, which has no multi-device code). The accumulations and
+ * `out` hold only those rows (index 0 = row_begin); row_begin must be a multiple of 2^(lifting_log - acc_log + 1)
+ * for every accumulation, so that lifted pairs do not straddle the shard. */
+int zkb_quot_combine_rows(zkb_ctx* ctx, int n_acc, const uint32_t* const* acc_cols, const int* h_acc_log, const uint32_t* h_first_lin,
+                          const uint32_t* h_points, int lifting_log, size_t row_begin, size_t n_rows, uint32_t* const out[4]);
 
 /* ---- AccumulationOps (STWO/prover/air/accumulation.rs:127-145; cpu/accumulation.rs:9-48) --- */
 int zkb_accumulate(zkb_ctx* ctx, uint32_t* const col[4], const uint32_t* const other[4], size_t n);

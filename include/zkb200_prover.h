@@ -109,6 +109,40 @@ int zkb_stark_prove_multi_host(zkb_ctx* ctx, int n_trees, const int* tree_ncols,
 int zkb_gkr_prove_device(zkb_ctx* ctx, int n_inst, const int* kinds, const uint32_t* const* d_nums, const uint32_t* const* d_dens,
                          const uint64_t* ns, uint64_t seed, uint32_t* h_out, size_t cap, size_t* n_words);
 
+/* ---- One PCS proof over G devices (no counterpart in the reference, which has no multi-device code) ----------
+ * The proof zkb_pcs_prove_device gives for ONE tree of ncols_total columns of 2^log_n rows with one out-of-domain
+ * sample per column, word for word, computed by `world` ranks (a power of two that divides ncols_total), one
+ * context per rank. The library moves nothing between devices: between the calls below the caller performs the
+ * exchanges (NCCL, MPI, peer copies ...), in this order:
+ *   begin    every rank, same arguments except `rank`
+ *   extend   d_cols: this rank's ncols_total / world columns (evaluations, bit-reversed; consumed). Returns
+ *            *d_evals = [ncl][N] extended columns and *d_rows = [ncols_total][N / world] to receive into.
+ *            EXCHANGE: rows [d R, (d+1) R) of local column j go to rank d at d_rows + ((rank * ncl + j) * R)  (R = N / world)
+ *   subtree  hashes the Merkle subtree over the rank's rows. *d_root: its root (8 words, device);
+ *            EXCHANGE: all-gather the roots into *d_roots ([world][8], device), rank order
+ *   sample   top layers of the tree, channel, out-of-domain point; h_samples receives this rank's ncl x 4 words
+ *            EXCHANGE: all-gather the samples (host), rank order = global column order
+ *   quotients  mixes all samples, draws the coefficient, computes the quotients of the rank's rows:
+ *            d_quot_local[k] (R words) is coordinate k;
+ *            EXCHANGE: all-gather coordinate k into d_quot_full[k] (N words), for k = 0..3
+ *   fri_and_decommit  every rank runs the same FRI commitment, grind and query draw on the gathered column (it is
+ *            4 / ncols of the evaluations: sharding it would cost a collective per layer for less than 2 ms of work),
+ *            then serialises the decommitment of the queried rows it owns into h_part
+ *            EXCHANGE: gather the parts (host) on the rank that calls finish
+ *   finish   merges the parts into the proof words (plus the 8 words of the channel digest, as zkb_pcs_prove_device)
+ *   end      frees the session
+ * Errors: ZKB_EINVAL for shapes that do not shard (world not a power of two, fewer than 8 rows per rank). */
+typedef struct zkb_shard_pcs zkb_shard_pcs;
+int zkb_shard_pcs_begin(zkb_ctx* ctx, int rank, int world, int ncols_total, int log_n, const zkb_pcs_config* config, zkb_shard_pcs** out);
+int zkb_shard_pcs_extend(zkb_shard_pcs* s, uint32_t* const* d_cols, uint32_t** d_evals, uint32_t** d_rows);
+int zkb_shard_pcs_subtree(zkb_shard_pcs* s, uint32_t** d_root, uint32_t** d_roots);
+int zkb_shard_pcs_sample(zkb_shard_pcs* s, uint32_t* h_samples);
+int zkb_shard_pcs_quotients(zkb_shard_pcs* s, const uint32_t* h_all_samples, uint32_t* d_quot_local[4], uint32_t* d_quot_full[4]);
+int zkb_shard_pcs_fri_and_decommit(zkb_shard_pcs* s, uint32_t* h_part, size_t cap, size_t* n_words);
+int zkb_shard_pcs_finish(zkb_shard_pcs* s, const uint32_t* const* h_parts, const size_t* part_words, uint32_t* h_out, size_t cap,
+                         size_t* n_words);
+int zkb_shard_pcs_end(zkb_shard_pcs* s);
+
 #ifdef __cplusplus
 }
 #endif

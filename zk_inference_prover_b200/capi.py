@@ -16,13 +16,15 @@ EXPORTED_SYMBOLS = [
     "zkb_malloc", "zkb_free", "zkb_memset_zero", "zkb_h2d", "zkb_d2h", "zkb_h2d_async", "zkb_d2h_async", "zkb_h2d_overlapped", "zkb_wait_fence", "zkb_d2d",
     "zkb_host_alloc_pinned", "zkb_host_free_pinned", "zkb_gather_multi", "zkb_gather_hashes", "zkb_gather_words", "zkb_twiddles_d2h",
     "zkb_ifft_cols", "zkb_lde_cols", "zkb_eval_at_point_cols", "zkb_bit_reverse_m31", "zkb_bit_reverse_qm31",
-    "zkb_merkle_layer", "zkb_merkle_leaves_partial", "zkb_merkle_top", "zkb_fold_line_dalpha", "zkb_fold_circle_into_line_dalpha", "zkb_channel_mix_root_draw", "zkb_fold_line_dalpha_leaves", "zkb_fold_circle_into_line_dalpha_leaves", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine",
+    "zkb_merkle_layer", "zkb_merkle_leaves_partial", "zkb_merkle_top", "zkb_fold_line_dalpha", "zkb_fold_circle_into_line_dalpha", "zkb_channel_mix_root_draw", "zkb_fold_line_dalpha_leaves", "zkb_fold_circle_into_line_dalpha_leaves", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine", "zkb_quot_combine_rows",
     "zkb_accumulate", "zkb_lift_accumulate", "zkb_secure_powers", "zkb_gkr_eq_evals", "zkb_gkr_next_layer",
     "zkb_gkr_sum", "zkb_gkr_fix_and_sum", "zkb_mle_fix_qm31", "zkb_mle_fix_m31", "zkb_grind", "zkb_gkr_sum_noalloc", "zkb_gkr_sum_noalloc_error",
     "zkb_freivalds_scatter", "zkb_freivalds_acc", "zkb_witness_tables", "zkb_witness_dequant",
 ]
 # Every symbol include/zkb200_prover.h declares.
-PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_stark_prove_device", "zkb_stark_prove_host", "zkb_stark_prove_multi_device", "zkb_stark_prove_multi_host", "zkb_gkr_prove_device"]
+PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_stark_prove_device", "zkb_stark_prove_host", "zkb_stark_prove_multi_device", "zkb_stark_prove_multi_host", "zkb_gkr_prove_device",
+                  "zkb_shard_pcs_begin", "zkb_shard_pcs_extend", "zkb_shard_pcs_subtree", "zkb_shard_pcs_sample", "zkb_shard_pcs_quotients",
+                  "zkb_shard_pcs_fri_and_decommit", "zkb_shard_pcs_finish", "zkb_shard_pcs_end"]
 # Every symbol include/zkb200_air.h declares.
 AIR_SYMBOLS = ["zkb_air_compile", "zkb_air_analyze", "zkb_air_free", "zkb_air_specialize", "zkb_air_select", "zkb_air_get_stats", "zkb_constraint_quotients", "zkb_constraint_denom_inv"]
 PCS_PHASES = ["interpolate", "extend", "merkle", "sample", "quotients", "fri_commit", "grind", "decommit"]
@@ -101,6 +103,70 @@ def gkr_sum_noalloc(device, stream, kind, num_ptr, den_ptr, n, eq_ptr, lam, out_
                                  C.c_size_t(n), C.c_void_p(eq_ptr), l.ctypes.data_as(C.c_void_p), C.c_void_p(out_ptr))
     if rc != 0:
         raise ZkbError(rc, lib.zkb_gkr_sum_noalloc_error().decode())
+
+
+class ShardPcsSession:
+    """One rank's side of a PCS proof over several devices (include/zkb200_prover.h, zkb_shard_pcs_*). Every method is one
+    stage; the caller performs the exchange the stage's docstring names before calling the next one."""
+
+    def __init__(self, ctx, rank, world, ncols_total, log_n, cfg):
+        self.ctx, self.rank, self.world, self.ncols, self.log_n = ctx, rank, world, ncols_total, log_n
+        self.ncl = ncols_total // world
+        self.log_out = log_n + cfg.log_blowup_factor
+        self.N = 1 << self.log_out
+        self.R = self.N // world
+        self.h = C.c_void_p()
+        self._cfg = cfg
+        ctx._check(ctx.lib.zkb_shard_pcs_begin(ctx.h, C.c_int(rank), C.c_int(world), C.c_int(ncols_total), C.c_int(log_n), C.byref(cfg),
+                                               C.byref(self.h)))
+
+    def extend(self, col_ptrs):
+        """-> (evals address [ncl][N], rows address [ncols][R]). Then: rows [d R, (d+1) R) of local column j go to rank d at
+        rows + ((rank * ncl + j) * R) words."""
+        e, r = C.c_void_p(), C.c_void_p()
+        self.ctx._check(self.ctx.lib.zkb_shard_pcs_extend(self.h, _ptr_array(col_ptrs), C.byref(e), C.byref(r)))
+        return e.value, r.value
+
+    def subtree(self):
+        """-> (root address (8 words), roots address [world][8]). Then: all-gather the roots."""
+        a, b = C.c_void_p(), C.c_void_p()
+        self.ctx._check(self.ctx.lib.zkb_shard_pcs_subtree(self.h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    def sample(self):
+        """-> this rank's sampled values [ncl][4] (host). Then: all-gather them in rank order."""
+        out = np.empty((self.ncl, 4), np.uint32)
+        self.ctx._check(self.ctx.lib.zkb_shard_pcs_sample(self.h, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def quotients(self, all_samples):
+        """-> (addresses of the 4 local coordinate columns (R words), of the 4 full ones (N words)). Then: all-gather each."""
+        a = _u32(all_samples).reshape(-1)
+        loc, full = (C.c_void_p * 4)(), (C.c_void_p * 4)()
+        self.ctx._check(self.ctx.lib.zkb_shard_pcs_quotients(self.h, a.ctypes.data_as(C.c_void_p), loc, full))
+        return [loc[k] for k in range(4)], [full[k] for k in range(4)]
+
+    def fri_and_decommit(self, cap=1 << 22):
+        """-> this rank's part of the decommitment (host words). Then: gather the parts on the finishing rank."""
+        out = np.empty(cap, np.uint32)
+        n = C.c_size_t()
+        self.ctx._check(self.ctx.lib.zkb_shard_pcs_fri_and_decommit(self.h, out.ctypes.data_as(C.c_void_p), C.c_size_t(cap), C.byref(n)))
+        return out[: n.value].copy()
+
+    def finish(self, parts, cap=1 << 24):
+        """parts: every rank's part, in rank order -> proof words (with the channel digest appended)."""
+        keep = [_u32(p) for p in parts]
+        ptrs = (C.c_void_p * len(keep))(*[k.ctypes.data for k in keep])
+        sizes = (C.c_size_t * len(keep))(*[len(k) for k in keep])
+        out = np.empty(cap, np.uint32)
+        n = C.c_size_t()
+        self.ctx._check(self.ctx.lib.zkb_shard_pcs_finish(self.h, ptrs, sizes, out.ctypes.data_as(C.c_void_p), C.c_size_t(cap), C.byref(n)))
+        return out[: n.value].copy()
+
+    def close(self):
+        if self.h:
+            self.ctx.lib.zkb_shard_pcs_end(self.h)
+            self.h = C.c_void_p()
 
 
 class DeviceBuffer:
@@ -543,6 +609,10 @@ class Context:
         """trees_ptrs: per tree, device addresses of the trace columns (consumed). logs: flat log sizes."""
         return self._pcs(self.lib.zkb_pcs_prove_device, trees_ptrs, logs, pow_bits, log_blowup, log_last_layer, n_queries,
                          two_sample_every, cap, phases)
+
+    def shard_pcs(self, rank, world, ncols_total, log_n, pow_bits=10, log_blowup=1, log_last_layer=0, n_queries=3):
+        """A sharded-proof session of this rank (zkb_shard_pcs_*); see ShardPcsSession."""
+        return ShardPcsSession(self, rank, world, ncols_total, log_n, PcsConfig(pow_bits, log_blowup, log_last_layer, n_queries))
 
     def pcs_prove_host(self, trees, pow_bits=10, log_blowup=1, log_last_layer=0, n_queries=3, two_sample_every=0, cap=1 << 24,
                        phases=False):

@@ -143,8 +143,9 @@ struct MerkleProver {
 
     // :84-217 — the reference plans the indices of all layers on the host first (its phase 1) and then
     // reads layer by layer; here the reads of all layers join one GatherPlan.
+    // `hashes_per_layer`, when given, receives the number of witness hashes each layer contributed (largest layer first).
     PendingMerkle plan_decommit(GatherPlan& plan, const std::map<uint32_t, std::vector<size_t>>& queries_per_log_size,
-                                const std::vector<const BaseColumn*>& columns) const {
+                                const std::vector<const BaseColumn*>& columns, std::vector<size_t>* hashes_per_layer = nullptr) const {
         PendingMerkle pm;
         std::vector<const BaseColumn*> sorted(columns);
         std::stable_sort(sorted.begin(), sorted.end(), [](const BaseColumn* a, const BaseColumn* b) { return a->len() > b->len(); });
@@ -169,6 +170,7 @@ struct MerkleProver {
                 (col_queries.count(node) ? queried_nodes : witness_nodes).push_back(node);
             }
             for (size_t child : witness_children) pm.hash_slots.push_back(plan.add_hash(layers[log + 1].ptr() + 8 * child));
+            if (hashes_per_layer) hashes_per_layer->push_back(witness_children.size());
             if (!layer_cols.empty() && !merged_nodes.empty()) {
                 // every node of the layer is read once; the proof lists the queried nodes' values first, then the witnesses'
                 std::vector<const uint32_t*> ptrs;
@@ -1157,9 +1159,274 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
     return o;
 }
 
+// ------------------------------------------------------------------ one PCS proof over G ranks
+// The reference has no multi-device code; this is the proof of pcs_prove_impl (one tree of equally sized columns, one
+// out-of-domain sample per column) with the data-parallel phases sharded: rank r interpolates and extends ncols / G
+// columns; an exchange (the caller's: the library moves no data between devices) turns the column shards into row
+// shards [ncols][N / G]; every rank hashes the Merkle subtree over its rows, evaluates its own polynomials at the
+// out-of-domain point and computes the quotients of its rows. The Fiat-Shamir channel is replicated: every rank mixes
+// the same values in the same order. The quotient column (4 x N words, 1 / (ncols / 4) of the evaluations) is gathered
+// by the caller and every rank runs the same FRI commitment, grind and query draw on it; a rank then decommits the
+// queried rows it owns, and any rank merges the parts, layer by layer in rank order, into the single-device proof's words.
+struct ShardSession {
+    zkb_ctx* ctx;
+    Device dev;
+    int rank, world, log_g, ncols, ncl;
+    uint32_t log_n, log_out, log_local;
+    size_t N, R;
+    PcsConfig config;
+    Channel ch;
+    std::vector<BaseColumn> coeffs;    // views of the caller's local columns, interpolated in place
+    BaseColumn evals;                  // [ncl][N]
+    BaseColumn rows;                   // [ncols][R]; global column c = source rank * ncl + j
+    std::vector<BaseColumn> row_cols;  // views of `rows`
+    MerkleProver subtree, top;
+    BaseColumn roots;                  // [world][8]
+    Hash root{};
+    CirclePointQ oods{};
+    std::vector<qm31> samples;
+    SecureColumnByCoords quot_local, quot_full;
+    FriProver fri;
+    uint64_t nonce = 0;
+    std::vector<size_t> query_positions;
+    FriProof fri_proof;
+    MerkleDecommitment top_dec;
+    ShardSession(zkb_ctx* c) : ctx(c), dev(c) {}
+};
+
+}  // namespace b200
+
+struct zkb_shard_pcs { b200::ShardSession s; zkb_shard_pcs(zkb_ctx* c) : s(c) {} };
+
+namespace b200 {
+
+template <class F> static int shard_guard(zkb_ctx* ctx, F&& f) {
+    try {
+        f();
+        return ZKB_OK;
+    } catch (const Error& e) {
+        return zk_set_error_public(ctx, e.code, e.what());
+    } catch (const std::exception& e) {
+        return zk_set_error_public(ctx, ZKB_ENOMEM, e.what());
+    }
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" {
+
+int zkb_shard_pcs_begin(zkb_ctx* ctx, int rank, int world, int ncols_total, int log_n, const zkb_pcs_config* cfg, zkb_shard_pcs** out) {
+    if (!ctx || !cfg || !out) return ZKB_EINVAL;
+    *out = nullptr;
+    if (world < 1 || (world & (world - 1)) || rank < 0 || rank >= world || ncols_total < world || ncols_total % world || log_n < 1)
+        return zk_set_error_public(ctx, ZKB_EINVAL, "zkb_shard_pcs_begin: the rank count must be a power of two that divides the column count");
+    int log_g = 0;
+    while ((1 << log_g) < world) log_g++;
+    int log_out = log_n + (int)cfg->log_blowup_factor;
+    if (log_out > zkb_max_log_size(ctx) || log_out - log_g < 3)
+        return zk_set_error_public(ctx, ZKB_EINVAL, "zkb_shard_pcs_begin: every rank needs at least 8 rows and the context must cover the evaluation domain");
+    return shard_guard(ctx, [&] {
+        auto* h = new zkb_shard_pcs(ctx);
+        ShardSession& s = h->s;
+        s.rank = rank; s.world = world; s.log_g = log_g; s.ncols = ncols_total; s.ncl = ncols_total / world;
+        s.log_n = (uint32_t)log_n; s.log_out = (uint32_t)log_out; s.log_local = (uint32_t)(log_out - log_g);
+        s.N = (size_t)1 << log_out; s.R = s.N >> log_g;
+        s.config = PcsConfig{cfg->pow_bits, {cfg->log_blowup_factor, cfg->log_last_layer_degree_bound, cfg->n_queries, 1}};
+        s.config.mix_into(s.ch);
+        *out = h;
+    });
+}
+
+int zkb_shard_pcs_end(zkb_shard_pcs* h) {
+    if (!h) return ZKB_EINVAL;
+    zkb_ctx* ctx = h->s.ctx;
+    zkb_sync(ctx);
+    delete h;
+    return ZKB_OK;
+}
+
+int zkb_shard_pcs_extend(zkb_shard_pcs* h, uint32_t* const* d_cols, uint32_t** d_evals, uint32_t** d_rows) {
+    if (!h || !d_cols || !d_evals || !d_rows) return ZKB_EINVAL;
+    ShardSession& s = h->s;
+    return shard_guard(s.ctx, [&] {
+        std::vector<BaseColumn*> cols;
+        std::vector<const uint32_t*> src;
+        std::vector<uint32_t*> dst;
+        s.coeffs.clear();
+        for (int c = 0; c < s.ncl; c++) s.coeffs.push_back(BaseColumn::view(s.dev, d_cols[c], (size_t)1 << s.log_n));
+        for (auto& c : s.coeffs) cols.push_back(&c);
+        B200Backend::interpolate_columns(s.dev, cols);
+        s.evals = BaseColumn(s.dev, (size_t)s.ncl * s.N);
+        s.rows = BaseColumn(s.dev, (size_t)s.ncols * s.R);
+        for (int c = 0; c < s.ncl; c++) { src.push_back(s.coeffs[c].ptr()); dst.push_back(s.evals.ptr() + (size_t)c * s.N); }
+        s.dev.check(zkb_lde_cols(s.ctx, src.data(), s.ncl, (int)s.log_n, dst.data(), (int)s.log_out));
+        *d_evals = s.evals.ptr();
+        *d_rows = s.rows.ptr();
+    });
+}
+
+int zkb_shard_pcs_subtree(zkb_shard_pcs* h, uint32_t** d_root, uint32_t** d_roots) {
+    if (!h || !d_root || !d_roots) return ZKB_EINVAL;
+    ShardSession& s = h->s;
+    return shard_guard(s.ctx, [&] {
+        s.evals = BaseColumn();  // the column shards have been sent
+        s.row_cols.clear();
+        for (int c = 0; c < s.ncols; c++) s.row_cols.push_back(BaseColumn::view(s.dev, s.rows.ptr() + (size_t)c * s.R, s.R));
+        std::vector<const BaseColumn*> refs;
+        for (auto& c : s.row_cols) refs.push_back(&c);
+        s.subtree = MerkleProver::commit(s.dev, refs);
+        s.roots = BaseColumn(s.dev, (size_t)8 * s.world);
+        *d_root = s.subtree.layers[0].ptr();
+        *d_roots = s.roots.ptr();
+    });
+}
+
+int zkb_shard_pcs_sample(zkb_shard_pcs* h, uint32_t* h_samples) {
+    if (!h || !h_samples) return ZKB_EINVAL;
+    ShardSession& s = h->s;
+    return shard_guard(s.ctx, [&] {
+        // the top log2(G) layers over the gathered subtree roots: the same nodes the single-device tree has there
+        s.top = MerkleProver();
+        s.top.layers.resize(s.log_g + 1);
+        s.top.layers[s.log_g] = BaseColumn::view(s.dev, s.roots.ptr(), (size_t)8 * s.world);
+        for (int lg = s.log_g - 1; lg >= 0; lg--) s.top.layers[lg] = B200Backend::commit_on_layer(s.dev, (uint32_t)lg, &s.top.layers[lg + 1], {});
+        s.root = s.top.root(s.dev);
+        s.ch.mix_root(s.root);
+        s.oods = get_random_point(s.ch);
+        std::vector<const BaseColumn*> polys;
+        for (auto& c : s.coeffs) polys.push_back(&c);
+        auto vals = B200Backend::batch_eval_at_point(s.dev, polys, s.oods);
+        for (int c = 0; c < s.ncl; c++) memcpy(h_samples + 4 * c, vals[c].c, 16);
+    });
+}
+
+int zkb_shard_pcs_quotients(zkb_shard_pcs* h, const uint32_t* h_all_samples, uint32_t* d_quot_local[4], uint32_t* d_quot_full[4]) {
+    if (!h || !h_all_samples || !d_quot_local || !d_quot_full) return ZKB_EINVAL;
+    ShardSession& s = h->s;
+    return shard_guard(s.ctx, [&] {
+        s.samples.resize(s.ncols);
+        for (int c = 0; c < s.ncols; c++) memcpy(s.samples[c].c, h_all_samples + 4 * c, 16);
+        s.ch.mix_felts(s.samples);
+        qm31 random_coeff = s.ch.draw_secure_felt();
+        // compute_fri_quotients for one size group and one sample point, on this rank's rows: the numerators are
+        // row-local; the denominators need the rows' domain points (zkb_quot_combine_rows)
+        std::vector<const BaseColumn*> refs;
+        for (auto& c : s.row_cols) refs.push_back(&c);
+        ColumnSampleBatch batch{s.oods, {}};
+        qm31 pow = qm31_one();
+        for (int c = 0; c < s.ncols; c++) { batch.cols_vals_randpows.push_back({(size_t)c, s.samples[c], pow}); pow = pow * random_coeff; }
+        std::vector<AccumulatedNumerators> accs;
+        B200Backend::accumulate_numerators(s.dev, refs, {batch}, accs);
+        s.quot_local = SecureColumnByCoords(s.dev, s.R);
+        s.quot_full = SecureColumnByCoords(s.dev, s.N);
+        std::vector<const uint32_t*> cols;
+        for (auto p : accs[0].partial_numerators_acc.cptrs()) cols.push_back(p);
+        int acc_log = (int)s.log_out;
+        uint32_t pts[8];
+        memcpy(pts, s.oods.x.c, 16);
+        memcpy(pts + 4, s.oods.y.c, 16);
+        auto o = s.quot_local.ptrs();
+        s.dev.check(zkb_quot_combine_rows(s.ctx, 1, cols.data(), &acc_log, accs[0].first_linear_term_acc.c, pts, (int)s.log_out,
+                                          (size_t)s.rank * s.R, s.R, o.data()));
+        s.dev.check(zkb_sync(s.ctx));  // the accumulation is freed when this returns; the caller's gather may run on another stream
+        auto f = s.quot_full.ptrs();
+        for (int k = 0; k < 4; k++) { d_quot_local[k] = o[k]; d_quot_full[k] = f[k]; }
+    });
+}
+
+// Serialised part of one rank: [layers L][per layer: count, count x 8 words][n value words][values].
+int zkb_shard_pcs_fri_and_decommit(zkb_shard_pcs* h, uint32_t* h_part, size_t cap, size_t* n_words) {
+    if (!h || !h_part || !n_words) return ZKB_EINVAL;
+    ShardSession& s = h->s;
+    return shard_guard(s.ctx, [&] {
+        s.fri = FriProver::commit(s.dev, s.ch, s.config.fri, s.quot_full);
+        s.nonce = B200Backend::grind(s.dev, s.ch.pow_prefixed_digest(s.config.pow_bits), s.config.pow_bits);
+        s.ch.mix_u64(s.nonce);
+        GatherPlan plan;
+        auto fri_pending = s.fri.plan_decommit(plan, s.dev, s.ch, s.query_positions);
+        // this rank's rows among the queried ones, and the ranks that own any
+        std::vector<size_t> local, owners;
+        for (auto q : s.query_positions) {
+            if ((q >> s.log_local) == (size_t)s.rank) local.push_back(q - ((size_t)s.rank << s.log_local));
+            owners.push_back(q >> s.log_local);
+        }
+        std::vector<const BaseColumn*> refs;
+        for (auto& c : s.row_cols) refs.push_back(&c);
+        std::vector<size_t> per_layer, top_per_layer;
+        PendingMerkle pm = s.subtree.plan_decommit(plan, {{s.log_local, sorted_dedup(local)}}, refs, &per_layer);
+        PendingMerkle pt = s.top.plan_decommit(plan, {{(uint32_t)s.log_g, sorted_dedup(owners)}}, {}, &top_per_layer);
+        plan.execute(s.dev);
+        s.fri_proof = s.fri.finish_decommit(plan, fri_pending);
+        s.top_dec = pt.finish(plan).second;
+        auto mine = pm.finish(plan);
+        std::vector<uint32_t> o;
+        o.push_back((uint32_t)per_layer.size());
+        size_t at = 0;
+        for (size_t cnt : per_layer) {
+            o.push_back((uint32_t)cnt);
+            for (size_t k = 0; k < cnt; k++, at++) o.insert(o.end(), mine.second.hash_witness[at].begin(), mine.second.hash_witness[at].end());
+        }
+        o.push_back((uint32_t)mine.first.size());
+        o.insert(o.end(), mine.first.begin(), mine.first.end());
+        *n_words = o.size();
+        if (o.size() > cap) throw Error(ZKB_EINVAL, "zkb_shard_pcs_fri_and_decommit: output buffer too small");
+        memcpy(h_part, o.data(), o.size() * 4);
+    });
+}
+
+int zkb_shard_pcs_finish(zkb_shard_pcs* h, const uint32_t* const* h_parts, const size_t* part_words, uint32_t* h_out, size_t cap,
+                         size_t* n_words) {
+    if (!h || !h_parts || !part_words || !h_out || !n_words) return ZKB_EINVAL;
+    ShardSession& s = h->s;
+    return shard_guard(s.ctx, [&] {
+        PcsProof proof;
+        proof.commitments.push_back(s.root);
+        proof.sampled_values.emplace_back();
+        for (auto v : s.samples) proof.sampled_values[0].push_back({v});
+        MerkleDecommitment dec;
+        std::vector<uint32_t> values;
+        std::vector<size_t> cursor(s.world, 1);
+        size_t n_layers = 0;
+        for (int r = 0; r < s.world; r++) {
+            if (part_words[r] < 2) throw Error(ZKB_EINVAL, "zkb_shard_pcs_finish: truncated part");
+            if (r == 0) n_layers = h_parts[0][0];
+            else if (h_parts[r][0] != n_layers) throw Error(ZKB_EINVAL, "zkb_shard_pcs_finish: the parts disagree on the layer count");
+        }
+        // the single-device decommitment lists a layer's witness hashes in node order: rank order within each layer
+        for (size_t l = 0; l < n_layers; l++)
+            for (int r = 0; r < s.world; r++) {
+                const uint32_t* p = h_parts[r];
+                size_t& c = cursor[r];
+                if (c >= part_words[r]) throw Error(ZKB_EINVAL, "zkb_shard_pcs_finish: truncated part");
+                size_t cnt = p[c++];
+                if (c + 8 * cnt > part_words[r]) throw Error(ZKB_EINVAL, "zkb_shard_pcs_finish: truncated part");
+                for (size_t k = 0; k < cnt; k++, c += 8) { Hash hh; memcpy(hh.data(), p + c, 32); dec.hash_witness.push_back(hh); }
+            }
+        dec.hash_witness.insert(dec.hash_witness.end(), s.top_dec.hash_witness.begin(), s.top_dec.hash_witness.end());
+        for (int r = 0; r < s.world; r++) {
+            const uint32_t* p = h_parts[r];
+            size_t c = cursor[r];
+            if (c >= part_words[r]) throw Error(ZKB_EINVAL, "zkb_shard_pcs_finish: truncated part");
+            size_t cnt = p[c++];
+            if (c + cnt > part_words[r]) throw Error(ZKB_EINVAL, "zkb_shard_pcs_finish: truncated part");
+            values.insert(values.end(), p + c, p + c + cnt);
+        }
+        proof.decommitments.push_back(std::move(dec));
+        proof.queried_values.push_back(std::move(values));
+        proof.proof_of_work = s.nonce;
+        proof.fri = s.fri_proof;
+        PcsProof::RawSink w{h_out, cap};
+        proof.write(w);
+        w.insert(w.end(), s.ch.digest().begin(), s.ch.digest().end());
+        *n_words = w.size();
+        if (w.size() > cap) throw Error(ZKB_EINVAL, "zkb_shard_pcs_finish: output buffer too small");
+    });
+}
+
+}  // extern "C"
+
 
 // Commits the caller's trees in order (TreeBuilder::extend_evals + commit per tree), from device columns or from host
 // columns with the upload overlapped.

@@ -138,10 +138,13 @@ struct CombineArgs {
     int first;  // 1: overwrite out, 0: add to out (more than MAX_ACCS accumulations)
 };
 
+// Rows [row_begin, row_begin + n_rows) of the lifting domain; the accumulations and `out` are indexed from row_begin
+// (a row shard holds only its own rows; the whole domain is row_begin = 0, n_rows = 2^lifting_log).
 __global__ void __launch_bounds__(256) quot_combine_kernel(CombineArgs a, int lifting_log, Secure4 out,
-                                                           const uint32_t* __restrict__ tw) {
-    size_t row = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (row >= ((size_t)1 << lifting_log)) return;
+                                                           const uint32_t* __restrict__ tw, size_t row_begin, size_t n_rows) {
+    const size_t local = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (local >= n_rows) return;
+    const size_t row = row_begin + local;
     uint32_t px, py;
     half_coset_point(tw, lifting_log, (uint32_t)(row >> 1), px, py);
     if (row & 1) py = m31_neg(py);  // odd rows hold the conjugate point
@@ -167,18 +170,18 @@ __global__ void __launch_bounds__(256) quot_combine_kernel(CombineArgs a, int li
             uint32_t ninv = m31_mul(inv, pref[z]);
             inv = m31_mul(inv, norm[z]);
             cm31 dinv = {m31_mul(den[z].a, ninv), m31_mul(m31_neg(den[z].b), ninv)};
-            size_t li = ((row >> (a.log_ratio[z] + 1)) << 1) + (row & 1);
+            const size_t li = ((row >> (a.log_ratio[z] + 1)) << 1) + (row & 1) - (((row_begin >> (a.log_ratio[z] + 1)) << 1));
             qm31 num{{a.acc[z][0][li], a.acc[z][1][li], a.acc[z][2][li], a.acc[z][3][li]}};
             num = qm31_sub(num, qm31_mul_m31(a.first_lin[z], py));
             q = qm31_add(q, qm31_mul_cm31(num, dinv));
         }
     }
     if (!a.first) {
-        qm31 o{{out.c[0][row], out.c[1][row], out.c[2][row], out.c[3][row]}};
+        qm31 o{{out.c[0][local], out.c[1][local], out.c[2][local], out.c[3][local]}};
         q = qm31_add(q, o);
     }
 #pragma unroll
-    for (int k = 0; k < 4; k++) out.c[k][row] = q.c[k];
+    for (int k = 0; k < 4; k++) out.c[k][local] = q.c[k];
 }
 
 // Slow path for lifting domains of log size 1 and 2, whose points are not in the tower.
@@ -300,16 +303,29 @@ int zkb_quot_numerators(zkb_ctx* ctx, const uint32_t* const* cols, int ncols, in
 int zkb_quot_combine(zkb_ctx* ctx, int n_acc, const uint32_t* const* acc_cols, const int* h_acc_log,
                      const uint32_t* h_first_lin, const uint32_t* h_points, int lifting_log, uint32_t* const out[4]) {
     if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, lifting_log >= 1 && lifting_log <= ctx->max_log);
+    return zkb_quot_combine_rows(ctx, n_acc, acc_cols, h_acc_log, h_first_lin, h_points, lifting_log, 0, (size_t)1 << lifting_log, out);
+}
+
+int zkb_quot_combine_rows(zkb_ctx* ctx, int n_acc, const uint32_t* const* acc_cols, const int* h_acc_log, const uint32_t* h_first_lin,
+                          const uint32_t* h_points, int lifting_log, size_t row_begin, size_t n_rows, uint32_t* const out[4]) {
+    if (!ctx) return ZKB_EINVAL;
     ZKB_CHECK_ARG(ctx, n_acc >= 1 && acc_cols && h_acc_log && h_first_lin && h_points && out);
     ZKB_CHECK_ARG(ctx, lifting_log >= 1 && lifting_log <= ctx->max_log);
+    ZKB_CHECK_ARG(ctx, n_rows >= 1 && row_begin + n_rows <= ((size_t)1 << lifting_log));
+    const bool whole = row_begin == 0 && n_rows == ((size_t)1 << lifting_log);
+    // a shard starts on a row that every lifted accumulation starts a pair on, and small domains are not sharded
+    ZKB_CHECK_ARG(ctx, whole || (lifting_log > 2 && (row_begin & 1) == 0 && (n_rows & 1) == 0));
     Secure4 o;
     for (int q = 0; q < 4; q++) {
         ZKB_CHECK_ARG(ctx, out[q] != nullptr);
         o.c[q] = out[q];
     }
     for (int a = 0; a < n_acc; a++) ZKB_CHECK_ARG(ctx, h_acc_log[a] >= 1 && h_acc_log[a] <= lifting_log);
+    for (int a = 0; a < n_acc; a++)
+        ZKB_CHECK_ARG(ctx, whole || (row_begin & (((size_t)2 << (lifting_log - h_acc_log[a])) - 1)) == 0);
     DeviceGuard g(ctx);
-    size_t n = (size_t)1 << lifting_log;
+    size_t n = n_rows;
     for (int base = 0; base < n_acc; base += MAX_ACCS) {
         CombineArgs args;
         memset(&args, 0, sizeof(args));
@@ -336,7 +352,7 @@ int zkb_quot_combine(zkb_ctx* ctx, int n_acc, const uint32_t* const* acc_cols, c
             quot_combine_small_kernel<<<1, 32, 0, ctx->stream>>>(args, lifting_log, o, p0.x, p0.y, p1.x, p1.y);
         } else {
             ProfScope prof(ctx, "quot_combine_kernel");
-            quot_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(args, lifting_log, o, ctx->tw);
+            quot_combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(args, lifting_log, o, ctx->tw, row_begin, n_rows);
         }
         ZKB_LAUNCH_CHECK(ctx);
     }

@@ -145,3 +145,169 @@ class ContextOps:
 
     def sync(self):
         self.ctx.sync()
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# One whole PCS proof over G ranks (include/zkb200_prover.h, zkb_shard_pcs_*): the library computes, this class moves.
+
+class _Alias:
+    """A device range as something torch.as_tensor can alias (the CUDA array interface)."""
+
+    def __init__(self, ptr, words):
+        self.__cuda_array_interface__ = {"shape": (int(words),), "typestr": "<i4", "data": (int(ptr), False), "version": 2}
+
+
+class Exchange:
+    """The four data movements a sharded proof needs, over torch.distributed.
+
+    `nccl`: device tensors alias the library's buffers and the collectives are ordered on the context's own stream
+    (torch.cuda.ExternalStream), so nothing synchronises with the host. `gloo`: the ranges are staged through host
+    memory; this is what lets several ranks share one GPU in tests (no kernel of one rank waits on another rank:
+    every wait is a host-side collective) and what the CPU tests of this logic run on."""
+
+    def __init__(self, mem, device, group=None):
+        self.mem, self.device, self.group = mem, device, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.nccl = dist.get_backend(group) == "nccl"
+
+    def _dev(self, ptr, words):
+        return torch.as_tensor(_Alias(ptr, words), device=self.device)
+
+    def _stream(self):
+        if not self.nccl:
+            import contextlib
+
+            return contextlib.nullcontext()
+        return torch.cuda.stream(torch.cuda.ExternalStream(self.mem.stream(), device=self.device))
+
+    def rows_to_owners(self, evals_ptr, rows_ptr, ncl, N, R):
+        """Rows [d R, (d+1) R) of local column j go to rank d at rows + ((rank * ncl + j) * R): no repack on either
+        side, every piece is contiguous where it lies and where it lands."""
+        G, me = self.world, self.rank
+        if self.nccl:
+            with self._stream():
+                ev = self._dev(evals_ptr, ncl * N).view(ncl, G, R)
+                rw = self._dev(rows_ptr, G * ncl * R).view(G, ncl, R)
+                rw[me].copy_(ev[:, me, :])
+                ops = []
+                for peer in range(G):
+                    if peer == me:
+                        continue
+                    for j in range(ncl):
+                        ops.append(dist.P2POp(dist.isend, ev[j, peer], peer, group=self.group))
+                        ops.append(dist.P2POp(dist.irecv, rw[peer, j], peer, group=self.group))
+                if ops:
+                    for w in dist.batch_isend_irecv(ops):
+                        w.wait()
+            return
+        ev = torch.from_numpy(self.mem.read(evals_ptr, ncl * N).view("int32")).view(ncl, G, R)
+        rw = torch.empty((G, ncl, R), dtype=torch.int32)
+        rw[me].copy_(ev[:, me, :])
+        for peer in range(G):  # gloo: pairwise, the lower rank sends first
+            if peer == me:
+                continue
+            block = ev[:, peer, :].contiguous()
+            if me < peer:
+                dist.send(block, peer, group=self.group)
+                dist.recv(rw[peer], peer, group=self.group)
+            else:
+                dist.recv(rw[peer], peer, group=self.group)
+                dist.send(block, peer, group=self.group)
+        self.mem.write(rows_ptr, rw.numpy().view("uint32").reshape(-1))
+
+    def all_gather_device(self, src_ptr, dst_ptr, words):
+        """dst[r * words ...] <- src of rank r."""
+        if self.nccl:
+            with self._stream():
+                dist.all_gather_into_tensor(self._dev(dst_ptr, words * self.world), self._dev(src_ptr, words), group=self.group)
+            return
+        mine = torch.from_numpy(self.mem.read(src_ptr, words).view("int32"))
+        parts = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(parts, mine, group=self.group)
+        self.mem.write(dst_ptr, torch.cat(parts).numpy().view("uint32"))
+
+    def all_gather_host(self, arr):
+        """Equal-sized host arrays, concatenated in rank order."""
+        import numpy as np
+
+        mine = torch.from_numpy(np.ascontiguousarray(arr).view("int32").reshape(-1))
+        if self.nccl:
+            mine = mine.to(self.device)
+        parts = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(parts, mine, group=self.group)
+        return torch.cat(parts).cpu().numpy().view("uint32")
+
+    def all_gather_varlen(self, arr):
+        """Host arrays of different lengths -> list in rank order (on every rank)."""
+        import numpy as np
+
+        lens = self.all_gather_host(np.array([len(arr)], np.uint32))
+        cap = int(lens.max())
+        pad = np.zeros(cap, np.uint32)
+        pad[: len(arr)] = arr
+        flat = self.all_gather_host(pad).reshape(self.world, cap)
+        return [flat[r, : int(lens[r])].copy() for r in range(self.world)]
+
+
+class ContextMem:
+    """Raw device ranges of a zkb200 Context, for Exchange (`gloo` staging reads and writes them through the host)."""
+
+    def __init__(self, ctx):
+        self.ctx = ctx
+
+    def stream(self):
+        return self.ctx.stream()
+
+    def read(self, ptr, words):
+        import numpy as np
+
+        import ctypes as C
+
+        out = np.empty(int(words), np.uint32)
+        self.ctx._check(self.ctx.lib.zkb_d2h(self.ctx.h, out.ctypes.data_as(C.c_void_p), C.c_void_p(ptr), C.c_size_t(out.nbytes)))
+        return out
+
+    def write(self, ptr, arr):
+        import ctypes as C
+        import numpy as np
+
+        a = np.ascontiguousarray(arr, dtype=np.uint32)
+        self.ctx._check(self.ctx.lib.zkb_h2d(self.ctx.h, C.c_void_p(ptr), a.ctypes.data_as(C.c_void_p), C.c_size_t(a.nbytes)))
+
+
+def sharded_pcs_prove(session, exchange, col_ptrs, timings=None):
+    """Runs one sharded proof: `session` is this rank's ShardPcsSession (or an object with the same stages), `exchange`
+    an Exchange over the same ranks, col_ptrs this rank's trace columns. Returns the proof words on every rank.
+    timings, when a dict, receives host-clock milliseconds per stage (diagnostic; the stages are asynchronous)."""
+    import time
+
+    t0 = time.perf_counter()
+
+    def lap(name):
+        nonlocal t0
+        if timings is not None:
+            t1 = time.perf_counter()
+            timings[name] = timings.get(name, 0.0) + (t1 - t0) * 1e3
+            t0 = t1
+
+    s, x = session, exchange
+    evals, rows = s.extend(col_ptrs)
+    lap("extend")
+    x.rows_to_owners(evals, rows, s.ncl, s.N, s.R)
+    lap("exchange_rows")
+    root, roots = s.subtree()
+    x.all_gather_device(root, roots, 8)
+    lap("subtree")
+    mine = s.sample()
+    everyone = x.all_gather_host(mine)
+    lap("sample")
+    local, full = s.quotients(everyone)
+    for k in range(4):
+        x.all_gather_device(local[k], full[k], s.R)
+    lap("quotients")
+    part = s.fri_and_decommit()
+    parts = x.all_gather_varlen(part)
+    lap("fri_decommit")
+    words = s.finish(parts)
+    lap("finish")
+    return words
