@@ -347,6 +347,7 @@ def run_ours(args, rank, world, local_rank):
         del cols_b, sec, half, quarter
     e2e_ms, words_e2e = timed(True, False)
     assert len(words_dev) == len(words_e2e) and (words_dev == words_e2e).all(), "resident and end-to-end legs disagree"
+    extras = {} if args.no_extras else extra_legs(args, z, ctx, dist, rank, world, local_rank, words_dev, dev_ms / args.steps, h_addr, d_work)
 
     if dist is not None:
         import torch
@@ -423,6 +424,7 @@ def run_ours(args, rank, world, local_rank):
             "gpu_launches": launches * args.steps,
             "roofline": roofline, "cpu_baseline": cpu, "gpu_baseline": gpu_ref, "clocks": clocks,
             "proof_words": int(len(words_dev)), "proof_sha256": hashlib.sha256(words_dev.tobytes()).hexdigest(),
+            **extras,
             "parity": golden_check(f"pcs_{ncols}x2e{log_n}_blowup{1 << args.log_blowup}" +
                                    ("" if (args.pow_bits, args.n_queries) == (10, 3) else f"_pow{args.pow_bits}_q{args.n_queries}"), words_dev),
         }
@@ -431,6 +433,113 @@ def run_ours(args, rank, world, local_rank):
     ctx.close()
     if dist is not None:
         dist.destroy_process_group()
+
+
+def extra_legs(args, z, ctx, dist, rank, world, local_rank, words_single, single_ms, h_addr, d_work):
+    """Legs beside the headline, on the same GPUs in the same run, so that the driver's one line per N also carries: what the
+    host can deliver to the ranks at once (reads the end-to-end scaling against), ONE proof sharded over all ranks (strong
+    scaling of the proof itself; its words must equal the single-GPU proof), and BASELINE.json's first metric, the proof
+    time of a composed decode segment (N = 1) or of a whole decode step dealt over the ranks (N > 1), as operator-trace
+    replays. Every rank runs every leg; rank 0 keeps the results."""
+    import torch
+
+    out = {}
+    dev = torch.device("cuda", local_rank)
+    log_n, ncols = args.log_size, args.cols
+    n = 1 << log_n
+
+    def allmax(v):
+        if dist is None:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            dist.barrier()
+
+    # ---- pinned host -> device, every rank at once
+    nbytes = ncols * n * 4
+    for _ in range(2):
+        ctx.h2d_async(d_work.ptr, h_addr, nbytes)
+    barrier()
+    ctx.event_record(0)
+    for _ in range(3):
+        ctx.h2d_async(d_work.ptr, h_addr, nbytes)
+    ctx.event_record(1)
+    ms = allmax(ctx.event_elapsed_ms(0, 1) / 3)
+    out["h2d_ceiling"] = {"gbs_per_rank": nbytes / (ms * 1e-3) / 1e9, "gbs_all_ranks": world * nbytes / (ms * 1e-3) / 1e9,
+                          "bytes_per_copy": nbytes, "note": "one pinned-to-device copy of the trace per rank, all ranks at once, slowest rank"}
+
+    # ---- one proof over all ranks
+    if dist is not None and ncols % world == 0 and (world & (world - 1)) == 0:
+        from zk_inference_prover_b200.sharded import ContextMem, Exchange, sharded_pcs_prove
+
+        ncl = ncols // world
+        mine = ctx.alloc(ncl * n)
+        keep = ctx.alloc(ncl * n)
+        for j in range(ncl):
+            ctx.h2d_async(keep.view(j * n), h_addr + 4 * (rank * ncl + j) * n, n * 4)
+        x = Exchange(ContextMem(ctx), dev)
+        times, words, stages = [], None, {}
+        for it in range(2 + 3):
+            ctx.d2d(mine.ptr, keep.ptr, ncl * n * 4)
+            barrier()
+            t0 = time.perf_counter()
+            sess = ctx.shard_pcs(rank, world, ncols, log_n, pow_bits=args.pow_bits, log_blowup=args.log_blowup, log_last_layer=0,
+                                 n_queries=args.n_queries)
+            words = sharded_pcs_prove(sess, x, [mine.view(j * n) for j in range(ncl)], stages if it >= 2 else None)
+            ctx.sync()
+            dt = (time.perf_counter() - t0) * 1e3
+            sess.close()
+            if it >= 2:
+                times.append(dt)
+        ms = allmax(sum(times) / len(times))
+        same = bool(len(words) == len(words_single) and (words == words_single).all())
+        out["sharded_proof"] = {"ms": ms, "cells_per_s": ncols * n / (ms * 1e-3), "single_gpu_ms": single_ms,
+                                "strong_efficiency": single_ms / ms / world, "equals_single_gpu_proof": same,
+                                "device_ms_per_stage_rank0": {k: v / 3 for k, v in stages.items()},
+                                "commit_ms_rank0": (stages.get("interpolate_extend_exchange", 0.0) + stages.get("merkle_subtree_roots", 0.0)) / 3,
+                                "timer": "host clock between barriers, slowest rank",
+                                "what": "columns sharded for interpolate + LDE, one exchange to row shards, Merkle subtrees, sampling and "
+                                        "quotients on the shards, FRI on the gathered quotient column, decommitment merged from the ranks"}
+        if not same:
+            raise SystemExit("the sharded proof differs from the single-GPU proof")
+        del mine, keep
+
+    # ---- the decode segment / decode step replays
+    try:
+        rctx = z.Context(device=local_rank, max_log_size=24)
+        names = ["layer_8b_s32_c2048"] if world == 1 else (["layer_8b_s32_c2048"] * 32 + ["head_8b_s32_c2048"])[rank::world]
+        shapes = {nm: SegmentReplay(z, rctx, nm, 0x5EED0006 + rank) for nm in sorted(set(names))}
+        for nm in names[:1]:
+            shapes[nm].step()
+        rctx.sync()
+        if dist is not None:
+            dist.barrier()
+        rctx.event_record(0)
+        for nm in names:
+            shapes[nm].step()
+        rctx.event_record(1)
+        ms = allmax(rctx.event_elapsed_ms(0, 1))
+        if world == 1:
+            sr = shapes[names[0]]
+            out["segment_replay"] = {"segment": names[0], "ms_per_segment": ms, "cells": sr.cells, "cells_per_s": sr.cells / (ms * 1e-3),
+                                     "what": "BASELINE.json's first metric as an operator-trace replay: the trees and GKR batches of one "
+                                             "layer segment of the config-4 model on random data (timing only; the shape comes from the "
+                                             "reference's cell-exact cost model)"}
+        else:
+            cells = 32 * 226711536 + 191812784
+            out["decode_step_replay"] = {"ms": ms, "segments": 33, "segments_on_rank_0": len((["l"] * 33)[0::world]), "cells": cells,
+                                         "cells_per_s": cells / (ms * 1e-3), "streams_per_gpu": 1,
+                                         "what": "32 layer segments + the output head dealt round-robin to the ranks, no collective; slowest rank"}
+        shapes.clear()
+        rctx.close()
+    except Exception as e:  # a replay must never cost the headline line
+        out["segment_replay" if world == 1 else "decode_step_replay"] = {"unavailable": repr(e)}
+    return out
 
 
 def run_sharded_commit(args, rank, world, local_rank):
@@ -1132,6 +1241,7 @@ def main():
     ap.add_argument("--ref-cols", type=int, default=32, help="columns in the bounded CPU sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-gpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the legs beside the headline (h2d ceiling, sharded proof, segment replays)")
     ap.add_argument("--gkr-log", type=int, default=24)
     ap.add_argument("--streams", type=int, default=1, help="decode-step: proofs side by side on one GPU (host threads, one context each)")
     ap.add_argument("--segment", default="layer_8b_s32_c2048", help="segment-replay: a key of tests/golden/segment_shapes.json")

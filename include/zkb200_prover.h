@@ -115,9 +115,10 @@ int zkb_gkr_prove_device(zkb_ctx* ctx, int n_inst, const int* kinds, const uint3
  * context per rank. The library moves nothing between devices: between the calls below the caller performs the
  * exchanges (NCCL, MPI, peer copies ...), in this order:
  *   begin    every rank, same arguments except `rank`
- *   extend   d_cols: this rank's ncols_total / world columns (evaluations, bit-reversed; consumed). Returns
- *            *d_evals = [ncl][N] extended columns and *d_rows = [ncols_total][N / world] to receive into.
- *            EXCHANGE: rows [d R, (d+1) R) of local column j go to rank d at d_rows + ((rank * ncl + j) * R)  (R = N / world)
+ *   extend   d_cols: this rank's ncl = ncols_total / world columns (evaluations, bit-reversed; consumed). Returns
+ *            *d_send = [world][ncl][R] (R = N / world): block d holds rows [d R, (d+1) R) of the extended local columns (the
+ *            transform's last pass writes them there directly), and *d_rows = [world][ncl][R] to receive into.
+ *            EXCHANGE: one all-to-all: block d of d_send goes to rank d, which stores it as block `rank` of its d_rows
  *   subtree  hashes the Merkle subtree over the rank's rows. *d_root: its root (8 words, device);
  *            EXCHANGE: all-gather the roots into *d_roots ([world][8], device), rank order
  *   sample   top layers of the tree, channel, out-of-domain point; h_samples receives this rank's ncl x 4 words
@@ -134,7 +135,7 @@ int zkb_gkr_prove_device(zkb_ctx* ctx, int n_inst, const int* kinds, const uint3
  * Errors: ZKB_EINVAL for shapes that do not shard (world not a power of two, fewer than 8 rows per rank). */
 typedef struct zkb_shard_pcs zkb_shard_pcs;
 int zkb_shard_pcs_begin(zkb_ctx* ctx, int rank, int world, int ncols_total, int log_n, const zkb_pcs_config* config, zkb_shard_pcs** out);
-int zkb_shard_pcs_extend(zkb_shard_pcs* s, uint32_t* const* d_cols, uint32_t** d_evals, uint32_t** d_rows);
+int zkb_shard_pcs_extend(zkb_shard_pcs* s, uint32_t* const* d_cols, uint32_t** d_send, uint32_t** d_rows);
 int zkb_shard_pcs_subtree(zkb_shard_pcs* s, uint32_t** d_root, uint32_t** d_roots);
 int zkb_shard_pcs_sample(zkb_shard_pcs* s, uint32_t* h_samples);
 int zkb_shard_pcs_quotients(zkb_shard_pcs* s, const uint32_t* h_all_samples, uint32_t* d_quot_local[4], uint32_t* d_quot_full[4]);

@@ -121,8 +121,8 @@ class ShardPcsSession:
                                                C.byref(self.h)))
 
     def extend(self, col_ptrs):
-        """-> (evals address [ncl][N], rows address [ncols][R]). Then: rows [d R, (d+1) R) of local column j go to rank d at
-        rows + ((rank * ncl + j) * R) words."""
+        """-> (send address, rows address), both [world][ncl][R]. Then: one all-to-all, block d of `send` becomes block `rank`
+        of rank d's `rows`."""
         e, r = C.c_void_p(), C.c_void_p()
         self.ctx._check(self.ctx.lib.zkb_shard_pcs_extend(self.h, _ptr_array(col_ptrs), C.byref(e), C.byref(r)))
         return e.value, r.value

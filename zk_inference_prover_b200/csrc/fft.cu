@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "fft_internal.hpp"
 #include "fft_r32.cuh"
 
 namespace zk {
@@ -204,7 +205,7 @@ static int launch_pass(zkb_ctx* ctx, uint32_t* const* d_dst, const uint32_t* con
 
 template <bool INVERSE>
 static int launch_step(zkb_ctx* ctx, uint32_t* const* d_dst, const uint32_t* const* d_src, uint32_t src_mask, int ncols,
-                       int log_n, int dom_log, const FftStep& st, uint32_t scale) {
+                       int log_n, int dom_log, const FftStep& st, uint32_t scale, RowBlocks rb = {31, 0u}, bool src_blocked = false) {
     if (st.kind == 0) return launch_pass<INVERSE>(ctx, d_dst, d_src, src_mask, ncols, log_n, dom_log, st.generic, scale);
     // Persistent launch: as many CTAs as fit on the device at once, each walking over work items.
     // The opt-in shared-memory size is a per-device function attribute and the SM count differs between
@@ -249,9 +250,10 @@ static int launch_step(zkb_ctx* ctx, uint32_t* const* d_dst, const uint32_t* con
     if (which == 0)
         fft_r32_contig_kernel<INVERSE><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log, st.r32, tower, scale);
     else if (which == 1)
-        fft_r32_contig12_kernel<INVERSE><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log, st.r32, tower, scale);
+        fft_r32_contig12_kernel<INVERSE><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log, st.r32, tower, scale,
+                                                                                 rb, src_blocked ? 1 : 0);
     else
-        fft_r32_wide_kernel<INVERSE><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log, st.r32, tower, scale);
+        fft_r32_wide_kernel<INVERSE><<<grid, threads, smem, ctx->stream>>>(d_dst, d_src, src_mask, ncols, log_n, dom_log, st.r32, tower, scale, rb);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }
@@ -272,6 +274,86 @@ __global__ void __launch_bounds__(256, 2) butterfly_ceiling_kernel(uint32_t* __r
     for (int i = 0; i < 32; i++) acc ^= v[i];
     out[(size_t)blockIdx.x * 256 + threadIdx.x] = acc;
 }
+
+// First point of Coset::half_odds(log) on the host: index 2^(31 - log - 2).
+static cpoint host_half_odds_initial_zk(int log) {
+    cpoint g{2u, 1268011823u};
+    for (int b = 0; b < 31 - log - 2; b++) g = cpoint_add(g, g);
+    return g;
+}
+
+// zkb_lde_cols with the output columns laid out in row blocks (see RowBlocks): out[c] is the base of column c, block b of
+// it starts blk_stride words further per block. blk_log = 31: plain columns. Blocked output needs the radix-32 plan
+// (2^13 words or more per column, 16-byte aligned) and blocks of at least 4096 words; lde_blocked_supported says so.
+bool lde_blocked_supported(int log_n, int log_out, int blk_log) {
+    // one wide pass at most (the second one of a longer transform would have to read blocked input too)
+    return log_n >= 2 && log_n <= 20 && log_out >= 13 && blk_log >= 12 && blk_log <= log_out;
+}
+
+__global__ void repack_row_blocks_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int ncols, int log_out, int blk_log) {
+    const size_t total = ((size_t)ncols << log_out) >> 2;  // 16-byte pieces
+    for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
+        const size_t w = t << 2, c = w >> log_out, idx = w & (((size_t)1 << log_out) - 1);
+        const size_t b = idx >> blk_log, i = idx & (((size_t)1 << blk_log) - 1);
+        out[((((b * ncols + c) << blk_log) + i)) >> 2] = in[t];
+    }
+}
+
+int repack_row_blocks(zkb_ctx* ctx, const uint32_t* in, uint32_t* out, int ncols, int log_out, int blk_log) {
+    ZKB_CHECK_ARG(ctx, in && out && ncols > 0 && blk_log >= 2 && blk_log <= log_out && (((uintptr_t)in | (uintptr_t)out) & 15) == 0);
+    DeviceGuard g(ctx);
+    repack_row_blocks_kernel<<<148 * 8, 256, 0, ctx->stream>>>((const uint4*)in, (uint4*)out, ncols, log_out, blk_log);
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
+}
+
+int lde_cols_blocked(zkb_ctx* ctx, const uint32_t* const* coeffs, int ncols, int log_n, uint32_t* const* out, int log_out, int blk_log,
+                     uint32_t blk_stride) {
+    const bool plain = blk_log >= 31;
+    const RowBlocks rb{plain ? 31 : blk_log, plain ? 0u : blk_stride};
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, ncols >= 0 && log_n >= 0 && log_out >= 1 && log_n <= log_out && log_out <= ctx->max_log);
+    if (ncols == 0) return ZKB_OK;
+    ZKB_CHECK_ARG(ctx, coeffs != nullptr && out != nullptr);
+    for (int c = 0; c < ncols; c++) ZKB_CHECK_ARG(ctx, (const void*)coeffs[c] != (const void*)out[c]);
+    DeviceGuard g(ctx);
+    void **d_src, **d_dst;
+    int rc = stage_ptrs(ctx, (const void* const*)coeffs, ncols, &d_src);
+    if (rc) return rc;
+    rc = stage_ptrs(ctx, (const void* const*)out, ncols, &d_dst);
+    if (rc) return rc;
+    if (log_out <= 2) {
+        cpoint p = host_half_odds_initial_zk(log_out - 1);
+        fft_small_kernel<false><<<(ncols + 127) / 128, 128, 0, ctx->stream>>>(
+            (uint32_t* const*)d_dst, (const uint32_t* const*)d_src, 1 << log_n, ncols, log_out, p.x, p.y, 0u);
+        ZKB_LAUNCH_CHECK(ctx);
+        return ZKB_OK;
+    }
+    bool aligned = true;
+    for (int c = 0; c < ncols; c++) aligned = aligned && (((uintptr_t)out[c] | (uintptr_t)coeffs[c]) & 15) == 0;
+    if (log_n < 2) aligned = false;  // the staged copies move 16 bytes at a time
+    if (!plain) ZKB_CHECK_ARG(ctx, aligned && lde_blocked_supported(log_n, log_out, blk_log) && (blk_stride & 3u) == 0);
+    auto steps = plan_steps(log_n, log_out, aligned);
+    uint32_t src_mask = (1u << log_n) - 1u;
+    // ZKB_LDE_CHUNK=k runs all passes over k columns at a time, so that the array between two passes (2^log_out
+    // words per column) is still in the L2 cache when the next pass reads it. Off by default: at 256 x 2^22 the
+    // DRAM traffic drops but the many short launches cost more time than the traffic saves (the passes are bound
+    // by instruction issue, not by DRAM).
+    static const int env_chunk = []() { const char* e = getenv("ZKB_LDE_CHUNK"); return e ? atoi(e) : 0; }();
+    const int chunk = env_chunk > 0 && steps.size() > 1 ? env_chunk : ncols;
+    for (int c0 = 0; c0 < ncols; c0 += chunk) {
+        const int nc = ncols - c0 < chunk ? ncols - c0 : chunk;
+        for (size_t p = steps.size(); p-- > 0;) {
+            bool first = p + 1 == steps.size();
+            rc = launch_step<false>(ctx, (uint32_t* const*)d_dst + c0,
+                                    (first ? (const uint32_t* const*)d_src : (const uint32_t* const*)d_dst) + c0,
+                                    first ? src_mask : 0xffffffffu, nc, log_out, log_out, steps[p], 0u, rb, !first && !plain);
+            if (rc) return rc;
+        }
+    }
+    return ZKB_OK;
+}
+
 
 }  // namespace zk
 
@@ -339,46 +421,7 @@ int zkb_ifft_cols(zkb_ctx* ctx, uint32_t* const* cols, int ncols, int log_n) {
 }
 
 int zkb_lde_cols(zkb_ctx* ctx, const uint32_t* const* coeffs, int ncols, int log_n, uint32_t* const* out, int log_out) {
-    if (!ctx) return ZKB_EINVAL;
-    ZKB_CHECK_ARG(ctx, ncols >= 0 && log_n >= 0 && log_out >= 1 && log_n <= log_out && log_out <= ctx->max_log);
-    if (ncols == 0) return ZKB_OK;
-    ZKB_CHECK_ARG(ctx, coeffs != nullptr && out != nullptr);
-    for (int c = 0; c < ncols; c++) ZKB_CHECK_ARG(ctx, (const void*)coeffs[c] != (const void*)out[c]);
-    DeviceGuard g(ctx);
-    void **d_src, **d_dst;
-    int rc = stage_ptrs(ctx, (const void* const*)coeffs, ncols, &d_src);
-    if (rc) return rc;
-    rc = stage_ptrs(ctx, (const void* const*)out, ncols, &d_dst);
-    if (rc) return rc;
-    if (log_out <= 2) {
-        cpoint p = host_half_odds_initial(log_out - 1);
-        fft_small_kernel<false><<<(ncols + 127) / 128, 128, 0, ctx->stream>>>(
-            (uint32_t* const*)d_dst, (const uint32_t* const*)d_src, 1 << log_n, ncols, log_out, p.x, p.y, 0u);
-        ZKB_LAUNCH_CHECK(ctx);
-        return ZKB_OK;
-    }
-    bool aligned = true;
-    for (int c = 0; c < ncols; c++) aligned = aligned && (((uintptr_t)out[c] | (uintptr_t)coeffs[c]) & 15) == 0;
-    if (log_n < 2) aligned = false;  // the staged copies move 16 bytes at a time
-    auto steps = plan_steps(log_n, log_out, aligned);
-    uint32_t src_mask = (1u << log_n) - 1u;
-    // ZKB_LDE_CHUNK=k runs all passes over k columns at a time, so that the array between two passes (2^log_out
-    // words per column) is still in the L2 cache when the next pass reads it. Off by default: at 256 x 2^22 the
-    // DRAM traffic drops but the many short launches cost more time than the traffic saves (the passes are bound
-    // by instruction issue, not by DRAM).
-    static const int env_chunk = []() { const char* e = getenv("ZKB_LDE_CHUNK"); return e ? atoi(e) : 0; }();
-    const int chunk = env_chunk > 0 && steps.size() > 1 ? env_chunk : ncols;
-    for (int c0 = 0; c0 < ncols; c0 += chunk) {
-        const int nc = ncols - c0 < chunk ? ncols - c0 : chunk;
-        for (size_t p = steps.size(); p-- > 0;) {
-            bool first = p + 1 == steps.size();
-            rc = launch_step<false>(ctx, (uint32_t* const*)d_dst + c0,
-                                    (first ? (const uint32_t* const*)d_src : (const uint32_t* const*)d_dst) + c0,
-                                    first ? src_mask : 0xffffffffu, nc, log_out, log_out, steps[p], 0u);
-            if (rc) return rc;
-        }
-    }
-    return ZKB_OK;
+    return zk::lde_cols_blocked(ctx, coeffs, ncols, log_n, out, log_out, 31, 0u);
 }
 
 }  // extern "C"

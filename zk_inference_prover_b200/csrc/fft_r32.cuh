@@ -150,6 +150,17 @@ struct R32Pass {
     int lo;              // first index bit of the window
     int act_lo, act_hi;  // active layers, window-local: [act_lo, act_hi) within 0..10
 };
+// Destination layout in row blocks: word idx of a column lies at (idx >> log) * stride + (idx mod 2^log) from the
+// column's base, i.e. consecutive blocks of 2^log rows are `stride` words apart (a sharded commitment lays the
+// extended columns out by destination rank this way). log = 31 is the plain contiguous column. A block is at least
+// 4096 words, so a tile row or a unit never straddles two blocks.
+struct RowBlocks {
+    int log;
+    uint32_t stride;
+};
+__device__ __forceinline__ size_t blocked(uint32_t idx, RowBlocks rb) {
+    return (size_t)(idx >> rb.log) * rb.stride + (idx & ((1u << rb.log) - 1u));
+}
 
 // Both kernels are persistent: a CTA (strided) or a warp (contiguous) walks over work items
 // (tile, column) and, while it computes one item from shared memory, the next item's words are
@@ -330,7 +341,7 @@ __device__ __forceinline__ void radix8x4_stage(uint32_t (&v)[32], const uint32_t
 template <bool INVERSE>
 __global__ void __launch_bounds__(256, R32_WIDE_CTAS)
     fft_r32_wide_kernel(uint32_t* const* __restrict__ dst_cols, const uint32_t* const* __restrict__ src_cols, uint32_t src_mask,
-                        int ncols, int log_n, int dom_log, R32Pass ps, const uint32_t* __restrict__ tower, uint32_t scale) {
+                        int ncols, int log_n, int dom_log, R32Pass ps, const uint32_t* __restrict__ tower, uint32_t scale, RowBlocks rb) {
     extern __shared__ __align__(16) uint32_t dyn_smem[];
     uint32_t* const buf0 = dyn_smem;
     constexpr int BUF = R32_WIDE_TILE;
@@ -424,7 +435,7 @@ __global__ void __launch_bounds__(256, R32_WIDE_CTAS)
             radix8x4_stage<false>(v, tw + 4 * R, tw + 128 + 2 * R, tw + 192 + R, ps.act_lo, ps.act_hi);
 #pragma unroll
             for (int q = 0; q < 8; q++)
-                *reinterpret_cast<uint4*>(dst + (base | ((8 * R + q) << ps.lo)) + 4 * c) =
+                *reinterpret_cast<uint4*>(dst + blocked(base | ((8 * R + q) << ps.lo), rb) + 4 * c) =
                     make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
         } else {
 #pragma unroll
@@ -463,7 +474,8 @@ __host__ __device__ constexpr size_t r32_c12_smem() { return (size_t)2 * (R32_C1
 template <bool INVERSE>
 __global__ void __launch_bounds__(32 * R32_C12_WARPS, 4)
     fft_r32_contig12_kernel(uint32_t* const* __restrict__ dst_cols, const uint32_t* const* __restrict__ src_cols, uint32_t src_mask,
-                            int ncols, int log_n, int dom_log, R32Pass ps, const uint32_t* __restrict__ tower, uint32_t scale) {
+                            int ncols, int log_n, int dom_log, R32Pass ps, const uint32_t* __restrict__ tower, uint32_t scale, RowBlocks rb,
+                            int src_blocked) {
     extern __shared__ __align__(16) uint32_t dyn_smem[];
     constexpr int BLK = R32_PITCH * 32, BUF = R32_C12_BUF, NT = 32 * R32_C12_WARPS;
     uint32_t* const buf0 = dyn_smem;
@@ -478,11 +490,13 @@ __global__ void __launch_bounds__(32 * R32_C12_WARPS, 4)
         const uint32_t* __restrict__ src = src_cols[it >> unit_bits];
         const uint32_t un = (uint32_t)(it & (((size_t)1 << unit_bits) - 1));
         const uint32_t base = un << 12;
+        // an in-place pass over a column laid out in row blocks reads the unit where the pass before it wrote it
+        const uint32_t* __restrict__ usrc = src_blocked ? src + blocked(base, rb) - base : src;
 #pragma unroll
         for (int k = 0; k < 8; k++) {
             const int ch = k * NT + tid;  // 16-byte chunk: block ch / 256, row (ch / 8) % 32, part ch % 8
             const int blk = ch >> 8, r = (ch >> 3) & 31, q = ch & 7;
-            cp_async16(buf + blk * BLK + R32_PITCH * r + 4 * q, src + ((base + (blk << 10) + 32 * r + 4 * q) & src_mask));
+            cp_async16(buf + blk * BLK + R32_PITCH * r + 4 * q, usrc + ((base + (blk << 10) + 32 * r + 4 * q) & src_mask));
         }
         uint32_t* tw = tw0 + b * R32_C12_TW;
 #pragma unroll
@@ -530,7 +544,7 @@ __global__ void __launch_bounds__(32 * R32_C12_WARPS, 4)
         cp_async_commit();
         uint32_t* __restrict__ sb = buf0 + cur * BUF;
         uint32_t* __restrict__ s = sb + warp * BLK;
-        uint32_t* __restrict__ dst = dst_cols[item >> unit_bits] + ((size_t)(item & (((size_t)1 << unit_bits) - 1)) << 12);
+        uint32_t* __restrict__ dst = dst_cols[item >> unit_bits] + blocked((uint32_t)(item & (((size_t)1 << unit_bits) - 1)) << 12, rb);
         const uint32_t* tw = tw0 + cur * R32_C12_TW;
         const uint32_t* const tb_uni[5] = {tw + 1920 + 16 * warp, tw + 1984 + 8 * warp, tw + 2016 + 4 * warp, tw + 2032 + 2 * warp,
                                            tw + 2040 + warp};

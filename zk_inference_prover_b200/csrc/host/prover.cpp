@@ -13,6 +13,7 @@
 #include "../../../include/zkb200_prover.h"
 #include "../air_program.hpp"
 #include "b200_backend.hpp"
+#include "../fft_internal.hpp"
 #include "../gkr_resident.hpp"
 #include "../gkr_batch.hpp"
 #include "../gather_blocks.hpp"
@@ -1247,8 +1248,8 @@ int zkb_shard_pcs_end(zkb_shard_pcs* h) {
     return ZKB_OK;
 }
 
-int zkb_shard_pcs_extend(zkb_shard_pcs* h, uint32_t* const* d_cols, uint32_t** d_evals, uint32_t** d_rows) {
-    if (!h || !d_cols || !d_evals || !d_rows) return ZKB_EINVAL;
+int zkb_shard_pcs_extend(zkb_shard_pcs* h, uint32_t* const* d_cols, uint32_t** d_send, uint32_t** d_rows) {
+    if (!h || !d_cols || !d_send || !d_rows) return ZKB_EINVAL;
     ShardSession& s = h->s;
     return shard_guard(s.ctx, [&] {
         std::vector<BaseColumn*> cols;
@@ -1258,11 +1259,21 @@ int zkb_shard_pcs_extend(zkb_shard_pcs* h, uint32_t* const* d_cols, uint32_t** d
         for (int c = 0; c < s.ncl; c++) s.coeffs.push_back(BaseColumn::view(s.dev, d_cols[c], (size_t)1 << s.log_n));
         for (auto& c : s.coeffs) cols.push_back(&c);
         B200Backend::interpolate_columns(s.dev, cols);
-        s.evals = BaseColumn(s.dev, (size_t)s.ncl * s.N);
+        s.evals = BaseColumn(s.dev, (size_t)s.ncl * s.N);  // [world][ncl][R]: block d is what rank d receives
         s.rows = BaseColumn(s.dev, (size_t)s.ncols * s.R);
-        for (int c = 0; c < s.ncl; c++) { src.push_back(s.coeffs[c].ptr()); dst.push_back(s.evals.ptr() + (size_t)c * s.N); }
-        s.dev.check(zkb_lde_cols(s.ctx, src.data(), s.ncl, (int)s.log_n, dst.data(), (int)s.log_out));
-        *d_evals = s.evals.ptr();
+        for (int c = 0; c < s.ncl; c++) src.push_back(s.coeffs[c].ptr());
+        if (zk::lde_blocked_supported((int)s.log_n, (int)s.log_out, (int)s.log_local)) {
+            // the transform's last pass writes every row block where the exchange sends it from: no repack
+            for (int c = 0; c < s.ncl; c++) dst.push_back(s.evals.ptr() + (size_t)c * s.R);
+            s.dev.check(zk::lde_cols_blocked(s.ctx, src.data(), s.ncl, (int)s.log_n, dst.data(), (int)s.log_out, (int)s.log_local,
+                                             (uint32_t)((size_t)s.ncl * s.R)));
+        } else {
+            BaseColumn plain(s.dev, (size_t)s.ncl * s.N);
+            for (int c = 0; c < s.ncl; c++) dst.push_back(plain.ptr() + (size_t)c * s.N);
+            s.dev.check(zkb_lde_cols(s.ctx, src.data(), s.ncl, (int)s.log_n, dst.data(), (int)s.log_out));
+            s.dev.check(zk::repack_row_blocks(s.ctx, plain.ptr(), s.evals.ptr(), s.ncl, (int)s.log_out, (int)s.log_local));
+        }
+        *d_send = s.evals.ptr();
         *d_rows = s.rows.ptr();
     });
 }

@@ -158,7 +158,7 @@ class _Alias:
 
 
 class Exchange:
-    """The four data movements a sharded proof needs, over torch.distributed.
+    """The data movements a sharded proof needs, over torch.distributed.
 
     `nccl`: device tensors alias the library's buffers and the collectives are ordered on the context's own stream
     (torch.cuda.ExternalStream), so nothing synchronises with the host. `gloo`: the ranges are staged through host
@@ -180,40 +180,26 @@ class Exchange:
             return contextlib.nullcontext()
         return torch.cuda.stream(torch.cuda.ExternalStream(self.mem.stream(), device=self.device))
 
-    def rows_to_owners(self, evals_ptr, rows_ptr, ncl, N, R):
-        """Rows [d R, (d+1) R) of local column j go to rank d at rows + ((rank * ncl + j) * R): no repack on either
-        side, every piece is contiguous where it lies and where it lands."""
+    def all_to_all(self, send_ptr, recv_ptr, words_per_peer):
+        """Block d of `send` ([world][words_per_peer]) becomes block `rank` of rank d's `recv`."""
         G, me = self.world, self.rank
         if self.nccl:
             with self._stream():
-                ev = self._dev(evals_ptr, ncl * N).view(ncl, G, R)
-                rw = self._dev(rows_ptr, G * ncl * R).view(G, ncl, R)
-                rw[me].copy_(ev[:, me, :])
-                ops = []
-                for peer in range(G):
-                    if peer == me:
-                        continue
-                    for j in range(ncl):
-                        ops.append(dist.P2POp(dist.isend, ev[j, peer], peer, group=self.group))
-                        ops.append(dist.P2POp(dist.irecv, rw[peer, j], peer, group=self.group))
-                if ops:
-                    for w in dist.batch_isend_irecv(ops):
-                        w.wait()
+                dist.all_to_all_single(self._dev(recv_ptr, G * words_per_peer), self._dev(send_ptr, G * words_per_peer), group=self.group)
             return
-        ev = torch.from_numpy(self.mem.read(evals_ptr, ncl * N).view("int32")).view(ncl, G, R)
-        rw = torch.empty((G, ncl, R), dtype=torch.int32)
-        rw[me].copy_(ev[:, me, :])
-        for peer in range(G):  # gloo: pairwise, the lower rank sends first
+        sd = torch.from_numpy(self.mem.read(send_ptr, G * words_per_peer).view("int32")).view(G, words_per_peer)
+        rv = torch.empty_like(sd)
+        rv[me].copy_(sd[me])
+        for peer in range(G):  # gloo has no all-to-all: pairwise, the lower rank sends first
             if peer == me:
                 continue
-            block = ev[:, peer, :].contiguous()
             if me < peer:
-                dist.send(block, peer, group=self.group)
-                dist.recv(rw[peer], peer, group=self.group)
+                dist.send(sd[peer], peer, group=self.group)
+                dist.recv(rv[peer], peer, group=self.group)
             else:
-                dist.recv(rw[peer], peer, group=self.group)
-                dist.send(block, peer, group=self.group)
-        self.mem.write(rows_ptr, rw.numpy().view("uint32").reshape(-1))
+                dist.recv(rv[peer], peer, group=self.group)
+                dist.send(sd[peer], peer, group=self.group)
+        self.mem.write(recv_ptr, rv.numpy().view("uint32").reshape(-1))
 
     def all_gather_device(self, src_ptr, dst_ptr, words):
         """dst[r * words ...] <- src of rank r."""
@@ -278,36 +264,36 @@ class ContextMem:
 def sharded_pcs_prove(session, exchange, col_ptrs, timings=None):
     """Runs one sharded proof: `session` is this rank's ShardPcsSession (or an object with the same stages), `exchange`
     an Exchange over the same ranks, col_ptrs this rank's trace columns. Returns the proof words on every rank.
-    timings, when a dict, receives host-clock milliseconds per stage (diagnostic; the stages are asynchronous)."""
-    import time
-
-    t0 = time.perf_counter()
+    timings, when a dict, receives per stage the device time between CUDA events on the context's stream (the collectives
+    are ordered on that stream), summed over calls."""
+    s, x = session, exchange
+    ctx = getattr(s, "ctx", None) if timings is not None else None
+    marks = []
 
     def lap(name):
-        nonlocal t0
-        if timings is not None:
-            t1 = time.perf_counter()
-            timings[name] = timings.get(name, 0.0) + (t1 - t0) * 1e3
-            t0 = t1
+        if ctx is not None:
+            ctx.event_record(40 + len(marks))
+            marks.append(name)
 
-    s, x = session, exchange
-    evals, rows = s.extend(col_ptrs)
-    lap("extend")
-    x.rows_to_owners(evals, rows, s.ncl, s.N, s.R)
-    lap("exchange_rows")
+    lap("start")
+    send, rows = s.extend(col_ptrs)
+    x.all_to_all(send, rows, s.ncl * s.R)
+    lap("interpolate_extend_exchange")
     root, roots = s.subtree()
     x.all_gather_device(root, roots, 8)
-    lap("subtree")
+    lap("merkle_subtree_roots")
     mine = s.sample()
     everyone = x.all_gather_host(mine)
-    lap("sample")
+    lap("top_layers_sample")
     local, full = s.quotients(everyone)
     for k in range(4):
         x.all_gather_device(local[k], full[k], s.R)
-    lap("quotients")
+    lap("quotients_gather")
     part = s.fri_and_decommit()
     parts = x.all_gather_varlen(part)
-    lap("fri_decommit")
     words = s.finish(parts)
-    lap("finish")
+    lap("fri_grind_decommit_merge")
+    if ctx is not None:
+        for i in range(1, len(marks)):
+            timings[marks[i]] = timings.get(marks[i], 0.0) + ctx.event_elapsed_ms(40 + i - 1, 40 + i)
     return words
