@@ -85,3 +85,105 @@ def test_sharded_commit_matches_single_tree(oracle, tmp_path, world, log_n, log_
     for r in range(world):
         assert (np.load(tmp_path / f"root{r}.npy") == layer[0]).all()
         assert (np.load(tmp_path / f"local{r}.npy") == evals[:, r * rows:(r + 1) * rows]).all()
+
+
+# ------------------------------------------------------------------ the whole-proof driver's data movement
+# The library's sharded session needs a GPU; what runs on CPU ranks here is everything around it: the order of the stages in
+# sharded_pcs_prove and every movement of Exchange under gloo (all-to-all of row blocks, device and host all-gathers, the
+# gather of parts of different lengths). The stand-in session keeps "device memory" in a numpy arena and computes, at every
+# stage, values that depend on every word another rank must have delivered, so that a misplaced block changes the result.
+class ArenaMem:
+    def __init__(self, words):
+        self.a = np.zeros(words, np.uint32)
+
+    def stream(self):
+        return 0
+
+    def read(self, ptr, words):
+        return self.a[ptr:ptr + int(words)].copy()
+
+    def write(self, ptr, arr):
+        arr = np.asarray(arr, np.uint32).reshape(-1)
+        self.a[ptr:ptr + len(arr)] = arr
+
+
+def _cell(c, i):
+    return (np.uint64(2654435761) * np.uint64(c + 1) + np.uint64(40503) * np.asarray(i, np.uint64)) % np.uint64(2**31 - 1)
+
+
+class StandInSession:
+    def __init__(self, mem, rank, world, ncols, N):
+        self.mem, self.rank, self.world, self.ncols, self.N = mem, rank, world, ncols, N
+        self.ncl, self.R = ncols // world, N // world
+        self.send, self.rows, self.root, self.roots = 0, ncols * N, 2 * ncols * N, 2 * ncols * N + 8
+        self.ql = [self.roots + 8 * world + k * self.R for k in range(4)]
+        self.qf = [self.ql[3] + self.R + k * N for k in range(4)]
+
+    def extend(self, col_ptrs):
+        ncl, R, G = self.ncl, self.R, self.world
+        for d in range(G):
+            for j in range(ncl):
+                c = self.rank * ncl + j
+                self.mem.write(self.send + (d * ncl + j) * R, _cell(c, np.arange(d * R, (d + 1) * R)).astype(np.uint32))
+        return self.send, self.rows
+
+    def _local(self):
+        return self.mem.read(self.rows, self.ncols * self.R).reshape(self.ncols, self.R)
+
+    def subtree(self):
+        self.mem.write(self.root, (self._local().astype(np.uint64).sum(axis=0)[:8] % np.uint64(2**31 - 1)).astype(np.uint32))
+        return self.root, self.roots
+
+    def sample(self):
+        self.all_roots = self.mem.read(self.roots, 8 * self.world)
+        return np.stack([_cell(self.rank * self.ncl + j, np.arange(4)).astype(np.uint32) for j in range(self.ncl)])
+
+    def quotients(self, everyone):
+        self.samples = np.asarray(everyone).copy()
+        loc = self._local().astype(np.uint64)
+        for k in range(4):
+            self.mem.write(self.ql[k], ((loc * np.uint64(k + 1)).sum(axis=0) % np.uint64(2**31 - 1)).astype(np.uint32))
+        return self.ql, self.qf
+
+    def fri_and_decommit(self):
+        full = np.concatenate([self.mem.read(self.qf[k], self.N) for k in range(4)])
+        self.full_sum = int(full.astype(np.uint64).sum() % (2**31 - 1))
+        return np.arange(3 + 2 * self.rank, dtype=np.uint32) + np.uint32(1000 * self.rank)  # parts of different lengths
+
+    def finish(self, parts):
+        return np.concatenate([self.all_roots, self.samples.reshape(-1), np.array([self.full_sum], np.uint32)] + list(parts)).astype(np.uint32)
+
+
+def _driver_worker(rank, world, port, ncols, N, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from zk_inference_prover_b200.sharded import Exchange, sharded_pcs_prove
+
+    mem = ArenaMem(2 * ncols * N + 8 + 8 * world + 4 * (N // world) + 4 * N)
+    sess = StandInSession(mem, rank, world, ncols, N)
+    words = sharded_pcs_prove(sess, Exchange(mem, torch.device("cpu")), [])
+    np.save(os.path.join(out_dir, f"words{rank}.npy"), words)
+    np.save(os.path.join(out_dir, f"rows{rank}.npy"), sess._local())
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,ncols,N", [(2, 6, 64), (4, 8, 128)])
+def test_sharded_proof_driver_moves_every_block_to_its_owner(tmp_path, world, ncols, N):
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    mp.spawn(_driver_worker, args=(world, port, ncols, N, str(tmp_path)), nprocs=world, join=True)
+    R, P = N // world, np.uint64(2**31 - 1)
+    table = np.stack([_cell(c, np.arange(N)) for c in range(ncols)])  # [ncols][N], uint64
+    roots = np.concatenate([(table[:, r * R:(r + 1) * R].sum(axis=0)[:8] % P).astype(np.uint32) for r in range(world)])
+    samples = np.concatenate([_cell(c, np.arange(4)).astype(np.uint32) for c in range(ncols)])
+    full = np.concatenate([((table * np.uint64(k + 1)).sum(axis=0) % P) for k in range(4)])
+    full_sum = np.array([int(full.sum() % P)], np.uint32)
+    parts = [np.arange(3 + 2 * r, dtype=np.uint32) + np.uint32(1000 * r) for r in range(world)]
+    want = np.concatenate([roots, samples, full_sum] + parts)
+    for r in range(world):
+        assert (np.load(tmp_path / f"rows{r}.npy") == table[:, r * R:(r + 1) * R].astype(np.uint32)).all()  # the all-to-all
+        assert (np.load(tmp_path / f"words{r}.npy") == want).all()
