@@ -227,6 +227,21 @@ def golden_check(name, words):
     return {"golden": name, "match": True}
 
 
+def verifier_accepts(words, ncols, log_n, args):
+    """The proof of the timed run, checked by the CPU restatement of the reference's verifier (oracle/verify.hpp:
+    CommitmentSchemeVerifier::verify_values with FriVerifier and MerkleVerifier). A checker, outside every timed region."""
+    try:
+        import oracle
+
+        rc = oracle.pcs_verify(words, [[log_n] * ncols], pow_bits=args.pow_bits, log_blowup=args.log_blowup, log_last_layer=0,
+                               n_queries=args.n_queries)
+    except Exception as e:
+        return {"unavailable": repr(e)}
+    if rc[0] != 0:
+        raise SystemExit(f"the reference's verifier rejects the proof: {rc}")
+    return True
+
+
 def workload_config(args):
     return {"workload": f"pcs_prove_{args.cols}cols_log{args.log_size}_blowup{1 << args.log_blowup}",
             "columns": args.cols, "log_size": args.log_size, "log_blowup": args.log_blowup, "pow_bits": args.pow_bits,
@@ -425,6 +440,7 @@ def run_ours(args, rank, world, local_rank):
             "roofline": roofline, "cpu_baseline": cpu, "gpu_baseline": gpu_ref, "clocks": clocks,
             "proof_words": int(len(words_dev)), "proof_sha256": hashlib.sha256(words_dev.tobytes()).hexdigest(),
             **extras,
+            "accepts": verifier_accepts(words_dev, ncols, log_n, args),
             "parity": golden_check(f"pcs_{ncols}x2e{log_n}_blowup{1 << args.log_blowup}" +
                                    ("" if (args.pow_bits, args.n_queries) == (10, 3) else f"_pow{args.pow_bits}_q{args.n_queries}"), words_dev),
         }

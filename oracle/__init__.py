@@ -383,6 +383,28 @@ def pcs_prove(trees, pow_bits=10, log_blowup=1, log_last_layer=0, n_queries=3, t
     return out[:n].copy()
 
 
+VERIFY_ERRORS = {0: "ok", 1: "merkle: witness too short", 2: "merkle: witness too long", 3: "merkle: too many queried values",
+                 4: "merkle: too few queried values", 5: "merkle: root mismatch", 10: "fri: invalid number of layers",
+                 11: "fri: first layer evaluations invalid", 12: "fri: first layer commitment invalid",
+                 13: "fri: inner layer commitment invalid", 14: "fri: inner layer evaluations invalid",
+                 15: "fri: last layer degree invalid", 16: "fri: last layer evaluations invalid", 20: "proof of work",
+                 21: "trace decommitment invalid", 30: "malformed word stream", 31: "channel digest after the proof differs"}
+
+
+def pcs_verify(words, tree_logs, pow_bits=10, log_blowup=1, log_last_layer=0, n_queries=3, two_sample_every=0):
+    """The reference's verifier (CommitmentSchemeVerifier::verify_values + FriVerifier + MerkleVerifier) on proof words as
+    zko_pcs_prove / zkb_pcs_prove_* write them (the 8 channel-digest words at the end included). tree_logs: per tree, the
+    TRACE log size of every column. Returns (code, nested merkle code, layer or tree index); code 0 = accepts."""
+    w = _u32(words)
+    ncols = np.array([len(t) for t in tree_logs], np.int32)
+    logs = _u32([l for t in tree_logs for l in t])
+    info = np.zeros(2, np.int32)
+    lib().zko_pcs_verify.restype = C.c_int
+    rc = lib().zko_pcs_verify(_p(w), C.c_size_t(len(w)), C.c_int(len(tree_logs)), _p(ncols), _p(logs), C.c_uint32(pow_bits),
+                              C.c_uint32(log_blowup), C.c_uint32(log_last_layer), C.c_uint32(n_queries), C.c_int(two_sample_every), _p(info))
+    return int(rc), int(info[0]), int(info[1])
+
+
 def gkr_prove(instances, seed, verify=True, cap=1 << 22):
     """instances: list of (kind, num or None, den). Returns the proof words (rejects raise)."""
     kinds = np.array([k for k, _, _ in instances], np.int32)

@@ -5,6 +5,7 @@
 // (coordinate layout, as SecureColumnByCoords, nitroo/crates/stwo/src/prover/secure_column.rs:13-15);
 // GKR multilinear columns are arrays of QM31 as 4 consecutive uint32_t.
 #include "protocol.hpp"
+#include "verify.hpp"
 #include <cstdlib>
 #ifdef _OPENMP
 #include <omp.h>
@@ -351,6 +352,53 @@ long zko_pcs_prove(int n_trees, const int* tree_ncols, const uint32_t* const* co
     if (w.size() > cap) return -1;
     memcpy(out, w.data(), w.size() * 4);
     return (long)w.size();
+}
+
+// Verifies a proof made by zko_pcs_prove (or by the CUDA path's zkb_pcs_prove_*, same words) for trees of trace columns of
+// the given log sizes: the verifier replays the channel (config, commitments from the proof, out-of-domain point, the same
+// sampled points per column as the prover's rule) and runs CommitmentSchemeVerifier::verify_values. Returns 0 when the
+// proof is accepted AND the channel digest after it equals the 8 words that follow the proof; otherwise the VerifyError
+// code, with the nested Merkle error in info[0] and the layer / tree index in info[1] (info may be NULL). 31: the
+// trailing digest differs although the proof verifies.
+int zko_pcs_verify(const uint32_t* words, size_t n_words, int n_trees, const int* tree_ncols, const uint32_t* col_logs, uint32_t pow_bits,
+                   uint32_t log_blowup, uint32_t log_last_layer, uint32_t n_queries, int two_sample_every, int* info) {
+    PcsConfig cfg;
+    cfg.pow_bits = pow_bits;
+    cfg.fri = {log_blowup, log_last_layer, n_queries, 1};
+    std::vector<size_t> ncols;
+    for (int t = 0; t < n_trees; t++) ncols.push_back((size_t)tree_ncols[t]);
+    PcsProof proof;
+    size_t used = 0;
+    if (info) { info[0] = 0; info[1] = -1; }
+    if (!parse_pcs_proof(words, n_words, ncols, proof, used)) return (int)VerifyError::Malformed;
+    Channel ch(true);
+    cfg.mix_into(ch);
+    CommitmentSchemeVerifier v;
+    v.config = cfg;
+    int flat = 0;
+    for (int t = 0; t < n_trees; t++) {
+        std::vector<uint32_t> logs;
+        for (int c = 0; c < tree_ncols[t]; c++, flat++) logs.push_back(col_logs[flat]);
+        v.commit(proof.commitments[t], logs, ch);
+    }
+    CirclePoint<QM31> oods = get_random_point(ch);
+    std::vector<std::vector<std::vector<CirclePoint<QM31>>>> points(n_trees);
+    flat = 0;
+    for (int t = 0; t < n_trees; t++)
+        for (int c = 0; c < tree_ncols[t]; c++, flat++) {
+            std::vector<CirclePoint<QM31>> p;
+            if (two_sample_every && flat % two_sample_every == 0)
+                p.push_back(oods + into_ef(CanonicCoset(col_logs[flat]).step().conjugate()));
+            p.push_back(oods);
+            points[t].push_back(p);
+        }
+    VerifyResult r = v.verify_values(points, proof, ch);
+    if (info) { info[0] = (int)r.detail; info[1] = r.layer; }
+    if (!r.ok()) return (int)r.error;
+    if (used + 8 <= n_words)
+        for (int i = 0; i < 8; i++)
+            if (words[used + i] != load_le32(&ch.digest[4 * i])) return 31;
+    return 0;
 }
 
 // GKR batch proof of `n_inst` instances (kinds as in ops.hpp; nums[i] may be NULL). The channel is

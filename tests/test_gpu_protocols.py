@@ -35,6 +35,22 @@ def test_pcs_proof_matches_oracle(ctx, oracle, shape, kw):
     got = ctx.pcs_prove_host(trees, **kw)
     assert len(got) == len(want)
     assert (got == want).all()
+    # and the reference's verifier (oracle/verify.hpp) accepts what the CUDA path wrote
+    assert oracle.pcs_verify(got, shape, **kw) == (0, 0, -1)
+
+
+def test_verifier_rejects_a_tampered_cuda_proof(ctx, oracle):
+    """accepts=true has to mean something: the same verifier that accepts the CUDA path's proof rejects it after one word
+    of a queried value, of a FRI witness or of the nonce has been changed on the host."""
+    from proof_words import ProofWords
+
+    shape, kw = [[9] * 6, [10] * 2], dict(pow_bits=6, log_blowup=1, n_queries=12)
+    words = ctx.pcs_prove_host(_trees(shape, 4300), **kw)
+    assert oracle.pcs_verify(words, shape, **kw) == (0, 0, -1)
+    pw = ProofWords(words, [len(t) for t in shape])
+    assert oracle.pcs_verify(pw.flip(pw.queried[0]["at"] + 1), shape, **kw) == (21, 5, 0)
+    assert oracle.pcs_verify(pw.flip(pw.fri_layers[0]["witness_at"]), shape, **kw) == (12, 5, -1)
+    assert oracle.pcs_verify(pw.flip(pw.pow_at, 4), shape, **kw)[0] == 20
 
 
 def test_pcs_device_columns_and_phases(ctx, oracle):
