@@ -383,6 +383,13 @@ def pcs_prove(trees, pow_bits=10, log_blowup=1, log_last_layer=0, n_queries=3, t
     return out[:n].copy()
 
 
+def set_simd(on=True):
+    """Packed (16-lane) restatement of the reference's SIMD backend for the FFTs, leaf hashing, out-of-domain evaluation and
+    quotient numerators, on or off for every later call. Returns the lanes in use (16: AVX-512, 8: AVX2, 0: scalar)."""
+    lib().zko_set_simd.restype = C.c_int
+    return int(lib().zko_set_simd(C.c_int(1 if on else 0)))
+
+
 VERIFY_ERRORS = {0: "ok", 1: "merkle: witness too short", 2: "merkle: witness too long", 3: "merkle: too many queried values",
                  4: "merkle: too few queried values", 5: "merkle: root mismatch", 10: "fri: invalid number of layers",
                  11: "fri: first layer evaluations invalid", 12: "fri: first layer commitment invalid",

@@ -6,6 +6,11 @@
 // GKR multilinear columns are arrays of QM31 as 4 consecutive uint32_t.
 #include "protocol.hpp"
 #include "verify.hpp"
+#include "accel.hpp"
+namespace zko {
+void fill_accel_avx512(Accel& a);
+void fill_accel_avx2(Accel& a);
+}
 #include <cstdlib>
 #ifdef _OPENMP
 #include <omp.h>
@@ -137,15 +142,12 @@ void zko_blake2s(const uint8_t* data, size_t len, int m31, uint8_t* out32) {
 // prev: 2^(log_size+1) hashes of 32 bytes, or NULL. out: 2^log_size hashes.
 void zko_commit_on_layer(uint32_t log_size, const uint8_t* prev, const uint32_t* const* cols, int ncols, int m31, uint8_t* out) {
     size_t n = (size_t)1 << log_size;
-#pragma omp parallel for schedule(static)
-    for (size_t i = 0; i < n; i++) {
-        std::vector<M31> row(ncols);
-        for (int c = 0; c < ncols; c++) row[c] = M31(cols[c][i]);
-        Hash l, r;
-        if (prev) { memcpy(l.data(), prev + 64 * i, 32); memcpy(r.data(), prev + 64 * i + 32, 32); }
-        Hash h = hash_node(prev ? &l : nullptr, prev ? &r : nullptr, row.data(), row.size(), m31 != 0);
-        memcpy(out + 32 * i, h.data(), 32);
-    }
+    std::vector<Hash> pv;
+    if (prev) { pv.resize(2 * n); memcpy(pv.data(), prev, 64 * n); }
+    std::vector<const M31*> cp;
+    for (int c = 0; c < ncols; c++) cp.push_back(reinterpret_cast<const M31*>(cols[c]));
+    std::vector<Hash> h = commit_on_layer(log_size, prev ? &pv : nullptr, cp, m31 != 0);  // scalar, or packed when zko_set_simd(1)
+    memcpy(out, h.data(), 32 * n);
 }
 
 // ---- channel (opaque handle)
@@ -326,12 +328,15 @@ long zko_pcs_prove(int n_trees, const int* tree_ncols, const uint32_t* const* co
     int flat = 0;
     for (int t = 0; t < n_trees; t++) {
         std::vector<std::vector<M31>> columns;
-        for (int c = 0; c < tree_ncols[t]; c++, flat++) {
-            size_t n = (size_t)1 << col_logs[flat];
-            std::vector<M31> v(n);
-            for (size_t i = 0; i < n; i++) v[i] = M31(cols[flat][i]);
-            columns.push_back(std::move(v));
+        columns.resize(tree_ncols[t]);
+        const int flat0 = flat;
+#pragma omp parallel for schedule(dynamic)
+        for (int c = 0; c < tree_ncols[t]; c++) {
+            size_t n = (size_t)1 << col_logs[flat0 + c];
+            columns[c].resize(n);
+            memcpy(static_cast<void*>(columns[c].data()), cols[flat0 + c], 4 * n);  // M31 is one canonical word
         }
+        flat += tree_ncols[t];
         prover.commit_evals(columns, ch);
     }
     CirclePoint<QM31> oods = get_random_point(ch);
@@ -399,6 +404,22 @@ int zko_pcs_verify(const uint32_t* words, size_t n_words, int n_trees, const int
         for (int i = 0; i < 8; i++)
             if (words[used + i] != load_le32(&ch.digest[4 * i])) return 31;
     return 0;
+}
+
+// Switches the packed restatement of the SIMD backend on (1) or off (0) for every later call; returns the lanes in use:
+// 16 (AVX-512), 8 (AVX2) or 0 (scalar: off, or the CPU has neither).
+int zko_set_simd(int on) {
+    Accel& a = accel();
+    a = Accel();
+    if (on) {
+        __builtin_cpu_init();
+        if (__builtin_cpu_supports("avx512f") && __builtin_cpu_supports("avx512bw") && __builtin_cpu_supports("avx512dq") &&
+            __builtin_cpu_supports("avx512vl"))
+            fill_accel_avx512(a);
+        else if (__builtin_cpu_supports("avx2"))
+            fill_accel_avx2(a);
+    }
+    return a.lanes;
 }
 
 // GKR batch proof of `n_inst` instances (kinds as in ops.hpp; nums[i] may be NULL). The channel is

@@ -11,6 +11,7 @@
 //   nitroo/crates/stwo/src/prover/backend/cpu/grind.rs:6-15 and
 //   nitroo/crates/stwo/src/prover/backend/simd/grind.rs:18-25 (smallest nonce wins)
 #pragma once
+#include "accel.hpp"
 #include "fields.hpp"
 #include <array>
 #include <cstring>
@@ -145,6 +146,16 @@ inline std::vector<Hash> commit_on_layer(uint32_t log_size, const std::vector<Ha
                                          const std::vector<const M31*>& columns, bool m31) {
     size_t n = (size_t)1 << log_size;
     std::vector<Hash> out(n);
+    if (accel().leaf_hashes && !prev && !columns.empty() && log_size >= 4) {  // 16 rows per compression (simd.hpp)
+        std::vector<const uint32_t*> cp;
+        for (auto c : columns) cp.push_back(&c->v);
+        accel().leaf_hashes(reinterpret_cast<uint32_t*>(out.data()), cp.data(), cp.size(), n, m31);
+        return out;
+    }
+    if (accel().node_hashes && prev && columns.empty() && log_size >= 4) {
+        accel().node_hashes(reinterpret_cast<uint32_t*>(out.data()), reinterpret_cast<const uint32_t*>(prev->data()), n, m31);
+        return out;
+    }
 #pragma omp parallel for schedule(static) if (n >= 1024)
     for (size_t i = 0; i < n; i++) {
         std::vector<M31> row(columns.size());

@@ -13,11 +13,51 @@
 //   nitroo/crates/stwo/src/prover/lookups/utils.rs:26-54, 165-186    (Lagrange interpolation, horner, eq, fold_mle_evals)
 //   nitroo/crates/stwo/src/prover/lookups/gkr_prover.rs:884-923      (correct_sum_as_poly_in_first_variable)
 #pragma once
+#include "accel.hpp"
 #include "poly.hpp"
 
 namespace zko {
 
 using SecureColumn = std::vector<QM31>;
+
+// ---------------------------------------------------------------- domain tables for the timed baseline
+// The scalar statements below take every domain point by a scalar multiplication on the circle (Coset::at), as
+// CpuBackend does. The reference's SIMD backend walks domains incrementally instead (simd/domain.rs:14-60,
+// simd/fri.rs:27-116, simd/quotients.rs:73-164); when the packed restatement is switched on, the three functions that
+// need a point per row take it from these tables: the coset's points by repeated addition of its step, inverted in
+// one batch (core/fields/mod.rs batch_inverse). Same values, same results.
+inline std::vector<CirclePoint<M31>> coset_points_natural(const Coset& c) {
+    size_t n = c.size();
+    std::vector<CirclePoint<M31>> pts(n);
+    size_t chunk = n < 4096 ? n : 4096;
+#pragma omp parallel for schedule(static)
+    for (size_t a = 0; a < n; a += chunk) {
+        CirclePoint<M31> p = c.at(a);
+        for (size_t k = a; k < a + chunk && k < n; k++) { pts[k] = p; p = p + c.step; }
+    }
+    return pts;
+}
+inline void batch_inverse_in_place(std::vector<M31>& v) {
+    size_t n = v.size(), chunk = 1024;
+#pragma omp parallel for schedule(static)
+    for (size_t a = 0; a < n; a += chunk) {
+        size_t b = a + chunk < n ? a + chunk : n;
+        std::vector<M31> pre(b - a);
+        M31 run(1);
+        for (size_t k = a; k < b; k++) { pre[k - a] = run; run = run * v[k]; }
+        M31 inv = run.inverse();
+        for (size_t k = b; k-- > a;) { M31 x = v[k]; v[k] = inv * pre[k - a]; inv = inv * x; }
+    }
+}
+inline size_t fast_bit_reverse(size_t i, uint32_t log_size) {
+    if (!log_size) return i;
+    uint32_t x = (uint32_t)i;
+    x = ((x >> 1) & 0x55555555u) | ((x & 0x55555555u) << 1);
+    x = ((x >> 2) & 0x33333333u) | ((x & 0x33333333u) << 2);
+    x = ((x >> 4) & 0x0f0f0f0fu) | ((x & 0x0f0f0f0fu) << 4);
+    x = __builtin_bswap32(x);
+    return (size_t)(x >> (32 - log_size));
+}
 
 // ---------------------------------------------------------------- FRI folds
 // cpu/fri.rs:67-92. `eval` lives on `domain` (bit-reversed); the result lives on domain.dbl().
@@ -25,6 +65,19 @@ inline SecureColumn fold_line(const SecureColumn& eval, const LineDomain& domain
     size_t n = eval.size();
     assert(n >= 2);
     SecureColumn out(n / 2);
+    if (accel().lanes && n >= 64) {
+        auto pts = coset_points_natural(domain.coset);
+        std::vector<M31> xi(n / 2);
+        for (size_t i = 0; i < n / 2; i++) xi[i] = pts[fast_bit_reverse(i << 1, domain.log_size())].x;
+        batch_inverse_in_place(xi);
+#pragma omp parallel for schedule(static)
+        for (size_t i = 0; i < n / 2; i++) {
+            QM31 f0 = eval[2 * i], f1 = eval[2 * i + 1];
+            ibutterfly(f0, f1, xi[i]);
+            out[i] = f0 + alpha * f1;
+        }
+        return out;
+    }
 #pragma omp parallel for schedule(static) if (n >= 4096)
     for (size_t i = 0; i < n / 2; i++) {
         M31 x = domain.at(bit_reverse_index(i << 1, domain.log_size()));
@@ -38,6 +91,23 @@ inline SecureColumn fold_line(const SecureColumn& eval, const LineDomain& domain
 inline void fold_circle_into_line(SecureColumn& dst, const SecureColumn& src, const CircleDomain& domain, QM31 alpha) {
     assert(src.size() >> 1 == dst.size());
     QM31 alpha_sq = alpha * alpha;
+    if (accel().lanes && dst.size() >= 64) {
+        // rows 2i of the bit-reversed circle domain are the half coset's points in bit-reversed order
+        auto pts = coset_points_natural(domain.half_coset);
+        std::vector<M31> yi(dst.size());
+        for (size_t i = 0; i < dst.size(); i++) {
+            size_t j = fast_bit_reverse(i << 1, domain.log_size());
+            yi[i] = j < pts.size() ? pts[j].y : -pts[j - pts.size()].y;
+        }
+        batch_inverse_in_place(yi);
+#pragma omp parallel for schedule(static)
+        for (size_t i = 0; i < dst.size(); i++) {
+            QM31 f0 = src[2 * i], f1 = src[2 * i + 1];
+            ibutterfly(f0, f1, yi[i]);
+            dst[i] = dst[i] * alpha_sq + (alpha * f1 + f0);
+        }
+        return;
+    }
 #pragma omp parallel for schedule(static) if (dst.size() >= 4096)
     for (size_t i = 0; i < dst.size(); i++) {
         CirclePoint<M31> p = domain.at(bit_reverse_index(i << 1, domain.log_size()));
@@ -97,6 +167,23 @@ inline void accumulate_numerators(const std::vector<const M31*>& columns, size_t
     auto coeffs = column_line_coeffs(batches);
     for (size_t bi = 0; bi < batches.size(); bi++) {
         SecureColumn acc(size);
+        if (accel().numerators && size >= 16) {  // 16 rows per step (simd.hpp); sum_j (c_j v_j - b_j) = sum_j c_j v_j - sum_j b_j
+            std::vector<const uint32_t*> cp;
+            for (auto c : columns) cp.push_back(&c->v);
+            std::vector<size_t> idx;
+            std::vector<QM31> cs;
+            QM31 b_sum = QM31::zero();
+            for (size_t j = 0; j < batches[bi].cols_vals_randpows.size(); j++) {
+                idx.push_back(batches[bi].cols_vals_randpows[j].column_index);
+                cs.push_back(coeffs[bi][j].c);
+                b_sum = b_sum + coeffs[bi][j].b;
+            }
+            accel().numerators(reinterpret_cast<uint32_t*>(acc.data()), cp.data(), idx.data(), cs.data(), idx.size(), b_sum, size);
+            QM31 first = QM31::zero();
+            for (auto& lc : coeffs[bi]) first = first + lc.a;
+            out.push_back({batches[bi].point, acc, first});
+            continue;
+        }
 #pragma omp parallel for schedule(static) if (size >= 4096)
         for (size_t row = 0; row < size; row++) {
             QM31 numerator = QM31::zero();
@@ -119,9 +206,17 @@ inline SecureColumn compute_quotients_and_combine(const std::vector<AccumulatedN
     SecureColumn q(n);
     std::vector<CirclePoint<QM31>> pts;
     for (auto& a : accs) pts.push_back(a.sample_point);
+    std::vector<CirclePoint<M31>> table;
+    if (accel().lanes && n >= 64) table = coset_points_natural(domain.half_coset);
 #pragma omp parallel for schedule(static) if (n >= 4096)
     for (size_t row = 0; row < n; row++) {
-        CirclePoint<M31> dp = domain.at(bit_reverse_index(row, lifting_log_size));
+        CirclePoint<M31> dp;
+        if (!table.empty()) {
+            size_t j = fast_bit_reverse(row, lifting_log_size);
+            dp = j < table.size() ? table[j] : table[j - table.size()].conjugate();
+        } else {
+            dp = domain.at(bit_reverse_index(row, lifting_log_size));
+        }
         auto inv = denominator_inverses(pts, dp);
         QM31 quotient = QM31::zero();
         for (size_t k = 0; k < accs.size(); k++) {

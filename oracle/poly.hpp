@@ -9,6 +9,7 @@
 //        slow_precompute_twiddles, fft_layer_loop, circle_twiddles_from_line_twiddles)
 //   nitroo/crates/stwo/src/core/poly/utils.rs:11-23, 98-114       (fold, domain_line_twiddles_from_tree)
 #pragma once
+#include "accel.hpp"
 #include "circle.hpp"
 
 namespace zko {
@@ -125,6 +126,12 @@ inline void interpolate(std::vector<M31>& values, const CircleDomain& domain, co
     }
     auto line_tw = domain_line_twiddles_from_tree(domain.half_coset, tw.itwiddles);
     auto circle_tw = circle_twiddles_from_line_twiddles(line_tw[0]);
+    if (accel().interpolate && domain.log_size() >= 5) {  // the packed restatement of the SIMD backend (simd.hpp)
+        std::vector<const uint32_t*> lt;
+        for (auto& s : line_tw) lt.push_back(&s.p->v);
+        accel().interpolate(&values[0].v, domain.log_size(), lt.data(), &circle_tw[0].v, M31((uint32_t)domain.size()).inverse().v);
+        return;
+    }
     for (size_t h = 0; h < circle_tw.size(); h++) fft_layer_loop(values.data(), 0, h, circle_tw[h], ibf);
     for (size_t layer = 0; layer < line_tw.size(); layer++)
         for (size_t h = 0; h < line_tw[layer].n; h++)
@@ -154,6 +161,12 @@ inline std::vector<M31> evaluate(const std::vector<M31>& coeffs, const CircleDom
     }
     auto line_tw = domain_line_twiddles_from_tree(domain.half_coset, tw.twiddles);
     auto circle_tw = circle_twiddles_from_line_twiddles(line_tw[0]);
+    if (accel().evaluate && domain.log_size() >= 5) {
+        std::vector<const uint32_t*> lt;
+        for (auto& s : line_tw) lt.push_back(&s.p->v);
+        accel().evaluate(&values[0].v, domain.log_size(), lt.data(), &circle_tw[0].v);
+        return values;
+    }
     for (size_t layer = line_tw.size(); layer-- > 0;)
         for (size_t h = 0; h < line_tw[layer].n; h++)
             fft_layer_loop(values.data(), layer + 1, h, line_tw[layer].p[h], bf);
@@ -184,6 +197,7 @@ inline QM31 eval_at_point(const std::vector<M31>& coeffs, CirclePoint<QM31> poin
         x = double_x(x);
     }
     std::vector<QM31> rev(mappings.rbegin(), mappings.rend());
+    if (accel().eval_by_folding && coeffs.size() >= 64) return accel().eval_by_folding(&coeffs[0].v, coeffs.size(), rev.data());
     return fold(coeffs.data(), coeffs.size(), rev.data());
 }
 

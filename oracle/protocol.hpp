@@ -15,6 +15,9 @@
 //   nitroo/crates/stwo/src/prover/lookups/sumcheck.rs:96-176  (sumcheck prove_batch)
 //   nitroo/crates/stwo/src/prover/lookups/gkr_verifier.rs:17-149 (partially_verify_batch)
 #pragma once
+#include <omp.h>
+#include <cstdio>
+#include <cstdlib>
 #include <map>
 #include <numeric>
 
@@ -71,7 +74,9 @@ struct MerkleProver {
         for (uint32_t log = max_log + 1; log-- > 0;) {
             std::vector<const M31*> layer_cols;
             while (pos < sorted.size() && ilog2(sorted[pos].len) == log) layer_cols.push_back(sorted[pos++].data);
+            double t0 = omp_get_wtime();
             mp.layers[log] = commit_on_layer(log, log == max_log ? nullptr : &mp.layers[log + 1], layer_cols, m31);
+            if (getenv("ZKO_TIMING") && log + 3 > max_log) fprintf(stderr, "[zko]   layer %u: %.3f s (%zu cols)\n", log, omp_get_wtime() - t0, layer_cols.size());
         }
         return mp;
     }
@@ -319,6 +324,18 @@ struct PcsProof {
     }
 };
 
+// Phase times on stderr when ZKO_TIMING is set (a diagnostic for the timed CPU baseline).
+struct PhaseClock {
+    bool on = getenv("ZKO_TIMING") != nullptr;
+    double t0 = on ? omp_get_wtime() : 0.0;
+    void lap(const char* name) {
+        if (!on) return;
+        double t1 = omp_get_wtime();
+        fprintf(stderr, "[zko] %-12s %.3f s\n", name, t1 - t0);
+        t0 = t1;
+    }
+};
+
 struct CommitmentSchemeProver {
     PcsConfig config;
     std::vector<CommitmentTree> trees;
@@ -332,6 +349,7 @@ struct CommitmentSchemeProver {
         CommitmentTree t;
         t.evals.resize(columns.size());
         t.coeffs.resize(columns.size());
+        PhaseClock clock;
 #pragma omp parallel for schedule(dynamic)
         for (size_t k = 0; k < columns.size(); k++) {
             const auto& col = columns[k];
@@ -341,10 +359,12 @@ struct CommitmentSchemeProver {
             t.evals[k] = evaluate(c, CanonicCoset(log + config.fri.log_blowup_factor).circle_domain(), twiddles);
             t.coeffs[k] = std::move(c);
         }
+        clock.lap("fft");
         std::vector<ColumnRef> refs;
         for (auto& e : t.evals) refs.push_back({e.data(), e.size()});
         t.tree = MerkleProver::commit(refs, ch.m31);
         ch.mix_root(t.tree.root());
+        clock.lap("merkle");
         trees.push_back(std::move(t));
     }
 
@@ -420,6 +440,7 @@ struct CommitmentSchemeProver {
     // pcs/mod.rs:168-419
     PcsProof prove_values(const std::vector<std::vector<std::vector<CirclePoint<QM31>>>>& sampled_points, Channel& ch) {
         PcsProof proof;
+        PhaseClock clock;
         uint32_t lifting_log = trees.back().max_log();
         std::vector<std::vector<std::vector<PointSample>>> samples(trees.size());
         std::vector<QM31> flat_values;
@@ -438,12 +459,16 @@ struct CommitmentSchemeProver {
                 proof.sampled_values[t].push_back(vals);
             }
         }
+        clock.lap("sample");
         ch.mix_felts(flat_values);
         QM31 random_coeff = ch.draw_secure_felt();
         SecureColumn quotients = compute_fri_quotients(samples, random_coeff, lifting_log);
+        clock.lap("quotients");
         FriProver fri = FriProver::commit(ch, config.fri, quotients);
+        clock.lap("fri_commit");
         proof.proof_of_work = ch.grind(config.pow_bits);
         ch.mix_u64(proof.proof_of_work);
+        clock.lap("grind");
         std::vector<size_t> query_positions, unsorted;
         proof.fri = fri.decommit(ch, query_positions, unsorted);
         for (auto& t : trees) {
