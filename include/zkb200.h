@@ -126,6 +126,20 @@ int zkb_lde_cols(zkb_ctx* ctx, const uint32_t* const* coeffs, int ncols, int log
  * value of column c's polynomial at the QM31 circle point h_point = (x[4], y[4]). */
 int zkb_eval_at_point_cols(zkb_ctx* ctx, const uint32_t* const* coeffs, int ncols, int log_n,
                            const uint32_t* h_point, uint32_t* h_out);
+/* The PolyOps methods that evaluate from EVALUATIONS (STWO/prover/poly/circle/ops.rs:59-86; CPU statements
+ * backend/cpu/circle.rs:101-180). Off the prover's path (it keeps coefficients), provided in simplest correct form.
+ * barycentric_weights: 2^log_size weights (QM31, 4 consecutive words each, 16-byte aligned) for the canonic domain of
+ * that size and the point h_point (x[4], y[4]); log_size >= 3. */
+int zkb_barycentric_weights(zkb_ctx* ctx, int log_size, const uint32_t h_point[8], uint32_t* d_weights);
+/* barycentric_eval_at_point: sum_i evals[i] * weights[i] (evals bit-reversed on the canonic domain). */
+int zkb_barycentric_eval_at_point(zkb_ctx* ctx, const uint32_t* d_evals, const uint32_t* d_weights, int log_size, uint32_t h_out[4]);
+/* eval_at_point_by_folding: one circle fold and log_size - 1 line folds with the point's folding factors
+ * (core/poly/utils.rs:45-70), then division by 2^log_size; log_size >= 2. The evaluations are not modified. */
+int zkb_eval_at_point_by_folding(zkb_ctx* ctx, const uint32_t* d_evals, int log_size, const uint32_t h_point[8], uint32_t h_out[4]);
+/* FriOps::decompose (STWO/prover/fri.rs:82): not used by the prover and `todo!()` in the reference's own device
+ * backend (backend/cuda/fri.rs:71-77). Always returns ZKB_EINVAL with a message saying so. */
+int zkb_fri_decompose(zkb_ctx* ctx, const uint32_t* const d_eval[4], int log_size, uint32_t* const d_out[4], uint32_t h_lambda[4]);
+
 
 /* ---- ColumnOps::bit_reverse_column (STWO/prover/backend/mod.rs:39-42; core/utils.rs:71-81) -- */
 int zkb_bit_reverse_m31(zkb_ctx* ctx, uint32_t* col, int log_n);

@@ -169,6 +169,25 @@ def eval_at_point(coeffs, point8):
     return o
 
 
+def barycentric_weights(log_n, point8):
+    """cpu/circle.rs:101-132: [2^log_n][4] weights for the canonic domain and the point (x[4], y[4])."""
+    o = np.zeros((1 << log_n, 4), np.uint32)
+    lib().zko_barycentric_weights(C.c_uint32(log_n), _p(_u32(point8)), _p(o))
+    return o
+
+
+def barycentric_eval_at_point(evals, weights):
+    e, w, o = _u32(evals), _u32(weights), np.zeros(4, np.uint32)
+    lib().zko_barycentric_eval(_p(e), _p(w), C.c_uint32(int(len(e)).bit_length() - 1), _p(o))
+    return o
+
+
+def eval_at_point_by_folding(evals, point8):
+    e, o = _u32(evals), np.zeros(4, np.uint32)
+    lib().zko_eval_by_folding(_p(e), C.c_uint32(int(len(e)).bit_length() - 1), _p(_u32(point8)), _p(o))
+    return o
+
+
 def bit_reverse(v):
     v = np.array(v, dtype=np.uint32, copy=True)
     lib().zko_bit_reverse_u32(_p(v), C.c_uint32(int(len(v)).bit_length() - 1))

@@ -6,6 +6,7 @@
 // GKR multilinear columns are arrays of QM31 as 4 consecutive uint32_t.
 #include "protocol.hpp"
 #include "verify.hpp"
+#include "bary.hpp"
 #include "accel.hpp"
 namespace zko {
 void fill_accel_avx512(Accel& a);
@@ -130,6 +131,26 @@ void zko_eval_at_point(const uint32_t* coeffs, uint32_t log_n, const uint32_t* p
     for (size_t i = 0; i < v.size(); i++) v[i] = M31(coeffs[i]);
     CirclePoint<QM31> p{q_from(point8), q_from(point8 + 4)};
     q_to(eval_at_point(v, p), out4);
+}
+
+// PolyOps from evaluations: weights (2^log x 4 words), the weighted sum, and evaluation by folding (cpu/circle.rs:101-180).
+void zko_barycentric_weights(uint32_t log_n, const uint32_t* point8, uint32_t* out) {
+    CirclePoint<QM31> p{q_from(point8), q_from(point8 + 4)};
+    auto w = barycentric_weights(log_n, p);
+    for (size_t i = 0; i < w.size(); i++) q_to(w[i], out + 4 * i);
+}
+void zko_barycentric_eval(const uint32_t* evals, const uint32_t* weights, uint32_t log_n, uint32_t* out4) {
+    size_t n = (size_t)1 << log_n;
+    std::vector<M31> e(n);
+    std::vector<QM31> w(n);
+    for (size_t i = 0; i < n; i++) { e[i] = M31(evals[i]); w[i] = q_from(weights + 4 * i); }
+    q_to(barycentric_eval_at_point(e, w), out4);
+}
+void zko_eval_by_folding(const uint32_t* evals, uint32_t log_n, const uint32_t* point8, uint32_t* out4) {
+    std::vector<M31> e((size_t)1 << log_n);
+    for (size_t i = 0; i < e.size(); i++) e[i] = M31(evals[i]);
+    CirclePoint<QM31> p{q_from(point8), q_from(point8 + 4)};
+    q_to(eval_at_point_by_folding(e, p), out4);
 }
 
 void zko_bit_reverse_u32(uint32_t* v, uint32_t log_n) { bit_reverse(v, (size_t)1 << log_n); }

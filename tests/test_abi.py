@@ -32,3 +32,53 @@ def test_no_oracle_in_product():
                 text = open(os.path.join(dirpath, f)).read()
                 for needle in ("import oracle", "from oracle", "oracle/", "zko_", "zkoracle"):
                     assert needle not in text, (os.path.join(dirpath, f), needle)
+
+
+def test_rust_binding_matches_the_headers():
+    """shim/src/ffi.rs is what shim/gen_ffi.py writes from include/*.h today (the Rust binding cannot drift)."""
+    import subprocess
+    import sys
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "shim", "gen_ffi.py"), "--check"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    ffi = open(os.path.join(ROOT, "shim", "src", "ffi.rs")).read()
+    bound = set(re.findall(r"pub fn (zkb_[a-z0-9_]+)\(", ffi))
+    assert bound == set(zkb_all_symbols())
+    # every module lib.rs declares exists, and every zkb_* a module calls is declared in ffi.rs
+    src = os.path.join(ROOT, "shim", "src")
+    for mod in re.findall(r"^(?:pub )?mod ([a-z_]+);", open(os.path.join(src, "lib.rs")).read(), flags=re.M):
+        text = open(os.path.join(src, mod + ".rs")).read()
+        if mod != "ffi":
+            called = set(re.findall(r"ffi::(zkb_[a-z0-9_]+)", text))
+            assert called <= bound, (mod, sorted(called - bound))
+            # no rustc here: at least the number of arguments at each call site equals the declaration's
+            for m in re.finditer(r"ffi::(zkb_[a-z0-9_]+)\(", text):
+                assert _call_args(text, m.end() - 1) == _declared_args(ffi, m.group(1)), (mod, m.group(1))
+
+
+def _declared_args(ffi, name):
+    m = re.search(r"pub fn " + name + r"\(([^;]*?)\)\s*(?:->[^;]*)?;", ffi, flags=re.S)
+    return len([a for a in m.group(1).split(",") if a.strip()])
+
+
+def _call_args(text, open_paren):
+    depth, commas, j = 0, 0, open_paren
+    while True:
+        c = text[j]
+        if c in "([{":
+            depth += 1
+        elif c in ")]}":
+            depth -= 1
+            if depth == 0:
+                break
+        elif c == "," and depth == 1:
+            commas += 1
+        j += 1
+    inner = text[open_paren + 1:j].strip()
+    if not inner:
+        return 0
+    return commas + (0 if inner.endswith(",") else 1)
+
+
+def zkb_all_symbols():
+    from zk_inference_prover_b200 import capi
+    return list(capi.EXPORTED_SYMBOLS) + list(capi.PROVER_SYMBOLS) + list(capi.AIR_SYMBOLS)

@@ -430,3 +430,32 @@ def test_device_channel_step_and_folds_with_device_challenge(ctx, oracle):
             ctx.fold_circle_into_line_dalpha_leaves([b.ptr for b in c3], [b.ptr for b in bi], log_n, d_alpha.ptr + 32, lv.ptr)
             ctx.merkle_layer(log_n - 1, 0, [b.ptr for b in c1], want_lv.ptr)
             assert all((a.download() == b.download()).all() for a, b in zip(c1, c3)) and (lv.download() == want_lv.download()).all()
+
+
+# ------------------------------------------------------------------ PolyOps from evaluations (barycentric, folding)
+@pytest.mark.parametrize("log_n", [3, 4, 7, 10, 14])
+def test_barycentric_and_folding_evaluation(ctx, oracle, log_n):
+    vals = edge_m31_column(8800 + log_n, 1 << log_n)
+    point = oracle.secure_circle_mul(0x2468ACE + log_n)
+    ev = ctx.upload(vals)
+    w = ctx.barycentric_weights(log_n, point)
+    want_w = oracle.barycentric_weights(log_n, point)
+    assert (w.download(shape=(-1, 4)) == want_w).all()
+    got = ctx.barycentric_eval_at_point(ev.ptr, w.ptr, log_n)
+    assert (got == oracle.barycentric_eval_at_point(vals, want_w)).all()
+    by_folding = ctx.eval_at_point_by_folding(ev.ptr, log_n, point)
+    assert (by_folding == oracle.eval_at_point_by_folding(vals, point)).all()
+    # the relation the reference's own tests check: all routes give the polynomial's value at the point
+    coeffs = oracle.interpolate_cols([vals], log_n)[0]
+    assert (got == oracle.eval_at_point(coeffs, point)).all() and (by_folding == got).all()
+    assert (ev.download() == vals).all()
+
+
+def test_fri_decompose_is_refused(ctx, zkb):
+    import ctypes as C
+
+    buf = ctx.alloc(64)
+    arr = (C.c_void_p * 4)(*[buf.ptr] * 4)
+    lam = np.zeros(4, np.uint32)
+    rc = ctx.lib.zkb_fri_decompose(ctx.h, arr, C.c_int(4), arr, lam.ctypes.data_as(C.c_void_p))
+    assert rc == -1 and b"decompose" in ctx.lib.zkb_last_error(ctx.h)

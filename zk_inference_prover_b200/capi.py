@@ -15,7 +15,7 @@ EXPORTED_SYMBOLS = [
     "zkb_event_record", "zkb_event_elapsed_ms", "zkb_profile_begin", "zkb_profile_end", "zkb_fft_arith_ceiling",
     "zkb_malloc", "zkb_free", "zkb_memset_zero", "zkb_h2d", "zkb_d2h", "zkb_h2d_async", "zkb_d2h_async", "zkb_h2d_overlapped", "zkb_wait_fence", "zkb_d2d",
     "zkb_host_alloc_pinned", "zkb_host_free_pinned", "zkb_gather_multi", "zkb_gather_hashes", "zkb_gather_words", "zkb_twiddles_d2h",
-    "zkb_ifft_cols", "zkb_lde_cols", "zkb_eval_at_point_cols", "zkb_bit_reverse_m31", "zkb_bit_reverse_qm31",
+    "zkb_ifft_cols", "zkb_lde_cols", "zkb_eval_at_point_cols", "zkb_barycentric_weights", "zkb_barycentric_eval_at_point", "zkb_eval_at_point_by_folding", "zkb_fri_decompose", "zkb_bit_reverse_m31", "zkb_bit_reverse_qm31",
     "zkb_merkle_layer", "zkb_merkle_leaves_partial", "zkb_merkle_top", "zkb_fold_line_dalpha", "zkb_fold_circle_into_line_dalpha", "zkb_channel_mix_root_draw", "zkb_fold_line_dalpha_leaves", "zkb_fold_circle_into_line_dalpha_leaves", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine", "zkb_quot_combine_rows",
     "zkb_accumulate", "zkb_lift_accumulate", "zkb_secure_powers", "zkb_gkr_eq_evals", "zkb_gkr_next_layer",
     "zkb_gkr_sum", "zkb_gkr_fix_and_sum", "zkb_mle_fix_qm31", "zkb_mle_fix_m31", "zkb_grind", "zkb_gkr_sum_noalloc", "zkb_gkr_sum_noalloc_error",
@@ -342,6 +342,24 @@ class Context:
         n = C.c_int()
         self._check(self.lib.zkb_profile_end(self.h, names, ms, cnt, C.c_int(cap), C.byref(n)))
         return {names[i].decode(): (ms[i], cnt[i]) for i in range(n.value)}
+
+    def barycentric_weights(self, log_size, point8):
+        """-> DeviceBuffer of 2^log_size QM31 weights."""
+        out = self.alloc(4 << log_size)
+        self._check(self.lib.zkb_barycentric_weights(self.h, C.c_int(log_size), _u32(point8).ctypes.data_as(C.c_void_p), C.c_void_p(out.ptr)))
+        return out
+
+    def barycentric_eval_at_point(self, evals_ptr, weights_ptr, log_size):
+        o = np.zeros(4, np.uint32)
+        self._check(self.lib.zkb_barycentric_eval_at_point(self.h, C.c_void_p(evals_ptr), C.c_void_p(weights_ptr), C.c_int(log_size),
+                                                           o.ctypes.data_as(C.c_void_p)))
+        return o
+
+    def eval_at_point_by_folding(self, evals_ptr, log_size, point8):
+        o = np.zeros(4, np.uint32)
+        self._check(self.lib.zkb_eval_at_point_by_folding(self.h, C.c_void_p(evals_ptr), C.c_int(log_size),
+                                                          _u32(point8).ctypes.data_as(C.c_void_p), o.ctypes.data_as(C.c_void_p)))
+        return o
 
     def fft_arith_ceiling(self):
         """Butterflies per second of the register-only butterfly kernel (the ceiling of the FFT passes)."""
