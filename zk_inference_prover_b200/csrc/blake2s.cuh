@@ -20,16 +20,29 @@ __device__ __forceinline__ uint32_t rotr8(uint32_t x) { return __byte_perm(x, 0,
 __device__ __forceinline__ uint32_t rotr12(uint32_t x) { return __funnelshift_r(x, x, 12); }
 __device__ __forceinline__ uint32_t rotr7(uint32_t x) { return __funnelshift_r(x, x, 7); }
 
-#define B2S_G(a, b, c, d, x, y) \
-    do {                        \
-        a = a + b + (x);        \
-        d = rotr16(d ^ a);      \
-        c = c + d;              \
-        b = rotr12(b ^ c);      \
-        a = a + b + (y);        \
-        d = rotr8(d ^ a);       \
-        c = c + d;              \
-        b = rotr7(b ^ c);       \
+// Where the additions run. Every instruction of a G function (additions, xors, rotations) would go to the integer ALU
+// pipe, which issues one warp instruction every two cycles, and the compression is bound by that pipe. A multiply-add
+// by one runs on the FMA-heavy pipe instead, in parallel. The compiler moves `c + d` there by itself; forcing
+// `(a + x) + b` to add `x` on the ALU and `b` on the FMA pipe as well measured 8% more compressions per second than
+// leaving it one three-input ALU addition (all additions on the FMA pipe: 3% fewer). The multiplier is read from
+// constant memory so that the compiler can not fold the multiplication away.
+static __constant__ uint32_t b2s_one = 1u;
+__device__ __forceinline__ uint32_t b2s_fma_add(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b2s_one), "r"(b));
+    return r;
+}
+
+#define B2S_G(a, b, c, d, x, y)        \
+    do {                               \
+        a = b2s_fma_add(a + (x), b);   \
+        d = rotr16(d ^ a);             \
+        c = b2s_fma_add(c, d);         \
+        b = rotr12(b ^ c);             \
+        a = b2s_fma_add(a + (y), b);   \
+        d = rotr8(d ^ a);              \
+        c = b2s_fma_add(c, d);         \
+        b = rotr7(b ^ c);              \
     } while (0)
 
 #define B2S_ROUND(s0, s1, s2, s3, s4, s5, s6, s7, s8, s9, s10, s11, s12, s13, s14, s15) \
