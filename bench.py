@@ -1203,17 +1203,21 @@ def run_decode_step(args, rank, world, local_rank):
 
 
 def run_witness(args, rank):
-    """--mode witness: the two device witness generators at the sizes of a layer segment: the tables' own columns at 2^23 rows
-    with four key-tile counters, and a dequantize component of the bf16-chain variant for a 4096 x 4096 matmul over 512 tokens
-    (16 slots per row, 2^17 rows, 242 committed and 37 preprocessed columns). Byte work: reported against the HBM peak with
-    the algorithmic bytes (every column written once, every counter and accumulator read once)."""
+    """--mode witness: the device witness generators at the sizes of a layer segment, and a proof whose trace never leaves the
+    device. Generators: the tables' own columns at 2^23 rows with four key-tile counters; a dequantize component of the
+    bf16-chain variant for a 4096 x 4096 matmul over 512 tokens (16 slots per row, 2^17 rows, 242 committed and 37
+    preprocessed columns); a residual-stream component (128 bf16 additions per row over 2^15 rows: 2,304 committed columns);
+    the normalisation table's six preprocessed columns and its multiplicities. Byte work: reported against the HBM peak with
+    the algorithmic bytes (every column written once, every input read once). The last leg generates the dequantize and
+    residual-stream traces on the device and commits and opens them in one PCS proof (the reference's own device path: witness
+    kernels, then commit, with no trace upload)."""
     if rank != 0:
         return
     import zk_inference_prover_b200 as z
-    from zk_inference_prover_b200.witness_cases import dequant_case, tables_case
+    from zk_inference_prover_b200.witness_cases import dequant_case, residual_stream_case, tables_case
 
     peak, peak_kind = measured_hbm_peak()
-    ctx = z.Context(device=0, max_log_size=10)
+    ctx = z.Context(device=0, max_log_size=20)
     log_rows, n_counters = 23, 4
     expmap, counters, _, _ = tables_case(7, log_rows, n_counters)
     rows = 1 << log_rows
@@ -1227,33 +1231,83 @@ def run_witness(args, rank):
     pre = [ctx.alloc(drows) for _ in range(case["n_pre"])]
     m_norm, m_frac = ctx.alloc(cfg["n_norm"]).zero(), ctx.alloc(cfg["n_frac"]).zero()
     m_mul, m_r8, counts = ctx.alloc(cfg["n_mul"]).zero(), ctx.alloc(cfg["n_r8"]).zero(), ctx.alloc(3).zero()
-    t_tab, t_deq = [], []
+    # residual stream: hd = 128 additions per row
+    rs_log = 15
+    rs = residual_stream_case(9, "pairs", 128, rs_log, 1 << rs_log, kind=0, sticky=True, kmax=13, spread=8)
+    rrows, ml = 1 << rs_log, rs["m_len"]
+    r_wit, r_norm = ctx.upload(rs["wit"]), ctx.upload(rs["norm3"])
+    r_smul = up(np.ascontiguousarray(rs["smul3"], np.int32))
+    r_cols = [ctx.alloc(rrows) for _ in range(rs["n_cols"])]
+    r_out_pat, r_out_nat, r_in_nat = ctx.alloc(rrows * 128), ctx.alloc(rrows * 256), ctx.alloc(rrows * rs["n_leaves"] * 2)
+    r_ms = {k: ctx.alloc(ml[k]).zero() for k in ("pow", "norm", "val", "frac", "smul")}
+    r_counts = ctx.alloc(4).zero()
+    # the normalisation table of that component: 256 + 14 * 512 rows in 2^13
+    t_cols, t_m = [ctx.alloc(1 << 13) for _ in range(6)], ctx.alloc(1 << 13)
+
+    def gen_residual():
+        ctx.witness_residual_stream(rs["lowered_groups"], rs["lowered_slots"], rs["out_slot"], 0, True, 13, r_norm.ptr, len(rs["norm3"]) // 3,
+                                    r_smul.ptr, len(rs["smul3"]) // 3, [], rs["n_val"], r_wit.ptr, rrows, rs_log, [c.ptr for c in r_cols],
+                                    r_out_pat.ptr, r_out_nat.ptr, r_in_nat.ptr, {k: (v.ptr, ml[k]) for k, v in r_ms.items()}, [], r_counts.ptr)
+
+    def gen_dequant():
+        ctx.witness_dequant(cfg, d_acc.ptr, 0, 0, d_sx.ptr, d_sw.ptr, d_norm.ptr, d_mul.ptr, [b.ptr for b in base], [p.ptr for p in pre],
+                            m_norm.ptr, m_frac.ptr, m_mul.ptr, m_r8.ptr, counts.ptr, 0)
+
+    trace_ptrs = [b.ptr for b in base] + [c.ptr for c in r_cols]
+    trace_logs = [drows.bit_length() - 1] * len(base) + [rs_log] * len(r_cols)
+    t_tab, t_deq, t_rs, t_pre, t_gen, t_prove = [], [], [], [], [], []
+    words = None
     for it in range(args.warmup + args.steps):
         ctx.sync()
         ctx.event_record(0)
         ctx.witness_tables(d_map.ptr, [c.ptr for c in d_cnt], log_rows, False, 2.0 ** 7, x.ptr, y.ptr, m.ptr)
         ctx.event_record(1)
-        ctx.witness_dequant(cfg, d_acc.ptr, 0, 0, d_sx.ptr, d_sw.ptr, d_norm.ptr, d_mul.ptr, [b.ptr for b in base], [p.ptr for p in pre],
-                            m_norm.ptr, m_frac.ptr, m_mul.ptr, m_r8.ptr, counts.ptr, 0)
+        gen_dequant()
         ctx.event_record(2)
+        gen_residual()
+        ctx.event_record(3)
+        ctx.witness_pre_table(0, 13, 13, 0, [r_ms["norm"].ptr], [c.ptr for c in t_cols], t_m.ptr)
+        ctx.event_record(4)
+        ctx.sync()
+        # the trace generated on the device, committed and opened where it lies
+        ctx.event_record(5)
+        gen_dequant()
+        gen_residual()
+        ctx.event_record(6)
+        words = ctx.pcs_prove_device([trace_ptrs], trace_logs, pow_bits=10, log_blowup=1, log_last_layer=0, n_queries=70, cap=1 << 26)
+        ctx.event_record(7)
         ctx.sync()
         if it >= args.warmup:
             t_tab.append(ctx.event_elapsed_ms(0, 1))
             t_deq.append(ctx.event_elapsed_ms(1, 2))
-    tab_ms, deq_ms = float(np.mean(t_tab)), float(np.mean(t_deq))
+            t_rs.append(ctx.event_elapsed_ms(2, 3))
+            t_pre.append(ctx.event_elapsed_ms(3, 4))
+            t_gen.append(ctx.event_elapsed_ms(5, 6))
+            t_prove.append(ctx.event_elapsed_ms(6, 7))
+    tab_ms, deq_ms, rs_ms, pre_ms = (float(np.mean(t)) for t in (t_tab, t_deq, t_rs, t_pre))
+    gen_ms, prove_ms = float(np.mean(t_gen)), float(np.mean(t_prove))
     tab_bytes = rows * 4 * (3 + n_counters)
     deq_bytes = drows * 4 * (case["n_base"] + case["n_pre"] + cfg["per_row"])
-    cells = 3 * rows + drows * (case["n_base"] + case["n_pre"])
+    rs_bytes = rrows * 4 * (rs["n_cols"] + rs["n_leaves"] * 3 + 128 * 3)  # columns, patterns in, natural pairs in and out, patterns out
+    cells = 3 * rows + drows * (case["n_base"] + case["n_pre"]) + rrows * rs["n_cols"]
+    trace_cells = drows * len(base) + rrows * len(r_cols)
+    gbs = lambda by, ms: by / (ms * 1e-3) / 1e9
     print(json.dumps({
-        "metric": "witness_cells_per_s", "value": cells / ((tab_ms + deq_ms) * 1e-3), "unit": "cells/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": tab_ms + deq_ms, "higher_is_better": True, "dtype": "u32 / i32", "data": "synthetic",
-        "config": {"workload": "witness_tables_2^23_4counters + witness_dequant_chain_512x4096_per_row16"},
-        "tables": {"ms": tab_ms, "algorithmic_bytes": tab_bytes, "gbs": tab_bytes / (tab_ms * 1e-3) / 1e9,
-                   "frac_of_hbm_peak": tab_bytes / (tab_ms * 1e-3) / 1e9 / peak},
+        "metric": "witness_cells_per_s", "value": cells / ((tab_ms + deq_ms + rs_ms) * 1e-3), "unit": "cells/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": tab_ms + deq_ms + rs_ms, "higher_is_better": True, "dtype": "u32 / i32", "data": "synthetic",
+        "config": {"workload": "witness_tables_2^23_4counters + witness_dequant_chain_512x4096_per_row16 + residual_stream_128adds_2^15"},
+        "tables": {"ms": tab_ms, "algorithmic_bytes": tab_bytes, "gbs": gbs(tab_bytes, tab_ms), "frac_of_hbm_peak": gbs(tab_bytes, tab_ms) / peak},
         "dequant": {"ms": deq_ms, "columns": case["n_base"] + case["n_pre"], "rows": drows, "algorithmic_bytes": deq_bytes,
-                    "gbs": deq_bytes / (deq_ms * 1e-3) / 1e9, "frac_of_hbm_peak": deq_bytes / (deq_ms * 1e-3) / 1e9 / peak,
-                    "counts": counts.download().tolist()},
-        "peak_gbs": peak, "peak_kind": peak_kind, "gpu_launches": 2 * args.steps}))
+                    "gbs": gbs(deq_bytes, deq_ms), "frac_of_hbm_peak": gbs(deq_bytes, deq_ms) / peak, "counts": counts.download().tolist()},
+        "residual_stream": {"ms": rs_ms, "columns": rs["n_cols"], "rows": rrows, "slots_per_row": 128, "algorithmic_bytes": rs_bytes,
+                            "gbs": gbs(rs_bytes, rs_ms), "frac_of_hbm_peak": gbs(rs_bytes, rs_ms) / peak, "counts": r_counts.download()[:3].tolist()},
+        "norm_table": {"ms": pre_ms, "rows": 1 << 13, "columns": 7, "note": "launch-latency sized: 229 KB written"},
+        "device_trace_to_proof": {"ms": gen_ms + prove_ms, "witness_ms": gen_ms, "proof_ms": prove_ms, "cells": trace_cells,
+                                  "cells_per_s": trace_cells / ((gen_ms + prove_ms) * 1e-3), "columns": len(trace_ptrs),
+                                  "h2d_trace_bytes": 0, "proof_words": int(words.size),
+                                  "what": "dequantize (2^17 rows) and residual-stream (2^15 rows) traces written by the witness kernels and "
+                                          "committed and opened in one PCS proof (blow-up 2, 70 queries); nothing of the trace is uploaded"},
+        "peak_gbs": peak, "peak_kind": peak_kind, "gpu_launches": 4 * args.steps}))
     ctx.close()
 
 

@@ -348,6 +348,109 @@ int zkb_witness_dequant(zkb_ctx* ctx, const int32_t* acc, const int32_t* jx, con
                         uint32_t n_pre, uint32_t* m_norm, uint32_t* m_frac, uint32_t* m_mul, uint32_t* m_r8, uint32_t* counts,
                         uint32_t* want_out, const zkb_dequant_cfg* cfg);
 
+/* ---- Witness generation, three more families: shared bf16 tables, key tile selectors, residual stream ------
+ * Same conventions as above: committed order, device pointers unless named h_ or said to be host arrays, nothing
+ * synchronised. The reference kernels' `mutate` arguments (deliberate defects for negative controls) are not built. */
+
+#define ZKB_PRE_NORM 0  /* 6 columns: m2, ph, st, m7, exponent field, non-zero flag (prover/src/bf16.rs:130-158) */
+#define ZKB_PRE_FRAC 1  /* 3 columns: ph, r, st (prover/src/gadgets/residual_stream/mod.rs:1116-1122) */
+#define ZKB_PRE_MUL 2   /* 4 columns: a, b, m7, carry (prover/src/bf16.rs:264-281) */
+#define ZKB_PRE_QNZ 3   /* 2 columns: the row index and whether it is non-zero */
+#define ZKB_PRE_RANGE 4 /* 1 column: the row index */
+/* One shared table's preprocessed columns and its multiplicity column (device original zk_witness_gen_pre_table,
+ * stwo_cuda/cuda/zk_pre_witness_gen.cu:150-270, called from prover/src/devpre.rs:482). Every row is computed from its
+ * own index d = coset_perm(i): no table is uploaded. round: 0 nearest-even (the tables then carry a sticky bit),
+ * 1 nearest-away, 2 truncate. The table's own length (256 + (kmax+1) * 256 * (1 + sticky) for NORM, 2^(kmax+1) for
+ * FRAC, 2^14 for MUL, 2^log_rows otherwise) must fit 2^log_rows; rows past it commit zero. n_cols must be the
+ * kind's column count; cols is a host array of n_cols device columns (8-byte aligned). m_col (may be NULL)
+ * receives the sum over the n_counters counter arrays at the row. Then natural row patch_idx[t] takes the n_cols
+ * values patch_val[t * n_cols ..] (the rows where a witness's own table is not the closed form). log_rows >= 1. */
+int zkb_witness_pre_table(zkb_ctx* ctx, uint32_t kind, uint32_t log_rows, uint32_t kmax, uint32_t round, const uint32_t* const* counters,
+                          uint32_t n_counters, const uint32_t* patch_idx, const uint32_t* patch_val, uint32_t n_patch, uint32_t* const* cols,
+                          uint32_t n_cols, uint32_t* m_col);
+
+#define ZKB_TILE_CHAN 0
+#define ZKB_TILE_KEY 1
+#define ZKB_TILE_TOK 2
+#define ZKB_TILE_ACTIVE 1u  /* the row belongs to a group (not an inert lead row) */
+#define ZKB_TILE_NOFIRST 2u /* not the first row of its group */
+#define ZKB_TILE_LAST 4u    /* the last row of its group */
+#define ZKB_TILE_ISTART 8u  /* the first row of an instance */
+/* The per-row layout flags of one key tile sub-component, in NATURAL row order (device original zk_flags_key_tile,
+ * stwo_cuda/cuda/zk_acc.cu:78-97 with zk_acc.cuh:116-180; host statement prover/src/gadgets/attention/trace.rs:742-790
+ * over Grid::row, prover/src/layout.rs:141-183). CHAN and KEY rows are tiled groups * chunks + lead = 2^log_rows
+ * (descending: groups run downwards); an instance starts at the first row of a group g with g mod modulus ==
+ * modulus - 1 (modulus = head dimension for CHAN, context length for KEY). TOK has no groups: every row is active and
+ * an instance starts where (rows - j) * rw is a multiple of modulus (the sequence length). */
+int zkb_key_tile_flags(zkb_ctx* ctx, uint32_t shape, uint32_t log_rows, uint32_t groups, uint32_t chunks, uint32_t lead, uint32_t descending,
+                       uint32_t modulus, uint32_t rw, uint32_t* flags);
+/* The selector columns of that sub-component, committed order, from its flags (device original zk_witness_gen_sel,
+ * stwo_cuda/cuda/zk_pre_witness_gen.cu:292-385, called from prover/src/devpre.rs:635). With pos = (j > 0) and
+ * end = (j + 1 == rows): TOK (3 columns) pos, end, ISTART; CHAN (5) NOFIRST, LAST, pos, end, ISTART; KEY (8 or 9)
+ * NOFIRST, LAST, pos, end, pos & !LAST, pos & LAST, ISTART, the key scale scale[group / ctx_len] of the row's
+ * instance (1 on inert rows, and everywhere when with_scale is 0; scale holds n_insts inverted scales), and as a
+ * ninth column ACTIVE. cols: host array of n_cols device columns. */
+int zkb_witness_selectors(zkb_ctx* ctx, uint32_t shape, uint32_t log_rows, uint32_t groups, uint32_t chunks, uint32_t lead, uint32_t descending,
+                          const uint32_t* flags, const uint32_t* scale, uint32_t ctx_len, uint32_t n_insts, int with_scale, uint32_t* const* cols,
+                          uint32_t n_cols);
+
+/* The residual-stream component's program, lowered to column indices (Prog, prover/src/gadgets/residual_stream/mod.rs:387-611;
+ * the reference passes the same records, stwo_cuda/cuda/zk_residual_stream_witness_gen.cuh:70-115, filled at
+ * prover/src/gadgets/residual_stream/device.rs:300-420). Values are bf16 numbers held as (sm, ef): signed significand
+ * +-[128, 256) or 0, and exponent field. */
+#define ZKB_RS_NONE 0xffffffffu /* an operand that is the constant zero */
+typedef struct zkb_rs_group {
+    uint32_t n;        /* leaves of this group per row */
+    uint32_t leaf_col; /* column of leaf 0's sm; leaf k is at leaf_col + k * width: sm, ef[, unary sm, unary ef] */
+    uint32_t width;    /* 2, or 4 when the group carries a unary image */
+    uint32_t un;       /* 0: none; else 1 + index of the unary table */
+    uint32_t flat;     /* index of the group's first leaf inside a row of `wit` (the sum of the earlier groups' n) */
+} zkb_rs_group;
+typedef struct zkb_rs_slot {
+    uint32_t a_sm, a_ef, b_sm, b_ef; /* columns of the two operands (a_sm == ZKB_RS_NONE: the constant zero) */
+    uint32_t base;                   /* first column of the slot's own cells */
+    uint32_t o_sm, o_ef;             /* columns of the slot's output pair */
+    uint32_t from_slot;              /* bit 0: operand a is a slot output (its exponent is clamped to 0xfe on reading); bit 1: b */
+} zkb_rs_slot;
+typedef struct zkb_rs_program {
+    const zkb_rs_group* groups; /* host array */
+    uint32_t n_groups;
+    const zkb_rs_slot* slots;   /* host array, evaluation order */
+    uint32_t n_slots;
+    const uint32_t* out_slot;   /* host array: the slots whose outputs are reported, flattened */
+    uint32_t out_w;
+    uint32_t kind;              /* 0: every slot adds (13 cells, 14 with the sticky bit); 1: every slot multiplies (4 cells) */
+    uint32_t sticky, kmax;      /* as for the tables above */
+} zkb_rs_program;
+typedef struct zkb_rs_tables {
+    const uint32_t* norm3;     /* device: (m7, exponent field, non-zero flag) per normalisation row; adds only */
+    uint32_t n_norm;
+    const int32_t* smul3;      /* device: (signed significand, carry, non-zero flag) per signed-product row; multiplies only */
+    uint32_t n_smul;
+    const int32_t* const* un2; /* host array of n_un device tables: (sm, ef) of the unary image per value-table row, 8-byte aligned */
+    uint32_t n_un, n_val;
+} zkb_rs_tables;
+typedef struct zkb_rs_mult {
+    uint32_t* m; /* device multiplicity array, zeroed by the caller */
+    uint32_t n;
+} zkb_rs_mult;
+typedef struct zkb_rs_mults {
+    zkb_rs_mult pow, norm, val, frac, smul;
+    const zkb_rs_mult* un; /* host array, one per unary table */
+} zkb_rs_mults;
+/* One residual-stream component (device original zk_witness_gen_residual_stream, stwo_cuda/cuda/
+ * zk_residual_stream_witness_gen.cu:231-470; host statement residual_stream_component,
+ * prover/src/gadgets/residual_stream/mod.rs:1418-1760). wit: live_rows x n_leaves bf16 patterns (one per word),
+ * row-flat; rows from live_rows up to 2^log_rows are evaluated on zero leaves. Writes every committed cell (cols: host
+ * array of n_cols device columns), adds every lookup to its multiplicity array, and writes in NATURAL row order
+ * out_pat (rows x out_w bf16 patterns of the reported slots), out_nat (rows x out_w pairs: significand and unclamped
+ * exponent) and in_nat (rows x n_leaves pairs); out_nat and in_nat 8-byte aligned. counts[0] += lookups that fall
+ * outside their table, counts[1] += results whose exponent leaves bf16's normal range, counts[2] += leaves whose unary
+ * image has no table row. Every column index of the program is checked against n_cols before the launch. */
+int zkb_witness_residual_stream(zkb_ctx* ctx, const zkb_rs_program* prog, const zkb_rs_tables* tables, const uint32_t* wit, uint32_t live_rows,
+                                uint32_t log_rows, uint32_t* const* cols, uint32_t n_cols, uint32_t* out_pat, int32_t* out_nat, int32_t* in_nat,
+                                const zkb_rs_mults* mults, uint32_t* counts);
+
 #ifdef __cplusplus
 }
 #endif

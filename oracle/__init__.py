@@ -525,6 +525,71 @@ def witness_dequant(acc, jx, jw, sx, sw, norm3, mul2, n_base, n_pre, cfg):
             "counts": counts, "want": want}
 
 
+# ---- witness generation: shared bf16 tables, key tile selectors, residual stream (oracle/witness_pre.hpp)
+PRE_TABLE_COLS = {0: 6, 1: 3, 2: 4, 3: 2, 4: 1}
+
+
+def witness_pre_table(kind, log_rows, kmax, round_mode, counters=(), patch_idx=(), patch_val=(), with_m=True):
+    """Returns (cols [n_cols, rows], m or None) in committed order. patch_val: n_patch x n_cols."""
+    rows, n_cols = 1 << log_rows, PRE_TABLE_COLS[kind]
+    counters = [_u32(c) for c in counters]
+    pi, pv = _u32(list(patch_idx)), _u32(np.asarray(patch_val, np.uint32).reshape(-1))
+    cols = [np.zeros(rows, np.uint32) for _ in range(n_cols)]
+    m = np.zeros(rows, np.uint32) if with_m else None
+    lib().zko_witness_pre_table(C.c_uint32(kind), C.c_uint32(log_rows), C.c_uint32(kmax), C.c_uint32(round_mode), _pp(counters),
+                                C.c_uint32(len(counters)), _p(pi), _p(pv), C.c_uint32(len(pi)), _pp(cols), _p(m) if with_m else None)
+    return np.stack(cols), m
+
+
+def key_tile_flags(shape, log_rows, groups, chunks, lead, descending, modulus, rw):
+    flags = np.zeros(1 << log_rows, np.uint32)
+    lib().zko_key_tile_flags(*(C.c_uint32(int(v)) for v in (shape, log_rows, groups, chunks, lead, descending, modulus, rw)), _p(flags))
+    return flags
+
+
+def witness_selectors(shape, log_rows, groups, chunks, lead, descending, flags, scale, ctx_len, with_scale, n_cols):
+    flags, scale = _u32(flags), _u32(scale)
+    cols = [np.zeros(1 << log_rows, np.uint32) for _ in range(n_cols)]
+    lib().zko_witness_selectors(*(C.c_uint32(int(v)) for v in (shape, log_rows, groups, chunks, lead, descending)), _p(flags), _p(scale),
+                                C.c_uint32(ctx_len), C.c_int(int(with_scale)), _pp(cols), C.c_uint32(n_cols))
+    return np.stack(cols)
+
+
+def rs_n_cols(groups, n_slots, kind, sticky):
+    g = _u32(np.asarray(groups, np.uint32).reshape(-1))
+    f = lib().zko_rs_n_cols
+    f.restype = C.c_uint32
+    return int(f(_p(g), C.c_uint32(len(groups)), C.c_uint32(n_slots), C.c_uint32(kind), C.c_uint32(int(sticky))))
+
+
+def witness_residual_stream(case):
+    """case: the dict zk_inference_prover_b200.witness_cases.residual_stream_case builds (the program in its host form under
+    "groups", "src_slots", "out_slot"). Returns dict(cols [n_cols, rows], out_pat, out_nat, in_nat, m_pow, m_norm, m_val, m_frac,
+    m_smul, m_un [n_un, n], counts [3])."""
+    groups = _u32(np.asarray(case["groups"], np.uint32).reshape(-1))
+    slots = _u32(np.asarray(case["src_slots"], np.uint32).reshape(-1))
+    out_slot = _u32(case["out_slot"])
+    n_groups, n_slots, out_w = len(case["groups"]), len(case["src_slots"]), len(case["out_slot"])
+    rows, n_leaves = 1 << case["log_rows"], sum(g[0] for g in case["groups"])
+    n_cols = rs_n_cols(case["groups"], n_slots, case["kind"], case["sticky"])
+    norm3, smul3 = _u32(case["norm3"]), np.ascontiguousarray(case["smul3"], np.int32)
+    un2 = [np.ascontiguousarray(u, np.int32) for u in case["un2"]]
+    wit = _u32(case["wit"])
+    m_len = np.asarray([case["m_len"][k] for k in ("pow", "norm", "val", "frac", "smul", "un")], np.uint64)
+    cols = [np.zeros(rows, np.uint32) for _ in range(n_cols)]
+    out_pat, out_nat = np.zeros(rows * out_w, np.uint32), np.zeros(rows * out_w * 2, np.int32)
+    in_nat = np.zeros(rows * n_leaves * 2, np.int32)
+    ms = [np.zeros(int(m_len[k]), np.uint32) for k in range(5)] + [np.zeros(int(m_len[5]), np.uint32) for _ in un2]
+    counts = np.zeros(3, np.uint32)
+    lib().zko_witness_residual_stream(_p(groups), C.c_uint32(n_groups), _p(slots), C.c_uint32(n_slots), _p(out_slot), C.c_uint32(out_w),
+                                      C.c_uint32(case["kind"]), C.c_uint32(int(case["sticky"])), C.c_uint32(case["kmax"]), _p(norm3),
+                                      C.c_uint32(len(norm3) // 3), _p(smul3), C.c_uint32(len(smul3) // 3), _pp(un2), C.c_uint32(len(un2)),
+                                      C.c_uint32(case["n_val"]), _p(wit), C.c_uint32(case["live_rows"]), C.c_uint32(case["log_rows"]),
+                                      _p(m_len), _pp(cols), _p(out_pat), _p(out_nat), _p(in_nat), _pp(ms), _p(counts))
+    return {"cols": np.stack(cols), "out_pat": out_pat, "out_nat": out_nat, "in_nat": in_nat, "m_pow": ms[0], "m_norm": ms[1], "m_val": ms[2],
+            "m_frac": ms[3], "m_smul": ms[4], "m_un": np.stack(ms[5:]) if un2 else np.zeros((0, int(m_len[5])), np.uint32), "counts": counts}
+
+
 # ---- constraint quotients of an AIR (oracle/air.hpp)
 def offset_bit_reversed_circle_domain_index(i, domain_log, eval_log, offset):
     f = lib().zko_offset_bit_reversed_circle_domain_index

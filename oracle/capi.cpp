@@ -550,6 +550,72 @@ void zko_witness_dequant(const int32_t* acc, const int32_t* jx, const int32_t* j
 
 }  // extern "C"
 
+// ---------------------------------------------------------------- witness generation: shared tables, key tile selectors, residual stream
+#include "witness_pre.hpp"
+extern "C" {
+
+// cols_out: n_cols columns of 2^log_rows words; m_out may be NULL.
+void zko_witness_pre_table(uint32_t kind, uint32_t log_rows, uint32_t kmax, uint32_t round, const uint32_t* const* counters, uint32_t n_counters,
+                           const uint32_t* patch_idx, const uint32_t* patch_val, uint32_t n_patch, uint32_t* const* cols_out, uint32_t* m_out) {
+    std::vector<const uint32_t*> cn(counters, counters + n_counters);
+    PreTableOut o = witness_pre_table(kind, log_rows, kmax, round, cn, m_out != nullptr, patch_idx, patch_val, n_patch);
+    size_t rows = (size_t)1 << log_rows;
+    for (size_t k = 0; k < o.cols.size(); k++) std::memcpy(cols_out[k], o.cols[k].data(), rows * 4);
+    if (m_out) std::memcpy(m_out, o.m.data(), rows * 4);
+}
+
+void zko_key_tile_flags(uint32_t shape, uint32_t log_rows, uint32_t groups, uint32_t chunks, uint32_t lead, uint32_t descending, uint32_t modulus,
+                        uint32_t rw, uint32_t* flags) {
+    auto f = key_tile_flags(shape, KtGrid{log_rows, groups, chunks, lead, descending}, modulus, rw);
+    std::memcpy(flags, f.data(), f.size() * 4);
+}
+
+void zko_witness_selectors(uint32_t shape, uint32_t log_rows, uint32_t groups, uint32_t chunks, uint32_t lead, uint32_t descending,
+                           const uint32_t* flags, const uint32_t* scale, uint32_t ctx_len, int with_scale, uint32_t* const* cols_out, uint32_t n_cols) {
+    size_t rows = (size_t)1 << log_rows;
+    std::vector<uint32_t> f(flags, flags + rows);
+    auto cols = witness_selectors(shape, KtGrid{log_rows, groups, chunks, lead, descending}, f, scale, ctx_len, with_scale != 0, n_cols);
+    for (uint32_t k = 0; k < n_cols; k++) std::memcpy(cols_out[k], cols[k].data(), rows * 4);
+}
+
+// groups: n_groups x (n, un). slots: n_slots x (kind, g, i, kind, g, i) with kind 0 zero, 1 leaf (g, i), 2 unary image (g, i), 3 slot g.
+// m_len: lengths of the multiplicity arrays pow, norm, val, frac, smul, un; m_out: pointers in the same order, the unary ones appended.
+uint32_t zko_rs_n_cols(const uint32_t* groups, uint32_t n_groups, uint32_t n_slots, uint32_t kind, uint32_t sticky) {
+    RsProg p;
+    for (uint32_t g = 0; g < n_groups; g++) p.groups.push_back({groups[2 * g], groups[2 * g + 1]});
+    p.kind = kind; p.sticky = sticky != 0; p.slots.resize(n_slots);
+    return (uint32_t)p.n_cols();
+}
+void zko_witness_residual_stream(const uint32_t* groups, uint32_t n_groups, const uint32_t* slots, uint32_t n_slots, const uint32_t* out_slot,
+                                 uint32_t out_w, uint32_t kind, uint32_t sticky, uint32_t kmax, const uint32_t* norm3, uint32_t n_norm,
+                                 const int32_t* smul3, uint32_t n_smul, const int32_t* const* un2, uint32_t n_un, uint32_t n_val,
+                                 const uint32_t* wit, uint32_t live_rows, uint32_t log_rows, const uint64_t* m_len, uint32_t* const* cols_out,
+                                 uint32_t* out_pat, int32_t* out_nat, int32_t* in_nat, uint32_t* const* m_out, uint32_t* counts) {
+    RsProg p;
+    for (uint32_t g = 0; g < n_groups; g++) p.groups.push_back({groups[2 * g], groups[2 * g + 1]});
+    p.kind = kind; p.sticky = sticky != 0; p.kmax = kmax;
+    for (uint32_t s = 0; s < n_slots; s++) {
+        const uint32_t* w = slots + 6 * s;
+        p.slots.push_back({RsSrc{w[0], w[1], w[2]}, RsSrc{w[3], w[4], w[5]}});
+    }
+    p.out_slot.assign(out_slot, out_slot + out_w);
+    RsTables t{norm3, n_norm, smul3, n_smul, std::vector<const int32_t*>(un2, un2 + n_un), n_val};
+    size_t ml[6];
+    for (int k = 0; k < 6; k++) ml[k] = (size_t)m_len[k];
+    RsOut o = witness_residual_stream(p, t, wit, live_rows, log_rows, ml);
+    size_t rows = (size_t)1 << log_rows;
+    for (size_t k = 0; k < o.cols.size(); k++) std::memcpy(cols_out[k], o.cols[k].data(), rows * 4);
+    std::memcpy(out_pat, o.out_pat.data(), o.out_pat.size() * 4);
+    std::memcpy(out_nat, o.out_nat.data(), o.out_nat.size() * 4);
+    std::memcpy(in_nat, o.in_nat.data(), o.in_nat.size() * 4);
+    const std::vector<uint32_t>* ms[5] = {&o.m_pow, &o.m_norm, &o.m_val, &o.m_frac, &o.m_smul};
+    for (int k = 0; k < 5; k++) std::memcpy(m_out[k], ms[k]->data(), ms[k]->size() * 4);
+    for (uint32_t u = 0; u < n_un; u++) std::memcpy(m_out[5 + u], o.m_un[u].data(), o.m_un[u].size() * 4);
+    std::memcpy(counts, o.counts, 12);
+}
+
+}  // extern "C"
+
 // ---------------------------------------------------------------- constraint quotients of an AIR
 #include "air.hpp"
 extern "C" {

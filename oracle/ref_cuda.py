@@ -481,6 +481,111 @@ class RefCudaWitness(RefCudaMore):
         return out
 
 
+class _ZkPreCfg(C.Structure):  # stwo_cuda/cuda/zk_pre_witness_gen.cuh:103-115
+    _fields_ = [(n, C.c_uint32) for n in ("kind", "log_rows", "rows", "real_rows", "kmax", "round", "sticky", "n_cols", "n_counters", "mutate", "at")]
+
+
+class _ZkAccGrid(C.Structure):  # stwo_cuda/cuda/zk_acc.cuh:88-95
+    _fields_ = [(n, C.c_uint32) for n in ("log_rows", "rows", "groups", "chunks", "lead", "descending")]
+
+
+class _ZkAccFlags(C.Structure):  # stwo_cuda/cuda/zk_acc.cuh:185-190
+    _fields_ = [("shape", C.c_uint32), ("g", _ZkAccGrid), ("modulus", C.c_uint32), ("rw", C.c_uint32)]
+
+
+class _ZkSelCfg(C.Structure):  # stwo_cuda/cuda/zk_pre_witness_gen.cuh:118-128
+    _fields_ = [("shape", C.c_uint32), ("g", _ZkAccGrid)] + [(n, C.c_uint32) for n in ("ctx", "n_insts", "with_scale", "n_cols", "fam", "mutate", "at")]
+
+
+class _ZkRsMult(C.Structure):  # stwo_cuda/cuda/zk_residual_stream_witness_gen.cuh (ZkResidualStreamMult)
+    _fields_ = [("m", C.c_void_p), ("n", C.c_uint32)]
+
+
+class _ZkRsCfg(C.Structure):  # ZkResidualStreamCfg
+    _fields_ = [(n, C.c_uint32) for n in ("log_rows", "rows", "live", "n_groups", "n_leaves", "n_slots", "n_cols", "kind", "sticky", "kmax", "out_w",
+                                          "mutate")]
+
+
+class RefCudaWitnessPre(RefCudaWitness):
+    """The reference's device witness generation for the shared tables (prover/src/devpre.rs:440-500), the key tile's flags and
+    selectors (devpre.rs:590-640) and the residual-stream component (prover/src/gadgets/residual_stream/device.rs:300-440), with
+    no defect selected (mutate = 0)."""
+
+    def __init__(self):
+        super().__init__()
+        L, vp, u32 = self.lib, C.c_void_p, C.c_uint32
+        L.zk_witness_gen_pre_table.restype = None
+        L.zk_witness_gen_pre_table.argtypes = [vp, vp, vp, u32, vp, vp, _ZkPreCfg]
+        L.zk_flags_key_tile.restype = None
+        L.zk_flags_key_tile.argtypes = [vp, _ZkAccFlags]
+        L.zk_witness_gen_sel.restype = None
+        L.zk_witness_gen_sel.argtypes = [vp, vp, vp, _ZkSelCfg]
+        L.zk_witness_gen_residual_stream.restype = None
+        L.zk_witness_gen_residual_stream.argtypes = ([vp] * 4 + [u32, vp, u32, vp, u32, u32] + [vp] * 5 + [_ZkRsMult] * 5 + [vp, vp, _ZkRsCfg])
+
+    def pre_table(self, kind, log_rows, kmax, round_mode, counters, patch_idx, patch_val):
+        rows, n_cols = 1 << log_rows, {0: 6, 1: 3, 2: 4, 3: 2, 4: 1}[kind]
+        sticky = 1 if round_mode == 0 else 0
+        real = {0: 256 + (kmax + 1) * 256 * (1 + sticky), 1: 1 << (kmax + 1), 2: 1 << 14}.get(kind, rows)
+        d_cnt = [self.upload(c) for c in counters]
+        cols, m = [self.alloc_zero(rows) for _ in range(n_cols)], self.alloc_zero(rows)
+        pi = self.upload(patch_idx) if len(patch_idx) else None
+        pv = self.upload(np.ascontiguousarray(patch_val).reshape(-1)) if len(patch_idx) else None
+        cfg = _ZkPreCfg(kind, log_rows, rows, real, kmax, round_mode, sticky, n_cols, len(counters), 0, 0)
+        self.lib.zk_witness_gen_pre_table(_ptrs(d_cnt) if d_cnt else None, pi, pv, len(patch_idx), _ptrs(cols), m if counters else None, cfg)
+        out = np.stack([self.download(c, rows) for c in cols]), self.download(m, rows)
+        for p_ in cols + [m] + d_cnt + ([pi, pv] if pi else []):
+            self.free(p_)
+        return out
+
+    def flags_and_selectors(self, shape, log_rows, groups, chunks, lead, descending, modulus, rw, scale, ctx_len, n_insts, with_scale, n_cols):
+        rows = 1 << log_rows
+        grid = _ZkAccGrid(log_rows, rows, groups, chunks, lead, descending)
+        d_flags = self.alloc_zero(rows)
+        self.lib.zk_flags_key_tile(d_flags, _ZkAccFlags(shape, grid, modulus, rw))
+        flags = self.download(d_flags, rows)
+        cols, d_scale = [self.alloc_zero(rows) for _ in range(n_cols)], self.upload(scale)
+        fam = {0: 5, 1: 6, 2: 7}[shape]  # ZK_PRE_AT_CHAN / _KEY / _ROW
+        self.lib.zk_witness_gen_sel(d_flags, _ptrs(cols), d_scale, _ZkSelCfg(shape, grid, ctx_len, n_insts, 1 if with_scale else 0, n_cols, fam, 0, 8))
+        out = flags, np.stack([self.download(c, rows) for c in cols])
+        for p_ in cols + [d_flags, d_scale]:
+            self.free(p_)
+        return out
+
+    def residual_stream(self, case):
+        rows, n_leaves, n_cols, out_w = 1 << case["log_rows"], case["n_leaves"], case["n_cols"], len(case["out_slot"])
+        ml, n_un = case["m_len"], len(case["un2"])
+        d = {k: self.upload_any(case[k]) for k in ("wit", "norm3", "smul3", "lowered_groups", "lowered_slots")}
+        d_out_slot = self.upload(np.asarray(case["out_slot"], np.uint32))
+        d_un = [self.upload_any(u) for u in case["un2"]]
+        cols = [self.alloc_zero(rows) for _ in range(n_cols)]
+        out_pat, out_nat, in_nat = self.alloc_zero(max(1, rows * out_w)), self.alloc_zero(max(1, rows * out_w * 2)), self.alloc_zero(rows * n_leaves * 2)
+        ms = {k: self.alloc_zero(ml[k]) for k in ("pow", "norm", "val", "frac", "smul")}
+        m_un = [self.alloc_zero(ml["un"]) for _ in range(n_un)]
+        un_recs = np.zeros(max(1, n_un) * 4, np.uint32)  # ZkResidualStreamMult records: pointer (8 bytes), n, padding
+        for u, p_ in enumerate(m_un):
+            un_recs[4 * u:4 * u + 2] = np.array([int(p_)], np.uint64).view(np.uint32)
+            un_recs[4 * u + 2] = ml["un"]
+        d_un_recs, counts = self.upload(un_recs), self.alloc_zero(3)
+        cfg = _ZkRsCfg(case["log_rows"], rows, case["live_rows"], len(case["groups"]), n_leaves, len(case["src_slots"]), n_cols, case["kind"],
+                       1 if case["sticky"] else 0, case["kmax"], out_w, 0)
+        mult = lambda k: _ZkRsMult(ms[k], ml[k])
+        self.lib.zk_witness_gen_residual_stream(d["wit"], d["lowered_groups"], d["lowered_slots"], d["norm3"], len(case["norm3"]) // 3, d["smul3"],
+                                                len(case["smul3"]) // 3, _ptrs(d_un) if d_un else None, n_un, case["n_val"], d_out_slot, _ptrs(cols),
+                                                out_pat, out_nat, in_nat, mult("pow"), mult("norm"), mult("val"), mult("frac"), mult("smul"),
+                                                d_un_recs, counts, cfg)
+        out = {"cols": np.stack([self.download(c, rows) for c in cols]), "out_pat": self.download(out_pat, max(1, rows * out_w))[:rows * out_w],
+               "out_nat": self.download(out_nat, max(1, rows * out_w * 2))[:rows * out_w * 2].view(np.int32),
+               "in_nat": self.download(in_nat, rows * n_leaves * 2).view(np.int32), "m_pow": self.download(ms["pow"], ml["pow"]),
+               "m_norm": self.download(ms["norm"], ml["norm"]), "m_val": self.download(ms["val"], ml["val"]),
+               "m_frac": self.download(ms["frac"], ml["frac"]), "m_smul": self.download(ms["smul"], ml["smul"]),
+               "m_un": np.stack([self.download(m_, ml["un"]) for m_ in m_un]) if m_un else np.zeros((0, ml["un"]), np.uint32),
+               "counts": self.download(counts, 3)}
+        for p_ in list(d.values()) + [d_out_slot, d_un_recs, counts, out_pat, out_nat, in_nat] + d_un + cols + list(ms.values()) + m_un:
+            self.free(p_)
+        return out
+
+
 class RefCudaAir(RefCudaOps):
     """The reference's hand-written constraint kernel for the wide Fibonacci example AIR
     (stwo_cuda/cuda/evaluate_wide_fibonacci.cu:6-63, launcher :65-125; the AIR is

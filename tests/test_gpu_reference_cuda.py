@@ -341,3 +341,70 @@ def test_witness_dequant_matches_reference_cuda(ctx, oracle, refwit, variant, to
     for k in ("counts", "m_norm", "m_frac", "m_mul", "m_r8", "pre", "base", "want"):
         assert np.array_equal(ref[k], got[k]), k
         assert np.array_equal(ref[k], want[k]), k
+
+
+@pytest.fixture(scope="module")
+def refpre():
+    from oracle import ref_cuda
+
+    if not ref_cuda.available():
+        pytest.skip("oracle/_ref/libstwo_cuda_ref.so is not built (the reference checkout is needed to build it)")
+    try:
+        return ref_cuda.RefCudaWitnessPre()
+    except AttributeError:
+        pytest.skip("oracle/_ref/libstwo_cuda_ref.so predates the shared-table and residual-stream kernels; rebuild it")
+
+
+@pytest.mark.parametrize("kind,log_rows,kmax,round_mode,n_counters,n_patch", [
+    (0, 13, 13, 0, 2, 1), (0, 12, 13, 1, 1, 0), (0, 15, 21, 0, 3, 2), (1, 14, 13, 0, 1, 0), (1, 16, 14, 1, 2, 1), (2, 14, 13, 0, 2, 0),
+    (2, 15, 13, 2, 1, 3), (3, 8, 0, 0, 1, 0), (4, 16, 0, 0, 2, 0)])
+def test_pre_tables_match_reference_cuda(ctx, oracle, refpre, kind, log_rows, kmax, round_mode, n_counters, n_patch):
+    """zk_witness_gen_pre_table (stwo_cuda/cuda/zk_pre_witness_gen.cu) against zkb_witness_pre_table and the oracle: every
+    preprocessed column of the five shared tables and their multiplicity columns."""
+    from test_witness_pre import run_pre_table
+    from witness_cases import pre_table_case
+
+    counters, pi, pv = pre_table_case(40 + 3 * kind + log_rows, kind, log_rows, n_counters, n_patch)
+    ref_cols, ref_m = refpre.pre_table(kind, log_rows, kmax, round_mode, counters, pi, pv)
+    got_cols, got_m = run_pre_table(ctx, kind, log_rows, kmax, round_mode, counters, pi, pv)
+    want_cols, want_m = oracle.witness_pre_table(kind, log_rows, kmax, round_mode, counters, pi, pv)
+    assert np.array_equal(ref_cols, got_cols) and np.array_equal(ref_cols, want_cols)
+    assert np.array_equal(ref_m, got_m) and np.array_equal(ref_m, want_m)
+
+
+def test_key_tile_selectors_match_reference_cuda(ctx, oracle, refpre):
+    """zk_flags_key_tile (zk_acc.cu) and zk_witness_gen_sel (zk_pre_witness_gen.cu) against zkb_key_tile_flags,
+    zkb_witness_selectors and the oracle, for the three sub-component shapes."""
+    from test_witness_pre import TILE_CASES
+
+    for shape, log_rows, groups, chunks, lead, desc, modulus, rw, ctx_len, n_cols, with_scale in TILE_CASES:
+        rows = 1 << log_rows
+        n_insts = (groups + ctx_len - 1) // ctx_len if shape == 1 else 0
+        scale = np.random.default_rng(log_rows).integers(1, 2**31 - 1, max(1, n_insts), dtype=np.uint32)
+        ref_flags, ref_cols = refpre.flags_and_selectors(shape, log_rows, groups, chunks, lead, desc, modulus, rw, scale, ctx_len, n_insts,
+                                                         with_scale, n_cols)
+        d_flags = ctx.alloc(rows)
+        ctx.key_tile_flags(shape, log_rows, groups, chunks, lead, desc, modulus, rw, d_flags.ptr)
+        cols = [ctx.alloc(rows) for _ in range(n_cols)]
+        ctx.witness_selectors(shape, log_rows, groups, chunks, lead, desc, d_flags.ptr, ctx.upload(scale).ptr, ctx_len, n_insts, with_scale,
+                              [c.ptr for c in cols])
+        assert np.array_equal(ref_flags, d_flags.download()), (shape, log_rows)
+        assert np.array_equal(ref_flags, oracle.key_tile_flags(shape, log_rows, groups, chunks, lead, desc, modulus, rw))
+        assert np.array_equal(ref_cols, np.stack([c.download() for c in cols])), (shape, log_rows)
+        assert np.array_equal(ref_cols, oracle.witness_selectors(shape, log_rows, groups, chunks, lead, desc, ref_flags, scale, ctx_len,
+                                                                 with_scale, n_cols))
+
+
+def test_residual_stream_matches_reference_cuda(ctx, oracle, refpre):
+    """zk_witness_gen_residual_stream (stwo_cuda/cuda/zk_residual_stream_witness_gen.cu) against zkb_witness_residual_stream and
+    the oracle: every committed cell, the natural-order outputs, every multiplicity array and the three counters."""
+    from test_witness_pre import RS_CASES, run_residual_stream
+    from witness_cases import residual_stream_case
+
+    for shape, n, log_rows, live_rows, pad, un, kind, sticky, kmax, spread in RS_CASES:
+        case = residual_stream_case(70 + n + log_rows, shape, n, log_rows, live_rows, pad=pad, un=un, kind=kind, sticky=sticky, kmax=kmax,
+                                    spread=spread)
+        ref, got, want = refpre.residual_stream(case), run_residual_stream(ctx, case), oracle.witness_residual_stream(case)
+        for k in want:
+            assert np.array_equal(ref[k], got[k]), (shape, n, log_rows, k)
+            assert np.array_equal(ref[k], want[k]), (shape, n, log_rows, k)

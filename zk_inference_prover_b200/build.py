@@ -11,7 +11,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libzkb200.so")
 
-SOURCES = ["ctx.cu", "fft.cu", "bitrev.cu", "blake2s.cu", "fri.cu", "quotients.cu", "gkr.cu", "gkr_fused.cu", "gkr_resident.cu", "gkr_batch.cu", "poly_eval.cu", "poly_bary.cu", "freivalds.cu", "witness_gen.cu", "constraints.cu", "host/prover.cpp", "host/air_compile.cpp", "host/air_jit.cpp"]
+SOURCES = ["ctx.cu", "fft.cu", "bitrev.cu", "blake2s.cu", "fri.cu", "quotients.cu", "gkr.cu", "gkr_fused.cu", "gkr_resident.cu", "gkr_batch.cu", "poly_eval.cu", "poly_bary.cu", "freivalds.cu", "witness_gen.cu", "witness_pre.cu", "constraints.cu", "host/prover.cpp", "host/air_compile.cpp", "host/air_jit.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -19,7 +19,8 @@ EXPORTED_SYMBOLS = [
     "zkb_merkle_layer", "zkb_merkle_leaves_partial", "zkb_merkle_top", "zkb_fold_line_dalpha", "zkb_fold_circle_into_line_dalpha", "zkb_channel_mix_root_draw", "zkb_fold_line_dalpha_leaves", "zkb_fold_circle_into_line_dalpha_leaves", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine", "zkb_quot_combine_rows",
     "zkb_accumulate", "zkb_lift_accumulate", "zkb_secure_powers", "zkb_gkr_eq_evals", "zkb_gkr_next_layer",
     "zkb_gkr_sum", "zkb_gkr_fix_and_sum", "zkb_mle_fix_qm31", "zkb_mle_fix_m31", "zkb_grind", "zkb_gkr_sum_noalloc", "zkb_gkr_sum_noalloc_error",
-    "zkb_freivalds_scatter", "zkb_freivalds_acc", "zkb_witness_tables", "zkb_witness_dequant",
+    "zkb_freivalds_scatter", "zkb_freivalds_acc", "zkb_witness_tables", "zkb_witness_dequant", "zkb_witness_pre_table", "zkb_key_tile_flags",
+    "zkb_witness_selectors", "zkb_witness_residual_stream",
 ]
 # Every symbol include/zkb200_prover.h declares.
 PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_stark_prove_device", "zkb_stark_prove_host", "zkb_stark_prove_multi_device", "zkb_stark_prove_multi_host", "zkb_gkr_prove_device",
@@ -42,6 +43,24 @@ DEQUANT_CFG_FIELDS = ("variant", "sticky", "kmax", "do_ref", "tokens", "n_out", 
 class DequantCfg(C.Structure):
     """zkb_dequant_cfg (f_mul[6] spelled as six fields)."""
     _fields_ = [(k, C.c_uint32) for k in DEQUANT_CFG_FIELDS]
+
+
+class RsProgram(C.Structure):  # zkb_rs_program
+    _fields_ = [("groups", C.c_void_p), ("n_groups", C.c_uint32), ("slots", C.c_void_p), ("n_slots", C.c_uint32), ("out_slot", C.c_void_p),
+                ("out_w", C.c_uint32), ("kind", C.c_uint32), ("sticky", C.c_uint32), ("kmax", C.c_uint32)]
+
+
+class RsTables(C.Structure):  # zkb_rs_tables
+    _fields_ = [("norm3", C.c_void_p), ("n_norm", C.c_uint32), ("smul3", C.c_void_p), ("n_smul", C.c_uint32), ("un2", C.c_void_p),
+                ("n_un", C.c_uint32), ("n_val", C.c_uint32)]
+
+
+class RsMult(C.Structure):  # zkb_rs_mult
+    _fields_ = [("m", C.c_void_p), ("n", C.c_uint32)]
+
+
+class RsMults(C.Structure):  # zkb_rs_mults
+    _fields_ = [("pow", RsMult), ("norm", RsMult), ("val", RsMult), ("frac", RsMult), ("smul", RsMult), ("un", C.c_void_p)]
 
 
 class PcsConfig(C.Structure):
@@ -574,6 +593,40 @@ class Context:
                                                  _ptr_array(base_ptrs), C.c_uint32(len(base_ptrs)), _ptr_array(pre_ptrs),
                                                  C.c_uint32(len(pre_ptrs)), vp(m_norm_ptr), vp(m_frac_ptr), vp(m_mul_ptr), vp(m_r8_ptr),
                                                  vp(counts_ptr), vp(want_ptr), C.byref(c)))
+
+    def witness_pre_table(self, kind, log_rows, kmax, round_mode, counter_ptrs, col_ptrs, m_ptr=0, patch_idx_ptr=0, patch_val_ptr=0, n_patch=0):
+        self._check(self.lib.zkb_witness_pre_table(self.h, C.c_uint32(kind), C.c_uint32(log_rows), C.c_uint32(kmax), C.c_uint32(round_mode),
+                                                   _ptr_array(counter_ptrs) if counter_ptrs else None, C.c_uint32(len(counter_ptrs)),
+                                                   C.c_void_p(patch_idx_ptr or None), C.c_void_p(patch_val_ptr or None), C.c_uint32(n_patch),
+                                                   _ptr_array(col_ptrs), C.c_uint32(len(col_ptrs)), C.c_void_p(m_ptr or None)))
+
+    def key_tile_flags(self, shape, log_rows, groups, chunks, lead, descending, modulus, rw, flags_ptr):
+        self._check(self.lib.zkb_key_tile_flags(self.h, *(C.c_uint32(int(v)) for v in (shape, log_rows, groups, chunks, lead, descending, modulus, rw)),
+                                                C.c_void_p(flags_ptr)))
+
+    def witness_selectors(self, shape, log_rows, groups, chunks, lead, descending, flags_ptr, scale_ptr, ctx_len, n_insts, with_scale, col_ptrs):
+        self._check(self.lib.zkb_witness_selectors(self.h, *(C.c_uint32(int(v)) for v in (shape, log_rows, groups, chunks, lead, descending)),
+                                                   C.c_void_p(flags_ptr), C.c_void_p(scale_ptr or None), C.c_uint32(ctx_len), C.c_uint32(n_insts),
+                                                   C.c_int(int(with_scale)), _ptr_array(col_ptrs), C.c_uint32(len(col_ptrs))))
+
+    def witness_residual_stream(self, groups, slots, out_slot, kind, sticky, kmax, norm3_ptr, n_norm, smul3_ptr, n_smul, un2_ptrs, n_val, wit_ptr,
+                                live_rows, log_rows, col_ptrs, out_pat_ptr, out_nat_ptr, in_nat_ptr, mults, un_mults, counts_ptr):
+        """groups [n, 5] / slots [n, 8] / out_slot: host uint32 arrays (zkb_rs_group, zkb_rs_slot records). mults: dict name -> (ptr, n)
+        over pow, norm, val, frac, smul; un_mults: list of (ptr, n)."""
+        groups = np.ascontiguousarray(groups, np.uint32).reshape(-1, 5)
+        slots = np.ascontiguousarray(slots, np.uint32).reshape(-1, 8)
+        out_slot = np.ascontiguousarray(out_slot, np.uint32)
+        prog = RsProgram(groups.ctypes.data, len(groups), slots.ctypes.data if len(slots) else None, len(slots),
+                         out_slot.ctypes.data if len(out_slot) else None, len(out_slot), int(kind), int(sticky), int(kmax))
+        un2 = _ptr_array(un2_ptrs) if un2_ptrs else None
+        tables = RsTables(norm3_ptr or None, n_norm, smul3_ptr or None, n_smul, C.cast(un2, C.c_void_p) if un2_ptrs else None, len(un2_ptrs), n_val)
+        un_arr = (RsMult * max(1, len(un_mults)))(*[RsMult(p, n) for p, n in un_mults])
+        m = RsMults(*[RsMult(mults[k][0] or None, mults[k][1]) for k in ("pow", "norm", "val", "frac", "smul")],
+                    C.cast(un_arr, C.c_void_p) if un_mults else None)
+        self._check(self.lib.zkb_witness_residual_stream(self.h, C.byref(prog), C.byref(tables), C.c_void_p(wit_ptr), C.c_uint32(live_rows),
+                                                         C.c_uint32(log_rows), _ptr_array(col_ptrs), C.c_uint32(len(col_ptrs)),
+                                                         C.c_void_p(out_pat_ptr), C.c_void_p(out_nat_ptr), C.c_void_p(in_nat_ptr), C.byref(m),
+                                                         C.c_void_p(counts_ptr)))
 
     # ---- constraint quotients of a lowered AIR (include/zkb200_air.h)
     def air_compile(self, source):
