@@ -25,8 +25,13 @@ __device__ __forceinline__ uint32_t coset_perm(uint32_t i, uint32_t log_n) {
 
 // A possibly negative integer as a field element (attn_trace::m31_of).
 __device__ __forceinline__ uint32_t m31_of(long long v) {
-    long long x = v % (long long)P;
-    return (uint32_t)(x < 0 ? x + (long long)P : x);
+    // two folds of 31 bits bring any |v| < 2^62 below 2p (2^31 = 1 mod p); no 64-bit division
+    unsigned long long u = (unsigned long long)(v < 0 ? -v : v);
+    u = (u & P) + (u >> 31);
+    u = (u & P) + (u >> 31);
+    uint32_t r = (uint32_t)u;
+    if (r >= P) r -= P;
+    return (v < 0 && r) ? P - r : r;
 }
 
 // ---------------------------------------------------------------------------------------------------

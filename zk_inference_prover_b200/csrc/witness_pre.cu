@@ -9,6 +9,7 @@
 // zk_witness_gen_sel (stwo_cuda/cuda/zk_pre_witness_gen.cu), zk_flags_key_tile (stwo_cuda/cuda/zk_acc.cu:78-97) and
 // zk_witness_gen_residual_stream (stwo_cuda/cuda/zk_residual_stream_witness_gen.cu). Their "mutate" arguments
 // (deliberate defects for negative controls) are not part of the operators and are not built.
+#include <algorithm>
 #include <cstring>
 #include <vector>
 
@@ -24,9 +25,14 @@ __device__ __forceinline__ uint32_t committed_to_natural(uint32_t i, uint32_t lo
     uint32_t c = (i & 1u) ? (((2u << log_n) - i - 1u) >> 1) : (i >> 1);
     return __brev(c) >> (32u - log_n);
 }
-__device__ __forceinline__ uint32_t field_of(long long v) {  // encoding.rs:29-32
-    long long x = v % (long long)P;
-    return (uint32_t)(x < 0 ? x + (long long)P : x);
+__device__ __forceinline__ uint32_t field_of(long long v) {  // ((v % p) + p) % p, encoding.rs:29-32
+    // two folds of 31 bits bring any |v| < 2^62 below 2p (2^31 = 1 mod p); no 64-bit division
+    unsigned long long u = (unsigned long long)(v < 0 ? -v : v);
+    u = (u & P) + (u >> 31);
+    u = (u & P) + (u >> 31);
+    uint32_t r = (uint32_t)u;
+    if (r >= P) r -= P;
+    return (v < 0 && r) ? P - r : r;
 }
 __device__ __forceinline__ long long signed_of(uint32_t v) { return v > P / 2 ? (long long)v - (long long)P : (long long)v; }
 
@@ -185,6 +191,8 @@ struct RsArgs {
     const int32_t* smul3;
     const int32_t* const* un2;
     const uint32_t* out_slot;
+    const uint32_t* order;        // slot indices sorted by level
+    const uint32_t* level_start;  // n_levels + 1 offsets into `order`
     uint32_t* const* cols;
     uint32_t* out_pat;
     int32_t* out_nat;
@@ -192,9 +200,9 @@ struct RsArgs {
     RsMult m_pow, m_norm, m_val, m_frac, m_smul;
     const RsMult* m_un;
     uint32_t* counts;
-    uint32_t n_norm, n_smul, n_val, log_rows, live, n_groups, n_leaves, n_slots, kmax, out_w;
+    uint32_t n_norm, n_smul, n_val, log_rows, live, n_groups, n_leaves, n_slots, n_levels, kmax, out_w;
 };
-constexpr uint32_t RS_DMAX = 12, RS_UMIN = 260, RS_BIAS = 134;
+constexpr uint32_t RS_DMAX = 12, RS_UMIN = 260, RS_BIAS = 134, RS_POW_ROWS = RS_DMAX + 1 + RS_UMIN;
 
 // One lookup: bump the table's multiplicity, or count the lookup as off the table. Lanes of a warp that hit the same
 // entry (a padded row's leaves all hit entry 0) are merged into one atomic.
@@ -219,28 +227,48 @@ __device__ __forceinline__ uint32_t signed_significand_index(long long v) {
     unsigned long long a = (unsigned long long)(v < 0 ? -v : v);
     return (a < 128 || a >= 256) ? OFF_TABLE : 1u + (v < 0 ? 128u : 0u) + (uint32_t)(a - 128);
 }
+// The column table is never written by the kernel: its entries are fetched through the read-only path, so that the loads
+// of a slot's fourteen column addresses are independent of the stores between them (a plain load would have to be
+// ordered after every earlier store, one address at a time).
+__device__ __forceinline__ uint32_t* column(uint32_t* const* cols, uint32_t c) {
+    return reinterpret_cast<uint32_t*>(__ldg(reinterpret_cast<const unsigned long long*>(cols) + c));
+}
 // An operand as the (significand, exponent) it encodes. A slot's output exponent is clamped to [0, 0xfe] on the way
 // out of the slot while its cell keeps the unclamped value, so the clamp applies to slot sources only.
 __device__ __forceinline__ void operand(uint32_t* const* cols, uint32_t i, uint32_t c_sm, uint32_t c_ef, bool from_slot, long long& sm, long long& ef) {
     if (c_sm == OFF_TABLE) { sm = 0; ef = 0; return; }
-    sm = signed_of(cols[c_sm][i]);
-    long long e = signed_of(cols[c_ef][i]);
+    const uint32_t *p_sm = column(cols, c_sm), *p_ef = column(cols, c_ef);
+    sm = signed_of(p_sm[i]);
+    long long e = signed_of(p_ef[i]);
     ef = e < 0 ? 0 : (from_slot && e > 0xfe) ? 0xfe : e;
 }
 
+// A CTA owns 32 consecutive committed rows: lane = row, so that every column access of a warp is one 128-byte line.
+// Its RS_LANES warps share the row's work: the leaves, then the slots level by level (a level holds the slots whose
+// operands are leaves or outputs of earlier levels; `order` lists the slots by level, `level_start` where each begins),
+// with a CTA barrier between levels, since a slot's operand may be a cell another warp of the CTA wrote.
+constexpr uint32_t RS_LANES = 8;
 template <bool MUL, bool STICKY>
-__global__ void __launch_bounds__(128) residual_stream_kernel(RsArgs a) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >> a.log_rows) return;
-    const uint32_t j = committed_to_natural(i, a.log_rows);
+__global__ void __launch_bounds__(32 * RS_LANES) residual_stream_kernel(RsArgs a) {
+    // The power table has 273 rows and every addition hits row DMAX with its larger operand: counted per CTA in shared
+    // memory and added to the global array once at the end (one hot address would serialise every warp of the grid).
+    __shared__ uint32_t pow_hist[RS_POW_ROWS];
+    if (!MUL) {
+        for (uint32_t k = threadIdx.x; k < RS_POW_ROWS; k += blockDim.x) pow_hist[k] = 0;
+        __syncthreads();
+    }
+    const uint32_t i = blockIdx.x * 32u + (threadIdx.x & 31u), t = threadIdx.x >> 5;
+    const bool in_range = (i >> a.log_rows) == 0;
+    const uint32_t j = in_range ? committed_to_natural(i, a.log_rows) : 0u;
     const bool live = j < a.live;
     uint32_t off = 0, bad_exp = 0, un_off = 0;
     uint32_t* const* cols = a.cols;
     const size_t leaf0 = (size_t)j * a.n_leaves;
 
+    if (in_range)
     for (uint32_t g = 0; g < a.n_groups; g++) {
         const RsGroup gr = a.groups[g];
-        for (uint32_t k = 0; k < gr.n; k++) {
+        for (uint32_t k = t; k < gr.n; k += RS_LANES) {
             const uint32_t pat = live ? __ldg(a.wit + leaf0 + gr.flat + k) : 0u;
             // a bf16 pattern as (sm, ef); both zeros, infinities and NaNs collapse to (0, 0)
             const uint32_t e = (pat >> 7) & 0xffu;
@@ -249,8 +277,10 @@ __global__ void __launch_bounds__(128) residual_stream_kernel(RsArgs a) {
             const long long sm = finite ? ((pat >> 15) & 1u ? -mag : mag) : 0;
             const uint32_t ef = finite ? e : 0u;
             const uint32_t b = gr.leaf_col + k * gr.width;
-            cols[b][i] = field_of(sm);
-            cols[b + 1][i] = ef;
+            uint32_t *c0 = column(cols, b), *c1 = column(cols, b + 1), *c2 = nullptr, *c3 = nullptr;
+            if (gr.un) { c2 = column(cols, b + 2); c3 = column(cols, b + 3); }
+            c0[i] = field_of(sm);
+            c1[i] = ef;
             reinterpret_cast<int2*>(a.in_nat)[leaf0 + gr.flat + k] = make_int2((int)sm, (int)ef);  // natural row order
             const uint32_t v = value_index(sm, ef);
             if (gr.un == 0) { lookup(a.m_val, v, off); continue; }
@@ -258,25 +288,32 @@ __global__ void __launch_bounds__(128) residual_stream_kernel(RsArgs a) {
             int2 img = make_int2(0, 0);  // the unary image, tabulated over the value table's rows
             if (v < a.n_val) img = __ldg(reinterpret_cast<const int2*>(a.un2[gr.un - 1]) + v);
             else un_off++;
-            cols[b + 2][i] = field_of(img.x);
-            cols[b + 3][i] = field_of(img.y);
+            c2[i] = field_of(img.x);
+            c3[i] = field_of(img.y);
         }
     }
 
-    for (uint32_t s = 0; s < a.n_slots; s++) {
-        const RsSlot sl = a.slots[s];
+    for (uint32_t level = 0; level < a.n_levels; level++) {
+      __syncthreads();
+      if (in_range)
+      for (uint32_t at = a.level_start[level] + t; at < a.level_start[level + 1]; at += RS_LANES) {
+        const RsSlot sl = a.slots[a.order[at]];
         long long a_sm, a_ef, b_sm, b_ef, c_sm, c_ef;
         operand(cols, i, sl.a_sm, sl.a_ef, sl.from_slot & 1u, a_sm, a_ef);
         operand(cols, i, sl.b_sm, sl.b_ef, sl.from_slot & 2u, b_sm, b_ef);
         const uint32_t b = sl.base;
+        constexpr uint32_t W = MUL ? 4u : (STICKY ? 14u : 13u);
+        uint32_t* cell[W];
+#pragma unroll
+        for (uint32_t k = 0; k < W; k++) cell[k] = column(cols, b + k);
         if (!MUL) {
             // align both operands to the larger exponent (a shift of up to DMAX bits is kept, a smaller operand is dropped),
             // add, normalise the magnitude to a 9-bit M2 with its round-bit weight ph, round through the table
             const long long etop = a_ef > b_ef ? a_ef : b_ef;
             const long long ua = a_ef - etop + RS_DMAX, ub = b_ef - etop + RS_DMAX;
             const uint32_t pa = pow_index(ua), pb = pow_index(ub);
-            lookup(a.m_pow, pa, off);
-            lookup(a.m_pow, pb, off);
+            if (pa < a.m_pow.n) atomicAdd(pow_hist + pa, 1u); else off++;
+            if (pb < a.m_pow.n) atomicAdd(pow_hist + pb, 1u); else off++;
             const long long fa = (pa != OFF_TABLE && ua >= 0) ? (1LL << ua) : 0, fb = (pb != OFF_TABLE && ub >= 0) ? (1LL << ub) : 0;
             const long long acc = a_sm * fa + b_sm * fb;
             const uint32_t sg = acc < 0;
@@ -302,21 +339,21 @@ __global__ void __launch_bounds__(128) residual_stream_kernel(RsArgs a) {
             c_sm = (long long)(128u * nzn + m7n) * (sg ? -1 : 1);
             c_ef = nzn == 1 ? (long long)efn + etop - RS_DMAX - RS_BIAS : 0;
             bad_exp += nzn == 1 && !(c_ef >= 1 && c_ef < 0xff);
-            cols[b][i] = field_of(fa);
-            cols[b + 1][i] = field_of(fb);
-            cols[b + 2][i] = field_of(etop);
-            cols[b + 3][i] = field_of((long long)mag);
-            cols[b + 4][i] = sg;
-            cols[b + 5][i] = m2;
-            cols[b + 6][i] = ph;
-            cols[b + 7][i] = field_of((long long)r);
-            if (STICKY) cols[b + 8][i] = st;
-            const uint32_t kk = b + (STICKY ? 9u : 8u);
-            cols[kk][i] = m7n;
-            cols[kk + 1][i] = efn;
-            cols[kk + 2][i] = nzn;
-            cols[kk + 3][i] = field_of(c_sm);
-            cols[kk + 4][i] = field_of(c_ef);
+            cell[0][i] = field_of(fa);
+            cell[1][i] = field_of(fb);
+            cell[2][i] = field_of(etop);
+            cell[3][i] = field_of((long long)mag);
+            cell[4][i] = sg;
+            cell[5][i] = m2;
+            cell[6][i] = ph;
+            cell[7][i] = field_of((long long)r);
+            if (STICKY) cell[8][i] = st;
+            constexpr uint32_t kk = STICKY ? 9u : 8u;
+            cell[kk][i] = m7n;
+            cell[kk + 1][i] = efn;
+            cell[kk + 2][i] = nzn;
+            cell[kk + 3][i] = field_of(c_sm);
+            cell[kk + 4][i] = field_of(c_ef);
         } else {
             // the signed significands' correctly rounded product and binade carry come from one table row
             const uint32_t ia = signed_significand_index(a_sm), ib = signed_significand_index(b_sm);
@@ -328,27 +365,40 @@ __global__ void __launch_bounds__(128) residual_stream_kernel(RsArgs a) {
             c_sm = prod;
             c_ef = nzc == 1 ? a_ef + b_ef + cy - 127 : 0;
             bad_exp += nzc == 1 && !(c_ef >= 1 && c_ef < 0xff);
-            cols[b][i] = field_of(c_sm);
-            cols[b + 1][i] = (uint32_t)cy;
-            cols[b + 2][i] = (uint32_t)nzc;
-            cols[b + 3][i] = field_of(c_ef);
+            cell[0][i] = field_of(c_sm);
+            cell[1][i] = (uint32_t)cy;
+            cell[2][i] = (uint32_t)nzc;
+            cell[3][i] = field_of(c_ef);
         }
         lookup(a.m_val, (c_ef >= 0 && c_ef < 0xff) ? value_index(c_sm, c_ef) : OFF_TABLE, off);  // the slot's own output is a looked-up pair too
+      }
     }
+    __syncthreads();
 
     // what the bindings and the next component read, in natural row order
-    for (uint32_t k = 0; k < a.out_w; k++) {
+    if (in_range)
+    for (uint32_t k = t; k < a.out_w; k += RS_LANES) {
         const RsSlot sl = a.slots[a.out_slot[k]];
-        const long long sm = signed_of(cols[sl.o_sm][i]), e = signed_of(cols[sl.o_ef][i]);
+        const long long sm = signed_of(column(cols, sl.o_sm)[i]), e = signed_of(column(cols, sl.o_ef)[i]);
         const uint32_t ef = (uint32_t)(e < 0 ? 0 : e > 0xfe ? 0xfe : e);
         uint32_t pat = 0;
         if (sm != 0) pat = ((sm < 0 ? 1u << 15 : 0u) | (ef << 7) | (uint32_t)((sm < 0 ? -sm : sm) - 128)) & 0xffffu;
         a.out_pat[(size_t)j * a.out_w + k] = pat;
         reinterpret_cast<int2*>(a.out_nat)[(size_t)j * a.out_w + k] = make_int2((int)sm, (int)e);
     }
-    if (off) atomicAdd(a.counts, off);
-    if (bad_exp) atomicAdd(a.counts + 1, bad_exp);
-    if (un_off) atomicAdd(a.counts + 2, un_off);
+    if (!MUL) {
+        __syncthreads();
+        for (uint32_t k = threadIdx.x; k < RS_POW_ROWS && k < a.m_pow.n; k += blockDim.x)
+            if (pow_hist[k]) atomicAdd(a.m_pow.m + k, pow_hist[k]);
+    }
+    off = __reduce_add_sync(0xffffffffu, off);
+    bad_exp = __reduce_add_sync(0xffffffffu, bad_exp);
+    un_off = __reduce_add_sync(0xffffffffu, un_off);
+    if ((threadIdx.x & 31u) == 0) {
+        if (off) atomicAdd(a.counts, off);
+        if (bad_exp) atomicAdd(a.counts + 1, bad_exp);
+        if (un_off) atomicAdd(a.counts + 2, un_off);
+    }
 }
 
 }  // namespace
@@ -484,6 +534,36 @@ int zkb_witness_residual_stream(zkb_ctx* ctx, const zkb_rs_program* prog, const 
         ZKB_CHECK_ARG(ctx, col_ok(sl.a_sm) && col_ok(sl.b_sm) && (sl.a_sm == OFF_TABLE || sl.a_ef < n_cols) && (sl.b_sm == OFF_TABLE || sl.b_ef < n_cols));
     }
     for (uint32_t k = 0; k < p.out_w; k++) ZKB_CHECK_ARG(ctx, p.out_slot[k] < p.n_slots);
+    // Levels: a slot that reads a cell of another slot comes one level after it, and that slot must come earlier in
+    // evaluation order (an operand inside a later slot's cells would be read before it is written).
+    std::vector<uint32_t> level(p.n_slots, 0), owner(n_cols, OFF_TABLE);
+    for (uint32_t s = 0; s < p.n_slots; s++)
+        for (uint32_t c = 0; c < slot_w; c++) {
+            ZKB_CHECK_ARG(ctx, owner[p.slots[s].base + c] == OFF_TABLE);  // two slots' cells overlap
+            owner[p.slots[s].base + c] = s;
+        }
+    for (uint32_t g = 0; g < p.n_groups; g++)
+        for (uint64_t c = p.groups[g].leaf_col; c < (uint64_t)p.groups[g].leaf_col + (uint64_t)p.groups[g].n * p.groups[g].width; c++)
+            ZKB_CHECK_ARG(ctx, owner[c] == OFF_TABLE);  // a leaf inside a slot's cells
+    uint32_t n_levels = 0;
+    for (uint32_t s = 0; s < p.n_slots; s++) {
+        const zkb_rs_slot& sl = p.slots[s];
+        ZKB_CHECK_ARG(ctx, owner[sl.o_sm] == s && owner[sl.o_ef] == s);
+        const uint32_t ops[4] = {sl.a_sm, sl.a_ef, sl.b_sm, sl.b_ef};
+        for (int o = 0; o < 4; o++) {
+            if (ops[o & 2] == OFF_TABLE || owner[ops[o]] == OFF_TABLE) continue;
+            ZKB_CHECK_ARG(ctx, owner[ops[o]] < s);
+            level[s] = std::max(level[s], level[owner[ops[o]]] + 1u);
+        }
+        n_levels = std::max(n_levels, level[s] + 1u);
+    }
+    std::vector<uint32_t> order, level_start(n_levels + 1, 0);
+    for (uint32_t l = 0; l < n_levels; l++) {
+        level_start[l] = (uint32_t)order.size();
+        for (uint32_t s = 0; s < p.n_slots; s++)
+            if (level[s] == l) order.push_back(s);
+    }
+    level_start[n_levels] = (uint32_t)order.size();
     for (uint32_t u = 0; u < tables->n_un; u++) ZKB_CHECK_ARG(ctx, tables->un2[u] && ((uintptr_t)tables->un2[u] & 7) == 0 && mults->un[u].m);
     for (uint32_t k = 0; k < n_cols; k++) ZKB_CHECK_ARG(ctx, cols[k] != nullptr);
     DeviceGuard g(ctx);
@@ -495,6 +575,8 @@ int zkb_witness_residual_stream(zkb_ctx* ctx, const zkb_rs_program* prog, const 
     if ((rc = stage_array(ctx, reinterpret_cast<const RsGroup*>(p.groups), p.n_groups, &a.groups))) return rc;
     if ((rc = stage_array(ctx, reinterpret_cast<const RsSlot*>(p.slots), p.n_slots, &a.slots))) return rc;
     if ((rc = stage_array(ctx, p.out_slot, p.out_w, &a.out_slot))) return rc;
+    if ((rc = stage_array(ctx, order.data(), order.size(), &a.order))) return rc;
+    if ((rc = stage_array(ctx, level_start.data(), level_start.size(), &a.level_start))) return rc;
     if ((rc = stage_array(ctx, tables->un2, tables->n_un, &a.un2))) return rc;
     if ((rc = stage_array(ctx, reinterpret_cast<const RsMult*>(mults->un), tables->n_un, &a.m_un))) return rc;
     a.wit = wit; a.norm3 = tables->norm3; a.smul3 = tables->smul3; a.cols = (uint32_t* const*)d_cols;
@@ -503,12 +585,12 @@ int zkb_witness_residual_stream(zkb_ctx* ctx, const zkb_rs_program* prog, const 
     a.m_pow = mult(mults->pow); a.m_norm = mult(mults->norm); a.m_val = mult(mults->val); a.m_frac = mult(mults->frac); a.m_smul = mult(mults->smul);
     a.n_norm = tables->norm3 ? tables->n_norm : 0; a.n_smul = tables->smul3 ? tables->n_smul : 0; a.n_val = tables->n_val;
     a.log_rows = log_rows; a.live = live_rows; a.n_groups = p.n_groups; a.n_leaves = (uint32_t)n_leaves; a.n_slots = p.n_slots;
-    a.kmax = p.kmax; a.out_w = p.out_w;
-    const uint32_t rows = 1u << log_rows, grid = (rows + 127) / 128;
+    a.kmax = p.kmax; a.out_w = p.out_w; a.n_levels = n_levels;
+    const uint32_t rows = 1u << log_rows, grid = (rows + 31) / 32, threads = 32 * RS_LANES;
     ProfScope prof(ctx, "residual_stream_kernel");
-    if (p.kind == 1) residual_stream_kernel<true, false><<<grid, 128, 0, ctx->stream>>>(a);
-    else if (p.sticky) residual_stream_kernel<false, true><<<grid, 128, 0, ctx->stream>>>(a);
-    else residual_stream_kernel<false, false><<<grid, 128, 0, ctx->stream>>>(a);
+    if (p.kind == 1) residual_stream_kernel<true, false><<<grid, threads, 0, ctx->stream>>>(a);
+    else if (p.sticky) residual_stream_kernel<false, true><<<grid, threads, 0, ctx->stream>>>(a);
+    else residual_stream_kernel<false, false><<<grid, threads, 0, ctx->stream>>>(a);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }
