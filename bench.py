@@ -351,7 +351,7 @@ def run_ours(args, rank, world, local_rank):
     kernels = ctx.profile_end()
     # operators of the workload that the proof does not time on their own: bit reversal of extended columns,
     # the first circle fold and the first line fold (algorithmic bytes: 8n, 34n, 26n for n source elements)
-    standalone = {}
+    standalone, copy_ceiling = {}, {}
     if rank == 0:
         nb = min(ncols, 32)
         cols_b = [ctx.alloc(N) for _ in range(nb)]
@@ -371,6 +371,20 @@ def run_ours(args, rank, world, local_rank):
         standalone = {"bit_reverse": 8.0 * N * nb / (ctx.event_elapsed_ms(2, 3) * 1e-3) / 1e9,
                       "fold_circle_into_line": 34.0 * N / (ctx.event_elapsed_ms(3, 4) * 1e-3) / 1e9,
                       "fold_line": 26.0 * (N // 2) / (ctx.event_elapsed_ms(4, 5) * 1e-3) / 1e9}
+        # The same numbers of bytes moved by the driver's own device-to-device copy, one launch each as above: at these sizes
+        # (a launch of 14-40 us) a launch's fixed cost shows, and this is what a plain copy makes of it.
+        copy_ceiling = {}
+        for name, nbytes, launches in (("bit_reverse", 8 * N, nb), ("fold_circle_into_line", 34 * N, 1), ("fold_line", 13 * N, 1)):
+            cw = nbytes // 8 // 4 * 4  # a copy of cw words moves 8 cw bytes
+            src_c, dst_c = ctx.alloc(cw), ctx.alloc(cw)
+            for rep in range(2):
+                ctx.event_record(2)
+                for _ in range(launches):
+                    ctx.d2d(dst_c.ptr, src_c.ptr, cw * 4)
+                ctx.event_record(3)
+            ctx.sync()
+            copy_ceiling[name] = 8.0 * cw * launches / (ctx.event_elapsed_ms(2, 3) * 1e-3) / 1e9
+            del src_c, dst_c
         del cols_b, sec, half, quarter
     e2e_ms, words_e2e = timed(True, False)
     assert len(words_dev) == len(words_e2e) and (words_dev == words_e2e).all(), "resident and end-to-end legs disagree"
@@ -425,6 +439,7 @@ def run_ours(args, rank, world, local_rank):
                         "quot_numerators": ab["quot_numerators"] / (kernels.get("quot_numerators_kernel", (1e9, 1))[0] * 1e-3) / 1e9,
                         **standalone}}
         roofline["per_operator_frac_of_hbm_peak"] = {k: v / peak for k, v in roofline["per_operator_gbs"].items()}
+        roofline["same_bytes_by_device_copy_gbs"] = copy_ceiling  # one cudaMemcpyAsync D2D per launch, same byte counts
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             sample_cols = ncols if args.ref_cols <= 0 else min(ncols, args.ref_cols)
@@ -703,14 +718,19 @@ def run_freivalds(args, rank):
     m_r8, off = ctx.alloc(256).zero(), ctx.alloc(2).zero()
     s, rv = qm31_array(1, 1)[0], qm31_array(2, 1)[0]
     t_sc, t_acc = [], []
-    for it in range(args.warmup + args.steps):
+    kernels = {}
+    for it in range(args.warmup + args.steps + 1):
+        if it == args.warmup + args.steps:
+            ctx.profile_begin()  # one more, untimed pass with the library's own per-kernel events
         ctx.event_record(0)
         ctx.freivalds_scatter(d_qx.ptr, [w.ptr for w in d_qw], [n_out] * n_mats, grid, pq, pk, n_in, tokens, [b.ptr for b in base],
                               [p.ptr for p in pre], m_r8.ptr, 256, off.ptr)
         ctx.event_record(1)
         ctx.freivalds_acc([b.ptr for b in base], [p.ptr for p in pre[:n_mats * pk]], grid, pq, pk, n_mats, s, rv, [o.ptr for o in out])
         ctx.event_record(2)
-        if it >= args.warmup:
+        if it == args.warmup + args.steps:
+            kernels = {k: round(v[0], 4) for k, v in ctx.profile_end().items()}
+        elif it >= args.warmup:
             t_sc.append(ctx.event_elapsed_ms(0, 1))
             t_acc.append(ctx.event_elapsed_ms(1, 2))
     cells = (pq + n_mats * pk + 4) * R
@@ -748,7 +768,7 @@ def run_freivalds(args, rank):
                       "config": {"workload": "freivalds_nin4096_nout4096_tokens32_chunks256_2mats", "rows": R, "pq": pq, "pk": pk},
                       "scatter_ms": sc, "scatter_gbs": (cells * 4 + n_mats * n_in * n_out) / (sc * 1e-3) / 1e9,
                       "acc_ms": ac, "acc_gbs": (4.0 * (pq + n_mats * pk) * R + 16.0 * (1 + 2 * n_mats) * R) / (ac * 1e-3) / 1e9,
-                      "gpu_baseline": gpu_ref}))
+                      "kernels_ms": kernels, "gpu_baseline": gpu_ref}))
     ctx.close()
 
 

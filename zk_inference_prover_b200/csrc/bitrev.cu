@@ -49,11 +49,54 @@ __global__ void __launch_bounds__(256) bit_reverse_tiled_kernel(T* __restrict__ 
     }
 }
 
+// 32-bit words, 2^12 elements and up: 64 x 64-word blocks, so that a block row is a 256-byte run, moved with 16-byte
+// accesses. Rows are padded to 66 words: the transposed reads of a warp (sixteen rows two words apart, two adjacent
+// columns) then fall into 32 different banks.
+constexpr int TB6 = 6;
+__device__ __forceinline__ uint32_t rev6(uint32_t x) { return __brev(x) >> 26; }
+__global__ void __launch_bounds__(256) bit_reverse_tiled64_kernel(uint32_t* __restrict__ v, int log_n) {
+    __shared__ uint32_t sa[64][66];
+    __shared__ uint32_t sb[64][66];
+    const int mid_bits = log_n - 2 * TB6;
+    const uint32_t mid = blockIdx.x;
+    const uint32_t rmid = mid_bits ? (__brev(mid) >> (32 - mid_bits)) : 0u;
+    if (rmid < mid) return;  // the partner block does this pair
+    const int shift_hi = TB6 + mid_bits;
+    const bool two = rmid != mid;
+    // load: a thread brings four consecutive words of a row
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+        const uint32_t idx = threadIdx.x + 256u * r, hi = idx >> 4, q = idx & 15u;
+        const uint4 x = *reinterpret_cast<const uint4*>(v + (((size_t)hi << shift_hi) | (mid << TB6) | (4u * q)));
+        *reinterpret_cast<uint2*>(&sa[hi][4 * q]) = make_uint2(x.x, x.y);
+        *reinterpret_cast<uint2*>(&sa[hi][4 * q + 2]) = make_uint2(x.z, x.w);
+        if (two) {
+            const uint4 y = *reinterpret_cast<const uint4*>(v + (((size_t)hi << shift_hi) | (rmid << TB6) | (4u * q)));
+            *reinterpret_cast<uint2*>(&sb[hi][4 * q]) = make_uint2(y.x, y.y);
+            *reinterpret_cast<uint2*>(&sb[hi][4 * q + 2]) = make_uint2(y.z, y.w);
+        }
+    }
+    __syncthreads();
+    // store: v[hi' : rmid : lo'] = old v[rev lo' : mid : rev hi'] = sa[rev lo'][rev hi']; the two half-warps take rows hi'
+    // and hi' + 32, whose reversed indices are adjacent columns
+    const uint32_t lane = threadIdx.x & 31u, w = threadIdx.x >> 5, q = lane & 15u;
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+        const uint32_t hi = w + 8u * r + 32u * (lane >> 4), col = rev6(hi);
+        const uint32_t r0 = rev6(4 * q), r1 = r0 | 32u, r2 = r0 | 16u, r3 = r0 | 48u;  // rev6(4q + k) for k = 0..3
+        *reinterpret_cast<uint4*>(v + (((size_t)hi << shift_hi) | (rmid << TB6) | (4u * q))) = make_uint4(sa[r0][col], sa[r1][col], sa[r2][col], sa[r3][col]);
+        if (two)
+            *reinterpret_cast<uint4*>(v + (((size_t)hi << shift_hi) | (mid << TB6) | (4u * q))) = make_uint4(sb[r0][col], sb[r1][col], sb[r2][col], sb[r3][col]);
+    }
+}
+
 template <typename T>
 static int bit_reverse_impl(zkb_ctx* ctx, T* col, int log_n) {
     if (log_n < 2 * TB) {
         unsigned n = 1u << log_n;
         bit_reverse_small_kernel<T><<<(n + 255) / 256, 256, 0, ctx->stream>>>(col, log_n);
+    } else if (sizeof(T) == 4 && log_n >= 2 * TB6 && ((uintptr_t)col & 15) == 0) {
+        bit_reverse_tiled64_kernel<<<1u << (log_n - 2 * TB6), 256, 0, ctx->stream>>>(reinterpret_cast<uint32_t*>(col), log_n);
     } else {
         bit_reverse_tiled_kernel<T><<<1u << (log_n - 2 * TB), 256, 0, ctx->stream>>>(col, log_n);
     }

@@ -132,6 +132,100 @@ __global__ void __launch_bounds__(128) freivalds_group_scan_kernel(uint4* __rest
     }
 }
 
+// The same recurrence with one WARP per group (groups of at most 256 rows): lane l takes rows 8l .. 8l+7, runs them from a
+// zero carry into registers, the lanes' (multiplier, value) pairs are combined by a shuffle scan of affine maps
+// ((A2, B2) o (A1, B1) = (A1 A2, B1 A2 + B2)), and each lane then adds its carry times the running power of the step. All
+// lanes of the group go through the same warp one after the other, so that the product u_m v of the group's last row
+// (what the prefix over groups sums) is at hand and is written to prod[m][slot]. One thread per (group, lane) walking 256
+// rows in sequence kept 6% of the warp slots busy and took as long as the pass over all the input columns.
+struct ScanSteps {
+    qm31 pw[2][9];  // pw[kind][k] = step^k for k = 0..8; kind 0 is lane 0 (v, step s^pq), kind 1 the lanes u_m (step rv^pk)
+};
+__global__ void __launch_bounds__(256) freivalds_group_scan_warp_kernel(uint4* __restrict__ lanes, FGrid g, uint32_t n_mats, ScanSteps st,
+                                                                        uint4* __restrict__ prod) {
+    const uint32_t slot = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
+    if (slot >= g.groups) return;
+    const uint32_t r0 = lane * 8u, n_here = r0 >= g.chunks ? 0u : (g.chunks - r0 < 8u ? g.chunks - r0 : 8u);
+    qm31 v_last = qm31_zero();
+    for (uint32_t l = 0; l <= n_mats; l++) {
+        const qm31* pw = st.pw[l ? 1 : 0];
+        const qm31 step = pw[1];
+        uint4* __restrict__ p = lanes + ((size_t)l << g.log_rows) + g.lead + (size_t)slot * g.chunks + r0;
+        qm31 y[8];
+        qm31 acc = qm31_zero();
+#pragma unroll
+        for (uint32_t k = 0; k < 8; k++)
+            if (k < n_here) {
+                acc = qm31_add(qm31_mul(acc, step), q_of(p[k]));
+                y[k] = acc;
+            }
+        const qm31 mult = pw[n_here];  // this lane's map: x -> mult x + acc
+        // inclusive scan of the maps over the lanes
+        qm31 A = mult, B = acc;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            qm31 a1, b1;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                a1.c[c] = __shfl_up_sync(0xffffffffu, A.c[c], off);
+                b1.c[c] = __shfl_up_sync(0xffffffffu, B.c[c], off);
+            }
+            if ((int)lane >= off) {
+                B = qm31_add(qm31_mul(b1, A), B);
+                A = qm31_mul(a1, A);
+            }
+        }
+        // carry into this lane = the value at the end of the previous lane
+        qm31 carry;
+#pragma unroll
+        for (int c = 0; c < 4; c++) carry.c[c] = __shfl_up_sync(0xffffffffu, B.c[c], 1);
+        if (lane == 0) carry = qm31_zero();
+#pragma unroll
+        for (uint32_t k = 0; k < 8; k++)
+            if (k < n_here) p[k] = u_of(qm31_add(y[k], qm31_mul(carry, pw[k + 1])));
+        // the group's last row is in the last lane that has rows; B of lane 31 is the value there either way
+        qm31 end;
+#pragma unroll
+        for (int c = 0; c < 4; c++) end.c[c] = __shfl_sync(0xffffffffu, B.c[c], 31);
+        if (l == 0) v_last = end;
+        else if (lane == 0) prod[(size_t)(l - 1) * g.groups + slot] = u_of(qm31_mul(end, v_last));
+    }
+}
+
+// prefix[m][slot] = sum over slots <= slot of prod[m][slot]; one CTA, coalesced reads.
+__global__ void __launch_bounds__(1024) freivalds_prefix_prod_kernel(const uint4* __restrict__ prod, uint32_t groups, uint32_t n_mats,
+                                                                     uint4* __restrict__ prefix) {
+    __shared__ uint32_t warp_tot[32][4];
+    __shared__ uint32_t carry_s[4];
+    const int lane_id = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint32_t m = 0; m < n_mats; m++) {
+        if (threadIdx.x < 4) carry_s[threadIdx.x] = 0;
+        __syncthreads();
+        for (uint32_t base = 0; base < groups; base += blockDim.x) {
+            const uint32_t slot = base + threadIdx.x;
+            qm31 x = slot < groups ? q_of(prod[(size_t)m * groups + slot]) : qm31_zero();
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                qm31 o;
+#pragma unroll
+                for (int k = 0; k < 4; k++) o.c[k] = __shfl_up_sync(0xffffffffu, x.c[k], off);
+                if (lane_id >= off) x = qm31_add(x, o);
+            }
+            if (lane_id == 31)
+                for (int k = 0; k < 4; k++) warp_tot[warp][k] = x.c[k];
+            __syncthreads();
+            qm31 pre{{carry_s[0], carry_s[1], carry_s[2], carry_s[3]}};
+            for (int w = 0; w < warp; w++) pre = qm31_add(pre, qm31{{warp_tot[w][0], warp_tot[w][1], warp_tot[w][2], warp_tot[w][3]}});
+            x = qm31_add(x, pre);
+            if (slot < groups) prefix[(size_t)m * groups + slot] = u_of(x);
+            __syncthreads();
+            if (threadIdx.x == blockDim.x - 1)
+                for (int k = 0; k < 4; k++) carry_s[k] = x.c[k];
+            __syncthreads();
+        }
+    }
+}
+
 // One CTA: prefix[m][slot] = sum over slots <= slot of u_m[last row] * v[last row].
 __global__ void __launch_bounds__(1024) freivalds_prefix_kernel(const uint4* __restrict__ lanes, FGrid g, uint32_t n_mats,
                                                                 uint4* __restrict__ prefix) {
@@ -261,11 +355,17 @@ int zkb_freivalds_acc(zkb_ctx* ctx, const uint32_t* const* base_cols, const uint
     cur = qm31_one();
     for (uint32_t p = 0; p < pk; p++) { pows.push_back(cur); cur = qm31_mul(cur, rv); }
     qm31 rv_step = cur;
-    uint4* d_pows = reinterpret_cast<uint4*>(ctx->scratch);
-    ZKB_CUDA(ctx, cudaMemcpyAsync(d_pows, pows.data(), pows.size() * 16, cudaMemcpyHostToDevice, ctx->stream));
-    ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // `pows` is pageable and leaves scope
-    void **d_base, **d_pre, **d_out;
-    int rc = stage_ptrs(ctx, (const void* const*)base_cols, (int)pq, &d_base);
+    // the powers go up through the pinned staging ring (two 8-byte slots each): no synchronisation with the work before
+    void **d_base, **d_pre, **d_out, **d_pw;
+    int rc = ZKB_OK;
+    if (ctx->ring_pos & 1) {  // the ring hands out 8-byte slots; the kernels read the powers as 16-byte words
+        const void* pad = nullptr;
+        if ((rc = stage_ptrs(ctx, &pad, 1, &d_pw))) return rc;
+    }
+    if ((rc = stage_ptrs(ctx, reinterpret_cast<const void* const*>(pows.data()), (int)(pows.size() * 2), &d_pw))) return rc;
+    if ((uintptr_t)d_pw & 15) return set_error(ctx, ZKB_ECUDA, "zkb_freivalds_acc: staging ring misaligned");
+    uint4* d_pows = reinterpret_cast<uint4*>(d_pw);
+    rc = stage_ptrs(ctx, (const void* const*)base_cols, (int)pq, &d_base);
     if (rc) return rc;
     rc = stage_ptrs(ctx, (const void* const*)pre_cols, (int)(n_mats * pk), &d_pre);
     if (rc) return rc;
@@ -282,14 +382,39 @@ int zkb_freivalds_acc(zkb_ctx* ctx, const uint32_t* const* base_cols, const uint
         freivalds_inner_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, ctx->stream>>>(
             (const uint32_t* const*)d_base, (const uint32_t* const*)d_pre, d_pows, d_pows + pq, fg, pq, pk, n_mats, lanes);
     }
-    {
-        ProfScope prof(ctx, "freivalds_group_scan_kernel");
-        unsigned threads_total = grid->groups * n_lanes;
-        freivalds_group_scan_kernel<<<(threads_total + 127) / 128, 128, 0, ctx->stream>>>(lanes, fg, n_lanes, s_step, rv_step);
-    }
-    {
-        ProfScope prof(ctx, "freivalds_prefix_kernel");
-        freivalds_prefix_kernel<<<1, 1024, 0, ctx->stream>>>(lanes, fg, n_mats, prefix);
+    if (grid->chunks <= 256) {
+        ScanSteps scan_steps;
+        for (int kind = 0; kind < 2; kind++) {
+            scan_steps.pw[kind][0] = qm31_one();
+            for (int k = 1; k <= 8; k++) scan_steps.pw[kind][k] = qm31_mul(scan_steps.pw[kind][k - 1], kind ? rv_step : s_step);
+        }
+        uint4* prod = nullptr;  // u_m v at each group's last row
+        e = cudaMallocAsync((void**)&prod, (size_t)n_mats * grid->groups * 16, ctx->stream);
+        if (e != cudaSuccess) {
+            cudaFreeAsync(lanes, ctx->stream);
+            cudaFreeAsync(prefix, ctx->stream);
+            return set_error(ctx, ZKB_ENOMEM, "zkb_freivalds_acc: %s", cudaGetErrorString(e));
+        }
+        {
+            ProfScope prof(ctx, "freivalds_group_scan_kernel");
+            freivalds_group_scan_warp_kernel<<<(unsigned)(((size_t)grid->groups * 32 + 255) / 256), 256, 0, ctx->stream>>>(
+                lanes, fg, n_mats, scan_steps, prod);
+        }
+        {
+            ProfScope prof(ctx, "freivalds_prefix_kernel");
+            freivalds_prefix_prod_kernel<<<1, 1024, 0, ctx->stream>>>(prod, grid->groups, n_mats, prefix);
+        }
+        cudaFreeAsync(prod, ctx->stream);
+    } else {
+        {
+            ProfScope prof(ctx, "freivalds_group_scan_kernel");
+            unsigned threads_total = grid->groups * n_lanes;
+            freivalds_group_scan_kernel<<<(threads_total + 127) / 128, 128, 0, ctx->stream>>>(lanes, fg, n_lanes, s_step, rv_step);
+        }
+        {
+            ProfScope prof(ctx, "freivalds_prefix_kernel");
+            freivalds_prefix_kernel<<<1, 1024, 0, ctx->stream>>>(lanes, fg, n_mats, prefix);
+        }
     }
     {
         ProfScope prof(ctx, "freivalds_split_kernel");

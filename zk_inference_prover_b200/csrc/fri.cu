@@ -94,6 +94,59 @@ __global__ void __launch_bounds__(256) fold_line_kernel2(Secure4 out, Secure4C i
     if (leaves) { store_leaf(leaves, 2 * i2, r0); store_leaf(leaves, 2 * i2 + 1, r1); }
 }
 
+// Four output elements per thread (the variant without leaf hashing): eight 16-byte loads in flight per thread and one
+// 16-byte store per coordinate column. A fold moves 26 (line) or 34 (circle) bytes per output pair and does about 60
+// instructions for them; what limits it is the number of bytes each thread keeps in flight.
+__device__ __forceinline__ void fold_quad(const Secure4C& in, size_t i4, const uint32_t t[4], qm31 alpha, qm31 r[4]) {
+    qm31 a[4], b[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const uint4 v = reinterpret_cast<const uint4*>(in.c[k])[2 * i4], w = reinterpret_cast<const uint4*>(in.c[k])[2 * i4 + 1];
+        a[0].c[k] = v.x; b[0].c[k] = v.y; a[1].c[k] = v.z; b[1].c[k] = v.w;
+        a[2].c[k] = w.x; b[2].c[k] = w.y; a[3].c[k] = w.z; b[3].c[k] = w.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; e++) r[e] = qm31_add(qm31_add(a[e], b[e]), qm31_mul(alpha, qm31_mul_m31(qm31_sub(a[e], b[e]), t[e])));
+}
+
+__global__ void __launch_bounds__(256) fold_line_kernel4(Secure4 out, Secure4C in, int log_n, qm31 alpha,
+                                                         const uint32_t* __restrict__ d_alpha, const uint32_t* __restrict__ itw) {
+    alpha = load_alpha(d_alpha, alpha);
+    const size_t half = (size_t)1 << (log_n - 1);
+    const size_t i4 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (4 * i4 >= half) return;
+    const uint4 tw = reinterpret_cast<const uint4*>(itw + half)[i4];
+    const uint32_t t[4] = {tw.x, tw.y, tw.z, tw.w};
+    qm31 r[4];
+    fold_quad(in, i4, t, alpha, r);
+#pragma unroll
+    for (int k = 0; k < 4; k++) reinterpret_cast<uint4*>(out.c[k])[i4] = make_uint4(r[0].c[k], r[1].c[k], r[2].c[k], r[3].c[k]);
+}
+
+__global__ void __launch_bounds__(256) fold_circle_kernel4(Secure4 dst, Secure4C src, int log_n_src, qm31 alpha,
+                                                           const uint32_t* __restrict__ d_alpha, const uint32_t* __restrict__ itw) {
+    alpha = load_alpha(d_alpha, alpha);
+    const qm31 alpha_sq = qm31_sqr(alpha);
+    const size_t half = (size_t)1 << (log_n_src - 1);
+    const size_t i4 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (4 * i4 >= half) return;
+    uint32_t ix, t[4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) half_coset_point(itw, log_n_src, (uint32_t)(4 * i4 + e), ix, t[e]);
+    qm31 f[4];
+    fold_quad(src, i4, t, alpha, f);
+    uint4 d[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) d[k] = reinterpret_cast<const uint4*>(dst.c[k])[i4];
+#pragma unroll
+    for (int e = 0; e < 4; e++) {
+        const qm31 de{{(&d[0].x)[e], (&d[1].x)[e], (&d[2].x)[e], (&d[3].x)[e]}};
+        f[e] = qm31_add(qm31_mul(de, alpha_sq), f[e]);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; k++) reinterpret_cast<uint4*>(dst.c[k])[i4] = make_uint4(f[0].c[k], f[1].c[k], f[2].c[k], f[3].c[k]);
+}
+
 __global__ void __launch_bounds__(256) fold_circle_kernel2(Secure4 dst, Secure4C src, int log_n_src, qm31 alpha,
                                                            const uint32_t* __restrict__ d_alpha, const uint32_t* __restrict__ itw,
                                                            uint32_t* __restrict__ leaves) {
@@ -193,7 +246,11 @@ static int fold_line_impl(zkb_ctx* ctx, uint32_t* const out[4], const uint32_t* 
     bool wide = log_n >= 3;
     for (int k = 0; k < 4; k++) wide = wide && ((uintptr_t)in[k] & 15) == 0 && ((uintptr_t)out[k] & 7) == 0;
     ProfScope prof(ctx, "fold_line_kernel");
-    if (wide)
+    bool quad = wide && log_n >= 4 && !leaves;
+    for (int k = 0; k < 4; k++) quad = quad && ((uintptr_t)out[k] & 15) == 0;
+    if (quad)
+        fold_line_kernel4<<<(unsigned)((half / 4 + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n, alpha, d_alpha, ctx->itw);
+    else if (wide)
         fold_line_kernel2<<<(unsigned)((half / 2 + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n, alpha, d_alpha, ctx->itw, leaves);
     else
         fold_line_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n, alpha, d_alpha, ctx->itw, leaves);
@@ -234,7 +291,11 @@ static int fold_circle_impl(zkb_ctx* ctx, uint32_t* const dst[4], const uint32_t
     bool wide = log_n_src >= 4;
     for (int k = 0; k < 4; k++) wide = wide && ((uintptr_t)src[k] & 15) == 0 && ((uintptr_t)dst[k] & 7) == 0;
     ProfScope prof(ctx, "fold_circle_kernel");
-    if (wide)
+    bool quad = wide && log_n_src >= 5 && !leaves;
+    for (int k = 0; k < 4; k++) quad = quad && ((uintptr_t)dst[k] & 15) == 0;
+    if (quad)
+        fold_circle_kernel4<<<(unsigned)((half / 4 + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n_src, alpha, d_alpha, ctx->itw);
+    else if (wide)
         fold_circle_kernel2<<<(unsigned)((half / 2 + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n_src, alpha, d_alpha, ctx->itw, leaves);
     else
         fold_circle_kernel<<<(unsigned)((half + 255) / 256), 256, 0, ctx->stream>>>(o, s, log_n_src, alpha, d_alpha, ctx->itw, leaves);
