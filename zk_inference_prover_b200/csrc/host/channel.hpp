@@ -30,10 +30,14 @@ class Blake2sState {
         }
     }
     void update_words(const uint32_t* w, size_t n) {
+#if defined(__BYTE_ORDER__) && __BYTE_ORDER__ == __ORDER_LITTLE_ENDIAN__
+        update(reinterpret_cast<const uint8_t*>(w), 4 * n);  // the words' memory is their little-endian serialisation
+#else
         for (size_t i = 0; i < n; i++) {
             uint8_t b[4] = {(uint8_t)w[i], (uint8_t)(w[i] >> 8), (uint8_t)(w[i] >> 16), (uint8_t)(w[i] >> 24)};
             update(b, 4);
         }
+#endif
     }
     // Digest with every word taken mod 2^31-1 (the M31 variant of the hasher).
     HashWords finalize_m31() {
@@ -58,8 +62,12 @@ class Blake2sState {
             {12, 5, 1, 15, 14, 13, 4, 10, 0, 7, 6, 3, 9, 2, 8, 11}, {13, 11, 7, 14, 12, 1, 3, 9, 5, 0, 15, 4, 8, 6, 2, 10},
             {6, 15, 14, 9, 11, 3, 0, 8, 12, 2, 13, 7, 1, 4, 10, 5}, {10, 2, 8, 4, 7, 6, 1, 5, 15, 11, 9, 14, 3, 12, 13, 0}};
         uint32_t m[16], v[16];
+#if defined(__BYTE_ORDER__) && __BYTE_ORDER__ == __ORDER_LITTLE_ENDIAN__
+        memcpy(m, buf_, 64);
+#else
         for (int i = 0; i < 16; i++)
             m[i] = (uint32_t)buf_[4 * i] | ((uint32_t)buf_[4 * i + 1] << 8) | ((uint32_t)buf_[4 * i + 2] << 16) | ((uint32_t)buf_[4 * i + 3] << 24);
+#endif
         for (int i = 0; i < 8; i++) { v[i] = h_[i]; v[8 + i] = iv[i]; }
         v[12] ^= (uint32_t)t_;
         v[13] ^= (uint32_t)(t_ >> 32);

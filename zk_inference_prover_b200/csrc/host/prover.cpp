@@ -9,6 +9,9 @@
 #include <memory>
 #include <numeric>
 #include <set>
+#include <string>
+#include <cstdio>
+#include <cstdlib>
 
 #include "../../../include/zkb200_prover.h"
 #include "../air_program.hpp"
@@ -25,6 +28,28 @@ extern "C" int zk_set_error_public(zkb_ctx* ctx, int code, const char* msg);
 namespace b200 {
 
 using namespace zk;
+
+// Host-side timing of the protocol code's own steps (the device has per-kernel events; this is for the time the host
+// spends between launches). Off unless ZKB_HOST_TIMING is set; totals per label go to stderr when a proof call returns.
+struct HostClock {
+    static bool on() { static const bool v = getenv("ZKB_HOST_TIMING") != nullptr; return v; }
+    static std::map<std::string, std::pair<double, size_t>>& totals() { static std::map<std::string, std::pair<double, size_t>> m; return m; }
+    const char* label;
+    std::chrono::steady_clock::time_point t0;
+    explicit HostClock(const char* l) : label(l) { if (on()) t0 = std::chrono::steady_clock::now(); }
+    ~HostClock() {
+        if (!on()) return;
+        auto& e = totals()[label];
+        e.first += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        e.second++;
+    }
+    static void dump(const char* what) {
+        if (!on()) return;
+        fprintf(stderr, "[host timing] %s\n", what);
+        for (auto& kv : totals()) fprintf(stderr, "  %-34s %10.3f ms %8zu calls\n", kv.first.c_str(), kv.second.first, kv.second.second);
+        totals().clear();
+    }
+};
 
 static inline uint32_t ilog2(size_t n) { uint32_t l = 0; while (((size_t)1 << (l + 1)) <= n) l++; return l; }
 static inline qm31 operator+(qm31 a, qm31 b) { return qm31_add(a, b); }
@@ -604,6 +629,7 @@ struct CommitmentSchemeProver {
     // pcs/quotient_ops.rs:73-194 with STWO/core/pcs/quotients.rs:306-345 and :75-104
     SecureColumnByCoords compute_fri_quotients(const std::vector<std::vector<std::vector<PointSample>>>& samples, qm31 random_coeff,
                                                uint32_t lifting_log) {
+        std::unique_ptr<HostClock> hc(new HostClock("pcs.quot.flatten"));
         std::vector<const BaseColumn*> flat_cols;
         std::vector<uint32_t> flat_logs;
         std::vector<std::vector<std::pair<PointSample, qm31>>> flat_samples;
@@ -629,6 +655,7 @@ struct CommitmentSchemeProver {
                 }
                 flat_samples.push_back(v);
             }
+        hc.reset(new HostClock("pcs.quot.groups"));
         std::vector<size_t> order(flat_cols.size());
         std::iota(order.begin(), order.end(), 0);
         std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return flat_logs[a] < flat_logs[b]; });
@@ -647,9 +674,13 @@ struct CommitmentSchemeProver {
                     b->cols_vals_randpows.push_back({k - i, sp.first.value, sp.second});
                 }
             }
-            B200Backend::accumulate_numerators(d, group_cols, batches, accs);
+            {
+                HostClock hn("pcs.quot.numerators");
+                B200Backend::accumulate_numerators(d, group_cols, batches, accs);
+            }
             i = j;
         }
+        hc.reset(new HostClock("pcs.quot.combine"));
         std::stable_sort(accs.begin(), accs.end(),
                          [](const AccumulatedNumerators& a, const AccumulatedNumerators& b) { return point_less(a.sample_point, b.sample_point); });
         std::vector<AccumulatedNumerators> per_point;
@@ -679,6 +710,7 @@ struct CommitmentSchemeProver {
             if (!t.evals.empty() && t.max_log() > lifting_log)
                 throw Error(ZKB_EINVAL, "pcs: the last tree must hold the tallest column (every column is lifted to its height)");
         // batch out-of-domain evaluation: one call per (coefficient size, transformed point) group (:187-265)
+        std::unique_ptr<HostClock> hc(new HostClock("pcs.sample.group"));
         std::vector<std::vector<std::vector<PointSample>>> samples(trees.size());
         struct Group { uint32_t log; CirclePointQ pt; std::vector<std::array<size_t, 3>> where; std::vector<const BaseColumn*> cols; };
         std::vector<Group> groups;
@@ -704,10 +736,12 @@ struct CommitmentSchemeProver {
                 }
             }
         }
+        hc.reset(new HostClock("pcs.sample.eval"));
         for (auto& g : groups) {
             auto vals = B200Backend::batch_eval_at_point(d, g.cols, g.pt);
             for (size_t i = 0; i < vals.size(); i++) samples[g.where[i][0]][g.where[i][1]][g.where[i][2]].value = vals[i];
         }
+        hc.reset(new HostClock("pcs.sample.flatten"));
         std::vector<qm31> flat_values;
         for (size_t t = 0; t < trees.size(); t++) {
             proof.sampled_values.emplace_back();
@@ -718,15 +752,19 @@ struct CommitmentSchemeProver {
             }
         }
         mark(3);
+        hc.reset(new HostClock("pcs.quot.mix"));
         ch.mix_felts(flat_values);
         qm31 random_coeff = ch.draw_secure_felt();
+        hc.reset(new HostClock("pcs.quot.compute"));
         SecureColumnByCoords quotients = compute_fri_quotients(samples, random_coeff, lifting_log);
+        hc.reset();
         mark(4);
         FriProver fri = FriProver::commit(d, ch, config.fri, quotients);
         mark(5);
         proof.proof_of_work = B200Backend::grind(d, ch.pow_prefixed_digest(config.pow_bits), config.pow_bits);
         ch.mix_u64(proof.proof_of_work);
         mark(6);
+        hc.reset(new HostClock("pcs.decommit.plan"));
         std::vector<size_t> query_positions;
         GatherPlan plan;
         auto fri_pending = fri.plan_decommit(plan, d, ch, query_positions);
@@ -747,7 +785,9 @@ struct CommitmentSchemeProver {
             }
             tree_pending.push_back(t.commitment.plan_decommit(plan, per_log, refs));
         }
+        hc.reset(new HostClock("pcs.decommit.gather"));
         plan.execute(d);
+        hc.reset(new HostClock("pcs.decommit.finish"));
         proof.fri = fri.finish_decommit(plan, fri_pending);
         for (size_t k = 0; k < trees.size(); k++) {
             auto r = tree_pending[k].finish(plan);
@@ -755,6 +795,7 @@ struct CommitmentSchemeProver {
             proof.decommitments.push_back(std::move(r.second));
             proof.commitments.push_back(trees[k].commitment.root(d));
         }
+        hc.reset();
         mark(7);
         return proof;
     }
@@ -900,6 +941,7 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
         return it;
     };
     std::vector<BaseColumn> slabs;  // one allocation per tower level; the layers of that level are views of it
+    std::unique_ptr<HostClock> hc_towers(new HostClock("gkr.towers"));
     for (;;) {
         items.clear();
         size_t words = 0;
@@ -926,6 +968,7 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
         }
         d.check(zk::gkr_batch_next_layer(d.ctx(), items.data(), (int)items.size()));
     }
+    hc_towers.reset();
     std::vector<uint32_t> results;
     // the output layers (one entry per column) of all instances, read in one gather
     GatherPlan top_plan;
@@ -941,7 +984,9 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
     if (!top_plan.addrs.empty()) top_plan.execute(d);
     auto top_q = [&](size_t slot) { return qm31{{top_plan.words[slot], top_plan.words[slot + 1], top_plan.words[slot + 2], top_plan.words[slot + 3]}}; };
     std::vector<std::vector<UniPoly>> sumcheck_round_polys;
-    std::vector<std::vector<std::vector<std::array<qm31, 2>>>> masks_by_inst(n_inst);
+    struct MaskRec { uint32_t n_cols; qm31 v[4]; };  // column c is (v[2c], v[2c+1])
+    std::vector<std::vector<MaskRec>> masks_by_inst(n_inst);
+    for (size_t i = 0; i < n_inst; i++) masks_by_inst[i].reserve(n_layers_by_inst[i]);
     std::vector<std::vector<qm31>> output_claims(n_inst), claims(n_inst);
     std::vector<bool> active(n_inst, false);
     std::vector<qm31> ood_point;
@@ -966,9 +1011,11 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
         for (size_t i = 0; i < n_inst; i++)
             if (active[i]) ch.mix_felts(claims[i]);
         // EqEvals::generate, :235-247
+        std::unique_ptr<HostClock> hc_eq(new HostClock("gkr.layer.eq_evals"));
         SecureMle eq_evals;
         if (ood_point.empty()) eq_evals = B200Backend::gen_eq_evals(d, {}, qm31_one());
         else eq_evals = B200Backend::gen_eq_evals(d, std::vector<qm31>(ood_point.begin() + 1, ood_point.end()), eq1(qm31_zero(), ood_point[0]));
+        hc_eq.reset();
         qm31 sumcheck_alpha = ch.draw_secure_felt();
         qm31 lambda = ch.draw_secure_felt();
         std::vector<GkrOracle> oracles;
@@ -989,6 +1036,7 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
         for (size_t round = 0; round < nv; round++) {
             size_t n_rem = nv - round;
             // the oracles that enter the sum-check in this round have no sums yet: one launch for all of them
+            std::unique_ptr<HostClock> hc(new HostClock("gkr.round.first_sums"));
             items.clear();
             std::vector<size_t> who;
             for (size_t k = 0; k < oracles.size(); k++)
@@ -1017,6 +1065,7 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
             // last oracle down) is (sum alpha^k r0_k) L0 + (sum alpha^k r1_k) L1 + (sum alpha^k r2_k) L2 plus the constants of
             // the oracles that wait: eleven multiplications per oracle and round instead of a Lagrange interpolation each.
             // r0 + r1 is the claim by construction, which is the check sumcheck.rs:128-130 makes.
+            hc.reset(new HostClock("gkr.round.algebra"));
             const RoundBasis basis(ood_point, n_rem);
             const size_t K = oracles.size();
             std::vector<qm31> rv(3 * K);
@@ -1054,14 +1103,17 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
                     combined = UniPoly::add(combined, rp);
                 }
             }
+            hc.reset(new HostClock("gkr.round.channel"));
             ch.mix_felts(combined.c);
             qm31 challenge = ch.draw_secure_felt();
+            hc.reset(new HostClock("gkr.round.claims"));
             qm31 Lc[3];
             for (int t = 0; t < 3; t++) Lc[t] = ((basis.L[t][3] * challenge + basis.L[t][2]) * challenge + basis.L[t][1]) * challenge + basis.L[t][0];
             for (size_t k = 0; k < K; k++)
                 sc_claims[k] = act[k] ? rv[3 * k] * Lc[0] + rv[3 * k + 1] * Lc[1] + rv[3 * k + 2] * Lc[2] : rv[3 * k];
             const qm31 eq_step = eq1(challenge, ood_point[ood_point.size() - n_rem]);  // the same for every active oracle
             // fix the first variable of every active oracle (and take the next round's sums in the same pass): one launch
+            hc.reset(new HostClock("gkr.round.fix_prepare"));
             items.clear();
             who.clear();
             std::vector<Layer> fixed;
@@ -1092,8 +1144,10 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
                     who.push_back(k);
                 }
             if (!items.empty()) {
+                hc.reset(new HostClock("gkr.round.fix_launch_wait"));
                 results.resize(items.size() * zk::GKR_BATCH_RESULT_WORDS);
                 d.check(zk::gkr_batch_round(d.ctx(), items.data(), (int)items.size(), challenge.c, eq_evals.words.ptr(), lambda.c, results.data()));
+                hc.reset(new HostClock("gkr.round.fix_results"));
                 for (size_t j = 0; j < who.size(); j++) {
                     GkrOracle& o = oracles[who[j]];
                     const uint32_t* w = results.data() + j * zk::GKR_BATCH_RESULT_WORDS;
@@ -1110,36 +1164,56 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
                     o.input_layer = std::move(fixed[j]);
                 }
             }
+            hc.reset();
             round_polys.push_back(combined);
             assignment.push_back(challenge);
         }
+        HostClock hc_masks("gkr.layer.masks");
         sumcheck_round_polys.push_back(round_polys);
-        std::vector<std::vector<std::array<qm31, 2>>> masks;  // try_into_mask, :572-597
-        for (auto& o : oracles) {
+        // try_into_mask, :572-597. A mask is one column pair (grand product) or two (numerators, denominators): kept as flat
+        // records; a batch has hundreds of oracles per layer, and a vector of vectors per oracle cost more than the hashing.
+        std::vector<MaskRec> masks(oracles.size());
+        // An oracle that entered this layer with two entries had no sum-check round, so no launch has returned its mask:
+        // those (every instance once, in the layer above its output) are read in one gather, not one copy per column.
+        GatherPlan mask_plan;
+        std::vector<size_t> mask_slot(oracles.size(), SIZE_MAX);
+        for (size_t k = 0; k < oracles.size(); k++) {
+            const GkrOracle& o = oracles[k];
+            if (o.have_mask || o.input_layer.len() != 2) continue;
+            mask_slot[k] = mask_plan.addrs.size();
+            for (int w = 0; w < 8; w++) mask_plan.add(o.input_layer.den.words.ptr() + w);
+            if (o.input_layer.kind == ZKB_GKR_LOGUP_GENERIC)
+                for (int w = 0; w < 8; w++) mask_plan.add(o.input_layer.num.words.ptr() + w);
+        }
+        if (!mask_plan.addrs.empty()) mask_plan.execute(d);
+        auto gathered = [&](size_t slot) { return qm31{{mask_plan.words[slot], mask_plan.words[slot + 1], mask_plan.words[slot + 2], mask_plan.words[slot + 3]}}; };
+        for (size_t k = 0; k < oracles.size(); k++) {
+            const GkrOracle& o = oracles[k];
             const Layer& l = o.input_layer;
             if (l.len() != 2) throw Error(ZKB_EINVAL, "gkr: oracle is not constant after sumcheck");
-            std::vector<qm31> den = o.have_mask ? std::vector<qm31>{o.mask_den[0], o.mask_den[1]} : mle_to_cpu(d, l.den);
-            if (l.kind == ZKB_GKR_GRAND_PRODUCT) masks.push_back({{den[0], den[1]}});
-            else if (l.kind == ZKB_GKR_LOGUP_GENERIC) {
-                std::vector<qm31> num = o.have_mask ? std::vector<qm31>{o.mask_num[0], o.mask_num[1]} : mle_to_cpu(d, l.num);
-                masks.push_back({{num[0], num[1]}, {den[0], den[1]}});
-            }
-            else if (l.kind == ZKB_GKR_LOGUP_SINGLES) masks.push_back({{qm31_one(), qm31_one()}, {den[0], den[1]}});
+            MaskRec& m = masks[k];
+            qm31 den[2], num[2];
+            if (o.have_mask) { den[0] = o.mask_den[0]; den[1] = o.mask_den[1]; }
+            else { den[0] = gathered(mask_slot[k]); den[1] = gathered(mask_slot[k] + 4); }
+            if (l.kind == ZKB_GKR_GRAND_PRODUCT) { m.n_cols = 1; m.v[0] = den[0]; m.v[1] = den[1]; continue; }
+            if (l.kind == ZKB_GKR_LOGUP_GENERIC) {
+                if (o.have_mask) { num[0] = o.mask_num[0]; num[1] = o.mask_num[1]; }
+                else { num[0] = gathered(mask_slot[k] + 8); num[1] = gathered(mask_slot[k] + 12); }
+            } else if (l.kind == ZKB_GKR_LOGUP_SINGLES) num[0] = num[1] = qm31_one();
             else throw Error(ZKB_EINVAL, "gkr: a multiplicities layer cannot be a mask");
+            m.n_cols = 2; m.v[0] = num[0]; m.v[1] = num[1]; m.v[2] = den[0]; m.v[3] = den[1];
         }
         for (size_t k = 0; k < oracles.size(); k++) {
-            std::vector<qm31> flat;
-            for (auto& col : masks[k]) { flat.push_back(col[0]); flat.push_back(col[1]); }
-            ch.mix_felts(flat);
+            ch.mix_felts(masks[k].v, 2 * masks[k].n_cols);
             masks_by_inst[sc_inst[k]].push_back(masks[k]);
         }
         qm31 challenge = ch.draw_secure_felt();
         ood_point = assignment;
         ood_point.push_back(challenge);
         for (size_t k = 0; k < oracles.size(); k++) {
-            std::vector<qm31> next;
-            for (auto& col : masks[k]) next.push_back(challenge * (col[1] - col[0]) + col[0]);
-            claims[sc_inst[k]] = next;
+            std::vector<qm31>& next = claims[sc_inst[k]];
+            next.resize(masks[k].n_cols);
+            for (uint32_t c = 0; c < masks[k].n_cols; c++) next[c] = challenge * (masks[k].v[2 * c + 1] - masks[k].v[2 * c]) + masks[k].v[2 * c];
         }
     }
     std::vector<uint32_t> o;
@@ -1151,7 +1225,7 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
     }
     for (auto& inst : masks_by_inst) {
         o.push_back((uint32_t)inst.size());
-        for (auto& m : inst) { o.push_back((uint32_t)m.size()); for (auto& col : m) { put(col[0]); put(col[1]); } }
+        for (auto& m : inst) { o.push_back(m.n_cols); for (uint32_t c = 0; c < 2 * m.n_cols; c++) put(m.v[c]); }
     }
     for (auto& c : output_claims) { o.push_back((uint32_t)c.size()); for (auto q : c) put(q); }
     o.push_back((uint32_t)ood_point.size());
@@ -1528,7 +1602,10 @@ static int pcs_prove_impl(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint
         Channel ch;
         config.mix_into(ch);
         CommitmentSchemeProver prover(dev, config, h_phase_ms);
-        commit_input_trees(dev, ctx, prover, ch, n_trees, tree_ncols, d_cols, h_cols, col_logs, total);
+        {
+            HostClock hcc("pcs.commit_trees");
+            commit_input_trees(dev, ctx, prover, ch, n_trees, tree_ncols, d_cols, h_cols, col_logs, total);
+        }
         int flat = 0;
         CirclePointQ oods = get_random_point(ch);
         std::vector<std::vector<std::vector<CirclePointQ>>> points(n_trees);
@@ -1544,12 +1621,16 @@ static int pcs_prove_impl(zkb_ctx* ctx, int n_trees, const int* tree_ncols, uint
                 p.push_back(oods);
                 points[t].push_back(p);
             }
+        std::unique_ptr<HostClock> hc(new HostClock("pcs.prove_values"));
         PcsProof proof = prover.prove_values(points, ch);
         prover.finish_timing();
+        hc.reset(new HostClock("pcs.write"));
         PcsProof::RawSink w{h_out, cap};  // straight into the caller's buffer: a proof of many columns is tens of megabytes
         proof.write(w);
         w.insert(w.end(), ch.digest().begin(), ch.digest().end());
         *n_words = w.size();
+        hc.reset();
+        HostClock::dump("zkb_pcs_prove");
         if (w.size() > cap) return zk_set_error_public(ctx, ZKB_EINVAL, "zkb_pcs_prove: output buffer too small");
         return ZKB_OK;
     } catch (const Error& e) {
@@ -1848,6 +1929,7 @@ int zkb_gkr_prove_device(zkb_ctx* ctx, int n_inst, const int* kinds, const uint3
         *n_words = w.size();
         if (w.size() > cap) return zk_set_error_public(ctx, ZKB_EINVAL, "zkb_gkr_prove: output buffer too small");
         memcpy(h_out, w.data(), w.size() * 4);
+        HostClock::dump("zkb_gkr_prove_device");
         return ZKB_OK;
     } catch (const Error& e) {
         return zk_set_error_public(ctx, e.code, e.what());
