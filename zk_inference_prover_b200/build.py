@@ -52,7 +52,7 @@ def build(force=False, verbose=False):
             sys.stderr.write(out)
     if failed:
         raise RuntimeError("nvcc failed; see messages above")
-    cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-ldl"]  # cudart is linked statically (nvcc default)
+    cmd = [nvcc, "-shared", "-o", LIB] + objs + ["-ldl", "-lpthread"]  # cudart is linked statically (nvcc default)
     subprocess.run(cmd, check=True)
     return LIB
 

@@ -31,6 +31,10 @@ struct zkb_ctx {
     size_t scratch_words = 0;
     unsigned int* ticket = nullptr;
     uint32_t* h_small = nullptr;  // pinned, for small results read back by the host
+    // Batched GKR rounds (gkr_batch.cu): per-item tickets (zero between launches: the last CTA of an item clears its own)
+    // and a pinned landing buffer for the per-item results; both allocated on first use.
+    unsigned int* batch_tickets = nullptr;
+    uint32_t* h_batch = nullptr;
     cudaEvent_t events[64] = {nullptr};
     // A second stream for host-to-device copies that overlap compute, and the fences between the two.
     cudaStream_t copy_stream = nullptr;

@@ -157,6 +157,8 @@ int zkb_destroy(zkb_ctx* ctx) {
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->ticket) cudaFree(ctx->ticket);
     if (ctx->h_small) cudaFreeHost(ctx->h_small);
+    if (ctx->h_batch) cudaFreeHost(ctx->h_batch);
+    if (ctx->batch_tickets) cudaFree(ctx->batch_tickets);
     for (int i = 0; i < 64; i++)
         if (ctx->events[i]) cudaEventDestroy(ctx->events[i]);
     if (ctx->prof) {

@@ -261,24 +261,35 @@ int gkr_batch_round(zkb_ctx* ctx, GkrBatchItem* items, int n_items, const uint32
     if ((size_t)n_items > GKR_BATCH_MAX_ITEMS) return set_error(ctx, ZKB_EINVAL, "gkr batch: more than %d instances", (int)GKR_BATCH_MAX_ITEMS);
     DeviceGuard g(ctx);
     uint32_t total = plan_blocks(items, n_items, 0);
-    // scratch: [results | tickets | partials]
+    if (!ctx->batch_tickets) {
+        ZKB_CUDA(ctx, cudaMalloc(&ctx->batch_tickets, GKR_BATCH_MAX_ITEMS * sizeof(unsigned int)));
+        ZKB_CUDA(ctx, cudaMemsetAsync(ctx->batch_tickets, 0, GKR_BATCH_MAX_ITEMS * sizeof(unsigned int), ctx->stream));
+        ZKB_CUDA(ctx, cudaMallocHost(&ctx->h_batch, GKR_BATCH_RESULT_WORDS * GKR_BATCH_MAX_ITEMS * 4));
+    }
+    // scratch: [results | (unused) | partials]
     uint32_t* results = ctx->scratch;
-    unsigned int* tickets = reinterpret_cast<unsigned int*>(ctx->scratch + (size_t)GKR_BATCH_RESULT_WORDS * GKR_BATCH_MAX_ITEMS);
+    unsigned int* tickets = ctx->batch_tickets;
     uint32_t* partials = ctx->scratch + (size_t)(GKR_BATCH_RESULT_WORDS + 1) * GKR_BATCH_MAX_ITEMS;
     if ((size_t)(GKR_BATCH_RESULT_WORDS + 1) * GKR_BATCH_MAX_ITEMS + 8 * (size_t)total > ctx->scratch_words)
         return set_error(ctx, ZKB_EINVAL, "gkr batch: %u CTAs exceed the scratch buffer", total);
     const GkrBatchItem* d_items;
     int rc = stage_items(ctx, items, n_items, &d_items);
     if (rc) return rc;
-    ZKB_CUDA(ctx, cudaMemsetAsync(tickets, 0, (size_t)n_items * 4, ctx->stream));
     qm31 r{{h_r[0], h_r[1], h_r[2], h_r[3]}}, lam{{h_lambda[0], h_lambda[1], h_lambda[2], h_lambda[3]}};
     {
         ProfScope prof(ctx, "gkr_batch_round_kernel");
         gkr_batch_round_kernel<<<total, 256, 0, ctx->stream>>>(d_items, n_items, r, eq_evals, lam, partials, tickets, results);
     }
-    ZKB_LAUNCH_CHECK(ctx);
-    ZKB_CUDA(ctx, cudaMemcpyAsync(h_results, results, (size_t)n_items * GKR_BATCH_RESULT_WORDS * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    const size_t bytes = (size_t)n_items * GKR_BATCH_RESULT_WORDS * 4;
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaMemcpyAsync(ctx->h_batch, results, bytes, cudaMemcpyDeviceToHost, ctx->stream);  // pinned: one DMA, no bounce buffer
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) {
+        // a launch that did not run to its end may have left tickets counted up
+        cudaMemsetAsync(ctx->batch_tickets, 0, GKR_BATCH_MAX_ITEMS * sizeof(unsigned int), ctx->stream);
+        return set_error(ctx, ZKB_ECUDA, "gkr batch round: %s", cudaGetErrorString(e));
+    }
+    memcpy(h_results, ctx->h_batch, bytes);
     return ZKB_OK;
 }
 

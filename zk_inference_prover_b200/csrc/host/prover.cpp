@@ -10,6 +10,7 @@
 #include <numeric>
 #include <set>
 #include <string>
+#include <thread>
 #include <cstdio>
 #include <cstdlib>
 
@@ -110,28 +111,38 @@ struct GatherPlan {
 };
 
 // ------------------------------------------------------------------ MerkleProver (STWO/prover/vcs/prover.rs:17-217)
-struct MerkleDecommitment { std::vector<Hash> hash_witness; std::vector<uint32_t> column_witness; };
+// A word sequence of a proof: its own vector, or runs inside the gather buffer of the plan that read them (the buffer is
+// kept per thread until the next proof on that thread, so a proof can be serialised straight out of it: a tree of tens of
+// thousands of columns has tens of megabytes of queried values, and every copy of them costs milliseconds).
+struct Words {
+    std::vector<uint32_t> own;
+    std::vector<std::pair<const uint32_t*, size_t>> runs;
+    size_t size() const { size_t n = own.size(); for (auto& r : runs) n += r.second; return n; }
+    template <class O> void append_to(O& o) const {
+        o.insert(o.end(), own.begin(), own.end());
+        for (auto& r : runs) o.insert(o.end(), r.first, r.first + r.second);
+    }
+};
+struct MerkleDecommitment { std::vector<Hash> hash_witness; Words column_witness; };
 struct PendingMerkle {  // slots of a planned decommitment
     std::vector<size_t> hash_slots;
     struct Run { size_t off, count; bool queried; };  // `count` words of plan.block_words, in proof order
     std::vector<Run> runs;
-    std::pair<std::vector<uint32_t>, MerkleDecommitment> finish(const GatherPlan& plan) const {
-        std::pair<std::vector<uint32_t>, MerkleDecommitment> r;
+    std::pair<Words, MerkleDecommitment> finish(const GatherPlan& plan) const {
+        std::pair<Words, MerkleDecommitment> r;
+        r.second.hash_witness.reserve(hash_slots.size());
         for (auto s : hash_slots) r.second.hash_witness.push_back(plan.hash_at(s));
-        size_t nq = 0, nw = 0;
-        for (auto& run : runs) (run.queried ? nq : nw) += run.count;
-        r.first.reserve(nq);
-        r.second.column_witness.reserve(nw);
-        for (auto& run : runs) {
-            auto& dst = run.queried ? r.first : r.second.column_witness;
-            dst.insert(dst.end(), plan.block_words + run.off, plan.block_words + run.off + run.count);
-        }
+        for (auto& run : runs) (run.queried ? r.first : r.second.column_witness).runs.push_back({plan.block_words + run.off, run.count});
         return r;
     }
 };
 
 struct MerkleProver {
     std::vector<HashColumn> layers;  // layers[log_size]; layers[0] holds the root
+    // the committed columns of each layer (device addresses, in commitment order), kept for the decommitment: sorting tens
+    // of thousands of columns by size a second time costs milliseconds
+    std::vector<std::vector<const uint32_t*>> layer_col_ptrs;
+    size_t n_columns = 0;
 
     // `leaves`, when given, is the already hashed largest layer (see zkb_merkle_leaves_partial).
     static MerkleProver commit(const Device& d, const std::vector<const BaseColumn*>& columns, HashColumn* leaves = nullptr) {  // :39-64
@@ -144,10 +155,13 @@ struct MerkleProver {
         std::stable_sort(sorted.begin(), sorted.end(), [](const BaseColumn* a, const BaseColumn* b) { return a->len() > b->len(); });
         uint32_t max_log = sorted[0]->log_size();
         mp.layers.resize(max_log + 1);
+        mp.layer_col_ptrs.resize(max_log + 1);
+        mp.n_columns = sorted.size();
         size_t pos = 0;
         for (uint32_t log = max_log + 1; log-- > 0;) {
             std::vector<const BaseColumn*> layer_cols;
             while (pos < sorted.size() && sorted[pos]->log_size() == log) layer_cols.push_back(sorted[pos++]);
+            for (auto c : layer_cols) mp.layer_col_ptrs[log].push_back(c->ptr());
             if (log == max_log && leaves) mp.layers[log] = std::move(*leaves);
             else mp.layers[log] = B200Backend::commit_on_layer(d, log, log == max_log ? nullptr : &mp.layers[log + 1], layer_cols);
             if (log > 0 && log <= 10 && pos == sorted.size()) {
@@ -173,8 +187,13 @@ struct MerkleProver {
     PendingMerkle plan_decommit(GatherPlan& plan, const std::map<uint32_t, std::vector<size_t>>& queries_per_log_size,
                                 const std::vector<const BaseColumn*>& columns, std::vector<size_t>* hashes_per_layer = nullptr) const {
         PendingMerkle pm;
-        std::vector<const BaseColumn*> sorted(columns);
-        std::stable_sort(sorted.begin(), sorted.end(), [](const BaseColumn* a, const BaseColumn* b) { return a->len() > b->len(); });
+        // the layers' column lists as recorded by commit(); sorted again only for a tree that was not built there
+        const bool recorded = layer_col_ptrs.size() == layers.size() && n_columns == columns.size();
+        std::vector<const BaseColumn*> sorted;
+        if (!recorded) {
+            sorted = columns;
+            std::stable_sort(sorted.begin(), sorted.end(), [](const BaseColumn* a, const BaseColumn* b) { return a->len() > b->len(); });
+        }
         size_t pos = 0;
         std::vector<size_t> last;
         for (uint32_t log = (uint32_t)layers.size(); log-- > 0;) {
@@ -185,8 +204,10 @@ struct MerkleProver {
             if (it != queries_per_log_size.end()) col_queries.insert(it->second.begin(), it->second.end());
             merged.insert(col_queries.begin(), col_queries.end());
             std::vector<size_t> merged_nodes(merged.begin(), merged.end());
-            std::vector<const BaseColumn*> layer_cols;
-            while (pos < sorted.size() && sorted[pos]->log_size() == log) layer_cols.push_back(sorted[pos++]);
+            std::vector<const uint32_t*> layer_ptrs_own;
+            if (!recorded)
+                while (pos < sorted.size() && sorted[pos]->log_size() == log) layer_ptrs_own.push_back(sorted[pos++]->ptr());
+            const std::vector<const uint32_t*>& ptrs = recorded ? layer_col_ptrs[log] : layer_ptrs_own;
             std::vector<size_t> witness_children, queried_nodes, witness_nodes;
             for (size_t node : merged_nodes) {
                 if (has_prev) {
@@ -197,10 +218,8 @@ struct MerkleProver {
             }
             for (size_t child : witness_children) pm.hash_slots.push_back(plan.add_hash(layers[log + 1].ptr() + 8 * child));
             if (hashes_per_layer) hashes_per_layer->push_back(witness_children.size());
-            if (!layer_cols.empty() && !merged_nodes.empty()) {
+            if (!ptrs.empty() && !merged_nodes.empty()) {
                 // every node of the layer is read once; the proof lists the queried nodes' values first, then the witnesses'
-                std::vector<const uint32_t*> ptrs;
-                for (auto c : layer_cols) ptrs.push_back(c->ptr());
                 std::vector<size_t> order(queried_nodes);
                 order.insert(order.end(), witness_nodes.begin(), witness_nodes.end());
                 size_t off = plan.add_block(ptrs, order);
@@ -468,7 +487,7 @@ struct PcsProof {
     std::vector<Hash> commitments;
     std::vector<std::vector<std::vector<qm31>>> sampled_values;
     std::vector<MerkleDecommitment> decommitments;
-    std::vector<std::vector<uint32_t>> queried_values;
+    std::vector<Words> queried_values;
     uint64_t proof_of_work = 0;
     FriProof fri;
     // A sink with the two vector operations the writers use, over a caller's buffer: words past the capacity are counted, not
@@ -481,8 +500,21 @@ struct PcsProof {
         void push_back(uint32_t v) { if (n < cap) out[n] = v; n++; }
         template <class It> void insert(int, It b, It e) {
             size_t k = (size_t)(e - b);
-            if (n + k <= cap && k) memcpy(out + n, &*b, k * 4);
+            if (n + k <= cap && k) copy_words(out + n, &*b, k);
             n += k;
+        }
+        // A run of many megabytes (the queried values of a wide tree) is copied by four threads: one core moves about
+        // 10 GB/s, and the proof of a composed segment is 50 MB.
+        static void copy_words(uint32_t* dst, const uint32_t* src, size_t k) {
+            if (k < ((size_t)2 << 20)) { memcpy(dst, src, k * 4); return; }
+            const size_t part = (k + 3) / 4;
+            std::thread th[3];
+            for (int t = 0; t < 3; t++) {
+                size_t lo = (size_t)(t + 1) * part, hi = std::min(k, lo + part);
+                th[t] = std::thread([=] { if (lo < hi) memcpy(dst + lo, src + lo, (hi - lo) * 4); });
+            }
+            memcpy(dst, src, std::min(k, part) * 4);
+            for (auto& t : th) t.join();
         }
         size_t size() const { return n; }
     };
@@ -492,7 +524,7 @@ struct PcsProof {
         o.push_back((uint32_t)d.hash_witness.size());
         for (auto& h : d.hash_witness) put_hash(o, h);
         o.push_back((uint32_t)d.column_witness.size());
-        o.insert(o.end(), d.column_witness.begin(), d.column_witness.end());
+        d.column_witness.append_to(o);
     }
     template <class O> static void put_layer(O& o, const FriLayerProof& l) {
         o.push_back((uint32_t)l.fri_witness.size());
@@ -518,7 +550,7 @@ struct PcsProof {
             for (auto& c : t) { o.push_back((uint32_t)c.size()); for (auto q : c) put_q(o, q); }
         }
         for (auto& d : decommitments) put_dec(o, d);
-        for (auto& t : queried_values) { o.push_back((uint32_t)t.size()); o.insert(o.end(), t.begin(), t.end()); }
+        for (auto& t : queried_values) { o.push_back((uint32_t)t.size()); t.append_to(o); }
         o.push_back((uint32_t)proof_of_work);
         o.push_back((uint32_t)(proof_of_work >> 32));
         put_layer(o, fri.first_layer);
@@ -1454,7 +1486,7 @@ int zkb_shard_pcs_fri_and_decommit(zkb_shard_pcs* h, uint32_t* h_part, size_t ca
             for (size_t k = 0; k < cnt; k++, at++) o.insert(o.end(), mine.second.hash_witness[at].begin(), mine.second.hash_witness[at].end());
         }
         o.push_back((uint32_t)mine.first.size());
-        o.insert(o.end(), mine.first.begin(), mine.first.end());
+        mine.first.append_to(o);
         *n_words = o.size();
         if (o.size() > cap) throw Error(ZKB_EINVAL, "zkb_shard_pcs_fri_and_decommit: output buffer too small");
         memcpy(h_part, o.data(), o.size() * 4);
@@ -1499,7 +1531,7 @@ int zkb_shard_pcs_finish(zkb_shard_pcs* h, const uint32_t* const* h_parts, const
             values.insert(values.end(), p + c, p + c + cnt);
         }
         proof.decommitments.push_back(std::move(dec));
-        proof.queried_values.push_back(std::move(values));
+        proof.queried_values.push_back(Words{std::move(values), {}});
         proof.proof_of_work = s.nonce;
         proof.fri = s.fri_proof;
         PcsProof::RawSink w{h_out, cap};
