@@ -160,11 +160,20 @@ int zkb_merkle_layer(zkb_ctx* ctx, int log_size, const uint32_t* prev, const uin
  * NULL, all columns) would produce after the last one. */
 int zkb_merkle_leaves_partial(zkb_ctx* ctx, int log_size, const uint32_t* const* cols, int ncols, int cols_before, int total_cols,
                               int m31_out, uint32_t* out);
+/* `levels` (1..9) consecutive layers of nodes without columns in one launch (MerkleProver::commit's loop,
+ * STWO/prover/vcs/prover.rs:39-64, for the layers that hold no column): children = the 2^child_log hashes of a layer
+ * (child_log >= 9), out_layers[j] = the layer j + 1 levels above it (2^(child_log - j - 1) hashes). Same node hash as
+ * zkb_merkle_layer with no columns. */
+int zkb_merkle_levels(zkb_ctx* ctx, int child_log, const uint32_t* children, int levels, uint32_t* const* out_layers, int m31_out);
 /* The upper part of a tree in one launch, for trees whose small layers take no columns (every FRI
  * layer tree; a trace tree without tiny columns): given the layer of 2^top_log hashes
  * (top_log <= 10), writes lower_layers[k] (2^k hashes) for k = top_log-1 .. 0, each node being
  * commit_on_layer(k, prev = layer k+1, no columns). Equivalent to top_log calls of zkb_merkle_layer. */
 int zkb_merkle_top(zkb_ctx* ctx, int top_log, const uint32_t* top_layer, uint32_t* const* lower_layers, int m31_out);
+/* The same, followed in the same launch by a FRI layer's channel step on the root it has just built: as
+ * zkb_channel_mix_root_draw(d_chan, root, d_alpha, d_root_copy) right after zkb_merkle_top (top_log >= 1). */
+int zkb_merkle_top_channel(zkb_ctx* ctx, int top_log, const uint32_t* top_layer, uint32_t* const* lower_layers, int m31_out, uint32_t* d_chan,
+                           uint32_t* d_alpha, uint32_t* d_root_copy);
 
 /* ---- FriOps (STWO/prover/fri.rs:37-85; cpu/fri.rs:67-123) ---------------------------------- */
 /* fold_circle_into_line: src on the canonic circle domain of log_n_src; dst (2^(log_n_src-1)

@@ -136,6 +136,14 @@ int zkb_gkr_prove_device(zkb_ctx* ctx, int n_inst, const int* kinds, const uint3
 typedef struct zkb_shard_pcs zkb_shard_pcs;
 int zkb_shard_pcs_begin(zkb_ctx* ctx, int rank, int world, int ncols_total, int log_n, const zkb_pcs_config* config, zkb_shard_pcs** out);
 int zkb_shard_pcs_extend(zkb_shard_pcs* s, uint32_t* const* d_cols, uint32_t** d_send, uint32_t** d_rows);
+/* The same stage by chunks of columns, so that a chunk's exchange runs while the next chunk is extended: begin interpolates all
+ * local columns and fixes the chunk count (it must divide ncl); chunk k extends columns [k ncl / n_chunks, (k + 1) ncl / n_chunks)
+ * and returns that chunk's send block ([world][ncl / n_chunks][R]), where to receive it ([world][ncl / n_chunks][R]: block s
+ * from rank s) and the words per peer. Every launch is stream-ordered: the caller starts chunk k's all-to-all after what has
+ * been enqueued so far and only has to order the subtree stage after the last one. zkb_shard_pcs_extend is begin with one
+ * chunk followed by chunk 0. */
+int zkb_shard_pcs_extend_begin(zkb_shard_pcs* s, uint32_t* const* d_cols, int n_chunks);
+int zkb_shard_pcs_extend_chunk(zkb_shard_pcs* s, int k, uint32_t** d_send, uint32_t** d_recv, size_t* words_per_peer);
 int zkb_shard_pcs_subtree(zkb_shard_pcs* s, uint32_t** d_root, uint32_t** d_roots);
 int zkb_shard_pcs_sample(zkb_shard_pcs* s, uint32_t* h_samples);
 int zkb_shard_pcs_quotients(zkb_shard_pcs* s, const uint32_t* h_all_samples, uint32_t* d_quot_local[4], uint32_t* d_quot_full[4]);

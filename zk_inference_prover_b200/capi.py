@@ -16,7 +16,7 @@ EXPORTED_SYMBOLS = [
     "zkb_malloc", "zkb_free", "zkb_memset_zero", "zkb_h2d", "zkb_d2h", "zkb_h2d_async", "zkb_d2h_async", "zkb_h2d_overlapped", "zkb_wait_fence", "zkb_d2d",
     "zkb_host_alloc_pinned", "zkb_host_free_pinned", "zkb_gather_multi", "zkb_gather_hashes", "zkb_gather_words", "zkb_twiddles_d2h",
     "zkb_ifft_cols", "zkb_lde_cols", "zkb_eval_at_point_cols", "zkb_barycentric_weights", "zkb_barycentric_eval_at_point", "zkb_eval_at_point_by_folding", "zkb_fri_decompose", "zkb_bit_reverse_m31", "zkb_bit_reverse_qm31",
-    "zkb_merkle_layer", "zkb_merkle_leaves_partial", "zkb_merkle_top", "zkb_fold_line_dalpha", "zkb_fold_circle_into_line_dalpha", "zkb_channel_mix_root_draw", "zkb_fold_line_dalpha_leaves", "zkb_fold_circle_into_line_dalpha_leaves", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine", "zkb_quot_combine_rows",
+    "zkb_merkle_layer", "zkb_merkle_leaves_partial", "zkb_merkle_levels", "zkb_merkle_top", "zkb_merkle_top_channel", "zkb_fold_line_dalpha", "zkb_fold_circle_into_line_dalpha", "zkb_channel_mix_root_draw", "zkb_fold_line_dalpha_leaves", "zkb_fold_circle_into_line_dalpha_leaves", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine", "zkb_quot_combine_rows",
     "zkb_accumulate", "zkb_lift_accumulate", "zkb_secure_powers", "zkb_gkr_eq_evals", "zkb_gkr_next_layer",
     "zkb_gkr_sum", "zkb_gkr_fix_and_sum", "zkb_mle_fix_qm31", "zkb_mle_fix_m31", "zkb_grind", "zkb_gkr_sum_noalloc", "zkb_gkr_sum_noalloc_error",
     "zkb_freivalds_scatter", "zkb_freivalds_acc", "zkb_witness_tables", "zkb_witness_dequant", "zkb_witness_pre_table", "zkb_key_tile_flags",
@@ -24,7 +24,7 @@ EXPORTED_SYMBOLS = [
 ]
 # Every symbol include/zkb200_prover.h declares.
 PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_stark_prove_device", "zkb_stark_prove_host", "zkb_stark_prove_multi_device", "zkb_stark_prove_multi_host", "zkb_gkr_prove_device",
-                  "zkb_shard_pcs_begin", "zkb_shard_pcs_extend", "zkb_shard_pcs_subtree", "zkb_shard_pcs_sample", "zkb_shard_pcs_quotients",
+                  "zkb_shard_pcs_begin", "zkb_shard_pcs_extend", "zkb_shard_pcs_extend_begin", "zkb_shard_pcs_extend_chunk", "zkb_shard_pcs_subtree", "zkb_shard_pcs_sample", "zkb_shard_pcs_quotients",
                   "zkb_shard_pcs_fri_and_decommit", "zkb_shard_pcs_finish", "zkb_shard_pcs_end"]
 # Every symbol include/zkb200_air.h declares.
 AIR_SYMBOLS = ["zkb_air_compile", "zkb_air_analyze", "zkb_air_free", "zkb_air_specialize", "zkb_air_select", "zkb_air_get_stats", "zkb_constraint_quotients", "zkb_constraint_denom_inv"]
@@ -145,6 +145,17 @@ class ShardPcsSession:
         e, r = C.c_void_p(), C.c_void_p()
         self.ctx._check(self.ctx.lib.zkb_shard_pcs_extend(self.h, _ptr_array(col_ptrs), C.byref(e), C.byref(r)))
         return e.value, r.value
+
+    def extend_begin(self, col_ptrs, n_chunks):
+        """The extend stage by chunks of columns (n_chunks must divide ncl): interpolates; then call extend_chunk(k) for every k."""
+        self.ctx._check(self.ctx.lib.zkb_shard_pcs_extend_begin(self.h, _ptr_array(col_ptrs), C.c_int(n_chunks)))
+
+    def extend_chunk(self, k):
+        """-> (send address, receive address, words per peer) of chunk k, both [world][ncl / n_chunks][R]. Then: one all-to-all
+        of the chunk (it may run while the next chunk is extended; the subtree stage must come after all of them)."""
+        e, r, w = C.c_void_p(), C.c_void_p(), C.c_size_t()
+        self.ctx._check(self.ctx.lib.zkb_shard_pcs_extend_chunk(self.h, C.c_int(k), C.byref(e), C.byref(r), C.byref(w)))
+        return e.value, r.value, int(w.value)
 
     def subtree(self):
         """-> (root address (8 words), roots address [world][8]). Then: all-gather the roots."""
@@ -467,6 +478,10 @@ class Context:
         arr = (C.c_void_p * len(col_ptrs))(*col_ptrs)
         self._check(self.lib.zkb_merkle_leaves_partial(self.h, C.c_int(log_size), arr, C.c_int(len(col_ptrs)), C.c_int(cols_before),
                                                        C.c_int(total_cols), C.c_int(1 if m31_out else 0), C.c_void_p(out_ptr)))
+
+    def merkle_levels(self, child_log, children_ptr, out_ptrs, m31_out=True):
+        self._check(self.lib.zkb_merkle_levels(self.h, C.c_int(child_log), C.c_void_p(children_ptr), C.c_int(len(out_ptrs)), _ptr_array(out_ptrs),
+                                               C.c_int(int(m31_out))))
 
     def merkle_top(self, top_log, top_ptr, lower_ptrs, m31_out=True):
         self._check(self.lib.zkb_merkle_top(self.h, C.c_int(top_log), C.c_void_p(top_ptr), _ptr_array(lower_ptrs), C.c_int(int(m31_out))))

@@ -153,21 +153,44 @@ __global__ void __launch_bounds__(256) merkle_leaves_partial_kernel(int log_size
 constexpr int MERKLE_TOP_MAX_LOG = 10;
 struct MerkleTopArgs { uint32_t* layer[MERKLE_TOP_MAX_LOG + 1]; };  // layer[k]: 2^k hashes
 
-__global__ void __launch_bounds__(512) merkle_top_kernel(MerkleTopArgs a, int top_log, int m31_out) {
-    for (int lg = top_log - 1; lg >= 0; lg--) {
-        const uint32_t* __restrict__ prev = a.layer[lg + 1];
-        for (uint32_t i = threadIdx.x; i < (1u << lg); i += blockDim.x) {
-            uint32_t h[8], m[16];
-            blake2s_init(h);
-            const uint4* p = reinterpret_cast<const uint4*>(prev + 16 * (size_t)i);
-            uint4 x0 = p[0], x1 = p[1], x2 = p[2], x3 = p[3];
-            m[0] = x0.x; m[1] = x0.y; m[2] = x0.z; m[3] = x0.w; m[4] = x1.x; m[5] = x1.y; m[6] = x1.z; m[7] = x1.w;
-            m[8] = x2.x; m[9] = x2.y; m[10] = x2.z; m[11] = x2.w; m[12] = x3.x; m[13] = x3.y; m[14] = x3.z; m[15] = x3.w;
-            blake2s_compress(h, m, 64u, true);
-            store_hash(a.layer[lg], i, h, m31_out != 0);
-        }
-        __threadfence_block();
+
+// Several consecutive layers of nodes (no columns) in one launch: a CTA takes 512 child hashes and builds up to nine levels
+// above them, every level written to its own layer array and kept in shared memory for the next one. A layer of a tree is
+// one compression per node whatever the launch shape; what this saves is a launch (and its drain and refill of the whole
+// GPU) per layer, for the layers between the leaves and the last ten, which merkle_top_kernel builds.
+constexpr int MERKLE_LEVELS_MAX = 9;
+struct MerkleLevelsArgs {
+    const uint32_t* children;             // 2^child_log hashes
+    uint32_t* out[MERKLE_LEVELS_MAX + 1];  // out[j]: the layer j levels above the children (2^(child_log - j) hashes), j = 1..levels
+};
+__global__ void __launch_bounds__(256) merkle_levels_kernel(MerkleLevelsArgs a, int levels, int m31_out) {
+    __shared__ uint32_t sh[2][256][8];
+    const size_t cta = blockIdx.x;
+    uint32_t h[8], m[16];
+    {
+        blake2s_init(h);
+        const uint4* p = reinterpret_cast<const uint4*>(a.children + 16 * (cta * 256 + threadIdx.x));
+        uint4 x0 = p[0], x1 = p[1], x2 = p[2], x3 = p[3];
+        m[0] = x0.x; m[1] = x0.y; m[2] = x0.z; m[3] = x0.w; m[4] = x1.x; m[5] = x1.y; m[6] = x1.z; m[7] = x1.w;
+        m[8] = x2.x; m[9] = x2.y; m[10] = x2.z; m[11] = x2.w; m[12] = x3.x; m[13] = x3.y; m[14] = x3.z; m[15] = x3.w;
+        blake2s_compress(h, m, 64u, true);
+#pragma unroll
+        for (int k = 0; k < 8; k++) { h[k] = m31_out ? reduce_word_m31(h[k]) : h[k]; sh[1][threadIdx.x][k] = h[k]; }
+        store_hash(a.out[1], cta * 256 + threadIdx.x, h, false);
+    }
+    for (int j = 2; j <= levels; j++) {
         __syncthreads();
+        const uint32_t n = 512u >> j;  // nodes of this level in the CTA
+        if (threadIdx.x < n) {
+            const uint32_t(*src)[8] = sh[(j - 1) & 1];
+            blake2s_init(h);
+#pragma unroll
+            for (int k = 0; k < 8; k++) { m[k] = src[2 * threadIdx.x][k]; m[8 + k] = src[2 * threadIdx.x + 1][k]; }
+            blake2s_compress(h, m, 64u, true);
+#pragma unroll
+            for (int k = 0; k < 8; k++) { h[k] = m31_out ? reduce_word_m31(h[k]) : h[k]; sh[j & 1][threadIdx.x][k] = h[k]; }
+            store_hash(a.out[j], cta * n + threadIdx.x, h, false);
+        }
     }
 }
 
@@ -176,9 +199,8 @@ __global__ void __launch_bounds__(512) merkle_top_kernel(MerkleTopArgs a, int to
 // mix_root is H(digest || root) (core/vcs/blake2_merkle.rs:53-58); draw_secure_felt hashes
 // digest || n_draws (LE) || 0x00 and retries while a word is >= 2p (core/channel/blake2s.rs:34-52,
 // 95-120); every digest word is reduced mod p.
-__global__ void channel_mix_root_draw_kernel(uint32_t* __restrict__ chan, const uint32_t* __restrict__ root,
-                                             uint32_t* __restrict__ alpha_out, uint32_t* __restrict__ root_copy) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+__device__ __forceinline__ void channel_mix_root_draw(uint32_t* __restrict__ chan, const uint32_t* root,
+                                                      uint32_t* __restrict__ alpha_out, uint32_t* __restrict__ root_copy) {
     uint32_t h[8], m[16];
     blake2s_init(h);
 #pragma unroll
@@ -202,15 +224,55 @@ __global__ void channel_mix_root_draw_kernel(uint32_t* __restrict__ chan, const 
         for (int k = 0; k < 8; k++) { u[k] = reduce_word_m31(h[k]); ok = ok && u[k] < 2u * P; }
         if (ok) break;
     }
+    if (root_copy) {
+#pragma unroll
+        for (int k = 0; k < 8; k++) root_copy[k] = root[k];
+    }
 #pragma unroll
     for (int k = 0; k < 8; k++) chan[k] = digest[k];
     chan[8] = n_draws;
 #pragma unroll
     for (int k = 0; k < 4; k++) alpha_out[k] = u[k] >= P ? u[k] - P : u[k];
-    if (root_copy) {
+}
+__global__ void channel_mix_root_draw_kernel(uint32_t* __restrict__ chan, const uint32_t* __restrict__ root,
+                                             uint32_t* __restrict__ alpha_out, uint32_t* __restrict__ root_copy) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    channel_mix_root_draw(chan, root, alpha_out, root_copy);
+}
+
+// The last (at most ten) layers of a tree in one CTA. Every level is written to its layer array and kept in shared memory
+// for the next one (a level read back from global memory costs an L2 round trip on top of the compression; ten levels are a
+// chain of ten dependent hashes either way). When `chan` is given, the thread that wrote the root goes on with the channel
+// step of a FRI layer (mix the root, draw the folding challenge), which would otherwise be a launch of its own.
+// (Spreading a compression of the upper levels over four lanes, one G function each, was tried here and is slower: 35 us per
+// tree top against 20: the per-lane message schedule becomes divergent constant-memory reads and the state rotation shuffles
+// cost more than the shorter dependency chain saves.)
+__global__ void __launch_bounds__(512) merkle_top_kernel(MerkleTopArgs a, int top_log, int m31_out, uint32_t* __restrict__ chan,
+                                                         uint32_t* __restrict__ alpha_out, uint32_t* __restrict__ root_copy) {
+    __shared__ uint32_t sh[2][512][8];
+    for (int lg = top_log - 1; lg >= 0; lg--) {
+        const bool from_global = lg == top_log - 1;
+        const uint32_t(*src)[8] = sh[(lg + 1) & 1];
+        for (uint32_t i = threadIdx.x; i < (1u << lg); i += blockDim.x) {
+            uint32_t h[8], m[16];
+            blake2s_init(h);
+            if (from_global) {
+                const uint4* p = reinterpret_cast<const uint4*>(a.layer[lg + 1] + 16 * (size_t)i);
+                uint4 x0 = p[0], x1 = p[1], x2 = p[2], x3 = p[3];
+                m[0] = x0.x; m[1] = x0.y; m[2] = x0.z; m[3] = x0.w; m[4] = x1.x; m[5] = x1.y; m[6] = x1.z; m[7] = x1.w;
+                m[8] = x2.x; m[9] = x2.y; m[10] = x2.z; m[11] = x2.w; m[12] = x3.x; m[13] = x3.y; m[14] = x3.z; m[15] = x3.w;
+            } else {
 #pragma unroll
-        for (int k = 0; k < 8; k++) root_copy[k] = root[k];
+                for (int k = 0; k < 8; k++) { m[k] = src[2 * i][k]; m[8 + k] = src[2 * i + 1][k]; }
+            }
+            blake2s_compress(h, m, 64u, true);
+#pragma unroll
+            for (int k = 0; k < 8; k++) { h[k] = m31_out ? reduce_word_m31(h[k]) : h[k]; sh[lg & 1][i][k] = h[k]; }
+            store_hash(a.layer[lg], i, h, false);
+        }
+        __syncthreads();
     }
+    if (chan && threadIdx.x == 0) channel_mix_root_draw(chan, sh[0][0], alpha_out, root_copy);
 }
 
 // Grind: thread `lo` tests nonce (hi << 32) | lo; the minimum passing lo is kept.
@@ -281,7 +343,35 @@ int zkb_merkle_leaves_partial(zkb_ctx* ctx, int log_size, const uint32_t* const*
     return ZKB_OK;
 }
 
+int zkb_merkle_levels(zkb_ctx* ctx, int child_log, const uint32_t* children, int levels, uint32_t* const* out_layers, int m31_out) {
+    if (!ctx) return ZKB_EINVAL;
+    ZKB_CHECK_ARG(ctx, children != nullptr && out_layers != nullptr && ((uintptr_t)children & 15) == 0);
+    ZKB_CHECK_ARG(ctx, levels >= 1 && levels <= MERKLE_LEVELS_MAX && child_log >= 9 && child_log <= 31 && child_log - levels >= 0);
+    MerkleLevelsArgs a{};
+    a.children = children;
+    for (int j = 1; j <= levels; j++) {
+        ZKB_CHECK_ARG(ctx, out_layers[j - 1] != nullptr && ((uintptr_t)out_layers[j - 1] & 15) == 0);
+        a.out[j] = out_layers[j - 1];
+    }
+    DeviceGuard g(ctx);
+    ProfScope prof(ctx, "merkle_levels_kernel");
+    merkle_levels_kernel<<<1u << (child_log - 9), 256, 0, ctx->stream>>>(a, levels, m31_out);
+    ZKB_LAUNCH_CHECK(ctx);
+    return ZKB_OK;
+}
+
+static int merkle_top_impl(zkb_ctx* ctx, int top_log, const uint32_t* top_layer, uint32_t* const* lower_layers, int m31_out, uint32_t* d_chan,
+                           uint32_t* d_alpha, uint32_t* d_root_copy);
 int zkb_merkle_top(zkb_ctx* ctx, int top_log, const uint32_t* top_layer, uint32_t* const* lower_layers, int m31_out) {
+    return merkle_top_impl(ctx, top_log, top_layer, lower_layers, m31_out, nullptr, nullptr, nullptr);
+}
+int zkb_merkle_top_channel(zkb_ctx* ctx, int top_log, const uint32_t* top_layer, uint32_t* const* lower_layers, int m31_out, uint32_t* d_chan,
+                           uint32_t* d_alpha, uint32_t* d_root_copy) {
+    if (ctx && (!d_chan || !d_alpha || top_log < 1)) return zk::set_error(ctx, ZKB_EINVAL, "zkb_merkle_top_channel: needs a channel, a challenge slot and at least one layer to build");
+    return merkle_top_impl(ctx, top_log, top_layer, lower_layers, m31_out, d_chan, d_alpha, d_root_copy);
+}
+static int merkle_top_impl(zkb_ctx* ctx, int top_log, const uint32_t* top_layer, uint32_t* const* lower_layers, int m31_out, uint32_t* d_chan,
+                           uint32_t* d_alpha, uint32_t* d_root_copy) {
     if (!ctx) return ZKB_EINVAL;
     ZKB_CHECK_ARG(ctx, top_log >= 0 && top_log <= MERKLE_TOP_MAX_LOG && top_layer != nullptr && ((uintptr_t)top_layer & 15) == 0);
     if (top_log == 0) return ZKB_OK;
@@ -294,7 +384,8 @@ int zkb_merkle_top(zkb_ctx* ctx, int top_log, const uint32_t* top_layer, uint32_
     }
     DeviceGuard g(ctx);
     ProfScope prof(ctx, "merkle_top_kernel");
-    merkle_top_kernel<<<1, top_log >= 10 ? 512 : (top_log >= 6 ? 1 << (top_log - 1) : 32), 0, ctx->stream>>>(a, top_log, m31_out);
+    merkle_top_kernel<<<1, top_log >= 10 ? 512 : (top_log >= 6 ? 1 << (top_log - 1) : 32), 0, ctx->stream>>>(a, top_log, m31_out, d_chan, d_alpha,
+                                                                                                              d_root_copy);
     ZKB_LAUNCH_CHECK(ctx);
     return ZKB_OK;
 }

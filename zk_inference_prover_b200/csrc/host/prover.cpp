@@ -145,7 +145,18 @@ struct MerkleProver {
     size_t n_columns = 0;
 
     // `leaves`, when given, is the already hashed largest layer (see zkb_merkle_leaves_partial).
-    static MerkleProver commit(const Device& d, const std::vector<const BaseColumn*>& columns, HashColumn* leaves = nullptr) {  // :39-64
+    // `chan_step`, when given, is a FRI layer's channel step (channel state, challenge slot, root copy; device addresses) to run
+    // in the launch that builds the root; *chan_done says whether it ran (a tree of one node has no such launch).
+    struct ChanStep { uint32_t *chan, *alpha, *root_copy; };
+    static MerkleProver commit(const Device& d, const std::vector<const BaseColumn*>& columns, HashColumn* leaves = nullptr,
+                               const ChanStep* chan_step = nullptr, bool* chan_done = nullptr) {  // :39-64
+        if (chan_done) *chan_done = false;
+        auto top = [&](uint32_t log, uint32_t* top_layer, uint32_t** lower) {
+            if (chan_step && log >= 1) {
+                d.check(zkb_merkle_top_channel(d.ctx(), (int)log, top_layer, lower, 1, chan_step->chan, chan_step->alpha, chan_step->root_copy));
+                if (chan_done) *chan_done = true;
+            } else d.check(zkb_merkle_top(d.ctx(), (int)log, top_layer, lower, 1));
+        };
         MerkleProver mp;
         if (columns.empty()) {
             mp.layers.push_back(B200Backend::commit_on_layer(d, 0, nullptr, {}));
@@ -168,7 +179,23 @@ struct MerkleProver {
                 // no columns left below: the rest of the tree is nodes only, built in one launch
                 std::vector<uint32_t*> lower;
                 for (uint32_t k = 0; k < log; k++) { mp.layers[k] = HashColumn(d, (size_t)8 << k); lower.push_back(mp.layers[k].ptr()); }
-                d.check(zkb_merkle_top(d.ctx(), (int)log, mp.layers[log].ptr(), lower.data(), 1));
+                top(log, mp.layers[log].ptr(), lower.data());
+                break;
+            }
+            // The layers below this one that hold no column (down to the next layer that has one, or to the last ten, which
+            // the launch above builds): up to nine of them per launch.
+            const uint32_t floor_log = pos == sorted.size() ? 10u : sorted[pos]->log_size() + 1;
+            while (log > floor_log && log >= 9) {
+                const uint32_t levels = std::min<uint32_t>(9, log - floor_log);
+                std::vector<uint32_t*> outs;
+                for (uint32_t j = 1; j <= levels; j++) { mp.layers[log - j] = HashColumn(d, (size_t)8 << (log - j)); outs.push_back(mp.layers[log - j].ptr()); }
+                d.check(zkb_merkle_levels(d.ctx(), (int)log, mp.layers[log].ptr(), (int)levels, outs.data(), 1));
+                log -= levels;
+            }
+            if (log > 0 && log <= 10 && pos == sorted.size() && mp.layers[log - 1].len() == 0) {
+                std::vector<uint32_t*> lower;
+                for (uint32_t k = 0; k < log; k++) { mp.layers[k] = HashColumn(d, (size_t)8 << k); lower.push_back(mp.layers[k].ptr()); }
+                top(log, mp.layers[log].ptr(), lower.data());
                 break;
             }
         }
@@ -345,8 +372,10 @@ struct FriProver {
             for (int k = 0; k < 8; k++) st[k] = ch.digest()[k];
             st[8] = ch.n_draws();
             d.check(zkb_h2d(d.ctx(), chan, st, sizeof(st)));
-            fp.first_tree = MerkleProver::commit(d, column.refs());
-            d.check(zkb_channel_mix_root_draw(d.ctx(), chan, fp.first_tree.layers[0].ptr(), alphas, roots));
+            bool stepped = false;
+            MerkleProver::ChanStep step0{chan, alphas, roots};
+            fp.first_tree = MerkleProver::commit(d, column.refs(), nullptr, &step0, &stepped);
+            if (!stepped) d.check(zkb_channel_mix_root_draw(d.ctx(), chan, fp.first_tree.layers[0].ptr(), alphas, roots));
             // every fold but the last also hashes the leaves of the layer it produces: that layer is committed next
             HashColumn leaves;
             bool have_leaves = n_layers > 1 && first_log >= 3;
@@ -354,8 +383,9 @@ struct FriProver {
             for (size_t k = 1; k < n_layers; k++) {
                 Inner in{std::move(layer), {}, 1};
                 std::vector<const BaseColumn*> refs = in.eval.refs();
-                in.tree = MerkleProver::commit(d, refs, have_leaves ? &leaves : nullptr);
-                d.check(zkb_channel_mix_root_draw(d.ctx(), chan, in.tree.layers[0].ptr(), alphas + 4 * k, roots + 8 * k));
+                MerkleProver::ChanStep step{chan, alphas + 4 * k, roots + 8 * k};
+                in.tree = MerkleProver::commit(d, refs, have_leaves ? &leaves : nullptr, &step, &stepped);
+                if (!stepped) d.check(zkb_channel_mix_root_draw(d.ctx(), chan, in.tree.layers[0].ptr(), alphas + 4 * k, roots + 8 * k));
                 have_leaves = k + 1 < n_layers;
                 if (have_leaves) layer = B200Backend::fold_line(d, in.eval, alphas + 4 * k, leaves);
                 else layer = B200Backend::fold_line(d, in.eval, alphas + 4 * k);
@@ -1278,7 +1308,7 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
 struct ShardSession {
     zkb_ctx* ctx;
     Device dev;
-    int rank, world, log_g, ncols, ncl;
+    int rank, world, log_g, ncols, ncl, n_chunks = 1;
     uint32_t log_n, log_out, log_local;
     size_t N, R;
     PcsConfig config;
@@ -1354,34 +1384,55 @@ int zkb_shard_pcs_end(zkb_shard_pcs* h) {
     return ZKB_OK;
 }
 
-int zkb_shard_pcs_extend(zkb_shard_pcs* h, uint32_t* const* d_cols, uint32_t** d_send, uint32_t** d_rows) {
-    if (!h || !d_cols || !d_send || !d_rows) return ZKB_EINVAL;
+int zkb_shard_pcs_extend_begin(zkb_shard_pcs* h, uint32_t* const* d_cols, int n_chunks) {
+    if (!h || !d_cols) return ZKB_EINVAL;
     ShardSession& s = h->s;
+    if (n_chunks < 1 || s.ncl % n_chunks) return zk_set_error_public(s.ctx, ZKB_EINVAL, "zkb_shard_pcs_extend_begin: the chunk count must divide the local column count");
     return shard_guard(s.ctx, [&] {
         std::vector<BaseColumn*> cols;
-        std::vector<const uint32_t*> src;
-        std::vector<uint32_t*> dst;
         s.coeffs.clear();
         for (int c = 0; c < s.ncl; c++) s.coeffs.push_back(BaseColumn::view(s.dev, d_cols[c], (size_t)1 << s.log_n));
         for (auto& c : s.coeffs) cols.push_back(&c);
         B200Backend::interpolate_columns(s.dev, cols);
-        s.evals = BaseColumn(s.dev, (size_t)s.ncl * s.N);  // [world][ncl][R]: block d is what rank d receives
-        s.rows = BaseColumn(s.dev, (size_t)s.ncols * s.R);
-        for (int c = 0; c < s.ncl; c++) src.push_back(s.coeffs[c].ptr());
+        s.n_chunks = n_chunks;
+        s.evals = BaseColumn(s.dev, (size_t)s.ncl * s.N);  // [chunk][world][ncl / chunks][R]: block d of a chunk is what rank d receives
+        s.rows = BaseColumn(s.dev, (size_t)s.ncols * s.R);  // [chunk][source rank][ncl / chunks][R]
+    });
+}
+
+int zkb_shard_pcs_extend_chunk(zkb_shard_pcs* h, int k, uint32_t** d_send, uint32_t** d_recv, size_t* words_per_peer) {
+    if (!h || !d_send || !d_recv || !words_per_peer) return ZKB_EINVAL;
+    ShardSession& s = h->s;
+    if (k < 0 || k >= s.n_chunks || s.coeffs.empty()) return zk_set_error_public(s.ctx, ZKB_EINVAL, "zkb_shard_pcs_extend_chunk: no such chunk");
+    return shard_guard(s.ctx, [&] {
+        const int cc = s.ncl / s.n_chunks;
+        std::vector<const uint32_t*> src;
+        std::vector<uint32_t*> dst;
+        uint32_t* send = s.evals.ptr() + (size_t)k * s.world * cc * s.R;
+        for (int j = 0; j < cc; j++) src.push_back(s.coeffs[k * cc + j].ptr());
         if (zk::lde_blocked_supported((int)s.log_n, (int)s.log_out, (int)s.log_local)) {
             // the transform's last pass writes every row block where the exchange sends it from: no repack
-            for (int c = 0; c < s.ncl; c++) dst.push_back(s.evals.ptr() + (size_t)c * s.R);
-            s.dev.check(zk::lde_cols_blocked(s.ctx, src.data(), s.ncl, (int)s.log_n, dst.data(), (int)s.log_out, (int)s.log_local,
-                                             (uint32_t)((size_t)s.ncl * s.R)));
+            for (int j = 0; j < cc; j++) dst.push_back(send + (size_t)j * s.R);
+            s.dev.check(zk::lde_cols_blocked(s.ctx, src.data(), cc, (int)s.log_n, dst.data(), (int)s.log_out, (int)s.log_local,
+                                             (uint32_t)((size_t)cc * s.R)));
         } else {
-            BaseColumn plain(s.dev, (size_t)s.ncl * s.N);
-            for (int c = 0; c < s.ncl; c++) dst.push_back(plain.ptr() + (size_t)c * s.N);
-            s.dev.check(zkb_lde_cols(s.ctx, src.data(), s.ncl, (int)s.log_n, dst.data(), (int)s.log_out));
-            s.dev.check(zk::repack_row_blocks(s.ctx, plain.ptr(), s.evals.ptr(), s.ncl, (int)s.log_out, (int)s.log_local));
+            BaseColumn plain(s.dev, (size_t)cc * s.N);
+            for (int j = 0; j < cc; j++) dst.push_back(plain.ptr() + (size_t)j * s.N);
+            s.dev.check(zkb_lde_cols(s.ctx, src.data(), cc, (int)s.log_n, dst.data(), (int)s.log_out));
+            s.dev.check(zk::repack_row_blocks(s.ctx, plain.ptr(), send, cc, (int)s.log_out, (int)s.log_local));
         }
-        *d_send = s.evals.ptr();
-        *d_rows = s.rows.ptr();
+        *d_send = send;
+        *d_recv = s.rows.ptr() + (size_t)k * s.world * cc * s.R;
+        *words_per_peer = (size_t)cc * s.R;
     });
+}
+
+int zkb_shard_pcs_extend(zkb_shard_pcs* h, uint32_t* const* d_cols, uint32_t** d_send, uint32_t** d_rows) {
+    if (!h || !d_cols || !d_send || !d_rows) return ZKB_EINVAL;
+    int rc = zkb_shard_pcs_extend_begin(h, d_cols, 1);
+    if (rc) return rc;
+    size_t words = 0;
+    return zkb_shard_pcs_extend_chunk(h, 0, d_send, d_rows, &words);
 }
 
 int zkb_shard_pcs_subtree(zkb_shard_pcs* h, uint32_t** d_root, uint32_t** d_roots) {
@@ -1390,7 +1441,12 @@ int zkb_shard_pcs_subtree(zkb_shard_pcs* h, uint32_t** d_root, uint32_t** d_root
     return shard_guard(s.ctx, [&] {
         s.evals = BaseColumn();  // the column shards have been sent
         s.row_cols.clear();
-        for (int c = 0; c < s.ncols; c++) s.row_cols.push_back(BaseColumn::view(s.dev, s.rows.ptr() + (size_t)c * s.R, s.R));
+        // global column c = source rank * ncl + chunk * cc + j lies in block [chunk][source rank] of the received rows
+        const int cc = s.ncl / s.n_chunks;
+        for (int c = 0; c < s.ncols; c++) {
+            const int src = c / s.ncl, k = (c % s.ncl) / cc, j = c % cc;
+            s.row_cols.push_back(BaseColumn::view(s.dev, s.rows.ptr() + ((size_t)(k * s.world + src) * cc + j) * s.R, s.R));
+        }
         std::vector<const BaseColumn*> refs;
         for (auto& c : s.row_cols) refs.push_back(&c);
         s.subtree = MerkleProver::commit(s.dev, refs);

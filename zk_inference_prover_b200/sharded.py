@@ -169,6 +169,7 @@ class Exchange:
         self.mem, self.device, self.group = mem, device, group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.nccl = dist.get_backend(group) == "nccl"
+        self._pending = []
 
     def _dev(self, ptr, words):
         return torch.as_tensor(_Alias(ptr, words), device=self.device)
@@ -180,12 +181,17 @@ class Exchange:
             return contextlib.nullcontext()
         return torch.cuda.stream(torch.cuda.ExternalStream(self.mem.stream(), device=self.device))
 
-    def all_to_all(self, send_ptr, recv_ptr, words_per_peer):
-        """Block d of `send` ([world][words_per_peer]) becomes block `rank` of rank d's `recv`."""
+    def all_to_all(self, send_ptr, recv_ptr, words_per_peer, defer=False):
+        """Block d of `send` ([world][words_per_peer]) becomes block `rank` of rank d's `recv`. With defer (nccl), the
+        collective starts after what the context's stream holds so far and runs beside what is enqueued after it; the
+        stream waits for it only at flush()."""
         G, me = self.world, self.rank
         if self.nccl:
             with self._stream():
-                dist.all_to_all_single(self._dev(recv_ptr, G * words_per_peer), self._dev(send_ptr, G * words_per_peer), group=self.group)
+                work = dist.all_to_all_single(self._dev(recv_ptr, G * words_per_peer), self._dev(send_ptr, G * words_per_peer),
+                                              group=self.group, async_op=defer)
+            if defer:
+                self._pending.append(work)
             return
         sd = torch.from_numpy(self.mem.read(send_ptr, G * words_per_peer).view("int32")).view(G, words_per_peer)
         rv = torch.empty_like(sd)
@@ -200,6 +206,14 @@ class Exchange:
                 dist.recv(rv[peer], peer, group=self.group)
                 dist.send(sd[peer], peer, group=self.group)
         self.mem.write(recv_ptr, rv.numpy().view("uint32").reshape(-1))
+
+    def flush(self):
+        """Orders the context's stream after every deferred collective (a stream-side wait, the host does not block)."""
+        if self._pending:
+            with self._stream():
+                for work in self._pending:
+                    work.wait()
+            self._pending = []
 
     def all_gather_device(self, src_ptr, dst_ptr, words):
         """dst[r * words ...] <- src of rank r."""
@@ -276,8 +290,20 @@ def sharded_pcs_prove(session, exchange, col_ptrs, timings=None):
             marks.append(name)
 
     lap("start")
-    send, rows = s.extend(col_ptrs)
-    x.all_to_all(send, rows, s.ncl * s.R)
+    # By chunks of columns, so that a chunk travels while the next one is extended (sessions without the chunked stage, as
+    # the stand-in of the CPU tests, take the whole shard at once).
+    n_chunks = 1
+    if hasattr(s, "extend_begin"):
+        n_chunks = next((c for c in (4, 2) if s.ncl % c == 0), 1)
+    if n_chunks > 1:
+        s.extend_begin(col_ptrs, n_chunks)
+        for k in range(n_chunks):
+            send, recv, words_per_peer = s.extend_chunk(k)
+            x.all_to_all(send, recv, words_per_peer, defer=True)
+        x.flush()
+    else:
+        send, rows = s.extend(col_ptrs)
+        x.all_to_all(send, rows, s.ncl * s.R)
     lap("interpolate_extend_exchange")
     root, roots = s.subtree()
     x.all_gather_device(root, roots, 8)
