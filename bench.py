@@ -388,7 +388,8 @@ def run_ours(args, rank, world, local_rank):
         del cols_b, sec, half, quarter
     e2e_ms, words_e2e = timed(True, False)
     assert len(words_dev) == len(words_e2e) and (words_dev == words_e2e).all(), "resident and end-to-end legs disagree"
-    extras = {} if args.no_extras else extra_legs(args, z, ctx, dist, rank, world, local_rank, words_dev, dev_ms / args.steps, h_addr, d_work)
+    commit_ms = sum(phases.get(k, 0.0) for k in ("interpolate", "extend", "merkle")) / args.steps
+    extras = {} if args.no_extras else extra_legs(args, z, ctx, dist, rank, world, local_rank, words_dev, dev_ms / args.steps, h_addr, d_work, commit_ms)
 
     if dist is not None:
         import torch
@@ -480,7 +481,7 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-def extra_legs(args, z, ctx, dist, rank, world, local_rank, words_single, single_ms, h_addr, d_work):
+def extra_legs(args, z, ctx, dist, rank, world, local_rank, words_single, single_ms, h_addr, d_work, single_commit_ms=0.0):
     """Legs beside the headline, on the same GPUs in the same run, so that the driver's one line per N also carries: what the
     host can deliver to the ranks at once (reads the end-to-end scaling against), ONE proof sharded over all ranks (strong
     scaling of the proof itself; its words must equal the single-GPU proof), and BASELINE.json's first metric, the proof
@@ -541,8 +542,15 @@ def extra_legs(args, z, ctx, dist, rank, world, local_rank, words_single, single
             sess.close()
             if it >= 2:
                 times.append(dt)
+        direct = x._peer is not None
+        x.peer_close()
         ms = allmax(sum(times) / len(times))
         same = bool(len(words) == len(words_single) and (words == words_single).all())
+        commit_ms = allmax((stages.get("interpolate_extend_exchange", 0.0) + stages.get("merkle_subtree_roots", 0.0)) / 3)
+        # the commitment part on its own (columns -> exchange -> subtrees -> root), against the same phases of the one-GPU proof
+        out["sharded_commit"] = {"ms": commit_ms, "single_gpu_ms": single_commit_ms, "strong_efficiency": single_commit_ms / commit_ms / world,
+                                 "root_equals_single_gpu": same, "exchange": "direct copies between the GPUs (copy engines)" if direct else "all-to-all collective",
+                                 "timer": "CUDA events on each rank's stream, slowest rank; the proof words (root included) are compared below"}
         out["sharded_proof"] = {"ms": ms, "cells_per_s": ncols * n / (ms * 1e-3), "single_gpu_ms": single_ms,
                                 "strong_efficiency": single_ms / ms / world, "equals_single_gpu_proof": same,
                                 "device_ms_per_stage_rank0": {k: v / 3 for k, v in stages.items()},

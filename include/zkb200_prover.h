@@ -142,6 +142,10 @@ int zkb_shard_pcs_extend(zkb_shard_pcs* s, uint32_t* const* d_cols, uint32_t** d
  * from rank s) and the words per peer. Every launch is stream-ordered: the caller starts chunk k's all-to-all after what has
  * been enqueued so far and only has to order the subtree stage after the last one. zkb_shard_pcs_extend is begin with one
  * chunk followed by chunk 0. */
+/* Optional, before extend_begin: the buffer the row shards are received into (ncols_total x N / world words), e.g. one from
+ * zkb_peer_buffer_alloc that the other ranks copy into directly; NULL (the default) lets the session allocate it. The
+ * caller keeps the buffer alive until zkb_shard_pcs_end. */
+int zkb_shard_pcs_set_rows(zkb_shard_pcs* s, uint32_t* d_rows);
 int zkb_shard_pcs_extend_begin(zkb_shard_pcs* s, uint32_t* const* d_cols, int n_chunks);
 int zkb_shard_pcs_extend_chunk(zkb_shard_pcs* s, int k, uint32_t** d_send, uint32_t** d_recv, size_t* words_per_peer);
 int zkb_shard_pcs_subtree(zkb_shard_pcs* s, uint32_t** d_root, uint32_t** d_roots);

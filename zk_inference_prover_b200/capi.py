@@ -13,7 +13,8 @@ GKR_GRAND_PRODUCT, GKR_LOGUP_GENERIC, GKR_LOGUP_MULTIPLICITIES, GKR_LOGUP_SINGLE
 EXPORTED_SYMBOLS = [
     "zkb_init", "zkb_destroy", "zkb_last_error", "zkb_sync", "zkb_get_stream", "zkb_max_log_size",
     "zkb_event_record", "zkb_event_elapsed_ms", "zkb_profile_begin", "zkb_profile_end", "zkb_fft_arith_ceiling",
-    "zkb_malloc", "zkb_free", "zkb_memset_zero", "zkb_h2d", "zkb_d2h", "zkb_h2d_async", "zkb_d2h_async", "zkb_h2d_overlapped", "zkb_wait_fence", "zkb_d2d",
+    "zkb_malloc", "zkb_free", "zkb_memset_zero", "zkb_h2d", "zkb_d2h", "zkb_h2d_async", "zkb_d2h_async", "zkb_h2d_overlapped", "zkb_wait_fence", "zkb_peer_buffer_alloc", "zkb_peer_buffer_free", "zkb_peer_buffer_open",
+    "zkb_peer_buffer_close", "zkb_copy_to_peer", "zkb_peer_copies_wait", "zkb_d2d",
     "zkb_host_alloc_pinned", "zkb_host_free_pinned", "zkb_gather_multi", "zkb_gather_hashes", "zkb_gather_words", "zkb_twiddles_d2h",
     "zkb_ifft_cols", "zkb_lde_cols", "zkb_eval_at_point_cols", "zkb_barycentric_weights", "zkb_barycentric_eval_at_point", "zkb_eval_at_point_by_folding", "zkb_fri_decompose", "zkb_bit_reverse_m31", "zkb_bit_reverse_qm31",
     "zkb_merkle_layer", "zkb_merkle_leaves_partial", "zkb_merkle_levels", "zkb_merkle_top", "zkb_merkle_top_channel", "zkb_fold_line_dalpha", "zkb_fold_circle_into_line_dalpha", "zkb_channel_mix_root_draw", "zkb_fold_line_dalpha_leaves", "zkb_fold_circle_into_line_dalpha_leaves", "zkb_fold_circle_into_line", "zkb_fold_line", "zkb_quot_numerators", "zkb_quot_combine", "zkb_quot_combine_rows",
@@ -24,7 +25,7 @@ EXPORTED_SYMBOLS = [
 ]
 # Every symbol include/zkb200_prover.h declares.
 PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_stark_prove_device", "zkb_stark_prove_host", "zkb_stark_prove_multi_device", "zkb_stark_prove_multi_host", "zkb_gkr_prove_device",
-                  "zkb_shard_pcs_begin", "zkb_shard_pcs_extend", "zkb_shard_pcs_extend_begin", "zkb_shard_pcs_extend_chunk", "zkb_shard_pcs_subtree", "zkb_shard_pcs_sample", "zkb_shard_pcs_quotients",
+                  "zkb_shard_pcs_begin", "zkb_shard_pcs_extend", "zkb_shard_pcs_set_rows", "zkb_shard_pcs_extend_begin", "zkb_shard_pcs_extend_chunk", "zkb_shard_pcs_subtree", "zkb_shard_pcs_sample", "zkb_shard_pcs_quotients",
                   "zkb_shard_pcs_fri_and_decommit", "zkb_shard_pcs_finish", "zkb_shard_pcs_end"]
 # Every symbol include/zkb200_air.h declares.
 AIR_SYMBOLS = ["zkb_air_compile", "zkb_air_analyze", "zkb_air_free", "zkb_air_specialize", "zkb_air_select", "zkb_air_get_stats", "zkb_constraint_quotients", "zkb_constraint_denom_inv"]
@@ -145,6 +146,10 @@ class ShardPcsSession:
         e, r = C.c_void_p(), C.c_void_p()
         self.ctx._check(self.ctx.lib.zkb_shard_pcs_extend(self.h, _ptr_array(col_ptrs), C.byref(e), C.byref(r)))
         return e.value, r.value
+
+    def set_rows(self, rows_ptr):
+        """The buffer the row shards are received into (ncols x R words); must outlive the session."""
+        self.ctx._check(self.ctx.lib.zkb_shard_pcs_set_rows(self.h, C.c_void_p(rows_ptr)))
 
     def extend_begin(self, col_ptrs, n_chunks):
         """The extend stage by chunks of columns (n_chunks must divide ncl): interpolates; then call extend_chunk(k) for every k."""
@@ -412,6 +417,30 @@ class Context:
 
     def d2h_async(self, host_addr, dptr, nbytes):
         self._check(self.lib.zkb_d2h_async(self.h, C.c_void_p(host_addr), C.c_void_p(dptr), C.c_size_t(nbytes)))
+
+    def peer_buffer_alloc(self, nbytes):
+        """-> (device address, 64-byte handle as uint8 array)."""
+        p, h = C.c_void_p(), (C.c_ubyte * 64)()
+        self._check(self.lib.zkb_peer_buffer_alloc(self.h, C.c_size_t(nbytes), C.byref(p), h))
+        return p.value, np.frombuffer(bytes(h), np.uint8).copy()
+
+    def peer_buffer_free(self, ptr):
+        self._check(self.lib.zkb_peer_buffer_free(self.h, C.c_void_p(ptr)))
+
+    def peer_buffer_open(self, handle):
+        p = C.c_void_p()
+        hb = (C.c_ubyte * 64)(*[int(b) for b in handle])
+        self._check(self.lib.zkb_peer_buffer_open(self.h, hb, C.byref(p)))
+        return p.value
+
+    def peer_buffer_close(self, ptr):
+        self._check(self.lib.zkb_peer_buffer_close(self.h, C.c_void_p(ptr)))
+
+    def copy_to_peer(self, dst, src, nbytes):
+        self._check(self.lib.zkb_copy_to_peer(self.h, C.c_void_p(dst), C.c_void_p(src), C.c_size_t(nbytes)))
+
+    def peer_copies_wait(self):
+        self._check(self.lib.zkb_peer_copies_wait(self.h))
 
     def d2d(self, dst, src, nbytes):
         self._check(self.lib.zkb_d2d(self.h, C.c_void_p(dst), C.c_void_p(src), C.c_size_t(nbytes)))

@@ -336,6 +336,70 @@ int zkb_wait_fence(zkb_ctx* ctx, int fence) {
     return ZKB_OK;
 }
 
+// ---- buffers another process's GPU can write into (one process per GPU on one host) -----------------------------
+// The stream-ordered pool's memory can not be shared between processes, so these come from cudaMalloc. A peer opens the
+// handle and copies into the buffer with the copy engines (zkb_copy_to_peer): no SM is used, which is what lets the
+// exchange of a sharded commitment run under the transform kernels (a collective's copy kernels wait for SMs the
+// persistent transform passes hold).
+int zkb_peer_buffer_alloc(zkb_ctx* ctx, size_t bytes, void** dptr, unsigned char handle[64]) {
+    if (!ctx || !dptr || !handle || bytes == 0) return ZKB_EINVAL;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    DeviceGuard g(ctx);
+    *dptr = nullptr;
+    ZKB_CUDA(ctx, cudaMalloc(dptr, bytes));
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, *dptr);
+    if (e != cudaSuccess) {
+        cudaFree(*dptr);
+        *dptr = nullptr;
+        return set_error(ctx, ZKB_ECUDA, "zkb_peer_buffer_alloc: %s", cudaGetErrorString(e));
+    }
+    memcpy(handle, &h, 64);
+    return ZKB_OK;
+}
+int zkb_peer_buffer_free(zkb_ctx* ctx, void* dptr) {
+    if (!ctx) return ZKB_EINVAL;
+    if (!dptr) return ZKB_OK;
+    DeviceGuard g(ctx);
+    ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    ZKB_CUDA(ctx, cudaFree(dptr));
+    return ZKB_OK;
+}
+int zkb_peer_buffer_open(zkb_ctx* ctx, const unsigned char handle[64], void** peer_ptr) {
+    if (!ctx || !handle || !peer_ptr) return ZKB_EINVAL;
+    DeviceGuard g(ctx);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    *peer_ptr = nullptr;
+    ZKB_CUDA(ctx, cudaIpcOpenMemHandle(peer_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return ZKB_OK;
+}
+int zkb_peer_buffer_close(zkb_ctx* ctx, void* peer_ptr) {
+    if (!ctx) return ZKB_EINVAL;
+    if (!peer_ptr) return ZKB_OK;
+    DeviceGuard g(ctx);
+    if (ctx->copy_stream) ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->copy_stream));
+    ZKB_CUDA(ctx, cudaIpcCloseMemHandle(peer_ptr));
+    return ZKB_OK;
+}
+int zkb_copy_to_peer(zkb_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (!ctx || !dst || !src) return ZKB_EINVAL;
+    DeviceGuard g(ctx);
+    if (!ctx->copy_stream) ZKB_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+    if (!ctx->copy_gate) ZKB_CUDA(ctx, cudaEventCreateWithFlags(&ctx->copy_gate, cudaEventDisableTiming));
+    // after everything enqueued on the compute stream so far (the source has just been written there)
+    ZKB_CUDA(ctx, cudaEventRecord(ctx->copy_gate, ctx->stream));
+    ZKB_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->copy_gate, 0));
+    if (bytes) ZKB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, ctx->copy_stream));
+    return ZKB_OK;
+}
+int zkb_peer_copies_wait(zkb_ctx* ctx) {
+    if (!ctx) return ZKB_EINVAL;
+    DeviceGuard g(ctx);
+    if (ctx->copy_stream) ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->copy_stream));
+    return ZKB_OK;
+}
+
 int zkb_d2h_async(zkb_ctx* ctx, void* h_pinned_dst, const void* dptr, size_t bytes) {
     if (!ctx) return ZKB_EINVAL;
     if (bytes == 0) return ZKB_OK;

@@ -1309,6 +1309,7 @@ struct ShardSession {
     zkb_ctx* ctx;
     Device dev;
     int rank, world, log_g, ncols, ncl, n_chunks = 1;
+    uint32_t* ext_rows = nullptr;
     uint32_t log_n, log_out, log_local;
     size_t N, R;
     PcsConfig config;
@@ -1384,6 +1385,12 @@ int zkb_shard_pcs_end(zkb_shard_pcs* h) {
     return ZKB_OK;
 }
 
+int zkb_shard_pcs_set_rows(zkb_shard_pcs* h, uint32_t* d_rows) {
+    if (!h) return ZKB_EINVAL;
+    h->s.ext_rows = d_rows;
+    return ZKB_OK;
+}
+
 int zkb_shard_pcs_extend_begin(zkb_shard_pcs* h, uint32_t* const* d_cols, int n_chunks) {
     if (!h || !d_cols) return ZKB_EINVAL;
     ShardSession& s = h->s;
@@ -1396,7 +1403,8 @@ int zkb_shard_pcs_extend_begin(zkb_shard_pcs* h, uint32_t* const* d_cols, int n_
         B200Backend::interpolate_columns(s.dev, cols);
         s.n_chunks = n_chunks;
         s.evals = BaseColumn(s.dev, (size_t)s.ncl * s.N);  // [chunk][world][ncl / chunks][R]: block d of a chunk is what rank d receives
-        s.rows = BaseColumn(s.dev, (size_t)s.ncols * s.R);  // [chunk][source rank][ncl / chunks][R]
+        // [chunk][source rank][ncl / chunks][R]; the caller's own buffer when it has given one (a buffer its peers can write)
+        s.rows = s.ext_rows ? BaseColumn::view(s.dev, s.ext_rows, (size_t)s.ncols * s.R) : BaseColumn(s.dev, (size_t)s.ncols * s.R);
     });
 }
 

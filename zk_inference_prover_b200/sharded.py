@@ -170,6 +170,7 @@ class Exchange:
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.nccl = dist.get_backend(group) == "nccl"
         self._pending = []
+        self._peer = None
 
     def _dev(self, ptr, words):
         return torch.as_tensor(_Alias(ptr, words), device=self.device)
@@ -180,6 +181,60 @@ class Exchange:
 
             return contextlib.nullcontext()
         return torch.cuda.stream(torch.cuda.ExternalStream(self.mem.stream(), device=self.device))
+
+    # ---- direct copies between the ranks' GPUs (one host): the receive buffers are shared between the processes and a
+    # rank writes its blocks into its peers' buffers with the copy engines, which need no SM and so run under kernels
+    def peer_setup(self, ctx, words):
+        """Collective: every rank allocates a receive buffer of `words` words its peers can write and opens the others'.
+        Returns False (and sets nothing up) when the ranks are not GPUs of one host under nccl."""
+        if self._peer is not None and self._peer["words"] >= words:
+            return True
+        if not self.nccl or not hasattr(ctx, "peer_buffer_alloc"):
+            return False
+        import socket
+
+        import numpy as np
+
+        self.peer_close()
+        host = np.frombuffer(socket.gethostname().encode()[:32].ljust(32, b"\0"), np.uint32).copy()
+        if len({bytes(h) for h in self.all_gather_host(host).reshape(self.world, -1)}) != 1:
+            return False
+        mine, handle = ctx.peer_buffer_alloc(words * 4)
+        handles = self.all_gather_host(handle.view(np.uint32)).reshape(self.world, 16).view(np.uint8)
+        ptrs = [mine if r == self.rank else ctx.peer_buffer_open(handles[r]) for r in range(self.world)]
+        self._peer = {"ctx": ctx, "words": words, "mine": mine, "ptrs": ptrs}
+        dist.barrier(group=self.group)
+        return True
+
+    def peer_close(self):
+        """Collective: releases the shared receive buffers."""
+        if self._peer is None:
+            return
+        p, self._peer = self._peer, None
+        p["ctx"].sync()
+        dist.barrier(group=self.group)  # nobody copies into a buffer that is about to go
+        for r, ptr in enumerate(p["ptrs"]):
+            if r != self.rank:
+                p["ctx"].peer_buffer_close(ptr)
+        dist.barrier(group=self.group)
+        p["ctx"].peer_buffer_free(p["mine"])
+
+    def peer_rows(self):
+        return self._peer["mine"]
+
+    def peer_all_to_all(self, send_ptr, recv_ptr, words_per_peer):
+        """Block d of `send` goes to the place of rank d's receive buffer that `recv_ptr` is in mine, block `rank`: enqueued on
+        the copy stream after what the compute stream holds so far; peer_finish() makes the data visible."""
+        p = self._peer
+        off = recv_ptr - p["mine"] + 4 * self.rank * words_per_peer
+        for k in range(self.world):
+            d = (self.rank + k) % self.world  # start with the local block, then a different peer on every rank
+            p["ctx"].copy_to_peer(p["ptrs"][d] + off, send_ptr + 4 * d * words_per_peer, 4 * words_per_peer)
+
+    def peer_finish(self):
+        """Waits for this rank's copies, then for everybody's: after it every rank's receive buffer is complete."""
+        self._peer["ctx"].peer_copies_wait()
+        dist.barrier(group=self.group)
 
     def all_to_all(self, send_ptr, recv_ptr, words_per_peer, defer=False):
         """Block d of `send` ([world][words_per_peer]) becomes block `rank` of rank d's `recv`. With defer (nccl), the
@@ -295,7 +350,17 @@ def sharded_pcs_prove(session, exchange, col_ptrs, timings=None):
     n_chunks = 1
     if hasattr(s, "extend_begin"):
         n_chunks = next((c for c in (4, 2) if s.ncl % c == 0), 1)
-    if n_chunks > 1:
+    peer = n_chunks >= 1 and hasattr(s, "set_rows") and hasattr(x, "peer_setup") and x.peer_setup(s.ctx, s.ncols * s.R)
+    if peer:
+        # the ranks write their blocks straight into each other's receive buffers with the copy engines, chunk by chunk
+        # under the transform of the next chunk (a collective's copy kernels would wait for the SMs the transform holds)
+        s.set_rows(x.peer_rows())
+        s.extend_begin(col_ptrs, n_chunks)
+        for k in range(n_chunks):
+            send, recv, words_per_peer = s.extend_chunk(k)
+            x.peer_all_to_all(send, recv, words_per_peer)
+        x.peer_finish()
+    elif n_chunks > 1:
         s.extend_begin(col_ptrs, n_chunks)
         for k in range(n_chunks):
             send, recv, words_per_peer = s.extend_chunk(k)
