@@ -93,16 +93,16 @@ int zkb_wait_fence(zkb_ctx* ctx, int fence);
 /* Buffers that another process's GPU on the same host can copy into (one process per GPU): alloc returns device
  * memory of this context's GPU (plain cudaMalloc: pool memory can not be shared) and a 64-byte handle to send to the
  * peers; a peer opens the handle (peer access is enabled on first use) and gets an address valid in ITS process.
- * zkb_copy_to_peer copies `bytes` from this GPU's `src` to `dst` (a peer address, or a local one) on the context's copy
- * stream with the copy engines, after everything enqueued on the compute stream so far; it does not block the host and
- * uses no SM, so it runs under kernels. zkb_peer_copies_wait blocks the host until this context's copies have landed; the
+ * zkb_copy_to_peer copies `bytes` from this GPU's `src` to `dst` (a peer address, or a local one) with the copy engines,
+ * after everything enqueued on the compute stream so far, on one of four copy streams (`lane` mod 4: copies on different
+ * lanes run side by side); it does not block the host and uses no SM, so it runs under kernels. zkb_peer_copies_wait blocks the host until this context's copies have landed; the
  * RECEIVER learns that its data is there from the caller (a barrier between the processes after every sender has waited).
  * close before the owner frees; free synchronises the compute stream. ZKB_ECUDA when the GPUs can not reach each other. */
 int zkb_peer_buffer_alloc(zkb_ctx* ctx, size_t bytes, void** dptr, unsigned char handle[64]);
 int zkb_peer_buffer_free(zkb_ctx* ctx, void* dptr);
 int zkb_peer_buffer_open(zkb_ctx* ctx, const unsigned char handle[64], void** peer_ptr);
 int zkb_peer_buffer_close(zkb_ctx* ctx, void* peer_ptr);
-int zkb_copy_to_peer(zkb_ctx* ctx, void* dst, const void* src, size_t bytes);
+int zkb_copy_to_peer(zkb_ctx* ctx, void* dst, const void* src, size_t bytes, int lane);
 int zkb_peer_copies_wait(zkb_ctx* ctx);
 int zkb_d2d(zkb_ctx* ctx, void* dst, const void* src, size_t bytes);
 int zkb_host_alloc_pinned(zkb_ctx* ctx, size_t bytes, void** h_ptr);

@@ -146,6 +146,11 @@ int zkb_shard_pcs_extend(zkb_shard_pcs* s, uint32_t* const* d_cols, uint32_t** d
  * zkb_peer_buffer_alloc that the other ranks copy into directly; NULL (the default) lets the session allocate it. The
  * caller keeps the buffer alive until zkb_shard_pcs_end. */
 int zkb_shard_pcs_set_rows(zkb_shard_pcs* s, uint32_t* d_rows);
+/* Optional, instead of set_rows: every rank's receive buffer as THIS process sees it (peer_rows[r] for rank r, opened with
+ * zkb_peer_buffer_open; peer_rows[rank] is this rank's own). Every chunk's blocks are then copied into the peers' buffers by
+ * the library right after the chunk's transform is enqueued (zkb_copy_to_peer), and the caller's part of the exchange is
+ * zkb_peer_copies_wait followed by a barrier between the ranks. NULL returns to a caller-side exchange. */
+int zkb_shard_pcs_set_peer_rows(zkb_shard_pcs* s, uint32_t* const* peer_rows);
 int zkb_shard_pcs_extend_begin(zkb_shard_pcs* s, uint32_t* const* d_cols, int n_chunks);
 int zkb_shard_pcs_extend_chunk(zkb_shard_pcs* s, int k, uint32_t** d_send, uint32_t** d_recv, size_t* words_per_peer);
 int zkb_shard_pcs_subtree(zkb_shard_pcs* s, uint32_t** d_root, uint32_t** d_roots);

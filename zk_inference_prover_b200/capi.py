@@ -25,7 +25,7 @@ EXPORTED_SYMBOLS = [
 ]
 # Every symbol include/zkb200_prover.h declares.
 PROVER_SYMBOLS = ["zkb_pcs_prove_device", "zkb_pcs_prove_host", "zkb_stark_prove_device", "zkb_stark_prove_host", "zkb_stark_prove_multi_device", "zkb_stark_prove_multi_host", "zkb_gkr_prove_device",
-                  "zkb_shard_pcs_begin", "zkb_shard_pcs_extend", "zkb_shard_pcs_set_rows", "zkb_shard_pcs_extend_begin", "zkb_shard_pcs_extend_chunk", "zkb_shard_pcs_subtree", "zkb_shard_pcs_sample", "zkb_shard_pcs_quotients",
+                  "zkb_shard_pcs_begin", "zkb_shard_pcs_extend", "zkb_shard_pcs_set_rows", "zkb_shard_pcs_set_peer_rows", "zkb_shard_pcs_extend_begin", "zkb_shard_pcs_extend_chunk", "zkb_shard_pcs_subtree", "zkb_shard_pcs_sample", "zkb_shard_pcs_quotients",
                   "zkb_shard_pcs_fri_and_decommit", "zkb_shard_pcs_finish", "zkb_shard_pcs_end"]
 # Every symbol include/zkb200_air.h declares.
 AIR_SYMBOLS = ["zkb_air_compile", "zkb_air_analyze", "zkb_air_free", "zkb_air_specialize", "zkb_air_select", "zkb_air_get_stats", "zkb_constraint_quotients", "zkb_constraint_denom_inv"]
@@ -150,6 +150,10 @@ class ShardPcsSession:
     def set_rows(self, rows_ptr):
         """The buffer the row shards are received into (ncols x R words); must outlive the session."""
         self.ctx._check(self.ctx.lib.zkb_shard_pcs_set_rows(self.h, C.c_void_p(rows_ptr)))
+
+    def set_peer_rows(self, peer_ptrs):
+        """Every rank's receive buffer as this process sees it: the chunks' blocks are then copied there by extend_chunk."""
+        self.ctx._check(self.ctx.lib.zkb_shard_pcs_set_peer_rows(self.h, _ptr_array(peer_ptrs)))
 
     def extend_begin(self, col_ptrs, n_chunks):
         """The extend stage by chunks of columns (n_chunks must divide ncl): interpolates; then call extend_chunk(k) for every k."""
@@ -436,8 +440,8 @@ class Context:
     def peer_buffer_close(self, ptr):
         self._check(self.lib.zkb_peer_buffer_close(self.h, C.c_void_p(ptr)))
 
-    def copy_to_peer(self, dst, src, nbytes):
-        self._check(self.lib.zkb_copy_to_peer(self.h, C.c_void_p(dst), C.c_void_p(src), C.c_size_t(nbytes)))
+    def copy_to_peer(self, dst, src, nbytes, lane=0):
+        self._check(self.lib.zkb_copy_to_peer(self.h, C.c_void_p(dst), C.c_void_p(src), C.c_size_t(nbytes), C.c_int(lane)))
 
     def peer_copies_wait(self):
         self._check(self.lib.zkb_peer_copies_wait(self.h))

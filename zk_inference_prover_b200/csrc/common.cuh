@@ -40,6 +40,7 @@ struct zkb_ctx {
     cudaStream_t copy_stream = nullptr;
     cudaEvent_t fences[64] = {nullptr};
     cudaEvent_t copy_gate = nullptr;  // orders the copy stream after allocations made on `stream`
+    cudaStream_t peer_streams[4] = {nullptr, nullptr, nullptr, nullptr};  // device-to-device copies to other GPUs, side by side
     // Optional per-kernel timeline (zkb_profile_*): pairs of events around selected launches.
     bool prof_on = false;
     struct ProfRec { const char* name; cudaEvent_t a, b; };

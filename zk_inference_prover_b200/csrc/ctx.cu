@@ -170,6 +170,8 @@ int zkb_destroy(zkb_ctx* ctx) {
         if (ctx->fences[i]) cudaEventDestroy(ctx->fences[i]);
     if (ctx->copy_gate) cudaEventDestroy(ctx->copy_gate);
     if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
+    for (auto st : ctx->peer_streams)
+        if (st) cudaStreamDestroy(st);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return ZKB_OK;
@@ -378,25 +380,28 @@ int zkb_peer_buffer_close(zkb_ctx* ctx, void* peer_ptr) {
     if (!ctx) return ZKB_EINVAL;
     if (!peer_ptr) return ZKB_OK;
     DeviceGuard g(ctx);
-    if (ctx->copy_stream) ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->copy_stream));
+    for (auto st : ctx->peer_streams)
+        if (st) ZKB_CUDA(ctx, cudaStreamSynchronize(st));
     ZKB_CUDA(ctx, cudaIpcCloseMemHandle(peer_ptr));
     return ZKB_OK;
 }
-int zkb_copy_to_peer(zkb_ctx* ctx, void* dst, const void* src, size_t bytes) {
-    if (!ctx || !dst || !src) return ZKB_EINVAL;
+int zkb_copy_to_peer(zkb_ctx* ctx, void* dst, const void* src, size_t bytes, int lane) {
+    if (!ctx || !dst || !src || lane < 0) return ZKB_EINVAL;
     DeviceGuard g(ctx);
-    if (!ctx->copy_stream) ZKB_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+    cudaStream_t& st = ctx->peer_streams[lane & 3];
+    if (!st) ZKB_CUDA(ctx, cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
     if (!ctx->copy_gate) ZKB_CUDA(ctx, cudaEventCreateWithFlags(&ctx->copy_gate, cudaEventDisableTiming));
     // after everything enqueued on the compute stream so far (the source has just been written there)
     ZKB_CUDA(ctx, cudaEventRecord(ctx->copy_gate, ctx->stream));
-    ZKB_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->copy_gate, 0));
-    if (bytes) ZKB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, ctx->copy_stream));
+    ZKB_CUDA(ctx, cudaStreamWaitEvent(st, ctx->copy_gate, 0));
+    if (bytes) ZKB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, st));
     return ZKB_OK;
 }
 int zkb_peer_copies_wait(zkb_ctx* ctx) {
     if (!ctx) return ZKB_EINVAL;
     DeviceGuard g(ctx);
-    if (ctx->copy_stream) ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->copy_stream));
+    for (auto st : ctx->peer_streams)
+        if (st) ZKB_CUDA(ctx, cudaStreamSynchronize(st));
     return ZKB_OK;
 }
 

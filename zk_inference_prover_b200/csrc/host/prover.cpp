@@ -1310,6 +1310,7 @@ struct ShardSession {
     Device dev;
     int rank, world, log_g, ncols, ncl, n_chunks = 1;
     uint32_t* ext_rows = nullptr;
+    std::vector<uint32_t*> peer_rows;  // every rank's receive buffer as this process sees it (own buffer at [rank]); empty: the caller exchanges
     uint32_t log_n, log_out, log_local;
     size_t N, R;
     PcsConfig config;
@@ -1391,6 +1392,19 @@ int zkb_shard_pcs_set_rows(zkb_shard_pcs* h, uint32_t* d_rows) {
     return ZKB_OK;
 }
 
+int zkb_shard_pcs_set_peer_rows(zkb_shard_pcs* h, uint32_t* const* peer_rows) {
+    if (!h) return ZKB_EINVAL;
+    ShardSession& s = h->s;
+    s.peer_rows.clear();
+    if (!peer_rows) return ZKB_OK;
+    for (int r = 0; r < s.world; r++) {
+        if (!peer_rows[r]) return zk_set_error_public(s.ctx, ZKB_EINVAL, "zkb_shard_pcs_set_peer_rows: null buffer");
+        s.peer_rows.push_back(peer_rows[r]);
+    }
+    s.ext_rows = s.peer_rows[s.rank];
+    return ZKB_OK;
+}
+
 int zkb_shard_pcs_extend_begin(zkb_shard_pcs* h, uint32_t* const* d_cols, int n_chunks) {
     if (!h || !d_cols) return ZKB_EINVAL;
     ShardSession& s = h->s;
@@ -1432,6 +1446,15 @@ int zkb_shard_pcs_extend_chunk(zkb_shard_pcs* h, int k, uint32_t** d_send, uint3
         *d_send = send;
         *d_recv = s.rows.ptr() + (size_t)k * s.world * cc * s.R;
         *words_per_peer = (size_t)cc * s.R;
+        if (!s.peer_rows.empty()) {
+            // block d of the chunk goes to rank d's buffer, into the place of this rank's block there: copy engines, after the
+            // transform just enqueued, four copies side by side; every rank starts with a different peer
+            const size_t words = (size_t)cc * s.R, at = ((size_t)k * s.world + s.rank) * words;
+            for (int j = 0; j < s.world; j++) {
+                const int dst = (s.rank + j) % s.world;
+                s.dev.check(zkb_copy_to_peer(s.ctx, s.peer_rows[dst] + at, send + (size_t)dst * words, words * 4, j));
+            }
+        }
     });
 }
 

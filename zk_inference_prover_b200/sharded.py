@@ -222,6 +222,9 @@ class Exchange:
     def peer_rows(self):
         return self._peer["mine"]
 
+    def peer_ptrs(self):
+        return list(self._peer["ptrs"])
+
     def peer_all_to_all(self, send_ptr, recv_ptr, words_per_peer):
         """Block d of `send` goes to the place of rank d's receive buffer that `recv_ptr` is in mine, block `rank`: enqueued on
         the copy stream after what the compute stream holds so far; peer_finish() makes the data visible."""
@@ -229,7 +232,7 @@ class Exchange:
         off = recv_ptr - p["mine"] + 4 * self.rank * words_per_peer
         for k in range(self.world):
             d = (self.rank + k) % self.world  # start with the local block, then a different peer on every rank
-            p["ctx"].copy_to_peer(p["ptrs"][d] + off, send_ptr + 4 * d * words_per_peer, 4 * words_per_peer)
+            p["ctx"].copy_to_peer(p["ptrs"][d] + off, send_ptr + 4 * d * words_per_peer, 4 * words_per_peer, lane=k)
 
     def peer_finish(self):
         """Waits for this rank's copies, then for everybody's: after it every rank's receive buffer is complete."""
@@ -350,15 +353,14 @@ def sharded_pcs_prove(session, exchange, col_ptrs, timings=None):
     n_chunks = 1
     if hasattr(s, "extend_begin"):
         n_chunks = next((c for c in (4, 2) if s.ncl % c == 0), 1)
-    peer = n_chunks >= 1 and hasattr(s, "set_rows") and hasattr(x, "peer_setup") and x.peer_setup(s.ctx, s.ncols * s.R)
+    peer = hasattr(s, "set_peer_rows") and hasattr(x, "peer_setup") and x.peer_setup(s.ctx, s.ncols * s.R)
     if peer:
         # the ranks write their blocks straight into each other's receive buffers with the copy engines, chunk by chunk
         # under the transform of the next chunk (a collective's copy kernels would wait for the SMs the transform holds)
-        s.set_rows(x.peer_rows())
+        s.set_peer_rows(x.peer_ptrs())
         s.extend_begin(col_ptrs, n_chunks)
         for k in range(n_chunks):
-            send, recv, words_per_peer = s.extend_chunk(k)
-            x.peer_all_to_all(send, recv, words_per_peer)
+            s.extend_chunk(k)  # transform, then the copies of the chunk's blocks into the peers' buffers
         x.peer_finish()
     elif n_chunks > 1:
         s.extend_begin(col_ptrs, n_chunks)
