@@ -14,6 +14,8 @@
 #include <cstdio>
 #include <cstdlib>
 
+#include <cuda_runtime_api.h>
+
 #include "../../../include/zkb200_prover.h"
 #include "../air_program.hpp"
 #include "b200_backend.hpp"
@@ -83,10 +85,33 @@ struct GatherPlan {
     // that size comes from mmap, and its first-touch page faults cost as much as the gather itself.
     uint32_t* block_words = nullptr;
     size_t block_total = 0;
+    // Page-locked once it is large (from 4 MiB): the device-to-host copy of a wide tree's values then runs at the link's
+    // speed instead of through the driver's bounce buffers (50 MB: 4 ms pageable). Small buffers stay ordinary memory:
+    // pinning costs more than it saves there.
+    struct Arena {
+        uint32_t* p = nullptr;
+        size_t words = 0;
+        bool pinned = false;
+        void release() {
+            if (!p) return;
+            if (pinned) cudaFreeHost(p); else free(p);
+            p = nullptr; words = 0;
+        }
+        // Nothing is released when the thread ends: at process exit the CUDA runtime may already be gone.
+    };
     static uint32_t* arena(size_t words) {
-        thread_local std::vector<uint32_t> buf;
-        if (buf.size() < words) buf.resize(words);
-        return buf.data();
+        thread_local Arena a;
+        if (a.words < words) {
+            a.release();
+            size_t want = words + words / 4;
+            void* q = nullptr;
+            if (want * 4 >= ((size_t)4 << 20) && cudaMallocHost(&q, want * 4) == cudaSuccess && q) a.pinned = true;
+            else { (void)cudaGetLastError(); q = malloc(want * 4); a.pinned = false; }
+            if (!q) throw Error(ZKB_ENOMEM, "gather buffer");
+            a.p = (uint32_t*)q;
+            a.words = want;
+        }
+        return a.p;
     }
     size_t add_block(const std::vector<const uint32_t*>& cols, const std::vector<size_t>& rows) {
         Block b;
@@ -695,6 +720,9 @@ struct CommitmentSchemeProver {
         std::vector<const BaseColumn*> flat_cols;
         std::vector<uint32_t> flat_logs;
         std::vector<std::vector<std::pair<PointSample, qm31>>> flat_samples;
+        size_t n_flat = 0;
+        for (auto& t : trees) n_flat += t.evals.size();
+        flat_cols.reserve(n_flat); flat_logs.reserve(n_flat); flat_samples.reserve(n_flat);
         qm31 pow = qm31_one();
         // step of CanonicCoset(lifting_log): the point of index 2^(31 - lifting_log)
         cpoint gen = host_circle_point(1u << (31 - lifting_log));
@@ -703,8 +731,10 @@ struct CommitmentSchemeProver {
                 uint32_t log_size = trees[t].evals[c].log_size();
                 flat_cols.push_back(&trees[t].evals[c]);
                 flat_logs.push_back(log_size);
-                std::vector<std::pair<PointSample, qm31>> v;
+                flat_samples.emplace_back();  // filled in place: a copy per column is an allocation per column
+                std::vector<std::pair<PointSample, qm31>>& v = flat_samples.back();
                 const auto& sc = samples[t][c];
+                v.reserve(sc.size() + (sc.size() == 2 ? 1 : 0));
                 if (!sc.empty()) {
                     if (sc.size() == 2) {
                         cpoint per = gen;
@@ -715,7 +745,6 @@ struct CommitmentSchemeProver {
                     }
                     for (auto& smp : sc) { v.push_back({smp, pow}); pow = pow * random_coeff; }
                 }
-                flat_samples.push_back(v);
             }
         hc.reset(new HostClock("pcs.quot.groups"));
         std::vector<size_t> order(flat_cols.size());
@@ -782,6 +811,7 @@ struct CommitmentSchemeProver {
             samples[t].resize(trees[t].coeffs.size());
             for (size_t c = 0; c < trees[t].coeffs.size(); c++) {
                 uint32_t poly_log = trees[t].evals[c].log_size(), coeff_log = trees[t].coeffs[c].log_size();
+                samples[t][c].reserve(sampled_points[t][c].size());
                 for (size_t k = 0; k < sampled_points[t][c].size(); k++) {
                     CirclePointQ p = sampled_points[t][c][k];
                     samples[t][c].push_back({p, qm31_zero()});
@@ -805,12 +835,16 @@ struct CommitmentSchemeProver {
         }
         hc.reset(new HostClock("pcs.sample.flatten"));
         std::vector<qm31> flat_values;
+        size_t n_values = 0;
+        for (auto& t : samples) for (auto& col : t) n_values += col.size();
+        flat_values.reserve(n_values);
         for (size_t t = 0; t < trees.size(); t++) {
             proof.sampled_values.emplace_back();
-            for (auto& col : samples[t]) {
-                std::vector<qm31> v;
-                for (auto& smp : col) { v.push_back(smp.value); flat_values.push_back(smp.value); }
-                proof.sampled_values[t].push_back(v);
+            proof.sampled_values[t].resize(samples[t].size());
+            for (size_t c = 0; c < samples[t].size(); c++) {
+                std::vector<qm31>& v = proof.sampled_values[t][c];
+                v.reserve(samples[t][c].size());
+                for (auto& smp : samples[t][c]) { v.push_back(smp.value); flat_values.push_back(smp.value); }
             }
         }
         mark(3);
