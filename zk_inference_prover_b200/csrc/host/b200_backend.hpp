@@ -79,7 +79,7 @@ class BaseColumn {
     uint32_t* ptr() const { return ptr_; }
     size_t len() const { return len_; }
     void shrink(size_t len) { if (len < len_) len_ = len; }  // keeps the allocation, forgets the tail
-    uint32_t log_size() const { uint32_t l = 0; while (((size_t)1 << (l + 1)) <= len_) l++; return l; }
+    uint32_t log_size() const { return len_ ? 63u - (uint32_t)__builtin_clzll((unsigned long long)len_) : 0u; }
     std::vector<uint32_t> to_cpu() const {
         std::vector<uint32_t> v(len_);
         if (len_) dev_->check(zkb_d2h(dev_->ctx(), v.data(), ptr_, len_ * 4));
@@ -279,9 +279,13 @@ struct B200Backend {
                                       std::vector<AccumulatedNumerators>& accumulated_numerators_vec) {
         uint32_t log_n = columns[0]->log_size();
         std::vector<const uint32_t*> p;
+        p.reserve(columns.size());
         for (auto c : columns) p.push_back(c->ptr());
         for (auto& batch : sample_batches) {
             std::vector<uint32_t> idx, b, c;
+            idx.reserve(batch.cols_vals_randpows.size());
+            b.reserve(4 * batch.cols_vals_randpows.size());
+            c.reserve(4 * batch.cols_vals_randpows.size());
             qm31 first = zk::qm31_zero();
             for (auto& nd : batch.cols_vals_randpows) {
                 LineCoeffs lc = complex_conjugate_line_coeffs({batch.point, nd.sample_value}, nd.random_coeff);

@@ -54,7 +54,7 @@ struct HostClock {
     }
 };
 
-static inline uint32_t ilog2(size_t n) { uint32_t l = 0; while (((size_t)1 << (l + 1)) <= n) l++; return l; }
+static inline uint32_t ilog2(size_t n) { return n ? 63u - (uint32_t)__builtin_clzll((unsigned long long)n) : 0u; }
 static inline qm31 operator+(qm31 a, qm31 b) { return qm31_add(a, b); }
 static inline qm31 operator-(qm31 a, qm31 b) { return qm31_sub(a, b); }
 static inline qm31 operator*(qm31 a, qm31 b) { return qm31_mul(a, b); }
@@ -871,10 +871,13 @@ struct CommitmentSchemeProver {
             for (auto pos : query_positions) q.push_back(((pos >> (lifting_log - tree_max + 1)) << 1) + (pos & 1));
             std::map<uint32_t, std::vector<size_t>> per_log;
             std::vector<const BaseColumn*> refs;
+            refs.reserve(t.evals.size());
+            uint64_t seen_logs = 0;  // a tree has tens of thousands of columns and a handful of heights
             for (auto& e : t.evals) {
                 refs.push_back(&e);
                 uint32_t log = e.log_size();
-                if (per_log.count(log)) continue;
+                if ((seen_logs >> log) & 1) continue;
+                seen_logs |= (uint64_t)1 << log;
                 std::vector<size_t> positions;
                 for (auto pos : q) positions.push_back(((pos >> (tree_max - log + 1)) << 1) + (pos & 1));
                 per_log[log] = sorted_dedup(positions);
