@@ -35,6 +35,7 @@ struct zkb_ctx {
     // and a pinned landing buffer for the per-item results; both allocated on first use.
     unsigned int* batch_tickets = nullptr;
     uint32_t* h_batch = nullptr;
+    unsigned int batch_round = 0;  // sequence number of the last batched round launched
     cudaEvent_t events[64] = {nullptr};
     // A second stream for host-to-device copies that overlap compute, and the fences between the two.
     cudaStream_t copy_stream = nullptr;

@@ -123,9 +123,26 @@ __device__ __forceinline__ void item_sums(const GkrBatchItem& it, uint32_t bx, q
     }
 }
 
+// The CTA that completes an item reports it: when every item of the launch has reported, the round's sequence number is
+// written after the results. `results` and `flag` are page-locked host memory the device writes directly, so the host sees
+// a round's results a PCIe write after the last CTA ends, without a copy and a stream synchronisation of its own (a round of
+// a small batch is a 5-10 us kernel; the copy and the wake-up cost as much again).
+__device__ __forceinline__ void item_done(unsigned int* done, int n_items, volatile unsigned int* flag, unsigned int round_id) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        if (atomicAdd(done, 1u) == (unsigned int)n_items - 1u) {
+            *done = 0u;  // every item has counted: ready for the next launch
+            __threadfence_system();
+            *flag = round_id;
+        }
+    }
+}
+
 __global__ void __launch_bounds__(256) gkr_batch_round_kernel(const GkrBatchItem* __restrict__ items, int n_items, qm31 r,
                                                               const uint32_t* __restrict__ eq, qm31 lambda, uint32_t* __restrict__ partials,
-                                                              unsigned int* __restrict__ tickets, uint32_t* __restrict__ results) {
+                                                              unsigned int* __restrict__ tickets, uint32_t* __restrict__ results,
+                                                              unsigned int* __restrict__ done, volatile unsigned int* flag, unsigned int round_id) {
     const int idx = find_item(items, n_items, blockIdx.x);
     const GkrBatchItem it = items[idx];
     const uint32_t bx = blockIdx.x - it.first_block;
@@ -143,6 +160,7 @@ __global__ void __launch_bounds__(256) gkr_batch_round_kernel(const GkrBatchItem
                 stqb(res + 16, threadIdx.x, nv);
             }
         }
+        item_done(done, n_items, flag, round_id);
         return;
     }
     qm31 s0 = qm31_zero(), s2 = qm31_zero();
@@ -169,7 +187,10 @@ __global__ void __launch_bounds__(256) gkr_batch_round_kernel(const GkrBatchItem
         if (it.blocks == 1) res[threadIdx.x] = acc;
         else { part[8 * bx + threadIdx.x] = acc; __threadfence(); }
     }
-    if (it.blocks == 1) return;
+    if (it.blocks == 1) {
+        item_done(done, n_items, flag, round_id);
+        return;
+    }
     __syncthreads();
     if (threadIdx.x == 0) is_last = atomicAdd(tickets + idx, 1u) == it.blocks - 1;
     __syncthreads();
@@ -181,6 +202,7 @@ __global__ void __launch_bounds__(256) gkr_batch_round_kernel(const GkrBatchItem
             res[threadIdx.x] = acc;
         }
         if (threadIdx.x == 0) tickets[idx] = 0u;
+        item_done(done, n_items, flag, round_id);
     }
 }
 
@@ -262,12 +284,17 @@ int gkr_batch_round(zkb_ctx* ctx, GkrBatchItem* items, int n_items, const uint32
     DeviceGuard g(ctx);
     uint32_t total = plan_blocks(items, n_items, 0);
     if (!ctx->batch_tickets) {
-        ZKB_CUDA(ctx, cudaMalloc(&ctx->batch_tickets, GKR_BATCH_MAX_ITEMS * sizeof(unsigned int)));
-        ZKB_CUDA(ctx, cudaMemsetAsync(ctx->batch_tickets, 0, GKR_BATCH_MAX_ITEMS * sizeof(unsigned int), ctx->stream));
-        ZKB_CUDA(ctx, cudaMallocHost(&ctx->h_batch, GKR_BATCH_RESULT_WORDS * GKR_BATCH_MAX_ITEMS * 4));
+        // tickets per item, then the launch's count of completed items
+        ZKB_CUDA(ctx, cudaMalloc(&ctx->batch_tickets, (GKR_BATCH_MAX_ITEMS + 1) * sizeof(unsigned int)));
+        ZKB_CUDA(ctx, cudaMemsetAsync(ctx->batch_tickets, 0, (GKR_BATCH_MAX_ITEMS + 1) * sizeof(unsigned int), ctx->stream));
+        // results per item, then the sequence number of the last completed round
+        ZKB_CUDA(ctx, cudaMallocHost(&ctx->h_batch, (GKR_BATCH_RESULT_WORDS * GKR_BATCH_MAX_ITEMS + 1) * 4));
+        ctx->h_batch[GKR_BATCH_RESULT_WORDS * GKR_BATCH_MAX_ITEMS] = 0;
+        ctx->batch_round = 0;
     }
-    // scratch: [results | (unused) | partials]
-    uint32_t* results = ctx->scratch;
+    // The device writes the results straight into the page-locked host buffer (unified addressing: the host pointer is valid
+    // on the device). scratch: [(unused) | partials]
+    uint32_t* results = ctx->h_batch;
     unsigned int* tickets = ctx->batch_tickets;
     uint32_t* partials = ctx->scratch + (size_t)(GKR_BATCH_RESULT_WORDS + 1) * GKR_BATCH_MAX_ITEMS;
     if ((size_t)(GKR_BATCH_RESULT_WORDS + 1) * GKR_BATCH_MAX_ITEMS + 8 * (size_t)total > ctx->scratch_words)
@@ -275,18 +302,29 @@ int gkr_batch_round(zkb_ctx* ctx, GkrBatchItem* items, int n_items, const uint32
     const GkrBatchItem* d_items;
     int rc = stage_items(ctx, items, n_items, &d_items);
     if (rc) return rc;
+    volatile unsigned int* flag = reinterpret_cast<volatile unsigned int*>(ctx->h_batch + GKR_BATCH_RESULT_WORDS * GKR_BATCH_MAX_ITEMS);
+    const unsigned int round_id = ++ctx->batch_round;
     qm31 r{{h_r[0], h_r[1], h_r[2], h_r[3]}}, lam{{h_lambda[0], h_lambda[1], h_lambda[2], h_lambda[3]}};
     {
         ProfScope prof(ctx, "gkr_batch_round_kernel");
-        gkr_batch_round_kernel<<<total, 256, 0, ctx->stream>>>(d_items, n_items, r, eq_evals, lam, partials, tickets, results);
+        gkr_batch_round_kernel<<<total, 256, 0, ctx->stream>>>(d_items, n_items, r, eq_evals, lam, partials, tickets, results,
+                                                               ctx->batch_tickets + GKR_BATCH_MAX_ITEMS, flag, round_id);
     }
     const size_t bytes = (size_t)n_items * GKR_BATCH_RESULT_WORDS * 4;
     cudaError_t e = cudaGetLastError();
-    if (e == cudaSuccess) e = cudaMemcpyAsync(ctx->h_batch, results, bytes, cudaMemcpyDeviceToHost, ctx->stream);  // pinned: one DMA, no bounce buffer
-    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess && !ctx->prof_on) {
+        // wait on the host for the round's sequence number: a bounded spin (about 20 ms), then the stream
+        for (long spin = 0; spin < 20000000L && *flag != round_id; spin++) {
+#if defined(__x86_64__)
+            __builtin_ia32_pause();
+#endif
+        }
+    }
+    if (e == cudaSuccess && *flag != round_id) e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess && *flag != round_id) e = cudaErrorUnknown;  // the launch ended without completing every item
     if (e != cudaSuccess) {
         // a launch that did not run to its end may have left tickets counted up
-        cudaMemsetAsync(ctx->batch_tickets, 0, GKR_BATCH_MAX_ITEMS * sizeof(unsigned int), ctx->stream);
+        cudaMemsetAsync(ctx->batch_tickets, 0, (GKR_BATCH_MAX_ITEMS + 1) * sizeof(unsigned int), ctx->stream);
         return set_error(ctx, ZKB_ECUDA, "gkr batch round: %s", cudaGetErrorString(e));
     }
     memcpy(h_results, ctx->h_batch, bytes);
