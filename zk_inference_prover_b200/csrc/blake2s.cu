@@ -59,9 +59,11 @@ __global__ void __launch_bounds__(256) merkle_layer_kernel(int log_size, const u
 
 // The same node hash for layers of few rows and many columns (a segment's trees hold tens of thousands of columns of
 // 2^8 ... 2^11 rows: a leaf is then a chain of up to 2,000 compressions on a few hundred threads, and what a thread waits for
-// is the memory latency of its next sixteen column words, not the arithmetic). The next block's words are requested before
-// the current block is compressed. (Spreading a compression over four lanes was tried for these layers and is slower: the
-// four column steps of a round are already independent instructions of one thread, and the lane exchanges add latency.)
+// is the memory latency of its next sixteen column words, not the arithmetic). A warp issues in order, so a word whose column
+// pointer has not arrived holds up the compression behind it: the loads therefore run two blocks deep. During the compression
+// of block b the sixteen words of block b + 1 are in flight (their pointers arrived during block b - 1) and so are the sixteen
+// pointers of block b + 2. (Spreading a compression over four lanes was tried for these layers and is slower: the four column
+// steps of a round are already independent instructions of one thread, and the lane exchanges add latency.)
 __global__ void __launch_bounds__(256) merkle_layer_prefetch_kernel(int log_size, const uint32_t* __restrict__ prev,
                                                                     const uint32_t* const* __restrict__ cols, int ncols, int m31_out,
                                                                     uint32_t* __restrict__ out) {
@@ -69,14 +71,20 @@ __global__ void __launch_bounds__(256) merkle_layer_prefetch_kernel(int log_size
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     uint32_t h[8], m[16], nx[16];
+    const uint32_t* pp[16];
     blake2s_init(h);
     const uint32_t total = (prev ? 64u : 0u) + 4u * (uint32_t)ncols;
     uint32_t t = 0;
-    int c = 0;
-    bool have = ncols > 16;  // a full block that is not the last one
-    if (have) {
+    const int full = ncols > 0 ? (ncols - 1) / 16 : 0;  // blocks of sixteen columns that are not the last block
+    if (full > 0) {
 #pragma unroll
-        for (int k = 0; k < 16; k++) nx[k] = cols[k][i];
+        for (int k = 0; k < 16; k++) pp[k] = cols[k];
+#pragma unroll
+        for (int k = 0; k < 16; k++) nx[k] = __ldg(pp[k] + i);
+    }
+    if (full > 1) {
+#pragma unroll
+        for (int k = 0; k < 16; k++) pp[k] = cols[16 + k];
     }
     if (prev) {
         const uint4* p = reinterpret_cast<const uint4*>(prev + 16 * i);
@@ -86,18 +94,22 @@ __global__ void __launch_bounds__(256) merkle_layer_prefetch_kernel(int log_size
         t = 64;
         blake2s_compress(h, m, t, total == 64u);
     }
-    while (have) {
+    for (int b = 0; b < full; b++) {
 #pragma unroll
         for (int k = 0; k < 16; k++) m[k] = nx[k];
-        c += 16;
-        have = ncols - c > 16;
-        if (have) {
+        if (b + 1 < full) {
 #pragma unroll
-            for (int k = 0; k < 16; k++) nx[k] = cols[c + k][i];
+            for (int k = 0; k < 16; k++) nx[k] = __ldg(pp[k] + i);
+        }
+        if (b + 2 < full) {
+            const uint32_t* const* cp = cols + 16 * (b + 2);
+#pragma unroll
+            for (int k = 0; k < 16; k++) pp[k] = cp[k];
         }
         t += 64;
         blake2s_compress(h, m, t, false);
     }
+    const int c = 16 * full;
     if (ncols - c > 0 || total == 0u) {
         int rem = ncols - c;
 #pragma unroll
