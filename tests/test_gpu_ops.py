@@ -125,7 +125,7 @@ def test_bit_reverse_qm31(ctx, log_n):
                                                       (12, 256, False), (3, 4, True),
                                                       # few rows, many columns: the variant that requests the next block's words ahead (merkle_layer_prefetch_kernel)
                                                       (0, 64, False), (2, 65, True), (5, 80, False), (6, 127, True), (7, 128, True),
-                                                      (9, 1000, True), (11, 300, False), (13, 64, True)])
+                                                      (9, 1000, True), (11, 300, False), (13, 64, True), (15, 97, True), (17, 66, False)])
 def test_merkle_layer(ctx, oracle, log_size, ncols, with_prev, m31):
     n = 1 << log_size
     cols = [edge_m31_column(600 + c, n) for c in range(ncols)]

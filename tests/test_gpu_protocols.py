@@ -114,12 +114,25 @@ def test_gkr_proof_matches_oracle(ctx, oracle, spec):
     assert (keep[1].download(shape=(-1, 4)) == insts[0][2]).all()
 
 
+_WIDE_BATCH = [(3, 13)] * 20 + [(3, 11)] * 12 + [(2, 12), (1, 10)]
+_MIXED_BATCH = [(3, 9)] * 6 + [(3, 7)] * 5 + [(1, 8)] * 3 + [(2, 6), (0, 5), (3, 2), (2, 2), (1, 1), (3, 1), (0, 2), (0, 1)]
+
+
 @pytest.mark.parametrize("driver,spec", [("resident", [(2, 10), (3, 7), (0, 8), (1, 3)]), ("resident", [(3, 12), (3, 12), (2, 12)]),
-                                         ("batch", [(2, 11)]), ("batch", [(1, 6), (0, 6)])])
+                                         ("batch", [(2, 11)]), ("batch", [(1, 6), (0, 6)]),
+                                         # the batch driver's three ways through a layer's rounds: the transcript on the host and a
+                                         # round trip per round; on the device with a launch per round; on the device with the small
+                                         # rounds in one launch (the default, which the cases of the test above take)
+                                         ("batch:host", _WIDE_BATCH), ("batch:host", _MIXED_BATCH),
+                                         ("batch:launches", _WIDE_BATCH), ("batch:launches", _MIXED_BATCH), ("batch:launches", [(2, 11)]),
+                                         ("batch", [(0, 15), (1, 14), (2, 15)])])
 def test_gkr_drivers_give_the_same_proof(ctx, oracle, monkeypatch, driver, spec):
     """The library picks the device-resident transcript for one or two instances and the batched rounds otherwise;
     ZKB_GKR_DRIVER forces either, and both must reproduce the oracle's proof for any batch they accept."""
+    driver, _, rounds = driver.partition(":")
     monkeypatch.setenv("ZKB_GKR_DRIVER", driver)
+    if rounds:
+        monkeypatch.setenv("ZKB_GKR_ROUNDS", rounds)
     insts = [_instance(k, lg, 5200 + 10 * i) for i, (k, lg) in enumerate(spec)]
     want = oracle.gkr_prove(insts, 0x5EED0004, verify=True)
     keep, dev = [], []

@@ -320,9 +320,9 @@ int zkb_merkle_layer(zkb_ctx* ctx, int log_size, const uint32_t* prev, const uin
     size_t n = (size_t)1 << log_size;
     unsigned threads = n < 256 ? 32 : 256;
     unsigned blocks = (unsigned)((n + threads - 1) / threads);
-    if (ncols >= 64 && n <= 8192) {
-        // few rows, a long chain of compressions each: the next block's loads are in flight during a compression;
-        // small CTAs so that the few rows spread over all SMs
+    if (ncols >= 64 && n <= ((size_t)1 << 17)) {
+        // few rows (at 2^17 there are still only seven warps per scheduler), a long chain of compressions each: the next
+        // block's loads are in flight during a compression; small CTAs so that the few rows spread over all SMs
         ProfScope prof(ctx, "merkle_layer_prefetch_kernel");
         merkle_layer_prefetch_kernel<<<(unsigned)((n + 31) / 32), 32, 0, ctx->stream>>>(log_size, prev, (const uint32_t* const*)d_cols, ncols, m31_out, out);
         ZKB_LAUNCH_CHECK(ctx);

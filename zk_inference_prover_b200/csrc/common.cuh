@@ -89,6 +89,8 @@ struct DeviceGuard {
 // Copies `n` host-resident device pointers into the staging ring and returns their device
 // address through *out. Ordered on the context's stream.
 int stage_ptrs(zkb_ctx* ctx, const void* const* h_ptrs, int n, void*** out);
+// The same ring for a block of bytes that the device reads as 16-byte vectors: starts on a 16-byte boundary.
+int stage_blob(zkb_ctx* ctx, const void* h_data, size_t bytes, void** out);
 
 // Brackets a kernel launch with events when the timeline is on (see zkb_profile_begin).
 struct ProfScope {

@@ -34,6 +34,21 @@ int stage_ptrs(zkb_ctx* ctx, const void* const* h_ptrs, int n, void*** out) {
     return ZKB_OK;
 }
 
+int stage_blob(zkb_ctx* ctx, const void* h_data, size_t bytes, void** out) {
+    const size_t slots = (bytes + sizeof(void*) - 1) / sizeof(void*);
+    if (slots + 1 > ctx->ring_cap) return set_error(ctx, ZKB_EINVAL, "stage_blob: %zu bytes exceed the staging ring", bytes);
+    size_t pos = (ctx->ring_pos + 1) & ~(size_t)1;  // slots are 8 bytes and the ring's base is aligned: even slots are 16-byte aligned
+    if (pos + slots > ctx->ring_cap) {
+        ZKB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // earlier slots may still be in flight
+        pos = 0;
+    }
+    memcpy(ctx->h_ring + pos, h_data, bytes);
+    ZKB_CUDA(ctx, cudaMemcpyAsync(ctx->d_ring + pos, ctx->h_ring + pos, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    ctx->ring_pos = pos + slots;
+    *out = ctx->d_ring + pos;
+    return ZKB_OK;
+}
+
 // G * 2^b for the generator G of the order-2^31 circle group over M31
 // (nitroo/crates/stwo/src/core/circle.rs:202-205).
 __constant__ cpoint c_gen_pow2[31];

@@ -18,7 +18,7 @@ struct GkrBatchItem {
     uint32_t* den_out;
     unsigned long long n;
     uint32_t kind, mode, first_block, blocks;
-    unsigned long long pad;
+    unsigned long long slot;  // gkr_batch_layer: the oracle the item belongs to (its results go to that oracle's record)
 };
 static_assert(sizeof(GkrBatchItem) == 64, "GkrBatchItem layout");
 
@@ -31,5 +31,42 @@ int gkr_batch_next_layer(zkb_ctx* ctx, GkrBatchItem* items, int n_items);
 // One round for every item: one launch, one copy of n_items * GKR_BATCH_RESULT_WORDS words to h_results, one synchronisation.
 int gkr_batch_round(zkb_ctx* ctx, GkrBatchItem* items, int n_items, const uint32_t h_r[4], const uint32_t* eq_evals, const uint32_t h_lambda[4],
                     uint32_t* h_results);
+
+
+// ---- a layer's whole sum-check enqueued at once (no host round trip per round)
+//
+// What runs in a round depends on the oracles' sizes only, never on the transcript, so the host describes every round of a
+// layer's sum-check up front and the device keeps the transcript between the launches: per round the sums of the oracles that
+// enter (mode 0 items), one single-CTA step that forms the batch's round polynomial from all oracles' sums, mixes it into
+// the channel, draws the challenge and updates every oracle's claim, and the fix of every active oracle (mode 1 / 2 items)
+// with that challenge read from device memory. One copy brings back the round polynomials, the challenges, the masks and the
+// channel (sumcheck.rs:96-176 inside gkr_prover.rs:669-844).
+struct GkrRoundConst {
+    // The basis of the round's polynomials (all active oracles have n_rem variables left, so their round polynomials are
+    // r0 L0 + r1 L1 + r2 L2 over one basis): e0a = eq(0, y) / prod, e2a = eq(2, y) / prod, L[i] the coefficients (low first)
+    // of the basis polynomial of node i; y = the coordinate of the layer's point this round fixes.
+    uint32_t e0a[4], e2a[4], L[3][4][4], y[4];
+    uint32_t n_rem, pad[3];
+};
+static_assert(sizeof(GkrRoundConst) == 256, "GkrRoundConst layout");
+
+struct GkrLayerRound {
+    GkrRoundConst rc;
+    GkrBatchItem* first;  // mode 0 items of the oracles that enter in this round (slot = oracle)
+    int n_first;
+    GkrBatchItem* fix;    // mode 1 / 2 items of every active oracle (slot = oracle)
+    int n_fix;
+};
+
+constexpr int GKR_LAYER_MAX_ROUNDS = 60;
+constexpr size_t GKR_LAYER_OUT_WORDS = 24;  // per round: [0,16) coefficients, [16] length, [20,24) challenge
+
+// n_vars[k]: variables of oracle k's sum-check (it is active in the rounds with n_rem <= n_vars[k]); alpha_pow[k] = alpha^k;
+// claims[k]: its claim before the first round (4 words each). chan: digest (8 words) and n_draws, in and out.
+// h_out: n_rounds x GKR_LAYER_OUT_WORDS; h_res: n_oracles x GKR_BATCH_RESULT_WORDS (the last sums and, for every oracle that
+// had a round, its mask).
+int gkr_batch_layer(zkb_ctx* ctx, int n_oracles, const uint32_t* n_vars, const uint32_t* alpha_pow, const uint32_t* claims,
+                    GkrLayerRound* rounds, int n_rounds, const uint32_t* eq_evals, const uint32_t h_lambda[4], uint32_t chan[9],
+                    uint32_t* h_out, uint32_t* h_res);
 
 }  // namespace zk

@@ -1132,7 +1132,106 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
         std::vector<UniPoly> round_polys;
         std::vector<qm31> assignment;
         const uint32_t half = m31_inv(2);
-        for (size_t round = 0; round < nv; round++) {
+        // By default the whole sum-check of the layer is enqueued at once and the transcript of its rounds stays on the
+        // device (gkr_batch_layer); ZKB_GKR_ROUNDS=host keeps the channel on the host and returns to it every round, and
+        // ZKB_GKR_ROUNDS=launches keeps a launch per round also for the small rounds (both for comparison and tests).
+        const char* rounds_env = getenv("ZKB_GKR_ROUNDS");
+        const bool host_rounds = rounds_env && !strcmp(rounds_env, "host");
+        if (nv > 0 && !host_rounds) {
+            std::unique_ptr<HostClock> hc(new HostClock("gkr.layer.plan"));
+            const size_t K = oracles.size();
+            std::vector<uint32_t> n_vars(K);
+            std::vector<qm31> alpha_pow(K);
+            for (size_t k = 0; k < K; k++) {
+                n_vars[k] = (uint32_t)oracles[k].n_variables();
+                alpha_pow[k] = k ? alpha_pow[k - 1] * sumcheck_alpha : qm31_one();
+            }
+            std::vector<std::vector<zk::GkrBatchItem>> first(nv), fix(nv);
+            std::vector<zk::GkrLayerRound> plan(nv);
+            std::vector<Layer> retired;  // layers replaced by their fixed copies: alive until the enqueued launches have read them
+            for (size_t round = 0; round < nv; round++) {
+                const size_t n_rem = nv - round;
+                const RoundBasis basis(ood_point, n_rem);
+                zk::GkrRoundConst& rc = plan[round].rc;
+                memset(&rc, 0, sizeof(rc));
+                memcpy(rc.e0a, basis.e0a.c, 16);
+                memcpy(rc.e2a, basis.e2a.c, 16);
+                for (int i = 0; i < 3; i++)
+                    for (int t = 0; t < 4; t++) memcpy(rc.L[i][t], basis.L[i][t].c, 16);
+                memcpy(rc.y, ood_point[ood_point.size() - n_rem].c, 16);
+                rc.n_rem = (uint32_t)n_rem;
+                for (size_t k = 0; k < K; k++) {
+                    GkrOracle& o = oracles[k];
+                    if (n_rem != o.n_variables() || o.n_variables() == 0) continue;
+                    Layer& in = o.input_layer;
+                    if (n_vars[k] == n_rem) {  // enters in this round: its first sums
+                        zk::GkrBatchItem it{};
+                        it.num = in.num_ptr();
+                        it.den = in.den.words.ptr();
+                        it.n = in.len();
+                        it.kind = (uint32_t)in.kind;
+                        it.mode = 0;
+                        it.slot = k;
+                        first[round].push_back(it);
+                    }
+                    Layer out;  // Layer::fix_first_variable, gkr_prover.rs:354-381
+                    out.writable = true;
+                    out.kind = in.kind == ZKB_GKR_LOGUP_MULTIPLICITIES ? ZKB_GKR_LOGUP_GENERIC : in.kind;
+                    const uint32_t mode = in.len() >= 8 ? 1 : 2;
+                    if (in.writable && in.kind != ZKB_GKR_LOGUP_MULTIPLICITIES) {
+                        // in place: the result is the first half of the layer (see the host-round path below)
+                        out.den.words = BaseColumn::view(d, in.den.words.ptr(), in.den.words.len() / 2);
+                        if (out.kind == ZKB_GKR_LOGUP_GENERIC) out.num.words = BaseColumn::view(d, in.num.words.ptr(), in.num.words.len() / 2);
+                        zk::GkrBatchItem it = item_of(in, out, mode);
+                        it.slot = k;
+                        fix[round].push_back(it);
+                        in.den.words.shrink(in.den.words.len() / 2);
+                        if (out.kind == ZKB_GKR_LOGUP_GENERIC) in.num.words.shrink(in.num.words.len() / 2);
+                    } else {
+                        out.den = SecureMle(d, in.len() / 2);
+                        if (out.kind == ZKB_GKR_LOGUP_GENERIC) out.num = SecureMle(d, in.len() / 2);
+                        zk::GkrBatchItem it = item_of(in, out, mode);
+                        it.slot = k;
+                        fix[round].push_back(it);
+                        retired.push_back(std::move(in));
+                        in = std::move(out);
+                    }
+                }
+                plan[round].first = first[round].data();
+                plan[round].n_first = (int)first[round].size();
+                plan[round].fix = fix[round].data();
+                plan[round].n_fix = (int)fix[round].size();
+            }
+            hc.reset(new HostClock("gkr.layer.rounds"));
+            uint32_t chan[9];
+            memcpy(chan, ch.digest().data(), 32);
+            chan[8] = ch.n_draws();
+            std::vector<uint32_t> out_words(zk::GKR_LAYER_OUT_WORDS * nv), res(zk::GKR_BATCH_RESULT_WORDS * K);
+            d.check(zk::gkr_batch_layer(d.ctx(), (int)K, n_vars.data(), alpha_pow[0].c, sc_claims[0].c, plan.data(), (int)nv, eq_evals.words.ptr(),
+                                        lambda.c, chan, out_words.data(), res.data()));
+            retired.clear();
+            HashWords digest;
+            memcpy(digest.data(), chan, 32);
+            ch.set_state(digest, chan[8]);
+            for (size_t round = 0; round < nv; round++) {
+                const uint32_t* w = out_words.data() + zk::GKR_LAYER_OUT_WORDS * round;
+                UniPoly rp;
+                for (uint32_t t = 0; t < w[16] && t < 4; t++) rp.c.push_back(qm31{{w[4 * t], w[4 * t + 1], w[4 * t + 2], w[4 * t + 3]}});
+                round_polys.push_back(std::move(rp));
+                assignment.push_back(qm31{{w[20], w[21], w[22], w[23]}});
+            }
+            for (size_t k = 0; k < K; k++) {
+                if (n_vars[k] == 0) continue;  // no round, no mask from a launch: read with the others below
+                GkrOracle& o = oracles[k];
+                const uint32_t* w = res.data() + zk::GKR_BATCH_RESULT_WORDS * k;
+                for (int e = 0; e < 2; e++) {
+                    o.mask_den[e] = qm31{{w[8 + 4 * e], w[9 + 4 * e], w[10 + 4 * e], w[11 + 4 * e]}};
+                    o.mask_num[e] = qm31{{w[16 + 4 * e], w[17 + 4 * e], w[18 + 4 * e], w[19 + 4 * e]}};
+                }
+                o.have_mask = true;
+            }
+        }
+        for (size_t round = 0; host_rounds && round < nv; round++) {
             size_t n_rem = nv - round;
             // the oracles that enter the sum-check in this round have no sums yet: one launch for all of them
             std::unique_ptr<HostClock> hc(new HostClock("gkr.round.first_sums"));
