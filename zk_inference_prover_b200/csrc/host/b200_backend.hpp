@@ -9,9 +9,12 @@
 #pragma once
 #include <array>
 #include <cstdint>
+#include <cstring>
+#include <exception>
 #include <memory>
 #include <stdexcept>
 #include <string>
+#include <thread>
 #include <utility>
 #include <vector>
 
@@ -144,6 +147,28 @@ struct Layer {
         return kind == ZKB_GKR_LOGUP_GENERIC ? num.words.ptr() : kind == ZKB_GKR_LOGUP_MULTIPLICITIES ? num_base.ptr() : nullptr;
     }
 };
+
+// f(begin, end, chunk) over [0, n) on up to four host threads (the caller's among them; chunk = 0 ... 3) when every thread
+// gets at least `min_per_thread` items: the per-column arithmetic of a proof over tens of thousands of columns (powers of
+// the random coefficient, line coefficients) is independent per item. An exception of any chunk is rethrown on the caller's
+// thread after all chunks have ended.
+template <class F>
+inline void parallel_chunks(size_t n, size_t min_per_thread, F f) {
+    size_t nt = min_per_thread ? n / min_per_thread : 1;
+    if (nt > 4) nt = 4;
+    if (nt <= 1) { f((size_t)0, n, (size_t)0); return; }
+    const size_t per = (n + nt - 1) / nt;
+    std::exception_ptr failed[4];
+    auto run = [&](size_t t) {
+        try { f(t * per < n ? t * per : n, (t + 1) * per < n ? (t + 1) * per : n, t); } catch (...) { failed[t] = std::current_exception(); }
+    };
+    std::thread th[3];
+    for (size_t t = 1; t < nt; t++) th[t - 1] = std::thread(run, t);
+    run(0);
+    for (size_t t = 1; t < nt; t++) th[t - 1].join();
+    for (size_t t = 0; t < nt; t++)
+        if (failed[t]) std::rethrow_exception(failed[t]);
+}
 
 // complex_conjugate_line_coeffs (core/constraints.rs:119-134): (alpha a, alpha b, alpha c).
 struct LineCoeffs { qm31 a, b, c; };
@@ -282,18 +307,22 @@ struct B200Backend {
         p.reserve(columns.size());
         for (auto c : columns) p.push_back(c->ptr());
         for (auto& batch : sample_batches) {
-            std::vector<uint32_t> idx, b, c;
-            idx.reserve(batch.cols_vals_randpows.size());
-            b.reserve(4 * batch.cols_vals_randpows.size());
-            c.reserve(4 * batch.cols_vals_randpows.size());
-            qm31 first = zk::qm31_zero();
-            for (auto& nd : batch.cols_vals_randpows) {
-                LineCoeffs lc = complex_conjugate_line_coeffs({batch.point, nd.sample_value}, nd.random_coeff);
-                idx.push_back((uint32_t)nd.column_index);
-                b.insert(b.end(), lc.b.c, lc.b.c + 4);
-                c.insert(c.end(), lc.c.c, lc.c.c + 4);
-                first = zk::qm31_add(first, lc.a);
-            }
+            const size_t ns = batch.cols_vals_randpows.size();
+            std::vector<uint32_t> idx(ns), b(4 * ns), c(4 * ns);
+            qm31 firsts[4] = {zk::qm31_zero(), zk::qm31_zero(), zk::qm31_zero(), zk::qm31_zero()};
+            parallel_chunks(ns, 4096, [&](size_t lo, size_t hi, size_t chunk) {
+                qm31 acc = zk::qm31_zero();
+                for (size_t i = lo; i < hi; i++) {
+                    const auto& nd = batch.cols_vals_randpows[i];
+                    LineCoeffs lc = complex_conjugate_line_coeffs({batch.point, nd.sample_value}, nd.random_coeff);
+                    idx[i] = (uint32_t)nd.column_index;
+                    memcpy(&b[4 * i], lc.b.c, 16);
+                    memcpy(&c[4 * i], lc.c.c, 16);
+                    acc = zk::qm31_add(acc, lc.a);
+                }
+                firsts[chunk] = acc;
+            });
+            qm31 first = zk::qm31_add(zk::qm31_add(firsts[0], firsts[1]), zk::qm31_add(firsts[2], firsts[3]));
             SecureColumnByCoords acc(d, (size_t)1 << log_n);
             auto o = acc.ptrs();
             d.check(zkb_quot_numerators(d.ctx(), p.data(), (int)p.size(), (int)log_n, idx.data(), b.data(), c.data(), (int)idx.size(), o.data()));

@@ -719,31 +719,55 @@ struct CommitmentSchemeProver {
         std::unique_ptr<HostClock> hc(new HostClock("pcs.quot.flatten"));
         std::vector<const BaseColumn*> flat_cols;
         std::vector<uint32_t> flat_logs;
-        std::vector<std::vector<std::pair<PointSample, qm31>>> flat_samples;
         size_t n_flat = 0;
         for (auto& t : trees) n_flat += t.evals.size();
-        flat_cols.reserve(n_flat); flat_logs.reserve(n_flat); flat_samples.reserve(n_flat);
-        qm31 pow = qm31_one();
+        flat_cols.reserve(n_flat); flat_logs.reserve(n_flat);
         // step of CanonicCoset(lifting_log): the point of index 2^(31 - lifting_log)
         cpoint gen = host_circle_point(1u << (31 - lifting_log));
+        // Sample j of the flattened list takes random_coeff^j (quotients.rs:306-345 multiplies as it goes): the powers are
+        // filled in chunks on several threads, each starting from its own power.
+        std::vector<size_t> first_pow;
+        first_pow.reserve(n_flat + 1);
+        size_t n_pows = 0;
+        for (size_t t = 0; t < trees.size(); t++)
+            for (size_t c = 0; c < trees[t].evals.size(); c++) {
+                first_pow.push_back(n_pows);
+                const size_t ns = samples[t][c].size();
+                n_pows += ns + (ns == 2 ? 1 : 0);
+            }
+        first_pow.push_back(n_pows);
+        // column i's samples with their powers: flat_samples[first_pow[i] .. first_pow[i + 1]) (one array: a vector per column
+        // is an allocation per column)
+        std::vector<std::pair<PointSample, qm31>> flat_samples(n_pows);
+        parallel_chunks(n_pows, 8192, [&](size_t lo, size_t hi, size_t) {
+            qm31 p = qm31_one(), sq = random_coeff;
+            for (size_t e = lo; e; e >>= 1) { if (e & 1) p = p * sq; sq = sq * sq; }
+            for (size_t i = lo; i < hi; i++) { flat_samples[i].second = p; p = p * random_coeff; }
+        });
+        // the periodicity sample's point depends on the column's height and the sampled point only: a handful of distinct ones
+        struct Shifted { uint32_t log_size; CirclePointQ from, to; };
+        std::vector<Shifted> shifted;
         for (size_t t = 0; t < trees.size(); t++)
             for (size_t c = 0; c < trees[t].evals.size(); c++) {
                 uint32_t log_size = trees[t].evals[c].log_size();
                 flat_cols.push_back(&trees[t].evals[c]);
                 flat_logs.push_back(log_size);
-                flat_samples.emplace_back();  // filled in place: a copy per column is an allocation per column
-                std::vector<std::pair<PointSample, qm31>>& v = flat_samples.back();
                 const auto& sc = samples[t][c];
-                v.reserve(sc.size() + (sc.size() == 2 ? 1 : 0));
+                std::pair<PointSample, qm31>* v = flat_samples.data() + first_pow[flat_cols.size() - 1];
                 if (!sc.empty()) {
                     if (sc.size() == 2) {
-                        cpoint per = gen;
-                        for (uint32_t k = 0; k < log_size; k++) per = cpoint_add(per, per);
-                        CirclePointQ pq{qm31_from_m31(per.x), qm31_from_m31(per.y)};
-                        v.push_back({PointSample{point_add(sc[1].point, pq), sc[1].value}, pow});
-                        pow = pow * random_coeff;
+                        const Shifted* hit = nullptr;
+                        for (auto& sh : shifted) if (sh.log_size == log_size && sh.from == sc[1].point) { hit = &sh; break; }
+                        if (!hit) {
+                            cpoint per = gen;
+                            for (uint32_t k = 0; k < log_size; k++) per = cpoint_add(per, per);
+                            CirclePointQ pq{qm31_from_m31(per.x), qm31_from_m31(per.y)};
+                            shifted.push_back({log_size, sc[1].point, point_add(sc[1].point, pq)});
+                            hit = &shifted.back();
+                        }
+                        (v++)->first = PointSample{hit->to, sc[1].value};
                     }
-                    for (auto& smp : sc) { v.push_back({smp, pow}); pow = pow * random_coeff; }
+                    for (auto& smp : sc) (v++)->first = smp;
                 }
             }
         hc.reset(new HostClock("pcs.quot.groups"));
@@ -758,7 +782,8 @@ struct CommitmentSchemeProver {
             std::vector<ColumnSampleBatch> batches;
             for (size_t k = i; k < j; k++) {
                 group_cols.push_back(flat_cols[order[k]]);
-                for (auto& sp : flat_samples[order[k]]) {
+                for (size_t q = first_pow[order[k]]; q < first_pow[order[k] + 1]; q++) {
+                    const std::pair<PointSample, qm31>& sp = flat_samples[q];
                     ColumnSampleBatch* b = nullptr;
                     for (auto& x : batches) if (x.point == sp.first.point) { b = &x; break; }
                     if (!b) { batches.push_back({sp.first.point, {}}); b = &batches.back(); }
