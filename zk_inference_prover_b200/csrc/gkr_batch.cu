@@ -361,6 +361,13 @@ __device__ void transcript_step(const GkrLayerDev& s, int round) {
     }
 }
 
+// The transcript step as the tail of a launch: every other CTA has ended, so the next launch of the layer may be scheduled
+// now and run up to its wait while this one CTA finishes the round.
+__device__ __forceinline__ void transcript_tail(const GkrLayerDev& s, int round) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    transcript_step(s, round);
+}
+
 // The CTA that completes an item reports it. A single round (flag given): when every item of the launch has reported, the
 // round's sequence number is written after the results. `results` and `flag` are then page-locked host memory the device
 // writes directly, so the host sees a round's results a PCIe write after the last CTA ends, without a copy and a stream
@@ -399,6 +406,10 @@ __global__ void __launch_bounds__(256) gkr_batch_round_kernel(const GkrBatchItem
     const int idx = find_item(items, n_items, blockIdx.x);
     const GkrBatchItem it = items[idx];
     const uint32_t bx = blockIdx.x - it.first_block;
+    // A launch of a layer enqueued at once may start while the launch before it is still in its transcript step (programmatic
+    // dependent launch): its CTAs get here, with their items looked up, and wait for that grid to end before they touch
+    // anything it writes. (No effect on a launch made without the attribute.)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (d_r) r = ldqb(d_r, 0);
     uint32_t* res = results + (size_t)GKR_BATCH_RESULT_WORDS * (by_slot ? (size_t)it.slot : (size_t)idx);
     if (it.mode == 2) {
@@ -414,7 +425,7 @@ __global__ void __launch_bounds__(256) gkr_batch_round_kernel(const GkrBatchItem
                 stqb(res + 16, threadIdx.x, nv);
             }
         }
-        if (item_done(done, n_items, flag, round_id) && tr_round >= 0) transcript_step(layer, tr_round);
+        if (item_done(done, n_items, flag, round_id) && tr_round >= 0) transcript_tail(layer, tr_round);
         return;
     }
     qm31 s0 = qm31_zero(), s2 = qm31_zero();
@@ -445,7 +456,7 @@ __global__ void __launch_bounds__(256) gkr_batch_round_kernel(const GkrBatchItem
         else { part[8 * bx + threadIdx.x] = acc; __threadfence(); }
     }
     if (it.blocks == 1) {
-        if (item_done(done, n_items, flag, round_id) && tr_round >= 0) transcript_step(layer, tr_round);
+        if (item_done(done, n_items, flag, round_id) && tr_round >= 0) transcript_tail(layer, tr_round);
         return;
     }
     __syncthreads();
@@ -459,7 +470,7 @@ __global__ void __launch_bounds__(256) gkr_batch_round_kernel(const GkrBatchItem
             res[threadIdx.x] = acc;
         }
         if (threadIdx.x == 0) tickets[idx] = 0u;
-        if (item_done(done, n_items, flag, round_id) && tr_round >= 0) transcript_step(layer, tr_round);
+        if (item_done(done, n_items, flag, round_id) && tr_round >= 0) transcript_tail(layer, tr_round);
     }
 }
 
@@ -473,6 +484,7 @@ __global__ void __launch_bounds__(256) gkr_batch_round_kernel(const GkrBatchItem
 __global__ void __launch_bounds__(GKR_TAIL_THREADS) gkr_batch_tail_kernel(const GkrBatchItem* __restrict__ items_base, const uint4* __restrict__ tables,
                                                                           int n_tables, const uint32_t* __restrict__ eq, qm31 lambda, GkrLayerDev layer,
                                                                           uint32_t* __restrict__ results) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");  // see gkr_batch_round_kernel
     for (int t = 0; t < n_tables; t++) {
         const uint4 tb = tables[t];
         const GkrBatchItem* items = items_base + tb.x;
@@ -768,21 +780,36 @@ int gkr_batch_layer(zkb_ctx* ctx, int n_oracles, const uint32_t* n_vars, const u
     uint32_t* partials = ctx->scratch + (size_t)(GKR_BATCH_RESULT_WORDS + 1) * GKR_BATCH_MAX_ITEMS;
     const qm31 zero = qm31_zero(), lam{{h_lambda[0], h_lambda[1], h_lambda[2], h_lambda[3]}};
     cudaError_t e = cudaSuccess;
+    // Each launch but the first is a programmatic dependent of the one before it (ZKB_GKR_PDL=0: plain stream order).
+    const char* pdl_env = getenv("ZKB_GKR_PDL");
+    const bool pdl = !(pdl_env && pdl_env[0] == '0') && !ctx->prof_on;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = ctx->stream;
+    cfg.attrs = attr;
+    bool launched = false;
     for (int j = 0; j < j_tail && j <= n_rounds && e == cudaSuccess; j++) {
         if (tables[j].empty()) continue;
         ProfScope prof(ctx, totals[j] <= 8 ? "gkr_batch_round_kernel(<=8 CTAs)" : totals[j] <= 128 ? "gkr_batch_round_kernel(<=128 CTAs)"
                                  : totals[j] <= 2048 ? "gkr_batch_round_kernel(<=2048 CTAs)" : "gkr_batch_round_kernel(>2048 CTAs)");
-        gkr_batch_round_kernel<<<totals[j], 256, 0, ctx->stream>>>(reinterpret_cast<const GkrBatchItem*>(d_blob + table_at[j]), (int)tables[j].size(), zero,
-                                                                   s.challenge, 1, eq_evals, lam, partials, ctx->batch_tickets, ctx->scratch,
-                                                                   ctx->batch_tickets + GKR_BATCH_MAX_ITEMS, nullptr, 0u, s, j < n_rounds ? j : -1);
-        e = cudaGetLastError();
+        cfg.gridDim = dim3(totals[j]);
+        cfg.blockDim = dim3(256);
+        cfg.numAttrs = pdl && launched ? 1 : 0;  // the first launch follows a copy, not a kernel of this chain
+        e = cudaLaunchKernelEx(&cfg, gkr_batch_round_kernel, reinterpret_cast<const GkrBatchItem*>(d_blob + table_at[j]), (int)tables[j].size(), zero,
+                               (const uint32_t*)s.challenge, 1, eq_evals, lam, partials, ctx->batch_tickets, ctx->scratch,
+                               ctx->batch_tickets + GKR_BATCH_MAX_ITEMS, (volatile unsigned int*)nullptr, 0u, s, j < n_rounds ? j : -1);
+        launched = true;
     }
     if (n_tail_tables && e == cudaSuccess) {
         ProfScope prof(ctx, "gkr_batch_tail_kernel");
-        gkr_batch_tail_kernel<<<1, GKR_TAIL_THREADS, 0, ctx->stream>>>(reinterpret_cast<const GkrBatchItem*>(d_blob + o_items),
-                                                                      reinterpret_cast<const uint4*>(d_blob + o_tables), (int)n_tail_tables, eq_evals, lam, s,
-                                                                      ctx->scratch);
-        e = cudaGetLastError();
+        cfg.gridDim = dim3(1);
+        cfg.blockDim = dim3(GKR_TAIL_THREADS);
+        cfg.numAttrs = pdl && launched ? 1 : 0;
+        e = cudaLaunchKernelEx(&cfg, gkr_batch_tail_kernel, reinterpret_cast<const GkrBatchItem*>(d_blob + o_items),
+                               reinterpret_cast<const uint4*>(d_blob + o_tables), (int)n_tail_tables, eq_evals, lam, s, ctx->scratch);
     }
     uint32_t* h = ctx->h_batch;
     if (e == cudaSuccess) e = cudaMemcpyAsync(h, ctx->scratch, K * GKR_BATCH_RESULT_WORDS * 4, cudaMemcpyDeviceToHost, ctx->stream);
