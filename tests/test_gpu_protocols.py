@@ -145,6 +145,32 @@ def test_gkr_drivers_give_the_same_proof(ctx, oracle, monkeypatch, driver, spec)
     assert len(got) == len(want) and (got == want).all()
 
 
+@pytest.mark.parametrize("rounds", ["", "launches", "host"])
+@pytest.mark.parametrize("spec", [[(1, 6)] * 3, [(1, 4), (0, 6), (1, 5), (0, 3)], [(1, 3)] * 20 + [(0, 7)], [(1, 12), (1, 12), (0, 12)]])
+def test_gkr_batch_with_round_polynomials_of_low_degree(ctx, oracle, monkeypatch, rounds, spec):
+    """Constant layers (numerators 0, denominators 1; a grand product of ones) give round polynomials whose leading coefficients
+    vanish. The batch's combination then keeps the length of its longest trimmed term (lookups/utils.rs:165-170 under
+    sumcheck.rs:139-149), which the proof shows as shorter polynomials: the three ways through a layer's rounds must all
+    reproduce the oracle's words."""
+    if rounds:
+        monkeypatch.setenv("ZKB_GKR_ROUNDS", rounds)
+    insts = []
+    for kind, lg in spec:
+        n = 1 << lg
+        den = np.zeros((n, 4), np.uint32)
+        den[:, 0] = 1
+        insts.append((kind, np.zeros((n, 4), np.uint32) if kind == 1 else None, den))
+    want = oracle.gkr_prove(insts, 0x5EED0014, verify=True)
+    keep, dev = [], []
+    for kind, num, den in insts:
+        nb = ctx.upload(num) if num is not None else None
+        db = ctx.upload(den)
+        keep += [nb, db]
+        dev.append((kind, nb.ptr if nb else 0, db.ptr, den.shape[0]))
+    got = ctx.gkr_prove_device(dev, 0x5EED0014)
+    assert len(got) == len(want) and (got == want).all()
+
+
 def test_two_contexts_on_two_threads_prove_side_by_side(zkb, oracle):
     """Several contexts may be used from different host threads at once (one thread per context): two threads, each with
     its own context, prove a PCS opening over many short columns and a GKR batch of 20 instances three times over while the
