@@ -28,7 +28,8 @@ constexpr size_t GKR_BATCH_RESULT_WORDS = 24;
 
 // next_layer of every item, one launch, stream-ordered.
 int gkr_batch_next_layer(zkb_ctx* ctx, GkrBatchItem* items, int n_items);
-// One round for every item: one launch, one copy of n_items * GKR_BATCH_RESULT_WORDS words to h_results, one synchronisation.
+// One round for every item with the transcript on the host: one launch that writes n_items * GKR_BATCH_RESULT_WORDS words and
+// a completion word into page-locked host memory; returns when the host has seen the completion word (h_results filled).
 int gkr_batch_round(zkb_ctx* ctx, GkrBatchItem* items, int n_items, const uint32_t h_r[4], const uint32_t* eq_evals, const uint32_t h_lambda[4],
                     uint32_t* h_results);
 
@@ -36,10 +37,12 @@ int gkr_batch_round(zkb_ctx* ctx, GkrBatchItem* items, int n_items, const uint32
 // ---- a layer's whole sum-check enqueued at once (no host round trip per round)
 //
 // What runs in a round depends on the oracles' sizes only, never on the transcript, so the host describes every round of a
-// layer's sum-check up front and the device keeps the transcript between the launches: per round the sums of the oracles that
-// enter (mode 0 items), one single-CTA step that forms the batch's round polynomial from all oracles' sums, mixes it into
-// the channel, draws the challenge and updates every oracle's claim, and the fix of every active oracle (mode 1 / 2 items)
-// with that challenge read from device memory. One copy brings back the round polynomials, the challenges, the masks and the
+// layer's sum-check up front and the device keeps the transcript between the launches. Launch j (0 <= j <= rounds) carries the
+// fixes of round j - 1 (mode 1 / 2 items, the challenge read from device memory) and the first sums of the oracles that
+// enter in round j (mode 0 items); the CTA that completes the launch goes on with the transcript step of round j: the
+// batch's round polynomial from all oracles' sums, mixed into the channel, the challenge drawn, every oracle's claim and
+// correction updated. The launches of the small rounds at the end of the layer are replaced by one single-CTA launch that
+// runs the same tables one after the other. One copy brings back the round polynomials, the challenges, the masks and the
 // channel (sumcheck.rs:96-176 inside gkr_prover.rs:669-844).
 struct GkrRoundConst {
     // The basis of the round's polynomials (all active oracles have n_rem variables left, so their round polynomials are
