@@ -187,3 +187,32 @@ def test_sharded_proof_driver_moves_every_block_to_its_owner(tmp_path, world, nc
     for r in range(world):
         assert (np.load(tmp_path / f"rows{r}.npy") == table[:, r * R:(r + 1) * R].astype(np.uint32)).all()  # the all-to-all
         assert (np.load(tmp_path / f"words{r}.npy") == want).all()
+
+
+def _varlen_worker(rank, world, port, lengths, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from zk_inference_prover_b200.sharded import Exchange
+
+    x = Exchange(None, torch.device("cpu"))
+    mine = np.arange(lengths[rank], dtype=np.uint32) * np.uint32(3) + np.uint32(7 * rank)
+    parts = x.all_gather_varlen(mine)
+    np.save(os.path.join(out_dir, f"parts{rank}.npy"), np.concatenate([np.array([len(p) for p in parts], np.uint32)] + list(parts)))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("lengths", [(5, 0), (3, 40000), (16383, 16383), (16384, 1)])
+def test_all_gather_varlen_one_round_or_two(tmp_path, lengths):
+    """Arrays that fit the first round (length and head in one block) arrive with one collective, longer ones with a second
+    one sized by the longest: both ways must return every rank's array on every rank, empty ones included."""
+    world = len(lengths)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    mp.spawn(_varlen_worker, args=(world, port, lengths, str(tmp_path)), nprocs=world, join=True)
+    want = np.concatenate([np.array(lengths, np.uint32)] + [np.arange(n, dtype=np.uint32) * np.uint32(3) + np.uint32(7 * r) for r, n in enumerate(lengths)])
+    for r in range(world):
+        assert (np.load(tmp_path / f"parts{r}.npy") == want).all()

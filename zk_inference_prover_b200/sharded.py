@@ -284,22 +284,50 @@ class Exchange:
         dist.all_gather(parts, mine, group=self.group)
         self.mem.write(dst_ptr, torch.cat(parts).numpy().view("uint32"))
 
+    def _gather_buffers(self, words):
+        """Page-locked host and device buffers for all_gather_host under nccl, kept between calls."""
+        if getattr(self, "_gb", None) is None or self._gb[0] < words:
+            cap = max(1024, 1 << (int(words) - 1).bit_length())
+            self._gb = (cap, torch.empty(cap, dtype=torch.int32).pin_memory(), torch.empty(self.world * cap, dtype=torch.int32).pin_memory(),
+                        torch.empty(cap, dtype=torch.int32, device=self.device), torch.empty(self.world * cap, dtype=torch.int32, device=self.device))
+        return self._gb
+
     def all_gather_host(self, arr):
         """Equal-sized host arrays, concatenated in rank order."""
         import numpy as np
 
         mine = torch.from_numpy(np.ascontiguousarray(arr).view("int32").reshape(-1))
         if self.nccl:
-            mine = mine.to(self.device)
+            # one collective on one tensor, staged through page-locked memory on both sides
+            n = mine.numel()
+            _, send_h, recv_h, send_d, recv_d = self._gather_buffers(n)
+            send_h[:n].copy_(mine)
+            send_d[:n].copy_(send_h[:n], non_blocking=True)
+            dist.all_gather_into_tensor(recv_d[: self.world * n], send_d[:n], group=self.group)
+            recv_h[: self.world * n].copy_(recv_d[: self.world * n], non_blocking=True)
+            torch.cuda.current_stream(self.device).synchronize()
+            return recv_h[: self.world * n].numpy().view("uint32").copy()
         parts = [torch.empty_like(mine) for _ in range(self.world)]
         dist.all_gather(parts, mine, group=self.group)
-        return torch.cat(parts).cpu().numpy().view("uint32")
+        return torch.cat(parts).numpy().view("uint32")
+
+    VARLEN_HEAD = 1 << 14  # words of the first round of all_gather_varlen: the length, then the array's head
 
     def all_gather_varlen(self, arr):
-        """Host arrays of different lengths -> list in rank order (on every rank)."""
+        """Host arrays of different lengths -> list in rank order (on every rank). One collective when every array fits
+        the first round (its length travels in the same block), a second one sized by the longest array otherwise: every
+        rank sees every length after the first round, so all take the same way."""
         import numpy as np
 
-        lens = self.all_gather_host(np.array([len(arr)], np.uint32))
+        cap = self.VARLEN_HEAD
+        head = np.zeros(cap, np.uint32)
+        head[0] = len(arr)
+        k = min(len(arr), cap - 1)
+        head[1 : 1 + k] = arr[:k]
+        flat = self.all_gather_host(head).reshape(self.world, cap)
+        lens = flat[:, 0]
+        if int(lens.max()) <= cap - 1:
+            return [flat[r, 1 : 1 + int(lens[r])].copy() for r in range(self.world)]
         cap = int(lens.max())
         pad = np.zeros(cap, np.uint32)
         pad[: len(arr)] = arr
