@@ -212,3 +212,27 @@ def test_grind_and_verify(oracle):
     nonce = ch.grind(10)
     assert ch.verify_pow_nonce(10, nonce)
     assert all(not ch.verify_pow_nonce(10, k) for k in range(nonce))
+
+
+@pytest.mark.parametrize("spec", [[(1, 6)] * 3, [(1, 4), (0, 6), (1, 5), (0, 3)]])
+def test_gkr_constant_layers_give_short_round_polynomials(oracle, spec):
+    """Numerators 0 over denominators 1 and grand products of ones: every round polynomial loses its leading coefficients,
+    and the batch's combination keeps the length of its longest trimmed term (lookups/utils.rs:165-170 under
+    sumcheck.rs:139-149). The restated verifier (run inside gkr_prove) must accept the shorter proof, and the proof must be
+    shorter than the one of random layers of the same shapes."""
+    def instances(constant):
+        out = []
+        for i, (kind, lg) in enumerate(spec):
+            n = 1 << lg
+            if constant:
+                den = np.zeros((n, 4), np.uint32)
+                den[:, 0] = 1
+                num = np.zeros((n, 4), np.uint32) if kind == 1 else None
+            else:
+                den = qm31_array(900 + i, n, nonzero=True)
+                num = qm31_array(950 + i, n) if kind == 1 else None
+            out.append((kind, num, den))
+        return out
+    short = oracle.gkr_prove(instances(True), 0x5EED0014, verify=True)
+    full = oracle.gkr_prove(instances(False), 0x5EED0014, verify=True)
+    assert 0 < len(short) < len(full)
