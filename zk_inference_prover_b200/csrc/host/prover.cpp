@@ -4,6 +4,7 @@
 // device through the operator ABI; the host runs the Fiat-Shamir channel, the query bookkeeping
 // and scalar QM31 arithmetic on a handful of values per round.
 #include <algorithm>
+#include <iterator>
 #include <chrono>
 #include <map>
 #include <memory>
@@ -250,12 +251,23 @@ struct MerkleProver {
         std::vector<size_t> last;
         for (uint32_t log = (uint32_t)layers.size(); log-- > 0;) {
             bool has_prev = (size_t)log + 1 < layers.size();
-            std::set<size_t> prev_set(last.begin(), last.end()), merged, col_queries;
-            for (auto q : last) merged.insert(q / 2);
+            // Sorted vectors, not sets: `last` (the nodes of the layer below) is ascending, so are its halves and the layer's
+            // own queries; a FRI proof plans some twenty trees of some twenty layers each.
+            const std::vector<size_t>& prev_nodes = last;
+            std::vector<size_t> parents, col_queries, merged_nodes;
+            parents.reserve(last.size());
+            for (auto q : last)
+                if (parents.empty() || parents.back() != q / 2) parents.push_back(q / 2);
             auto it = queries_per_log_size.find(log);
-            if (it != queries_per_log_size.end()) col_queries.insert(it->second.begin(), it->second.end());
-            merged.insert(col_queries.begin(), col_queries.end());
-            std::vector<size_t> merged_nodes(merged.begin(), merged.end());
+            if (it != queries_per_log_size.end()) {
+                col_queries = it->second;
+                if (!std::is_sorted(col_queries.begin(), col_queries.end())) std::sort(col_queries.begin(), col_queries.end());
+                col_queries.erase(std::unique(col_queries.begin(), col_queries.end()), col_queries.end());
+            }
+            merged_nodes.reserve(parents.size() + col_queries.size());
+            std::set_union(parents.begin(), parents.end(), col_queries.begin(), col_queries.end(), std::back_inserter(merged_nodes));
+            auto in_prev = [&](size_t node) { return std::binary_search(prev_nodes.begin(), prev_nodes.end(), node); };
+            auto is_query = [&](size_t node) { return std::binary_search(col_queries.begin(), col_queries.end(), node); };
             std::vector<const uint32_t*> layer_ptrs_own;
             if (!recorded)
                 while (pos < sorted.size() && sorted[pos]->log_size() == log) layer_ptrs_own.push_back(sorted[pos++]->ptr());
@@ -263,10 +275,10 @@ struct MerkleProver {
             std::vector<size_t> witness_children, queried_nodes, witness_nodes;
             for (size_t node : merged_nodes) {
                 if (has_prev) {
-                    if (!prev_set.count(2 * node)) witness_children.push_back(2 * node);
-                    if (!prev_set.count(2 * node + 1)) witness_children.push_back(2 * node + 1);
+                    if (!in_prev(2 * node)) witness_children.push_back(2 * node);
+                    if (!in_prev(2 * node + 1)) witness_children.push_back(2 * node + 1);
                 }
-                (col_queries.count(node) ? queried_nodes : witness_nodes).push_back(node);
+                (is_query(node) ? queried_nodes : witness_nodes).push_back(node);
             }
             for (size_t child : witness_children) pm.hash_slots.push_back(plan.add_hash(layers[log + 1].ptr() + 8 * child));
             if (hashes_per_layer) hashes_per_layer->push_back(witness_children.size());
@@ -888,7 +900,9 @@ struct CommitmentSchemeProver {
         hc.reset(new HostClock("pcs.decommit.plan"));
         std::vector<size_t> query_positions;
         GatherPlan plan;
+        std::unique_ptr<HostClock> hc2(new HostClock("pcs.decommit.plan.fri"));
         auto fri_pending = fri.plan_decommit(plan, d, ch, query_positions);
+        hc2.reset(new HostClock("pcs.decommit.plan.trees"));
         std::vector<PendingMerkle> tree_pending;
         for (auto& t : trees) {  // STWO/core/pcs/utils.rs:200-218, then pcs/mod.rs:575-630
             uint32_t tree_max = t.max_log();
@@ -909,6 +923,7 @@ struct CommitmentSchemeProver {
             }
             tree_pending.push_back(t.commitment.plan_decommit(plan, per_log, refs));
         }
+        hc2.reset();
         hc.reset(new HostClock("pcs.decommit.gather"));
         plan.execute(d);
         hc.reset(new HostClock("pcs.decommit.finish"));
