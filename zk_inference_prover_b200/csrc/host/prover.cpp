@@ -783,9 +783,14 @@ struct CommitmentSchemeProver {
                 }
             }
         hc.reset(new HostClock("pcs.quot.groups"));
+        // the columns by ascending size, in their own order within a size: a counting sort (sizes are below 2^32)
         std::vector<size_t> order(flat_cols.size());
-        std::iota(order.begin(), order.end(), 0);
-        std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return flat_logs[a] < flat_logs[b]; });
+        {
+            size_t first_of[34] = {0};
+            for (uint32_t lg : flat_logs) first_of[std::min<uint32_t>(lg, 32) + 1]++;
+            for (int k = 1; k < 34; k++) first_of[k] += first_of[k - 1];
+            for (size_t i = 0; i < flat_logs.size(); i++) order[first_of[std::min<uint32_t>(flat_logs[i], 32)]++] = i;
+        }
         std::vector<AccumulatedNumerators> accs;
         for (size_t i = 0; i < order.size();) {
             size_t j = i;
