@@ -484,7 +484,7 @@ def run_ours(args, rank, world, local_rank):
 def extra_legs(args, z, ctx, dist, rank, world, local_rank, words_single, single_ms, h_addr, d_work, single_commit_ms=0.0):
     """Legs beside the headline, on the same GPUs in the same run, so that the driver's one line per N also carries: what the
     host can deliver to the ranks at once (reads the end-to-end scaling against), ONE proof sharded over all ranks (strong
-    scaling of the proof itself; its words must equal the single-GPU proof), and BASELINE.json's first metric, the proof
+    scaling of the proof itself; its words must equal the single-GPU proof), and the reference's first headline metric, the proof
     time of a composed decode segment (N = 1) or of a whole decode step dealt over the ranks (N > 1), as operator-trace
     replays. Every rank runs every leg; rank 0 keeps the results."""
     import torch
@@ -583,7 +583,7 @@ def extra_legs(args, z, ctx, dist, rank, world, local_rank, words_single, single
         if world == 1:
             sr = shapes[names[0]]
             out["segment_replay"] = {"segment": names[0], "ms_per_segment": ms, "cells": sr.cells, "cells_per_s": sr.cells / (ms * 1e-3),
-                                     "what": "BASELINE.json's first metric as an operator-trace replay: the trees and GKR batches of one "
+                                     "what": "the reference's first headline metric (proof ms per decode segment) as an operator-trace replay: the trees and GKR batches of one "
                                              "layer segment of the config-4 model on random data (timing only; the shape comes from the "
                                              "reference's cell-exact cost model)"}
         else:
