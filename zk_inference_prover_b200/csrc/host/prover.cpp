@@ -1181,7 +1181,15 @@ static std::vector<uint32_t> gkr_prove_batch(const Device& d, Channel& ch, std::
         // device (gkr_batch_layer); ZKB_GKR_ROUNDS=host keeps the channel on the host and returns to it every round, and
         // ZKB_GKR_ROUNDS=launches keeps a launch per round also for the small rounds (both for comparison and tests).
         const char* rounds_env = getenv("ZKB_GKR_ROUNDS");
-        const bool host_rounds = rounds_env && !strcmp(rounds_env, "host");
+        bool host_rounds = rounds_env && !strcmp(rounds_env, "host");
+        {
+            // The layer's description is staged as one block (an item per oracle and active round, 64 bytes each, and some
+            // 52 bytes per oracle): a batch of thousands of tall instances would not fit the staging ring (2 MiB) and takes
+            // the round-by-round path, which stages one round's items at a time.
+            size_t items = 0;
+            for (auto& o : oracles) items += o.n_variables() + 1;
+            if (64 * items + 64 * oracles.size() + 256 * nv + 4096 > ((size_t)1 << 20)) host_rounds = true;
+        }
         if (nv > 0 && !host_rounds) {
             std::unique_ptr<HostClock> hc(new HostClock("gkr.layer.plan"));
             const size_t K = oracles.size();
